@@ -1,0 +1,322 @@
+// bf16 GEMM on the 5th-generation tensor cores:  C[M,N] (+)= A[M,K] * B[N,K]^T.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0  : TMA producer   (cp.async.bulk.tensor -> 128B-swizzled smem ring, 4 stages)
+//   warp 1  : MMA issuer     (one elected thread issues tcgen05.mma 128x256x16; owns TMEM)
+//   warps 2-5: epilogue      (tcgen05.ld TMEM -> registers -> bf16/fp32 global stores)
+// The fp32 accumulator lives in tensor memory and is double buffered (2 x 256 columns),
+// so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Each operand may be "K-major" (reduction dim contiguous: activations x[M,K], weights
+// W[N,K]) or "MN-major" (reduction dim strided: the transposed uses in dgrad / wgrad),
+// selected by template flags; the smem descriptors and the instruction descriptor carry
+// the layout, so no operand is ever transposed in memory.
+//
+// Covers the Linear call sites of the reference model (attention q/k/v/o projections,
+// SwiGLU gate/up/down, output head: kempnerforge/model/attention.py:150-152,236,
+// kempnerforge/model/mlp.py:26, kempnerforge/model/embedding.py:51) and their backward.
+#include "common.cuh"
+
+namespace kf {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;  // tile rasterisation: 8 row-blocks share each column-block sweep
+constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct TileCoord {
+  int m, n;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_blocks) {
+  const int per_group = GROUP_M * n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int r = t - g * per_group;
+  return {first_m + r % rows, r / rows};
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&acc)[32], int valid_cols,
+                                            bool accumulate);
+
+template <>
+__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&acc)[32],
+                                                           int valid_cols, bool accumulate) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (v * 8 >= valid_cols) break;
+    uint4* p = reinterpret_cast<uint4*>(dst + v * 8);
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
+    if (accumulate) {
+      uint4 old = *p;
+      float2 a = unpack_bf16(old.x), b = unpack_bf16(old.y), c = unpack_bf16(old.z), d = unpack_bf16(old.w);
+      f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+      f[4] += c.x; f[5] += c.y; f[6] += d.x; f[7] += d.y;
+    }
+    uint4 out;
+    out.x = pack_bf16(f[0], f[1]);
+    out.y = pack_bf16(f[2], f[3]);
+    out.z = pack_bf16(f[4], f[5]);
+    out.w = pack_bf16(f[6], f[7]);
+    *p = out;
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t (&acc)[32], int valid_cols,
+                                                   bool accumulate) {
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    if (v * 4 >= valid_cols) break;
+    float4* p = reinterpret_cast<float4*>(dst + v * 4);
+    float4 o = make_float4(__uint_as_float(acc[v * 4]), __uint_as_float(acc[v * 4 + 1]),
+                           __uint_as_float(acc[v * 4 + 2]), __uint_as_float(acc[v * 4 + 3]));
+    if (accumulate) {
+      float4 old = *p;
+      o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+    }
+    *p = o;
+  }
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+kf_gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     OutT* __restrict__ C, int M, int N, int K, int ldc, int accumulate, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128B swizzle atoms are 1024 B; tile bases must be 1024-aligned
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barrier layout (8 B each): full[S], empty[S], tmem_full[2], tmem_empty[2], drain, then tmem ptr
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (M + BM - 1) / BM;
+  const int n_blocks = (N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+        const int m0 = tc.m * BM, n0 = tc.n * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &map_a, full_bar(s), k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(a_dst + c * (64 * BK * 2), &map_a, full_bar(s), m0 + 64 * c, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &map_b, full_bar(s), k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * (64 * BK * 2), &map_b, full_bar(s), n0 + 64 * c, k0);
+          }
+        }
+      }
+      // never leave with copies still landing in this CTA's shared memory
+      for (int j = max(0, it - STAGES); j < it; ++j)
+        mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const int acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + s * STAGE_BYTES;
+          const uint32_t b_src = a_src + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = A_MN ? umma_desc_sw128(a_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? umma_desc_sw128(b_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          tc_commit(empty_bar(s));  // stage is free once these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(acc));
+      }
+      // make sure every MMA retired before TMEM is released
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+      const int acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), acc_ph, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tc.m * BM + quarter * 32 + lane;
+      const int col0 = tc.n * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      OutT* c_row = C + size_t(row) * ldc + col0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait();
+        const int valid = min(32, N - (col0 + c * 32));
+        if (row < M && valid > 0) store_chunk<OutT>(c_row + c * 32, v, valid, accumulate != 0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static int* g_status[16] = {nullptr};
+
+static int* status_ptr() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!g_status[dev]) {
+    cudaMalloc(&g_status[dev], 64);
+    cudaMemset(g_status[dev], 0, 64);
+  }
+  return g_status[dev];
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                       int ldc, int accumulate, int num_sms, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  int rc;
+  // K-major: rows = M (or N), cols = K, one (64 x rows) box.  MN-major: rows = K, cols = M (or N), 64x64 boxes.
+  rc = A_MN ? make_map_2d_bf16(&ma, A, K, M, lda, 64, BK) : make_map_2d_bf16(&ma, A, M, K, lda, BK, BM);
+  if (rc) return 100 + rc;
+  rc = B_MN ? make_map_2d_bf16(&mb, B, K, N, ldb, 64, BK) : make_map_2d_bf16(&mb, B, N, K, ldb, BK, BN);
+  if (rc) return 200 + rc;
+  auto kern = kf_gemm_bf16_tcgen05<A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, reinterpret_cast<OutT*>(C), M, N, K, ldc,
+                                                  accumulate, status_ptr());
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // namespace kf
+
+extern "C" {
+
+// C[M,N] (+)= op(A) * op(B)^T with bf16 inputs and fp32 accumulation.
+//   a_mn == 0: A is stored [M][lda] (K contiguous);  a_mn == 1: A is stored [K][lda] (M contiguous)
+//   b_mn == 0: B is stored [N][ldb] (K contiguous);  b_mn == 1: B is stored [K][ldb] (N contiguous)
+//   out_f32: C is fp32 instead of bf16.  All leading dimensions in elements; A/B pitches must be
+//   multiples of 8 elements and base pointers 16-byte aligned (TMA), ldc a multiple of 8 (bf16) / 4 (fp32).
+// Returns 0 on success, otherwise a code identifying the failing step.
+int kf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                 int a_mn, int b_mn, int out_f32, int accumulate, int num_sms, void* stream) {
+  using namespace kf;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+#define KF_DISPATCH(AM, BM_)                                                                        \
+  (out_f32 ? launch_gemm<AM, BM_, float>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, num_sms, st) \
+           : launch_gemm<AM, BM_, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, num_sms, st))
+  if (!a_mn && !b_mn) return KF_DISPATCH(false, false);
+  if (!a_mn && b_mn) return KF_DISPATCH(false, true);
+  if (a_mn && !b_mn) return KF_DISPATCH(true, false);
+  return KF_DISPATCH(true, true);
+#undef KF_DISPATCH
+}
+
+// Status word shared by all kernels of this library on the current device (0 = healthy).
+int kf_read_status() {
+  int v = 0;
+  cudaMemcpy(&v, kf::status_ptr(), sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+void kf_clear_status() { cudaMemset(kf::status_ptr(), 0, 64); }
+void* kf_status_device_ptr() { return kf::status_ptr(); }
+
+}  // extern "C"

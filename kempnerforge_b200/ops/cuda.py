@@ -1,0 +1,304 @@
+"""ctypes binding of ``libkfb200.so`` — the hand-written sm_100a kernels.
+
+Tensors are passed as raw device pointers together with the current CUDA
+stream, so every launch is ordered like an ordinary PyTorch op.  Importing this
+module on a machine with a GPU but without the built library raises: there is
+no silent fallback to library kernels.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from kempnerforge_b200.ops.build import LIB_PATH
+
+_lib = None
+LAUNCH_COUNT = 0  # number of native kernel launches issued through this module (bench bookkeeping)
+
+
+class NativeKernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NativeKernelError(
+                f"native library {LIB_PATH} is missing; run `python -m kempnerforge_b200.ops.build`"
+            )
+        _lib = ctypes.CDLL(str(LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available() and LIB_PATH.exists()
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    vp, i, ll, f = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "kf_gemm_bf16": [vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, vp],
+        "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
+        "kf_rmsnorm_bwd_blocks": [i],
+        "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp],
+        "kf_rope_bf16": [vp, vp, vp, vp, ll, i, i, i, i, i, vp],
+        "kf_swiglu_fwd_bf16": [vp, vp, ll, i, vp],
+        "kf_swiglu_bwd_bf16": [vp, vp, vp, ll, i, vp],
+        "kf_embedding_fwd_bf16": [vp, vp, vp, ll, i, i, vp],
+        "kf_embedding_bwd_bf16": [vp, vp, vp, ll, i, i, vp],
+        "kf_ce_fwd_bwd_bf16": [vp, vp, vp, vp, vp, f, i, i, i, vp],
+        "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
+        "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
+        "kf_read_status": [],
+        "kf_clear_status": [],
+        "kf_status_device_ptr": [],
+    }
+    for name, args in sigs.items():
+        fn = getattr(L, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = c_void_p if name == "kf_status_device_ptr" else c_int
+    if hasattr(L, "kf_clear_status"):
+        L.kf_clear_status.restype = None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += 1
+    if code != 0:
+        raise NativeKernelError(f"{what} failed with code {code}")
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _SM_COUNT:
+        _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _SM_COUNT[dev]
+
+
+def read_status() -> int:
+    """Status word of the library on the current device (0 = no kernel gave up a wait). Synchronises."""
+    return int(lib().kf_read_status())
+
+
+def clear_status() -> None:
+    lib().kf_clear_status()
+
+
+# --------------------------------------------------------------------------- row stacking of adjacent views
+def rows_adjacent(tensors) -> bool:
+    """True when 2-D tensors with equal width sit back to back in one storage (so they form one matrix)."""
+    first = tensors[0]
+    if first is None or not first.is_contiguous():
+        return False
+    ptr = first.data_ptr() + first.numel() * first.element_size()
+    for t in tensors[1:]:
+        if (
+            t is None
+            or not t.is_contiguous()
+            or t.shape[1:] != first.shape[1:]
+            or t.dtype != first.dtype
+            or t.data_ptr() != ptr
+            or t.untyped_storage().data_ptr() != first.untyped_storage().data_ptr()
+        ):
+            return False
+        ptr += t.numel() * t.element_size()
+    return True
+
+
+def stack_rows(tensors):
+    """One (sum rows, cols) matrix over the given row blocks: a zero-copy view when adjacent, else a copy."""
+    tensors = list(tensors)
+    if len(tensors) == 1:
+        return tensors[0]
+    if rows_adjacent(tensors):
+        first = tensors[0]
+        rows = sum(t.shape[0] for t in tensors)
+        return torch.as_strided(first.detach(), (rows, *first.shape[1:]), first.stride())
+    return torch.cat([t.detach() for t in tensors], dim=0)
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_kmajor: bool = True,
+    b_kmajor: bool = True,
+    out: torch.Tensor | None = None,
+    accumulate: bool = False,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    """out[M,N] (+)= A * Bᵀ on the tcgen05 tensor cores.
+
+    ``a_kmajor``: a is stored (M, K); otherwise (K, M).  ``b_kmajor``: b is stored (N, K); otherwise (K, N).
+    Rows may be strided (row pitch a multiple of 8 elements); columns must be contiguous.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    M, K = (a.shape[0], a.shape[1]) if a_kmajor else (a.shape[1], a.shape[0])
+    N, Kb = (b.shape[0], b.shape[1]) if b_kmajor else (b.shape[1], b.shape[0])
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    lda, ldb = a.stride(0), b.stride(0)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+        accumulate = False
+    assert out.shape == (M, N) and out.stride(1) == 1
+    ldc = out.stride(0)
+    out_f32 = out.dtype == torch.float32
+    assert out_f32 or out.dtype == torch.bfloat16
+    if lda % 8 or ldb % 8 or ldc % (4 if out_f32 else 8) or a.data_ptr() % 16 or b.data_ptr() % 16 or out.data_ptr() % 16:
+        raise NativeKernelError(
+            f"gemm operands must have 16-byte aligned bases and row pitches (lda={lda}, ldb={ldb}, ldc={ldc})"
+        )
+    code = lib().kf_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc,
+        0 if a_kmajor else 1, 0 if b_kmajor else 1, int(out_f32), int(accumulate), sm_count(), _stream(),
+    )
+    _check(code, "kf_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------- norm / rope / swiglu / embedding
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float):
+    rows, d = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(
+        lib().kf_rmsnorm_fwd_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, d, eps, _stream()),
+        "kf_rmsnorm_fwd_bf16",
+    )
+    return y, rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dx_accum: torch.Tensor | None = None):
+    """Returns (dx, dw).  With ``dx_accum`` the input gradient is added into that tensor instead."""
+    rows, d = x.shape
+    nb = lib().kf_rmsnorm_bwd_blocks(rows)
+    partial = torch.empty(nb * d, dtype=torch.float32, device=x.device)
+    dx = dx_accum if dx_accum is not None else torch.empty_like(x)
+    dw = torch.empty(d, dtype=torch.bfloat16, device=x.device)
+    _check(
+        lib().kf_rmsnorm_bwd_bf16(
+            dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), partial.data_ptr(),
+            dw.data_ptr(), None, rows, d, int(dx_accum is not None), _stream(),
+        ),
+        "kf_rmsnorm_bwd_bf16",
+    )
+    return dx, dw
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_rot: int, inverse: bool, out=None):
+    b, s, h, hd = x.shape
+    y = torch.empty_like(x) if out is None else out
+    assert cos.dtype == torch.float32 and cos.shape[0] >= s and cos.shape[1] == hd // 2
+    _check(
+        lib().kf_rope_bf16(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), b * s, s, h, n_rot, hd, int(inverse), _stream()),
+        "kf_rope_bf16",
+    )
+    return y
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    h = gu.shape[-1] // 2
+    rows = gu.numel() // (2 * h)
+    out = torch.empty((*gu.shape[:-1], h), dtype=gu.dtype, device=gu.device)
+    _check(lib().kf_swiglu_fwd_bf16(gu.data_ptr(), out.data_ptr(), rows, h, _stream()), "kf_swiglu_fwd_bf16")
+    return out
+
+
+def swiglu_bwd(dh: torch.Tensor, gu: torch.Tensor, out=None) -> torch.Tensor:
+    h = gu.shape[-1] // 2
+    rows = gu.numel() // (2 * h)
+    dgu = torch.empty_like(gu) if out is None else out
+    _check(lib().kf_swiglu_bwd_bf16(dh.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, h, _stream()), "kf_swiglu_bwd_bf16")
+    return dgu
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    ids = ids.contiguous()
+    if ids.dtype != torch.int64:
+        ids = ids.long()
+    v, d = table.shape
+    out = torch.empty((*ids.shape, d), dtype=table.dtype, device=table.device)
+    _check(lib().kf_embedding_fwd_bf16(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), d, v, _stream()), "kf_embedding_fwd_bf16")
+    return out
+
+
+def embedding_bwd(dy: torch.Tensor, ids: torch.Tensor, dtable: torch.Tensor, accumulate: bool) -> None:
+    ids = ids.contiguous()
+    if ids.dtype != torch.int64:
+        ids = ids.long()
+    v, d = dtable.shape
+    if not accumulate:
+        dtable.zero_()
+    _check(lib().kf_embedding_bwd_bf16(ids.data_ptr(), dy.data_ptr(), dtable.data_ptr(), ids.numel(), d, v, _stream()), "kf_embedding_bwd_bf16")
+
+
+# --------------------------------------------------------------------------- cross entropy
+def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, stats: torch.Tensor, inv_n: torch.Tensor, z_weight: float) -> None:
+    """Overwrites ``logits`` (rows, V) with d loss / d logits and adds [sum nll, sum lse²] into ``stats``."""
+    rows, v = logits.shape
+    assert logits.stride(1) == 1
+    row_nll = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    row_lse2 = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    labels = labels.contiguous()
+    _check(
+        lib().kf_ce_fwd_bwd_bf16(
+            logits.data_ptr(), labels.data_ptr(), row_nll.data_ptr(), row_lse2.data_ptr(), inv_n.data_ptr(),
+            float(z_weight), rows, v, logits.stride(0), _stream(),
+        ),
+        "kf_ce_fwd_bwd_bf16",
+    )
+    stats[0] += row_nll.sum()
+    stats[1] += row_lse2.sum()
+
+
+# --------------------------------------------------------------------------- optimizer
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def adamw_flat(p, g, m, v, n_decay: int, lr: float, beta1: float, beta2: float, eps: float, wd: float,
+               step: int, grad_scale: torch.Tensor | None = None, skip: torch.Tensor | None = None) -> None:
+    """One fused AdamW update over flat 1-D buffers; elements [0, n_decay) are weight-decayed."""
+    n = p.numel()
+    bc1 = 1.0 - beta1**step
+    bc2_sqrt = math.sqrt(1.0 - beta2**step)
+    _check(
+        lib().kf_adamw_flat(
+            p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n, n_decay, lr, beta1, beta2, eps, wd,
+            bc1, bc2_sqrt, grad_scale.data_ptr() if grad_scale is not None else None,
+            skip.data_ptr() if skip is not None else None, _DT[p.dtype], _DT[g.dtype], _DT[m.dtype], _stream(),
+        ),
+        "kf_adamw_flat",
+    )
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[0] (+)= sum(x²) in fp32 with a fixed reduction order."""
+    partial = torch.empty(1024, dtype=torch.float32, device=x.device)
+    _check(lib().kf_sumsq(x.data_ptr(), x.numel(), _DT[x.dtype], partial.data_ptr(), out.data_ptr(), int(accumulate), _stream()), "kf_sumsq")
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+def attn_supported(q, k, v, causal: bool) -> bool:
+    fn = getattr(lib(), "kf_attn_fwd_bf16", None)
+    if fn is None or os.environ.get("KF_DISABLE_NATIVE_ATTN"):
+        return False
+    hd = q.shape[-1]
+    return hd in (64, 128) and q.shape[1] == k.shape[1] and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1

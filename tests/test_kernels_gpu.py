@@ -1,0 +1,205 @@
+"""Numerics of every native kernel against a plain PyTorch fp32 formulation of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def _close(got, want, rtol=2e-2, atol=2e-2):
+    got, want = got.float(), want.float()
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item()
+    assert torch.allclose(got, want, rtol=rtol, atol=atol * max(1.0, ref)), f"max err {err} (ref max {ref})"
+
+
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 264, 136), (1000, 776, 520), (2048, 1024, 4096)])
+def test_gemm_all_layouts(native_lib, a_k, b_k, shape):
+    m, n, k = shape
+    a = _rand(m, k, scale=0.5)
+    b = _rand(n, k, scale=0.5)
+    want = a.float() @ b.float().t()
+    a_in = a if a_k else a.t().contiguous()
+    b_in = b if b_k else b.t().contiguous()
+    got = native_lib.gemm(a_in, b_in, a_kmajor=a_k, b_kmajor=b_k)
+    torch.cuda.synchronize()
+    assert native_lib.read_status() == 0
+    _close(got, want, rtol=2e-2, atol=1e-2)
+
+
+def test_gemm_accumulate_and_fp32_out(native_lib):
+    m, n, k = 256, 512, 320
+    a, b = _rand(m, k, scale=0.5), _rand(n, k, scale=0.5)
+    base = torch.randn(m, n, device=DEV)
+    out = base.clone()
+    native_lib.gemm(a, b, out=out, accumulate=True)
+    _close(out, base + a.float() @ b.float().t(), rtol=1e-2, atol=5e-3)
+    out_bf = base.to(torch.bfloat16)
+    want = out_bf.float() + a.float() @ b.float().t()
+    native_lib.gemm(a, b, out=out_bf, accumulate=True)
+    _close(out_bf, want)
+
+
+def test_gemm_strided_rows(native_lib):
+    big = _rand(512, 1024, scale=0.5)
+    a = big[:, 256:768]  # row pitch 1024, 512 columns
+    b = _rand(384, 512, scale=0.5)
+    got = native_lib.gemm(a, b)
+    _close(got, a.float() @ b.float().t())
+
+
+@pytest.mark.parametrize("rows,d", [(7, 256), (300, 4096), (64, 5120), (33, 16384)])
+def test_rmsnorm(native_lib, rows, d):
+    from kempnerforge_b200.ops import ref
+
+    x, w = _rand(rows, d), (1 + 0.1 * torch.randn(d, device=DEV)).to(torch.bfloat16)
+    y, rstd = native_lib.rmsnorm_fwd(x, w, 1e-5)
+    _close(y, ref.rmsnorm(x.float(), w.float(), 1e-5))
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    dy = _rand(rows, d)
+    ref.rmsnorm(xf, wf, 1e-5).backward(dy.float())
+    dx, dw = native_lib.rmsnorm_bwd(dy, x, w, rstd)
+    _close(dx, xf.grad)
+    _close(dw, wf.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_rope_roundtrip_and_reference(native_lib):
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hd = 2, 96, 6, 128
+    x = _rand(b, s, h, hd)
+    cos, sin = ref.rope_tables(hd, 128, 500000.0, device=DEV)
+    y = native_lib.rope(x, cos[:s].contiguous(), sin[:s].contiguous(), 4, inverse=False)
+    want = torch.cat([ref.apply_rope(x[:, :, :4].float(), cos[:s], sin[:s]), x[:, :, 4:].float()], dim=2)
+    _close(y, want)
+    back = native_lib.rope(y, cos[:s].contiguous(), sin[:s].contiguous(), 4, inverse=True)
+    _close(back, x, rtol=3e-2, atol=3e-2)
+
+
+def test_swiglu(native_lib):
+    rows, h = 129, 1408
+    gu = _rand(rows, 2 * h)
+    guf = gu.float().requires_grad_(True)
+    want = torch.nn.functional.silu(guf[:, :h]) * guf[:, h:]
+    got = native_lib.swiglu_fwd(gu)
+    _close(got, want)
+    dh = _rand(rows, h)
+    want.backward(dh.float())
+    _close(native_lib.swiglu_bwd(dh, gu), guf.grad)
+
+
+def test_embedding(native_lib):
+    v, d, t = 1000, 256, 777
+    table = _rand(v, d)
+    ids = torch.randint(0, v, (t,), device=DEV)
+    out = native_lib.embedding_fwd(ids, table)
+    assert torch.equal(out, table[ids])
+    dy = _rand(t, d, scale=0.1)
+    dt = torch.empty_like(table)
+    native_lib.embedding_bwd(dy, ids, dt, accumulate=False)
+    want = torch.zeros(v, d, device=DEV).index_add_(0, ids, dy.float())
+    _close(dt, want, rtol=5e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("v", [1024, 128256, 1003])
+def test_cross_entropy_fwd_bwd(native_lib, v):
+    rows = 64
+    ld = (v + 7) // 8 * 8
+    buf = _rand(rows, ld, scale=2.0)
+    logits = buf[:, :v]
+    labels = torch.randint(0, v, (rows,), device=DEV)
+    labels[::7] = -100
+    lf = logits.float().clone().requires_grad_(True)
+    z_w = 1e-3
+    n = (labels != -100).sum().float()
+    lse = torch.logsumexp(lf, -1)
+    valid = labels != -100
+    nll = (lse - lf.gather(1, labels.clamp_min(0)[:, None]).squeeze(1))[valid].sum()
+    z = (lse[valid] ** 2).sum()
+    ((nll + z_w * z) / n).backward()
+    stats = torch.zeros(2, device=DEV)
+    inv_n = (1.0 / n).reshape(1)
+    native_lib.ce_fwd_bwd(logits, labels, stats, inv_n, z_w)
+    _close(stats[0], nll.detach(), rtol=1e-3, atol=1e-3)
+    _close(stats[1], z.detach(), rtol=1e-3, atol=1e-3)
+    got, want = logits.float(), lf.grad
+    assert (got - want).abs().max().item() < 2e-2 * want.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("dtypes", [(torch.bfloat16, torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32, torch.float32)])
+def test_adamw_matches_torch(native_lib, dtypes):
+    pd, gd, sd = dtypes
+    n, n_decay = 10007, 6000
+    p0 = torch.randn(n, device=DEV)
+    p = p0.to(pd).clone()
+    m = torch.zeros(n, device=DEV, dtype=sd)
+    v = torch.zeros(n, device=DEV, dtype=sd)
+    ref_p = torch.nn.Parameter(p.float().clone())
+    opt = torch.optim.AdamW(
+        [{"params": [ref_p], "weight_decay": 0.0}], lr=1e-2, betas=(0.9, 0.95), eps=1e-8
+    )
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV).to(gd)
+        # reference: decay only the first n_decay elements
+        with torch.no_grad():
+            ref_p[:n_decay].mul_(1 - 1e-2 * 0.1)
+        ref_p.grad = g.float()
+        opt.step()
+        native_lib.adamw_flat(p, g, m, v, n_decay, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    tol = 3e-2 if pd == torch.bfloat16 else 1e-5
+    assert (p.float() - ref_p.detach()).abs().max().item() < tol
+
+
+def test_sumsq(native_lib):
+    x = _rand(1 << 20)
+    out = torch.zeros(1, device=DEV)
+    native_lib.sumsq(x, out)
+    _close(out[0], (x.float() ** 2).sum(), rtol=1e-4, atol=1e-4)
+
+
+def test_bounded_wait_reports_status(native_lib):
+    """A flag that nothing raises must end in a status code, not a hang (host reads it afterwards)."""
+    fn = getattr(native_lib.lib(), "kf_test_flag_timeout", None)
+    if fn is None:
+        pytest.skip("timeout probe not built")
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    native_lib.clear_status()
+    fn(flag.data_ptr(), 1, 2_000_000)  # ~1 ms budget
+    torch.cuda.synchronize()
+    assert native_lib.read_status() == 6
+    native_lib.clear_status()
+    # the context is still healthy
+    assert torch.ones(4, device=DEV).sum().item() == 4
+
+
+def test_model_step_native_vs_reference(native_lib):
+    from kempnerforge_b200.config import ModelConfig
+    from kempnerforge_b200.models import Transformer
+    from kempnerforge_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    cfg = ModelConfig(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, max_seq_len=128)
+    model = Transformer(cfg).to(device=DEV, dtype=torch.bfloat16)
+    tok = torch.randint(0, 1024, (2, 129), device=DEV)
+    loss = model.compute_loss(tok[:, :-1], tok[:, 1:])
+    loss.backward()
+    g_native = {n: p.grad.float().clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    with F.force_reference():
+        loss_ref = model.compute_loss(tok[:, :-1], tok[:, 1:])
+        loss_ref.backward()
+    assert abs(loss.item() - loss_ref.item()) < 5e-2
+    for n, p in model.named_parameters():
+        a, b = g_native[n], p.grad.float()
+        denom = b.abs().max().item() + 1e-6
+        assert (a - b).abs().max().item() / denom < 0.1, n
