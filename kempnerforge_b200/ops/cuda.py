@@ -56,6 +56,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_ce_fwd_bwd_bf16": [vp, vp, vp, vp, vp, f, i, i, i, vp],
         "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
         "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
+        "kf_test_flag_timeout": [vp, i, ll],
         "kf_read_status": [],
         "kf_clear_status": [],
         "kf_status_device_ptr": [],

@@ -1,0 +1,368 @@
+"""Optimizers: AdamW (fused over flat buffers), Lion, Schedule-Free AdamW, Muon.
+
+``build_optimizer`` makes two parameter groups (weight decay for tensors with
+more than one dimension whose name has no "bias", none for the rest) and hands
+them to the builder registered under ``config.name``.
+
+When the model's parameters live in flat buffers (``FlatParamGroup``), AdamW
+updates a whole group — parameters, gradients and both moments — with one
+kernel launch; the per-parameter ``state`` entries are views into the flat
+moment buffers, so ``get_optimizer_state_dict`` / DCP still see
+``exp_avg`` / ``exp_avg_sq`` / ``step`` under every parameter name.
+
+Parity: kempnerforge/training/optimizer.py:28-589 — AdamW(lr, betas, eps; groups carry
+the decay), Lion (sign of interpolated momentum, decoupled decay), Schedule-Free AdamW
+(z / x / v iterates, internal warm-up, ``eval_params`` / ``train_params``, extra ``_k``),
+Muon (momentum buffer, quintic Newton-Schulz on the local shard, sqrt(max(1, m/n)) scale,
+inner AdamW for ineligible tensors whose LR follows Muon's LR ratio), eligibility
+(>= 2-D, aspect ratio <= 10 after flattening trailing dims).
+"""
+
+from __future__ import annotations
+
+import logging
+import math
+
+import torch
+
+from kempnerforge_b200.config.registry import registry
+from kempnerforge_b200.config.sections import OptimizerConfig
+from kempnerforge_b200.ops import ref
+
+log = logging.getLogger(__name__)
+
+
+def _local(t: torch.Tensor) -> torch.Tensor:
+    """Local shard of a DTensor, or the tensor itself."""
+    return t.to_local() if hasattr(t, "to_local") else t
+
+
+# --------------------------------------------------------------------------- AdamW
+class FusedAdamW(torch.optim.AdamW):
+    """``torch.optim.AdamW`` numerics; flat parameter groups update with one native launch each."""
+
+    def __init__(self, params, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, fused=True):
+        use_torch_fused = bool(fused) and torch.cuda.is_available()
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                         fused=use_torch_fused or None)
+        self._flat_groups: list = []
+        self.grad_scale: torch.Tensor | None = None  # device scalar multiplied into every gradient
+        self.skip_flag: torch.Tensor | None = None  # device int: non-zero turns the step into a no-op
+
+    def attach_flat_groups(self, groups) -> None:
+        """Register flat buffers; their parameters are then updated by the fused kernel only."""
+        self._flat_groups = list(groups)
+        for fg in self._flat_groups:
+            fg.ensure_optimizer_state(self)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        if not self._flat_groups:
+            return super().step(closure)
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        from kempnerforge_b200.ops import cuda as kcuda
+
+        lr = self.param_groups[0]["lr"]
+        b1, b2 = self.param_groups[0]["betas"]
+        eps = self.param_groups[0]["eps"]
+        wd = max(g["weight_decay"] for g in self.param_groups)
+        for fg in self._flat_groups:
+            fg.step_count += 1
+            fg.step_tensor.fill_(float(fg.step_count))
+            p, g, m, v = fg.optimizer_views()
+            if p.numel() == 0:
+                continue
+            if p.is_cuda:
+                kcuda.adamw_flat(p, g, m, v, fg.n_decay_local, lr, b1, b2, eps, wd, fg.step_count,
+                                 self.grad_scale, self.skip_flag)
+            else:
+                if self.grad_scale is not None:
+                    g = g * self.grad_scale.to(g.dtype)
+                nd = fg.n_decay_local
+                ref.adamw_step_(p[:nd], g[:nd], m[:nd], v[:nd], fg.step_count, lr, b1, b2, eps, wd)
+                ref.adamw_step_(p[nd:], g[nd:], m[nd:], v[nd:], fg.step_count, lr, b1, b2, eps, 0.0)
+        return loss
+
+
+@registry.register("optimizer", "adamw")
+def _build_adamw(param_groups, config: OptimizerConfig):
+    return FusedAdamW(param_groups, lr=config.lr, betas=tuple(config.betas), eps=config.eps, fused=config.fused)
+
+
+# --------------------------------------------------------------------------- Lion
+class Lion(torch.optim.Optimizer):
+    """Sign-momentum optimizer: one state tensor (``exp_avg``) per parameter."""
+
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.0):
+        if lr <= 0:
+            raise ValueError(f"Invalid lr: {lr}")
+        super().__init__(params, dict(lr=lr, betas=betas, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr, (b1, b2), wd = group["lr"], group["betas"], group["weight_decay"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                state = self.state[p]
+                if "exp_avg" not in state:
+                    state["exp_avg"] = torch.zeros_like(p)
+                pl, gl, ml = _local(p), _local(p.grad), _local(state["exp_avg"])
+                direction = torch.lerp(gl.to(ml.dtype), ml, b1).sign_()
+                if wd:
+                    pl.mul_(1.0 - lr * wd)
+                pl.add_(direction.to(pl.dtype), alpha=-lr)
+                ml.lerp_(gl.to(ml.dtype), 1.0 - b2)
+        return loss
+
+
+@registry.register("optimizer", "lion")
+def _build_lion(param_groups, config: OptimizerConfig):
+    return Lion(param_groups, lr=config.lr, betas=tuple(config.betas))
+
+
+# --------------------------------------------------------------------------- Schedule-Free AdamW
+class ScheduleFreeAdamW(torch.optim.Optimizer):
+    """Schedule-free AdamW: gradient point y = lerp(z, x, beta1); x is the running average used for eval."""
+
+    def __init__(self, params, lr=0.025, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, warmup_steps=0):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.warmup_steps = warmup_steps
+        self._k = 0
+
+    def state_dict(self) -> dict:
+        sd = super().state_dict()
+        sd["_k"] = self._k
+        sd["_warmup_steps"] = self.warmup_steps
+        return sd
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        state_dict = dict(state_dict)
+        self._k = state_dict.pop("_k", self._k)
+        self.warmup_steps = state_dict.pop("_warmup_steps", self.warmup_steps)
+        super().load_state_dict(state_dict)
+        # the step counter is not part of the per-parameter state that DCP carries; recover it
+        for st in self.state.values():
+            if "k" in st:
+                self._k = max(self._k, int(st["k"]))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._k += 1
+        k = self._k
+        ramp = min(1.0, k / self.warmup_steps) if self.warmup_steps > 0 else 1.0
+        for group in self.param_groups:
+            lr = group["lr"] * ramp
+            b1, b2 = group["betas"]
+            eps, wd = group["eps"], group["weight_decay"]
+            w_k = lr * (1.0 - b1)
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if "z" not in st:
+                    st["z"] = p.detach().clone()
+                    st["v"] = torch.zeros_like(p)
+                    st["weight_sum"] = 0.0
+                z, v, g = _local(st["z"]), _local(st["v"]), _local(p.grad)
+                v.mul_(b2).addcmul_(g, g, value=1.0 - b2)
+                z.addcdiv_(g, (v / (1.0 - b2**k)).sqrt_().add_(eps), value=-lr)
+                if wd > 0:
+                    z.mul_(1.0 - lr * wd)
+                st["weight_sum"] = float(st["weight_sum"]) + w_k
+                st["k"] = k
+                if "x" not in st:
+                    st["x"] = st["z"].clone()
+                else:
+                    _local(st["x"]).lerp_(z, w_k / st["weight_sum"])
+                _local(p).copy_(z).lerp_(_local(st["x"]), b1)
+        return loss
+
+    @torch.no_grad()
+    def eval_params(self) -> None:
+        """Move parameters to the averaged iterate x (call before evaluation)."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                st = self.state.get(p, {})
+                if "x" in st:
+                    _local(p).copy_(_local(st["x"]))
+
+    @torch.no_grad()
+    def train_params(self) -> None:
+        """Move parameters back to the gradient point y = lerp(z, x, beta1)."""
+        for group in self.param_groups:
+            b1 = group["betas"][0]
+            for p in group["params"]:
+                st = self.state.get(p, {})
+                if "z" in st and "x" in st:
+                    _local(p).copy_(_local(st["z"])).lerp_(_local(st["x"]), b1)
+
+
+@registry.register("optimizer", "schedule_free_adamw")
+def _build_sf(param_groups, config: OptimizerConfig):
+    return ScheduleFreeAdamW(param_groups, lr=config.lr, betas=tuple(config.betas), eps=config.eps,
+                             warmup_steps=config.schedule_free_warmup_steps)
+
+
+# --------------------------------------------------------------------------- Muon
+def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """Quintic Newton-Schulz orthogonalisation (fp32 in, fp32 out).
+
+    On CUDA the three matrix products of every iteration run as bf16 tcgen05 GEMMs
+    with fp32 accumulation; elsewhere in plain fp32.
+    """
+    if g.is_cuda and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0 and min(g.shape) >= 64:
+        from kempnerforge_b200.ops import cuda as kcuda
+
+        if kcuda.available():
+            a, b, c = ref.NS_COEFFS
+            x = g.float()
+            x = (x / (x.norm() + 1e-7)).to(torch.bfloat16).contiguous()
+            for _ in range(steps):
+                gram = kcuda.gemm(x, x, a_kmajor=True, b_kmajor=True, out_dtype=torch.float32)  # X Xᵀ
+                gram_bf = gram.to(torch.bfloat16)
+                poly = kcuda.gemm(gram_bf, gram_bf, a_kmajor=True, b_kmajor=True, out_dtype=torch.float32)
+                poly = (b * gram + c * poly).to(torch.bfloat16)
+                upd = kcuda.gemm(poly, x, a_kmajor=True, b_kmajor=False, out_dtype=torch.float32)  # B X
+                x = (a * x.float() + upd).to(torch.bfloat16)
+            return x.float()
+    return ref.newton_schulz(g, steps)
+
+
+_newton_schulz = newton_schulz
+
+
+def is_muon_eligible(p: torch.Tensor) -> bool:
+    if p.dim() < 2:
+        return False
+    rows, cols = p.shape[0], p.numel() // max(1, p.shape[0])
+    return max(rows, cols) / max(1, min(rows, cols)) <= 10
+
+
+class Muon(torch.optim.Optimizer):
+    """Momentum + Newton-Schulz orthogonalised updates for matrices; AdamW for everything else."""
+
+    def __init__(self, muon_params, adam_params, lr=0.02, momentum=0.95, weight_decay=0.0,
+                 adam_betas=(0.9, 0.95), adam_eps=1e-8, ns_steps=5, adam_lr=None):
+        adam_lr = lr if adam_lr is None else adam_lr
+        self._initial_lr = lr
+        self._initial_adam_lr = adam_lr
+        has_adam = any(len(g["params"]) for g in adam_params)
+        self._adam = FusedAdamW(adam_params, lr=adam_lr, betas=adam_betas, eps=adam_eps) if has_adam else None
+        super().__init__(muon_params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay, ns_steps=ns_steps))
+
+    @property
+    def inner_adam(self):
+        return self._adam
+
+    def state_dict(self) -> dict:
+        sd = super().state_dict()
+        if self._adam is not None:
+            sd["_adam_state"] = self._adam.state_dict()
+        sd["_initial_lr"] = self._initial_lr
+        sd["_initial_adam_lr"] = self._initial_adam_lr
+        return sd
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        state_dict = dict(state_dict)
+        adam_state = state_dict.pop("_adam_state", None)
+        self._initial_lr = state_dict.pop("_initial_lr", self._initial_lr)
+        self._initial_adam_lr = state_dict.pop("_initial_adam_lr", self._initial_adam_lr)
+        super().load_state_dict(state_dict)
+        if adam_state is not None and self._adam is not None:
+            self._adam.load_state_dict(adam_state)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr, mu, wd, ns = group["lr"], group["momentum"], group["weight_decay"], group["ns_steps"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if "momentum_buffer" not in st:
+                    st["momentum_buffer"] = torch.zeros_like(p.grad)
+                pl, gl, buf = _local(p), _local(p.grad), _local(st["momentum_buffer"])
+                buf.mul_(mu).add_(gl)
+                if buf.numel() == 0:
+                    continue
+                mat = buf.reshape(buf.shape[0], -1)
+                upd = newton_schulz(mat.float(), ns).mul_(math.sqrt(max(1.0, mat.shape[0] / mat.shape[1])))
+                if wd > 0:
+                    pl.mul_(1.0 - lr * wd)
+                pl.add_(upd.to(pl.dtype).view_as(pl), alpha=-lr)
+        if self._adam is not None:
+            if self._initial_lr > 0:
+                ratio = self.param_groups[0]["lr"] / self._initial_lr
+                for g in self._adam.param_groups:
+                    g["lr"] = self._initial_adam_lr * ratio
+            self._adam.step()
+        return loss
+
+
+@registry.register("optimizer", "muon")
+def _build_muon(param_groups, config: OptimizerConfig):
+    muon_groups, adam_groups = [], []
+    for group in param_groups:
+        rest = {k: v for k, v in group.items() if k != "params"}
+        elig = [p for p in group["params"] if is_muon_eligible(p)]
+        other = [p for p in group["params"] if not is_muon_eligible(p)]
+        if elig:
+            muon_groups.append({**rest, "params": elig})
+        if other:
+            adam_groups.append({**rest, "params": other})
+    if not adam_groups:
+        adam_groups = [{"params": [], "weight_decay": 0.0}]
+    log.info(
+        "Muon: %s params (NS-orthogonalized), %s params (AdamW fallback)",
+        f"{sum(p.numel() for g in muon_groups for p in g['params']):,}",
+        f"{sum(p.numel() for g in adam_groups for p in g['params']):,}",
+    )
+    return Muon(muon_groups, adam_groups, lr=config.lr, momentum=config.muon_momentum,
+                weight_decay=config.weight_decay, adam_betas=tuple(config.betas), adam_eps=config.eps,
+                ns_steps=config.muon_ns_steps, adam_lr=config.muon_adam_lr)
+
+
+# --------------------------------------------------------------------------- groups
+def should_decay(name: str, param: torch.Tensor) -> bool:
+    return param.dim() > 1 and "bias" not in name
+
+
+_should_decay = should_decay
+
+
+def build_param_groups(model: torch.nn.Module, weight_decay: float) -> list[dict]:
+    decay, no_decay = [], []
+    for name, p in model.named_parameters():
+        if p.requires_grad:
+            (decay if should_decay(name, p) else no_decay).append(p)
+    log.info(
+        "Optimizer groups: %s params with decay, %s params without decay",
+        f"{sum(p.numel() for p in decay):,}", f"{sum(p.numel() for p in no_decay):,}",
+    )
+    return [{"params": decay, "weight_decay": weight_decay}, {"params": no_decay, "weight_decay": 0.0}]
+
+
+def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.optim.Optimizer:
+    groups = build_param_groups(model, config.weight_decay)
+    opt = registry.get("optimizer", config.name)(groups, config)
+    flat = getattr(model, "_kf_flat_groups", None)
+    if flat and isinstance(opt, FusedAdamW):
+        opt.attach_flat_groups(flat)
+    return opt
