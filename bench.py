@@ -1,0 +1,327 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B-shape pre-training throughput (tokens/s, whole job) on N B200s.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...        (the unmodified reference package from baseline/_ref)
+
+Config: dim 4096, 32 layers, 32 query / 8 KV heads, SwiGLU 14336, vocab 128256, RoPE theta 5e5, bf16,
+full activation checkpointing, fused AdamW (lr 3e-4, wd 0.1), cosine LR, sequence 4096, micro-batch 2 per
+GPU, sharded data parallel over all GPUs, synthetic uniform tokens, random N(0, 0.02) weights.
+
+Two timed regions, both through ``Trainer.train_step`` (forward, backward, gradient reduction, clipping,
+optimizer step, LR schedule; one host read of loss/grad-norm per step):
+  value : batches already resident on the device; CUDA events, max over ranks
+  e2e   : every step copies its batch from pinned host memory and reads the loss back
+Weak scaling: per-GPU work is fixed.  The working set (16 GB of weights, 16 GB of gradients, 32 GB of
+optimizer state, activations) is far larger than the 126 MB L2, so no explicit flush is needed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H200_PUBLISHED_TOKS = {1: 10471.0, 2: 18728.0, 4: 38983.0}  # reference, H200, FSDP rows
+MODELS = {
+    "llama3_8b": dict(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256,
+                      ffn_hidden_dim=14336, max_seq_len=4096, rope_theta=500000.0),
+    # small shape for quick functional checks of this script (not a benchmark number)
+    "tiny": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536,
+                 max_seq_len=512, rope_theta=500000.0),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--model", default="llama3_8b", choices=sorted(MODELS))
+    ap.add_argument("--batch-size", type=int, default=2)
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--transport", default=None)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of the local GPU with nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    return rank, local, world
+
+
+def timed_region(torch, dist, world, run_step, steps):
+    """barrier + synchronize, K steps between CUDA events, synchronize + barrier; returns max-over-ranks ms/step."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    last = None
+    for i in range(steps):
+        last = run_step(i)
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    ms = torch.tensor([start.elapsed_time(end) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item()), wall, last
+
+
+# --------------------------------------------------------------------------- our framework
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from kempnerforge_b200.config import config_from_dict
+    from kempnerforge_b200.metrics.mfu import compute_mfu
+    from kempnerforge_b200.ops import cuda as kcuda
+    from kempnerforge_b200.ops.build import build
+    from kempnerforge_b200.training.trainer import Trainer
+
+    rank, local, world = dist_env()
+    if rank == 0:
+        build()
+    shape = dict(MODELS[args.model])
+    seq = args.seq_len or shape["max_seq_len"]
+    cfg = config_from_dict({
+        "model": shape,
+        "train": {"batch_size": args.batch_size, "seq_len": seq, "max_steps": 1000, "grad_accum_steps": 1,
+                  "mixed_precision": "bf16", "activation_checkpointing": "full", "compile_model": False,
+                  "grad_clip_norm": 1.0, "seed": 0},
+        "optimizer": {"name": "adamw", "lr": 3e-4, "weight_decay": 0.1, "fused": True},
+        "scheduler": {"name": "cosine", "warmup_steps": 10},
+        "distributed": {"dp_shard": world},
+        "metrics": {"log_interval": 1000},
+        "data": {"pin_memory": True},
+    })
+    trainer = Trainer(cfg, transport=args.transport)
+    dev = trainer.device
+    vocab = shape["vocab_size"]
+    gen = torch.Generator().manual_seed(1234 + rank)
+
+    def host_batch():
+        tok = torch.randint(0, vocab, (args.batch_size, seq + 1), generator=gen)
+        return {"input_ids": tok[:, :-1].contiguous().pin_memory(), "labels": tok[:, 1:].contiguous().pin_memory()}
+
+    dev_batches = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(4)]
+    for i in range(args.warmup):
+        trainer.train_step([dev_batches[i % 4]])
+    status = kcuda.read_status()
+    if status != 0:
+        raise RuntimeError(f"native kernel wait status {status} during warm-up")
+
+    sampler = ClockSampler(local)
+    launches0 = kcuda.LAUNCH_COUNT
+    ms, wall, last = timed_region(torch, dist, world, lambda i: trainer.train_step([dev_batches[i % 4]]), args.steps)
+    launches = kcuda.LAUNCH_COUNT - launches0
+    clocks = sampler.stop()
+
+    host_batches = [host_batch() for _ in range(min(args.steps, 8))]
+    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    ms_e2e, _, last_e2e = timed_region(torch, dist, world,
+                                       lambda i: trainer.train_step([host_batches[i % len(host_batches)]]), args.steps)
+    tokens_per_step = args.batch_size * seq * world
+    value = tokens_per_step / (ms / 1e3)
+    e2e = tokens_per_step / (ms_e2e / 1e3)
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peaks = json.load(fh)
+    except OSError:
+        pass
+    mfu_nominal = compute_mfu(cfg.model, value, world, seq, 2250.0)
+    mfu_measured = compute_mfu(cfg.model, value, world, seq, peaks.get("bf16_tflops", 1590.0))
+    base = H200_PUBLISHED_TOKS.get(world)
+    return {
+        "metric": "llama3_8b_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b") else None,
+        "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
+        "config": {"model": args.model, "global_batch": args.batch_size * world, "seq_len": seq,
+                   "parallelism": f"dp{world}", "activation_checkpointing": "full", "optimizer": "adamw_fused",
+                   "l2": "working set (>60 GB) far exceeds L2; no flush needed"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 12},
+        "gpu_launches": launches,
+        "mfu_of_nominal_2250": mfu_nominal, "mfu_of_measured_cublas": mfu_measured,
+        "loss": last["loss"] if last else None, "wall_s_timed": wall,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+    }
+
+
+# --------------------------------------------------------------------------- reference framework
+def run_reference(args) -> dict:
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "kempnerforge")):
+        return {"impl": "reference", "unavailable": "reference package is not installed under baseline/_ref"}
+    sys.path.insert(0, ref_root)
+    sys.modules.pop("kempnerforge", None)
+    import torch
+    import torch.distributed as dist
+
+    try:
+        from kempnerforge.config.schema import JobConfig  # noqa: F401
+        from kempnerforge.config.loader import load_config
+        from kempnerforge.distributed import build_parallel_model, clip_grad_norm_, init_distributed
+        from kempnerforge.training.loss import build_loss_fn
+        from kempnerforge.training.optimizer import build_optimizer
+        from kempnerforge.training.scheduler import build_scheduler
+    except Exception as exc:  # e.g. a hard dependency that is not in the image
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:300]}
+
+    rank, local, world = dist_env()
+    shape = MODELS[args.model]
+    seq = args.seq_len or shape["max_seq_len"]
+    overrides = [f"--model.{k}={v}" for k, v in shape.items()] + [
+        f"--train.batch_size={args.batch_size}", f"--train.seq_len={seq}", "--train.max_steps=1000",
+        "--train.grad_accum_steps=1", "--train.mixed_precision=bf16", "--train.activation_checkpointing=full",
+        "--train.compile_model=true", "--train.grad_clip_norm=1.0", "--train.seed=0",
+        "--optimizer.name=adamw", "--optimizer.lr=3e-4", "--optimizer.weight_decay=0.1", "--optimizer.fused=true",
+        "--scheduler.name=cosine", "--scheduler.warmup_steps=10", f"--distributed.dp_shard={world}",
+    ]
+    config = load_config(None, overrides)
+    tc, mc = config.train, config.model
+    device_mesh = init_distributed(config.distributed, seed=tc.seed)
+    config.validate(world)
+    device = torch.device(f"cuda:{local}")
+    model = build_parallel_model(mc, device, device_mesh, ac_mode=tc.activation_checkpointing,
+                                 param_dtype=tc.param_dtype, compile_model=tc.compile_model, fp8=False)
+    optimizer = build_optimizer(model, config.optimizer)
+    scheduler = build_scheduler(optimizer, config.scheduler, max_steps=tc.max_steps)
+    loss_fn = build_loss_fn(tc)
+    model.train()
+    gen = torch.Generator().manual_seed(1234 + rank)
+
+    def host_batch():
+        tok = torch.randint(0, mc.vocab_size, (args.batch_size, seq + 1), generator=gen)
+        return tok[:, :-1].contiguous().pin_memory(), tok[:, 1:].contiguous().pin_memory()
+
+    def step(ids, labels):
+        # the reference's text training step (scripts/train.py: forward, loss, backward, loss.item(),
+        # clip_grad_norm_, grad_norm.item(), optimizer.step, scheduler.step, zero_grad)
+        ids, labels = ids.to(device, non_blocking=True), labels.to(device, non_blocking=True)
+        logits = model(ids)
+        loss = loss_fn(logits, labels)
+        loss.backward()
+        loss_val = loss.item()
+        grad_norm = clip_grad_norm_(model, tc.grad_clip_norm)
+        _ = grad_norm.item() if isinstance(grad_norm, torch.Tensor) else grad_norm
+        optimizer.step()
+        scheduler.step()
+        optimizer.zero_grad()
+        return {"loss": loss_val}
+
+    dev_batches = [tuple(t.to(device) for t in host_batch()) for _ in range(4)]
+    for i in range(args.warmup):
+        step(*dev_batches[i % 4])
+    sampler = ClockSampler(local)
+    ms, wall, last = timed_region(torch, dist, world, lambda i: step(*dev_batches[i % 4]), args.steps)
+    clocks = sampler.stop()
+    host_batches = [host_batch() for _ in range(min(args.steps, 8))]
+    h2d = sum(t.numel() * t.element_size() for t in host_batches[0])
+    ms_e2e, _, _ = timed_region(torch, dist, world, lambda i: step(*host_batches[i % len(host_batches)]), args.steps)
+    tokens_per_step = args.batch_size * seq * world
+    value = tokens_per_step / (ms / 1e3)
+    base = H200_PUBLISHED_TOKS.get(world)
+    return {
+        "metric": "llama3_8b_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b") else None,
+        "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "reference",
+        "config": {"model": args.model, "global_batch": args.batch_size * world, "seq_len": seq,
+                   "parallelism": f"dp{world}", "activation_checkpointing": "full", "optimizer": "adamw_fused",
+                   "compile_model": True},
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+        "gpu_launches": 0, "loss": last["loss"] if last else None, "wall_s_timed": wall,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+    }
+
+
+def main() -> int:
+    args = parse_args()
+    rank, _, world = dist_env()
+    if world != args.gpus and rank == 0:
+        print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using the launcher's world size", file=sys.stderr)
+    try:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    except Exception as exc:
+        if args.impl == "reference":
+            result = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        else:
+            raise
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    try:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:
+        pass
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

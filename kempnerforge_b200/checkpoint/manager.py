@@ -1,0 +1,416 @@
+"""Checkpoint manager: DCP tensor state + ``train_state.pt`` + ``metadata.json`` + a ``latest`` link.
+
+Directory layout (interchangeable with the reference):
+
+    {dir}/step_{N}/.metadata, __{rank}_{k}.distcp     tensors, keys "model.<fqn>" / "optimizer.state.<fqn>.*"
+    {dir}/step_{N}/train_state.pt                     counters, RNG, scheduler, data loader (rank 0)
+    {dir}/step_{N}/metadata.json                      {"step", "tokens_seen"[, "vlm_freeze"]}
+    {dir}/latest -> step_{N}                          committed atomically (symlink + rename)
+    {dir}/step_{N}/pp{r}/...                          one sub-directory per pipeline stage
+
+Tensors are written as whole (replicated) tensors, so a checkpoint does not depend on the number
+of GPUs that wrote it; sharded optimizer moments are gathered for the save and re-cut on load.
+
+Asynchronous saves commit ``latest`` late: a new save first waits for the previous flush, commits
+*that* checkpoint's link, then starts its own flush; ``wait()`` / ``flush_pending_save()`` commit
+the last one.  A crash in the middle therefore never leaves ``latest`` pointing at a partial
+directory.  Retention (``keep_last_n``) never removes ``latest``'s target, an in-flight directory
+or a dynamic-window milestone.  ``train_state.pt`` is a pickle: it is only loaded when the file
+belongs to the current user (or root) and is not writable by others.
+
+Parity: kempnerforge/checkpoint/manager.py:44-671.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+import os
+import shutil
+import stat
+from pathlib import Path
+from typing import Any
+
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+
+from kempnerforge_b200.checkpoint.async_save import AsyncCheckpointer
+from kempnerforge_b200.checkpoint.state import build_train_state, restore_train_state
+from kempnerforge_b200.resilience.elastic import list_step_dirs
+
+log = logging.getLogger(__name__)
+
+
+class UntrustedCheckpointError(RuntimeError):
+    pass
+
+
+def check_trusted_file(path: Path) -> None:
+    """Refuse to unpickle a file that another (non-root) user owns or that others may write."""
+    st = path.stat()
+    if st.st_uid not in (os.getuid(), 0):
+        raise UntrustedCheckpointError(f"{path} is owned by uid {st.st_uid}, not by the current user; refusing to unpickle")
+    if st.st_mode & (stat.S_IWGRP | stat.S_IWOTH):
+        raise UntrustedCheckpointError(f"{path} is writable by group/others; refusing to unpickle")
+
+
+# --------------------------------------------------------------------------- state dict assembly
+def _unwrap(model):
+    return getattr(model, "module", model)
+
+
+def model_state_dict(model) -> dict[str, torch.Tensor]:
+    return dict(_unwrap(model).state_dict())
+
+
+def _param_fqns(model) -> dict[int, str]:
+    return {id(p): n for n, p in _unwrap(model).named_parameters(remove_duplicate=False)}
+
+
+def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
+    """{"state": {fqn: {...}}, "param_groups": [{"params": [fqn...], ...}]} with whole tensors."""
+    fqn_of = _param_fqns(model)
+    engine = getattr(_unwrap(model), "_kf_engine", None)
+    opts = [optimizer] + ([optimizer.inner_adam] if getattr(optimizer, "inner_adam", None) is not None else [])
+    state: dict[str, dict] = {}
+    groups = []
+    for opt in opts:
+        flat_groups = getattr(opt, "_flat_groups", None) or []
+        flat_param_ids = set()
+        for fg in flat_groups:
+            if engine is not None and engine.world > 1:
+                m_full, v_full = engine.full_optimizer_state(fg)
+            else:
+                m_full, v_full = fg.exp_avg, fg.exp_avg_sq
+            for p, off in zip(fg.params, fg.offsets):
+                flat_param_ids.add(id(p))
+                state[fqn_of[id(p)]] = {
+                    "step": fg.step_tensor.detach().clone().cpu(),
+                    "exp_avg": m_full[off : off + p.numel()].view(p.shape),
+                    "exp_avg_sq": v_full[off : off + p.numel()].view(p.shape),
+                }
+        for p, st in opt.state.items():
+            if id(p) in flat_param_ids or id(p) not in fqn_of:
+                continue
+            state[fqn_of[id(p)]] = {
+                k: (v.to_local() if hasattr(v, "to_local") else v) if torch.is_tensor(v) else torch.tensor(float(v))
+                for k, v in st.items()
+            }
+        for g in opt.param_groups:
+            groups.append({**{k: v for k, v in g.items() if k != "params"},
+                           "params": [fqn_of[id(p)] for p in g["params"] if id(p) in fqn_of]})
+    return {"state": state, "param_groups": groups}
+
+
+def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
+    """Inverse of ``optimizer_state_dict`` for tensors that were loaded in place (flat views) or into copies."""
+    name_to_param = dict(_unwrap(model).named_parameters(remove_duplicate=False))
+    engine = getattr(_unwrap(model), "_kf_engine", None)
+    opts = [optimizer] + ([optimizer.inner_adam] if getattr(optimizer, "inner_adam", None) is not None else [])
+    handled = set()
+    for opt in opts:
+        for fg in getattr(opt, "_flat_groups", None) or []:
+            full_m = torch.zeros(fg.numel, dtype=fg.exp_avg.dtype, device=fg.exp_avg.device)
+            full_v = torch.zeros_like(full_m)
+            step = None
+            fqn_of = _param_fqns(model)
+            for p, off in zip(fg.params, fg.offsets):
+                entry = loaded["state"].get(fqn_of[id(p)])
+                handled.add(fqn_of[id(p)])
+                if entry is None:
+                    continue
+                full_m[off : off + p.numel()].copy_(entry["exp_avg"].reshape(-1))
+                full_v[off : off + p.numel()].copy_(entry["exp_avg_sq"].reshape(-1))
+                step = entry.get("step", step)
+            lo, hi = fg.shard_range
+            fg.exp_avg.copy_(full_m[lo:hi])
+            fg.exp_avg_sq.copy_(full_v[lo:hi])
+            if step is not None:
+                fg.load_step(int(float(step)))
+        owned = {id(p) for g in opt.param_groups for p in g["params"]}
+        for fqn, entry in loaded["state"].items():
+            p = name_to_param.get(fqn)
+            if fqn in handled or p is None or id(p) not in owned:
+                continue
+            dst = opt.state[p]
+            for k, v in entry.items():
+                if torch.is_tensor(v) and v.dim() > 0:
+                    cur = dst.get(k)
+                    if torch.is_tensor(cur) and cur.shape == v.shape:
+                        (cur.to_local() if hasattr(cur, "to_local") else cur).copy_(v)
+                    else:
+                        dst[k] = v.to(p.device)
+                elif k in ("weight_sum",):
+                    dst[k] = float(v)
+                elif k == "k":
+                    dst[k] = int(float(v))
+                else:
+                    dst[k] = v if torch.is_tensor(v) else torch.tensor(float(v))
+            handled.add(fqn)
+        # scalar hyper-parameters that the run may have changed (lr after scheduling is restored by the scheduler)
+    if hasattr(optimizer, "_k"):
+        ks = [int(st["k"]) for st in optimizer.state.values() if "k" in st]
+        if ks:
+            optimizer._k = max(ks)
+
+
+def _optimizer_template(model, optimizer) -> dict[str, Any]:
+    """Freshly allocated tensors of the right shapes for ``dcp.load`` to fill."""
+    tmpl = optimizer_state_dict(model, optimizer)
+    for fqn, entry in tmpl["state"].items():
+        tmpl["state"][fqn] = {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in entry.items()}
+    return tmpl
+
+
+def materialize_optimizer_state(model, optimizer) -> None:
+    """Create empty per-parameter state (as a first ``step`` would) so a template exists before loading."""
+    for opt in [optimizer] + ([optimizer.inner_adam] if getattr(optimizer, "inner_adam", None) is not None else []):
+        flat_ids = {id(p) for fg in (getattr(opt, "_flat_groups", None) or []) for p in fg.params}
+        name = type(opt).__name__
+        for g in opt.param_groups:
+            for p in g["params"]:
+                if not p.requires_grad or id(p) in flat_ids or len(opt.state[p]) > 0:
+                    continue
+                if name in ("FusedAdamW", "AdamW"):
+                    opt.state[p] = {"step": torch.zeros((), dtype=torch.float32, device=p.device),
+                                    "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+                elif name == "Lion":
+                    opt.state[p] = {"exp_avg": torch.zeros_like(p)}
+                elif name == "Muon":
+                    opt.state[p] = {"momentum_buffer": torch.zeros_like(p)}
+                elif name == "ScheduleFreeAdamW":
+                    opt.state[p] = {"z": p.detach().clone(), "v": torch.zeros_like(p), "x": p.detach().clone(),
+                                    "weight_sum": 0.0, "k": 0}
+
+
+# --------------------------------------------------------------------------- manager
+class CheckpointManager:
+    def __init__(self, config, model, optimizer, process_group=None, pp_rank: int | None = None) -> None:
+        self.config = config
+        self.model = model
+        self.optimizer = optimizer
+        self.pp_rank = pp_rank
+        self.dir = Path(config.dir)
+        self.process_group = process_group
+        self._dist = dist.is_available() and dist.is_initialized()
+        self.rank = dist.get_rank() if self._dist else 0
+        self.group_rank = dist.get_rank(process_group) if (self._dist and process_group is not None) else self.rank
+        self._sync_group = None
+        if self._dist and dist.get_world_size() > 1:
+            # a dedicated gloo group: barriers issued from the main thread must not interleave with the
+            # collectives DCP issues from its background thread on the default group
+            self._sync_group = dist.new_group(backend="gloo")
+        self._saver = AsyncCheckpointer(str(config.async_mode), process_group)
+        self._pending_finalize: tuple[Path, int] | None = None
+        self._stashed_dataloader_state: dict | None = None
+
+    # ------------------------------------------------------------------ paths
+    def step_dir(self, step: int) -> Path:
+        return self.dir / f"step_{step}"
+
+    def _dcp_dir(self, step_dir: Path) -> Path:
+        return step_dir / f"pp{self.pp_rank}" if self.pp_rank is not None else step_dir
+
+    def _is_writer(self) -> bool:
+        return self.rank == 0
+
+    def _barrier(self) -> None:
+        if self._sync_group is not None:
+            dist.barrier(group=self._sync_group)
+
+    def _commit_latest(self, step_dir: Path, step: int) -> None:
+        if self._is_writer():
+            tmp = self.dir / "latest.tmp"
+            if tmp.is_symlink() or tmp.exists():
+                tmp.unlink()
+            tmp.symlink_to(step_dir.name)
+            os.replace(tmp, self.dir / "latest")
+            log.info("Checkpoint committed: %s (step=%d)", step_dir, step)
+            log.info("Checkpoint saved: %s (step=%d)", step_dir, step)
+
+    def _drain_pending_finalize(self) -> None:
+        if self._pending_finalize is not None:
+            step_dir, step = self._pending_finalize
+            self._pending_finalize = None
+            self._commit_latest(step_dir, step)
+            self._cleanup()
+
+    # ------------------------------------------------------------------ save
+    def save(self, step: int, tokens_seen: int = 0, scheduler=None, dataloader=None, extra: dict | None = None) -> Path:
+        step_dir = self.step_dir(step)
+        dcp_dir = self._dcp_dir(step_dir)
+        dcp_dir.mkdir(parents=True, exist_ok=True)
+        state = {"model": model_state_dict(self.model), "optimizer": optimizer_state_dict(self.model, self.optimizer)}
+        self._saver.save(state, str(dcp_dir), self.process_group)  # waits for the previous flush first
+        self._drain_pending_finalize()
+        if self._is_writer() or (self.pp_rank is not None and self.group_rank == 0):
+            train_state = build_train_state(step, tokens_seen, scheduler, dataloader, extra)
+            target = dcp_dir if self.pp_rank is not None else step_dir
+            torch.save(train_state, target / "train_state.pt")
+        if self._is_writer():
+            meta = {"step": step, "tokens_seen": tokens_seen}
+            if extra and "vlm_freeze" in extra:
+                meta["vlm_freeze"] = extra["vlm_freeze"]
+            (step_dir / "metadata.json").write_text(json.dumps(meta))
+        if self._saver.is_async:
+            self._pending_finalize = (step_dir, step)
+        else:
+            self._barrier()
+            self._commit_latest(step_dir, step)
+            self._cleanup()
+        self._barrier()
+        return step_dir
+
+    def wait(self) -> None:
+        """Block until the in-flight save (if any) is on disk and committed."""
+        self._saver.wait()
+        self._barrier()
+        self._drain_pending_finalize()
+        self._barrier()
+
+    flush_pending_save = wait
+
+    def peek_saved_step(self, path: str | Path | None = None) -> int | None:
+        """Step number recorded in a checkpoint's metadata without loading tensors."""
+        target = self._resolve_load_path(path)
+        if target is None:
+            return None
+        meta = target / "metadata.json"
+        if meta.exists():
+            try:
+                return int(json.loads(meta.read_text())["step"])
+            except (ValueError, KeyError):
+                return None
+        return None
+
+    # ------------------------------------------------------------------ load
+    def _resolve_load_path(self, path) -> Path | None:
+        for cand in (path, self.config.load_path):
+            if cand:
+                p = Path(cand)
+                if p.name == "latest" or p.is_symlink():
+                    p = p.resolve()
+                return p if p.exists() else None
+        latest = self.dir / "latest"
+        if latest.exists():
+            return latest.resolve()
+        steps = list_step_dirs(self.dir)
+        return steps[-1][1] if steps else None
+
+    def _resolve_dcp_load_dir(self, step_dir: Path) -> Path | None:
+        """``step_dir`` if its tensor data is complete, else the newest earlier checkpoint that is."""
+        def complete(d: Path) -> bool:
+            return (self._dcp_dir(d) / ".metadata").exists()
+
+        if complete(step_dir):
+            return step_dir
+        log.warning("checkpoint %s is incomplete (no .metadata); looking for an older complete one", step_dir)
+        for _, cand in reversed(list_step_dirs(step_dir.parent)):
+            if cand != step_dir and complete(cand):
+                return cand
+        return None
+
+    def load(self, path=None, scheduler=None, dataloader=None, exclude_keys: list[str] | None = None,
+             vlm_freeze_expected: list[dict] | None = None) -> tuple[int, int, dict]:
+        """Restore model / optimizer / train state; returns (step, tokens_seen, extras) — (0, 0, {}) if nothing found."""
+        step_dir = self._resolve_load_path(path)
+        exists = step_dir is not None
+        if self._dist and dist.get_world_size() > 1:  # rank 0's view of the filesystem is authoritative
+            box = [str(step_dir) if exists else ""]
+            dist.broadcast_object_list(box, src=0, group=self._sync_group)
+            step_dir, exists = (Path(box[0]), True) if box[0] else (None, False)
+        if not exists:
+            log.info("no checkpoint found under %s; starting from scratch", self.dir)
+            return 0, 0, {}
+        step_dir = self._resolve_dcp_load_dir(step_dir)
+        if step_dir is None:
+            log.warning("no complete checkpoint available; starting from scratch")
+            return 0, 0, {}
+        self._check_freeze_metadata(step_dir, vlm_freeze_expected)
+        exclude = set(exclude_keys or [])
+        state: dict[str, Any] = {}
+        if "model" not in exclude:
+            state["model"] = model_state_dict(self.model)
+        if "optimizer" not in exclude:
+            materialize_optimizer_state(self.model, self.optimizer)
+            state["optimizer"] = _optimizer_template(self.model, self.optimizer)
+        if state:
+            dcp.load(state, checkpoint_id=str(self._dcp_dir(step_dir)), process_group=self.process_group)
+            if "model" in state:
+                _unwrap(self.model).load_state_dict(state["model"], strict=False)
+            if "optimizer" in state:
+                load_optimizer_state_dict(self.model, self.optimizer, state["optimizer"])
+        train_state = self._load_train_state(step_dir)
+        if train_state is None:
+            return self._step_from_name(step_dir), 0, {}
+        if dataloader is None and "dataloader" in train_state:
+            self._stashed_dataloader_state = train_state["dataloader"]
+        step, tokens, extra = restore_train_state(train_state, scheduler, dataloader)
+        log.info("Checkpoint loaded: %s (step=%d)", step_dir, step)
+        return step, tokens, extra
+
+    @staticmethod
+    def _step_from_name(step_dir: Path) -> int:
+        try:
+            return int(step_dir.name.split("_")[1])
+        except (IndexError, ValueError):
+            return 0
+
+    def _load_train_state(self, step_dir: Path) -> dict | None:
+        target = (self._dcp_dir(step_dir) if self.pp_rank is not None else step_dir) / "train_state.pt"
+        multi = self._dist and dist.get_world_size() > 1 and self.pp_rank is None
+        state = None
+        if not multi or self.rank == 0:
+            if target.exists():
+                check_trusted_file(target)
+                state = torch.load(target, map_location="cpu", weights_only=False)
+        if multi:
+            box = [state]
+            dist.broadcast_object_list(box, src=0, group=self._sync_group)
+            state = box[0]
+        return state
+
+    def _check_freeze_metadata(self, step_dir: Path, expected: list[dict] | None) -> None:
+        if expected is None:
+            return
+        meta_path = step_dir / "metadata.json"
+        if not meta_path.exists():
+            return
+        saved = json.loads(meta_path.read_text()).get("vlm_freeze")
+        if saved is None:
+            return
+        saved_map = {e["module"]: e["frozen"] for e in saved}
+        want_map = {e["module"]: e["frozen"] for e in expected}
+        diff = {k: (saved_map[k], want_map[k]) for k in saved_map.keys() & want_map.keys() if saved_map[k] != want_map[k]}
+        if diff:
+            msg = f"freeze configuration differs from the checkpoint: {diff}"
+            if self.config.ignore_freeze_mismatch:
+                log.warning(msg)
+            else:
+                raise ValueError(msg + " (set checkpoint.ignore_freeze_mismatch=true to continue)")
+
+    def apply_dataloader_state(self, dataloader) -> None:
+        """Hand a data-loader state that was loaded before the loader existed over to the loader."""
+        if self._stashed_dataloader_state is not None and dataloader is not None and hasattr(dataloader, "load_state_dict"):
+            dataloader.load_state_dict(self._stashed_dataloader_state)
+            self._stashed_dataloader_state = None
+
+    # ------------------------------------------------------------------ retention
+    def _cleanup(self) -> None:
+        keep = self.config.keep_last_n
+        if keep is None or keep <= 0 or not self._is_writer():
+            return
+        steps = list_step_dirs(self.dir)
+        protected = set()
+        latest = self.dir / "latest"
+        if latest.exists():
+            protected.add(latest.resolve())
+        if self._pending_finalize is not None:
+            protected.add(self._pending_finalize[0].resolve())
+        regular = [(s, d) for s, d in steps if not self.config.is_dynamic_milestone(s)]
+        for s, d in regular[:-keep] if len(regular) > keep else []:
+            if d.resolve() in protected:
+                continue
+            shutil.rmtree(d, ignore_errors=True)
+            log.info("removed old checkpoint %s", d)

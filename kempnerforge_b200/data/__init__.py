@@ -1,0 +1,62 @@
+"""Data pipeline: datasets, samplers, stateful loader and the factory the trainer uses."""
+
+from __future__ import annotations
+
+import os
+
+from kempnerforge_b200.data.dataloader import StatefulDataLoader
+from kempnerforge_b200.data.dataset import (
+    HuggingFaceDataset,
+    MemoryMappedDataset,
+    MixtureDataset,
+    StreamingHuggingFaceDataset,
+    compute_packed_output,
+)
+from kempnerforge_b200.data.sampler import DistributedSampler, MixtureSampler
+
+
+def _eos_id(config) -> int | None:
+    if not config.data.tokenizer_path:
+        return None
+    from transformers import AutoTokenizer
+
+    return AutoTokenizer.from_pretrained(config.data.tokenizer_path).eos_token_id
+
+
+def _one_dataset(config, path: str = "", hf_name: str = "", hf_config: str = "", rank: int = 0, world: int = 1):
+    dc, tc = config.data, config.train
+    window = tc.seq_len + 1
+    if path:
+        eos = _eos_id(config) if dc.pack_sequences else None
+        return MemoryMappedDataset(path, window, dc.file_pattern, dc.pack_sequences, eos)
+    if dc.hf_streaming:
+        return StreamingHuggingFaceDataset(hf_name, window, dc.tokenizer_path, hf_config or None,
+                                           dc.hf_dataset_split, dc.hf_dataset_text_field, rank, world,
+                                           dc.pack_sequences)
+    return HuggingFaceDataset(hf_name, window, dc.tokenizer_path, hf_config or None, dc.hf_dataset_split,
+                              dc.hf_dataset_text_field, dc.pack_sequences)
+
+
+def build_train_dataloader(config, dp_rank: int = 0, dp_size: int = 1):
+    """The training data source named by the config; synthetic uniform tokens when none is configured."""
+    dc, tc = config.data, config.train
+    seed = tc.effective_data_seed
+    if dc.datasets:
+        parts, names, weights = [], [], []
+        for i, src in enumerate(dc.datasets):
+            parts.append(_one_dataset(config, src.path, src.hf_name, src.hf_config, dp_rank, dp_size))
+            names.append(src.name or os.path.basename(os.path.normpath(src.path)) or src.hf_name or f"dataset_{i}")
+            weights.append(src.weight)
+        ds = MixtureDataset(parts, names)
+        sampler = MixtureSampler(ds.cumulative_sizes, weights, dp_size, dp_rank, True, seed, True, dc.mix_temperature)
+    elif dc.dataset_path or dc.hf_dataset_name:
+        ds = _one_dataset(config, dc.dataset_path, dc.hf_dataset_name or "", dc.hf_dataset_config or "", dp_rank, dp_size)
+        sampler = None if dc.hf_streaming and not dc.dataset_path else DistributedSampler(len(ds), dp_size, dp_rank, True, seed, True)
+    else:
+        from kempnerforge_b200.training.trainer import SyntheticTokens
+
+        return SyntheticTokens(config.model.vocab_size, tc.batch_size, tc.seq_len, seed, dp_rank, dc.pin_memory)
+    return StatefulDataLoader(ds, tc.batch_size, sampler, dc.num_workers, dc.pin_memory, dc.prefetch_factor, True)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

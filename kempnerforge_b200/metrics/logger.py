@@ -1,0 +1,104 @@
+"""Rank-aware logging.
+
+Only rank 0 prints by default; every record carries ``[rank r]``; colours are dropped when
+``NO_COLOR`` is set or the stream is not a terminal.  ``format_metrics`` renders the one-line
+step summary ``[step N] k=v | k=v | ...`` that tools (and the end-to-end tests) parse.
+
+Parity: kempnerforge/metrics/logger.py:29-156.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import sys
+
+_COLORS = {"DEBUG": "\033[36m", "INFO": "\033[32m", "WARNING": "\033[33m", "ERROR": "\033[31m", "CRITICAL": "\033[35m"}
+_RESET = "\033[0m"
+
+
+def _rank() -> int:
+    for key in ("RANK", "SLURM_PROCID"):
+        if key in os.environ:
+            try:
+                return int(os.environ[key])
+            except ValueError:
+                pass
+    return 0
+
+
+class RankFilter(logging.Filter):
+    """Let records through on rank 0 only (or on every rank when ``all_ranks``)."""
+
+    def __init__(self, all_ranks: bool = False) -> None:
+        super().__init__()
+        self.all_ranks = all_ranks
+
+    def filter(self, record: logging.LogRecord) -> bool:
+        return self.all_ranks or _rank() == 0 or record.levelno >= logging.ERROR
+
+
+class RankFormatter(logging.Formatter):
+    def __init__(self, use_color: bool | None = None) -> None:
+        super().__init__()
+        if use_color is None:
+            use_color = sys.stderr.isatty() and "NO_COLOR" not in os.environ
+        self.use_color = use_color
+
+    def format(self, record: logging.LogRecord) -> str:
+        level = record.levelname
+        if self.use_color and level in _COLORS:
+            level = f"{_COLORS[level]}{level}{_RESET}"
+        stamp = self.formatTime(record, "%H:%M:%S")
+        msg = record.getMessage()
+        if record.exc_info:
+            msg += "\n" + self.formatException(record.exc_info)
+        return f"{stamp} [rank {_rank()}] {level} {record.name}: {msg}"
+
+
+_configured = False
+
+
+def setup_logging(level: int | str = logging.INFO, all_ranks: bool = False) -> None:
+    global _configured
+    root = logging.getLogger("kempnerforge_b200")
+    root.setLevel(level)
+    if not _configured:
+        handler = logging.StreamHandler(sys.stdout)
+        handler.setFormatter(RankFormatter())
+        handler.addFilter(RankFilter(all_ranks))
+        root.addHandler(handler)
+        root.propagate = False
+        _configured = True
+
+
+def get_logger(name: str = "kempnerforge_b200") -> logging.Logger:
+    setup_logging()
+    if not name.startswith("kempnerforge_b200"):
+        name = f"kempnerforge_b200.{name}"
+    return logging.getLogger(name)
+
+
+def format_metrics(step: int, metrics: dict) -> str:
+    """``[step 12] loss=2.3456 | lr=3.00e-04 | grad_norm=0.812 | tok/s=12,345 | mfu=41.2% | mem=10.1/180GB | step_time=0.53s``"""
+    parts = []
+    for key, val in metrics.items():
+        if key == "loss" or key.endswith("/loss") or key.startswith("loss/"):
+            parts.append(f"{key}={val:.4f}")
+        elif key == "lr":
+            parts.append(f"lr={val:.2e}")
+        elif key == "grad_norm":
+            parts.append(f"grad_norm={val:.3f}")
+        elif key == "tok/s":
+            parts.append(f"tok/s={val:,.0f}")
+        elif key == "mfu":
+            parts.append(f"mfu={val:.1f}%")
+        elif key == "mem":
+            parts.append(f"mem={val}")
+        elif key == "step_time":
+            parts.append(f"step_time={val:.2f}s")
+        elif isinstance(val, float):
+            parts.append(f"{key}={val:.4g}")
+        else:
+            parts.append(f"{key}={val}")
+    return f"[step {step}] " + " | ".join(parts)

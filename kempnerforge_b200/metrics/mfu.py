@@ -1,0 +1,88 @@
+"""Model-FLOPs utilisation.
+
+FLOPs per token = 6 * P_active + 12 * L * D * S, where P_active excludes the token embedding
+(a lookup) but includes the output head, and for MoE layers counts only the routed top-k experts
+plus the shared expert that actually runs.  The peak is looked up by GPU name; Blackwell parts are
+listed with their dense (non-sparse) bf16 rates, and a measured peak can be supplied instead.
+
+Parity: kempnerforge/metrics/mfu.py:25-180 (formula and public functions).  Difference: the
+reference has no Blackwell entry and would fall back to the Hopper number on a B200.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+# dense bf16 tensor-core TFLOP/s
+GPU_PEAK_TFLOPS: dict[str, float] = {
+    "B200": 2250.0,
+    "GB200": 2500.0,
+    "B100": 1800.0,
+    "H200": 989.0,
+    "H100 PCIe": 756.0,
+    "H100": 989.0,
+    "A100": 312.0,
+    "L40S": 362.0,
+    "A10G": 125.0,
+    "RTX 4090": 330.0,
+    "RTX 3090": 142.0,
+}
+_GPU_PEAK_TFLOPS = GPU_PEAK_TFLOPS
+
+
+def get_gpu_peak_tflops(device: int | None = None, measured_peaks_path: str | None = None) -> float:
+    """Peak bf16 TFLOP/s: an explicit measurement file wins, then the name table, then a capability guess."""
+    path = measured_peaks_path or os.environ.get("KF_MEASURED_PEAKS")
+    if path and os.path.exists(path):
+        try:
+            with open(path) as fh:
+                return float(json.load(fh)["bf16_tflops"])
+        except (OSError, KeyError, ValueError):
+            pass
+    if not torch.cuda.is_available():
+        return 1.0
+    name = torch.cuda.get_device_name(device if device is not None else torch.cuda.current_device())
+    for key in sorted(GPU_PEAK_TFLOPS, key=len, reverse=True):
+        if key.lower() in name.lower():
+            return GPU_PEAK_TFLOPS[key]
+    major, _ = torch.cuda.get_device_capability(device)
+    if major >= 10:
+        return GPU_PEAK_TFLOPS["B200"]
+    if major >= 9:
+        return GPU_PEAK_TFLOPS["H100"]
+    if major >= 8:
+        return GPU_PEAK_TFLOPS["A100"]
+    return 100.0
+
+
+def active_params(model_config) -> int:
+    """Parameters that take part in one token's forward pass, without the embedding table."""
+    c = model_config
+    d, hd = c.dim, c.head_dim
+    attn = 2 * d * c.n_heads * hd + 2 * d * c.n_kv_heads * hd
+    total = 0
+    for i in range(c.n_layers):
+        if c.is_moe_layer(i):
+            he = c.computed_expert_ffn_hidden_dim
+            shared = 0
+            if c.moe_shared_experts > 0:  # one shared MLP runs (optionally widened)
+                shared = 3 * d * he * (c.moe_shared_experts if c.moe_shared_expert_widen else 1)
+            total += attn + c.moe_top_k * 3 * d * he + shared + d * c.num_experts
+        else:
+            total += attn + 3 * d * c.computed_ffn_hidden_dim
+    return total + c.vocab_size * d  # output head
+
+
+def estimate_model_flops_per_token(model_config, seq_len: int) -> float:
+    return 6.0 * active_params(model_config) + 12.0 * model_config.n_layers * model_config.dim * seq_len
+
+
+def compute_mfu(model_config, tokens_per_sec: float, num_gpus: int = 1, seq_len: int = 2048,
+                peak_tflops: float | None = None) -> float:
+    """Utilisation in [0, 1] of ``num_gpus`` GPUs at ``tokens_per_sec`` (whole job)."""
+    peak = peak_tflops if peak_tflops is not None else get_gpu_peak_tflops()
+    achieved = estimate_model_flops_per_token(model_config, seq_len) * tokens_per_sec / max(1, num_gpus)
+    return achieved / (peak * 1e12)

@@ -1,0 +1,157 @@
+"""Sharded data-parallel engine over flat parameter groups.
+
+Memory plan ("resident" ZeRO): every rank keeps the full bf16 parameters and a full
+gradient buffer of each unit — on a 180 GB part an 8 B-parameter model needs 32 GB for
+both — while optimizer state and the optimizer work are sharded 1/N.  A training step is
+
+  backward  -> flat gradient buffers (local sum over micro-batches)
+  reduce    -> every rank obtains the mean gradient of *its* shard (reduce-scatter)
+  clip      -> global norm from the shard sums of squares (one scalar all-reduce, no host sync)
+  update    -> fused AdamW on the shard
+  publish   -> the updated shard is written into every rank's parameter buffer (all-gather)
+
+Two transports implement reduce/publish:
+  * ``collective``: ``torch.distributed`` calls (NCCL on GPUs, gloo on CPU) — the portable baseline;
+  * ``symmetric``: our own kernels over NVLink symmetric memory (see ``kempnerforge_b200.comm``),
+    where the reduce-scatter is fused with the scaling / cast / norm partial and the
+    all-gather is fused into the AdamW kernel's stores.
+
+Gradient accumulation: ``set_requires_gradient_sync(False)`` marks a micro-step after which
+nothing is reduced (kempnerforge/training/grad.py:15-39).  Gradient clipping mirrors
+kempnerforge/distributed/utils.py:44-111: coef = max_norm / (norm + 1e-6) clamped to 1, the
+pre-clip norm is returned.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from kempnerforge_b200.parallel.flat import FlatParamGroup, flatten_model
+
+
+class DataParallelEngine:
+    def __init__(self, model: nn.Module, process_group=None, transport: str = "collective", allocator=None) -> None:
+        self.model = model
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if process_group is not None else 1
+        self.rank = dist.get_rank(process_group) if process_group is not None else 0
+        self.transport = transport
+        self.groups: list[FlatParamGroup] = flatten_model(model, self.world, self.rank, allocator)
+        self.requires_sync = True
+        dev = self.groups[0].device
+        self.device = dev
+        self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.grad_scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._reduced = False
+        model._kf_engine = self
+        model.set_requires_gradient_sync = self.set_requires_gradient_sync
+        if self.world > 1:
+            self.broadcast_parameters()
+
+    # ------------------------------------------------------------------ set-up
+    def broadcast_parameters(self, src: int = 0) -> None:
+        """Make every rank start from rank ``src``'s weights."""
+        root = dist.get_global_rank(self.pg, src) if self.pg is not None else src
+        for g in self.groups:
+            dist.broadcast(g.param, src=root, group=self.pg)
+
+    def set_requires_gradient_sync(self, flag: bool) -> None:
+        self.requires_sync = bool(flag)
+
+    # ------------------------------------------------------------------ step phases
+    def finish_backward(self) -> None:
+        """Fold stray autograd gradients into the flat buffers and reduce them across ranks."""
+        for g in self.groups:
+            g.finalize_grads()
+        if self.world > 1 and self.requires_sync:
+            self._reduce_gradients()
+        self._reduced = True
+
+    def _reduce_gradients(self) -> None:
+        for g in self.groups:
+            if g.grad.is_cuda and dist.get_backend(self.pg) == "nccl":
+                lo, hi = g.shard_range
+                dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg)
+            else:
+                dist.all_reduce(g.grad, group=self.pg)
+                g.grad.div_(self.world)
+
+    def clip_grad_norm(self, max_norm: float | None) -> torch.Tensor:
+        """Global gradient L2 norm (pre-clip, device scalar); sets ``grad_scale`` for the optimizer."""
+        use_native = self.groups[0].grad.is_cuda and self.groups[0].dtype in (torch.bfloat16, torch.float32)
+        if use_native:
+            from kempnerforge_b200.ops import cuda as kcuda
+
+            first = True
+            for g in self.groups:
+                lo, hi = g.shard_range
+                kcuda.sumsq(g.grad[lo:hi], self._sq, accumulate=not first)
+                first = False
+        else:
+            self._sq.zero_()
+            for g in self.groups:
+                lo, hi = g.shard_range
+                self._sq += g.grad[lo:hi].float().pow(2).sum()
+        if self.world > 1:
+            dist.all_reduce(self._sq, group=self.pg)
+        torch.sqrt(self._sq, out=self.grad_norm)
+        if max_norm is not None and max_norm > 0:
+            torch.clamp(max_norm / (self.grad_norm + 1e-6), max=1.0, out=self.grad_scale)
+        else:
+            self.grad_scale.fill_(1.0)
+        return self.grad_norm
+
+    def apply_grad_scale(self) -> None:
+        """Multiply the (shard) gradients by ``grad_scale``; only needed for optimizers that do not fuse it."""
+        for g in self.groups:
+            lo, hi = g.shard_range
+            g.grad[lo:hi].mul_(self.grad_scale.to(g.grad.dtype))
+
+    def after_optimizer_step(self) -> None:
+        """Publish the updated shards so that every rank holds the full new parameters."""
+        if self.world > 1:
+            for g in self.groups:
+                lo, hi = g.shard_range
+                dist.all_gather_into_tensor(g.param, g.param[lo:hi].clone(), group=self.pg)
+
+    def zero_grad(self) -> None:
+        for g in self.groups:
+            g.zero_grad()
+        self._reduced = False
+
+    # ------------------------------------------------------------------ checkpoint helpers
+    def full_optimizer_state(self, g: FlatParamGroup) -> tuple[torch.Tensor, torch.Tensor]:
+        """Whole-unit moment buffers assembled from every rank's shard."""
+        if self.world == 1:
+            return g.exp_avg, g.exp_avg_sq
+        out = []
+        for shard in (g.exp_avg, g.exp_avg_sq):
+            full = torch.empty(g.numel, dtype=shard.dtype, device=shard.device)
+            dist.all_gather_into_tensor(full, shard, group=self.pg)
+            out.append(full)
+        return out[0], out[1]
+
+    def load_full_optimizer_state(self, g: FlatParamGroup, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor) -> None:
+        lo, hi = g.shard_range
+        g.exp_avg.copy_(exp_avg[lo:hi])
+        g.exp_avg_sq.copy_(exp_avg_sq[lo:hi])
+
+
+def clip_grad_norm_(model: nn.Module, max_norm: float, foreach: bool | None = None) -> torch.Tensor:
+    """Clip the global gradient norm in place; returns the pre-clip norm.  Engine-aware."""
+    engine = getattr(model, "_kf_engine", None)
+    if engine is not None:
+        norm = engine.clip_grad_norm(max_norm)
+        return norm.reshape(())
+    grads = [p.grad for p in model.parameters() if p.grad is not None]
+    if not grads:
+        return torch.zeros(())
+    local = [g.to_local() if hasattr(g, "to_local") else g for g in grads]
+    total = torch.sqrt(sum(g.float().pow(2).sum() for g in local))
+    coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+    for g in local:
+        g.mul_(coef.to(g.dtype))
+    return total

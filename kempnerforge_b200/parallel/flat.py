@@ -1,0 +1,192 @@
+"""Flat parameter storage.
+
+A ``FlatParamGroup`` owns one contiguous buffer for the parameters of one unit
+(a transformer block, or the root unit: embedding + final norm + head), a
+same-shaped gradient buffer and — once an optimizer attaches — flat moment
+buffers.  Every ``nn.Parameter`` of the unit becomes a view into the buffer, so
+
+* adjacent projection weights (q|k|v, gate|up) form one GEMM operand without a copy,
+* weight-gradient GEMMs write straight into the flat gradient buffer,
+* the optimizer updates the whole unit with one kernel launch,
+* data-parallel reduction / broadcast work on one address range per unit
+  (the buffers can be placed in NVLink symmetric memory by passing an allocator).
+
+Layout: parameters that get weight decay first, then the rest, each aligned to
+16 bytes; under data parallelism the flat range is cut into ``world`` equal
+shards (optimizer state exists only for the local shard).
+
+Replaces what FSDP2's ``fully_shard`` does for the reference
+(kempnerforge/distributed/parallel.py:216-302): unit = one block, root unit =
+embedding + norm + head, parameters in the training dtype, gradients averaged
+over the data-parallel group.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable, Iterable
+
+import torch
+from torch import nn
+
+ALIGN_BYTES = 16
+
+
+def _should_decay(name: str, p: torch.Tensor) -> bool:
+    return p.dim() > 1 and "bias" not in name
+
+
+class FlatParamGroup:
+    def __init__(
+        self,
+        name: str,
+        named_params: Iterable[tuple[str, nn.Parameter]],
+        world: int = 1,
+        rank: int = 0,
+        allocator: Callable[[int, torch.dtype, torch.device], torch.Tensor] | None = None,
+    ) -> None:
+        self.name = name
+        self.world, self.rank = world, rank
+        items = [(n, p) for n, p in named_params if p.requires_grad]
+        if not items:
+            raise ValueError(f"flat group {name!r} has no trainable parameters")
+        self.dtype = items[0][1].dtype
+        self.device = items[0][1].device
+        if any(p.dtype != self.dtype or p.device != self.device for _, p in items):
+            raise ValueError(f"flat group {name!r} mixes dtypes or devices")
+        elem = torch.empty((), dtype=self.dtype).element_size()
+        align = max(1, ALIGN_BYTES // elem)
+        decay = [(n, p) for n, p in items if _should_decay(n, p)]
+        rest = [(n, p) for n, p in items if not _should_decay(n, p)]
+        self.names: list[str] = []
+        self.params: list[nn.Parameter] = []
+        self.offsets: list[int] = []
+        off = 0
+        for n, p in decay + rest:
+            self.names.append(n)
+            self.params.append(p)
+            self.offsets.append(off)
+            off += -(-p.numel() // align) * align
+        self.n_decay = self.offsets[len(decay)] if rest else off
+        if not decay:
+            self.n_decay = 0
+        # pad so that every rank's shard has the same, aligned length
+        chunk = align * world
+        self.numel = -(-off // chunk) * chunk
+        self.shard_numel = self.numel // world
+        alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
+        self.param = alloc(self.numel, self.dtype, self.device)
+        self.grad = alloc(self.numel, self.dtype, self.device)
+        self.exp_avg: torch.Tensor | None = None
+        self.exp_avg_sq: torch.Tensor | None = None
+        self.step_tensor = torch.zeros((), dtype=torch.float32)
+        self.step_count = 0
+        with torch.no_grad():
+            for p, o in zip(self.params, self.offsets):
+                view = self.param[o : o + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p._kf_grad = self.grad[o : o + p.numel()].view(p.shape)
+                p._kf_grad_live = False
+                p._kf_flat = self
+
+    # ------------------------------------------------------------------ shards
+    @property
+    def shard_range(self) -> tuple[int, int]:
+        lo = self.rank * self.shard_numel
+        return lo, lo + self.shard_numel
+
+    @property
+    def n_decay_local(self) -> int:
+        """Number of leading elements of the local shard that receive weight decay."""
+        lo, hi = self.shard_range
+        return max(0, min(self.n_decay, hi) - lo)
+
+    def optimizer_views(self):
+        """(param shard, grad shard, exp_avg, exp_avg_sq) for the local rank."""
+        lo, hi = self.shard_range
+        return self.param[lo:hi], self.grad[lo:hi], self.exp_avg, self.exp_avg_sq
+
+    # ------------------------------------------------------------------ gradients
+    def zero_grad(self) -> None:
+        """Forget accumulated gradients; the buffer itself is overwritten by the next backward."""
+        for p in self.params:
+            p._kf_grad_live = False
+            p.grad = None
+
+    def finalize_grads(self) -> None:
+        """Make the flat buffer hold every gradient: fold in autograd-produced ``.grad`` tensors, zero
+        the slots nothing wrote, and point ``.grad`` at the flat views."""
+        with torch.no_grad():
+            for p in self.params:
+                slot = p._kf_grad
+                g = p.grad
+                if g is not None and g.data_ptr() != slot.data_ptr():
+                    g = g.to_local() if hasattr(g, "to_local") else g
+                    if p._kf_grad_live:
+                        slot.add_(g.to(slot.dtype))
+                    else:
+                        slot.copy_(g)
+                    p._kf_grad_live = True
+                elif g is None and not p._kf_grad_live:
+                    slot.zero_()
+                p.grad = slot
+
+    # ------------------------------------------------------------------ optimizer state
+    def ensure_optimizer_state(self, optimizer: torch.optim.Optimizer, state_dtype: torch.dtype | None = None) -> None:
+        """Allocate flat moments for the local shard and expose per-parameter views in ``optimizer.state``.
+
+        With world == 1 the views cover whole parameters, so the state dict is exactly what
+        ``torch.optim.AdamW`` would hold.  With world > 1 the per-parameter entries are created on
+        demand by ``full_optimizer_state`` (checkpointing) instead.
+        """
+        dt = state_dtype or self.dtype
+        if self.exp_avg is None:
+            self.exp_avg = torch.zeros(self.shard_numel, dtype=dt, device=self.device)
+            self.exp_avg_sq = torch.zeros(self.shard_numel, dtype=dt, device=self.device)
+            self.step_tensor = torch.zeros((), dtype=torch.float32, device=self.device)
+        if self.world == 1:
+            for p, o in zip(self.params, self.offsets):
+                optimizer.state[p] = {
+                    "step": self.step_tensor,
+                    "exp_avg": self.exp_avg[o : o + p.numel()].view(p.shape),
+                    "exp_avg_sq": self.exp_avg_sq[o : o + p.numel()].view(p.shape),
+                }
+
+    def load_step(self, step: int) -> None:
+        self.step_count = int(step)
+        self.step_tensor.fill_(float(step))
+
+
+def group_module_params(module: nn.Module, prefix: str = "") -> list[tuple[str, nn.Parameter]]:
+    seen, out = set(), []
+    for n, p in module.named_parameters():
+        if id(p) in seen:
+            continue
+        seen.add(id(p))
+        out.append((prefix + n, p))
+    return out
+
+
+def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=None) -> list[FlatParamGroup]:
+    """One flat group per transformer block plus a root group for everything else.
+
+    Returns the groups in forward order (root group last) and records them on the model.
+    """
+    groups: list[FlatParamGroup] = []
+    taken: set[int] = set()
+    layers = getattr(model, "layers", None)
+    if isinstance(layers, nn.ModuleDict):
+        for key, block in layers.items():
+            items = [(n, p) for n, p in group_module_params(block, f"layers.{key}.") if id(p) not in taken]
+            items = [(n, p) for n, p in items if p.requires_grad]
+            if items:
+                groups.append(FlatParamGroup(f"layers.{key}", items, world, rank, allocator))
+                taken.update(id(p) for _, p in items)
+    by_dtype: dict[torch.dtype, list] = {}
+    for n, p in group_module_params(model):
+        if id(p) not in taken and p.requires_grad:
+            by_dtype.setdefault(p.dtype, []).append((n, p))
+    for i, (dt, items) in enumerate(by_dtype.items()):
+        groups.append(FlatParamGroup("root" if i == 0 else f"root.{i}", items, world, rank, allocator))
+    model._kf_flat_groups = groups
+    return groups

@@ -1,0 +1,127 @@
+"""Applies the parallelism / precision / memory transformations to a model in the one order that works:
+
+    tensor parallel -> expert parallel -> fp8 -> activation checkpointing -> sharded data parallel
+
+TP must see whole weights before anything shards them, EP must slice experts before the flat buffers
+are built, the fp8 conversion must happen before checkpointing wraps the block's forward, and the
+data-parallel engine flattens whatever parameters are left on this rank.
+
+Parity: kempnerforge/distributed/parallel.py:5-10,72-122,125-174,250-302,499-597 (same order, same
+``apply_*`` entry points and ``build_parallel_model`` signature; mixed precision = parameters in
+``param_dtype``; AC modes none / full / selective).
+"""
+
+from __future__ import annotations
+
+import logging
+
+import torch
+from torch import nn
+
+from kempnerforge_b200.config.registry import registry
+import kempnerforge_b200.models  # noqa: F401  (registers the built-in model builders)
+from kempnerforge_b200.parallel.engine import DataParallelEngine
+from kempnerforge_b200.parallel.setup import mesh_dim
+
+log = logging.getLogger(__name__)
+
+
+def get_dp_mesh(mesh):
+    """The data-parallel sub-mesh: 1-D ``dp_shard`` or 2-D ``(dp_replicate, dp_shard)``; None if absent."""
+    if mesh is None:
+        return None
+    names = mesh.mesh_dim_names or ()
+    has_rep, has_shard = "dp_replicate" in names, "dp_shard" in names
+    if has_rep and has_shard:
+        return mesh["dp_replicate", "dp_shard"]
+    if has_shard:
+        return mesh["dp_shard"]
+    if has_rep:
+        return mesh["dp_replicate"]
+    return None
+
+
+def dp_process_group(mesh):
+    """One process group spanning every data-parallel rank (replicate x shard), or None."""
+    dp = get_dp_mesh(mesh)
+    if dp is None:
+        return None
+    if dp.ndim == 1:
+        return dp.get_group()
+    return dp._flatten("dp").get_group() if hasattr(dp, "_flatten") else dp.get_group(0)
+
+
+def apply_ac(model: nn.Module, mode: str = "full") -> None:
+    """Activation checkpointing: ``full`` recomputes whole blocks, ``selective`` only attention."""
+    mode = str(mode)
+    if mode not in ("none", "full", "selective"):
+        raise ValueError(f"Unknown activation_checkpointing mode: {mode!r}")
+    n = 0
+    for m in model.modules():
+        if hasattr(m, "ac_mode"):
+            m.ac_mode = mode
+            n += 1
+    log.info("activation checkpointing = %s on %d blocks", mode, n)
+
+
+def apply_float8(model: nn.Module, enable_fsdp_float8_all_gather: bool = True) -> int:
+    """Switch the dense Linear call sites to block-scaled fp8 GEMMs; experts, shared experts and routers
+    keep bf16 (same module filter as the reference).  Returns the number of converted modules."""
+    from kempnerforge_b200.ops import fp8
+
+    return fp8.convert_model(model, skip=("experts", "shared_expert", "router"))
+
+
+def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, **_) -> DataParallelEngine:
+    """Flatten the model's parameters per block and shard optimizer state over the data-parallel group."""
+    pg = dp_process_group(mesh)
+    allocator = None
+    if transport is None:
+        transport = "collective"
+    if transport == "symmetric":
+        from kempnerforge_b200.comm import symmetric
+
+        allocator = symmetric.make_allocator(pg)
+    return DataParallelEngine(model, pg, transport=transport, allocator=allocator)
+
+
+def build_parallel_model(
+    model_config,
+    device: torch.device,
+    device_mesh=None,
+    *,
+    ac_mode: str = "none",
+    param_dtype: torch.dtype = torch.bfloat16,
+    fp8: bool = False,
+    compile_model: bool = False,
+    transport: str | None = None,
+    vlm_config=None,
+    **model_kwargs,
+) -> nn.Module:
+    """Build the registered model and apply TP -> EP -> FP8 -> AC -> sharded DP."""
+    builder = registry.get("model", model_config.model_type)
+    with torch.device(device):  # parameters are drawn on the target device (fp32), then cast
+        model = builder(model_config, **({"vlm_config": vlm_config} if vlm_config is not None else {}), **model_kwargs)
+    model = model.to(device=device, dtype=param_dtype)
+    if hasattr(model, "rope_tables"):
+        model.rope_tables(device, 0, 1)
+
+    _, tp_size, _ = mesh_dim(device_mesh, "tp")
+    if tp_size > 1:
+        from kempnerforge_b200.parallel.tensor_parallel import apply_tensor_parallel
+
+        apply_tensor_parallel(model, device_mesh)
+    if model_config.is_moe and device_mesh is not None:
+        from kempnerforge_b200.parallel.expert_parallel import apply_expert_parallel, ep_group_for
+
+        ep_pg, ep_size = ep_group_for(device_mesh)
+        if ep_size > 1:
+            apply_expert_parallel(model, ep_pg)
+    if fp8:
+        apply_float8(model)
+    if ac_mode and str(ac_mode) != "none":
+        apply_ac(model, str(ac_mode))
+    apply_fsdp2(model, device_mesh, transport=transport)
+    if compile_model:
+        log.info("compile_model is accepted for preset compatibility; this build has no tracing compiler")
+    return model

@@ -1,0 +1,59 @@
+"""Parameter freezing by module alias.
+
+A ``FreezeSpec(module, frozen)`` names an alias (``vision_encoder``, ``adapter``, ``transformer`` ...);
+``module_patterns`` maps the alias to fnmatch patterns over fully-qualified parameter names.  Later specs
+override earlier ones.  ``canonical_freeze_meta`` is what gets stored in checkpoint metadata so a resume
+can detect a changed freeze set-up.
+
+Parity: kempnerforge/training/freeze.py:35-136.
+"""
+
+from __future__ import annotations
+
+import fnmatch
+from collections.abc import Iterable
+
+from torch import nn
+
+
+def freeze_params(model: nn.Module, patterns: Iterable[str], frozen: bool = True) -> int:
+    """Set ``requires_grad = not frozen`` on every parameter whose name matches a pattern; returns the count."""
+    patterns = list(patterns)
+    hit = 0
+    for name, p in model.named_parameters():
+        owner = name.rsplit(".", 1)[0] if "." in name else name
+        if any(fnmatch.fnmatch(name, pat) or fnmatch.fnmatch(owner, pat) for pat in patterns):
+            p.requires_grad_(not frozen)
+            hit += 1
+    return hit
+
+
+def apply_freeze_specs(model: nn.Module, specs, module_patterns: dict[str, list[str]]) -> dict[str, int]:
+    counts = {}
+    for spec in specs:
+        if spec.module not in module_patterns:
+            raise ValueError(f"Unknown freeze module {spec.module!r}; known: {sorted(module_patterns)}")
+        counts[spec.module] = freeze_params(model, module_patterns[spec.module], spec.frozen)
+    return counts
+
+
+def canonical_freeze_meta(specs) -> list[dict]:
+    """Order-independent, de-duplicated (last one wins) description of a freeze list."""
+    latest = {}
+    for spec in specs:
+        latest[spec.module] = bool(spec.frozen)
+    return [{"module": k, "frozen": latest[k]} for k in sorted(latest)]
+
+
+def effective_freeze(vlm_config, step: int):
+    """Static freeze list overlaid by every schedule stage whose start_step <= step."""
+    if vlm_config is None:
+        return []
+    specs = list(vlm_config.freeze)
+    for stage in vlm_config.freeze_schedule:
+        if stage.start_step <= step:
+            specs.extend(stage.specs)
+    latest = {}
+    for spec in specs:
+        latest[spec.module] = spec
+    return [latest[k] for k in sorted(latest)]
