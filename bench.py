@@ -162,23 +162,25 @@ def run_ours(args) -> dict:
         tok = torch.randint(0, vocab, (args.batch_size, seq + 1), generator=gen)
         return {"input_ids": tok[:, :-1].contiguous().pin_memory(), "labels": tok[:, 1:].contiguous().pin_memory()}
 
-    dev_batches = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(4)]
-    for i in range(args.warmup):
-        trainer.train_step([dev_batches[i % 4]])
+    # a different random batch for every step, so nothing can be memorised
+    warm = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(args.warmup)]
+    dev_batches = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(args.steps)]
+    for b in warm:
+        trainer.train_step([b])
     status = kcuda.read_status()
     if status != 0:
         raise RuntimeError(f"native kernel wait status {status} during warm-up")
 
     sampler = ClockSampler(local)
     launches0 = kcuda.LAUNCH_COUNT
-    ms, wall, last = timed_region(torch, dist, world, lambda i: trainer.train_step([dev_batches[i % 4]]), args.steps)
+    ms, wall, last = timed_region(torch, dist, world, lambda i: trainer.train_step([dev_batches[i]]), args.steps)
     launches = kcuda.LAUNCH_COUNT - launches0
     clocks = sampler.stop()
 
-    host_batches = [host_batch() for _ in range(min(args.steps, 8))]
+    host_batches = [host_batch() for _ in range(args.steps)]
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
     ms_e2e, _, last_e2e = timed_region(torch, dist, world,
-                                       lambda i: trainer.train_step([host_batches[i % len(host_batches)]]), args.steps)
+                                       lambda i: trainer.train_step([host_batches[i]]), args.steps)
     tokens_per_step = args.batch_size * seq * world
     value = tokens_per_step / (ms / 1e3)
     e2e = tokens_per_step / (ms_e2e / 1e3)
@@ -222,7 +224,8 @@ def run_reference(args) -> dict:
     try:
         from kempnerforge.config.schema import JobConfig  # noqa: F401
         from kempnerforge.config.loader import load_config
-        from kempnerforge.distributed import build_parallel_model, clip_grad_norm_, init_distributed
+        from kempnerforge.distributed import clip_grad_norm_, init_distributed
+        from kempnerforge.distributed.parallel import build_parallel_model
         from kempnerforge.training.loss import build_loss_fn
         from kempnerforge.training.optimizer import build_optimizer
         from kempnerforge.training.scheduler import build_scheduler
@@ -271,15 +274,16 @@ def run_reference(args) -> dict:
         optimizer.zero_grad()
         return {"loss": loss_val}
 
-    dev_batches = [tuple(t.to(device) for t in host_batch()) for _ in range(4)]
-    for i in range(args.warmup):
-        step(*dev_batches[i % 4])
+    warm = [tuple(t.to(device) for t in host_batch()) for _ in range(args.warmup)]
+    dev_batches = [tuple(t.to(device) for t in host_batch()) for _ in range(args.steps)]
+    for b in warm:
+        step(*b)
     sampler = ClockSampler(local)
-    ms, wall, last = timed_region(torch, dist, world, lambda i: step(*dev_batches[i % 4]), args.steps)
+    ms, wall, last = timed_region(torch, dist, world, lambda i: step(*dev_batches[i]), args.steps)
     clocks = sampler.stop()
-    host_batches = [host_batch() for _ in range(min(args.steps, 8))]
+    host_batches = [host_batch() for _ in range(args.steps)]
     h2d = sum(t.numel() * t.element_size() for t in host_batches[0])
-    ms_e2e, _, _ = timed_region(torch, dist, world, lambda i: step(*host_batches[i % len(host_batches)]), args.steps)
+    ms_e2e, _, _ = timed_region(torch, dist, world, lambda i: step(*host_batches[i]), args.steps)
     tokens_per_step = args.batch_size * seq * world
     value = tokens_per_step / (ms / 1e3)
     base = H200_PUBLISHED_TOKS.get(world)
