@@ -71,6 +71,7 @@ class Attention(nn.Module):
         self.k_norm = RMSNorm(hd) if qk_norm else None
         self.capture_attention_weights = False
         self.last_attention_weights: torch.Tensor | None = None
+        self.tp = None  # TPContext when q/k/v are column-sharded and o row-sharded
 
     def forward(
         self,
@@ -81,6 +82,8 @@ class Attention(nn.Module):
         doc_ids: torch.Tensor | None = None,
         key_padding_mask: torch.Tensor | None = None,
     ) -> torch.Tensor:
+        if self.tp is not None:
+            x = self.tp.before_column_parallel(x)
         b, s, _ = x.shape
         # local head counts follow the weight shapes so a tensor-parallel shard works unchanged
         hd = self.head_dim
@@ -102,4 +105,5 @@ class Attention(nn.Module):
             self.last_attention_weights = probs.detach()
         else:
             out = F.attention(q, k, v, causal=causal, doc_ids=doc_ids, key_padding_mask=key_padding_mask)
-        return F.linear(out.reshape(b, s, h * hd), self.o_proj.weight)
+        y = F.linear(out.reshape(b, s, h * hd), self.o_proj.weight)
+        return self.tp.after_row_parallel(y) if self.tp is not None else y

@@ -22,10 +22,14 @@ class SwiGLUMLP(nn.Module):
         self.gate_proj = nn.Linear(dim, hidden_dim, bias=False)
         self.up_proj = nn.Linear(dim, hidden_dim, bias=False)
         self.down_proj = nn.Linear(hidden_dim, dim, bias=False)
+        self.tp = None  # TPContext when gate/up are column-sharded and down row-sharded
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            x = self.tp.before_column_parallel(x)
         gu = F.fused_linear(x, [self.gate_proj.weight, self.up_proj.weight])
-        return F.linear(F.swiglu_stacked(gu), self.down_proj.weight)
+        y = F.linear(F.swiglu_stacked(gu), self.down_proj.weight)
+        return self.tp.after_row_parallel(y) if self.tp is not None else y
 
 
 _ACTS = {"gelu": nn.GELU, "relu": nn.ReLU, "silu": nn.SiLU}
@@ -37,9 +41,13 @@ class StandardMLP(nn.Module):
         self.up_proj = nn.Linear(dim, hidden_dim, bias=False)
         self.down_proj = nn.Linear(hidden_dim, dim, bias=False)
         self.act = _ACTS[activation]()
+        self.tp = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(self.act(F.linear(x, self.up_proj.weight)), self.down_proj.weight)
+        if self.tp is not None:
+            x = self.tp.before_column_parallel(x)
+        y = F.linear(self.act(F.linear(x, self.up_proj.weight)), self.down_proj.weight)
+        return self.tp.after_row_parallel(y) if self.tp is not None else y
 
 
 registry.register("mlp", "swiglu", lambda dim, hidden: SwiGLUMLP(dim, hidden))

@@ -65,6 +65,7 @@ class MoEMLP(nn.Module):
         self.ep_comm = None  # device-side dispatch context (set by apply_expert_parallel)
         self.local_expert_start = 0
         self.num_local_experts = len(experts)
+        self.tp_input = None  # TPContext of a tensor-parallel model (experts themselves are replicated)
         self._is_swiglu = isinstance(experts[0], SwiGLUMLP) or hasattr(experts[0], "gate_proj")
         if packed_experts:
             stack = lambda name: nn.Parameter(  # noqa: E731
@@ -84,14 +85,19 @@ class MoEMLP(nn.Module):
         """(gate, up, down, layout): layout 'kn' = (E, in, out) packed, 'nk' = (E, out, in) stacked Linears."""
         if self.packed_experts:
             return (self.gate_w if self._is_swiglu else None), self.up_w, self.down_w, "kn"
-        stack = lambda name: grouped.stack_expert_weights([getattr(e, name).weight for e in self.experts])  # noqa: E731
+        stack = lambda name: grouped.stack_expert_weights([getattr(e, name).weight for e in self.expert_modules()])  # noqa: E731
         gate = stack("gate_proj") if self._is_swiglu else None
         return gate, stack("up_proj"), stack("down_proj"), "nk"
 
     def _activation(self):
         if self._is_swiglu:
             return None
-        return self._packed_activation if self.packed_experts else self.experts[0].act
+        return self._packed_activation if self.packed_experts else self.expert_modules()[0].act
+
+    def expert_modules(self) -> list[nn.Module]:
+        """Local expert modules in expert order (a ModuleList, or a ModuleDict keyed by global index under EP)."""
+        ex = self.experts
+        return list(ex.values()) if isinstance(ex, nn.ModuleDict) else list(ex)
 
     def run_experts(self, x_sorted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
         """Grouped expert FFN over rows already sorted by (local) expert."""

@@ -90,10 +90,16 @@ class TransformerBlock(nn.Module):
 
 
 class Transformer(nn.Module):
-    def __init__(self, config: ModelConfig, *, vlm_config=None, num_image_tokens: int = 0) -> None:
+    def __init__(self, config: ModelConfig, *, vlm_config=None, num_image_tokens: int = 0,
+                 layer_ids: list[int] | None = None, with_embedding: bool = True, with_head: bool = True) -> None:
+        """``layer_ids`` / ``with_embedding`` / ``with_head`` build only a slice of the network (a pipeline
+        stage); the layer keys stay the global indices so checkpoint names do not depend on the split."""
         super().__init__()
         self.config = config
-        self.token_embedding: TokenEmbedding | None = TokenEmbedding(config.vocab_size, config.dim)
+        self.is_pipeline_stage = layer_ids is not None
+        self.token_embedding: TokenEmbedding | None = (
+            TokenEmbedding(config.vocab_size, config.dim) if with_embedding else None
+        )
         self._mot_modalities: tuple[str, ...] = ()
         self._moma_modalities: tuple[str, ...] = ()
         self._mot_n_image = 0
@@ -114,7 +120,7 @@ class Transformer(nn.Module):
             for i in range(config.n_layers):
                 blocks[str(i)] = MoMaBlock(config, vlm_config, i)
         else:
-            for i in range(config.n_layers):
+            for i in (range(config.n_layers) if layer_ids is None else layer_ids):
                 blocks[str(i)] = TransformerBlock(config, i)
         self.layers = nn.ModuleDict(blocks)
         self.cross_attention_layers = nn.ModuleDict()
@@ -125,17 +131,18 @@ class Transformer(nn.Module):
             heads, kv_heads = vlm_config.resolved_heads(config.n_heads)
             for j in range(config.n_layers // self._ca_cadence):
                 self.cross_attention_layers[str(j)] = CrossAttentionBlock(config, heads, kv_heads)
-        self.norm: nn.Module | None = build_norm(config.norm_type, config.dim, config.norm_eps)
+        self.norm: nn.Module | None = build_norm(config.norm_type, config.dim, config.norm_eps) if with_head else None
         self.mot_norms = nn.ModuleDict()
         if self._mot_modalities:
             self.mot_norms = nn.ModuleDict(
                 {m: build_norm(config.norm_type, config.dim, config.norm_eps) for m in self._mot_modalities}
             )
-        self.output_head: OutputHead | None = OutputHead(config.dim, config.vocab_size)
-        if config.tie_embeddings:
+        self.output_head: OutputHead | None = OutputHead(config.dim, config.vocab_size) if with_head else None
+        if config.tie_embeddings and with_head and with_embedding:
             self.output_head.tie_weights(self.token_embedding)
         self._rope_cos: torch.Tensor | None = None
         self._rope_sin: torch.Tensor | None = None
+        self.tp = None  # TPContext set by apply_tensor_parallel
         if not any(p.is_meta for p in self.parameters()):
             self.init_weights_and_freqs()
 
@@ -233,6 +240,11 @@ class Transformer(nn.Module):
         start = kv_caches[0].seq_len if kv_caches is not None else 0
         cos, sin = self.rope_tables(h.device, start, seq_len)
         kpm = ctx.key_padding_mask
+        tp = self.tp
+        if tp is not None and tp.sequence_parallel:
+            if seq_len % tp.size:
+                raise ValueError(f"sequence length {seq_len} is not divisible by tp={tp.size}")
+            h = tp.scatter_sequence(h)
 
         if self._moma_modalities or self._mot_modalities:
             kind = "MoMa" if self._moma_modalities else "MoT"
@@ -258,8 +270,9 @@ class Transformer(nn.Module):
         else:
             ca_blocks = list(self.cross_attention_layers.values()) if self._ca_cadence else []
             image_features = ctx.image_features
-            for i, layer in enumerate(self.layers.values()):
-                cache = kv_caches[i] if kv_caches is not None else None
+            for pos, (key, layer) in enumerate(self.layers.items()):
+                i = int(key)
+                cache = kv_caches[pos] if kv_caches is not None else None
                 h = layer(h, cos, sin, kv_cache=cache, doc_ids=doc_ids, key_padding_mask=kpm)
                 if ca_blocks and (i + 1) % self._ca_cadence == 0:
                     j = (i + 1) // self._ca_cadence - 1
@@ -271,13 +284,21 @@ class Transformer(nn.Module):
                         h = ca_blocks[j](h, image_features.to(h.dtype), ctx.image_mask)
             if self.norm is not None:
                 h = self.norm(h)
+        if tp is not None and tp.sequence_parallel:
+            h = tp.gather_sequence(h)
         if ctx.output_slice is not None:
             h = h[:, ctx.output_slice, :]
         return h
 
     def forward(self, tokens=None, *, modality=None, kv_caches=None, doc_ids=None) -> torch.Tensor:
         h = self.forward_hidden(tokens, modality=modality, kv_caches=kv_caches, doc_ids=doc_ids)
-        return self.output_head(h) if self.output_head is not None else h
+        if self.output_head is None:
+            return h
+        head_tp = getattr(self.output_head, "tp", None)
+        if head_tp is None:
+            return self.output_head(h)
+        # vocabulary-parallel head: assemble the full vocabulary for callers that want logits
+        return head_tp.gather_vocab(self.output_head(head_tp.head_input(h)))
 
     def compute_loss(
         self,
@@ -291,6 +312,13 @@ class Transformer(nn.Module):
     ) -> torch.Tensor:
         """Mean next-token cross entropy (+ z-loss) with the head GEMM fused into the loss."""
         h = self.forward_hidden(tokens, modality=modality, doc_ids=doc_ids)
+        head_tp = getattr(self.output_head, "tp", None)
+        if head_tp is not None:
+            from kempnerforge_b200.parallel.tensor_parallel import vocab_parallel_cross_entropy
+
+            logits = self.output_head(head_tp.head_input(h))
+            return vocab_parallel_cross_entropy(
+                logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), head_tp, z_loss_weight)
         return F.linear_cross_entropy(
             h, self.output_head.proj.weight, labels, z_loss_weight, chunk_tokens or 4096
         )

@@ -42,7 +42,7 @@ class DataParallelEngine:
         self.requires_sync = True
         dev = self.groups[0].device
         self.device = dev
-        self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._sq3 = torch.zeros(3, dtype=torch.float32, device=dev)
         self.grad_scale = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._reduced = False
@@ -56,6 +56,8 @@ class DataParallelEngine:
         """Make every rank start from rank ``src``'s weights."""
         root = dist.get_global_rank(self.pg, src) if self.pg is not None else src
         for g in self.groups:
+            if g.local:
+                continue
             dist.broadcast(g.param, src=root, group=self.pg)
 
     def set_requires_gradient_sync(self, flag: bool) -> None:
@@ -66,12 +68,26 @@ class DataParallelEngine:
         """Fold stray autograd gradients into the flat buffers and reduce them across ranks."""
         for g in self.groups:
             g.finalize_grads()
+        if getattr(self.model, "tp", None) is not None:
+            from kempnerforge_b200.parallel.tensor_parallel import sync_partial_grads
+
+            sync_partial_grads(self.model)
+        ep_group = getattr(self.model, "ep_group", None)
+        if ep_group is not None and not getattr(self.model, "ep_in_dp", False) and self.requires_sync:
+            # EP peers route the *same* batch, so every expert saw each token once per peer: undo that factor
+            ep = dist.get_world_size(ep_group)
+            for g in self.groups:
+                if g.ep_sharded:
+                    g.grad.div_(ep)
         if self.world > 1 and self.requires_sync:
             self._reduce_gradients()
         self._reduced = True
 
     def _reduce_gradients(self) -> None:
         for g in self.groups:
+            if g.local:  # rank-private parameters: the gradient is complete, only the loss averaging applies
+                g.grad.div_(self.world)
+                continue
             if g.grad.is_cuda and dist.get_backend(self.pg) == "nccl":
                 lo, hi = g.shard_range
                 dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg)
@@ -79,25 +95,44 @@ class DataParallelEngine:
                 dist.all_reduce(g.grad, group=self.pg)
                 g.grad.div_(self.world)
 
-    def clip_grad_norm(self, max_norm: float | None) -> torch.Tensor:
-        """Global gradient L2 norm (pre-clip, device scalar); sets ``grad_scale`` for the optimizer."""
-        use_native = self.groups[0].grad.is_cuda and self.groups[0].dtype in (torch.bfloat16, torch.float32)
-        if use_native:
+    def _sumsq_into(self, x: torch.Tensor, slot: int) -> None:
+        if x.numel() == 0:
+            return
+        if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32):
             from kempnerforge_b200.ops import cuda as kcuda
 
-            first = True
-            for g in self.groups:
-                lo, hi = g.shard_range
-                kcuda.sumsq(g.grad[lo:hi], self._sq, accumulate=not first)
-                first = False
+            kcuda.sumsq(x, self._sq3[slot : slot + 1], accumulate=True)
         else:
-            self._sq.zero_()
-            for g in self.groups:
-                lo, hi = g.shard_range
-                self._sq += g.grad[lo:hi].float().pow(2).sum()
+            self._sq3[slot] += x.float().pow(2).sum()
+
+    def clip_grad_norm(self, max_norm: float | None, extra_groups=()) -> torch.Tensor:
+        """Global gradient L2 norm (pre-clip, device scalar); sets ``grad_scale`` for the optimizer.
+
+        Squared sums are kept in three buckets: tensors replicated over the model-parallel groups, tensor-parallel
+        shards (summed over the TP group) and expert-parallel shards (summed over the EP group).  Every bucket is
+        first summed over the data-parallel shards; ``extra_groups`` (pipeline stages) are summed last.
+        """
+        self._sq3.zero_()
+        for g in self.groups:
+            lo, hi = g.shard_range
+            if g.ep_sharded:
+                self._sumsq_into(g.grad[lo:hi], 2)
+                continue
+            cut = min(max(g.n_tp_sharded, lo), hi)
+            self._sumsq_into(g.grad[lo:cut], 1)
+            self._sumsq_into(g.grad[cut:hi], 0)
         if self.world > 1:
-            dist.all_reduce(self._sq, group=self.pg)
-        torch.sqrt(self._sq, out=self.grad_norm)
+            dist.all_reduce(self._sq3, group=self.pg)
+        tp = getattr(self.model, "tp", None)
+        if tp is not None:
+            dist.all_reduce(self._sq3[1:2], group=tp.group)
+        ep_group = getattr(self.model, "ep_group", None)
+        if ep_group is not None and not getattr(self.model, "ep_in_dp", False):
+            dist.all_reduce(self._sq3[2:3], group=ep_group)
+        total = self._sq3.sum().reshape(1)
+        for grp in extra_groups:
+            dist.all_reduce(total, group=grp)
+        torch.sqrt(total, out=self.grad_norm)
         if max_norm is not None and max_norm > 0:
             torch.clamp(max_norm / (self.grad_norm + 1e-6), max=1.0, out=self.grad_scale)
         else:
@@ -114,6 +149,8 @@ class DataParallelEngine:
         """Publish the updated shards so that every rank holds the full new parameters."""
         if self.world > 1:
             for g in self.groups:
+                if g.local:
+                    continue
                 lo, hi = g.shard_range
                 dist.all_gather_into_tensor(g.param, g.param[lo:hi].clone(), group=self.pg)
 
@@ -125,7 +162,7 @@ class DataParallelEngine:
     # ------------------------------------------------------------------ checkpoint helpers
     def full_optimizer_state(self, g: FlatParamGroup) -> tuple[torch.Tensor, torch.Tensor]:
         """Whole-unit moment buffers assembled from every rank's shard."""
-        if self.world == 1:
+        if self.world == 1 or g.local:
             return g.exp_avg, g.exp_avg_sq
         out = []
         for shard in (g.exp_avg, g.exp_avg_sq):

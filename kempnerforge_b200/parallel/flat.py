@@ -43,8 +43,14 @@ class FlatParamGroup:
         world: int = 1,
         rank: int = 0,
         allocator: Callable[[int, torch.dtype, torch.device], torch.Tensor] | None = None,
+        local: bool = False,
     ) -> None:
         self.name = name
+        # a "local" group holds parameters that exist only on this rank (expert-parallel experts inside the
+        # data-parallel group): it is neither reduced nor sharded across the data-parallel ranks
+        self.local = local
+        if local:
+            world, rank = 1, 0
         self.world, self.rank = world, rank
         items = [(n, p) for n, p in named_params if p.requires_grad]
         if not items:
@@ -57,6 +63,11 @@ class FlatParamGroup:
         align = max(1, ALIGN_BYTES // elem)
         decay = [(n, p) for n, p in items if _should_decay(n, p)]
         rest = [(n, p) for n, p in items if not _should_decay(n, p)]
+        # tensor-parallel shards first: their squared norm has to be summed over the TP group, while the
+        # replicated tensors behind the boundary count once (a stable partition keeps q|k|v and gate|up adjacent)
+        is_tp = lambda p: getattr(p, "_kf_shard", ("", 0))[0] == "tp"  # noqa: E731
+        n_tp_params = sum(1 for _, p in decay if is_tp(p))
+        decay = [x for x in decay if is_tp(x[1])] + [x for x in decay if not is_tp(x[1])]
         self.names: list[str] = []
         self.params: list[nn.Parameter] = []
         self.offsets: list[int] = []
@@ -69,6 +80,9 @@ class FlatParamGroup:
         self.n_decay = self.offsets[len(decay)] if rest else off
         if not decay:
             self.n_decay = 0
+        all_items = decay + rest
+        self.n_tp_sharded = (self.offsets[n_tp_params] if n_tp_params < len(all_items) else off) if n_tp_params else 0
+        self.ep_sharded = False  # set by flatten_model for expert groups of an expert-parallel model
         # pad so that every rank's shard has the same, aligned length
         chunk = align * world
         self.numel = -(-off // chunk) * chunk
@@ -174,19 +188,33 @@ def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=Non
     """
     groups: list[FlatParamGroup] = []
     taken: set[int] = set()
+    ep_local = bool(getattr(model, "ep_in_dp", False))
+
+    has_ep = getattr(model, "ep_group", None) is not None
+
+    def is_local(p) -> bool:
+        return has_ep and (getattr(p, "_kf_ep_local", False) or getattr(p, "_kf_shard", ("", 0))[0] == "ep")
+
+    def add(name: str, items) -> None:
+        items = [(n, p) for n, p in items if id(p) not in taken and p.requires_grad]
+        shared = [(n, p) for n, p in items if not is_local(p)]
+        mine = [(n, p) for n, p in items if is_local(p)]
+        if shared:
+            groups.append(FlatParamGroup(name, shared, world, rank, allocator))
+        if mine:
+            groups.append(FlatParamGroup(name + ".experts", mine, world, rank, None if ep_local else allocator, local=ep_local))
+            groups[-1].ep_sharded = True
+        taken.update(id(p) for _, p in items)
+
     layers = getattr(model, "layers", None)
     if isinstance(layers, nn.ModuleDict):
         for key, block in layers.items():
-            items = [(n, p) for n, p in group_module_params(block, f"layers.{key}.") if id(p) not in taken]
-            items = [(n, p) for n, p in items if p.requires_grad]
-            if items:
-                groups.append(FlatParamGroup(f"layers.{key}", items, world, rank, allocator))
-                taken.update(id(p) for _, p in items)
+            add(f"layers.{key}", group_module_params(block, f"layers.{key}."))
     by_dtype: dict[torch.dtype, list] = {}
     for n, p in group_module_params(model):
         if id(p) not in taken and p.requires_grad:
             by_dtype.setdefault(p.dtype, []).append((n, p))
     for i, (dt, items) in enumerate(by_dtype.items()):
-        groups.append(FlatParamGroup("root" if i == 0 else f"root.{i}", items, world, rank, allocator))
+        add("root" if i == 0 else f"root.{i}", items)
     model._kf_flat_groups = groups
     return groups

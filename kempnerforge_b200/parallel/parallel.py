@@ -96,6 +96,7 @@ def build_parallel_model(
     compile_model: bool = False,
     transport: str | None = None,
     vlm_config=None,
+    ep_in_dp: bool = False,
     **model_kwargs,
 ) -> nn.Module:
     """Build the registered model and apply TP -> EP -> FP8 -> AC -> sharded DP."""
@@ -114,9 +115,9 @@ def build_parallel_model(
     if model_config.is_moe and device_mesh is not None:
         from kempnerforge_b200.parallel.expert_parallel import apply_expert_parallel, ep_group_for
 
-        ep_pg, ep_size = ep_group_for(device_mesh)
+        ep_pg, ep_size = ep_group_for(device_mesh, ep_in_dp)
         if ep_size > 1:
-            apply_expert_parallel(model, ep_pg)
+            apply_expert_parallel(model, ep_pg, ep_in_dp)
     if fp8:
         apply_float8(model)
     if ac_mode and str(ac_mode) != "none":

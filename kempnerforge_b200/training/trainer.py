@@ -86,6 +86,10 @@ class Trainer:
         tc = config.train
         self.rank, self.local_rank, self.world_size = get_world_info()
         self.mesh = init_distributed(config.distributed, tc.seed) if init_dist else None
+        if not init_dist:
+            from kempnerforge_b200.parallel.setup import set_seed
+
+            set_seed(tc.seed)
         config.validate(self.world_size)
         self.device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.dp_rank, self.dp_size = get_dp_info(self.mesh)
@@ -111,6 +115,7 @@ class Trainer:
                 config.model, self.device, self.mesh,
                 ac_mode=str(tc.activation_checkpointing), param_dtype=tc.param_dtype,
                 fp8=tc.is_fp8, compile_model=False, transport=transport,
+                ep_in_dp=config.distributed.ep_in_dp and config.distributed.ep > 1,
             )
         self.engine = getattr(self.model, "_kf_engine", None)
         self.optimizer = build_optimizer(self.model, config.optimizer)

@@ -1,0 +1,228 @@
+"""Multi-rank behaviour on CPU (gloo, world sizes 2 and 4): every parallel mode must reproduce the
+single-process loss and update."""
+
+import os
+import socket
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+TINY = dict(dim=64, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=256, max_seq_len=32)
+MOE = dict(dim=64, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=256, max_seq_len=32, num_experts=4, moe_top_k=2,
+           moe_router="softmax_topk", moe_aux_loss_weight=0.0)
+
+
+INIT_FILE = os.path.join(tempfile.gettempdir(), f"kfb200_init_{os.getpid()}.pt")
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn, out_dir, args):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.set_num_threads(1)
+    try:
+        result = fn(rank, world, *args)
+        torch.save(result, os.path.join(out_dir, f"r{rank}.pt"))
+    except Exception:
+        with open(os.path.join(out_dir, f"err{rank}.txt"), "w") as fh:
+            fh.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_ranks(fn, world, *args):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_entry, args=(world, _free_port(), fn, d, args), nprocs=world, join=True)
+        errs = [open(os.path.join(d, f)).read() for f in sorted(os.listdir(d)) if f.startswith("err")]
+        assert not errs, "\n".join(errs)
+        return [torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def _job(model, world_dims, **train):
+    from kempnerforge_b200.config import config_from_dict
+
+    return config_from_dict({
+        "model": model,
+        "train": {"batch_size": 2, "seq_len": 32, "max_steps": 10, "mixed_precision": "fp32", "seed": 0,
+                  "grad_clip_norm": 1.0, **train},
+        "optimizer": {"lr": 1e-2},
+        "scheduler": {"warmup_steps": 0, "name": "constant"},
+        "distributed": world_dims,
+        "metrics": {"log_interval": 1000},
+    })
+
+
+def _batches(n, seed=7):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        tok = torch.randint(0, 256, (2, 33), generator=g)
+        out.append({"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()})
+    return out
+
+
+def _single_process_reference(model_cfg, batches_per_step, steps=2, accum=1):
+    """Loss / grad-norm trajectory and final weights of one process seeing all the data."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {}, grad_accum_steps=len(batches_per_step[0]))
+    t = Trainer(cfg, init_dist=False)
+    torch.save(t.model.state_dict(), INIT_FILE)
+    traj = [t.train_step(list(bs)) for bs in batches_per_step]
+    return traj, {n: p.detach().clone() for n, p in t.model.named_parameters()}
+
+
+# ------------------------------------------------------------------ workers
+def _dp_worker(rank, world, model_cfg, steps):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_job(model_cfg, {"dp_shard": world}))
+    data = _batches(world * steps)
+    traj = [t.train_step([data[s * world + rank]]) for s in range(steps)]
+    return traj, {n: p.detach().clone() for n, p in t.model.named_parameters()}
+
+
+def _tp_worker(rank, world, model_cfg, steps, sp):
+    from kempnerforge_b200.parallel.tensor_parallel import apply_tensor_parallel  # noqa: F401
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {"tp": world, "dp_shard": 1})
+    t = Trainer(cfg)
+    if not sp:  # rebuild the context without sequence parallelism
+        t.model.tp.sequence_parallel = False
+        for p in t.model.parameters():
+            if getattr(p, "_kf_tp_partial_grad", False):
+                p._kf_tp_partial_grad = False
+    data = _batches(steps)
+    traj = [t.train_step([data[s]]) for s in range(steps)]
+    return traj, {n: (p.detach().clone(), getattr(p, "_kf_shard", None)) for n, p in t.model.named_parameters()}
+
+
+def _ep_worker(rank, world, model_cfg, steps, in_dp):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    dims = {"ep": world, "ep_in_dp": True, "dp_shard": world} if in_dp else {"ep": world, "dp_shard": 1}
+    t = Trainer(_job(model_cfg, dims))
+    if in_dp:
+        data = _batches(world * steps)
+        traj = [t.train_step([data[s * world + rank]]) for s in range(steps)]
+    else:
+        data = _batches(steps)
+        traj = [t.train_step([data[s]]) for s in range(steps)]
+    params = {n: (p.detach().clone(), getattr(p, "_kf_shard", None)) for n, p in t.model.named_parameters()}
+    return traj, params
+
+
+def _pp_worker(rank, world, model_cfg, steps, schedule, n_micro, init_file):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {"pp": world, "dp_shard": 1, "pp_schedule": schedule}, grad_accum_steps=n_micro)
+    t = Trainer(cfg)
+    # stages draw their own random weights (seed + stage index); start from the single-process weights instead
+    missing = t.model.load_state_dict(torch.load(init_file), strict=False)
+    assert not missing.missing_keys
+    data = _batches(n_micro * steps)
+    traj = [t.train_step(data[s * n_micro : (s + 1) * n_micro]) for s in range(steps)]
+    return traj, {n: p.detach().clone() for n, p in t.model.named_parameters()}
+
+
+def _params_close(got, want, atol=3e-5, frac=2e-3):
+    """Adam turns a sign flip of a near-zero gradient into an update of size lr, so a different summation order
+    may move a few elements; require that all but a tiny fraction agree tightly."""
+    bad = ((got - want).abs() > atol).float().mean().item()
+    return bad <= frac
+
+
+def _close(a, b, tol=2e-4):
+    return abs(a - b) <= tol * max(1.0, abs(b))
+
+
+# ------------------------------------------------------------------ tests
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_data_parallel_matches_single_process(world):
+    steps = 2
+    data = _batches(world * steps)
+    ref_traj, ref_params = _single_process_reference(TINY, [data[s * world : (s + 1) * world] for s in range(steps)])
+    results = run_ranks(_dp_worker, world, TINY, steps)
+    for s in range(steps):
+        mean_loss = sum(r[0][s]["loss"] for r in results) / world
+        assert _close(mean_loss, ref_traj[s]["loss"])
+        assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
+    for r in results:  # every rank ends with the same, correct weights
+        for n, p in r[1].items():
+            assert torch.allclose(p, ref_params[n], atol=2e-5), n
+
+
+@pytest.mark.parametrize("sp", [True, False])
+def test_tensor_parallel_matches_single_process(sp):
+    steps, world = 2, 2
+    data = _batches(steps)
+    ref_traj, ref_params = _single_process_reference(TINY, [[data[s]] for s in range(steps)])
+    results = run_ranks(_tp_worker, world, TINY, steps, sp)
+    for s in range(steps):
+        for r in results:
+            assert _close(r[0][s]["loss"], ref_traj[s]["loss"])
+            assert _close(r[0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
+    for n, full in ref_params.items():
+        shards = [r[1][n] for r in results]
+        if shards[0][1] is not None:
+            dim = shards[0][1][1]
+            got = torch.cat([s[0] for s in shards], dim=dim)
+        else:
+            got = shards[0][0]
+            assert torch.allclose(shards[0][0], shards[1][0], atol=1e-6), n
+        assert _params_close(got, full), n
+
+
+@pytest.mark.parametrize("in_dp", [False, True])
+@pytest.mark.parametrize("packed", [False, True])
+def test_expert_parallel_matches_single_process(in_dp, packed):
+    steps, world = 2, 2
+    model_cfg = dict(MOE, moe_packed_experts=packed)
+    if in_dp:
+        data = _batches(world * steps)
+        per_step = [data[s * world : (s + 1) * world] for s in range(steps)]
+    else:
+        data = _batches(steps)
+        per_step = [[data[s]] for s in range(steps)]
+    ref_traj, ref_params = _single_process_reference(model_cfg, per_step)
+    results = run_ranks(_ep_worker, world, model_cfg, steps, in_dp)
+    for s in range(steps):
+        mean_loss = sum(r[0][s]["loss"] for r in results) / world
+        assert _close(mean_loss, ref_traj[s]["loss"])
+        assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 2e-3)
+    for rank, r in enumerate(results):
+        for n, (p, shard) in r[1].items():
+            full = ref_params[n]
+            if shard is not None:  # packed experts: a dim-0 slice
+                per = full.shape[0] // world
+                full = full[rank * per : (rank + 1) * per]
+            assert _params_close(p, full), n
+
+
+@pytest.mark.parametrize("schedule,world,n_micro", [("1f1b", 2, 4), ("gpipe", 2, 2), ("1f1b", 4, 4)])
+def test_pipeline_parallel_matches_single_process(schedule, world, n_micro):
+    steps = 2
+    data = _batches(n_micro * steps)
+    ref_traj, ref_params = _single_process_reference(TINY, [data[s * n_micro : (s + 1) * n_micro] for s in range(steps)])
+    results = run_ranks(_pp_worker, world, TINY, steps, schedule, n_micro, INIT_FILE)
+    for s in range(steps):
+        for r in results:
+            assert _close(r[0][s]["loss"], ref_traj[s]["loss"])
+            assert _close(r[0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
+    seen = set()
+    for r in results:
+        for n, p in r[1].items():
+            assert _params_close(p, ref_params[n]), n
+            seen.add(n)
+    assert seen == set(ref_params)  # the stages together own every parameter exactly under its global name
