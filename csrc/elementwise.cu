@@ -106,12 +106,13 @@ kf_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   }
 }
 
-// dx = r*g - x*r^3*mean(g*x) with g = dy*w;  dw partial = sum_rows dy*x*r (per block, fp32).
+// dx = [dx_in +] r*g - x*r^3*mean(g*x) with g = dy*w;  dw partial = sum_rows dy*x*r (per block, fp32).
+// dx_in (optional) is the gradient arriving over the residual connection; it may alias dx.
 __global__ void __launch_bounds__(NORM_THREADS)
 kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int D,
-               int add_to_dx) {
+               const __nv_bfloat16* __restrict__ dx_in) {
   __shared__ float red[40];
   const int nvec = D >> 3;
   F8 dw_acc[NORM_CACHE];
@@ -141,11 +142,11 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
     for (int v = threadIdx.x; v < nvec; v += NORM_THREADS, ++c) {
       F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
       F8 o;
-      if (add_to_dx) o = load8(dxr + v * 8);
+      if (dx_in) o = load8(dx_in + size_t(row) * D + v * 8);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float d = r * g.v[i] * ww.v[i] - a.v[i] * coef;
-        o.v[i] = add_to_dx ? o.v[i] + d : d;
+        o.v[i] = dx_in ? o.v[i] + d : d;
         const float dwv = g.v[i] * a.v[i] * r;
         if (c < NORM_CACHE) dw_acc[c].v[i] += dwv;
         else my_partial[v * 8 + i] += dwv;
@@ -461,14 +462,14 @@ int kf_rmsnorm_fwd_bf16(const void* x, const void* w, void* y, void* rstd, int r
 int kf_rmsnorm_bwd_blocks(int rows) { return rows < 148 * 2 ? rows : 148 * 2; }
 
 int kf_rmsnorm_bwd_bf16(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
-                        void* dw_partial, void* dw_bf16, void* dw_f32, int rows, int D, int add_to_dx,
+                        void* dw_partial, void* dw_bf16, void* dw_f32, int rows, int D, const void* dx_in,
                         void* stream) {
   using namespace kf;
   if (D % 8) return 1;
   const int nb = kf_rmsnorm_bwd_blocks(rows);
   kf_rmsnorm_bwd<<<nb, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)rstd,
-      (__nv_bfloat16*)dx, (float*)dw_partial, rows, D, add_to_dx);
+      (__nv_bfloat16*)dx, (float*)dw_partial, rows, D, (const __nv_bfloat16*)dx_in);
   kf_colsum_partials<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
       (const float*)dw_partial, (__nv_bfloat16*)dw_bf16, (float*)dw_f32, nb, D);
   KF_LAUNCH_CHECK();

@@ -18,6 +18,8 @@ rules, cross-attention cadence, MoT / MoMa dispatch).
 
 from __future__ import annotations
 
+import os
+
 import torch
 from torch import nn
 from torch.utils.checkpoint import checkpoint
@@ -33,6 +35,9 @@ from kempnerforge_b200.models.moe import MoEMLP, build_moe
 from kempnerforge_b200.models.norm import build_norm
 from kempnerforge_b200.models.position import precompute_rope_frequencies
 from kempnerforge_b200.ops import functional as F
+
+
+_FUSED_BLOCK_OFF = bool(os.environ.get("KF_DISABLE_FUSED_BLOCK"))
 
 
 class TransformerBlock(nn.Module):
@@ -82,6 +87,11 @@ class TransformerBlock(nn.Module):
         return x + self.mlp(self.mlp_norm(x))
 
     def forward(self, x, rope_cos, rope_sin, *, kv_cache: KVCache | None = None, doc_ids=None, key_padding_mask=None):
+        if x.is_cuda and self.ac_mode in ("none", "full") and not _FUSED_BLOCK_OFF:
+            from kempnerforge_b200.ops import fused_block
+
+            if F.use_native(x) and fused_block.dense_block_supported(self, x, kv_cache, doc_ids, key_padding_mask):
+                return fused_block.dense_block(self, x, rope_cos, rope_sin)
         if self.ac_mode == "full" and self.training and torch.is_grad_enabled() and kv_cache is None:
             return checkpoint(
                 self._body, x, rope_cos, rope_sin, None, doc_ids, key_padding_mask, use_reentrant=False

@@ -1,0 +1,76 @@
+"""Vision encoders: a deterministic random stub and HuggingFace SigLIP2 / CLIP towers.
+
+Every encoder maps pixel values (B, 3, H, W) to patch features (B, num_tokens, feature_dim) and exposes
+``num_tokens`` and ``feature_dim``.  The random encoder has no weights worth training: it produces, for a
+given image content, always the same pseudo-random features, which is all the plumbing tests need.
+
+Parity: kempnerforge/model/vision.py:43-200 (registry keys ``random`` / ``siglip2`` / ``clip``; defaults of the
+stub 16 tokens x 768; HF towers via ``AutoModel(...).vision_model``; CLIP's class token is dropped; the token
+count of an HF tower is (image_size // patch_size)^2).
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from kempnerforge_b200.config.registry import registry
+
+
+class VisionEncoder(nn.Module):
+    num_tokens: int
+    feature_dim: int
+
+
+class RandomVisionEncoder(VisionEncoder):
+    def __init__(self, num_tokens: int = 16, feature_dim: int = 768) -> None:
+        super().__init__()
+        self.num_tokens, self.feature_dim = num_tokens, feature_dim
+        # a fixed random projection of coarse image statistics: deterministic per image, different across images
+        gen = torch.Generator().manual_seed(1234)
+        self.register_buffer("basis", torch.randn(3 * 16, num_tokens * feature_dim, generator=gen) / 7.0, persistent=False)
+        self.anchor = nn.Parameter(torch.zeros(1))  # lets ``.parameters()`` / dtype queries work
+
+    def forward(self, pixel_values: torch.Tensor) -> torch.Tensor:
+        b = pixel_values.shape[0]
+        coarse = torch.nn.functional.adaptive_avg_pool2d(pixel_values.float(), 4).reshape(b, -1)
+        feats = torch.tanh(coarse @ self.basis.float()).reshape(b, self.num_tokens, self.feature_dim)
+        return feats.to(self.anchor.dtype) + 0.0 * self.anchor
+
+
+class HFVisionEncoder(VisionEncoder):
+    def __init__(self, path: str, drop_cls: bool, num_tokens: int | None = None, feature_dim: int | None = None) -> None:
+        super().__init__()
+        from transformers import AutoModel
+
+        full = AutoModel.from_pretrained(path)
+        self.model = getattr(full, "vision_model", full)
+        cfg = self.model.config
+        self.drop_cls = drop_cls
+        self.num_tokens = num_tokens or (cfg.image_size // cfg.patch_size) ** 2
+        self.feature_dim = feature_dim or cfg.hidden_size
+
+    def forward(self, pixel_values: torch.Tensor) -> torch.Tensor:
+        dtype = next(self.model.parameters()).dtype
+        hidden = self.model(pixel_values=pixel_values.to(dtype)).last_hidden_state
+        return hidden[:, 1:] if self.drop_cls else hidden
+
+
+@registry.register("vision_encoder", "random")
+def _build_random(path: str = "", num_tokens: int | None = None, feature_dim: int | None = None):
+    return RandomVisionEncoder(num_tokens or 16, feature_dim or 768)
+
+
+@registry.register("vision_encoder", "siglip2")
+def _build_siglip2(path: str, num_tokens: int | None = None, feature_dim: int | None = None):
+    return HFVisionEncoder(path, drop_cls=False, num_tokens=num_tokens, feature_dim=feature_dim)
+
+
+@registry.register("vision_encoder", "clip")
+def _build_clip(path: str, num_tokens: int | None = None, feature_dim: int | None = None):
+    return HFVisionEncoder(path, drop_cls=True, num_tokens=num_tokens, feature_dim=feature_dim)
+
+
+def build_vision_encoder(config) -> VisionEncoder:
+    return registry.get("vision_encoder", config.type)(
+        config.path, num_tokens=config.num_tokens or None, feature_dim=config.feature_dim or None)

@@ -47,7 +47,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_bf16": [vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
-        "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp],
+        "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
         "kf_rope_bf16": [vp, vp, vp, vp, ll, i, i, i, i, i, vp],
         "kf_swiglu_fwd_bf16": [vp, vp, ll, i, vp],
         "kf_swiglu_bwd_bf16": [vp, vp, vp, ll, i, vp],
@@ -186,17 +186,18 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float):
     return y, rstd
 
 
-def rmsnorm_bwd(dy, x, w, rstd, dx_accum: torch.Tensor | None = None):
-    """Returns (dx, dw).  With ``dx_accum`` the input gradient is added into that tensor instead."""
+def rmsnorm_bwd(dy, x, w, rstd, residual_grad: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                dw_out: torch.Tensor | None = None):
+    """Returns (dx, dw).  ``residual_grad`` is added to dx inside the kernel (it may be the same tensor as ``out``)."""
     rows, d = x.shape
     nb = lib().kf_rmsnorm_bwd_blocks(rows)
     partial = torch.empty(nb * d, dtype=torch.float32, device=x.device)
-    dx = dx_accum if dx_accum is not None else torch.empty_like(x)
-    dw = torch.empty(d, dtype=torch.bfloat16, device=x.device)
+    dx = out if out is not None else torch.empty_like(x)
+    dw = dw_out if dw_out is not None else torch.empty(d, dtype=torch.bfloat16, device=x.device)
     _check(
         lib().kf_rmsnorm_bwd_bf16(
             dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), partial.data_ptr(),
-            dw.data_ptr(), None, rows, d, int(dx_accum is not None), _stream(),
+            dw.data_ptr(), None, rows, d, residual_grad.data_ptr() if residual_grad is not None else None, _stream(),
         ),
         "kf_rmsnorm_bwd_bf16",
     )

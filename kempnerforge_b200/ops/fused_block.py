@@ -1,0 +1,211 @@
+"""One autograd node for a whole dense transformer block on the native kernels.
+
+Forward:  x -> RMSNorm -> fused QKV GEMM -> RoPE -> attention -> O GEMM -> +x
+            -> RMSNorm -> fused gate|up GEMM -> SwiGLU -> down GEMM -> +residual
+With ``recompute=True`` (full activation checkpointing) only the block input is kept; backward
+re-runs the forward *except the down projection* (its output is not needed for any gradient),
+which removes one of the four large GEMMs from the recomputation.  Without recomputation the
+intermediates are kept and backward starts immediately.
+
+Backward is written out by hand: every weight-gradient GEMM writes (or accumulates) straight
+into the parameter's flat gradient buffer, the two residual-gradient additions are folded into
+the RMSNorm backward kernel, and no autograd graph is built for the block's interior.
+
+Semantics are those of kempnerforge/model/transformer.py:82-103 with the activation
+checkpointing of kempnerforge/distributed/parallel.py:90-122.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from kempnerforge_b200.ops import cuda as kc
+
+
+def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weights) -> list:
+    """dW for row-stacked weights; deposits into flat gradient views when present, else returns tensors."""
+    slots = [getattr(w, "_kf_grad", None) for w in weights]
+    if all(s is not None for s in slots) and kc.rows_adjacent(slots):
+        live = [getattr(w, "_kf_grad_live", False) for w in weights]
+        if all(live) or not any(live):
+            kc.gemm(dy2, x2, a_kmajor=False, b_kmajor=False, out=kc.stack_rows(slots), accumulate=live[0])
+            for w in weights:
+                w._kf_grad_live = True
+            return [None] * len(weights)
+    dw = kc.gemm(dy2, x2, a_kmajor=False, b_kmajor=False)
+    out, row = [], 0
+    for w, slot in zip(weights, slots):
+        piece = dw[row : row + w.shape[0]]
+        row += w.shape[0]
+        if slot is None:
+            out.append(piece)
+        else:
+            if getattr(w, "_kf_grad_live", False):
+                slot.add_(piece)
+            else:
+                slot.copy_(piece)
+                w._kf_grad_live = True
+            out.append(None)
+    return out
+
+
+def _norm_wgrad(weight, dw):
+    slot = getattr(weight, "_kf_grad", None)
+    if slot is None:
+        return dw.to(weight.dtype)
+    if getattr(weight, "_kf_grad_live", False):
+        slot.add_(dw)
+    else:
+        slot.copy_(dw)
+        weight._kf_grad_live = True
+    return None
+
+
+def _attention_fwd(q, k, v, causal, scale):
+    """(out, ctx) with ctx holding what the backward needs."""
+    if kc.attn_supported(q, k, v, causal):
+        out, lse = kc.attn_fwd(q, k, v, causal, None, scale)
+        return out, ("native", lse)
+    with torch.enable_grad():
+        ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o = torch.nn.functional.scaled_dot_product_attention(
+            ql.transpose(1, 2), kl.transpose(1, 2), vl.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=kl.shape[2] != ql.shape[2]).transpose(1, 2)
+    return o.detach(), ("library", (ql, kl, vl, o))
+
+
+def _attention_bwd(dout, q, k, v, out, actx, causal, scale):
+    kind, saved = actx
+    if kind == "native":
+        return kc.attn_bwd(dout, q, k, v, out, saved, causal, None, scale)
+    ql, kl, vl, o = saved
+    return torch.autograd.grad(o, (ql, kl, vl), dout)
+
+
+class DenseBlockFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, wn1, wq, wk, wv, wo, wn2, wg, wu, wd, eps, head_dim, recompute):
+        b, s, d = x.shape
+        x2 = x.reshape(b * s, d)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ctx.meta = (b, s, d, eps, head_dim, recompute)
+        ctx.weights = (wn1, wq, wk, wv, wo, wn2, wg, wu, wd)
+        inter = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=True, keep=not recompute)
+        y = inter.pop("y")
+        if recompute:
+            ctx.save_for_backward(x2, cos, sin)
+            ctx.inter = None
+        else:
+            ctx.save_for_backward(x2, cos, sin)
+            ctx.inter = inter
+        return y.view(b, s, d)
+
+    @staticmethod
+    def _run_forward(x2, cos, sin, weights, meta, need_output: bool, keep: bool) -> dict:
+        wn1, wq, wk, wv, wo, wn2, wg, wu, wd = weights
+        b, s, d, eps, hd, _ = meta
+        h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        n1, rstd1 = kc.rmsnorm_fwd(x2, wn1, eps)
+        qkv = kc.gemm(n1, kc.stack_rows([wq, wk, wv]))
+        qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+        kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)  # in place: each element is read and written by one thread
+        q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
+        scale = 1.0 / math.sqrt(hd)
+        attn, actx = _attention_fwd(q, k, v, True, scale)
+        attn2 = attn.reshape(b * s, h * hd)
+        h1 = kc.gemm(attn2, wo)
+        h1.add_(x2)
+        n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)
+        gu = kc.gemm(n2, kc.stack_rows([wg, wu]))
+        hmid = kc.swiglu_fwd(gu)
+        out = {}
+        if need_output:
+            y = kc.gemm(hmid, wd)
+            y.add_(h1)
+            out["y"] = y
+        if keep:
+            out.update(n1=n1, rstd1=rstd1, qkv4=qkv4, attn2=attn2, actx=actx, h1=h1, n2=n2, rstd2=rstd2, gu=gu, hmid=hmid)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, cos, sin = ctx.saved_tensors
+        b, s, d, eps, hd, recompute = ctx.meta
+        wn1, wq, wk, wv, wo, wn2, wg, wu, wd = ctx.weights
+        it = ctx.inter
+        if it is None:
+            it = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=False, keep=True)
+        dy2 = dy.reshape(b * s, d)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        # ---- feed-forward branch
+        dhmid = kc.gemm(dy2, wd, a_kmajor=True, b_kmajor=False)
+        (g_wd,) = _wgrad(dy2, it["hmid"], [wd])
+        dgu = kc.swiglu_bwd(dhmid, it["gu"], out=it["gu"])  # gu is dead after this; reuse its storage
+        del dhmid
+        dn2 = kc.gemm(dgu, kc.stack_rows([wg, wu]), a_kmajor=True, b_kmajor=False)
+        g_wg, g_wu = _wgrad(dgu, it["n2"], [wg, wu])
+        dh1, dwn2 = kc.rmsnorm_bwd(dn2, it["h1"], wn2, it["rstd2"], residual_grad=dy2, out=dn2)
+        g_wn2 = _norm_wgrad(wn2, dwn2)
+        # ---- attention branch
+        dattn = kc.gemm(dh1, wo, a_kmajor=True, b_kmajor=False)
+        (g_wo,) = _wgrad(dh1, it["attn2"], [wo])
+        qkv4 = it["qkv4"]
+        q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
+        attn = it["attn2"].view(b, s, h, hd)
+        dq, dk, dv = _attention_bwd(dattn.view(b, s, h, hd), q, k, v, attn, it["actx"], True, 1.0 / math.sqrt(hd))
+        dqkv4 = torch.empty_like(qkv4)
+        dqkv4[:, :, :h].copy_(dq)
+        dqkv4[:, :, h : h + hkv].copy_(dk)
+        dqkv4[:, :, h + hkv :].copy_(dv)
+        del dq, dk, dv
+        kc.rope(dqkv4, cos, sin, h + hkv, inverse=True, out=dqkv4)
+        dqkv = dqkv4.view(b * s, (h + 2 * hkv) * hd)
+        dn1 = kc.gemm(dqkv, kc.stack_rows([wq, wk, wv]), a_kmajor=True, b_kmajor=False)
+        g_wq, g_wk, g_wv = _wgrad(dqkv, it["n1"], [wq, wk, wv])
+        dx, dwn1 = kc.rmsnorm_bwd(dn1, x2, wn1, it["rstd1"], residual_grad=dh1, out=dn1)
+        g_wn1 = _norm_wgrad(wn1, dwn1)
+        ctx.inter = None
+        return (dx.view(b, s, d), None, None, g_wn1, g_wq, g_wk, g_wv, g_wo, g_wn2, g_wg, g_wu, g_wd, None, None, None)
+
+
+def dense_block_supported(block, x, kv_cache, doc_ids, key_padding_mask) -> bool:
+    """The fused node covers the plain dense pre-norm SwiGLU block in bf16 on a GPU."""
+    att, mlp = block.attention, block.mlp
+    return (
+        x.is_cuda
+        and x.dtype == torch.bfloat16
+        and kv_cache is None
+        and doc_ids is None
+        and key_padding_mask is None
+        and torch.is_grad_enabled()
+        and getattr(att, "tp", None) is None
+        and att.q_norm is None
+        and not att.capture_attention_weights
+        and type(mlp).__name__ == "SwiGLUMLP"
+        and getattr(mlp, "tp", None) is None
+        and type(block.attention_norm).__name__ == "RMSNorm"
+        and not getattr(block, "fp8", False)
+        and block.ac_mode in ("none", "full")
+        and x.shape[-1] % 8 == 0
+        and att.head_dim % 16 == 0
+        and not block._forward_hooks
+        and not att._forward_hooks
+        and not mlp._forward_hooks
+        and not block.attention_norm._forward_hooks
+        and not block.mlp_norm._forward_hooks
+    )
+
+
+def dense_block(block, x, cos, sin):
+    att, mlp = block.attention, block.mlp
+    recompute = block.ac_mode == "full" and block.training
+    return DenseBlockFn.apply(
+        x, cos, sin, block.attention_norm.weight, att.q_proj.weight, att.k_proj.weight, att.v_proj.weight,
+        att.o_proj.weight, block.mlp_norm.weight, mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight,
+        block.attention_norm.eps, att.head_dim, recompute,
+    )
