@@ -148,7 +148,14 @@ def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
                 else:
                     dst[k] = v if torch.is_tensor(v) else torch.tensor(float(v))
             handled.add(fqn)
-        # scalar hyper-parameters that the run may have changed (lr after scheduling is restored by the scheduler)
+    # hyper-parameters travel with the groups (the scheduled lr above all): groups are matched by position
+    saved_groups = list(loaded.get("param_groups", []))
+    live_groups = [g for opt in opts for g in opt.param_groups]
+    if len(saved_groups) == len(live_groups):
+        for live, saved in zip(live_groups, saved_groups):
+            for k, v in saved.items():
+                if k != "params" and k in live:
+                    live[k] = tuple(v) if isinstance(live[k], tuple) and isinstance(v, list) else v
     if hasattr(optimizer, "_k"):
         ks = [int(st["k"]) for st in optimizer.state.values() if "k" in st]
         if ks:
