@@ -16,6 +16,7 @@
 // SwiGLU gate/up/down, output head: kempnerforge/model/attention.py:150-152,236,
 // kempnerforge/model/mlp.py:26, kempnerforge/model/embedding.py:51) and their backward.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace kf {
 
@@ -45,56 +46,11 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
   return {first_m + r % rows, r / rows};
 }
 
-template <typename OutT>
-__device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&acc)[32], int valid_cols,
-                                            bool accumulate);
-
-template <>
-__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&acc)[32],
-                                                           int valid_cols, bool accumulate) {
-#pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    if (v * 8 >= valid_cols) break;
-    uint4* p = reinterpret_cast<uint4*>(dst + v * 8);
-    float f[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
-    if (accumulate) {
-      uint4 old = *p;
-      float2 a = unpack_bf16(old.x), b = unpack_bf16(old.y), c = unpack_bf16(old.z), d = unpack_bf16(old.w);
-      f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
-      f[4] += c.x; f[5] += c.y; f[6] += d.x; f[7] += d.y;
-    }
-    uint4 out;
-    out.x = pack_bf16(f[0], f[1]);
-    out.y = pack_bf16(f[2], f[3]);
-    out.z = pack_bf16(f[4], f[5]);
-    out.w = pack_bf16(f[6], f[7]);
-    *p = out;
-  }
-}
-
-template <>
-__device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t (&acc)[32], int valid_cols,
-                                                   bool accumulate) {
-#pragma unroll
-  for (int v = 0; v < 8; ++v) {
-    if (v * 4 >= valid_cols) break;
-    float4* p = reinterpret_cast<float4*>(dst + v * 4);
-    float4 o = make_float4(__uint_as_float(acc[v * 4]), __uint_as_float(acc[v * 4 + 1]),
-                           __uint_as_float(acc[v * 4 + 2]), __uint_as_float(acc[v * 4 + 3]));
-    if (accumulate) {
-      float4 old = *p;
-      o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-    }
-    *p = o;
-  }
-}
-
 template <bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 kf_gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     OutT* __restrict__ C, int M, int N, int K, int ldc, int accumulate, int* status) {
+                     OutT* __restrict__ C, const OutT* __restrict__ R, int M, int N, int K, int ldc, int ldr, int accumulate,
+                     int* status) {
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle atoms are 1024 B; tile bases must be 1024-aligned
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -225,13 +181,15 @@ kf_gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const int col0 = tc.n * BN;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       OutT* c_row = C + size_t(row) * ldc + col0;
+      const OutT* r_row = R ? R + size_t(row) * ldr + col0 : nullptr;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(t_row + c * 32, v);
         tmem_ld_wait();
         const int valid = min(32, N - (col0 + c * 32));
-        if (row < M && valid > 0) store_chunk<OutT>(c_row + c * 32, v, valid, accumulate != 0);
+        if (row < M && valid > 0)
+          store_chunk<OutT>(c_row + c * 32, v, valid, accumulate != 0, r_row ? r_row + c * 32 : nullptr);
       }
       tc_fence_before();
       __syncwarp();
@@ -261,8 +219,8 @@ static int* status_ptr() {
 }
 
 template <bool A_MN, bool B_MN, typename OutT>
-static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
-                       int ldc, int accumulate, int num_sms, cudaStream_t stream) {
+static int launch_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                       int ldc, int ldr, int accumulate, int num_sms, cudaStream_t stream) {
   CUtensorMap ma, mb;
   int rc;
   // K-major: rows = M (or N), cols = K, one (64 x rows) box.  MN-major: rows = K, cols = M (or N), 64x64 boxes.
@@ -279,30 +237,47 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, reinterpret_cast<OutT*>(C), M, N, K, ldc,
-                                                  accumulate, status_ptr());
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, reinterpret_cast<OutT*>(C),
+                                                  reinterpret_cast<const OutT*>(R), M, N, K, ldc, ldr, accumulate,
+                                                  status_ptr());
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 
 }  // namespace kf
 
+namespace kf2 {
+int launch_gemm_2cta(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                     int ldc, int ldr, int a_mn, int b_mn, int out_f32, int accumulate, int num_sms,
+                     cudaStream_t stream, int* status);
+}
+
 extern "C" {
 
-// C[M,N] (+)= op(A) * op(B)^T with bf16 inputs and fp32 accumulation.
+// C[M,N] = op(A) * op(B)^T (+ C if accumulate) (+ R if given), bf16 inputs, fp32 accumulation.
 //   a_mn == 0: A is stored [M][lda] (K contiguous);  a_mn == 1: A is stored [K][lda] (M contiguous)
 //   b_mn == 0: B is stored [N][ldb] (K contiguous);  b_mn == 1: B is stored [K][ldb] (N contiguous)
-//   out_f32: C is fp32 instead of bf16.  All leading dimensions in elements; A/B pitches must be
-//   multiples of 8 elements and base pointers 16-byte aligned (TMA), ldc a multiple of 8 (bf16) / 4 (fp32).
+//   out_f32: C (and R) are fp32 instead of bf16.  Leading dimensions in elements; A/B pitches must be
+//   multiples of 8 elements and base pointers 16-byte aligned (TMA), ldc/ldr multiples of 8 (bf16) / 4 (fp32).
+//   mode: 0 = pick automatically, 1 = one CTA per 128x256 tile, 2 = CTA pairs (cta_group::2) on 256x256 tiles.
 // Returns 0 on success, otherwise a code identifying the failing step.
-int kf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                 int a_mn, int b_mn, int out_f32, int accumulate, int num_sms, void* stream) {
+int kf_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                 int ldc, int ldr, int a_mn, int b_mn, int out_f32, int accumulate, int mode, int num_sms,
+                 void* stream) {
   using namespace kf;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 0 || N <= 0 || K <= 0) return 1;
-#define KF_DISPATCH(AM, BM_)                                                                        \
-  (out_f32 ? launch_gemm<AM, BM_, float>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, num_sms, st) \
-           : launch_gemm<AM, BM_, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, num_sms, st))
+  if (mode == 0) {
+    // pairs pay off once there are enough 256x256 tiles to fill the machine a few times over
+    const long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    mode = pair_tiles >= 2LL * (num_sms / 2) ? 2 : 1;
+  }
+  if (mode == 2)
+    return kf2::launch_gemm_2cta(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, out_f32, accumulate, num_sms,
+                                 st, status_ptr());
+#define KF_DISPATCH(AM, BM_)                                                                                  \
+  (out_f32 ? launch_gemm<AM, BM_, float>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, accumulate, num_sms, st)    \
+           : launch_gemm<AM, BM_, __nv_bfloat16>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, accumulate, num_sms, st))
   if (!a_mn && !b_mn) return KF_DISPATCH(false, false);
   if (!a_mn && b_mn) return KF_DISPATCH(false, true);
   if (a_mn && !b_mn) return KF_DISPATCH(true, false);

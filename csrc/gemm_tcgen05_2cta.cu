@@ -1,0 +1,310 @@
+// bf16 GEMM with CTA pairs (tcgen05 cta_group::2):  C[M,N] = A[M,K] * B[N,K]^T (+ C) (+ R).
+//
+// A cluster of two CTAs on neighbouring SMs owns one 256x256 output tile.  CTA r of the pair loads
+// its 128 rows of A and its 128 rows of B (N-half r) with TMA; the leader CTA (rank 0) issues
+// tcgen05.mma.cta_group::2 instructions of shape 256x256x16 that read both CTAs' shared memory and
+// write each CTA's half of the accumulator (128 lanes x 256 columns) into that CTA's tensor memory.
+// Per CTA and k-block only 32 KB are loaded (half of what the single-CTA 128x256 tile needs for the
+// same math per SM), which leaves room for 6 pipeline stages.
+//
+// Synchronisation (all waits bounded, see common.cuh):
+//   full[s]    leader only: armed by the leader's producer with the bytes of BOTH CTAs; the peer's TMA
+//              loads complete on the leader's barrier (peer bit of the barrier address cleared)
+//   empty[s]   both CTAs: released by the leader's tcgen05.commit, multicast to the pair
+//   tfull[a]   both CTAs: accumulator a complete (multicast commit)
+//   tempty[a]  leader only: 8 arrivals = 4 epilogue warps of each CTA (the peer arrives remotely)
+// TMA loads carry no cluster multicast; every CTA fetches its own operands.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+
+namespace kf2 {
+
+using namespace kf;
+
+constexpr int CTA_M = 128;   // rows of A per CTA
+constexpr int TILE_M = 256;  // rows per CTA pair
+constexpr int TILE_N = 256;
+constexpr int HALF_N = 128;  // rows of B per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = CTA_M * BK * 2;   // 16 KB
+constexpr int B_BYTES = HALF_N * BK * 2;  // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are counted on the LEADER CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t leader_bar, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(m), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in both CTAs of the pair once all MMAs retired.
+__device__ __forceinline__ void commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"((uint16_t)0x3)
+      : "memory");
+}
+__device__ __forceinline__ void arrive_on_cta(uint32_t bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar),
+      "r"(cta)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+
+struct TileCoord {
+  int m, n;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_blocks) {
+  const int per_group = GROUP_M * n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int r = t - g * per_group;
+  return {first_m + r % rows, r / rows};
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          OutT* __restrict__ C, const OutT* __restrict__ R, int M, int N, int K, int ldc, int ldr,
+                          int accumulate, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_blocks = (M + TILE_M - 1) / TILE_M;
+  const int n_blocks = (N + TILE_N - 1) / TILE_N;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one per CTA)
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+        const int m0 = tc.m * TILE_M + int(rank) * CTA_M;
+        const int n0 = tc.n * TILE_N + int(rank) * HALF_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_BYTES;
+          const uint32_t lead_full = full_bar(s) & PEER_BIT_MASK;
+          if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(a_dst, &map_a, lead_full, k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < CTA_M / 64; ++c)
+              tma_load_2d_pair(a_dst + c * (64 * BK * 2), &map_a, lead_full, m0 + 64 * c, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(b_dst, &map_b, lead_full, k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < HALF_N / 64; ++c)
+              tma_load_2d_pair(b_dst + c * (64 * BK * 2), &map_b, lead_full, n0 + 64 * c, k0);
+          }
+        }
+      }
+      // Copies into this CTA's shared memory are complete once the stages they filled were consumed
+      // (empty flipped) or, on the error path, once the leader's full barrier flipped.
+      if (leader)
+        for (int j = max(0, it - STAGES); j < it; ++j)
+          mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, TILE_N, A_MN, B_MN);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_iter) {
+        const int acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + s * STAGE_BYTES;
+          const uint32_t b_src = a_src + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = A_MN ? umma_desc_sw128(a_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? umma_desc_sw128(b_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024);
+            mma_pair_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          commit_pair(empty_bar(s));
+        }
+        if (ok) commit_pair(tfull_bar(acc));
+      }
+      // every MMA must have retired before either CTA gives up its shared or tensor memory
+      asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar)
+                   : "memory");
+      mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quarter = warp & 3;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_iter) {
+      const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+      const int acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), acc_ph, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tc.m * TILE_M + int(rank) * CTA_M + quarter * 32 + lane;
+      const int col0 = tc.n * TILE_N;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TILE_N;
+      OutT* c_row = C + size_t(row) * ldc + col0;
+      const OutT* r_row = R ? R + size_t(row) * ldr + col0 : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < TILE_N / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait();
+        const int valid = min(32, N - (col0 + c * 32));
+        if (row < M && valid > 0)
+          store_chunk<OutT>(c_row + c * 32, v, valid, accumulate != 0, r_row ? r_row + c * 32 : nullptr);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) arrive_on_cta(tempty_bar(acc), 0);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's shared memory / tensor memory stay valid until both CTAs are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+static int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc,
+                  int ldr, int accumulate, int num_sms, cudaStream_t stream, int* status) {
+  CUtensorMap ma, mb;
+  int rc = A_MN ? make_map_2d_bf16(&ma, A, K, M, lda, 64, BK) : make_map_2d_bf16(&ma, A, M, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = B_MN ? make_map_2d_bf16(&mb, B, K, N, ldb, 64, BK) : make_map_2d_bf16(&mb, B, N, K, ldb, BK, HALF_N);
+  if (rc) return 200 + rc;
+  auto kern = kf_gemm_bf16_tcgen05_2cta<A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<OutT*>(C),
+                                                   reinterpret_cast<const OutT*>(R), M, N, K, ldc, ldr, accumulate,
+                                                   status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+int launch_gemm_2cta(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                     int ldc, int ldr, int a_mn, int b_mn, int out_f32, int accumulate, int num_sms,
+                     cudaStream_t stream, int* status) {
+#define KF2_DISPATCH(AM, BM_)                                                                                         \
+  (out_f32 ? launch<AM, BM_, float>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, accumulate, num_sms, stream, status)     \
+           : launch<AM, BM_, __nv_bfloat16>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, accumulate, num_sms, stream, status))
+  if (!a_mn && !b_mn) return KF2_DISPATCH(false, false);
+  if (!a_mn && b_mn) return KF2_DISPATCH(false, true);
+  if (a_mn && !b_mn) return KF2_DISPATCH(true, false);
+  return KF2_DISPATCH(true, true);
+#undef KF2_DISPATCH
+}
+
+}  // namespace kf2

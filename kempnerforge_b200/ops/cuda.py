@@ -18,6 +18,7 @@ import torch
 from kempnerforge_b200.ops.build import LIB_PATH
 
 _lib = None
+GEMM_MODE = int(os.environ.get("KF_GEMM_MODE", "0"))  # 0 = automatic, 1 = single CTA tiles, 2 = CTA pairs
 LAUNCH_COUNT = 0  # number of native kernel launches issued through this module (bench bookkeeping)
 
 
@@ -44,7 +45,7 @@ def available() -> bool:
 def _declare(L: ctypes.CDLL) -> None:
     vp, i, ll, f = c_void_p, c_int, c_longlong, c_float
     sigs = {
-        "kf_gemm_bf16": [vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, vp],
+        "kf_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, i, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
         "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
@@ -143,8 +144,12 @@ def gemm(
     out: torch.Tensor | None = None,
     accumulate: bool = False,
     out_dtype: torch.dtype | None = None,
+    residual: torch.Tensor | None = None,
+    mode: int | None = None,
 ) -> torch.Tensor:
-    """out[M,N] (+)= A * Bᵀ on the tcgen05 tensor cores.
+    """out[M,N] = A * Bᵀ (+ out if ``accumulate``) (+ ``residual``) on the tcgen05 tensor cores.
+
+    ``mode``: None/0 = automatic, 1 = single-CTA 128x256 tiles, 2 = CTA pairs (cta_group::2) on 256x256 tiles.
 
     ``a_kmajor``: a is stored (M, K); otherwise (K, M).  ``b_kmajor``: b is stored (N, K); otherwise (K, N).
     Rows may be strided (row pitch a multiple of 8 elements); columns must be contiguous.
@@ -166,9 +171,16 @@ def gemm(
         raise NativeKernelError(
             f"gemm operands must have 16-byte aligned bases and row pitches (lda={lda}, ldb={ldb}, ldc={ldc})"
         )
+    ldr = 0
+    if residual is not None:
+        assert residual.shape == (M, N) and residual.dtype == out.dtype and residual.stride(1) == 1
+        ldr = residual.stride(0)
+        if ldr % (4 if out_f32 else 8) or residual.data_ptr() % 16:
+            raise NativeKernelError("gemm residual must be 16-byte aligned")
     code = lib().kf_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc,
-        0 if a_kmajor else 1, 0 if b_kmajor else 1, int(out_f32), int(accumulate), sm_count(), _stream(),
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None,
+        M, N, K, lda, ldb, ldc, ldr, 0 if a_kmajor else 1, 0 if b_kmajor else 1, int(out_f32), int(accumulate),
+        GEMM_MODE if mode is None else mode, sm_count(), _stream(),
     )
     _check(code, "kf_gemm_bf16")
     return out

@@ -116,15 +116,13 @@ class DenseBlockFn(torch.autograd.Function):
         scale = 1.0 / math.sqrt(hd)
         attn, actx = _attention_fwd(q, k, v, True, scale)
         attn2 = attn.reshape(b * s, h * hd)
-        h1 = kc.gemm(attn2, wo)
-        h1.add_(x2)
+        h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
         n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)
         gu = kc.gemm(n2, kc.stack_rows([wg, wu]))
         hmid = kc.swiglu_fwd(gu)
         out = {}
         if need_output:
-            y = kc.gemm(hmid, wd)
-            y.add_(h1)
+            y = kc.gemm(hmid, wd, residual=h1)
             out["y"] = y
         if keep:
             out.update(n1=n1, rstd1=rstd1, qkv4=qkv4, attn2=attn2, actx=actx, h1=h1, n2=n2, rstd2=rstd2, gu=gu, hmid=hmid)

@@ -21,19 +21,44 @@ def _close(got, want, rtol=2e-2, atol=2e-2):
     assert torch.allclose(got, want, rtol=rtol, atol=atol * max(1.0, ref)), f"max err {err} (ref max {ref})"
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 264, 136), (1000, 776, 520), (2048, 1024, 4096)])
-def test_gemm_all_layouts(native_lib, a_k, b_k, shape):
+def test_gemm_all_layouts(native_lib, a_k, b_k, shape, mode):
     m, n, k = shape
     a = _rand(m, k, scale=0.5)
     b = _rand(n, k, scale=0.5)
     want = a.float() @ b.float().t()
     a_in = a if a_k else a.t().contiguous()
     b_in = b if b_k else b.t().contiguous()
-    got = native_lib.gemm(a_in, b_in, a_kmajor=a_k, b_kmajor=b_k)
+    got = native_lib.gemm(a_in, b_in, a_kmajor=a_k, b_kmajor=b_k, mode=mode)
     torch.cuda.synchronize()
     assert native_lib.read_status() == 0
     _close(got, want, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_residual_epilogue(native_lib, mode):
+    m, n, k = 520, 776, 264
+    a, b = _rand(m, k, scale=0.5), _rand(n, k, scale=0.5)
+    r = _rand(m, n)
+    got = native_lib.gemm(a, b, residual=r, mode=mode)
+    _close(got, a.float() @ b.float().t() + r.float())
+    acc = _rand(m, n)
+    want = acc.float() + a.float() @ b.float().t() + r.float()
+    native_lib.gemm(a, b, out=acc, accumulate=True, residual=r, mode=mode)
+    _close(acc, want)
+    assert native_lib.read_status() == 0
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_many_tiles_persistent(native_lib, mode):
+    """More tiles than CTAs (several per persistent CTA, both accumulator buffers, ring wrap-around)."""
+    m, n, k = 4096, 5120, 192
+    a, b = _rand(m, k, scale=0.5), _rand(n, k, scale=0.5)
+    got = native_lib.gemm(a, b, mode=mode)
+    _close(got, a.float() @ b.float().t())
+    assert native_lib.read_status() == 0
 
 
 def test_gemm_accumulate_and_fp32_out(native_lib):
