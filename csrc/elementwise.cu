@@ -81,24 +81,42 @@ kf_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
                __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int D, float eps) {
   __shared__ float red[40];
   const int nvec = D >> 3;
+  constexpr int CACHED = NORM_CACHE * NORM_THREADS;  // vectors kept in registers per row
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16* xr = x + size_t(row) * D;
     F8 cache[NORM_CACHE];
     float ss = 0.f;
-    int c = 0;
-    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS, ++c) {
-      F8 t = load8(xr + v * 8);
-      if (c < NORM_CACHE) cache[c] = t;
+#pragma unroll
+    for (int c = 0; c < NORM_CACHE; ++c) {
+      const int v = threadIdx.x + c * NORM_THREADS;
+      if (v < nvec) {
+        cache[c] = load8(xr + v * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += cache[c].v[i] * cache[c].v[i];
+      }
+    }
+    for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
+      const F8 t = load8(xr + v * 8);
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += t.v[i] * t.v[i];
     }
     const float r = rsqrtf(block_sum(ss, red) / D + eps);
     if (threadIdx.x == 0 && rstd) rstd[row] = r;
     __nv_bfloat16* yr = y + size_t(row) * D;
-    c = 0;
-    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS, ++c) {
-      F8 t = c < NORM_CACHE ? cache[c] : load8(xr + v * 8);
-      F8 g = load8(w + v * 8);
+#pragma unroll
+    for (int c = 0; c < NORM_CACHE; ++c) {
+      const int v = threadIdx.x + c * NORM_THREADS;
+      if (v < nvec) {
+        const F8 g = load8(w + v * 8);
+        F8 t = cache[c];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t.v[i] = t.v[i] * r * g.v[i];
+        store8(yr + v * 8, t);
+      }
+    }
+    for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
+      F8 t = load8(xr + v * 8);
+      const F8 g = load8(w + v * 8);
 #pragma unroll
       for (int i = 0; i < 8; ++i) t.v[i] = t.v[i] * r * g.v[i];
       store8(yr + v * 8, t);
@@ -108,6 +126,7 @@ kf_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
 
 // dx = [dx_in +] r*g - x*r^3*mean(g*x) with g = dy*w;  dw partial = sum_rows dy*x*r (per block, fp32).
 // dx_in (optional) is the gradient arriving over the residual connection; it may alias dx.
+// The first NORM_CACHE*NORM_THREADS vectors of a row (D <= 8192) stay in registers between the two passes.
 __global__ void __launch_bounds__(NORM_THREADS)
 kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -115,6 +134,7 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
                const __nv_bfloat16* __restrict__ dx_in) {
   __shared__ float red[40];
   const int nvec = D >> 3;
+  constexpr int CACHED = NORM_CACHE * NORM_THREADS;
   F8 dw_acc[NORM_CACHE];
 #pragma unroll
   for (int c = 0; c < NORM_CACHE; ++c)
@@ -122,7 +142,7 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
     for (int i = 0; i < 8; ++i) dw_acc[c].v[i] = 0.f;
   float* my_partial = dw_partial + size_t(blockIdx.x) * D;
   // columns beyond the register cache accumulate straight into this block's partial row
-  for (int v = threadIdx.x + NORM_CACHE * NORM_THREADS; v < nvec; v += NORM_THREADS)
+  for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS)
 #pragma unroll
     for (int i = 0; i < 8; ++i) my_partial[v * 8 + i] = 0.f;
 
@@ -131,33 +151,62 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
     const __nv_bfloat16* dyr = dy + size_t(row) * D;
     const float r = rstd[row];
     float dot = 0.f;
-    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS) {
-      F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
+    F8 xc[NORM_CACHE], dc[NORM_CACHE];
+#pragma unroll
+    for (int c = 0; c < NORM_CACHE; ++c) {
+      const int v = threadIdx.x + c * NORM_THREADS;
+      if (v < nvec) {
+        xc[c] = load8(xr + v * 8);
+        dc[c] = load8(dyr + v * 8);
+        const F8 ww = load8(w + v * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += dc[c].v[i] * ww.v[i] * xc[c].v[i];
+      }
+    }
+    for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
+      const F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
 #pragma unroll
       for (int i = 0; i < 8; ++i) dot += g.v[i] * ww.v[i] * a.v[i];
     }
     const float coef = block_sum(dot, red) / D * r * r * r;
     __nv_bfloat16* dxr = dx + size_t(row) * D;
-    int c = 0;
-    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS, ++c) {
-      F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
+    const __nv_bfloat16* dir = dx_in ? dx_in + size_t(row) * D : nullptr;
+#pragma unroll
+    for (int c = 0; c < NORM_CACHE; ++c) {
+      const int v = threadIdx.x + c * NORM_THREADS;
+      if (v < nvec) {
+        const F8 ww = load8(w + v * 8);
+        F8 o;
+        if (dir) o = load8(dir + v * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = r * dc[c].v[i] * ww.v[i] - xc[c].v[i] * coef;
+          o.v[i] = dir ? o.v[i] + d : d;
+          dw_acc[c].v[i] += dc[c].v[i] * xc[c].v[i] * r;
+        }
+        store8(dxr + v * 8, o);
+      }
+    }
+    for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
+      const F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
       F8 o;
-      if (dx_in) o = load8(dx_in + size_t(row) * D + v * 8);
+      if (dir) o = load8(dir + v * 8);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float d = r * g.v[i] * ww.v[i] - a.v[i] * coef;
-        o.v[i] = dx_in ? o.v[i] + d : d;
-        const float dwv = g.v[i] * a.v[i] * r;
-        if (c < NORM_CACHE) dw_acc[c].v[i] += dwv;
-        else my_partial[v * 8 + i] += dwv;
+        o.v[i] = dir ? o.v[i] + d : d;
+        my_partial[v * 8 + i] += g.v[i] * a.v[i] * r;
       }
       store8(dxr + v * 8, o);
     }
   }
-  int c = 0;
-  for (int v = threadIdx.x; v < nvec && c < NORM_CACHE; v += NORM_THREADS, ++c)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) my_partial[v * 8 + i] = dw_acc[c].v[i];
+  for (int c = 0; c < NORM_CACHE; ++c) {
+    const int v = threadIdx.x + c * NORM_THREADS;
+    if (v < nvec)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) my_partial[v * 8 + i] = dw_acc[c].v[i];
+  }
 }
 
 // dw[d] = sum_b partial[b][d]  (fixed order -> deterministic)
@@ -426,6 +475,25 @@ __global__ void kf_sumsq_stage1(const T* __restrict__ x, long long n, float* __r
   s = block_sum(s, red);
   if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
+// bf16, 16-byte aligned: 8 elements per load; the ragged tail (n % 8) is added by block 0
+__global__ void kf_sumsq_stage1_bf16x8(const __nv_bfloat16* __restrict__ x, long long n, float* __restrict__ partial) {
+  __shared__ float red[40];
+  const long long nvec = n >> 3;
+  float s = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const F8 t = load8(x + i * 8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += t.v[k] * t.v[k];
+  }
+  if (blockIdx.x == 0)
+    for (long long i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      const float t = __bfloat162float(x[i]);
+      s += t * t;
+    }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
 __global__ void kf_sumsq_stage2(const float* __restrict__ partial, int nparts, float* __restrict__ out,
                                 int accumulate) {
   __shared__ float red[40];
@@ -576,8 +644,10 @@ int kf_adamw_flat(void* p, const void* g, void* m, void* v, long long n, long lo
 int kf_sumsq(const void* x, long long n, int dt, void* partial, void* out, int accumulate, void* stream) {
   using namespace kf;
   cudaStream_t st = (cudaStream_t)stream;
-  const int nb = grid_for(n, 512, 1024);
-  if (dt == 0)
+  const int nb = grid_for(dt == 0 ? n / 8 + 1 : n, 512, 1024);
+  if (dt == 0 && ((uintptr_t)x & 15) == 0)
+    kf_sumsq_stage1_bf16x8<<<nb, 512, 0, st>>>((const __nv_bfloat16*)x, n, (float*)partial);
+  else if (dt == 0)
     kf_sumsq_stage1<__nv_bfloat16><<<nb, 512, 0, st>>>((const __nv_bfloat16*)x, n, (float*)partial);
   else
     kf_sumsq_stage1<float><<<nb, 512, 0, st>>>((const float*)x, n, (float*)partial);

@@ -61,6 +61,9 @@ def _unwrap(model):
 
 
 def model_state_dict(model) -> dict[str, torch.Tensor]:
+    engine = getattr(_unwrap(model), "_kf_engine", None)
+    if engine is not None and hasattr(engine, "wait_all"):
+        engine.wait_all()  # parameters being published asynchronously must have landed
     return dict(_unwrap(model).state_dict())
 
 

@@ -46,10 +46,14 @@ class DataParallelEngine:
         self.grad_scale = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._reduced = False
+        self._reduce_work: dict[int, object] = {}  # group index -> in-flight gradient reduction
+        self._gather_work: dict[int, object] = {}  # group index -> in-flight parameter publication
+        self._group_of_module: dict[int, int] = {}
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
         if self.world > 1:
             self.broadcast_parameters()
+            self._install_overlap_hooks()
 
     # ------------------------------------------------------------------ set-up
     def broadcast_parameters(self, src: int = 0) -> None:
@@ -59,6 +63,75 @@ class DataParallelEngine:
             if g.local:
                 continue
             dist.broadcast(g.param, src=root, group=self.pg)
+
+    # ------------------------------------------------------------------ overlap of communication with compute
+    def _install_overlap_hooks(self) -> None:
+        """Reduce a block's gradients as soon as its backward finished, and wait for a block's freshly
+        published parameters only when its forward starts."""
+        layers = getattr(self.model, "layers", None)
+        if not isinstance(layers, nn.ModuleDict):
+            return
+        by_name = {g.name: i for i, g in enumerate(self.groups)}
+        for key, block in layers.items():
+            idx = by_name.get(f"layers.{key}")
+            if idx is None:
+                continue
+            extra = by_name.get(f"layers.{key}.experts")
+            idxs = [idx] + ([extra] if extra is not None else [])
+            block.register_forward_pre_hook(self._make_pre_hook(idxs))
+        root = [i for i, g in enumerate(self.groups) if g.name.startswith("root")]
+        self.model.register_forward_pre_hook(lambda m, a: self.wait_params(root))
+        for name in ("forward_hidden", "compute_loss"):
+            fn = getattr(self.model, name, None)
+            if fn is not None:
+                setattr(self.model, name, self._wrap_wait(fn, root))
+
+    def _wrap_wait(self, fn, idxs):
+        def wrapped(*a, **k):
+            self.wait_params(idxs)
+            return fn(*a, **k)
+
+        return wrapped
+
+    def _make_pre_hook(self, idxs):
+        def hook(module, args):
+            self.wait_params(idxs)
+            x = args[0] if args else None
+            if torch.is_tensor(x) and x.requires_grad and torch.is_grad_enabled() and self.requires_sync:
+                x.register_hook(lambda g, idxs=idxs: self._block_backward_done(idxs))
+
+        return hook
+
+    def wait_params(self, idxs) -> None:
+        for i in idxs:
+            work = self._gather_work.pop(i, None)
+            if work is not None:
+                work.wait()
+
+    def _block_backward_done(self, idxs) -> None:
+        if not (self.world > 1 and self.requires_sync):
+            return None
+        for i in idxs:
+            g = self.groups[i]
+            if i in self._reduce_work or g.local:
+                continue
+            ready = all(
+                getattr(p, "_kf_grad_live", False) and (p.grad is None or p.grad.data_ptr() == p._kf_grad.data_ptr())
+                for p in g.params
+            )
+            if ready and getattr(self.model, "tp", None) is None and getattr(self.model, "ep_group", None) is None:
+                self._reduce_work[i] = self._reduce_one(g, async_op=True)
+        return None
+
+    def _reduce_one(self, g: FlatParamGroup, async_op: bool = False):
+        if g.grad.is_cuda and "nccl" in str(dist.get_backend(self.pg)):
+            lo, hi = g.shard_range
+            return dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
+        work = dist.all_reduce(g.grad, group=self.pg, async_op=async_op)
+        if async_op:
+            return _ScaledWork(work, g.grad, self.world)
+        g.grad.div_(self.world)
+        return None
 
     def set_requires_gradient_sync(self, flag: bool) -> None:
         self.requires_sync = bool(flag)
@@ -84,16 +157,15 @@ class DataParallelEngine:
         self._reduced = True
 
     def _reduce_gradients(self) -> None:
-        for g in self.groups:
+        for i, g in enumerate(self.groups):
             if g.local:  # rank-private parameters: the gradient is complete, only the loss averaging applies
                 g.grad.div_(self.world)
                 continue
-            if g.grad.is_cuda and dist.get_backend(self.pg) == "nccl":
-                lo, hi = g.shard_range
-                dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg)
-            else:
-                dist.all_reduce(g.grad, group=self.pg)
-                g.grad.div_(self.world)
+            work = self._reduce_work.pop(i, None)
+            if work is not None:  # already launched from the block's backward hook
+                work.wait()
+                continue
+            self._reduce_one(g)
 
     def _sumsq_into(self, x: torch.Tensor, slot: int) -> None:
         if x.numel() == 0:
@@ -146,13 +218,24 @@ class DataParallelEngine:
             g.grad[lo:hi].mul_(self.grad_scale.to(g.grad.dtype))
 
     def after_optimizer_step(self) -> None:
-        """Publish the updated shards so that every rank holds the full new parameters."""
+        """Publish the updated shards so that every rank holds the full new parameters.  On GPUs the
+        all-gathers are asynchronous and each block waits for its own only when its next forward starts."""
         if self.world > 1:
-            for g in self.groups:
+            use_async = self.groups[0].param.is_cuda and bool(self._group_of_module is not None)
+            for i, g in enumerate(self.groups):
                 if g.local:
                     continue
                 lo, hi = g.shard_range
-                dist.all_gather_into_tensor(g.param, g.param[lo:hi].clone(), group=self.pg)
+                if use_async:
+                    self._gather_work[i] = dist.all_gather_into_tensor(g.param, g.param[lo:hi], group=self.pg, async_op=True)
+                else:
+                    dist.all_gather_into_tensor(g.param, g.param[lo:hi].clone(), group=self.pg)
+
+    def wait_all(self) -> None:
+        """Drain every in-flight reduction / publication (before checkpoints, evaluation, shutdown)."""
+        for table in (self._reduce_work, self._gather_work):
+            for i in list(table):
+                table.pop(i).wait()
 
     def zero_grad(self) -> None:
         for g in self.groups:
@@ -175,6 +258,17 @@ class DataParallelEngine:
         lo, hi = g.shard_range
         g.exp_avg.copy_(exp_avg[lo:hi])
         g.exp_avg_sq.copy_(exp_avg_sq[lo:hi])
+
+
+class _ScaledWork:
+    """Handle of an asynchronous sum whose result still has to be divided by the world size."""
+
+    def __init__(self, work, tensor: torch.Tensor, world: int) -> None:
+        self.work, self.tensor, self.world = work, tensor, world
+
+    def wait(self) -> None:
+        self.work.wait()
+        self.tensor.div_(self.world)
 
 
 def clip_grad_norm_(model: nn.Module, max_norm: float, foreach: bool | None = None) -> torch.Tensor:

@@ -1,0 +1,58 @@
+"""Multi-GPU behaviour (NCCL over NVLink): launched as child processes, one rank per GPU."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, os.environ["KF_ROOT"])
+from kempnerforge_b200.config import config_from_dict
+from kempnerforge_b200.training.trainer import Trainer
+world = int(os.environ["WORLD_SIZE"]); rank = int(os.environ["RANK"])
+cfg = config_from_dict({
+    "model": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536, max_seq_len=256),
+    "train": dict(batch_size=2, seq_len=256, max_steps=10, mixed_precision="bf16", activation_checkpointing="full", seed=0),
+    "optimizer": dict(lr=1e-3), "scheduler": dict(warmup_steps=0, name="constant"),
+    "distributed": dict(dp_shard=world), "metrics": dict(log_interval=1000)})
+t = Trainer(cfg)
+g = torch.Generator().manual_seed(100 + rank)
+out = []
+for step in range(4):
+    tok = torch.randint(0, 4096, (2, 257), generator=g)
+    out.append(t.train_step([{"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}]))
+t.engine.wait_all()
+flat = torch.cat([p.detach().float().flatten() for p in t.model.parameters()])
+digest = torch.stack([flat.sum(), flat.abs().sum(), flat.pow(2).sum()])
+gathered = [torch.zeros_like(digest) for _ in range(world)]
+torch.distributed.all_gather(gathered, digest)
+if rank == 0:
+    same = all(torch.equal(gathered[0], x) for x in gathered)
+    print("RESULT " + json.dumps({"losses": [o["loss"] for o in out], "norms": [o["grad_norm"] for o in out], "replicas_identical": same}))
+torch.distributed.destroy_process_group()
+'''
+
+
+def _run(world: int):
+    env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29631", "-"]
+    res = subprocess.run(cmd, input=WORKER, capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0, res.stderr[-3000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_sharded_data_parallel_two_gpus():
+    r = _run(2)
+    assert r["replicas_identical"], "ranks ended with different parameters"
+    assert all(l == l and 0 < l < 20 for l in r["losses"]) and all(n > 0 for n in r["norms"])
+    assert r["losses"][-1] < r["losses"][0] + 0.5
