@@ -1,0 +1,228 @@
+// Fused communication + compute kernels over NVLink peer (symmetric) memory.
+//
+//   kf_symm_rs_norm      reduce-scatter fused with averaging, cast and the gradient-norm partial:
+//                        every rank sums ITS shard of the flat gradient buffer over all ranks' buffers
+//                        (plain peer loads, or one multimem.ld_reduce through NVSwitch), scales by 1/N,
+//                        writes the result into its own buffer and accumulates sum(g^2).
+//   kf_symm_adamw_bcast  sharded AdamW fused with the parameter all-gather: the rank updates its shard
+//                        and stores the new bf16 parameters into every rank's parameter buffer
+//                        (peer stores, or one multimem.st broadcast through NVSwitch).
+//   kf_symm_gather       plain all-gather of a shard into every peer's buffer (initial broadcast, tests).
+//
+// The kernels contain no waits on other GPUs: ordering between ranks is established on the host side of
+// the stream (a bounded signal-pad barrier before the reduce and after the publish).  Replaces FSDP2's
+// NCCL reduce-scatter + copy-out + fused AdamW + next-step all-gather + copy-in
+// (kempnerforge/distributed/parallel.py:72-87,250-302, kempnerforge/training/optimizer.py:28-39).
+#include "common.cuh"
+
+namespace kf {
+
+constexpr int MAX_PEERS = 8;
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ void ld_reduce_bf16x8(const void* mc_addr, float (&out)[8]) {
+  uint32_t a, b, c, d;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "l"(mc_addr)
+               : "memory");
+  float2 f;
+  f = unpack_bf16(a); out[0] = f.x; out[1] = f.y;
+  f = unpack_bf16(b); out[2] = f.x; out[3] = f.y;
+  f = unpack_bf16(c); out[4] = f.x; out[5] = f.y;
+  f = unpack_bf16(d); out[6] = f.x; out[7] = f.y;
+}
+__device__ __forceinline__ void multimem_st_16B(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float block_sum_f(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  if (warp == 0) {
+    t = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  }
+  return t;  // valid in thread 0
+}
+
+// grads: every rank's flat bf16 gradient buffer (same layout).  Elements [lo, lo + n) are this rank's shard.
+// The averaged shard is written back into this rank's own buffer; partial[blockIdx.x] receives sum(avg^2).
+__global__ void __launch_bounds__(512)
+kf_symm_rs_norm(PeerPtrs grads, const void* mc_grad, int world, int rank, long long lo, long long n,
+                float inv_world, float* __restrict__ partial) {
+  __shared__ float red[32];
+  const long long nvec = n >> 3;
+  __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(grads.p[rank]) + lo;
+  float ss = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+    if (mc_grad) {
+      ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grad) + lo + i * 8, acc);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int r = 0; r < world; ++r) {  // fixed order: bit-identical results on every run
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + lo + i * 8);
+        float2 f;
+        f = unpack_bf16(u.x); acc[0] += f.x; acc[1] += f.y;
+        f = unpack_bf16(u.y); acc[2] += f.x; acc[3] += f.y;
+        f = unpack_bf16(u.z); acc[4] += f.x; acc[5] += f.y;
+        f = unpack_bf16(u.w); acc[6] += f.x; acc[7] += f.y;
+      }
+    }
+    uint4 o;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= inv_world;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]);
+    o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(mine + i * 8) = o;
+    // the norm is taken of the values the optimizer will read (after rounding to bf16)
+    float2 f;
+    f = unpack_bf16(o.x); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16(o.y); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16(o.z); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16(o.w); ss += f.x * f.x + f.y * f.y;
+  }
+  const float total = block_sum_f(ss, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = total;
+}
+
+__global__ void kf_sum_partials(const float* __restrict__ partial, int n, float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+  const float t = block_sum_f(s, red);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + t : t;
+}
+
+// AdamW on the shard [lo, lo + n) (bf16 params / grads / moments) + broadcast of the new parameters.
+__global__ void __launch_bounds__(256)
+kf_symm_adamw_bcast(PeerPtrs params, void* mc_param, int world, int rank, const __nv_bfloat16* __restrict__ grad,
+                    __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v, long long lo, long long n,
+                    long long n_decay_global, float lr, float b1, float b2, float eps, float wd, float bc1,
+                    float bc2_sqrt, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
+  if (skip && *skip) return;
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  const float step = lr / bc1;
+  const long long nvec = n >> 3;
+  const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(params.p[rank]) + lo;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 pu = *reinterpret_cast<const uint4*>(mine + i * 8);
+    const uint4 gu = *reinterpret_cast<const uint4*>(grad + i * 8);
+    const uint4 mu = *reinterpret_cast<const uint4*>(m + i * 8);
+    const uint4 vu = *reinterpret_cast<const uint4*>(v + i * 8);
+    const uint32_t pw[4] = {pu.x, pu.y, pu.z, pu.w}, gw[4] = {gu.x, gu.y, gu.z, gu.w};
+    const uint32_t mw[4] = {mu.x, mu.y, mu.z, mu.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+    uint32_t po[4], mo[4], vo[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 p2 = unpack_bf16(pw[k]), g2 = unpack_bf16(gw[k]), m2 = unpack_bf16(mw[k]), v2 = unpack_bf16(vw[k]);
+      float pe[2] = {p2.x, p2.y}, ge[2] = {g2.x * gs, g2.y * gs}, me[2] = {m2.x, m2.y}, ve[2] = {v2.x, v2.y};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (lo + i * 8 + k * 2 + e < n_decay_global) pe[e] *= 1.f - lr * wd;
+        me[e] = b1 * me[e] + (1.f - b1) * ge[e];
+        ve[e] = b2 * ve[e] + (1.f - b2) * ge[e] * ge[e];
+        pe[e] -= step * me[e] / (sqrtf(ve[e]) / bc2_sqrt + eps);
+      }
+      po[k] = pack_bf16(pe[0], pe[1]);
+      mo[k] = pack_bf16(me[0], me[1]);
+      vo[k] = pack_bf16(ve[0], ve[1]);
+    }
+    *reinterpret_cast<uint4*>(m + i * 8) = make_uint4(mo[0], mo[1], mo[2], mo[3]);
+    *reinterpret_cast<uint4*>(v + i * 8) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+    const uint4 pn = make_uint4(po[0], po[1], po[2], po[3]);
+    if (mc_param) {
+      multimem_st_16B(reinterpret_cast<__nv_bfloat16*>(mc_param) + lo + i * 8, pn);
+    } else {
+      for (int r = 0; r < world; ++r)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + lo + i * 8) = pn;
+    }
+  }
+}
+
+// Copy this rank's shard [lo, lo + n) of its own buffer into the same range of every peer's buffer.
+__global__ void kf_symm_gather(PeerPtrs bufs, void* mc_buf, int world, int rank, long long lo, long long n) {
+  const long long nvec = n >> 3;
+  const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + lo;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 u = *reinterpret_cast<const uint4*>(mine + i * 8);
+    if (mc_buf) {
+      multimem_st_16B(reinterpret_cast<__nv_bfloat16*>(mc_buf) + lo + i * 8, u);
+    } else {
+      for (int r = 0; r < world; ++r)
+        if (r != rank) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i * 8) = u;
+    }
+  }
+}
+
+static inline PeerPtrs make_ptrs(const long long* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return pp;
+}
+
+}  // namespace kf
+
+extern "C" {
+
+// partial must hold 1024 floats; out[0] (+)= sum of squares of the averaged shard.  n % 8 == 0, lo % 8 == 0.
+int kf_symm_rs_norm_bf16(const long long* peer_grad_ptrs, const void* mc_grad, int world, int rank, long long lo,
+                         long long n, void* partial, void* out, int accumulate, int max_blocks, void* stream) {
+  using namespace kf;
+  if (world > MAX_PEERS || (n & 7) || (lo & 7)) return 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  long long want = (n / 8 + 511) / 512;
+  int nb = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  if (nb > 1024) nb = 1024;
+  kf_symm_rs_norm<<<nb, 512, 0, st>>>(make_ptrs(peer_grad_ptrs, world), mc_grad, world, rank, lo, n, 1.f / world,
+                                      (float*)partial);
+  kf_sum_partials<<<1, 256, 0, st>>>((const float*)partial, nb, (float*)out, accumulate);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+int kf_symm_adamw_bcast_bf16(const long long* peer_param_ptrs, void* mc_param, int world, int rank, const void* grad,
+                             void* m, void* v, long long lo, long long n, long long n_decay_global, float lr, float b1,
+                             float b2, float eps, float wd, float bc1, float bc2_sqrt, const void* grad_scale,
+                             const void* skip, int max_blocks, void* stream) {
+  using namespace kf;
+  if (world > MAX_PEERS || (n & 7) || (lo & 7)) return 1;
+  long long want = (n / 8 + 255) / 256;
+  int nb = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  kf_symm_adamw_bcast<<<nb, 256, 0, (cudaStream_t)stream>>>(
+      make_ptrs(peer_param_ptrs, world), mc_param, world, rank, (const __nv_bfloat16*)grad, (__nv_bfloat16*)m,
+      (__nv_bfloat16*)v, lo, n, n_decay_global, lr, b1, b2, eps, wd, bc1, bc2_sqrt, (const float*)grad_scale,
+      (const int*)skip);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+int kf_symm_gather_bf16(const long long* peer_ptrs, void* mc_buf, int world, int rank, long long lo, long long n,
+                        int max_blocks, void* stream) {
+  using namespace kf;
+  if (world > MAX_PEERS || (n & 7) || (lo & 7)) return 1;
+  long long want = (n / 8 + 255) / 256;
+  int nb = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  kf_symm_gather<<<nb, 256, 0, (cudaStream_t)stream>>>(make_ptrs(peer_ptrs, world), mc_buf, world, rank, lo, n);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // extern "C"

@@ -58,6 +58,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
         "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
         "kf_test_flag_timeout": [vp, i, ll],
+        "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
+        "kf_symm_adamw_bcast_bf16": [vp, vp, i, i, vp, vp, vp, ll, ll, ll, f, f, f, f, f, f, f, vp, vp, i, vp],
+        "kf_symm_gather_bf16": [vp, vp, i, i, ll, ll, i, vp],
         "kf_read_status": [],
         "kf_clear_status": [],
         "kf_status_device_ptr": [],
@@ -316,3 +319,35 @@ def attn_supported(q, k, v, causal: bool) -> bool:
         return False
     hd = q.shape[-1]
     return hd in (64, 128) and q.shape[1] == k.shape[1] and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+
+
+# --------------------------------------------------------------------------- fused communication kernels
+def symm_rs_norm(buf, lo: int, n: int, sumsq_out: torch.Tensor, accumulate: bool, max_blocks: int = 296) -> None:
+    """Average this rank's shard [lo, lo+n) of a symmetric gradient buffer over all ranks (in place, own copy)
+    and add the squared norm of the result to ``sumsq_out[0]``."""
+    partial = torch.empty(1024, dtype=torch.float32, device=buf.tensor.device)
+    _check(
+        lib().kf_symm_rs_norm_bf16(buf.peer_ptrs, buf.multicast_ptr, buf.world, buf.rank, lo, n, partial.data_ptr(),
+                                   sumsq_out.data_ptr(), int(accumulate), max_blocks, _stream()),
+        "kf_symm_rs_norm_bf16",
+    )
+
+
+def symm_adamw_bcast(param_buf, grad_shard, m, v, lo: int, n: int, n_decay_global: int, lr, beta1, beta2, eps, wd,
+                     step: int, grad_scale=None, skip=None, max_blocks: int = 592) -> None:
+    """AdamW on the shard [lo, lo+n) and store of the new parameters into every rank's parameter buffer."""
+    bc1 = 1.0 - beta1**step
+    bc2_sqrt = math.sqrt(1.0 - beta2**step)
+    _check(
+        lib().kf_symm_adamw_bcast_bf16(
+            param_buf.peer_ptrs, param_buf.multicast_ptr, param_buf.world, param_buf.rank, grad_shard.data_ptr(),
+            m.data_ptr(), v.data_ptr(), lo, n, n_decay_global, lr, beta1, beta2, eps, wd, bc1, bc2_sqrt,
+            grad_scale.data_ptr() if grad_scale is not None else None, skip.data_ptr() if skip is not None else None,
+            max_blocks, _stream()),
+        "kf_symm_adamw_bcast_bf16",
+    )
+
+
+def symm_gather(buf, lo: int, n: int, max_blocks: int = 592) -> None:
+    _check(lib().kf_symm_gather_bf16(buf.peer_ptrs, buf.multicast_ptr, buf.world, buf.rank, lo, n, max_blocks, _stream()),
+           "kf_symm_gather_bf16")

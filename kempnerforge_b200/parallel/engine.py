@@ -49,6 +49,9 @@ class DataParallelEngine:
         self._reduce_work: dict[int, object] = {}  # group index -> in-flight gradient reduction
         self._gather_work: dict[int, object] = {}  # group index -> in-flight parameter publication
         self._group_of_module: dict[int, int] = {}
+        self.symmetric = transport == "symmetric" and self.world > 1 and self.groups[0].grad_symm is not None
+        self._comm_stream = torch.cuda.Stream() if (self.symmetric and dev.type == "cuda") else None
+        self._sq_from_reduce = False
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
         if self.world > 1:
@@ -124,6 +127,8 @@ class DataParallelEngine:
         return None
 
     def _reduce_one(self, g: FlatParamGroup, async_op: bool = False):
+        if self.symmetric and g.grad_symm is not None:
+            return self._reduce_one_symmetric(g, async_op)
         if g.grad.is_cuda and "nccl" in str(dist.get_backend(self.pg)):
             lo, hi = g.shard_range
             return dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
@@ -132,6 +137,33 @@ class DataParallelEngine:
             return _ScaledWork(work, g.grad, self.world)
         g.grad.div_(self.world)
         return None
+
+    def _reduce_one_symmetric(self, g: FlatParamGroup, async_op: bool):
+        """Barrier (all ranks finished writing this unit's gradients) + fused reduce-scatter / scale / norm
+        kernel over peer memory; on the side stream when launched from a block's backward hook."""
+        from kempnerforge_b200.ops import cuda as kcuda
+
+        lo, hi = g.shard_range
+        slot = 2 if g.ep_sharded else 0
+        if not self._sq_from_reduce:
+            self._sq3.zero_()
+            self._sq_from_reduce = True
+
+        def launch():
+            g.grad_symm.barrier()
+            kcuda.symm_rs_norm(g.grad_symm, lo, hi - lo, self._sq3[slot : slot + 1], accumulate=True)
+
+        if not async_op or self._comm_stream is None:
+            launch()
+            return None
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ready)
+            launch()
+            done = torch.cuda.Event()
+            done.record()
+        return _EventWork(done)
 
     def set_requires_gradient_sync(self, flag: bool) -> None:
         self.requires_sync = bool(flag)
@@ -184,6 +216,19 @@ class DataParallelEngine:
         shards (summed over the TP group) and expert-parallel shards (summed over the EP group).  Every bucket is
         first summed over the data-parallel shards; ``extra_groups`` (pipeline stages) are summed last.
         """
+        if self._sq_from_reduce:  # the fused reduce kernels already produced the shard sums of squares
+            self._sq_from_reduce = False
+            if self.world > 1:
+                dist.all_reduce(self._sq3, group=self.pg)
+            total = self._sq3.sum().reshape(1)
+            for grp in extra_groups:
+                dist.all_reduce(total, group=grp)
+            torch.sqrt(total, out=self.grad_norm)
+            if max_norm is not None and max_norm > 0:
+                torch.clamp(max_norm / (self.grad_norm + 1e-6), max=1.0, out=self.grad_scale)
+            else:
+                self.grad_scale.fill_(1.0)
+            return self.grad_norm
         self._sq3.zero_()
         for g in self.groups:
             lo, hi = g.shard_range
@@ -220,6 +265,11 @@ class DataParallelEngine:
     def after_optimizer_step(self) -> None:
         """Publish the updated shards so that every rank holds the full new parameters.  On GPUs the
         all-gathers are asynchronous and each block waits for its own only when its next forward starts."""
+        if self.symmetric:
+            # the optimizer kernel already stored the new parameters on every rank; one barrier makes sure all
+            # ranks' stores (and their reads of our gradients) are complete before the next step touches them
+            self.groups[-1].param_symm.barrier()
+            return
         if self.world > 1:
             use_async = self.groups[0].param.is_cuda and bool(self._group_of_module is not None)
             for i, g in enumerate(self.groups):
@@ -258,6 +308,16 @@ class DataParallelEngine:
         lo, hi = g.shard_range
         g.exp_avg.copy_(exp_avg[lo:hi])
         g.exp_avg_sq.copy_(exp_avg_sq[lo:hi])
+
+
+class _EventWork:
+    """Handle of work queued on the communication stream: ``wait`` makes the current stream wait for it."""
+
+    def __init__(self, event) -> None:
+        self.event = event
+
+    def wait(self) -> None:
+        torch.cuda.current_stream().wait_event(self.event)
 
 
 class _ScaledWork:

@@ -90,6 +90,13 @@ class FlatParamGroup:
         alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
         self.param = alloc(self.numel, self.dtype, self.device)
         self.grad = alloc(self.numel, self.dtype, self.device)
+        # symmetric-memory descriptors of the two buffers (None with an ordinary allocator)
+        self.param_symm = self.grad_symm = None
+        if allocator is not None and not local:
+            from kempnerforge_b200.comm import symmetric
+
+            self.param_symm = symmetric.lookup(self.param)
+            self.grad_symm = symmetric.lookup(self.grad)
         self.exp_avg: torch.Tensor | None = None
         self.exp_avg_sq: torch.Tensor | None = None
         self.step_tensor = torch.zeros((), dtype=torch.float32)

@@ -75,7 +75,12 @@ class FusedAdamW(torch.optim.AdamW):
             p, g, m, v = fg.optimizer_views()
             if p.numel() == 0:
                 continue
-            if p.is_cuda:
+            if p.is_cuda and getattr(fg, "param_symm", None) is not None and fg.world > 1:
+                # sharded update fused with the parameter all-gather: new values go straight to every rank
+                lo, hi = fg.shard_range
+                kcuda.symm_adamw_bcast(fg.param_symm, g, m, v, lo, hi - lo, fg.n_decay, lr, b1, b2, eps, wd,
+                                       fg.step_count, self.grad_scale, self.skip_flag)
+            elif p.is_cuda:
                 kcuda.adamw_flat(p, g, m, v, fg.n_decay_local, lr, b1, b2, eps, wd, fg.step_count,
                                  self.grad_scale, self.skip_flag)
             else:

@@ -22,7 +22,7 @@ cfg = config_from_dict({
     "train": dict(batch_size=2, seq_len=256, max_steps=10, mixed_precision="bf16", activation_checkpointing="full", seed=0),
     "optimizer": dict(lr=1e-3), "scheduler": dict(warmup_steps=0, name="constant"),
     "distributed": dict(dp_shard=world), "metrics": dict(log_interval=1000)})
-t = Trainer(cfg)
+t = Trainer(cfg, transport=os.environ.get("KF_TRANSPORT") or None)
 g = torch.Generator().manual_seed(100 + rank)
 out = []
 for step in range(4):
@@ -40,8 +40,9 @@ torch.distributed.destroy_process_group()
 '''
 
 
-def _run(world: int):
-    env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+def _run(world: int, transport: str = "", multimem: bool = True):
+    env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KF_TRANSPORT=transport,
+               KF_SYMM_MULTIMEM="1" if multimem else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29631", "-"]
     res = subprocess.run(cmd, input=WORKER, capture_output=True, text=True, env=env, timeout=600)
@@ -56,3 +57,16 @@ def test_sharded_data_parallel_two_gpus():
     assert r["replicas_identical"], "ranks ended with different parameters"
     assert all(l == l and 0 < l < 20 for l in r["losses"]) and all(n > 0 for n in r["norms"])
     assert r["losses"][-1] < r["losses"][0] + 0.5
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("multimem", [False, True])
+def test_symmetric_transport_matches_collectives(multimem):
+    """Fused reduce-scatter / AdamW / publish kernels over peer memory against the NCCL path."""
+    base = _run(2)
+    fused = _run(2, transport="symmetric", multimem=multimem)
+    assert fused["replicas_identical"]
+    for a, b in zip(base["losses"], fused["losses"]):
+        assert abs(a - b) < 5e-2, (base["losses"], fused["losses"])
+    for a, b in zip(base["norms"], fused["norms"]):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (base["norms"], fused["norms"])
