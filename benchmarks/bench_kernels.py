@@ -1,0 +1,51 @@
+"""The hand-written sm_100a kernels against their roofs: tcgen05 GEMMs at the Llama-3-8B shapes
+(TFLOP/s, with the cuBLAS figure beside it) and the memory-bound kernels (GB/s). GPU only.
+No counterpart in the reference, which ships no kernels of its own."""
+
+from __future__ import annotations
+
+import torch
+
+from benchmarks.runner import Case, print_results, run_suite
+
+SUITE = "kernels"
+
+# (M, N, K): tokens x out x in for micro-batch 2 x 4096 of the 8B shape
+GEMM_SHAPES = [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336)]
+
+
+def cases(device: torch.device):
+    if device.type != "cuda":
+        return
+    from kempnerforge_b200.ops import cuda as K
+
+    bf = torch.bfloat16
+    for m, n, k in GEMM_SHAPES:
+        a = torch.randn(m, k, device=device, dtype=bf)
+        w = torch.randn(n, k, device=device, dtype=bf) * 0.02
+        out = torch.empty(m, n, device=device, dtype=bf)
+        flops = 2.0 * m * n * k
+        yield Case(f"tcgen05 GEMM {m}x{n}x{k}", lambda a=a, w=w, out=out: K.gemm(a, w, out=out), flops_per_iter=flops)
+        yield Case(f"cuBLAS  GEMM {m}x{n}x{k}", lambda a=a, w=w, out=out: torch.matmul(a, w.t(), out=out),
+                   flops_per_iter=flops)
+
+    t, d = 8192, 4096
+    x = torch.randn(t, d, device=device, dtype=bf)
+    wn = torch.ones(d, device=device, dtype=bf)
+    yield Case("rmsnorm fwd (8192x4096)", lambda: K.rmsnorm_fwd(x, wn, 1e-5), bytes_per_iter=2 * x.numel() * 2)
+    h = torch.randn(t, 2 * 14336, device=device, dtype=bf)
+    yield Case("swiglu fwd (8192x14336)", lambda: K.swiglu_fwd(h), bytes_per_iter=h.numel() * 2 * 1.5)
+    nparam = 218_112_000
+    p = torch.randn(nparam, device=device, dtype=bf)
+    g = torch.randn(nparam, device=device, dtype=bf)
+    m1 = torch.zeros(nparam, device=device, dtype=bf)
+    m2 = torch.zeros(nparam, device=device, dtype=bf)
+    yield Case("AdamW flat (one 8B block, 218M params)",
+               lambda: K.adamw_flat(p, g, m1, m2, nparam, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1),
+               bytes_per_iter=nparam * 2 * 7)
+    acc = torch.zeros(1, device=device, dtype=torch.float32)
+    yield Case("sum of squares (218M bf16)", lambda: K.sumsq(g, acc), bytes_per_iter=nparam * 2)
+
+
+if __name__ == "__main__":
+    print_results(run_suite(SUITE, torch.device("cuda")), "kernels")

@@ -320,8 +320,15 @@ class Trainer:
             self._maybe_advance_phase()
             extra = self._moe_metrics() if (self.step % cfg.metrics.log_interval == 0 or self.step == 1) else None
             self.tracker.end_step(self.step, out["loss"], out["grad_norm"], out["lr"], tokens_per_step, extra)
-            self.hook_runner.on_step_end(StepContext(self.step, out["loss"], out["grad_norm"], out["lr"],
-                                                     self.tokens_seen, self.model, self.optimizer))
+            ctx = StepContext(self.step, out["loss"], out["grad_norm"], out["lr"], self.tokens_seen, self.model,
+                              self.optimizer)
+            self.hook_runner.on_step_end(ctx)
+            if ctx.metrics:
+                self.tracker.log_extra(ctx.metrics, self.step)
+            if any(getattr(h, "should_stop", False) for h in self.hook_runner.hooks):
+                stop_reason = "hook"
+                log.info("a training hook asked to stop at step %d", self.step)
+                break
             if tc.nccl_health_check_interval > 0 and self.step % tc.nccl_health_check_interval == 0:
                 from kempnerforge_b200.resilience import check_nccl_health
 

@@ -40,13 +40,16 @@ torch.distributed.destroy_process_group()
 '''
 
 
-def _run(world: int, transport: str = "", multimem: bool = True):
+def _run(world: int, transport: str = "", multimem: bool = True, tmp_dir: str = "/tmp"):
+    script = os.path.join(tmp_dir, f"kf_multi_gpu_worker_{os.getpid()}.py")
+    with open(script, "w") as f:
+        f.write(WORKER)
     env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KF_TRANSPORT=transport,
                KF_SYMM_MULTIMEM="1" if multimem else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", "29631", "-"]
-    res = subprocess.run(cmd, input=WORKER, capture_output=True, text=True, env=env, timeout=600)
-    assert res.returncode == 0, res.stderr[-3000:]
+           "--master-addr", "127.0.0.1", "--master-port", "29631", script]
+    res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0, (res.stdout[-1500:] + "\n" + res.stderr[-4000:])
     line = [ln for ln in res.stdout.splitlines() if ln.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
 
