@@ -674,3 +674,43 @@ extern "C" int kf_test_flag_timeout(const void* flag, int expected, long long bu
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
+
+// ------------------------------------------------------------------ sum of squares without caller scratch
+// Same kernels as kf_sumsq; the partial sums live in a device array that is part of the library image.
+#include "kf_noalloc.h"
+
+namespace kf {
+constexpr int SUMSQ_SCRATCH_FLOATS = 1024;
+static __device__ __align__(256) float g_sumsq_scratch[SUMSQ_SCRATCH_FLOATS];
+static float* g_sumsq_scratch_addr[64] = {nullptr};  // per device: the array's device address
+}  // namespace kf
+
+extern "C" int kf_sumsq_noalloc(const void* x, long long n, int dt, void* out, int accumulate, void* stream) {
+  using namespace kf;
+  if (n < 0 || n > KF_SUMSQ_NOALLOC_MAX_ELEMS) return 3;
+  if (dt != 0 && dt != 1) return 4;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 500;
+  if (!g_sumsq_scratch_addr[dev]) {
+    // In host code `g_sumsq_scratch` names a host-side shadow, not device memory: ask the runtime for the
+    // device address of this device's instance (once per device, with that device current).
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sumsq_scratch);
+    if (e != cudaSuccess || p == nullptr) return 500 + (int)e;
+    g_sumsq_scratch_addr[dev] = p;
+  }
+  float* scratch = g_sumsq_scratch_addr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nb = grid_for(dt == 0 ? n / 8 + 1 : n, 512, SUMSQ_SCRATCH_FLOATS);
+  // every slot that stage 2 reads (0 .. nb-1) is written by stage 1 of this call, so stale contents of the
+  // shared array from an earlier call never enter the result
+  if (dt == 0 && ((uintptr_t)x & 15) == 0)
+    kf_sumsq_stage1_bf16x8<<<nb, 512, 0, st>>>((const __nv_bfloat16*)x, n, scratch);
+  else if (dt == 0)
+    kf_sumsq_stage1<__nv_bfloat16><<<nb, 512, 0, st>>>((const __nv_bfloat16*)x, n, scratch);
+  else
+    kf_sumsq_stage1<float><<<nb, 512, 0, st>>>((const float*)x, n, scratch);
+  kf_sumsq_stage2<<<1, 256, 0, st>>>(scratch, nb, (float*)out, accumulate);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
