@@ -59,4 +59,44 @@ def build_train_dataloader(config, dp_rank: int = 0, dp_size: int = 1):
     return StatefulDataLoader(ds, tc.batch_size, sampler, dc.num_workers, dc.pin_memory, dc.prefetch_factor, True)
 
 
+def build_vlm_dataloader(config, dp_rank: int = 0, dp_size: int = 1, *, dataset=None, tokenizer=None):
+    """Image-text or video-caption batches of fixed shape for a vision-language run.
+
+    ``[video]`` present -> the registered video dataset (clips -> frames + frame_mask); otherwise the
+    Hugging Face image-text dataset named by ``data.hf_dataset_name``.  Synthetic data is not offered for
+    VLM runs.  Parity: scripts/train.py:290-344 of the reference.
+    """
+    from kempnerforge_b200.data.vlm_dataset import HuggingFaceVLMDataset, VLMCollator, pad_token_id
+
+    dc, tc, vlm = config.data, config.train, config.vlm
+    if dataset is None:
+        if config.is_video:
+            from kempnerforge_b200.data.video_dataset import build_video_dataset
+
+            extra = {"tokenizer": tokenizer} if tokenizer is not None else {}
+            dataset = build_video_dataset(config.video, dc.tokenizer_path, vlm.max_text_len, **extra)
+        else:
+            if not (dc.hf_dataset_name and (dc.tokenizer_path or tokenizer is not None)):
+                raise ValueError("VLM training requires data.hf_dataset_name and data.tokenizer_path")
+            enc = config.vision_encoder
+            dataset = HuggingFaceVLMDataset(
+                dc.hf_dataset_name, dc.hf_dataset_split, dc.hf_dataset_image_field, dc.hf_dataset_text_field,
+                dc.tokenizer_path, vlm.max_text_len, prompt_field=dc.hf_dataset_prompt_field or None,
+                image_size=getattr(enc, "image_size", 224) or 224, dataset_config=dc.hf_dataset_config,
+                tokenizer=tokenizer)
+    tok = getattr(dataset, "tokenizer", tokenizer)
+    pad = getattr(dataset, "pad_id", None)
+    if pad is None:
+        pad = pad_token_id(tok) if tok is not None else 0
+    if config.is_video:
+        from kempnerforge_b200.data.video_dataset import VideoCollator
+
+        collate = VideoCollator(pad, vlm.max_text_len)
+    else:
+        collate = VLMCollator(pad, vlm.max_text_len)
+    sampler = DistributedSampler(len(dataset), dp_size, dp_rank, True, tc.effective_data_seed, True)
+    return StatefulDataLoader(dataset, tc.batch_size, sampler, dc.num_workers, dc.pin_memory, dc.prefetch_factor, True,
+                              collate_fn=collate)
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -58,6 +58,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
         "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
         "kf_test_flag_timeout": [vp, i, ll],
+        "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
         "kf_symm_adamw_bcast_bf16": [vp, vp, i, i, vp, vp, vp, ll, ll, ll, f, f, f, f, f, f, f, vp, vp, i, vp],
         "kf_symm_gather_bf16": [vp, vp, i, i, ll, ll, i, vp],
@@ -313,12 +314,44 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch
 
 
 # --------------------------------------------------------------------------- attention
-def attn_supported(q, k, v, causal: bool) -> bool:
-    fn = getattr(lib(), "kf_attn_fwd_bf16", None)
-    if fn is None or os.environ.get("KF_DISABLE_NATIVE_ATTN"):
+def _attn_rows_ok(t: torch.Tensor) -> bool:
+    """(B, S, heads, hd) whose (b, s) pairs form evenly pitched rows with the heads side by side."""
+    b, s, _, hd = t.shape
+    return (t.stride(-1) == 1 and t.stride(2) == hd and (b == 1 or t.stride(0) == s * t.stride(1))
+            and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0)
+
+
+def attn_supported(q, k, v, causal: bool, needs_grad: bool = False) -> bool:
+    """Shapes the tcgen05 attention kernels cover: bf16, head dim 64 or 128, grouped KV heads, causal or full,
+    optional document ids; q / k / v may be strided views of one fused projection output."""
+    L = lib()
+    if getattr(L, "kf_attn_fwd_bf16", None) is None or os.environ.get("KF_DISABLE_NATIVE_ATTN"):
         return False
-    hd = q.shape[-1]
-    return hd in (64, 128) and q.shape[1] == k.shape[1] and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    if needs_grad and getattr(L, "kf_attn_bwd_bf16", None) is None:
+        return False
+    if q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128) or q.shape[2] % k.shape[2] != 0:
+        return False
+    if causal and q.shape[1] != k.shape[1]:
+        return False
+    return _attn_rows_ok(q) and _attn_rows_ok(k) and _attn_rows_ok(v)
+
+
+def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
+    """q (B, Sq, H, hd), k / v (B, Sk, Hkv, hd) -> out (B, Sq, H, hd) bf16 and lse (B, H, Sq) fp32."""
+    b, sq, h, hd = q.shape
+    sk, hkv = k.shape[1], k.shape[2]
+    out = torch.empty((b, sq, h, hd), dtype=q.dtype, device=q.device)
+    lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    doc = None
+    if doc_ids is not None:
+        doc = doc_ids.to(torch.int32).contiguous()
+    _check(
+        lib().kf_attn_fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                               doc.data_ptr() if doc is not None else None, b, sq, sk, h, hkv, hd, q.stride(1),
+                               k.stride(1), v.stride(1), h * hd, float(scale), int(causal), _stream()),
+        "kf_attn_fwd_bf16",
+    )
+    return out, lse
 
 
 # --------------------------------------------------------------------------- fused communication kernels

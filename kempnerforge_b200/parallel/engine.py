@@ -49,6 +49,8 @@ class DataParallelEngine:
         self._reduce_work: dict[int, object] = {}  # group index -> in-flight gradient reduction
         self._gather_work: dict[int, object] = {}  # group index -> in-flight parameter publication
         self._group_of_module: dict[int, int] = {}
+        self._handles: list = []   # forward pre-hooks installed on the model
+        self._wrapped: list[str] = []  # model methods replaced by waiting wrappers
         self.symmetric = transport == "symmetric" and self.world > 1 and self.groups[0].grad_symm is not None
         self._comm_stream = torch.cuda.Stream() if (self.symmetric and dev.type == "cuda") else None
         self._sq_from_reduce = False
@@ -71,23 +73,30 @@ class DataParallelEngine:
     def _install_overlap_hooks(self) -> None:
         """Reduce a block's gradients as soon as its backward finished, and wait for a block's freshly
         published parameters only when its forward starts."""
-        layers = getattr(self.model, "layers", None)
-        if not isinstance(layers, nn.ModuleDict):
-            return
         by_name = {g.name: i for i, g in enumerate(self.groups)}
-        for key, block in layers.items():
-            idx = by_name.get(f"layers.{key}")
-            if idx is None:
+        covered: set[int] = set()
+        for mod_name, mod in self.model.named_modules():  # the block stack may sit below a wrapper module
+            layers = getattr(mod, "layers", None)
+            if not isinstance(layers, nn.ModuleDict):
                 continue
-            extra = by_name.get(f"layers.{key}.experts")
-            idxs = [idx] + ([extra] if extra is not None else [])
-            block.register_forward_pre_hook(self._make_pre_hook(idxs))
-        root = [i for i, g in enumerate(self.groups) if g.name.startswith("root")]
-        self.model.register_forward_pre_hook(lambda m, a: self.wait_params(root))
+            base = f"{mod_name}.layers" if mod_name else "layers"
+            for key, block in layers.items():
+                idx = by_name.get(f"{base}.{key}")
+                if idx is None:
+                    continue
+                extra = by_name.get(f"{base}.{key}.experts")
+                idxs = [idx] + ([extra] if extra is not None else [])
+                covered.update(idxs)
+                self._handles.append(block.register_forward_pre_hook(self._make_pre_hook(idxs)))
+            break
+        # everything that no block hook covers is waited for when the model itself is entered
+        root = [i for i in range(len(self.groups)) if i not in covered]
+        self._handles.append(self.model.register_forward_pre_hook(lambda m, a: self.wait_params(root)))
         for name in ("forward_hidden", "compute_loss"):
             fn = getattr(self.model, name, None)
             if fn is not None:
                 setattr(self.model, name, self._wrap_wait(fn, root))
+                self._wrapped.append(name)
 
     def _wrap_wait(self, fn, idxs):
         def wrapped(*a, **k):
@@ -280,6 +289,27 @@ class DataParallelEngine:
                     self._gather_work[i] = dist.all_gather_into_tensor(g.param, g.param[lo:hi], group=self.pg, async_op=True)
                 else:
                     dist.all_gather_into_tensor(g.param, g.param[lo:hi].clone(), group=self.pg)
+
+    def release(self) -> None:
+        """Detach from the model (before another engine is built over a changed set of trainable parameters):
+        drains communication, removes hooks and wrappers, and gives every parameter storage of its own."""
+        self.wait_all()
+        for h in self._handles:
+            h.remove()
+        self._handles.clear()
+        for name in self._wrapped:
+            self.model.__dict__.pop(name, None)
+        self._wrapped.clear()
+        for g in self.groups:
+            for p in g.params:
+                p.data = p.data.clone()
+                p.grad = None
+                for attr in ("_kf_grad", "_kf_grad_live"):
+                    if hasattr(p, attr):
+                        delattr(p, attr)
+        self.groups = []
+        if getattr(self.model, "_kf_engine", None) is self:
+            del self.model._kf_engine
 
     def wait_all(self) -> None:
         """Drain every in-flight reduction / publication (before checkpoints, evaluation, shutdown)."""

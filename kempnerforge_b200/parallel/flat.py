@@ -213,10 +213,14 @@ def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=Non
             groups[-1].ep_sharded = True
         taken.update(id(p) for _, p in items)
 
-    layers = getattr(model, "layers", None)
-    if isinstance(layers, nn.ModuleDict):
-        for key, block in layers.items():
-            add(f"layers.{key}", group_module_params(block, f"layers.{key}."))
+    # the block stack may sit below a wrapper (vision-language models): use the first ``layers`` ModuleDict
+    for mod_name, mod in model.named_modules():
+        layers = getattr(mod, "layers", None)
+        if isinstance(layers, nn.ModuleDict):
+            base = f"{mod_name}.layers" if mod_name else "layers"
+            for key, block in layers.items():
+                add(f"{base}.{key}", group_module_params(block, f"{base}.{key}."))
+            break
     by_dtype: dict[torch.dtype, list] = {}
     for n, p in group_module_params(model):
         if id(p) not in taken and p.requires_grad:

@@ -126,3 +126,39 @@ def build_parallel_model(
     if compile_model:
         log.info("compile_model is accepted for preset compatibility; this build has no tracing compiler")
     return model
+
+
+def build_parallel_vlm(job_config, device: torch.device, device_mesh=None, *, step: int = 0,
+                       transport: str | None = None) -> nn.Module:
+    """Vision encoder + adapter + transformer as one data-parallel model.
+
+    Order: build -> cast (the transformer and adapter to the training dtype; a frozen encoder keeps its own
+    dtype and stays in eval mode) -> freeze according to the schedule at ``step`` -> AC -> sharded DP over
+    the trainable parameters only (frozen ones are replicated and never enter a flat group).
+    Parity: kempnerforge/distributed/parallel.py:305-496 (VLM variants of the FSDP wrapping).
+    """
+    from kempnerforge_b200.models.vlm import build_vlm_wrapper, is_encoder_frozen
+    from kempnerforge_b200.training.freeze import apply_freeze_specs, effective_freeze
+
+    cfg = job_config
+    tc = cfg.train
+    frames = cfg.video.max_frames if cfg.video is not None else 1
+    with torch.device(device):
+        model = build_vlm_wrapper(cfg.model, cfg.vision_encoder, cfg.adapter, cfg.vlm, frames_per_clip=frames)
+    model.transformer.to(device=device, dtype=tc.param_dtype)
+    model.adapter.to(device=device, dtype=tc.param_dtype)
+    specs = effective_freeze(cfg.vlm, step)
+    apply_freeze_specs(model, specs, cfg.vlm.module_patterns)
+    if is_encoder_frozen(specs):
+        model.vision_encoder.to(device=device).eval()
+    else:
+        model.vision_encoder.to(device=device, dtype=tc.param_dtype)
+    model.transformer.rope_tables(device, 0, 1)
+    ac = str(tc.activation_checkpointing)
+    if ac != "none":
+        apply_ac(model, ac)
+    apply_fsdp2(model, device_mesh, transport=transport)
+    n_train = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    n_all = sum(p.numel() for p in model.parameters())
+    log.info("VLM (%s): %s trainable of %s parameters", cfg.vlm.arch, f"{n_train:,}", f"{n_all:,}")
+    return model

@@ -103,8 +103,14 @@ class Trainer:
         self.nan_detector = NaNDetector(action="warn", max_consecutive=10)
 
         self.pipeline = None
+        self._transport = transport
+        self._freeze_stage_idx = -1
         if model is not None:
             self.model = model
+        elif config.is_vlm:
+            from kempnerforge_b200.parallel.parallel import build_parallel_vlm
+
+            self.model = build_parallel_vlm(config, self.device, self.mesh, step=0, transport=transport)
         elif self.pp_size > 1:
             from kempnerforge_b200.parallel.pipeline_parallel import build_pipeline
 
@@ -138,9 +144,60 @@ class Trainer:
 
     # ------------------------------------------------------------------ data
     def _default_dataloader(self):
-        from kempnerforge_b200.data import build_train_dataloader
+        from kempnerforge_b200.data import build_train_dataloader, build_vlm_dataloader
 
+        if self.config.is_vlm:
+            return build_vlm_dataloader(self.config, self.dp_rank, self.dp_size)
         return build_train_dataloader(self.config, self.dp_rank, self.dp_size)
+
+    # ------------------------------------------------------------------ freeze schedule (vision-language runs)
+    def _maybe_advance_freeze_stage(self) -> None:
+        """At a stage boundary the set of trainable parameters changes: drain pending communication and
+        saves, flip ``requires_grad``, then rebuild the flat groups and the optimizer; moments of parameters
+        that stay trainable are carried over by name."""
+        vlm = self.config.vlm
+        if vlm is None or not vlm.freeze_schedule:
+            return
+        idx = -1
+        for i, stage in enumerate(vlm.freeze_schedule):
+            if self.step >= stage.start_step:
+                idx = i
+        if idx == self._freeze_stage_idx:
+            return
+        first = self._freeze_stage_idx == -1 and self.step == 0 and idx == -1
+        self._freeze_stage_idx = idx
+        if first:
+            return
+        from kempnerforge_b200.checkpoint.manager import load_optimizer_state_dict, optimizer_state_dict
+        from kempnerforge_b200.models.vlm import is_encoder_frozen
+        from kempnerforge_b200.parallel.parallel import apply_fsdp2
+        from kempnerforge_b200.training.freeze import apply_freeze_specs, effective_freeze
+
+        if self.engine is not None:
+            self.engine.wait_all()
+        if self.ckpt is not None:
+            self.ckpt.wait()
+        old_state = optimizer_state_dict(self.model, self.optimizer)
+        lr_now = [g["lr"] for g in self.optimizer.param_groups]
+        specs = effective_freeze(vlm, self.step)
+        counts = apply_freeze_specs(self.model, specs, vlm.module_patterns)
+        self.model.vision_encoder.train(not is_encoder_frozen(specs))
+        log.info("freeze stage %d at step %d: %s", idx, self.step, counts)
+        if self.engine is not None:
+            self.engine.release()
+        apply_fsdp2(self.model, self.mesh, transport=self._transport)
+        self.engine = getattr(self.model, "_kf_engine", None)
+        self.optimizer = build_optimizer(self.model, self.config.optimizer)
+        if isinstance(self.optimizer, FusedAdamW) and self.engine is not None:
+            self.optimizer.grad_scale = self.engine.grad_scale
+        load_optimizer_state_dict(self.model, self.optimizer, old_state)
+        sched_state = self.scheduler.state_dict()
+        self.scheduler = build_scheduler(self.optimizer, self.config.scheduler, self.config.train.max_steps)
+        self.scheduler.load_state_dict(sched_state)
+        for g, lr in zip(self.optimizer.param_groups, lr_now):
+            g["lr"] = lr
+        if self.ckpt is not None:
+            self.ckpt.optimizer = self.optimizer
 
     def next_batch(self) -> dict[str, torch.Tensor]:
         if self.dataloader is None:
@@ -160,6 +217,13 @@ class Trainer:
         ids = batch["input_ids"]
         labels = batch["labels"]
         doc_ids = batch.get("doc_ids")
+        if "pixel_values" in batch:
+            pixels = batch["pixel_values"]
+            enc_param = next(model.vision_encoder.parameters(), None)
+            if enc_param is not None and pixels.dtype != enc_param.dtype:
+                pixels = pixels.to(enc_param.dtype)
+            return model.compute_loss(pixels, ids, labels, frame_mask=batch.get("frame_mask"),
+                                      z_loss_weight=tc.z_loss_weight)
         if hasattr(model, "compute_loss"):
             loss = model.compute_loss(ids, labels, doc_ids=doc_ids, z_loss_weight=tc.z_loss_weight,
                                       chunk_tokens=tc.ce_chunk_size or 4096)
@@ -306,6 +370,7 @@ class Trainer:
         last = {"loss": float("nan"), "grad_norm": 0.0, "lr": 0.0}
         stop_reason = None
         while self.step < tc.max_steps:
+            self._maybe_advance_freeze_stage()
             self.tracker.start_step()
             out = self.train_step()
             self.step += 1

@@ -268,3 +268,64 @@ def test_fused_dense_block_matches_op_by_op_path(native_lib, ac):
     for n, p in model.named_parameters():
         ref = results[False][1][n]
         assert (p.grad.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6) < 0.05, n
+
+
+# --------------------------------------------------------------------------- attention (tcgen05)
+def _attn_inputs(b, s, h, hkv, hd, fused=True, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if fused:  # strided views of one projection output, as the model produces them
+        qkv = torch.randn(b, s, h + 2 * hkv, hd, device="cuda", dtype=torch.bfloat16, generator=g)
+        return qkv[:, :, :h], qkv[:, :, h:h + hkv], qkv[:, :, h + hkv:]
+    mk = lambda n: torch.randn(b, s, n, hd, device="cuda", dtype=torch.bfloat16, generator=g)  # noqa: E731
+    return mk(h), mk(hkv), mk(hkv)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(2, 256, 4, 2, 64), (1, 384, 4, 1, 128), (2, 200, 2, 2, 128), (1, 1000, 8, 2, 64),
+                                   (1, 2048, 2, 1, 128)])
+def test_attention_forward_matches_fp32_reference(native_lib, shape, causal):
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hkv, hd = shape
+    q, k, v = _attn_inputs(b, s, h, hkv, hd)
+    assert native_lib.attn_supported(q, k, v, causal)
+    scale = 1.0 / math.sqrt(hd)
+    out, lse = native_lib.attn_fwd(q, k, v, causal, None, scale)
+    want = ref.attention(q.float(), k.float(), v.float(), causal=causal, scale=scale)
+    assert native_lib.read_status() == 0
+    err = (out.float() - want).abs().max().item()
+    assert err < 2e-2, err
+    # log-sum-exp of the scaled scores, natural log
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float().repeat_interleave(h // hkv, dim=2)) * scale
+    if causal:
+        scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    assert (lse - torch.logsumexp(scores, dim=-1)).abs().max().item() < 2e-2
+
+
+def test_attention_forward_document_mask(native_lib):
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hkv, hd = 2, 512, 4, 2, 128
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, fused=False, seed=3)
+    cuts = torch.tensor([[0, 100, 130, 400], [0, 256, 300, 301]], device="cuda")
+    pos = torch.arange(s, device="cuda")
+    doc = (pos[None, :, None] >= cuts[:, None, :]).sum(-1).to(torch.int32)
+    out, _ = native_lib.attn_fwd(q, k, v, True, doc, 1.0 / math.sqrt(hd))
+    want = ref.attention(q.float(), k.float(), v.float(), causal=True, doc_ids=doc)
+    assert native_lib.read_status() == 0
+    assert (out.float() - want).abs().max().item() < 2e-2
+
+
+def test_attention_forward_large_scores_rescale(native_lib):
+    """Row maxima that keep growing along the sequence exercise the lazy O rescaling."""
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hkv, hd = 1, 1024, 2, 2, 64
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, fused=False, seed=5)
+    ramp = torch.linspace(0.2, 6.0, s, device="cuda")[None, :, None, None]
+    k = (k.float() * ramp).to(torch.bfloat16)
+    q = (q.float() * 2.0).to(torch.bfloat16)
+    out, _ = native_lib.attn_fwd(q, k, v, True, None, 1.0 / math.sqrt(hd))
+    want = ref.attention(q.float(), k.float(), v.float(), causal=True)
+    assert native_lib.read_status() == 0
+    assert (out.float() - want).abs().max().item() < 3e-2
