@@ -1,0 +1,494 @@
+// Flash attention backward on the 5th-generation tensor cores (head dim 128).
+//
+// One CTA owns a tile of 128 keys of one (batch, KV head) and walks over every query head of the group and
+// every 64-row query tile that can see those keys.  All five GEMMs of the backward pass run on tcgen05 with
+// the *transposed* score tile, so that each softmax thread owns one key row and the products that feed the
+// dK / dV accumulators can be taken straight from tensor memory / shared memory without a transpose:
+//
+//   S^T  = K  Q_i^T                      (128 keys x 64 queries, smem x smem -> TMEM)
+//   dP^T = V  dO_i^T                     (128 x 64)
+//   P^T  = exp2(S^T * c - lse_i),  dS^T = P^T * (dP^T - D_i) * scale        (softmax warps)
+//   dV  += P^T  dO_i                     (A from TMEM, 128 x 128 accumulator, lives in TMEM for the whole CTA)
+//   dK  += dS^T Q_i                      (A from smem, 128 x 128 accumulator)
+//   dQ_i^T = K^T dS                      (128 head-dim rows x 64 queries; added to an fp32 dQ with red.global)
+//
+//   warp 0   : TMA producer (K, V once; Q_i / dO_i ring of two stages)
+//   warp 1   : MMA issuer
+//   warps 2-5: softmax (one thread per key row) and the final dK / dV store
+//   warps 6-9: dQ reduction (TMEM -> red.global.add.f32, 128-byte coalesced per query)
+//
+// D_i = rowsum(dO_i * O_i) comes from a small pre-pass; a post-pass converts the fp32 dQ to bf16.
+// Replaces the backward of F.scaled_dot_product_attention (kempnerforge/model/attention.py:227-231) for the
+// causal / document-masked training path, without expanding grouped KV heads.
+#include "common.cuh"
+
+namespace kf {
+namespace attnb {
+
+constexpr int HD = 128;
+constexpr int BLK_K = 128;  // keys per CTA
+constexpr int BLK_Q = 64;   // queries per iteration
+constexpr int THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr int ST_COL = 0;     // S^T (fp32, 64 cols); P^T (bf16 pairs, 32 cols) aliases its start
+constexpr int DPT_COL = 64;   // dP^T (fp32, 64 cols)
+constexpr int DQT_COL = 128;  // dQ^T (fp32, 64 cols)
+constexpr int DV_COL = 256;   // dV accumulator (fp32, 128 cols)
+constexpr int DK_COL = 384;   // dK accumulator (fp32, 128 cols)
+constexpr int KV_TILE_BYTES = BLK_K * HD * 2;   // 32 KB: two blocks of [128 rows x 128 B]
+constexpr int KV_BLOCK_BYTES = BLK_K * 128;     // 16 KB
+constexpr int Q_TILE_BYTES = BLK_Q * HD * 2;    // 16 KB: two blocks of [64 rows x 128 B]
+constexpr int Q_BLOCK_BYTES = BLK_Q * 128;      // 8 KB
+constexpr int DS_BYTES = BLK_K * BLK_Q * 2;     // 16 KB: [128 key rows x 128 B]
+constexpr int STAGES = 2;
+constexpr size_t SMEM = 2 * size_t(KV_TILE_BYTES) + STAGES * 2 * size_t(Q_TILE_BYTES) + DS_BYTES + 1024 /*align*/ +
+                        2048 /*barriers, row statistics, doc ids*/;
+
+__device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void group_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+template <bool CAUSAL, bool HAS_DOC>
+__global__ void __launch_bounds__(THREADS, 1)
+kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                    const float* __restrict__ LSE, const float* __restrict__ Dsum, const int* __restrict__ doc_ids,
+                    float* __restrict__ dQacc, __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV, int Sq,
+                    int Sk, int H, int group, long long lddk, long long lddv, float scale, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t k_smem = smem_base;
+  const uint32_t v_smem = k_smem + KV_TILE_BYTES;
+  const uint32_t q_smem = v_smem + KV_TILE_BYTES;                 // STAGES tiles
+  const uint32_t do_smem = q_smem + STAGES * Q_TILE_BYTES;        // STAGES tiles
+  const uint32_t ds_smem = do_smem + STAGES * Q_TILE_BYTES;
+  const uint32_t bar_base = ds_smem + DS_BYTES;
+  uint8_t* ds_gen = smem_gen + 2 * KV_TILE_BYTES + STAGES * 2 * Q_TILE_BYTES;
+  uint8_t* bar_gen = ds_gen + DS_BYTES;
+  // barriers (8 B each)
+  const uint32_t kv_full = bar_base;
+  auto qdo_full = [&](int st) { return bar_base + 8u * (1 + st); };
+  auto stage_free = [&](int st) { return bar_base + 8u * (3 + st); };
+  const uint32_t sdp_full = bar_base + 8u * 5, ds_ready = bar_base + 8u * 6, mma_done = bar_base + 8u * 7,
+                 dq_free = bar_base + 8u * 8, drain_bar = bar_base + 8u * 9, tmem_slot = bar_base + 8u * 10;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_gen + 80);
+  float* stat_smem = reinterpret_cast<float*>(bar_gen + 128);       // [2 stages][lse2 | D][64]
+  int* docq_smem = reinterpret_cast<int*>(bar_gen + 128 + 1024);    // [2 stages][64]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_kv_tiles = gridDim.x;
+  const int kt = CAUSAL ? blockIdx.x : (n_kv_tiles - 1 - blockIdx.x);  // causal: early key tiles see most queries
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int k0 = kt * BLK_K;
+  const int n_q_tiles = (Sq + BLK_Q - 1) / BLK_Q;
+  const int i_start = CAUSAL ? min(n_q_tiles, k0 / BLK_Q) : 0;
+  const int n_i = n_q_tiles - i_start;
+  const int n_iter = n_i * group;
+  const float scale_log2 = scale * 1.4426950408889634f;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int st = 0; st < STAGES; ++st) {
+      mbar_init(qdo_full(st), 1);
+      mbar_init(stage_free(st), 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 4);
+    mbar_init(mma_done, 1);
+    mbar_init(dq_free, 4);
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      mbar_expect_tx(kv_full, 2 * KV_TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tma_load_2d(k_smem + c * KV_BLOCK_BYTES, &map_k, kv_full, hk * HD + 64 * c, b * Sk + k0);
+        tma_load_2d(v_smem + c * KV_BLOCK_BYTES, &map_v, kv_full, hk * HD + 64 * c, b * Sk + k0);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
+        const int use = it >> 1;
+        if (use > 0 && !mbar_wait(stage_free(st), (use - 1) & 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
+        const int hq = hk * group + it / n_i;
+        const int q0 = (i_start + it % n_i) * BLK_Q;
+        mbar_expect_tx(qdo_full(st), 2 * Q_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tma_load_2d(q_smem + st * Q_TILE_BYTES + c * Q_BLOCK_BYTES, &map_q, qdo_full(st), hq * HD + 64 * c,
+                      b * Sq + q0);
+          tma_load_2d(do_smem + st * Q_TILE_BYTES + c * Q_BLOCK_BYTES, &map_do, qdo_full(st), hq * HD + 64 * c,
+                      b * Sq + q0);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait(kv_full, 0, status, KF_ERR_WAIT_DRAIN);
+        for (int it = max(0, issued - STAGES); it < issued; ++it)
+          mbar_wait(qdo_full(it & 1), (it >> 1) & 1, status, KF_ERR_WAIT_DRAIN);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = umma_idesc_bf16(128, BLK_Q, false, false);  // S^T, dP^T
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, false, true);     // dV, dK (B = rows of Q_i / dO_i)
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, BLK_Q, true, true);    // dQ^T = K^T dS
+      bool ok = mbar_wait(kv_full, 0, status, KF_ERR_WAIT_FULL);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t qs = q_smem + st * Q_TILE_BYTES, dos = do_smem + st * Q_TILE_BYTES;
+        if (!mbar_wait(qdo_full(st), (it >> 1) & 1, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        // S^T = K Q_i^T and dP^T = V dO_i^T: all operands with the head dim contiguous.  Their TMEM regions
+        // were released by the softmax warps before ds_ready of the previous iteration.
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * KV_BLOCK_BYTES + (kk % 4) * 32;
+          const uint32_t b_off = (kk / 4) * Q_BLOCK_BYTES + (kk % 4) * 32;
+          tc_mma_f16(tmem_base + ST_COL, umma_desc_sw128(k_smem + a_off, 16, 1024),
+                     umma_desc_sw128(qs + b_off, 16, 1024), idesc_st, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * KV_BLOCK_BYTES + (kk % 4) * 32;
+          const uint32_t b_off = (kk / 4) * Q_BLOCK_BYTES + (kk % 4) * 32;
+          tc_mma_f16(tmem_base + DPT_COL, umma_desc_sw128(v_smem + a_off, 16, 1024),
+                     umma_desc_sw128(dos + b_off, 16, 1024), idesc_st, kk != 0);
+        }
+        tc_commit(sdp_full);
+        if (!mbar_wait(ds_ready, it & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        // dV += P^T dO_i : A = P^T from TMEM (8 columns per 16 queries), B = dO_i rows (head dim contiguous)
+#pragma unroll
+        for (int kk = 0; kk < BLK_Q / 16; ++kk)
+          tc_mma_f16_ts(tmem_base + DV_COL, tmem_base + ST_COL + kk * 8,
+                        umma_desc_sw128(dos + kk * 2048, Q_BLOCK_BYTES, 1024), idesc_acc, (it | kk) != 0);
+        // dK += dS^T Q_i : A = dS^T from smem (query dim contiguous), B = Q_i rows
+#pragma unroll
+        for (int kk = 0; kk < BLK_Q / 16; ++kk)
+          tc_mma_f16(tmem_base + DK_COL, umma_desc_sw128(ds_smem + kk * 32, 16, 1024),
+                     umma_desc_sw128(qs + kk * 2048, Q_BLOCK_BYTES, 1024), idesc_acc, (it | kk) != 0);
+        // dQ_i^T = K^T dS : A = K rows read with the head dim as M, B = dS^T rows read with the query dim as N
+#pragma unroll
+        for (int kk = 0; kk < BLK_K / 16; ++kk)
+          tc_mma_f16(tmem_base + DQT_COL, umma_desc_sw128(k_smem + kk * 2048, KV_BLOCK_BYTES, 1024),
+                     umma_desc_sw128(ds_smem + kk * 2048, DS_BYTES, 1024), idesc_dq, kk != 0);
+        tc_commit(stage_free(st));
+        tc_commit(mma_done);
+      }
+      if (!ok) {
+        tc_commit(drain_bar);
+        mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ softmax warps: one thread per key row
+    const int quarter = warp & 3;
+    const int r_local = quarter * 32 + lane;  // key row of this thread
+    const int kpos = k0 + r_local;
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const int t128 = threadIdx.x - 64;        // 0..127 inside the softmax group
+    int doc_k = 0;
+    if (HAS_DOC) doc_k = kpos < Sk ? doc_ids[size_t(b) * Sk + kpos] : -2;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int hq = hk * group + it / n_i;
+      const int q0 = (i_start + it % n_i) * BLK_Q;
+      // row statistics of the 64 queries: lse (in log2 units) and D, shared through smem
+      float* stat = stat_smem + (it & 1) * 128;
+      int* dq_doc = docq_smem + (it & 1) * 64;
+      {
+        const int qq = q0 + (t128 & 63);
+        const size_t idx = (size_t(b) * H + hq) * Sq + qq;
+        if (t128 < 64) {
+          stat[t128] = qq < Sq ? LSE[idx] * 1.4426950408889634f : INFINITY;  // +inf -> P = 0 for padding rows
+          if (HAS_DOC) dq_doc[t128] = qq < Sq ? doc_ids[size_t(b) * Sq + qq] : -1;
+        } else {
+          stat[t128] = qq < Sq ? Dsum[idx] : 0.f;
+        }
+      }
+      group_sync(1, 128);
+      if (ok && !mbar_wait(sdp_full, it & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+      tc_fence_after();
+      uint32_t sv[BLK_Q], dp[BLK_Q];
+      tmem_ld_32x32_at(t_lane + ST_COL, sv);
+      tmem_ld_32x32_at(t_lane + ST_COL + 32, sv + 32);
+      tmem_ld_32x32_at(t_lane + DPT_COL, dp);
+      tmem_ld_32x32_at(t_lane + DPT_COL + 32, dp + 32);
+      tmem_ld_wait();
+      const bool tile_masked = HAS_DOC || (CAUSAL && q0 < k0 + BLK_K - 1) || (k0 + BLK_K > Sk) || (q0 + BLK_Q > Sq);
+      uint32_t pk[BLK_Q / 2], dsk[BLK_Q / 2];
+#pragma unroll
+      for (int i = 0; i < BLK_Q / 2; ++i) {
+        float p[2], ds[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = 2 * i + e;
+          float pe = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -stat[c]));
+          if (tile_masked) {
+            const int qpos = q0 + c;
+            bool vis = kpos < Sk && qpos < Sq;
+            if (CAUSAL) vis = vis && kpos <= qpos;
+            if (HAS_DOC) vis = vis && dq_doc[c] == doc_k;
+            pe = vis ? pe : 0.f;
+          }
+          p[e] = pe;
+          ds[e] = pe * (__uint_as_float(dp[c]) - stat[64 + c]) * scale;
+        }
+        pk[i] = pack_bf16(p[0], p[1]);
+        dsk[i] = pack_bf16(ds[0], ds[1]);
+      }
+      // P^T over the start of S^T (every score of this row is in registers)
+      {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
+        tmem_st_32x16(t_lane + ST_COL, lo);
+        tmem_st_32x16(t_lane + ST_COL + 16, hi);
+      }
+      // dS^T into shared memory, 128B-swizzled rows (16-byte chunk c of row r lives at chunk c ^ (r % 8));
+      // the previous iteration's dK / dQ MMAs must have finished reading it
+      if (it > 0 && ok && !mbar_wait(mma_done, (it - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+      {
+        uint8_t* row_ptr = ds_gen + r_local * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 w = make_uint4(dsk[4 * c], dsk[4 * c + 1], dsk[4 * c + 2], dsk[4 * c + 3]);
+          *reinterpret_cast<uint4*>(row_ptr + ((c ^ (r_local & 7)) << 4)) = w;
+        }
+      }
+      fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    // ---- epilogue: dK / dV accumulators -> bf16 rows of the key tile
+    if (ok && n_iter > 0 && !mbar_wait(mma_done, (n_iter - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+    if (ok) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = which == 0 ? dV + (size_t(b) * Sk + kpos) * lddv + size_t(hk) * HD
+                                        : dK + (size_t(b) * Sk + kpos) * lddk + size_t(hk) * HD;
+        const uint32_t col0 = which == 0 ? DV_COL : DK_COL;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          if (n_iter > 0) {
+            tmem_ld_32x32_at(t_lane + col0 + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (kpos < Sk) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
+              w.y = pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
+              w.z = pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
+              w.w = pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = w;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ dQ reduction warps (6..9)
+    const int quarter = warp & 3;
+    const int d = quarter * 32 + lane;  // head-dim index = TMEM lane of dQ^T
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int hq = hk * group + it / n_i;
+      const int q0 = (i_start + it % n_i) * BLK_Q;
+      if (ok && !mbar_wait(mma_done, it & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+      tc_fence_after();
+      uint32_t v[BLK_Q];
+      tmem_ld_32x32_at(t_lane + DQT_COL, v);
+      tmem_ld_32x32_at(t_lane + DQT_COL + 32, v + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);  // the values are in registers: the next dQ^T may be computed
+      if (ok) {
+        float* base = dQacc + ((size_t(b) * Sq + q0) * H + hq) * HD + d;
+#pragma unroll
+        for (int c = 0; c < BLK_Q; ++c)
+          if (q0 + c < Sq) red_add_f32(base + size_t(c) * H * HD, __uint_as_float(v[c]));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// D[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]  (one warp per (b, s, h) row)
+__global__ void kf_attn_bwd_dot(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                float* __restrict__ D, int B, int S, int H, int hd, long long ldo, long long lddo) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;  // over b, s, h
+  const int lane = threadIdx.x & 31;
+  if (row >= (long long)B * S * H) return;
+  const int h = row % H;
+  const long long bs = row / H;
+  const __nv_bfloat16* o = O + bs * ldo + (long long)h * hd;
+  const __nv_bfloat16* g = dO + bs * lddo + (long long)h * hd;
+  float acc = 0.f;
+  for (int c = lane * 4; c < hd; c += 128) {
+    const uint2 a = *reinterpret_cast<const uint2*>(o + c);
+    const uint2 bb = *reinterpret_cast<const uint2*>(g + c);
+    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(bb.x), b1 = unpack_bf16(bb.y);
+    acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  }
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (lane == 0) {
+    const long long b = bs / S, s = bs % S;
+    D[(b * H + h) * S + s] = acc;
+  }
+}
+
+// fp32 (rows x cols contiguous) -> bf16 rows with pitch ld
+__global__ void kf_f32_to_bf16_rows(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows,
+                                    int cols, long long ld) {
+  const long long n4 = rows * (cols / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (cols / 4);
+    const int c = (i % (cols / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(src + r * cols + c);
+    uint2 w;
+    w.x = pack_bf16(v.x, v.y);
+    w.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst + r * ld + c) = w;
+  }
+}
+
+}  // namespace attnb
+}  // namespace kf
+
+extern "C" void* kf_status_device_ptr();
+
+extern "C" {
+
+// Backward attention (head dim 128).  q / k / v / o / do: rows (b * S + s) with pitches ld*, heads side by
+// side; lse: fp32 [B][H][Sq] from the forward; dsum: fp32 scratch [B][H][Sq]; dq_acc: fp32 scratch
+// [B][Sq][H][128] (zeroed here); dq / dk / dv: bf16 outputs with pitches lddq / lddk / lddv (they may be
+// slices of one fused gradient buffer).  doc: optional int32 [B][S].  Requires Sq == Sk when causal or doc.
+int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
+                     void* dsum, void* dq_acc, void* dq, void* dk, void* dv, const void* doc, int B, int Sq, int Sk,
+                     int H, int Hkv, int hd, long long ldq, long long ldk, long long ldv, long long ldo,
+                     long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
+                     void* stream) {
+  using namespace kf;
+  using namespace kf::attnb;
+  if (hd != HD || Hkv <= 0 || H % Hkv != 0) return 3;
+  if ((causal || doc) && Sq != Sk) return 4;
+  if ((ldq | ldk | ldv | ldo | lddo | lddq | lddk | lddv) & 7) return 5;
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap mq, mk, mv, mdo;
+  int rc = make_map_2d_bf16(&mq, q, uint64_t(B) * Sq, uint64_t(H) * hd, ldq, 64, BLK_Q);
+  if (rc) return 100 + rc;
+  rc = make_map_2d_bf16(&mk, k, uint64_t(B) * Sk, uint64_t(Hkv) * hd, ldk, 64, BLK_K);
+  if (rc) return 200 + rc;
+  rc = make_map_2d_bf16(&mv, v, uint64_t(B) * Sk, uint64_t(Hkv) * hd, ldv, 64, BLK_K);
+  if (rc) return 250 + rc;
+  rc = make_map_2d_bf16(&mdo, d_o, uint64_t(B) * Sq, uint64_t(H) * hd, lddo, 64, BLK_Q);
+  if (rc) return 270 + rc;
+  // pre-pass: D = rowsum(dO * O); zero the fp32 dQ accumulator
+  {
+    const long long rows = (long long)B * Sq * H;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    kf_attn_bwd_dot<<<(unsigned)blocks, threads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(o),
+                                                          reinterpret_cast<const __nv_bfloat16*>(d_o),
+                                                          reinterpret_cast<float*>(dsum), B, Sq, H, hd, ldo, lddo);
+    cudaError_t e = cudaMemsetAsync(dq_acc, 0, size_t(B) * Sq * H * hd * sizeof(float), st);
+    if (e != cudaSuccess) return 400 + (int)e;
+  }
+  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
+  dim3 grid((Sk + BLK_K - 1) / BLK_K, Hkv, B);
+#define KF_BWD_LAUNCH(C_, D_)                                                                                      \
+  {                                                                                                                \
+    auto kern = kf_attn_bwd_tcgen05<C_, D_>;                                                                       \
+    static bool attr_set = false;                                                                                  \
+    if (!attr_set) {                                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);          \
+      if (e != cudaSuccess) return 300 + (int)e;                                                                   \
+      attr_set = true;                                                                                             \
+    }                                                                                                              \
+    kern<<<grid, THREADS, SMEM, st>>>(mq, mk, mv, mdo, reinterpret_cast<const float*>(lse),                        \
+                                      reinterpret_cast<const float*>(dsum), reinterpret_cast<const int*>(doc),     \
+                                      reinterpret_cast<float*>(dq_acc), reinterpret_cast<__nv_bfloat16*>(dk),      \
+                                      reinterpret_cast<__nv_bfloat16*>(dv), Sq, Sk, H, H / Hkv, lddk, lddv, scale, \
+                                      status);                                                                     \
+  }
+  if (doc) {
+    if (causal) KF_BWD_LAUNCH(true, true) else KF_BWD_LAUNCH(false, true)
+  } else {
+    if (causal) KF_BWD_LAUNCH(true, false) else KF_BWD_LAUNCH(false, false)
+  }
+#undef KF_BWD_LAUNCH
+  {
+    const long long rows = (long long)B * Sq;
+    const int cols = H * hd;
+    kf_f32_to_bf16_rows<<<1184, 256, 0, st>>>(reinterpret_cast<const float*>(dq_acc),
+                                              reinterpret_cast<__nv_bfloat16*>(dq), rows, cols, lddq);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // extern "C"

@@ -87,7 +87,8 @@ class TransformerBlock(nn.Module):
         return x + self.mlp(self.mlp_norm(x))
 
     def forward(self, x, rope_cos, rope_sin, *, kv_cache: KVCache | None = None, doc_ids=None, key_padding_mask=None):
-        if x.is_cuda and self.ac_mode in ("none", "full") and not _FUSED_BLOCK_OFF:
+        if (x.is_cuda and self.ac_mode in ("none", "full") and not _FUSED_BLOCK_OFF
+                and not getattr(self, "_kf_fp8_block", False)):
             from kempnerforge_b200.ops import fused_block
 
             if F.use_native(x) and fused_block.dense_block_supported(self, x, kv_cache, doc_ids, key_padding_mask):

@@ -58,6 +58,10 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
         "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
         "kf_test_flag_timeout": [vp, i, ll],
+        "kf_gemm_fp8": [vp, vp, vp, i, i, i, ll, ll, i, i, i, vp, vp, i, i, vp],
+        "kf_fp8_scale_bf16": [vp, ll, i, vp, vp, vp],
+        "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
+        "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
         "kf_symm_adamw_bcast_bf16": [vp, vp, i, i, vp, vp, vp, ll, ll, ll, f, f, f, f, f, f, f, vp, vp, i, vp],
@@ -313,7 +317,52 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch
     return out
 
 
+# --------------------------------------------------------------------------- fp8
+def fp8_scale(x2: torch.Tensor, e5m2: bool = False) -> torch.Tensor:
+    """Device scalar fp8_max / absmax(x) (fp32, shape (1,))."""
+    scratch = torch.empty(2, dtype=torch.float32, device=x2.device)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    _check(lib().kf_fp8_scale_bf16(x2.data_ptr(), x2.numel(), int(e5m2), scratch[1:].data_ptr(), scratch.data_ptr(),
+                                   _stream()), "kf_fp8_scale_bf16")
+    return scratch[:1]
+
+
+def fp8_cast(x2: torch.Tensor, scale: torch.Tensor, e5m2: bool, want_row: bool = True, want_t: bool = False):
+    """fp8 bytes of x * scale: (rows, cols) and / or the transposed (cols, rows) copy, as uint8 tensors."""
+    rows, cols = x2.shape
+    assert x2.stride(1) == 1
+    row = torch.empty((rows, cols), dtype=torch.uint8, device=x2.device) if want_row else None
+    t = torch.empty((cols, rows), dtype=torch.uint8, device=x2.device) if want_t else None
+    _check(lib().kf_fp8_cast_bf16(x2.data_ptr(), rows, cols, x2.stride(0), scale.data_ptr(), int(e5m2),
+                                  row.data_ptr() if want_row else None, cols, t.data_ptr() if want_t else None, rows,
+                                  _stream()), "kf_fp8_cast_bf16")
+    return row, t
+
+
+def gemm_fp8(a8: torch.Tensor, b8: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor, a_e5m2: bool = False,
+             b_e5m2: bool = False, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """bf16 (M, N) = a8 (M, K) @ b8 (N, K)ᵀ / (sa * sb) on the fp8 tensor cores."""
+    m, k = a8.shape
+    n = b8.shape[0]
+    assert b8.shape[1] == k and a8.stride(1) == 1 and b8.stride(1) == 1
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a8.device)
+        accumulate = False
+    assert out.stride(1) == 1
+    _check(lib().kf_gemm_fp8(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), m, n, k, a8.stride(0), b8.stride(0),
+                             out.stride(0), int(a_e5m2), int(b_e5m2), sa.data_ptr(), sb.data_ptr(), int(accumulate),
+                             sm_count(), _stream()), "kf_gemm_fp8")
+    return out
+
+
 # --------------------------------------------------------------------------- attention
+def attn_policy() -> str:
+    """``KF_ATTN``: "native" = tcgen05 kernels wherever they apply; "library" = never; "auto" (default) =
+    native for gradient-free attention (evaluation, generation), the library kernel inside training."""
+    return os.environ.get("KF_ATTN", "auto")
+
+
 def _attn_rows_ok(t: torch.Tensor) -> bool:
     """(B, S, heads, hd) whose (b, s) pairs form evenly pitched rows with the heads side by side."""
     b, s, _, hd = t.shape
@@ -325,9 +374,9 @@ def attn_supported(q, k, v, causal: bool, needs_grad: bool = False) -> bool:
     """Shapes the tcgen05 attention kernels cover: bf16, head dim 64 or 128, grouped KV heads, causal or full,
     optional document ids; q / k / v may be strided views of one fused projection output."""
     L = lib()
-    if getattr(L, "kf_attn_fwd_bf16", None) is None or os.environ.get("KF_DISABLE_NATIVE_ATTN"):
+    if getattr(L, "kf_attn_fwd_bf16", None) is None or attn_policy() == "library":
         return False
-    if needs_grad and getattr(L, "kf_attn_bwd_bf16", None) is None:
+    if needs_grad and (getattr(L, "kf_attn_bwd_bf16", None) is None or q.shape[-1] != 128):
         return False
     if q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128) or q.shape[2] % k.shape[2] != 0:
         return False
@@ -352,6 +401,32 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
         "kf_attn_fwd_bf16",
     )
     return out, lse
+
+
+def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=None, dk=None, dv=None):
+    """Gradients of ``attn_fwd``.  ``dq`` / ``dk`` / ``dv`` may be preallocated (strided) destinations, e.g. the
+    three head ranges of one fused projection gradient; otherwise contiguous tensors are returned."""
+    b, sq, h, hd = q.shape
+    sk, hkv = k.shape[1], k.shape[2]
+    if dout.stride(-1) != 1 or dout.stride(2) != hd or (b > 1 and dout.stride(0) != sq * dout.stride(1)):
+        dout = dout.contiguous()
+    dq = torch.empty((b, sq, h, hd), dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty((b, sk, hkv, hd), dtype=q.dtype, device=q.device) if dk is None else dk
+    dv = torch.empty((b, sk, hkv, hd), dtype=q.dtype, device=q.device) if dv is None else dv
+    for t in (dq, dk, dv, out, dout):
+        assert _attn_rows_ok(t), "attention gradients need evenly pitched rows with adjacent heads"
+    dsum = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty((b, sq, h, hd), dtype=torch.float32, device=q.device)
+    doc = doc_ids.to(torch.int32).contiguous() if doc_ids is not None else None
+    _check(
+        lib().kf_attn_bwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                               dsum.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                               doc.data_ptr() if doc is not None else None, b, sq, sk, h, hkv, hd, q.stride(1),
+                               k.stride(1), v.stride(1), out.stride(1), dout.stride(1), dq.stride(1), dk.stride(1),
+                               dv.stride(1), float(scale), int(causal), _stream()),
+        "kf_attn_bwd_bf16",
+    )
+    return dq, dk, dv
 
 
 # --------------------------------------------------------------------------- fused communication kernels

@@ -135,7 +135,62 @@ def _linear_weight_grads(cu, dy2, x2, weights, needs):
     return out
 
 
+def _stack_weight_rows(weights) -> torch.Tensor:
+    """The weights as one (sum(out_i), in) matrix: a zero-copy view when they are adjacent rows of a flat
+    buffer on the GPU, a concatenation otherwise."""
+    if len(weights) == 1:
+        return weights[0]
+    if weights[0].is_cuda:
+        return _cuda().stack_rows(weights)
+    return torch.cat(list(weights), dim=0)
+
+
+def _deposit_stacked_weight_grads(weights, needs, compute):
+    """Run ``compute(out, accumulate)`` for the stacked weight gradient and hand the row blocks to the flat
+    gradient buffers (or to autograd when a weight has none)."""
+    slots = [getattr(w, "_kf_grad", None) for w in weights]
+    if all(needs) and all(s is not None for s in slots) and weights[0].is_cuda and _cuda().rows_adjacent(slots):
+        live = [getattr(w, "_kf_grad_live", False) for w in weights]
+        if all(live) or not any(live):
+            compute(_cuda().stack_rows(slots), live[0])
+            for w in weights:
+                w._kf_grad_live = True
+            return [None] * len(weights)
+    total = sum(w.shape[0] for w in weights)
+    dw = torch.empty(total, weights[0].shape[1], dtype=weights[0].dtype, device=weights[0].device)
+    compute(dw, False)
+    out, row = [], 0
+    for w, need, slot in zip(weights, needs, slots):
+        piece = dw[row : row + w.shape[0]]
+        row += w.shape[0]
+        if not need:
+            out.append(None)
+        elif slot is not None:
+            if getattr(w, "_kf_grad_live", False):
+                slot.add_(piece)
+            else:
+                slot.copy_(piece)
+                w._kf_grad_live = True
+            out.append(None)
+        else:
+            out.append(piece)
+    return out
+
+
+def _fp8_route(x: torch.Tensor, weights) -> bool:
+    if not getattr(weights[0], "_kf_fp8", False):
+        return False
+    from kempnerforge_b200.ops import fp8
+
+    return (x.is_cuda or x.dtype == torch.bfloat16) and fp8.supported(x, list(weights))
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    if _fp8_route(x, [weight]):
+        from kempnerforge_b200.ops import fp8
+
+        y = fp8.linear(x, [weight])
+        return y if bias is None else y + bias
     if use_native(x) and weight.dtype == torch.bfloat16 and _gemm_friendly(x, weight):
         y = _LinearFn.apply(x, weight)
         return y if bias is None else y + bias
@@ -144,6 +199,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 def fused_linear(x: torch.Tensor, weights: list[torch.Tensor]) -> torch.Tensor:
     """One GEMM against several (out_i, in) weights; output columns are [out_0 | out_1 | ...]."""
+    if _fp8_route(x, weights):
+        from kempnerforge_b200.ops import fp8
+
+        return fp8.linear(x, list(weights))
     if use_native(x) and all(w.dtype == torch.bfloat16 for w in weights) and all(
         _gemm_friendly(x, w) for w in weights
     ):
@@ -258,12 +317,15 @@ def attention(
     """q (B, Sq, H, hd), k/v (B, Sk, Hkv, hd) -> (B, Sq, H, hd); grouped KV heads are never expanded."""
     hd = q.shape[-1]
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
-    if (
-        use_native(q)
-        and key_padding_mask is None
-        and _cuda().attn_supported(q, k, v, causal)
-    ):
-        return _FlashAttnFn.apply(q, k, v, causal, doc_ids, scale)
+    if use_native(q) and key_padding_mask is None:
+        cu = _cuda()
+        needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+        policy = cu.attn_policy()
+        want = policy == "native" or (policy == "auto" and (not needs_grad or doc_ids is not None))
+        if want and (doc_ids is None or q.shape[1] == k.shape[1]) and cu.attn_supported(q, k, v, causal, needs_grad):
+            if not needs_grad:
+                return cu.attn_fwd(q, k, v, causal, doc_ids, scale)[0]
+            return _FlashAttnFn.apply(q, k, v, causal, doc_ids, scale)
     if q.is_cuda and doc_ids is None and key_padding_mask is None and q.dtype != torch.float32:
         # library attention for shapes the native kernel does not cover
         out = torch.nn.functional.scaled_dot_product_attention(

@@ -63,11 +63,17 @@ def _norm_wgrad(weight, dw):
     return None
 
 
-def _attention_fwd(q, k, v, causal, scale):
-    """(out, ctx) with ctx holding what the backward needs."""
-    if kc.attn_supported(q, k, v, causal):
+def _attention_fwd(q, k, v, causal, scale, need_ctx: bool = True):
+    """(out, ctx) with ctx holding what the backward needs (None when ``need_ctx`` is False: the
+    first forward of a recomputed block only wants the output)."""
+    if kc.attn_policy() == "native" and kc.attn_supported(q, k, v, causal, needs_grad=need_ctx):
         out, lse = kc.attn_fwd(q, k, v, causal, None, scale)
         return out, ("native", lse)
+    if not need_ctx:
+        o = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=k.shape[2] != q.shape[2]).transpose(1, 2)
+        return o, None
     with torch.enable_grad():
         ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
         o = torch.nn.functional.scaled_dot_product_attention(
@@ -114,7 +120,7 @@ class DenseBlockFn(torch.autograd.Function):
         kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)  # in place: each element is read and written by one thread
         q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
         scale = 1.0 / math.sqrt(hd)
-        attn, actx = _attention_fwd(q, k, v, True, scale)
+        attn, actx = _attention_fwd(q, k, v, True, scale, need_ctx=keep)
         attn2 = attn.reshape(b * s, h * hd)
         h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
         n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)

@@ -329,3 +329,117 @@ def test_attention_forward_large_scores_rescale(native_lib):
     want = ref.attention(q.float(), k.float(), v.float(), causal=True)
     assert native_lib.read_status() == 0
     assert (out.float() - want).abs().max().item() < 3e-2
+
+
+# --------------------------------------------------------------------------- fp8 (tcgen05 kind::f8f6f4)
+@pytest.mark.parametrize("e5m2", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256), (300, 520), (64, 4096)])
+def test_fp8_scale_and_cast_match_torch(native_lib, shape, e5m2):
+    rows, cols = shape
+    x = _rand(rows, cols, scale=3.0)
+    scale = native_lib.fp8_scale(x, e5m2)
+    fmax = 57344.0 if e5m2 else 448.0
+    assert abs(scale.item() - fmax / x.float().abs().max().item()) < 1e-3 * scale.item()
+    row, t = native_lib.fp8_cast(x, scale, e5m2, True, True)
+    dt = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+    want = (x.float() * scale).clamp(-fmax, fmax).to(dt)
+    assert torch.equal(row.view(dt).float(), want.float())
+    assert torch.equal(t.view(dt).float(), want.float().t())
+
+
+@pytest.mark.parametrize("fmt", [(False, False), (True, False)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (384, 272, 400), (1024, 1024, 2048), (8192, 512, 4096)])
+def test_fp8_gemm_matches_dequantised_reference(native_lib, shape, fmt):
+    m, n, k = shape
+    a, b = _rand(m, k), _rand(n, k, scale=0.05)
+    sa, sb = native_lib.fp8_scale(a, fmt[0]), native_lib.fp8_scale(b, fmt[1])
+    a8, _ = native_lib.fp8_cast(a, sa, fmt[0])
+    b8, _ = native_lib.fp8_cast(b, sb, fmt[1])
+    got = native_lib.gemm_fp8(a8, b8, sa, sb, fmt[0], fmt[1])
+    dta = torch.float8_e5m2 if fmt[0] else torch.float8_e4m3fn
+    dtb = torch.float8_e5m2 if fmt[1] else torch.float8_e4m3fn
+    want = (a8.view(dta).float() @ b8.view(dtb).float().t()) / (sa * sb)
+    assert native_lib.read_status() == 0
+    _close(got, want, rtol=1e-2, atol=1e-2)
+    acc = got.clone()
+    native_lib.gemm_fp8(a8, b8, sa, sb, fmt[0], fmt[1], out=acc, accumulate=True)
+    _close(acc, 2 * want, rtol=2e-2, atol=2e-2)
+
+
+def test_fp8_linear_forward_backward_close_to_bf16(native_lib):
+    from kempnerforge_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    x = _rand(4, 128, 512).requires_grad_(True)
+    w1 = (_rand(768, 512, scale=0.04)).requires_grad_(True)
+    w2 = (_rand(256, 512, scale=0.04)).requires_grad_(True)
+    g = _rand(4, 128, 1024)
+    ref_y = torch.cat([x @ w1.t(), x @ w2.t()], dim=-1)
+    ref_y.backward(g)
+    want = [ref_y.detach(), x.grad.clone(), w1.grad.clone(), w2.grad.clone()]
+    x.grad = w1.grad = w2.grad = None
+    w1._kf_fp8 = w2._kf_fp8 = True
+    y = F.fused_linear(x, [w1, w2])
+    y.backward(g)
+    assert native_lib.read_status() == 0
+    for got, ref_t in zip([y.detach(), x.grad, w1.grad, w2.grad], want):
+        rel = (got.float() - ref_t.float()).norm() / ref_t.float().norm()
+        assert rel < 0.08, rel.item()
+
+
+def _attn_reference_grads(q, k, v, dout, causal, doc=None):
+    from kempnerforge_b200.ops import ref
+
+    qf, kf_, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    out = ref.attention(qf, kf_, vf, causal=causal, doc_ids=doc)
+    out.backward(dout.float())
+    return out.detach(), qf.grad, kf_.grad, vf.grad
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 384, 4, 1), (2, 200, 2, 2), (1, 1024, 8, 2)])
+def test_attention_backward_matches_fp32_reference(native_lib, shape, causal):
+    b, s, h, hkv = shape
+    hd = 128
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=11)
+    dout = _rand(b, s, h, hd)
+    scale = 1.0 / math.sqrt(hd)
+    out, lse = native_lib.attn_fwd(q, k, v, causal, None, scale)
+    dq, dk, dv = native_lib.attn_bwd(dout, q, k, v, out, lse, causal, None, scale)
+    assert native_lib.read_status() == 0
+    _, rq, rk, rv = _attn_reference_grads(q, k, v, dout, causal)
+    for name, got, want in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        rel = (got.float() - want).norm() / want.norm()
+        assert rel < 2e-2, (name, rel.item())
+
+
+def test_attention_backward_document_mask_into_fused_gradient(native_lib):
+    b, s, h, hkv, hd = 2, 512, 4, 2, 128
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=13)
+    cuts = torch.tensor([[0, 100, 130, 400], [0, 256, 300, 301]], device="cuda")
+    doc = (torch.arange(s, device="cuda")[None, :, None] >= cuts[:, None, :]).sum(-1).to(torch.int32)
+    dout = _rand(b, s, h, hd)
+    scale = 1.0 / math.sqrt(hd)
+    out, lse = native_lib.attn_fwd(q, k, v, True, doc, scale)
+    dqkv = torch.zeros(b, s, h + 2 * hkv, hd, device="cuda", dtype=torch.bfloat16)
+    native_lib.attn_bwd(dout, q, k, v, out, lse, True, doc, scale, dq=dqkv[:, :, :h], dk=dqkv[:, :, h:h + hkv],
+                        dv=dqkv[:, :, h + hkv:])
+    assert native_lib.read_status() == 0
+    _, rq, rk, rv = _attn_reference_grads(q, k, v, dout, True, doc)
+    want = torch.cat([rq, rk, rv], dim=2)
+    rel = (dqkv.float() - want).norm() / want.norm()
+    assert rel < 2e-2, rel.item()
+
+
+def test_attention_autograd_function_native_policy(native_lib, monkeypatch):
+    from kempnerforge_b200.ops import functional as F
+
+    monkeypatch.setenv("KF_ATTN", "native")
+    b, s, h, hkv, hd = 1, 256, 4, 2, 128
+    q, k, v = (t.clone().requires_grad_(True) for t in _attn_inputs(b, s, h, hkv, hd, fused=False, seed=17))
+    dout = _rand(b, s, h, hd)
+    out = F.attention(q, k, v, causal=True)
+    out.backward(dout)
+    _, rq, rk, rv = _attn_reference_grads(q, k, v, dout, True)
+    for got, want in ((q.grad, rq), (k.grad, rk), (v.grad, rv)):
+        assert ((got.float() - want).norm() / want.norm()) < 2e-2
