@@ -12,7 +12,7 @@
 //   dK  += dS^T Q_i                      (A from smem, 128 x 128 accumulator)
 //   dQ_i^T = K^T dS                      (128 head-dim rows x 64 queries; added to an fp32 dQ with red.global)
 //
-//   warp 0   : TMA producer (K, V once; Q_i / dO_i ring of two stages)
+//   warp 0   : TMA producer (K, V once; Q_i / dO_i ring of three stages)
 //   warp 1   : MMA issuer
 //   warps 2-5: softmax (one thread per key row) and the final dK / dV store
 //   warps 6-9: dQ reduction (TMEM -> red.global.add.f32, 128-byte coalesced per query)
@@ -30,9 +30,9 @@ constexpr int BLK_K = 128;  // keys per CTA
 constexpr int BLK_Q = 64;   // queries per iteration
 constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr int ST_COL = 0;     // S^T (fp32, 64 cols); P^T (bf16 pairs, 32 cols) aliases its start
-constexpr int DPT_COL = 64;   // dP^T (fp32, 64 cols)
-constexpr int DQT_COL = 128;  // dQ^T (fp32, 64 cols)
+constexpr int ST_COL = 0;     // S^T buffers 0 / 1 (fp32, 64 cols each); P^T (bf16 pairs, 32 cols) aliases each start
+constexpr int DPT_COL = 128;  // dP^T (fp32, 64 cols)
+constexpr int DQT_COL = 192;  // dQ^T (fp32, 64 cols)
 constexpr int DV_COL = 256;   // dV accumulator (fp32, 128 cols)
 constexpr int DK_COL = 384;   // dK accumulator (fp32, 128 cols)
 constexpr int KV_TILE_BYTES = BLK_K * HD * 2;   // 32 KB: two blocks of [128 rows x 128 B]
@@ -40,8 +40,8 @@ constexpr int KV_BLOCK_BYTES = BLK_K * 128;     // 16 KB
 constexpr int Q_TILE_BYTES = BLK_Q * HD * 2;    // 16 KB: two blocks of [64 rows x 128 B]
 constexpr int Q_BLOCK_BYTES = BLK_Q * 128;      // 8 KB
 constexpr int DS_BYTES = BLK_K * BLK_Q * 2;     // 16 KB: [128 key rows x 128 B]
-constexpr int STAGES = 2;
-constexpr size_t SMEM = 2 * size_t(KV_TILE_BYTES) + STAGES * 2 * size_t(Q_TILE_BYTES) + DS_BYTES + 1024 /*align*/ +
+constexpr int STAGES = 3;  // Q_i / dO_i ring: a tile is loaded one whole iteration before its scores are issued
+constexpr size_t SMEM = 2 * size_t(KV_TILE_BYTES) + STAGES * 2 * size_t(Q_TILE_BYTES) + 2 * DS_BYTES + 1024 /*align*/ +
                         2048 /*barriers, row statistics, doc ids*/;
 
 __device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t* r) {
@@ -87,18 +87,20 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t q_smem = v_smem + KV_TILE_BYTES;                 // STAGES tiles
   const uint32_t do_smem = q_smem + STAGES * Q_TILE_BYTES;        // STAGES tiles
   const uint32_t ds_smem = do_smem + STAGES * Q_TILE_BYTES;
-  const uint32_t bar_base = ds_smem + DS_BYTES;
+  const uint32_t bar_base = ds_smem + 2 * DS_BYTES;  // dS^T is double buffered
   uint8_t* ds_gen = smem_gen + 2 * KV_TILE_BYTES + STAGES * 2 * Q_TILE_BYTES;
-  uint8_t* bar_gen = ds_gen + DS_BYTES;
+  uint8_t* bar_gen = ds_gen + 2 * DS_BYTES;
   // barriers (8 B each)
   const uint32_t kv_full = bar_base;
-  auto qdo_full = [&](int st) { return bar_base + 8u * (1 + st); };
-  auto stage_free = [&](int st) { return bar_base + 8u * (3 + st); };
-  const uint32_t sdp_full = bar_base + 8u * 5, ds_ready = bar_base + 8u * 6, mma_done = bar_base + 8u * 7,
-                 dq_free = bar_base + 8u * 8, drain_bar = bar_base + 8u * 9, tmem_slot = bar_base + 8u * 10;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_gen + 80);
-  float* stat_smem = reinterpret_cast<float*>(bar_gen + 128);       // [2 stages][lse2 | D][64]
-  int* docq_smem = reinterpret_cast<int*>(bar_gen + 128 + 1024);    // [2 stages][64]
+  auto qdo_full = [&](int st) { return bar_base + 8u * (1 + st); };     // 3
+  auto stage_free = [&](int st) { return bar_base + 8u * (4 + st); };   // 3
+  auto ds_free = [&](int buf) { return bar_base + 8u * (7 + buf); };    // 2
+  const uint32_t sdp_full = bar_base + 8u * 9, ds_ready = bar_base + 8u * 10, mma_done = bar_base + 8u * 11,
+                 dq_free = bar_base + 8u * 12, drain_bar = bar_base + 8u * 13, sdp_taken = bar_base + 8u * 14,
+                 final_bar = bar_base + 8u * 15, tmem_slot = bar_base + 8u * 16;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_gen + 128);
+  float* stat_smem = reinterpret_cast<float*>(bar_gen + 256);       // [2][lse2 | D][64]
+  int* docq_smem = reinterpret_cast<int*>(bar_gen + 256 + 1024);    // [2][64]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -122,6 +124,10 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(ds_ready, 4);
     mbar_init(mma_done, 1);
     mbar_init(dq_free, 4);
+    mbar_init(sdp_taken, 4);
+    mbar_init(final_bar, 1);
+    mbar_init(ds_free(0), 1);
+    mbar_init(ds_free(1), 1);
     mbar_init(drain_bar, 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -150,8 +156,8 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tma_load_2d(v_smem + c * KV_BLOCK_BYTES, &map_v, kv_full, hk * HD + 64 * c, b * Sk + k0);
       }
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1;
-        const int use = it >> 1;
+        const int st = it % STAGES;
+        const int use = it / STAGES;
         if (use > 0 && !mbar_wait(stage_free(st), (use - 1) & 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
         const int hq = hk * group + it / n_i;
         const int q0 = (i_start + it % n_i) * BLK_Q;
@@ -168,7 +174,7 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!ok) {
         mbar_wait(kv_full, 0, status, KF_ERR_WAIT_DRAIN);
         for (int it = max(0, issued - STAGES); it < issued; ++it)
-          mbar_wait(qdo_full(it & 1), (it >> 1) & 1, status, KF_ERR_WAIT_DRAIN);
+          mbar_wait(qdo_full(it % STAGES), (it / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
       }
     }
   } else if (warp == 1) {
@@ -178,18 +184,17 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, false, true);     // dV, dK (B = rows of Q_i / dO_i)
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, BLK_Q, true, true);    // dQ^T = K^T dS
       bool ok = mbar_wait(kv_full, 0, status, KF_ERR_WAIT_FULL);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
+      // S^T(t) = K Q^T into score buffer t & 1 and dP^T(t) = V dO^T: all operands with the head dim contiguous
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % STAGES, buf = t & 1;
         const uint32_t qs = q_smem + st * Q_TILE_BYTES, dos = do_smem + st * Q_TILE_BYTES;
-        if (!mbar_wait(qdo_full(st), (it >> 1) & 1, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
+        if (!mbar_wait(qdo_full(st), (t / STAGES) & 1, status, KF_ERR_WAIT_FULL)) return false;
         tc_fence_after();
-        // S^T = K Q_i^T and dP^T = V dO_i^T: all operands with the head dim contiguous.  Their TMEM regions
-        // were released by the softmax warps before ds_ready of the previous iteration.
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t a_off = (kk / 4) * KV_BLOCK_BYTES + (kk % 4) * 32;
           const uint32_t b_off = (kk / 4) * Q_BLOCK_BYTES + (kk % 4) * 32;
-          tc_mma_f16(tmem_base + ST_COL, umma_desc_sw128(k_smem + a_off, 16, 1024),
+          tc_mma_f16(tmem_base + ST_COL + buf * BLK_Q, umma_desc_sw128(k_smem + a_off, 16, 1024),
                      umma_desc_sw128(qs + b_off, 16, 1024), idesc_st, kk != 0);
         }
 #pragma unroll
@@ -200,27 +205,43 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                      umma_desc_sw128(dos + b_off, 16, 1024), idesc_st, kk != 0);
         }
         tc_commit(sdp_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % STAGES, buf = it & 1;
+        const uint32_t qs = q_smem + st * Q_TILE_BYTES, dos = do_smem + st * Q_TILE_BYTES;
+        const uint32_t dss = ds_smem + buf * DS_BYTES;
+        // The next tile's scores run while the softmax warps work on this one.  S^T(it+1) goes to the other
+        // score buffer (its old P^T was read by an MMA issued earlier by this thread); dP^T has one buffer,
+        // free once the softmax warps have copied dP^T(it) into registers.
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(sdp_taken, it & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
         if (!mbar_wait(ds_ready, it & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         // dV += P^T dO_i : A = P^T from TMEM (8 columns per 16 queries), B = dO_i rows (head dim contiguous)
 #pragma unroll
         for (int kk = 0; kk < BLK_Q / 16; ++kk)
-          tc_mma_f16_ts(tmem_base + DV_COL, tmem_base + ST_COL + kk * 8,
+          tc_mma_f16_ts(tmem_base + DV_COL, tmem_base + ST_COL + buf * BLK_Q + kk * 8,
                         umma_desc_sw128(dos + kk * 2048, Q_BLOCK_BYTES, 1024), idesc_acc, (it | kk) != 0);
         // dK += dS^T Q_i : A = dS^T from smem (query dim contiguous), B = Q_i rows
 #pragma unroll
         for (int kk = 0; kk < BLK_Q / 16; ++kk)
-          tc_mma_f16(tmem_base + DK_COL, umma_desc_sw128(ds_smem + kk * 32, 16, 1024),
+          tc_mma_f16(tmem_base + DK_COL, umma_desc_sw128(dss + kk * 32, 16, 1024),
                      umma_desc_sw128(qs + kk * 2048, Q_BLOCK_BYTES, 1024), idesc_acc, (it | kk) != 0);
         // dQ_i^T = K^T dS : A = K rows read with the head dim as M, B = dS^T rows read with the query dim as N
 #pragma unroll
         for (int kk = 0; kk < BLK_K / 16; ++kk)
           tc_mma_f16(tmem_base + DQT_COL, umma_desc_sw128(k_smem + kk * 2048, KV_BLOCK_BYTES, 1024),
-                     umma_desc_sw128(ds_smem + kk * 2048, DS_BYTES, 1024), idesc_dq, kk != 0);
+                     umma_desc_sw128(dss + kk * 2048, DS_BYTES, 1024), idesc_dq, kk != 0);
         tc_commit(stage_free(st));
+        tc_commit(ds_free(buf));
         tc_commit(mma_done);
       }
+      if (ok) tc_commit(final_bar);  // every MMA of this CTA has retired: dK / dV are final
       if (!ok) {
         tc_commit(drain_bar);
         mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
@@ -255,12 +276,16 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       group_sync(1, 128);
       if (ok && !mbar_wait(sdp_full, it & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
       tc_fence_after();
+      const uint32_t t_s = t_lane + ST_COL + (it & 1) * BLK_Q;
       uint32_t sv[BLK_Q], dp[BLK_Q];
-      tmem_ld_32x32_at(t_lane + ST_COL, sv);
-      tmem_ld_32x32_at(t_lane + ST_COL + 32, sv + 32);
+      tmem_ld_32x32_at(t_s, sv);
+      tmem_ld_32x32_at(t_s + 32, sv + 32);
       tmem_ld_32x32_at(t_lane + DPT_COL, dp);
       tmem_ld_32x32_at(t_lane + DPT_COL + 32, dp + 32);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sdp_taken);  // dP^T is in registers: the next tile's dP^T may be computed
       const bool tile_masked = HAS_DOC || (CAUSAL && q0 < k0 + BLK_K - 1) || (k0 + BLK_K > Sk) || (q0 + BLK_Q > Sq);
       uint32_t pk[BLK_Q / 2], dsk[BLK_Q / 2];
 #pragma unroll
@@ -288,14 +313,15 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         uint32_t lo[16], hi[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
-        tmem_st_32x16(t_lane + ST_COL, lo);
-        tmem_st_32x16(t_lane + ST_COL + 16, hi);
+        tmem_st_32x16(t_s, lo);
+        tmem_st_32x16(t_s + 16, hi);
       }
       // dS^T into shared memory, 128B-swizzled rows (16-byte chunk c of row r lives at chunk c ^ (r % 8));
       // the previous iteration's dK / dQ MMAs must have finished reading it
-      if (it > 0 && ok && !mbar_wait(mma_done, (it - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+      // (two buffers: the MMAs of iteration it-2 were the last readers of this one)
+      if (it > 1 && ok && !mbar_wait(ds_free(it & 1), ((it >> 1) - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
       {
-        uint8_t* row_ptr = ds_gen + r_local * 128;
+        uint8_t* row_ptr = ds_gen + (it & 1) * DS_BYTES + r_local * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 w = make_uint4(dsk[4 * c], dsk[4 * c + 1], dsk[4 * c + 2], dsk[4 * c + 3]);
@@ -309,7 +335,7 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (lane == 0) mbar_arrive(ds_ready);
     }
     // ---- epilogue: dK / dV accumulators -> bf16 rows of the key tile
-    if (ok && n_iter > 0 && !mbar_wait(mma_done, (n_iter - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+    if (ok && n_iter > 0 && !mbar_wait(final_bar, 0, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
     if (ok) {
       tc_fence_after();
 #pragma unroll 1
