@@ -29,6 +29,25 @@ def cases(device: torch.device):
         yield Case(f"cuBLAS  GEMM {m}x{n}x{k}", lambda a=a, w=w, out=out: torch.matmul(a, w.t(), out=out),
                    flops_per_iter=flops)
 
+    # attention at the 8B shape: (B, S, H + 2 Hkv, hd) fused projection output, causal
+    import math
+
+    b, sq, h, hkv, hd = 2, 4096, 32, 8, 128
+    qkv = torch.randn(b, sq, h + 2 * hkv, hd, device=device, dtype=bf)
+    q, k, v = qkv[:, :, :h], qkv[:, :, h:h + hkv], qkv[:, :, h + hkv:]
+    sc = 1.0 / math.sqrt(hd)
+    aflops = 4.0 * b * h * sq * sq * hd / 2
+    out, lse = K.attn_fwd(q, k, v, True, None, sc)
+    dout = torch.randn_like(out)
+    yield Case("tcgen05 attention fwd (2x32x4096x128, causal)", lambda: K.attn_fwd(q, k, v, True, None, sc),
+               flops_per_iter=aflops)
+    yield Case("tcgen05 attention bwd", lambda: K.attn_bwd(dout, q, k, v, out, lse, True, None, sc),
+               flops_per_iter=2.5 * aflops)
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    yield Case("library attention fwd (SDPA)",
+               lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True, scale=sc,
+                                                                        enable_gqa=True), flops_per_iter=aflops)
+
     t, d = 8192, 4096
     x = torch.randn(t, d, device=device, dtype=bf)
     wn = torch.ones(d, device=device, dtype=bf)

@@ -61,6 +61,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_fp8": [vp, vp, vp, i, i, i, ll, ll, i, i, i, vp, vp, i, i, vp],
         "kf_fp8_scale_bf16": [vp, ll, i, vp, vp, vp],
         "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
+        "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
@@ -401,6 +402,26 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
         "kf_attn_fwd_bf16",
     )
     return out, lse
+
+
+def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None,
+                        residual: torch.Tensor | None = None) -> torch.Tensor:
+    """out[T/tp, D] = reduce-scatter over the ranks of ``ctx`` of x2[T, K_local] @ w[D, K_local]ᵀ (+ residual), with the
+    tiles pushed to their owners from the GEMM epilogue.  ``ctx`` is a ``comm.fused_tp.GemmRSContext``."""
+    t, k = x2.shape
+    d = w.shape[0]
+    assert x2.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == k
+    tl = t // ctx.world
+    if out is None:
+        out = torch.empty((tl, d), dtype=torch.bfloat16, device=x2.device)
+    ctx.reserve(t, d)
+    _check(
+        lib().kf_gemm_rs_bf16(x2.data_ptr(), w.data_ptr(), ctx.stage_ptrs, ctx.flag_ptrs, out.data_ptr(),
+                              residual.data_ptr() if residual is not None else None, t, d, k, seq_len, x2.stride(0),
+                              w.stride(0), ctx.world, ctx.rank, ctx.next_call(), sm_count(), _stream()),
+        "kf_gemm_rs_bf16",
+    )
+    return out
 
 
 def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=None, dk=None, dv=None):

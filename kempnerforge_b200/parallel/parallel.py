@@ -13,6 +13,8 @@ Parity: kempnerforge/distributed/parallel.py:5-10,72-122,125-174,250-302,499-597
 
 from __future__ import annotations
 
+import os
+
 import logging
 
 import torch
@@ -77,11 +79,23 @@ def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, **_) -> Da
     pg = dp_process_group(mesh)
     allocator = None
     if transport is None:
-        transport = "collective"
+        transport = os.environ.get("KF_DP_TRANSPORT", "auto")
+    if transport == "auto":
+        # our peer-memory kernels when the job is plain data parallelism on GPUs of one NVLink domain;
+        # library collectives otherwise (other mesh dimensions, CPU, several nodes)
+        pure_dp = mesh is not None and all(mesh_dim(mesh, d)[1] <= 1 for d in ("tp", "ep", "pp", "dp_replicate"))
+        one_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) == int(os.environ.get("WORLD_SIZE", "1") or 1)
+        on_gpu = torch.cuda.is_available() and pg is not None and "nccl" in str(torch.distributed.get_backend(pg))
+        transport = "symmetric" if (pure_dp and one_node and on_gpu and torch.distributed.get_world_size(pg) > 1) else "collective"
     if transport == "symmetric":
-        from kempnerforge_b200.comm import symmetric
+        try:
+            from kempnerforge_b200.comm import symmetric
 
-        allocator = symmetric.make_allocator(pg)
+            allocator = symmetric.make_allocator(pg)
+            allocator(16, torch.bfloat16, torch.device("cuda", torch.cuda.current_device()))  # probe the rendezvous once
+        except Exception as e:  # noqa: BLE001  symmetric memory is optional: fall back, loudly
+            log.warning("symmetric-memory transport unavailable (%s); using library collectives", e)
+            transport, allocator = "collective", None
     return DataParallelEngine(model, pg, transport=transport, allocator=allocator)
 
 

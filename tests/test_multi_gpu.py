@@ -56,7 +56,7 @@ def _run(world: int, transport: str = "", multimem: bool = True, tmp_dir: str = 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_sharded_data_parallel_two_gpus():
-    r = _run(2)
+    r = _run(2, transport="collective")
     assert r["replicas_identical"], "ranks ended with different parameters"
     assert all(l == l and 0 < l < 20 for l in r["losses"]) and all(n > 0 for n in r["norms"])
     assert r["losses"][-1] < r["losses"][0] + 0.5
@@ -66,10 +66,67 @@ def test_sharded_data_parallel_two_gpus():
 @pytest.mark.parametrize("multimem", [False, True])
 def test_symmetric_transport_matches_collectives(multimem):
     """Fused reduce-scatter / AdamW / publish kernels over peer memory against the NCCL path."""
-    base = _run(2)
+    base = _run(2, transport="collective")
     fused = _run(2, transport="symmetric", multimem=multimem)
     assert fused["replicas_identical"]
     for a, b in zip(base["losses"], fused["losses"]):
         assert abs(a - b) < 5e-2, (base["losses"], fused["losses"])
     for a, b in zip(base["norms"], fused["norms"]):
         assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (base["norms"], fused["norms"])
+
+
+GEMM_RS_WORKER = r'''
+import json, os, sys, torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["KF_ROOT"])
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl")
+from kempnerforge_b200.comm.fused_tp import GemmRSContext
+from kempnerforge_b200.ops import cuda as K
+dev = torch.device("cuda")
+B, S, D, Kl = 2, 128 * world * 2, 768, 320
+T = B * S
+ctx = GemmRSContext(dist.group.WORLD, dev, T, D)
+errs = []
+for call in range(5):
+    g = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
+    x = torch.randn(T, Kl, device=dev, dtype=torch.bfloat16, generator=g)
+    w = torch.randn(D, Kl, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+    res = torch.randn(T // world, D, device=dev, dtype=torch.bfloat16, generator=g) if call % 2 else None
+    out = K.gemm_reduce_scatter(x, w, ctx, S, residual=res)
+    full = (x.float() @ w.float().t())
+    dist.all_reduce(full)
+    mine = full.view(B, world, S // world, D)[:, rank].reshape(T // world, D)
+    if res is not None:
+        mine = mine + res.float()
+    errs.append(((out.float() - mine).abs().max() / mine.abs().max()).item())
+torch.cuda.synchronize()
+status = K.read_status()
+worst = torch.tensor([max(errs), float(status)], device=dev)
+dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+if rank == 0:
+    print("RESULT " + json.dumps({"max_rel_err": worst[0].item(), "status": worst[1].item()}))
+dist.destroy_process_group()
+'''
+
+
+def _run_script(script_text: str, world: int, name: str, extra_env: dict | None = None):
+    path = os.path.join("/tmp", f"kf_{name}_{os.getpid()}.py")
+    with open(path, "w") as f:
+        f.write(script_text)
+    env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29641", path]
+    res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0, (res.stdout[-1500:] + "\n" + res.stderr[-4000:])
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_fused_gemm_reduce_scatter_matches_nccl():
+    """GEMM whose epilogue pushes tiles to the owning rank and reduces them, against matmul + all-reduce."""
+    r = _run_script(GEMM_RS_WORKER, 2, "gemm_rs")
+    assert r["status"] == 0
+    assert r["max_rel_err"] < 2e-2, r
