@@ -28,7 +28,8 @@ namespace rs {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2, STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int THREADS = 192, TMEM_COLS = 512;
-constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+constexpr int XPOSE_BYTES = 4 * 32 * 144;  // per epilogue warp: 32 rows x 128 B (+16 B pad against bank conflicts)
+constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + XPOSE_BYTES;
 constexpr int MAX_PEERS = 8;
 
 struct Peers {
@@ -52,8 +53,15 @@ __device__ __forceinline__ TileRef tile_ref(int t, int rank, int tp, int mb_per_
   const int r = t - oi * per_owner;
   TileRef x;
   x.owner = (rank + 1 + oi) % tp;
-  x.local_mb = r / n_blocks;  // row block inside the owner's [T / tp] rows
-  x.nb = r - x.local_mb * n_blocks;
+  // inside an owner's rows: eight row blocks share each sweep over the column blocks (weight tiles stay in L2)
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * n_blocks;
+  const int g = r / per_group;
+  const int first = g * GROUP_M;
+  const int rows = min(GROUP_M, mb_per_owner - first);
+  const int rr = r - g * per_group;
+  x.local_mb = first + rr % rows;
+  x.nb = rr / rows;
   const int b = x.local_mb / mb_per_seq_shard;
   const int sb = x.local_mb - b * mb_per_seq_shard;
   x.row0 = b * S + x.owner * (mb_per_seq_shard * BM) + sb * BM;
@@ -157,17 +165,41 @@ kf_gemm_rs_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_const
       // destination: the owner's staging slice for source `rank`
       __nv_bfloat16* slice = reinterpret_cast<__nv_bfloat16*>(peers.stage[tr.owner]) +
                              (size_t(parity) * tp + rank) * slice_elems;
-      const int lrow = tr.local_mb * BM + quarter * 32 + lane;
       const int col0 = tr.nb * BN;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      __nv_bfloat16* c_row = slice + size_t(lrow) * D + col0;
+      // Peer stores want long contiguous runs (a 16-byte store per row would cross NVLink as a 16-byte
+      // packet), so 64 columns at a time go through shared memory: thread = row on the way in, eight lanes per
+      // row (128 contiguous bytes) on the way out.
+      uint8_t* xp = smem_raw + (bar_base - smem_u32(smem_raw)) + 256 + quarter * (32 * 144);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(t_row + c * 64, v0);
+        tmem_ld_32x32(t_row + c * 64 + 32, v1);
         tmem_ld_wait();
-        const int valid = min(32, D - (col0 + c * 32));
-        if (ok && valid > 0) store_chunk<__nv_bfloat16>(c_row + c * 32, v, valid, false, nullptr);
+        uint4* mine = reinterpret_cast<uint4*>(xp + lane * 144);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mine[i] = make_uint4(pack_bf16(__uint_as_float(v0[8 * i]), __uint_as_float(v0[8 * i + 1])),
+                               pack_bf16(__uint_as_float(v0[8 * i + 2]), __uint_as_float(v0[8 * i + 3])),
+                               pack_bf16(__uint_as_float(v0[8 * i + 4]), __uint_as_float(v0[8 * i + 5])),
+                               pack_bf16(__uint_as_float(v0[8 * i + 6]), __uint_as_float(v0[8 * i + 7])));
+          mine[4 + i] = make_uint4(pack_bf16(__uint_as_float(v1[8 * i]), __uint_as_float(v1[8 * i + 1])),
+                                   pack_bf16(__uint_as_float(v1[8 * i + 2]), __uint_as_float(v1[8 * i + 3])),
+                                   pack_bf16(__uint_as_float(v1[8 * i + 4]), __uint_as_float(v1[8 * i + 5])),
+                                   pack_bf16(__uint_as_float(v1[8 * i + 6]), __uint_as_float(v1[8 * i + 7])));
+        }
+        __syncwarp();
+        const int cbase = col0 + c * 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3), piece = lane & 7;  // row of this warp's 32, 16-byte piece of its 128 B
+          const uint4 w = *reinterpret_cast<const uint4*>(xp + rr * 144 + piece * 16);
+          const int col = cbase + piece * 8;
+          if (ok && col < D)
+            *reinterpret_cast<uint4*>(slice + size_t(tr.local_mb * BM + quarter * 32 + rr) * D + col) = w;
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __threadfence_system();              // this thread's stores are visible system-wide ...

@@ -52,3 +52,23 @@ class GemmRSContext:
         n = self.calls
         self.calls += 1
         return n
+
+
+class AgGemmContext(GemmRSContext):
+    """Gather buffer ([2 parities][T][K] bf16) and per-(source, row block) counters for the fused
+    all-gather + GEMM kernel; same life cycle as ``GemmRSContext``."""
+
+    def __init__(self, group, device: torch.device, max_tokens: int, max_dim: int) -> None:
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.max_tokens, self.max_dim = max_tokens, max_dim
+        self.stage = SymmBuffer(2 * max_tokens * max_dim, torch.bfloat16, device, group)
+        self.flags = SymmBuffer(2 * self.world * (max_tokens // self.world // 128 + 1), torch.int32, device, group)
+        self.stage_ptrs = (ctypes.c_longlong * 8)(*self.stage.peer_ptrs)
+        self.flag_ptrs = (ctypes.c_longlong * 8)(*self.flags.peer_ptrs)
+        self.calls = 0
+        self.shape = None
+        self.stage.barrier()

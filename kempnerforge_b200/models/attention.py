@@ -82,14 +82,19 @@ class Attention(nn.Module):
         doc_ids: torch.Tensor | None = None,
         key_padding_mask: torch.Tensor | None = None,
     ) -> torch.Tensor:
+        qkv_w = [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight]
+        qkv = None
         if self.tp is not None:
-            x = self.tp.before_column_parallel(x)
-        b, s, _ = x.shape
+            qkv = self.tp.column_linear(x, qkv_w)  # gathers the sequence shards (inside the GEMM when it can)
+            b, s = qkv.shape[0], qkv.shape[1]
+        else:
+            b, s, _ = x.shape
         # local head counts follow the weight shapes so a tensor-parallel shard works unchanged
         hd = self.head_dim
         h = self.q_proj.weight.shape[0] // hd
         hkv = self.k_proj.weight.shape[0] // hd
-        qkv = F.fused_linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
+        if qkv is None:
+            qkv = F.fused_linear(x, qkv_w)
         qkv = qkv.view(b, s, h + 2 * hkv, hd)
         if self.q_norm is not None:
             qkv = torch.cat(
@@ -105,5 +110,6 @@ class Attention(nn.Module):
             self.last_attention_weights = probs.detach()
         else:
             out = F.attention(q, k, v, causal=causal, doc_ids=doc_ids, key_padding_mask=key_padding_mask)
-        y = F.linear(out.reshape(b, s, h * hd), self.o_proj.weight)
-        return self.tp.after_row_parallel(y) if self.tp is not None else y
+        if self.tp is not None:
+            return self.tp.row_linear(out.reshape(b, s, h * hd), self.o_proj.weight)
+        return F.linear(out.reshape(b, s, h * hd), self.o_proj.weight)

@@ -26,10 +26,10 @@ class SwiGLUMLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None:
-            x = self.tp.before_column_parallel(x)
+            gu = self.tp.column_linear(x, [self.gate_proj.weight, self.up_proj.weight])
+            return self.tp.row_linear(F.swiglu_stacked(gu), self.down_proj.weight)
         gu = F.fused_linear(x, [self.gate_proj.weight, self.up_proj.weight])
-        y = F.linear(F.swiglu_stacked(gu), self.down_proj.weight)
-        return self.tp.after_row_parallel(y) if self.tp is not None else y
+        return F.linear(F.swiglu_stacked(gu), self.down_proj.weight)
 
 
 _ACTS = {"gelu": nn.GELU, "relu": nn.ReLU, "silu": nn.SiLU}

@@ -61,6 +61,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_fp8": [vp, vp, vp, i, i, i, ll, ll, i, i, i, vp, vp, i, i, vp],
         "kf_fp8_scale_bf16": [vp, ll, i, vp, vp, vp],
         "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
+        "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
@@ -402,6 +403,25 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
         "kf_attn_fwd_bf16",
     )
     return out, lse
+
+
+def all_gather_gemm(x_shard: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[T, N] = gather over the ranks of ``ctx`` (along the sequence) of x_shard[T/tp, K], times w[N, K]ᵀ; the shard
+    is pushed to the peers by copy warps of the GEMM kernel itself.  ``ctx`` is a ``comm.fused_tp.AgGemmContext``."""
+    tl, k = x_shard.shape
+    t = tl * ctx.world
+    n = w.shape[0]
+    assert x_shard.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == k
+    if out is None:
+        out = torch.empty((t, n), dtype=torch.bfloat16, device=x_shard.device)
+    ctx.reserve(t, k)
+    _check(
+        lib().kf_ag_gemm_bf16(x_shard.data_ptr(), w.data_ptr(), ctx.stage_ptrs, ctx.flag_ptrs, out.data_ptr(), t, n, k,
+                              seq_len, x_shard.stride(0), w.stride(0), out.stride(0), ctx.world, ctx.rank, ctx.next_call(),
+                              sm_count(), _stream()),
+        "kf_ag_gemm_bf16",
+    )
+    return out
 
 
 def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None,

@@ -22,6 +22,8 @@ embeddings and MoE models, vocabulary-parallel output head).
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -41,7 +43,12 @@ def _all_gather_dim(x: torch.Tensor, dim: int, group) -> torch.Tensor:
 def _reduce_scatter_dim(x: torch.Tensor, dim: int, group) -> torch.Tensor:
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     x = x.contiguous()
-    dist.all_reduce(x, group=group)  # gloo has no reduce-scatter; NCCL paths are replaced by fused kernels
+    if x.is_cuda and "nccl" in str(dist.get_backend(group)):
+        parts = [p.contiguous() for p in x.chunk(world, dim=dim)]
+        out = torch.empty_like(parts[rank])
+        dist.reduce_scatter(out, parts, group=group)
+        return out
+    dist.all_reduce(x, group=group)  # gloo has no reduce-scatter
     return x.chunk(world, dim=dim)[rank].contiguous()
 
 
@@ -132,6 +139,8 @@ class TPContext:
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.sequence_parallel = sequence_parallel
+        self._fused: bool | None = None      # decided at the first call (needs a tensor to look at)
+        self._ctx: dict[str, object] = {}    # symmetric-memory buffers of the fused kernels
 
     def before_column_parallel(self, x: torch.Tensor) -> torch.Tensor:
         if self.sequence_parallel:
@@ -142,6 +151,43 @@ class TPContext:
         if self.sequence_parallel:
             return _ScatterSumSeq.apply(y, 1, self.group)
         return _AllReduceFwd.apply(y, self.group)
+
+    # ---- fused GEMM + collective kernels (sequence parallelism on GPUs of one NVLink domain) -------------
+    def _fused_ok(self, x: torch.Tensor, seq_shard: int, k: int) -> bool:
+        if self._fused is None:
+            self._fused = (os.environ.get("KF_TP_FUSED", "1") != "0" and self.sequence_parallel and x.is_cuda
+                           and "nccl" in str(dist.get_backend(self.group))
+                           and int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) == int(os.environ.get("WORLD_SIZE", "1")))
+        return bool(self._fused) and x.dtype == torch.bfloat16 and seq_shard % 128 == 0 and k % 32 == 0
+
+    def _context(self, kind: str, tokens: int, dim: int, device):
+        from kempnerforge_b200.comm.fused_tp import AgGemmContext, GemmRSContext
+
+        cur = self._ctx.get(kind)
+        if cur is None or tokens > cur.max_tokens or dim > cur.max_dim:
+            cls = AgGemmContext if kind == "ag" else GemmRSContext
+            if cur is not None:
+                tokens, dim = max(tokens, cur.max_tokens), max(dim, cur.max_dim)
+            cur = self._ctx[kind] = cls(self.group, device, tokens, dim)
+        return cur
+
+    def column_linear(self, x: torch.Tensor, weights: list[torch.Tensor]) -> torch.Tensor:
+        """Column-parallel Linear on a sequence-sharded (B, S/tp, K) input: one kernel gathers and multiplies when
+        the fused path applies, otherwise all-gather followed by the GEMM."""
+        from kempnerforge_b200.ops import functional as F
+
+        if x.dim() == 3 and self._fused_ok(x, x.shape[1], x.shape[2]) and all(w.dtype == torch.bfloat16 for w in weights):
+            return _FusedColumnLinearFn.apply(x, self, *weights)
+        return F.fused_linear(self.before_column_parallel(x), weights)
+
+    def row_linear(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """Row-parallel Linear whose (B, S, D) partial sums are reduce-scattered along the sequence."""
+        from kempnerforge_b200.ops import functional as F
+
+        if (x.dim() == 3 and x.shape[1] % self.size == 0 and self._fused_ok(x, x.shape[1] // self.size, 32)
+                and weight.dtype == torch.bfloat16 and x.shape[2] % 8 == 0 and weight.shape[0] % 8 == 0):
+            return _FusedRowLinearFn.apply(x, self, weight)
+        return self.after_row_parallel(F.linear(x, weight))
 
     def scatter_sequence(self, x: torch.Tensor) -> torch.Tensor:
         return _SliceSeq.apply(x, 1, self.group) if self.sequence_parallel else x
@@ -156,6 +202,80 @@ class TPContext:
 
     def gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         return _GatherReplicated.apply(logits, logits.dim() - 1, self.group)
+
+
+class _FusedColumnLinearFn(torch.autograd.Function):
+    """y = gather_seq(x) @ [W_0; W_1; ...]ᵀ with the gather inside the GEMM kernel.  The backward uses library
+    collectives: reduce-scatter of the input gradient, all-gather of the input for the weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, tp, *weights):
+        from kempnerforge_b200.ops import cuda as kc
+        from kempnerforge_b200.ops import functional as F
+
+        b, s_local, k = x.shape
+        w = F._stack_weight_rows(weights)
+        x2 = x.reshape(b * s_local, k)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        t = b * s_local * tp.size
+        y = kc.all_gather_gemm(x2, w, tp._context("ag", t, k, x.device), s_local * tp.size)
+        ctx.save_for_backward(x2, *weights)
+        ctx.tp, ctx.dims = tp, (b, s_local, k)
+        # rows come out in (b, s) order of the full sequence
+        return y.view(b, s_local * tp.size, w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from kempnerforge_b200.ops import cuda as kc
+        from kempnerforge_b200.ops import functional as F
+
+        x2, *weights = ctx.saved_tensors
+        tp, (b, s_local, k) = ctx.tp, ctx.dims
+        w = F._stack_weight_rows(weights)
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx_full = kc.gemm(dy2, w, a_kmajor=True, b_kmajor=False).view(b, s_local * tp.size, k)
+            dx = _reduce_scatter_dim(dx_full, 1, tp.group)
+        wgrads = [None] * len(weights)
+        if any(ctx.needs_input_grad[2:]):
+            x_full = _all_gather_dim(x2.view(b, s_local, k), 1, tp.group).reshape(-1, k)
+            wgrads = F._linear_weight_grads(kc, dy2, x_full, weights, ctx.needs_input_grad[2:])
+        return (dx, None, *wgrads)
+
+
+class _FusedRowLinearFn(torch.autograd.Function):
+    """out = reduce_scatter_seq(x @ Wᵀ) with the tiles pushed to their owners from the GEMM epilogue.  The backward
+    all-gathers the output gradient with the library and runs plain GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, tp, weight):
+        from kempnerforge_b200.ops import cuda as kc
+
+        b, s, k = x.shape
+        x2 = x.reshape(b * s, k)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        d = weight.shape[0]
+        out = kc.gemm_reduce_scatter(x2, weight, tp._context("rs", b * s, d, x.device), s)
+        ctx.save_for_backward(x2, weight)
+        ctx.tp, ctx.dims = tp, (b, s, k, d)
+        return out.view(b, s // tp.size, d)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from kempnerforge_b200.ops import cuda as kc
+        from kempnerforge_b200.ops import functional as F
+
+        x2, weight = ctx.saved_tensors
+        tp, (b, s, k, d) = ctx.tp, ctx.dims
+        dy_full = _all_gather_dim(dy, 1, tp.group).reshape(b * s, d)
+        dx = kc.gemm(dy_full, weight, a_kmajor=True, b_kmajor=False).view(b, s, k) if ctx.needs_input_grad[0] else None
+        (gw,) = F._linear_weight_grads(kc, dy_full, x2, [weight], [ctx.needs_input_grad[2]])
+        return dx, None, gw
 
 
 # --------------------------------------------------------------------------- sharding the weights

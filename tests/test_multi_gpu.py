@@ -130,3 +130,59 @@ def test_fused_gemm_reduce_scatter_matches_nccl():
     r = _run_script(GEMM_RS_WORKER, 2, "gemm_rs")
     assert r["status"] == 0
     assert r["max_rel_err"] < 2e-2, r
+
+
+AG_GEMM_WORKER = r'''
+import json, os, sys, torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["KF_ROOT"])
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl")
+from kempnerforge_b200.comm.fused_tp import AgGemmContext
+from kempnerforge_b200.ops import cuda as K
+dev = torch.device("cuda")
+B, S, N, Kd = 2, 128 * world * 2, 520, 384
+T = B * S
+ctx = AgGemmContext(dist.group.WORLD, dev, T, Kd)
+errs = []
+for call in range(5):
+    g = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
+    xs = torch.randn(T // world, Kd, device=dev, dtype=torch.bfloat16, generator=g)
+    w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+    out = K.all_gather_gemm(xs, w, ctx, S)
+    parts = [torch.empty_like(xs) for _ in range(world)]
+    dist.all_gather(parts, xs)
+    full = torch.stack([p.view(B, S // world, Kd) for p in parts], dim=1).reshape(T, Kd)
+    want = full.float() @ w.float().t()
+    errs.append(((out.float() - want).abs().max() / want.abs().max()).item())
+torch.cuda.synchronize()
+worst = torch.tensor([max(errs), float(K.read_status())], device=dev)
+dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+if rank == 0:
+    print("RESULT " + json.dumps({"max_rel_err": worst[0].item(), "status": worst[1].item()}))
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_fused_all_gather_gemm_matches_nccl():
+    """GEMM whose copy warps push the local shard to the peers, against all-gather + matmul."""
+    r = _run_script(AG_GEMM_WORKER, 2, "ag_gemm")
+    assert r["status"] == 0
+    assert r["max_rel_err"] < 2e-2, r
+
+
+TP_WORKER = WORKER.replace('"distributed": dict(dp_shard=world)', '"distributed": dict(tp=world, dp_shard=1)') \
+                  .replace("g = torch.Generator().manual_seed(100 + rank)", "g = torch.Generator().manual_seed(100)")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_fused_kernels_match_library_collectives():
+    """TP=2 with sequence parallelism: all-gather+GEMM / GEMM+reduce-scatter kernels against NCCL collectives."""
+    fused = _run_script(TP_WORKER, 2, "tp_fused", {"KF_TP_FUSED": "1", "KF_TRANSPORT": ""})
+    plain = _run_script(TP_WORKER, 2, "tp_plain", {"KF_TP_FUSED": "0", "KF_TRANSPORT": ""})
+    for a, b in zip(plain["losses"], fused["losses"]):
+        assert abs(a - b) < 5e-2, (plain["losses"], fused["losses"])
+    for a, b in zip(plain["norms"], fused["norms"]):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (plain["norms"], fused["norms"])
