@@ -60,11 +60,57 @@ def _unwrap(model):
     return getattr(model, "module", model)
 
 
+def _shard_meshes(model) -> dict[str, Any]:
+    """{"tp": 1-D DeviceMesh, "ep": 1-D DeviceMesh} for the mesh dimensions this model's parameters are sharded over."""
+    m = _unwrap(model)
+    mesh = getattr(m, "_kf_mesh", None)
+    out: dict[str, Any] = {}
+    if mesh is None:
+        return out
+    names = mesh.mesh_dim_names or ()
+    if "tp" in names:
+        out["tp"] = mesh["tp"]
+    if "ep" in names:
+        out["ep"] = mesh["ep"]
+    elif getattr(m, "ep_in_dp", False) and "dp_shard" in names:
+        out["ep"] = mesh["dp_shard"]  # experts sharded over the data-parallel ranks
+    return out
+
+
+def as_sharded(t: torch.Tensor, spec, meshes: dict[str, Any]):
+    """Describe a rank-local shard to the checkpoint layer: a DTensor over the 1-D mesh of its parallel dimension,
+    so that every rank's piece is written (not just rank 0's) and a different world size can re-shard on load."""
+    if spec is None or spec[0] not in meshes:
+        return t
+    from torch.distributed.tensor import DTensor, Shard
+
+    return DTensor.from_local(t, meshes[spec[0]], [Shard(spec[1])], run_check=False)
+
+
+def to_local(t):
+    return t.to_local() if hasattr(t, "to_local") else t
+
+
+def _shard_specs(model) -> dict[str, tuple[str, int]]:
+    return {n: p._kf_shard for n, p in _unwrap(model).named_parameters(remove_duplicate=False)
+            if getattr(p, "_kf_shard", None) is not None}
+
+
 def model_state_dict(model) -> dict[str, torch.Tensor]:
     engine = getattr(_unwrap(model), "_kf_engine", None)
     if engine is not None and hasattr(engine, "wait_all"):
         engine.wait_all()  # parameters being published asynchronously must have landed
-    return dict(_unwrap(model).state_dict())
+    sd = dict(_unwrap(model).state_dict())
+    meshes = _shard_meshes(model)
+    if meshes:
+        for name, spec in _shard_specs(model).items():
+            if name in sd:
+                sd[name] = as_sharded(sd[name], spec, meshes)
+    return sd
+
+
+def load_model_state_dict(model, loaded: dict[str, Any]) -> None:
+    _unwrap(model).load_state_dict({k: to_local(v) for k, v in loaded.items()}, strict=False)
 
 
 def _param_fqns(model) -> dict[int, str]:
@@ -103,11 +149,24 @@ def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
         for g in opt.param_groups:
             groups.append({**{k: v for k, v in g.items() if k != "params"},
                            "params": [fqn_of[id(p)] for p in g["params"] if id(p) in fqn_of]})
+    meshes = _shard_meshes(model)
+    if meshes:
+        specs = _shard_specs(model)
+        params = dict(_unwrap(model).named_parameters(remove_duplicate=False))
+        for fqn, entry in state.items():
+            spec = specs.get(fqn)
+            if spec is None:
+                continue
+            for k, v in entry.items():
+                if torch.is_tensor(v) and v.dim() > 0 and v.shape == params[fqn].shape:
+                    entry[k] = as_sharded(v.contiguous(), spec, meshes)
     return {"state": state, "param_groups": groups}
 
 
 def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
     """Inverse of ``optimizer_state_dict`` for tensors that were loaded in place (flat views) or into copies."""
+    loaded = {**loaded, "state": {fqn: {k: to_local(v) for k, v in entry.items()}
+                                  for fqn, entry in loaded["state"].items()}}
     name_to_param = dict(_unwrap(model).named_parameters(remove_duplicate=False))
     engine = getattr(_unwrap(model), "_kf_engine", None)
     opts = [optimizer] + ([optimizer.inner_adam] if getattr(optimizer, "inner_adam", None) is not None else [])
@@ -169,8 +228,16 @@ def _optimizer_template(model, optimizer) -> dict[str, Any]:
     """Freshly allocated tensors of the right shapes for ``dcp.load`` to fill."""
     tmpl = optimizer_state_dict(model, optimizer)
     for fqn, entry in tmpl["state"].items():
-        tmpl["state"][fqn] = {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in entry.items()}
+        tmpl["state"][fqn] = {k: (_clone_like(v) if torch.is_tensor(v) else v) for k, v in entry.items()}
     return tmpl
+
+
+def _clone_like(v: torch.Tensor) -> torch.Tensor:
+    if hasattr(v, "to_local"):
+        from torch.distributed.tensor import DTensor
+
+        return DTensor.from_local(v.to_local().detach().clone(), v.device_mesh, v.placements, run_check=False)
+    return v.detach().clone()
 
 
 def materialize_optimizer_state(model, optimizer) -> None:
@@ -348,7 +415,7 @@ class CheckpointManager:
         if state:
             dcp.load(state, checkpoint_id=str(self._dcp_dir(step_dir)), process_group=self.process_group)
             if "model" in state:
-                _unwrap(self.model).load_state_dict(state["model"], strict=False)
+                load_model_state_dict(self.model, state["model"])
             if "optimizer" in state:
                 load_optimizer_state_dict(self.model, self.optimizer, state["optimizer"])
         train_state = self._load_train_state(step_dir)

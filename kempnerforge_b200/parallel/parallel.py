@@ -121,6 +121,7 @@ def build_parallel_model(
     if hasattr(model, "rope_tables"):
         model.rope_tables(device, 0, 1)
 
+    model._kf_mesh = device_mesh  # checkpoints describe TP / EP shards as sharded tensors over this mesh
     _, tp_size, _ = mesh_dim(device_mesh, "tp")
     if tp_size > 1:
         from kempnerforge_b200.parallel.tensor_parallel import apply_tensor_parallel
