@@ -34,6 +34,13 @@ H200_PUBLISHED_TOKS = {1: 10471.0, 2: 18728.0, 4: 38983.0}  # reference, H200, F
 MODELS = {
     "llama3_8b": dict(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256,
                       ffn_hidden_dim=14336, max_seq_len=4096, rope_theta=500000.0),
+    # 13B shape of the tensor-parallel rows (dim 5120, 40 layers, ffn 13824)
+    "llama_13b": dict(dim=5120, n_layers=40, n_heads=40, n_kv_heads=8, vocab_size=128256, ffn_hidden_dim=13824,
+                      max_seq_len=4096, rope_theta=500000.0),
+    # MoE: softmax top-2 over 8 experts of 5632, every layer
+    "moe_8x": dict(dim=2048, n_layers=24, n_heads=16, n_kv_heads=16, vocab_size=102400, ffn_hidden_dim=5632,
+                   max_seq_len=4096, rope_theta=500000.0, num_experts=8, moe_top_k=2, moe_router="softmax_topk",
+                   moe_packed_experts=True),
     # small shape for quick functional checks of this script (not a benchmark number)
     "tiny": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536,
                  max_seq_len=512, rope_theta=500000.0),
@@ -50,7 +57,26 @@ def parse_args():
     ap.add_argument("--batch-size", type=int, default=2)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--transport", default=None)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (data parallel over the rest)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree")
+    ap.add_argument("--ep-in-dp", action="store_true", help="experts sharded over the data-parallel ranks (ours only)")
     return ap.parse_args()
+
+
+def mesh_dims(args, world: int) -> tuple[dict, int, str]:
+    """[distributed] fields, number of distinct batches per step, and a label such as "tp2xdp4"."""
+    if args.ep > 1 and args.ep_in_dp:
+        return {"ep": args.ep, "ep_in_dp": True, "dp_shard": world}, world, f"ep{args.ep}-in-dp{world}"
+    dp = world // (args.tp * args.ep)
+    dims = {"dp_shard": dp}
+    label = f"dp{dp}"
+    if args.tp > 1:
+        dims["tp"] = args.tp
+        label = f"tp{args.tp}x" + label
+    if args.ep > 1:
+        dims["ep"] = args.ep
+        label = f"ep{args.ep}x" + label
+    return dims, dp, label
 
 
 class ClockSampler:
@@ -149,14 +175,15 @@ def run_ours(args) -> dict:
                   "grad_clip_norm": 1.0, "seed": 0},
         "optimizer": {"name": "adamw", "lr": 3e-4, "weight_decay": 0.1, "fused": True},
         "scheduler": {"name": "cosine", "warmup_steps": 10},
-        "distributed": {"dp_shard": world},
+        "distributed": mesh_dims(args, world)[0],
         "metrics": {"log_interval": 1000},
         "data": {"pin_memory": True},
     })
+    _, n_batches, mesh_label = mesh_dims(args, world)
     trainer = Trainer(cfg, transport=args.transport)
     dev = trainer.device
     vocab = shape["vocab_size"]
-    gen = torch.Generator().manual_seed(1234 + rank)
+    gen = torch.Generator().manual_seed(1234 + trainer.dp_rank)  # ranks of one TP / EP group share their batch
 
     def host_batch():
         tok = torch.randint(0, vocab, (args.batch_size, seq + 1), generator=gen)
@@ -181,7 +208,7 @@ def run_ours(args) -> dict:
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
     ms_e2e, _, last_e2e = timed_region(torch, dist, world,
                                        lambda i: trainer.train_step([host_batches[i]]), args.steps)
-    tokens_per_step = args.batch_size * seq * world
+    tokens_per_step = args.batch_size * seq * n_batches
     value = tokens_per_step / (ms / 1e3)
     e2e = tokens_per_step / (ms_e2e / 1e3)
     peaks = {}
@@ -194,12 +221,13 @@ def run_ours(args) -> dict:
     mfu_measured = compute_mfu(cfg.model, value, world, seq, peaks.get("bf16_tflops", 1590.0))
     base = H200_PUBLISHED_TOKS.get(world)
     return {
-        "metric": "llama3_8b_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "metric": f"{args.model}_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b") else None,
+        "scaling": "weak",
+        "vs_baseline": (value / base) if (base and args.model == "llama3_8b" and mesh_label == f"dp{world}") else None,
         "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
-        "config": {"model": args.model, "global_batch": args.batch_size * world, "seq_len": seq,
-                   "parallelism": f"dp{world}", "activation_checkpointing": "full", "optimizer": "adamw_fused",
+        "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
+                   "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused",
                    "l2": "working set (>60 GB) far exceeds L2; no flush needed"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
@@ -240,8 +268,14 @@ def run_reference(args) -> dict:
         "--train.grad_accum_steps=1", "--train.mixed_precision=bf16", "--train.activation_checkpointing=full",
         "--train.compile_model=true", "--train.grad_clip_norm=1.0", "--train.seed=0",
         "--optimizer.name=adamw", "--optimizer.lr=3e-4", "--optimizer.weight_decay=0.1", "--optimizer.fused=true",
-        "--scheduler.name=cosine", "--scheduler.warmup_steps=10", f"--distributed.dp_shard={world}",
+        "--scheduler.name=cosine", "--scheduler.warmup_steps=10",
     ]
+    if args.ep_in_dp:
+        return {"impl": "reference", "unavailable": "the reference cannot shard experts over its data-parallel ranks"}
+    dims, n_batches, mesh_label = mesh_dims(args, world)
+    overrides += [f"--distributed.{k}={v}" for k, v in dims.items()]
+    if shape.get("num_experts"):
+        overrides = [o for o in overrides if o != "--train.compile_model=true"] + ["--train.compile_model=false"]
     config = load_config(None, overrides)
     tc, mc = config.train, config.model
     device_mesh = init_distributed(config.distributed, seed=tc.seed)
@@ -253,7 +287,10 @@ def run_reference(args) -> dict:
     scheduler = build_scheduler(optimizer, config.scheduler, max_steps=tc.max_steps)
     loss_fn = build_loss_fn(tc)
     model.train()
-    gen = torch.Generator().manual_seed(1234 + rank)
+    from kempnerforge.distributed.utils import get_dp_info
+
+    dp_rank = get_dp_info(device_mesh)[0] if device_mesh is not None else 0
+    gen = torch.Generator().manual_seed(1234 + dp_rank)
 
     def host_batch():
         tok = torch.randint(0, mc.vocab_size, (args.batch_size, seq + 1), generator=gen)
@@ -284,17 +321,17 @@ def run_reference(args) -> dict:
     host_batches = [host_batch() for _ in range(args.steps)]
     h2d = sum(t.numel() * t.element_size() for t in host_batches[0])
     ms_e2e, _, _ = timed_region(torch, dist, world, lambda i: step(*host_batches[i]), args.steps)
-    tokens_per_step = args.batch_size * seq * world
+    tokens_per_step = args.batch_size * seq * n_batches
     value = tokens_per_step / (ms / 1e3)
     base = H200_PUBLISHED_TOKS.get(world)
     return {
-        "metric": "llama3_8b_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "metric": f"{args.model}_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b") else None,
+        "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b" and mesh_label == f"dp{world}") else None,
         "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "reference",
-        "config": {"model": args.model, "global_batch": args.batch_size * world, "seq_len": seq,
-                   "parallelism": f"dp{world}", "activation_checkpointing": "full", "optimizer": "adamw_fused",
-                   "compile_model": True},
+        "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
+                   "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused",
+                   "compile_model": not shape.get("num_experts")},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},

@@ -1,0 +1,226 @@
+// Ragged grouped GEMM for mixture-of-experts layers on the 5th-generation tensor cores:
+//
+//   C[rows of expert e, :] = A[rows of expert e, :] * op(B_e)        for every expert e
+//
+// A holds the token rows sorted by expert; `offsets[e] .. offsets[e+1]` (int32, on the DEVICE) are expert e's
+// rows.  Nothing is padded and nothing is read back to the host: every CTA builds the table "first 128-row
+// tile of each expert" in shared memory from the offsets and walks the tiles persistently.  A tile's TMA box
+// may run past its expert's last row (into the next expert's rows); those accumulator rows are simply not
+// stored.  B is either [E][N][K] (K contiguous, nn.Linear weights of stacked experts) or [E][K][N]
+// (N contiguous, packed expert weights); the same kernel serves the forward and the input-gradient GEMM.
+//
+// Same pipeline as the dense kernel: TMA producer warp -> 4-stage 128B-swizzled ring -> one MMA-issuing
+// thread -> double-buffered fp32 accumulators in TMEM -> four epilogue warps.
+//
+// Replaces the padded `torch._grouped_mm` call and its Python pack / unpack loops in the reference
+// (kempnerforge/model/moe.py:20-145).
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+
+namespace kf {
+namespace grp {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2, STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int THREADS = 192, TMEM_COLS = 512;
+constexpr int MAX_EXPERTS = 256;
+constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + (MAX_EXPERTS + 1) * 4;
+
+struct Tile {
+  int e, row0, valid, nb;
+};
+
+// tile_start[e] = number of 128-row tiles of experts 0..e-1 (tile_start[E] = total)
+__device__ __forceinline__ Tile decode(int t, int n_blocks, const int* tile_start, const int* offsets, int E) {
+  const int nb = t % n_blocks;
+  const int tm = t / n_blocks;
+  int lo = 0, hi = E;  // largest e with tile_start[e] <= tm
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= tm) lo = mid; else hi = mid;
+  }
+  Tile x;
+  x.e = lo;
+  const int mb = tm - tile_start[lo];
+  x.row0 = offsets[lo] + mb * BM;
+  x.valid = min(BM, offsets[lo + 1] - x.row0);
+  x.nb = nb;
+  return x;
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        __nv_bfloat16* __restrict__ C, const int* __restrict__ offsets, int E, int N, int K,
+                        long long ldc, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 5);
+  uint8_t* bar_gen = smem_raw + (bar_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 5));
+  int* tile_start = reinterpret_cast<int*>(bar_gen + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blocks = (N + BN - 1) / BN;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      tile_start[e] = acc;
+      acc += (offsets[e + 1] - offsets[e] + BM - 1) / BM;
+    }
+    tile_start[E] = acc;
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const int num_tiles = tile_start[E] * n_blocks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Tile tl = decode(t, n_blocks, tile_start, offsets, E);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, tl.row0);
+          if (!B_MN) {
+            tma_load_2d(b_dst, &map_b, full_bar(s), kb * BK, tl.e * N + tl.nb * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * (64 * BK * 2), &map_b, full_bar(s), tl.nb * BN + 64 * c, tl.e * K + kb * BK);
+          }
+        }
+      }
+      for (int j = max(0, it - STAGES); j < it; ++j)
+        mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const int acc = tile_iter & 1;
+        if (!mbar_wait(tempty_bar(acc), ((tile_iter >> 1) & 1) ^ 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + s * STAGE_BYTES, b_src = a_src + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bd = B_MN ? umma_desc_sw128(b_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_f16(d_tmem, umma_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024), bd, idesc, (kb | k) != 0);
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(tfull_bar(acc));
+      }
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
+    }
+  } else {
+    const int quarter = warp & 3;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const Tile tl = decode(t, n_blocks, tile_start, offsets, E);
+      const int acc = tile_iter & 1;
+      if (!mbar_wait(tfull_bar(acc), (tile_iter >> 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int r = quarter * 32 + lane;
+      const int col0 = tl.nb * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      __nv_bfloat16* c_row = C + size_t(tl.row0 + r) * ldc + col0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait();
+        const int valid_cols = min(32, N - (col0 + c * 32));
+        if (r < tl.valid && valid_cols > 0) store_chunk<__nv_bfloat16>(c_row + c * 32, v, valid_cols, false, nullptr);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+}  // namespace grp
+}  // namespace kf
+
+extern "C" void* kf_status_device_ptr();
+
+extern "C" {
+
+// C[rows, N] = grouped A[rows, K] x B_e.  offsets: int32[E + 1] on the device (offsets[0] = 0, offsets[E] <= rows).
+//   b_mn == 0: B is [E][N][K] (K contiguous);  b_mn == 1: B is [E][K][N] (N contiguous; K must be a multiple of 64).
+//   lda / ldc in elements (multiples of 8); B is dense.  E <= 256.
+int kf_grouped_gemm_bf16(const void* A, const void* B, void* C, const void* offsets, int rows, int E, int N, int K,
+                         long long lda, long long ldc, int b_mn, int num_sms, void* stream) {
+  using namespace kf;
+  using namespace kf::grp;
+  if (E < 1 || E > MAX_EXPERTS || (lda & 7) || (ldc & 7) || (K & 7) || (N & 7) || (b_mn && (K % BK))) return 5;
+  if (rows <= 0) return 0;
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, A, rows, K, lda, BK, BM);
+  if (rc) return 100 + rc;
+  rc = b_mn ? make_map_2d_bf16(&mb, B, uint64_t(E) * K, N, N, 64, BK) : make_map_2d_bf16(&mb, B, uint64_t(E) * N, K, K, BK, BN);
+  if (rc) return 200 + rc;
+  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
+  const int upper = ((rows + BM - 1) / BM + E) * ((N + BN - 1) / BN);  // at most one partial tile per expert
+  const int grid = upper < num_sms ? upper : num_sms;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (b_mn) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_grouped_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_grouped_gemm_tcgen05<true><<<grid, THREADS, SMEM, st>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),
+                                                              reinterpret_cast<const int*>(offsets), E, N, K, ldc, status);
+  } else {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_grouped_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_grouped_gemm_tcgen05<false><<<grid, THREADS, SMEM, st>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),
+                                                               reinterpret_cast<const int*>(offsets), E, N, K, ldc, status);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // extern "C"

@@ -106,6 +106,16 @@ class MoEMLP(nn.Module):
 
     def _local_forward(self, x_flat, weights, indices):
         t, k = indices.shape
+        from kempnerforge_b200.ops import moe_ops
+
+        if (moe_ops.native_ok(x_flat, self.num_experts, k) and x_flat.dtype == torch.bfloat16
+                and x_flat.shape[1] % 8 == 0 and not (self.gradient_scale and self.training)):
+            # device-side stable sort by expert, row gather, grouped expert GEMMs, weighted combine
+            offsets, row_of_slot, slot_of_row = moe_ops.sort_by_expert(indices, self.num_experts)
+            counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
+            x_sorted = moe_ops.gather_rows(x_flat, slot_of_row, row_of_slot, k)
+            y = self.run_experts(x_sorted, counts)
+            return moe_ops.combine_rows(y, weights, row_of_slot, slot_of_row)
         flat_e = indices.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         token_of_row = order // k

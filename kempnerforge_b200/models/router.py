@@ -39,6 +39,16 @@ class SoftmaxTopKRouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         logits = self.gate(x)
+        from kempnerforge_b200.ops import moe_ops
+
+        if moe_ops.native_ok(logits, self.num_experts, self.top_k):
+            # one kernel: softmax, top-k, renormalised weights, counts, mean probabilities, z-loss
+            weights, indices, counts, pmean, z = moe_ops.route(logits, None, False, self.top_k)
+            self.expert_counts = counts.detach()
+            frac = counts / (x.shape[0] * self.top_k)
+            self.aux_loss = self.num_experts * (frac.detach() * pmean).sum()
+            self.z_loss = z
+            return weights.to(x.dtype), indices
         probs = torch.softmax(logits.float(), dim=-1)
         weights, indices = torch.topk(probs, self.top_k, dim=-1)
         weights = (weights / weights.sum(dim=-1, keepdim=True)).to(x.dtype)
@@ -92,10 +102,18 @@ class SigmoidTopKRouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         logits = self.gate(x)
-        scores = torch.sigmoid(logits.float() + self.expert_bias.float())
-        weights, indices = torch.topk(scores, self.top_k, dim=-1)
-        weights = (weights / weights.sum(dim=-1, keepdim=True)).to(x.dtype)
-        counts = _counts(indices, self.num_experts)
+        from kempnerforge_b200.ops import moe_ops
+
+        native = moe_ops.native_ok(logits, self.num_experts, self.top_k)
+        if native:
+            weights, indices, counts, smean, z = moe_ops.route(logits, self.expert_bias, True, self.top_k)
+            weights = weights.to(x.dtype)
+        else:
+            scores = torch.sigmoid(logits.float() + self.expert_bias.float())
+            weights, indices = torch.topk(scores, self.top_k, dim=-1)
+            weights = (weights / weights.sum(dim=-1, keepdim=True)).to(x.dtype)
+            counts = _counts(indices, self.num_experts)
+            smean = None
         self.expert_counts = counts.detach()
         util = counts / (x.shape[0] * self.top_k + 1e-8)
         if self.training:
@@ -104,11 +122,12 @@ class SigmoidTopKRouter(nn.Module):
                 nudge = self._effective_bias_rate() * (1.0 / self.num_experts - self.expert_ema.float())
                 self.expert_bias.add_(nudge.to(self.expert_bias.dtype))
         if self.sequence_aux_loss_weight > 0:
-            balance = self.num_experts * (util.detach() * scores.mean(dim=0)).sum()
+            mean_scores = smean if native else scores.mean(dim=0)
+            balance = self.num_experts * (util.detach() * mean_scores).sum()
             self.aux_loss = self.sequence_aux_loss_weight * balance
         else:
             self.aux_loss = torch.zeros((), device=x.device)
-        self.z_loss = torch.logsumexp(logits.float(), dim=-1).pow(2).mean()
+        self.z_loss = z if native else torch.logsumexp(logits.float(), dim=-1).pow(2).mean()
         return weights, indices
 
 

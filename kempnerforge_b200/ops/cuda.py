@@ -61,6 +61,12 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_fp8": [vp, vp, vp, i, i, i, ll, ll, i, i, i, vp, vp, i, i, vp],
         "kf_fp8_scale_bf16": [vp, ll, i, vp, vp, vp],
         "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
+        "kf_router_topk": [vp, i, vp, i, i, i, i, vp, vp, vp, vp, vp, vp],
+        "kf_moe_sort": [vp, i, i, vp, vp, vp, vp, vp],
+        "kf_moe_gather_bf16": [vp, vp, i, i, i, vp, vp],
+        "kf_moe_combine_bf16": [vp, vp, vp, i, i, i, vp, vp],
+        "kf_moe_combine_bwd_bf16": [vp, vp, vp, vp, i, i, i, vp, vp, vp],
+        "kf_grouped_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
@@ -403,6 +409,87 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
         "kf_attn_fwd_bf16",
     )
     return out, lse
+
+
+# --------------------------------------------------------------------------- mixture of experts
+def router_topk(logits: torch.Tensor, bias: torch.Tensor | None, sigmoid: bool, k: int):
+    """(weights fp32 (T, k), indices int64 (T, k), counts fp32 (E), prob_sum fp32 (E), sum of logsumexp² fp32 (1))."""
+    t, e = logits.shape
+    assert logits.is_contiguous() and logits.dtype in (torch.bfloat16, torch.float32)
+    idx = torch.empty((t, k), dtype=torch.int64, device=logits.device)
+    w = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+    acc = torch.zeros(2 * e + 1, dtype=torch.float32, device=logits.device)
+    b = bias.float().contiguous() if bias is not None else None
+    _check(lib().kf_router_topk(logits.data_ptr(), 0 if logits.dtype == torch.bfloat16 else 1,
+                                b.data_ptr() if b is not None else None, int(sigmoid), t, e, k, idx.data_ptr(),
+                                w.data_ptr(), acc.data_ptr(), acc[e:].data_ptr(), acc[2 * e:].data_ptr(), _stream()),
+           "kf_router_topk")
+    return w, idx, acc[:e], acc[e:2 * e], acc[2 * e:]
+
+
+def moe_sort(indices: torch.Tensor, num_experts: int):
+    """Stable sort of the (token, k) assignments by expert: (offsets int32 (E + 1), row_of_slot int32, slot_of_row int32)."""
+    flat = indices.reshape(-1)
+    assert flat.dtype == torch.int64 and flat.is_contiguous()
+    slots = flat.numel()
+    nb = (slots + 255) // 256
+    scratch = torch.empty(max(nb, 1) * num_experts, dtype=torch.int32, device=flat.device)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=flat.device)
+    row_of_slot = torch.empty(slots, dtype=torch.int32, device=flat.device)
+    slot_of_row = torch.empty(slots, dtype=torch.int32, device=flat.device)
+    _check(lib().kf_moe_sort(flat.data_ptr(), slots, num_experts, scratch.data_ptr(), offsets.data_ptr(),
+                             row_of_slot.data_ptr(), slot_of_row.data_ptr(), _stream()), "kf_moe_sort")
+    return offsets, row_of_slot, slot_of_row
+
+
+def moe_gather(x: torch.Tensor, slot_of_row: torch.Tensor, k: int) -> torch.Tensor:
+    rows, cols = slot_of_row.numel(), x.shape[1]
+    out = torch.empty((rows, cols), dtype=x.dtype, device=x.device)
+    _check(lib().kf_moe_gather_bf16(x.data_ptr(), slot_of_row.data_ptr(), rows, k, cols, out.data_ptr(), _stream()),
+           "kf_moe_gather_bf16")
+    return out
+
+
+def moe_combine(y: torch.Tensor, row_of_slot: torch.Tensor, w: torch.Tensor | None, tokens: int, k: int) -> torch.Tensor:
+    cols = y.shape[1]
+    out = torch.empty((tokens, cols), dtype=y.dtype, device=y.device)
+    _check(lib().kf_moe_combine_bf16(y.data_ptr(), row_of_slot.data_ptr(), w.data_ptr() if w is not None else None,
+                                     tokens, k, cols, out.data_ptr(), _stream()), "kf_moe_combine_bf16")
+    return out
+
+
+def moe_combine_bwd(dout: torch.Tensor, y: torch.Tensor, slot_of_row: torch.Tensor, w: torch.Tensor, k: int):
+    rows, cols = y.shape
+    dy = torch.empty_like(y)
+    dw = torch.empty(rows, dtype=torch.float32, device=y.device)
+    _check(lib().kf_moe_combine_bwd_bf16(dout.data_ptr(), y.data_ptr(), slot_of_row.data_ptr(), w.data_ptr(), rows, k, cols,
+                                         dy.data_ptr(), dw.data_ptr(), _stream()), "kf_moe_combine_bwd_bf16")
+    return dy, dw
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, b_mn: bool, out: torch.Tensor | None = None):
+    """Ragged grouped GEMM: rows ``offsets[e]:offsets[e+1]`` of ``a`` (rows, K) are multiplied by expert e's matrix.
+    ``b`` is (E, N, K) when ``b_mn`` is False and (E, K, N) when True; ``offsets`` is int32 (E + 1) on the device."""
+    rows, k = a.shape
+    e = b.shape[0]
+    n = b.shape[2] if b_mn else b.shape[1]
+    assert (b.shape[1] if b_mn else b.shape[2]) == k and b.is_contiguous() and a.stride(1) == 1
+    assert offsets.dtype == torch.int32 and offsets.numel() == e + 1
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=a.device)
+    _check(lib().kf_grouped_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), rows, e, n, k,
+                                      a.stride(0), out.stride(0), int(b_mn), sm_count(), _stream()),
+           "kf_grouped_gemm_bf16")
+    return out
+
+
+def grouped_gemm_supported(a: torch.Tensor, b: torch.Tensor, b_mn: bool) -> bool:
+    if getattr(lib(), "kf_grouped_gemm_bf16", None) is None or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        return False
+    k = a.shape[1]
+    n = b.shape[2] if b_mn else b.shape[1]
+    return (b.shape[0] <= 256 and k % 8 == 0 and n % 8 == 0 and (not b_mn or k % 64 == 0) and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and b.is_contiguous())
 
 
 def all_gather_gemm(x_shard: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None) -> torch.Tensor:

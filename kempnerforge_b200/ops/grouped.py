@@ -27,8 +27,56 @@ def stack_expert_weights(weights: list[torch.Tensor]) -> torch.Tensor:
     return torch.stack(weights)
 
 
+class _GroupedLinearFn(torch.autograd.Function):
+    """Ragged grouped Linear on the tcgen05 grouped GEMM: forward and input gradient native, weight gradient
+    (a reduction over each expert's ragged token range) through ``torch._grouped_mm``."""
+
+    @staticmethod
+    def forward(ctx, x, w, offsets, layout):
+        kc = _cuda_binding
+        ctx.save_for_backward(x, w, offsets)
+        ctx.layout = layout
+        return kc.grouped_gemm(x, w, offsets, b_mn=(layout == "kn"))
+
+    @staticmethod
+    def backward(ctx, dy):
+        kc = _cuda_binding
+        x, w, offsets = ctx.saved_tensors
+        layout = ctx.layout
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # 'nk': W_e is (N, K): dx = dy @ W_e reads W with the output dim (K) contiguous; 'kn': W_e is (K, N): dx = dy @ W_e^T
+            dx = kc.grouped_gemm(dy, w, offsets, b_mn=(layout == "nk"))
+        if ctx.needs_input_grad[1]:
+            offs = offsets[1:]
+            if layout == "kn":
+                dw = torch._grouped_mm(x.t(), dy, offs=offs)      # (E, K, N)
+            else:
+                dw = torch._grouped_mm(dy.t(), x, offs=offs)      # (E, N, K)
+        return dx, dw, None, None
+
+
+def _native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
+    from kempnerforge_b200.ops import functional as _F
+
+    if _F._FORCE_REF or not (x.is_cuda and x.dtype == torch.bfloat16 and w.dim() == 3 and w.is_contiguous()):
+        return False
+    kc = _cuda_binding
+    fwd_mn, bwd_mn = layout == "kn", layout == "nk"
+    n = w.shape[2] if fwd_mn else w.shape[1]
+    # the input-gradient GEMM reduces over n: its MN-major form needs n % 64
+    return (kc.available() and kc.grouped_gemm_supported(x, w, fwd_mn) and (not bwd_mn or n % 64 == 0)
+            and hasattr(torch, "_grouped_mm"))
+
+
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, layout: str) -> torch.Tensor:
     """y[rows of expert e] = x[rows of expert e] @ W_e, W_e = w[e] ('kn': (in, out)) or w[e].T ('nk')."""
+    if _native_ok(x, w, layout):
+        offsets = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=x.device)
+        offsets[1:] = counts.cumsum(0)
+        return _GroupedLinearFn.apply(x if x.is_contiguous() else x.contiguous(), w, offsets, layout)
     if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and hasattr(torch, "_grouped_mm"):
         offs = counts.cumsum(0).to(torch.int32)
         wb = w if layout == "kn" else w.transpose(1, 2)

@@ -277,3 +277,37 @@ def test_tensor_parallel_checkpoint_round_trip_and_reshard(tmp_path):
     CheckpointManager(cfg.checkpoint, single.model, single.optimizer).load(exclude_keys=["optimizer"])
     for name, p in single.model.named_parameters():
         assert torch.equal(p.detach(), full[name]), name
+
+
+# ------------------------------------------------------------------ combined meshes
+def _tp_dp_worker(rank, world, model_cfg, steps):
+    """tp = 2 inside, sharded data parallelism across: ranks (0, 1) and (2, 3) are the two TP groups."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_job(model_cfg, {"tp": 2, "dp_shard": world // 2}))
+    dp_rank, dp_size = t.dp_rank, t.dp_size
+    data = _batches(dp_size * steps)
+    traj = [t.train_step([data[s * dp_size + dp_rank]]) for s in range(steps)]
+    return traj, {n: (p.detach().clone(), getattr(p, "_kf_shard", None)) for n, p in t.model.named_parameters()}
+
+
+def test_tensor_parallel_times_data_parallel_matches_single_process():
+    steps = 2
+    data = _batches(2 * steps)
+    ref_traj, ref_params = _single_process_reference(TINY, [[data[2 * s], data[2 * s + 1]] for s in range(steps)])
+    results = run_ranks(_tp_dp_worker, 4, TINY, steps)
+    for r, (traj, _) in enumerate(results):
+        for s in range(steps):
+            # every rank reports the loss of its own micro-batch; the mean over the two DP ranks is the reference loss
+            pass
+    for s in range(steps):
+        mean_loss = 0.5 * (results[0][0][s]["loss"] + results[2][0][s]["loss"])
+        assert _close(mean_loss, ref_traj[s]["loss"], 1e-3), (s, mean_loss, ref_traj[s]["loss"])
+        assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 2e-3)
+    for name, want in ref_params.items():
+        t0, spec = results[0][1][name]
+        t1 = results[1][1][name][0]
+        full = torch.cat([t0, t1], dim=spec[1]) if spec is not None else t0
+        assert _params_close(full, want), name
+        # the second TP group holds the same weights as the first
+        assert torch.equal(results[2][1][name][0], t0), name

@@ -1,0 +1,96 @@
+"""End-to-end runs of the command-line entry points in child processes (CPU): train -> checkpoint -> eval /
+generate, SIGTERM -> emergency checkpoint -> automatic resume.  Mirrors the reference's smoke pipelines
+(tests/smoke/test_smoke.py) at toy size."""
+
+import json
+import os
+import signal
+import subprocess
+import sys
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = ["--model.dim=64", "--model.n_layers=2", "--model.n_heads=4", "--model.n_kv_heads=2", "--model.vocab_size=256",
+        "--model.max_seq_len=64", "--train.batch_size=2", "--train.seq_len=32", "--train.mixed_precision=fp32",
+        "--train.compile_model=false", "--metrics.log_interval=1", "--optimizer.lr=1e-3", "--scheduler.warmup_steps=0",
+        "--metrics.enable_wandb=false", "--metrics.enable_tensorboard=false"]
+
+
+def _env():
+    return dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1")
+
+
+def _train(args, **kw):
+    cmd = [sys.executable, os.path.join(ROOT, "scripts", "train.py"), os.path.join(ROOT, "configs", "train", "debug.toml"),
+           *TINY, *args]
+    return subprocess.run(cmd, capture_output=True, text=True, env=_env(), timeout=600, cwd=ROOT, **kw)
+
+
+def _steps_logged(text: str) -> list[int]:
+    import re
+
+    return [int(m) for m in re.findall(r"\[step (\d+)\]", text)]
+
+
+def test_train_checkpoint_eval_generate_pipeline(tmp_path):
+    ckpt = str(tmp_path / "ckpt")
+    r = _train([f"--checkpoint.dir={ckpt}", "--checkpoint.interval=4", "--train.max_steps=8"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    out = r.stdout + r.stderr
+    assert 8 in _steps_logged(out)
+    assert os.path.isdir(os.path.join(ckpt, "step_8")) and os.path.exists(os.path.join(ckpt, "latest"))
+    meta = json.load(open(os.path.join(ckpt, "step_8", "metadata.json")))
+    assert meta["step"] == 8
+    # resume: two more steps continue from step 8, not from 0
+    r2 = _train([f"--checkpoint.dir={ckpt}", "--checkpoint.interval=100", "--train.max_steps=10"])
+    assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-2000:]
+    steps = _steps_logged(r2.stdout + r2.stderr)
+    assert steps and min(steps) >= 9 and max(steps) == 10, steps
+    # the evaluation script reads the same checkpoint and a small token shard
+    import numpy as np
+
+    data_dir = tmp_path / "eval_tokens"
+    data_dir.mkdir()
+    np.save(data_dir / "shard_0.npy", np.random.default_rng(0).integers(0, 256, size=4096, dtype=np.uint16))
+    ev = subprocess.run([sys.executable, os.path.join(ROOT, "scripts", "eval.py"),
+                         os.path.join(ROOT, "configs", "train", "debug.toml"), *TINY, f"--checkpoint.load_path={ckpt}/latest",
+                         f"--eval.dataset_path={data_dir}", "--eval.steps=2"],
+                        capture_output=True, text=True, env=_env(), timeout=600, cwd=ROOT)
+    assert ev.returncode == 0, ev.stdout[-2000:] + ev.stderr[-2000:]
+    assert "loss" in (ev.stdout + ev.stderr).lower()
+
+
+def test_sigterm_writes_emergency_checkpoint_and_resumes(tmp_path):
+    ckpt = str(tmp_path / "ckpt")
+    cmd = [sys.executable, os.path.join(ROOT, "scripts", "train.py"), os.path.join(ROOT, "configs", "train", "debug.toml"),
+           *TINY, f"--checkpoint.dir={ckpt}", "--checkpoint.interval=100000", "--train.max_steps=100000"]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=_env(), cwd=ROOT)
+    seen = ""
+    deadline = time.time() + 300
+    try:
+        while time.time() < deadline:  # wait until the loop is really running
+            line = proc.stdout.readline()
+            if not line:
+                break
+            seen += line
+            if "[step 3]" in line:
+                break
+        assert "[step 3]" in seen, seen[-3000:]
+        proc.send_signal(signal.SIGTERM)
+        rest, _ = proc.communicate(timeout=300)
+        seen += rest
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert proc.returncode == 0, seen[-3000:]
+    assert "emergency checkpoint" in seen
+    saved = sorted(d for d in os.listdir(ckpt) if d.startswith("step_"))
+    assert saved, os.listdir(ckpt)
+    last_step = int(saved[-1].split("_")[1])
+    assert last_step >= 3 and os.path.exists(os.path.join(ckpt, "latest"))
+    r = _train([f"--checkpoint.dir={ckpt}", "--checkpoint.interval=100000", f"--train.max_steps={last_step + 2}"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    steps = _steps_logged(r.stdout + r.stderr)
+    assert steps and min(steps) == last_step + 1, (last_step, steps)

@@ -443,3 +443,173 @@ def test_attention_autograd_function_native_policy(native_lib, monkeypatch):
     _, rq, rk, rv = _attn_reference_grads(q, k, v, dout, True)
     for got, want in ((q.grad, rq), (k.grad, rk), (v.grad, rv)):
         assert ((got.float() - want).norm() / want.norm()) < 2e-2
+
+
+# --------------------------------------------------------------------------- ragged grouped GEMM (MoE experts)
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [1000, 24], [0, 0, 513]])
+def test_grouped_gemm_forward_backward(native_lib, counts, layout):
+    from kempnerforge_b200.ops import grouped
+
+    torch.manual_seed(0)
+    e, k, n = len(counts), 192, 320
+    rows = sum(counts)
+    x = _rand(rows, k).requires_grad_(True)
+    w = (_rand(e, k, n, scale=0.05) if layout == "kn" else _rand(e, n, k, scale=0.05)).requires_grad_(True)
+    cnt = torch.tensor(counts, device="cuda")
+    y = grouped.grouped_linear(x, w, cnt, layout)
+    g = _rand(rows, n)
+    y.backward(g)
+    assert native_lib.read_status() == 0
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    outs, start = [], 0
+    for i, c in enumerate(counts):
+        we = wf[i] if layout == "kn" else wf[i].t()
+        outs.append(xf[start:start + c] @ we)
+        start += c
+    want = torch.cat(outs)
+    want.backward(g.float())
+    _close(y, want)
+    _close(x.grad, xf.grad)
+    _close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
+
+
+# --------------------------------------------------------------------------- MoE routing / sort / gather / combine
+@pytest.mark.parametrize("sigmoid", [False, True])
+@pytest.mark.parametrize("shape", [(64, 8, 2), (1000, 64, 6), (333, 160, 8)])
+def test_router_topk_matches_torch(native_lib, shape, sigmoid):
+    from kempnerforge_b200.ops import moe_ops
+
+    t, e, k = shape
+    torch.manual_seed(1)
+    logits = (torch.randn(t, e, device="cuda") * 2).requires_grad_(True)
+    bias = (torch.randn(e, device="cuda") * 0.1) if sigmoid else None
+    w, idx, counts, mean, z = moe_ops.route(logits, bias, sigmoid, k)
+    lf = logits.detach().clone().requires_grad_(True)
+    scores = torch.sigmoid(lf + bias) if sigmoid else torch.softmax(lf, dim=-1)
+    rw, ridx = torch.topk(scores, k, dim=-1)
+    rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(idx.sort(dim=1).values, ridx.sort(dim=1).values)
+    assert torch.equal(idx, ridx)
+    assert torch.allclose(w, rw, atol=1e-5)
+    assert torch.equal(counts, torch.bincount(ridx.reshape(-1), minlength=e).float())
+    assert torch.allclose(mean, scores.mean(0), atol=1e-5)
+    rz = torch.logsumexp(lf, dim=-1).pow(2).mean()
+    assert torch.allclose(z, rz, rtol=1e-4)
+    gw = torch.randn_like(w)
+    gm = torch.randn(e, device="cuda")
+    (w * gw).sum().add((mean * gm).sum()).add(z * 0.3).backward()
+    (rw * gw).sum().add((scores.mean(0) * gm).sum()).add(rz * 0.3).backward()
+    assert torch.allclose(logits.grad, lf.grad, atol=2e-5, rtol=1e-3)
+
+
+def test_moe_sort_gather_combine_match_torch(native_lib):
+    from kempnerforge_b200.ops import moe_ops
+
+    torch.manual_seed(2)
+    t, e, k, d = 777, 16, 4, 256
+    idx = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(t)])
+    offsets, row_of_slot, slot_of_row = moe_ops.sort_by_expert(idx, e)
+    order = torch.argsort(idx.reshape(-1), stable=True)
+    assert torch.equal(slot_of_row.long(), order)
+    assert torch.equal(offsets[1:].long(), torch.bincount(idx.reshape(-1), minlength=e).cumsum(0))
+    x = _rand(t, d).requires_grad_(True)
+    w = torch.rand(t, k, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    xs = moe_ops.gather_rows(x, slot_of_row, row_of_slot, k)
+    assert torch.equal(xs, x.detach()[order // k])
+    y = (xs.float() * 1.5).to(torch.bfloat16)          # stand-in for the expert computation, keeps the graph
+    out = moe_ops.combine_rows(y, w, row_of_slot, slot_of_row)
+    g = _rand(t, d)
+    out.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = (xr[order // k] * 1.5).to(torch.bfloat16).float()
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device="cuda")
+    want = (yr[inv].view(t, k, d) * wr[:, :, None]).sum(1)
+    want.backward(g.float())
+    _close(out, want)
+    _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
+    _close(w.grad, wr.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_moe_layer_native_matches_reference_path(native_lib):
+    from kempnerforge_b200.models.moe import build_moe
+    from kempnerforge_b200.ops import functional as F
+
+    torch.manual_seed(3)
+    layer = build_moe(256, 512, 8, 2, packed_experts=True).to(device="cuda", dtype=torch.bfloat16)
+    x = _rand(2, 192, 256)
+    xa = x.clone().requires_grad_(True)
+    ya = layer(xa)
+    ya.float().sum().backward()
+    ga = {n: p.grad.clone() for n, p in layer.named_parameters() if p.grad is not None}
+    layer.zero_grad()
+    with F.force_reference():
+        xb = x.clone().requires_grad_(True)
+        yb = layer(xb)
+        yb.float().sum().backward()
+    assert native_lib.read_status() == 0
+    _close(ya, yb, rtol=3e-2, atol=3e-2)
+    _close(xa.grad, xb.grad, rtol=5e-2, atol=5e-2)
+    for n, p in layer.named_parameters():
+        if p.grad is not None and n in ga:
+            _close(ga[n], p.grad, rtol=6e-2, atol=6e-2)
+
+
+# --------------------------------------------------------------------------- end-to-end variants on one GPU
+def _tiny_job(**over):
+    from kempnerforge_b200.config import config_from_dict
+
+    cfg = {
+        "model": dict(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=512, ffn_hidden_dim=512, max_seq_len=128),
+        "train": dict(batch_size=4, seq_len=128, max_steps=20, mixed_precision="bf16", seed=0),
+        "optimizer": dict(lr=2e-3), "scheduler": dict(name="constant", warmup_steps=0),
+        "metrics": dict(log_interval=1000),
+    }
+    for section, vals in over.items():
+        cfg.setdefault(section, {}).update(vals)
+    return config_from_dict(cfg)
+
+
+def _overfit(trainer, steps=12):
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, 512, (4, 129), generator=g)
+    batch = {"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+    return [trainer.train_step([batch])["loss"] for _ in range(steps)]
+
+
+def test_fp8_training_learns(native_lib):
+    from kempnerforge_b200.ops import fp8
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_tiny_job(train=dict(mixed_precision="fp8")), init_dist=False)
+    tagged = [n for n, p in t.model.named_parameters() if fp8.is_fp8_weight(p)]
+    assert any("q_proj" in n for n in tagged) and any("down_proj" in n for n in tagged)
+    assert not any("output_head" in n or "embedding" in n for n in tagged)
+    losses = _overfit(t)
+    assert native_lib.read_status() == 0
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
+
+
+@pytest.mark.parametrize("router", ["softmax_topk", "sigmoid_topk"])
+def test_moe_training_learns_on_native_kernels(native_lib, router):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_tiny_job(model=dict(num_experts=4, moe_top_k=2, moe_router=router, moe_packed_experts=True)),
+                init_dist=False)
+    losses = _overfit(t)
+    assert native_lib.read_status() == 0
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
+
+
+def test_native_attention_policy_in_training(native_lib, monkeypatch):
+    """KF_ATTN=native: the tcgen05 attention kernels (forward and backward) inside the fused block train a model."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    monkeypatch.setenv("KF_ATTN", "native")
+    cfg = _tiny_job(model=dict(dim=512, n_heads=4, n_kv_heads=2, ffn_hidden_dim=1024),
+                    train=dict(activation_checkpointing="full"))
+    t = Trainer(cfg, init_dist=False)
+    losses = _overfit(t)
+    assert native_lib.read_status() == 0
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
