@@ -1,0 +1,6 @@
+"""Import path kept for code written against the reference layout (kempnerforge/config/adapter.py):
+the classes live in ``config/vlm.py``."""
+
+from kempnerforge_b200.config.vlm import AdapterConfig  # noqa: F401
+
+__all__ = ['AdapterConfig']

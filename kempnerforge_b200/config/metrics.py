@@ -1,0 +1,6 @@
+"""Import path kept for code written against the reference layout (kempnerforge/config/metrics.py):
+the classes live in ``config/sections.py``."""
+
+from kempnerforge_b200.config.sections import MetricsConfig  # noqa: F401
+
+__all__ = ['MetricsConfig']

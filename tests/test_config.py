@@ -223,3 +223,18 @@ def test_optimizer_scheduler_validation():
         SchedulerConfig(min_lr_ratio=2)
     with pytest.raises(ValueError):
         SchedulerConfig(wsd_decay_type="exp")
+
+
+def test_reference_import_paths_resolve():
+    """Code written against the reference's module layout finds the same objects here."""
+    from kempnerforge_b200.config.checkpoint import AsyncCheckpointMode, CheckpointConfig  # noqa: F401
+    from kempnerforge_b200.config.model import ModelConfig as M2
+    from kempnerforge_b200.config.schema import JobConfig, ModelConfig  # noqa: F401
+    from kempnerforge_b200.distributed import clip_grad_norm_, get_dp_info, init_distributed  # noqa: F401
+    from kempnerforge_b200.distributed.parallel import build_parallel_model  # noqa: F401
+    from kempnerforge_b200.distributed.utils import clip_grad_norm_ as c2
+    from kempnerforge_b200.model.attention import Attention, KVCache  # noqa: F401
+    from kempnerforge_b200.model.transformer import Transformer
+    from kempnerforge_b200.models.transformer import Transformer as T2
+
+    assert M2 is ModelConfig and Transformer is T2 and c2 is clip_grad_norm_
