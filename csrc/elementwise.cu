@@ -714,3 +714,84 @@ extern "C" int kf_sumsq_noalloc(const void* x, long long n, int dt, void* out, i
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
+
+// ------------------------------------------------------------------ Lion and schedule-free AdamW updates
+// One launch per parameter tensor, all tensors of one element type (bf16 or fp32), fp32 arithmetic.
+// Same update rules as the reference's Python loops (kempnerforge/training/optimizer.py:76-114,177-246).
+namespace kf {
+template <typename T>
+__device__ __forceinline__ float ld_f(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ld_f<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld_f<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T>
+__device__ __forceinline__ void st_f(T* p, long long i, float v);
+template <>
+__device__ __forceinline__ void st_f<float>(float* p, long long i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void st_f<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void kf_lion_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, long long n, float lr,
+                               float b1, float b2, float wd) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = ld_f(g, i), mi = ld_f(m, i);
+    const float c = b1 * mi + (1.f - b1) * gi;
+    const float dir = c > 0.f ? 1.f : (c < 0.f ? -1.f : 0.f);
+    st_f(p, i, ld_f(p, i) * (1.f - lr * wd) - lr * dir);
+    st_f(m, i, b2 * mi + (1.f - b2) * gi);
+  }
+}
+
+// y (the parameter the model reads), z (base iterate), x (averaged iterate), v (second moment)
+template <typename T>
+__global__ void kf_sf_adamw_kernel(T* __restrict__ y, const T* __restrict__ g, T* __restrict__ z, T* __restrict__ v,
+                                   T* __restrict__ x, long long n, float lr, float b1, float b2, float eps, float wd,
+                                   float bc2, float ck, int first) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = ld_f(g, i);
+    const float vi = b2 * ld_f(v, i) + (1.f - b2) * gi * gi;
+    float zi = ld_f(z, i) - lr * gi / (sqrtf(vi / bc2) + eps);
+    zi *= (1.f - lr * wd);
+    const float xi = first ? zi : ld_f(x, i) + ck * (zi - ld_f(x, i));
+    st_f(v, i, vi);
+    st_f(z, i, zi);
+    st_f(x, i, xi);
+    st_f(y, i, zi + b1 * (xi - zi));
+  }
+}
+}  // namespace kf
+
+extern "C" int kf_lion(void* p, const void* g, void* m, long long n, int dt, float lr, float b1, float b2, float wd,
+                       void* stream) {
+  using namespace kf;
+  if (n <= 0) return 0;
+  const int blocks = grid_for(n, 256, 2368);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dt == 0)
+    kf_lion_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)p, (const __nv_bfloat16*)g, (__nv_bfloat16*)m, n, lr, b1, b2, wd);
+  else if (dt == 1)
+    kf_lion_kernel<float><<<blocks, 256, 0, st>>>((float*)p, (const float*)g, (float*)m, n, lr, b1, b2, wd);
+  else
+    return 4;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+extern "C" int kf_sf_adamw(void* y, const void* g, void* z, void* v, void* x, long long n, int dt, float lr, float b1,
+                           float b2, float eps, float wd, float bc2, float ck, int first, void* stream) {
+  using namespace kf;
+  if (n <= 0) return 0;
+  const int blocks = grid_for(n, 256, 2368);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dt == 0)
+    kf_sf_adamw_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)g, (__nv_bfloat16*)z,
+                                                             (__nv_bfloat16*)v, (__nv_bfloat16*)x, n, lr, b1, b2, eps, wd, bc2, ck, first);
+  else if (dt == 1)
+    kf_sf_adamw_kernel<float><<<blocks, 256, 0, st>>>((float*)y, (const float*)g, (float*)z, (float*)v, (float*)x, n, lr, b1, b2, eps, wd, bc2, ck, first);
+  else
+    return 4;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

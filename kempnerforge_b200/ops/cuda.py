@@ -61,6 +61,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_fp8": [vp, vp, vp, i, i, i, ll, ll, i, i, i, vp, vp, i, i, vp],
         "kf_fp8_scale_bf16": [vp, ll, i, vp, vp, vp],
         "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
+        "kf_lion": [vp, vp, vp, ll, i, f, f, f, f, vp],
+        "kf_sf_adamw": [vp, vp, vp, vp, vp, ll, i, f, f, f, f, f, f, f, i, vp],
         "kf_router_topk": [vp, i, vp, i, i, i, i, vp, vp, vp, vp, vp, vp],
         "kf_moe_sort": [vp, i, i, vp, vp, vp, vp, vp],
         "kf_moe_gather_bf16": [vp, vp, i, i, i, vp, vp],
@@ -409,6 +411,29 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
         "kf_attn_fwd_bf16",
     )
     return out, lse
+
+
+# --------------------------------------------------------------------------- Lion / schedule-free AdamW
+def _same_flat(*ts: torch.Tensor) -> bool:
+    d = ts[0].dtype
+    return d in _DT and all(t.is_cuda and t.dtype == d and t.is_contiguous() and t.numel() == ts[0].numel() for t in ts)
+
+
+def lion_step(p, g, m, lr: float, b1: float, b2: float, wd: float) -> bool:
+    """In-place Lion update of one tensor; False when the tensors do not qualify (mixed dtypes, strided)."""
+    if getattr(lib(), "kf_lion", None) is None or not _same_flat(p, g, m):
+        return False
+    _check(lib().kf_lion(p.data_ptr(), g.data_ptr(), m.data_ptr(), p.numel(), _DT[p.dtype], lr, b1, b2, wd, _stream()), "kf_lion")
+    return True
+
+
+def sf_adamw_step(y, g, z, v, x, lr, b1, b2, eps, wd, bc2, ck, first: bool) -> bool:
+    """In-place schedule-free AdamW update: y is the tensor the model reads, z / x the base and averaged iterates."""
+    if getattr(lib(), "kf_sf_adamw", None) is None or not _same_flat(y, g, z, v, x):
+        return False
+    _check(lib().kf_sf_adamw(y.data_ptr(), g.data_ptr(), z.data_ptr(), v.data_ptr(), x.data_ptr(), y.numel(), _DT[y.dtype],
+                             lr, b1, b2, eps, wd, bc2, ck, int(first), _stream()), "kf_sf_adamw")
+    return True
 
 
 # --------------------------------------------------------------------------- mixture of experts

@@ -32,6 +32,12 @@ from kempnerforge_b200.ops import ref
 log = logging.getLogger(__name__)
 
 
+def _native():
+    from kempnerforge_b200.ops import cuda as kc
+
+    return kc
+
+
 def _local(t: torch.Tensor) -> torch.Tensor:
     """Local shard of a DTensor, or the tensor itself."""
     return t.to_local() if hasattr(t, "to_local") else t
@@ -121,6 +127,8 @@ class Lion(torch.optim.Optimizer):
                 if "exp_avg" not in state:
                     state["exp_avg"] = torch.zeros_like(p)
                 pl, gl, ml = _local(p), _local(p.grad), _local(state["exp_avg"])
+                if pl.is_cuda and _native().lion_step(pl, gl, ml, lr, b1, b2, wd):
+                    continue  # one fused kernel did the update
                 direction = torch.lerp(gl.to(ml.dtype), ml, b1).sign_()
                 if wd:
                     pl.mul_(1.0 - lr * wd)
@@ -182,6 +190,17 @@ class ScheduleFreeAdamW(torch.optim.Optimizer):
                     st["v"] = torch.zeros_like(p)
                     st["weight_sum"] = 0.0
                 z, v, g = _local(st["z"]), _local(st["v"]), _local(p.grad)
+                if z.is_cuda:
+                    first = "x" not in st
+                    if first:
+                        st["x"] = torch.empty_like(st["z"])
+                    wsum = float(st["weight_sum"]) + w_k
+                    if _native().sf_adamw_step(_local(p), g, z, v, _local(st["x"]), lr, b1, b2, eps, wd, 1.0 - b2**k,
+                                               w_k / wsum, first):
+                        st["weight_sum"], st["k"] = wsum, k
+                        continue
+                    if first:
+                        del st["x"]
                 v.mul_(b2).addcmul_(g, g, value=1.0 - b2)
                 z.addcdiv_(g, (v / (1.0 - b2**k)).sqrt_().add_(eps), value=-lr)
                 if wd > 0:

@@ -613,3 +613,29 @@ def test_native_attention_policy_in_training(native_lib, monkeypatch):
     losses = _overfit(t)
     assert native_lib.read_status() == 0
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
+
+
+@pytest.mark.parametrize("name", ["lion", "schedule_free_adamw"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_lion_and_schedule_free_kernels_match_python_rules(native_lib, name, dtype):
+    """The fused update kernels against the same optimizers running their PyTorch formulas on the CPU."""
+    from kempnerforge_b200.config import OptimizerConfig
+    from kempnerforge_b200.training.optimizer import build_optimizer
+
+    torch.manual_seed(0)
+    ref_m = torch.nn.Linear(64, 96, bias=True).to(dtype)
+    dev_m = torch.nn.Linear(64, 96, bias=True).to(dtype)
+    dev_m.load_state_dict(ref_m.state_dict())
+    dev_m = dev_m.cuda()
+    cfg = OptimizerConfig(name=name, lr=1e-2, weight_decay=0.1)
+    ro, do = build_optimizer(ref_m, cfg), build_optimizer(dev_m, cfg)
+    for step in range(4):
+        g = torch.Generator().manual_seed(step)
+        for (pr, pd) in zip(ref_m.parameters(), dev_m.parameters()):
+            grad = torch.randn(pr.shape, generator=g).to(dtype)
+            pr.grad, pd.grad = grad.clone(), grad.cuda()
+        ro.step()
+        do.step()
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    for pr, pd in zip(ref_m.parameters(), dev_m.parameters()):
+        assert torch.allclose(pr.float(), pd.float().cpu(), atol=tol, rtol=tol), (pr.float() - pd.float().cpu()).abs().max()
