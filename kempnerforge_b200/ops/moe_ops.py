@@ -32,7 +32,8 @@ class _RouterFn(torch.autograd.Function):
         logits = logits.contiguous()
         w, idx, counts, prob_sum, lse_sq = kc.router_topk(logits, bias, sigmoid, k)
         t = logits.shape[0]
-        ctx.save_for_backward(logits, bias if bias is not None else torch.empty(0), idx, w)
+        # the sigmoid router nudges its bias in place right after routing: keep a private copy for the backward
+        ctx.save_for_backward(logits, bias.detach().clone() if bias is not None else torch.empty(0), idx, w)
         ctx.sigmoid, ctx.has_bias = sigmoid, bias is not None
         ctx.mark_non_differentiable(idx, counts)
         return w, idx, counts, prob_sum / t, lse_sq.reshape(()) / t
