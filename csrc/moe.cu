@@ -346,3 +346,164 @@ int kf_moe_combine_bwd_bf16(const void* dout, const void* y, const void* slot_of
 }
 
 }  // extern "C"
+
+// ==================================================================== expert-parallel dispatch over peer memory
+// Rows travel between the ranks of an expert-parallel group with plain peer stores (NVLink / NVSwitch); no
+// library all-to-all, no host-side split sizes.
+//
+//   kf_ep_put      source side.  Rows sorted by GLOBAL expert (optionally gathered from token rows on the fly) are
+//                  stored into the destination rank's receive window [source][cap][cols]; the per-expert counts
+//                  and the source's base row of that destination are stored into the destination's table.
+//   kf_ep_layout   destination side, one block: from the count table build the expert-major layout
+//                  (offsets per local expert, first compact row of every (source, expert) chunk).
+//   kf_ep_compact  destination side: windows -> expert-major rows (the A operand of the grouped GEMM).
+//   kf_ep_return   destination side: expert-major rows -> the SOURCE's return buffer, at the row the source had
+//                  them in its own sorted order.
+// Between put and layout, and between return and the source's use of its return buffer, the ranks meet in a
+// bounded symmetric-memory barrier on the stream (host side).  Replaces the count / token / expert-id / combine
+// all-to-alls and their three host synchronisations (kempnerforge/distributed/expert_parallel.py:93-309).
+namespace kf {
+namespace ep {
+
+constexpr int MAX_PEERS = 8;
+struct Peers {
+  void* p[MAX_PEERS];
+};
+
+// table layout on every rank, per source s: [n_local counts][1 base row] -> stride n_local + 1 ints
+__global__ void kf_ep_put(const __nv_bfloat16* __restrict__ src, const int* __restrict__ slot_of_row, int k,
+                          const int* __restrict__ offsets_g, int n_local, int ep, int me, int cols, long long cap,
+                          Peers windows, Peers tables) {
+  const int total = offsets_g[ep * n_local];
+  // counts and base rows (a few ints per destination)
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < ep * (n_local + 1); i += blockDim.x) {
+      const int d = i / (n_local + 1), j = i - d * (n_local + 1);
+      int* tab = reinterpret_cast<int*>(tables.p[d]) + me * (n_local + 1);
+      tab[j] = j < n_local ? offsets_g[d * n_local + j + 1] - offsets_g[d * n_local + j] : offsets_g[d * n_local];
+    }
+  }
+  const int vec = cols / 8;
+  const int lane_vecs = blockDim.x;
+  for (int r = blockIdx.x; r < total; r += gridDim.x) {
+    // destination rank: the one whose expert range contains sorted row r
+    int d = 0;
+    while (d + 1 < ep && offsets_g[(d + 1) * n_local] <= r) ++d;
+    const int pos = r - offsets_g[d * n_local];
+    const int srow = slot_of_row ? slot_of_row[r] / k : r;
+    const __nv_bfloat16* s = src + size_t(srow) * cols;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(windows.p[d]) + (size_t(me) * cap + pos) * cols;
+    for (int c = threadIdx.x; c < vec; c += lane_vecs)
+      *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(s + c * 8);
+  }
+}
+
+// outputs: offsets_l int32 [n_local + 1]; chunk_dst int32 [ep][n_local] (first compact row of chunk (s, j));
+// chunk_src int32 [ep][n_local] (first window row of chunk (s, j)); total_rows int32 [1]
+__global__ void kf_ep_layout(const int* __restrict__ table, int ep, int n_local, int* __restrict__ offsets_l,
+                             int* __restrict__ chunk_dst, int* __restrict__ chunk_src, int* __restrict__ total_rows) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int acc = 0;
+  for (int j = 0; j < n_local; ++j) {
+    offsets_l[j] = acc;
+    for (int s = 0; s < ep; ++s) {
+      chunk_dst[s * n_local + j] = acc;
+      acc += table[s * (n_local + 1) + j];
+    }
+  }
+  offsets_l[n_local] = acc;
+  total_rows[0] = acc;
+  for (int s = 0; s < ep; ++s) {
+    int w = 0;
+    for (int j = 0; j < n_local; ++j) {
+      chunk_src[s * n_local + j] = w;
+      w += table[s * (n_local + 1) + j];
+    }
+  }
+}
+
+// one block per (chunk, row slice): copies window rows of chunk (s, j) to their compact position (to_compact = 1)
+// or compact rows back into a peer's return buffer at the source's own sorted row (to_compact = 0)
+__global__ void kf_ep_move(const __nv_bfloat16* __restrict__ window, __nv_bfloat16* __restrict__ compact,
+                           const int* __restrict__ table, const int* __restrict__ chunk_dst,
+                           const int* __restrict__ chunk_src, int ep, int n_local, int cols, long long cap, int to_compact,
+                           int my_local_start, Peers returns) {
+  const int chunk = blockIdx.y;
+  const int s = chunk / n_local, j = chunk - s * n_local;
+  const int count = table[s * (n_local + 1) + j];
+  const int base_in_source = table[s * (n_local + 1) + n_local];  // source's sorted row of its first row for this rank
+  const int vec = cols / 8;
+  for (int r = blockIdx.x; r < count; r += gridDim.x) {
+    const size_t crow = size_t(chunk_dst[chunk]) + r;
+    const int wrow = chunk_src[chunk] + r;
+    if (to_compact) {
+      const __nv_bfloat16* src = window + (size_t(s) * cap + wrow) * cols;
+      __nv_bfloat16* dst = compact + crow * cols;
+      for (int c = threadIdx.x; c < vec; c += blockDim.x)
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
+    } else {
+      const __nv_bfloat16* src = compact + crow * cols;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(returns.p[s]) + (size_t(base_in_source) + wrow) * cols;
+      for (int c = threadIdx.x; c < vec; c += blockDim.x)
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
+    }
+  }
+}
+
+}  // namespace ep
+}  // namespace kf
+
+extern "C" {
+
+// Source side of the dispatch.  src: token rows (slot_of_row given: row r comes from token slot_of_row[r] / k) or
+// rows already in sorted order (slot_of_row null).  offsets_g: int32 [ep * n_local + 1] of the global-expert sort.
+// window_ptrs / table_ptrs: ep device addresses each (every rank's receive windows [ep][cap][cols] bf16 and count
+// table [ep][n_local + 1] int32).  max_rows: upper bound of the number of sorted rows (grid sizing only).
+int kf_ep_put_bf16(const void* src, const void* slot_of_row, int k, const void* offsets_g, int n_local, int ep, int me,
+                   int cols, long long cap, const long long* window_ptrs, const long long* table_ptrs, int max_rows,
+                   void* stream) {
+  using namespace kf::ep;
+  if (ep < 1 || ep > MAX_PEERS || (cols & 7)) return 5;
+  Peers w, t;
+  for (int i = 0; i < MAX_PEERS; ++i) {
+    w.p[i] = i < ep ? reinterpret_cast<void*>(window_ptrs[i]) : nullptr;
+    t.p[i] = i < ep ? reinterpret_cast<void*>(table_ptrs[i]) : nullptr;
+  }
+  int blocks = max_rows < 1 ? 1 : (max_rows < 148 * 16 ? max_rows : 148 * 16);
+  kf_ep_put<<<blocks, 128, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(src),
+                                                     reinterpret_cast<const int*>(slot_of_row), k,
+                                                     reinterpret_cast<const int*>(offsets_g), n_local, ep, me, cols, cap, w, t);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+int kf_ep_layout(const void* table, int ep, int n_local, void* offsets_l, void* chunk_dst, void* chunk_src,
+                 void* total_rows, void* stream) {
+  using namespace kf::ep;
+  kf_ep_layout<<<1, 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<const int*>(table), ep, n_local,
+                                                  reinterpret_cast<int*>(offsets_l), reinterpret_cast<int*>(chunk_dst),
+                                                  reinterpret_cast<int*>(chunk_src), reinterpret_cast<int*>(total_rows));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// to_compact = 1: windows -> compact (local copy).  to_compact = 0: compact -> the sources' return buffers
+// (return_ptrs: ep device addresses of every rank's [max sorted rows][cols] bf16 return buffer).
+int kf_ep_move_bf16(const void* window, void* compact, const void* table, const void* chunk_dst, const void* chunk_src,
+                    int ep, int n_local, int cols, long long cap, int to_compact, const long long* return_ptrs,
+                    void* stream) {
+  using namespace kf::ep;
+  if (ep < 1 || ep > MAX_PEERS || (cols & 7)) return 5;
+  Peers r;
+  for (int i = 0; i < MAX_PEERS; ++i) r.p[i] = (i < ep && return_ptrs) ? reinterpret_cast<void*>(return_ptrs[i]) : nullptr;
+  dim3 grid(64, ep * n_local);
+  kf_ep_move<<<grid, 128, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(window),
+                                                    reinterpret_cast<__nv_bfloat16*>(compact),
+                                                    reinterpret_cast<const int*>(table), reinterpret_cast<const int*>(chunk_dst),
+                                                    reinterpret_cast<const int*>(chunk_src), ep, n_local, cols, cap, to_compact,
+                                                    0, r);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // extern "C"

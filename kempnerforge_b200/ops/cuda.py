@@ -63,6 +63,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_fp8_cast_bf16": [vp, i, i, ll, vp, i, vp, ll, vp, ll, vp],
         "kf_lion": [vp, vp, vp, ll, i, f, f, f, f, vp],
         "kf_sf_adamw": [vp, vp, vp, vp, vp, ll, i, f, f, f, f, f, f, f, i, vp],
+        "kf_ep_put_bf16": [vp, vp, i, vp, i, i, i, i, ll, vp, vp, i, vp],
+        "kf_ep_layout": [vp, i, i, vp, vp, vp, vp, vp],
+        "kf_ep_move_bf16": [vp, vp, vp, vp, vp, i, i, i, ll, i, vp, vp],
         "kf_router_topk": [vp, i, vp, i, i, i, i, vp, vp, vp, vp, vp, vp],
         "kf_moe_sort": [vp, i, i, vp, vp, vp, vp, vp],
         "kf_moe_gather_bf16": [vp, vp, i, i, i, vp, vp],

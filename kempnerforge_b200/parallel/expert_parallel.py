@@ -25,6 +25,8 @@ Parity: kempnerforge/distributed/expert_parallel.py:29-379.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -73,6 +75,9 @@ def ep_dispatch_and_compute(x_flat: torch.Tensor, weights: torch.Tensor, indices
     group, ep = moe.ep_group, moe.ep_world_size
     n_local = moe.num_local_experts
     t, k = indices.shape
+    fused = _fused_context(moe, x_flat, t * k)
+    if fused is not None:
+        return _ep_forward_peer_memory(x_flat, weights, indices, moe, fused)
     flat_e = indices.reshape(-1)
     # (1) sort pairs by global expert id: destination ranks are contiguous blocks of that order
     order = torch.argsort(flat_e, stable=True)
@@ -108,6 +113,51 @@ def ep_dispatch_and_compute(x_flat: torch.Tensor, weights: torch.Tensor, indices
     back = back.index_select(0, inv_order).view(t, k, -1)
     del src_of_chunk
     return (back * weights.unsqueeze(-1).to(back.dtype)).sum(dim=1)
+
+
+def _fused_context(moe, x_flat: torch.Tensor, n_sorted: int):
+    """The peer-memory exchange context of this layer's EP group, or None when the library path must be used
+    (CPU, several nodes, dtypes / options the kernels do not cover, ``KF_EP_FUSED=0``)."""
+    if not (x_flat.is_cuda and x_flat.dtype == torch.bfloat16 and x_flat.shape[1] % 8 == 0):
+        return None
+    if os.environ.get("KF_EP_FUSED", "1") == "0" or (moe.gradient_scale and moe.training):
+        return None
+    if "nccl" not in str(dist.get_backend(moe.ep_group)):
+        return None
+    if int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) != int(os.environ.get("WORLD_SIZE", "1")):
+        return None
+    from kempnerforge_b200.ops import moe_ops
+
+    if not moe_ops.native_ok(x_flat, moe.ep_world_size * moe.num_local_experts, 1) or moe.ep_world_size > 8:
+        return None
+    from kempnerforge_b200.comm.fused_ep import EPContext
+
+    key = id(moe.ep_group)
+    ctx = _EP_CONTEXTS.get(key)
+    if ctx is None or not ctx.fits(n_sorted, x_flat.shape[1], moe.num_local_experts):
+        cap = max(n_sorted, ctx.cap if ctx is not None else 0)
+        cols = max(x_flat.shape[1], ctx.cols if ctx is not None else 0)
+        ctx = _EP_CONTEXTS[key] = EPContext(moe.ep_group, x_flat.device, cap, cols, moe.num_local_experts)
+    return ctx if ctx.cols == x_flat.shape[1] else None
+
+
+_EP_CONTEXTS: dict[int, object] = {}
+
+
+def _ep_forward_peer_memory(x_flat, weights, indices, moe, ctx) -> torch.Tensor:
+    """Expert-parallel forward with our kernels end to end: device-side sort by global expert, rows stored straight
+    into the owners' receive windows over NVLink, ragged grouped GEMMs, rows stored back, weighted combine."""
+    from kempnerforge_b200.comm import fused_ep
+    from kempnerforge_b200.ops import moe_ops
+
+    t, k = indices.shape
+    e_global = moe.ep_world_size * moe.num_local_experts
+    offsets_g, row_of_slot, slot_of_row = moe_ops.sort_by_expert(indices, e_global)
+    x_c, offsets_l, lay = fused_ep.dispatch(x_flat, slot_of_row, row_of_slot, k, offsets_g, ctx)
+    counts_l = (offsets_l[1:] - offsets_l[:-1]).to(torch.int64)
+    y_c = moe.run_experts(x_c, counts_l)
+    y_sorted = fused_ep.return_rows(y_c, offsets_g, t * k, lay, ctx)
+    return moe_ops.combine_rows(y_sorted, weights, row_of_slot, slot_of_row)
 
 
 def apply_expert_parallel(model: nn.Module, ep_group, ep_in_dp: bool = False) -> int:

@@ -186,3 +186,22 @@ def test_tensor_parallel_fused_kernels_match_library_collectives():
         assert abs(a - b) < 5e-2, (plain["losses"], fused["losses"])
     for a, b in zip(plain["norms"], fused["norms"]):
         assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (plain["norms"], fused["norms"])
+
+
+EP_WORKER = WORKER.replace(
+    "model\": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536, max_seq_len=256)",
+    "model\": dict(dim=512, n_layers=2, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1024, max_seq_len=256, "
+    "num_experts=8, moe_top_k=2, moe_packed_experts=True, moe_aux_loss_weight=0.01)") \
+    .replace('"distributed": dict(dp_shard=world)', '"distributed": dict(ep=world, ep_in_dp=True, dp_shard=world)')
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_expert_parallel_peer_memory_dispatch_matches_all_to_all():
+    """EP=2 (experts sharded over the data-parallel ranks): rows exchanged by our peer-store kernels against NCCL all-to-all."""
+    assert "num_experts=8" in EP_WORKER and "ep_in_dp=True" in EP_WORKER
+    fused = _run_script(EP_WORKER, 2, "ep_fused", {"KF_EP_FUSED": "1", "KF_TRANSPORT": "collective"})
+    plain = _run_script(EP_WORKER, 2, "ep_plain", {"KF_EP_FUSED": "0", "KF_TRANSPORT": "collective"})
+    for a, b in zip(plain["losses"], fused["losses"]):
+        assert abs(a - b) < 5e-2, (plain["losses"], fused["losses"])
+    for a, b in zip(plain["norms"], fused["norms"]):
+        assert abs(a - b) < 8e-2 * max(1.0, abs(a)), (plain["norms"], fused["norms"])
