@@ -252,7 +252,22 @@ int launch_gemm_2cta(const void* A, const void* B, void* C, const void* R, int M
                      cudaStream_t stream, int* status);
 }
 
+namespace kf2 {
+int launch_gemm_swiglu_2cta(const void* A, const void* W, void* H, void* GU, int M, int F, int K, int lda, int ldw, int ldh,
+                            int ldgu, int num_sms, cudaStream_t stream, int* status);
+}
+
 extern "C" {
+
+// SwiGLU up-projection in one kernel: h[M, F] = silu(x Wg^T) * (x Wu^T), W = [Wg ; Wu] stacked as [2F][K] (K contiguous).
+// gu (optional, [M, 2F]) receives the bf16 pre-activations (gate | up) for the backward pass.  F must be a multiple of
+// 128; pitches in elements, multiples of 8.
+int kf_gemm_swiglu_bf16(const void* x, const void* w, void* h, void* gu, int M, int F, int K, int lda, int ldw, int ldh,
+                        int ldgu, int num_sms, void* stream) {
+  if ((F % 128) || (lda & 7) || (ldw & 7) || (ldh & 7) || (gu && (ldgu & 7))) return 5;
+  return kf2::launch_gemm_swiglu_2cta(x, w, h, gu, M, F, K, lda, ldw, ldh, ldgu, num_sms, (cudaStream_t)stream,
+                                      kf::status_ptr());
+}
 
 // C[M,N] = op(A) * op(B)^T (+ C if accumulate) (+ R if given), bf16 inputs, fp32 accumulation.
 //   a_mn == 0: A is stored [M][lda] (K contiguous);  a_mn == 1: A is stored [K][lda] (M contiguous)

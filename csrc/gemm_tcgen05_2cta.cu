@@ -102,7 +102,12 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
   return {first_m + r % rows, r / rows};
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
+// SWIGLU != 0 (bf16, K-major operands only): B is the stacked [gate ; up] weight of a SwiGLU MLP with F = N rows
+// each.  The pair's B tile is made of 128 gate rows (loaded by the leader) and the matching 128 up rows (loaded by
+// the peer), so every CTA's accumulator holds gate in columns 0..127 and up in columns 128..255 for the same 128
+// hidden units; the epilogue writes h = silu(gate) * up to C[M, F] and, when R is given, the pre-activations to
+// R[M, 2F] (gate | up) for the backward pass.
+template <bool A_MN, bool B_MN, typename OutT, int SWIGLU = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ C, const OutT* __restrict__ R, int M, int N, int K, int ldc, int ldr,
@@ -125,7 +130,7 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int m_blocks = (M + TILE_M - 1) / TILE_M;
-  const int n_blocks = (N + TILE_N - 1) / TILE_N;
+  const int n_blocks = SWIGLU ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (K + BK - 1) / BK;
 
@@ -161,7 +166,8 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
         const int m0 = tc.m * TILE_M + int(rank) * CTA_M;
-        const int n0 = tc.n * TILE_N + int(rank) * HALF_N;
+        const int n0 = SWIGLU ? tc.n * HALF_N + int(rank) * N  // leader: gate rows, peer: the matching up rows
+                              : tc.n * TILE_N + int(rank) * HALF_N;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -241,8 +247,40 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       if (!mbar_wait(tfull_bar(acc), acc_ph, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int row = tc.m * TILE_M + int(rank) * CTA_M + quarter * 32 + lane;
-      const int col0 = tc.n * TILE_N;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TILE_N;
+      if constexpr (SWIGLU != 0) {
+        const int h0 = tc.n * HALF_N;  // first hidden unit of this tile
+        __nv_bfloat16* h_row = reinterpret_cast<__nv_bfloat16*>(C) + size_t(row) * ldc + h0;
+        __nv_bfloat16* gu_row = R ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(R)) + size_t(row) * ldr + h0
+                                  : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < HALF_N / 32; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c * 32, g);
+          tmem_ld_32x32(t_row + HALF_N + c * 32, u);
+          tmem_ld_wait();
+          const int valid = min(32, N - (h0 + c * 32));
+          if (row < M && valid > 0) {
+            if (gu_row) {
+              store_chunk<__nv_bfloat16>(gu_row + c * 32, g, valid, false, nullptr);
+              store_chunk<__nv_bfloat16>(gu_row + N + c * 32, u, valid, false, nullptr);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              // same rounding as the two-kernel path: the activation sees the bf16 pre-activations
+              const float gf = __bfloat162float(__float2bfloat16(__uint_as_float(g[i])));
+              const float uf = __bfloat162float(__float2bfloat16(__uint_as_float(u[i])));
+              g[i] = __float_as_uint(gf / (1.f + __expf(-gf)) * uf);
+            }
+            store_chunk<__nv_bfloat16>(h_row + c * 32, g, valid, false, nullptr);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) arrive_on_cta(tempty_bar(acc), 0);
+        continue;
+      }
+      const int col0 = tc.n * TILE_N;
       OutT* c_row = C + size_t(row) * ldc + col0;
       const OutT* r_row = R ? R + size_t(row) * ldr + col0 : nullptr;
 #pragma unroll 1
@@ -290,6 +328,30 @@ static int launch(const void* A, const void* B, void* C, const void* R, int M, i
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<OutT*>(C),
                                                    reinterpret_cast<const OutT*>(R), M, N, K, ldc, ldr, accumulate,
                                                    status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// h[M, F] = silu(x Wg^T) * (x Wu^T) with W = [Wg ; Wu] stacked ([2F][K]); gu (optional) receives [M, 2F] pre-activations
+int launch_gemm_swiglu_2cta(const void* A, const void* W, void* H, void* GU, int M, int F, int K, int lda, int ldw, int ldh,
+                            int ldgu, int num_sms, cudaStream_t stream, int* status) {
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, A, M, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = make_map_2d_bf16(&mb, W, 2 * (uint64_t)F, K, ldw, BK, HALF_N);
+  if (rc) return 200 + rc;
+  auto kern = kf_gemm_bf16_tcgen05_2cta<false, false, __nv_bfloat16, 1>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * ((F + HALF_N - 1) / HALF_N);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(H),
+                                                   reinterpret_cast<const __nv_bfloat16*>(GU), M, F, K, ldh, ldgu, 0, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

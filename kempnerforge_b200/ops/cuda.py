@@ -46,6 +46,7 @@ def _declare(L: ctypes.CDLL) -> None:
     vp, i, ll, f = c_void_p, c_int, c_longlong, c_float
     sigs = {
         "kf_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, i, i, vp],
+        "kf_gemm_swiglu_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
         "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
@@ -328,6 +329,26 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch
     partial = torch.empty(1024, dtype=torch.float32, device=x.device)
     _check(lib().kf_sumsq(x.data_ptr(), x.numel(), _DT[x.dtype], partial.data_ptr(), out.data_ptr(), int(accumulate), _stream()), "kf_sumsq")
     return out
+
+
+def gemm_swiglu(x2: torch.Tensor, w_gate_up: torch.Tensor, want_gu: bool = True):
+    """(h, gu): h = silu(x Wgᵀ) * (x Wuᵀ) computed in the epilogue of one tcgen05 GEMM over the stacked weight
+    ``w_gate_up`` = [Wg ; Wu] of shape (2F, K); ``gu`` (M, 2F) holds the pre-activations when ``want_gu``."""
+    m, k = x2.shape
+    f = w_gate_up.shape[0] // 2
+    h = torch.empty((m, f), dtype=torch.bfloat16, device=x2.device)
+    gu = torch.empty((m, 2 * f), dtype=torch.bfloat16, device=x2.device) if want_gu else None
+    _check(lib().kf_gemm_swiglu_bf16(x2.data_ptr(), w_gate_up.data_ptr(), h.data_ptr(), gu.data_ptr() if want_gu else None,
+                                     m, f, k, x2.stride(0), w_gate_up.stride(0), f, 2 * f, sm_count(), _stream()),
+           "kf_gemm_swiglu_bf16")
+    return h, gu
+
+
+def gemm_swiglu_supported(x2: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
+    f = w_gate_up.shape[0] // 2
+    return (getattr(lib(), "kf_gemm_swiglu_bf16", None) is not None and not os.environ.get("KF_DISABLE_SWIGLU_EPILOGUE")
+            and f % 128 == 0 and x2.shape[0] >= 256 and x2.stride(1) == 1 and w_gate_up.stride(1) == 1
+            and x2.stride(0) % 8 == 0 and w_gate_up.stride(0) % 8 == 0 and x2.dtype == torch.bfloat16)
 
 
 # --------------------------------------------------------------------------- fp8

@@ -124,8 +124,13 @@ class DenseBlockFn(torch.autograd.Function):
         attn2 = attn.reshape(b * s, h * hd)
         h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
         n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)
-        gu = kc.gemm(n2, kc.stack_rows([wg, wu]))
-        hmid = kc.swiglu_fwd(gu)
+        w_gu = kc.stack_rows([wg, wu])
+        if kc.gemm_swiglu_supported(n2, w_gu):
+            # activation in the GEMM epilogue; the pre-activations are written only when the backward will need them
+            hmid, gu = kc.gemm_swiglu(n2, w_gu, want_gu=keep)
+        else:
+            gu = kc.gemm(n2, w_gu)
+            hmid = kc.swiglu_fwd(gu)
         out = {}
         if need_output:
             y = kc.gemm(hmid, wd, residual=h1)

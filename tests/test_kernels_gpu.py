@@ -639,3 +639,21 @@ def test_lion_and_schedule_free_kernels_match_python_rules(native_lib, name, dty
     tol = 1e-5 if dtype == torch.float32 else 3e-2
     for pr, pd in zip(ref_m.parameters(), dev_m.parameters()):
         assert torch.allclose(pr.float(), pd.float().cpu(), atol=tol, rtol=tol), (pr.float() - pd.float().cpu()).abs().max()
+
+
+@pytest.mark.parametrize("shape", [(256, 128, 64), (512, 384, 256), (1000, 1024, 520), (8192, 14336, 4096)])
+def test_gemm_swiglu_epilogue_matches_two_kernel_path(native_lib, shape):
+    m, f, k = shape
+    x = _rand(m, k)
+    w = _rand(2 * f, k, scale=0.05)
+    assert native_lib.gemm_swiglu_supported(x, w)
+    h, gu = native_lib.gemm_swiglu(x, w, want_gu=True)
+    h_only, none = native_lib.gemm_swiglu(x, w, want_gu=False)
+    assert none is None and native_lib.read_status() == 0
+    gu_ref = native_lib.gemm(x, w)
+    h_ref = native_lib.swiglu_fwd(gu_ref)
+    _close(gu, gu_ref, rtol=1e-2, atol=1e-2)
+    _close(h, h_ref, rtol=2e-2, atol=2e-2)
+    assert torch.equal(h, h_only)
+    want = torch.nn.functional.silu(x.float() @ w[:f].float().t()) * (x.float() @ w[f:].float().t())
+    _close(h, want, rtol=3e-2, atol=3e-2)
