@@ -17,7 +17,7 @@
 //
 // Replaces F.scaled_dot_product_attention and the repeat_interleave GQA expansion of the reference
 // (kempnerforge/model/attention.py:173-175,190-231) for the causal / document-masked cases.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 namespace kf {
 namespace attn {
@@ -40,64 +40,6 @@ struct Cfg {
   static constexpr int N_TILES_SMEM = 1 + K_STAGES + V_STAGES;  // Q, K ring, V ring
   static constexpr size_t SMEM = N_TILES_SMEM * size_t(TILE_BYTES) + 1024 /*align*/ + 4352 /*barriers, doc ids, row exchange*/;
 };
-
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
-        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
-        "r"(r[31])
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// Two-wide fp32 arithmetic (one issue slot for two lanes of work) and the three-input max of sm_100.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
 
 // Named barriers: ids 1-4 join the two softmax warps that share a TMEM lane quarter (64 threads),
 // id 5 joins all 256 softmax threads.
@@ -127,6 +69,7 @@ kf_attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   auto v_empty = [&](int st) { return bar_base + 8u * (9 + st); };
   auto s_full = [&](int buf) { return bar_base + 8u * (11 + buf); };
   const uint32_t p_full = bar_base + 8u * 13, pv_done = bar_base + 8u * 14, drain_bar = bar_base + 8u * 15;
+  const uint32_t o_final = bar_base + 8u * 17;  // every MMA of this CTA has retired (a phase of its own)
   uint8_t* aligned_generic = smem_raw + (smem_base - smem_u32(smem_raw));
   uint8_t* bar_generic = aligned_generic + C::N_TILES_SMEM * C::TILE_BYTES;
   const uint32_t tmem_slot = bar_base + 8u * 15 + 8u;
@@ -157,6 +100,7 @@ kf_attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
+    mbar_init(o_final, 1);
     mbar_init(drain_bar, 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -259,6 +203,7 @@ kf_attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         tc_commit(v_empty(st));  // V_j has been read
         tc_commit(pv_done);      // O includes tile j
+        if (j + 1 == n_tiles) tc_commit(o_final);
       }
       if (!ok) {
         tc_commit(drain_bar);
@@ -394,7 +339,7 @@ kf_attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     xl[half * BLK_M + r_local] = l_run;
     pair_sync(quarter);
     const float l_tot = l_run + xl[(half ^ 1) * BLK_M + r_local];
-    if (ok && n_tiles > 0 && !mbar_wait(pv_done, (n_tiles - 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+    if (ok && n_tiles > 0 && !mbar_wait(o_final, 0, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
     if (ok) {
       tc_fence_after();
       const float inv_l = l_tot > 0.f ? 1.f / l_tot : 0.f;

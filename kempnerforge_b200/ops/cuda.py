@@ -76,6 +76,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
+        "kf_attn_fwd2_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
         "kf_symm_adamw_bcast_bf16": [vp, vp, i, i, vp, vp, vp, ll, ll, ll, f, f, f, f, f, f, f, vp, vp, i, vp],
@@ -428,11 +429,16 @@ def attn_fwd(q, k, v, causal: bool, doc_ids, scale: float):
     doc = None
     if doc_ids is not None:
         doc = doc_ids.to(torch.int32).contiguous()
+    # two query tiles per CTA (interleaved softmax) once there are at least two tiles; KF_ATTN_FWD=1 forces the
+    # single-tile kernel
+    L = lib()
+    two = sq > 128 and getattr(L, "kf_attn_fwd2_bf16", None) is not None and os.environ.get("KF_ATTN_FWD", "2") != "1"
+    fn = L.kf_attn_fwd2_bf16 if two else L.kf_attn_fwd_bf16
     _check(
-        lib().kf_attn_fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+        fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                doc.data_ptr() if doc is not None else None, b, sq, sk, h, hkv, hd, q.stride(1),
-                               k.stride(1), v.stride(1), h * hd, float(scale), int(causal), _stream()),
-        "kf_attn_fwd_bf16",
+           k.stride(1), v.stride(1), h * hd, float(scale), int(causal), _stream()),
+        "kf_attn_fwd2_bf16" if two else "kf_attn_fwd_bf16",
     )
     return out, lse
 

@@ -657,3 +657,18 @@ def test_gemm_swiglu_epilogue_matches_two_kernel_path(native_lib, shape):
     assert torch.equal(h, h_only)
     want = torch.nn.functional.silu(x.float() @ w[:f].float().t()) * (x.float() @ w[f:].float().t())
     _close(h, want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(2, 256, 4, 2, 64), (1, 384, 4, 1, 128), (2, 200, 2, 2, 128), (1, 1000, 8, 2, 64)])
+def test_attention_forward_single_tile_kernel(native_lib, monkeypatch, shape, causal):
+    """The one-query-tile kernel (used for short sequences) on shapes that the two-tile kernel takes by default."""
+    from kempnerforge_b200.ops import ref
+
+    monkeypatch.setenv("KF_ATTN_FWD", "1")
+    b, s, h, hkv, hd = shape
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=23)
+    out, _ = native_lib.attn_fwd(q, k, v, causal, None, 1.0 / math.sqrt(hd))
+    want = ref.attention(q.float(), k.float(), v.float(), causal=causal)
+    assert native_lib.read_status() == 0
+    assert (out.float() - want).abs().max().item() < 2e-2
