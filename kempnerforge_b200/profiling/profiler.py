@@ -20,8 +20,9 @@ from kempnerforge_b200.metrics.logger import get_logger
 log = get_logger("profiler")
 
 _BUCKETS = (
-    ("fused_comm", ("kf_ag_gemm", "kf_gemm_rs", "kf_rs_adamw", "kf_moe_dispatch", "kf_moe_combine", "kf_symm")),
-    ("matmul", ("gemm", "cublas", "nvjet", "cutlass", "tcgen05", "matmul", "_mm", "flash", "attn", "fmha")),
+    ("fused_comm", ("kf_ag_gemm", "kf_gemm_rs", "kf_rs_adamw", "kf_ep_put", "kf_ep_move", "kf_symm")),
+    ("attention", ("kf_attn", "flash", "fmha", "sdpa")),
+    ("matmul", ("gemm", "cublas", "nvjet", "cutlass", "tcgen05", "matmul", "_mm")),
     ("comm", ("nccl", "allreduce", "all_reduce", "allgather", "all_gather", "reduce_scatter", "alltoall")),
     ("memory", ("memcpy", "memset")),
 )
