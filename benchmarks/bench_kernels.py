@@ -52,6 +52,10 @@ def cases(device: torch.device):
     x = torch.randn(t, d, device=device, dtype=bf)
     wn = torch.ones(d, device=device, dtype=bf)
     yield Case("rmsnorm fwd (8192x4096)", lambda: K.rmsnorm_fwd(x, wn, 1e-5), bytes_per_iter=2 * x.numel() * 2)
+    y0, rstd0 = K.rmsnorm_fwd(x, wn, 1e-5)
+    dy0 = torch.randn_like(x)
+    yield Case("rmsnorm bwd (8192x4096, with residual gradient)",
+               lambda: K.rmsnorm_bwd(dy0, x, wn, rstd0, residual_grad=dy0), bytes_per_iter=4 * x.numel() * 2)
     h = torch.randn(t, 2 * 14336, device=device, dtype=bf)
     yield Case("swiglu fwd (8192x14336)", lambda: K.swiglu_fwd(h), bytes_per_iter=h.numel() * 2 * 1.5)
     nparam = 218_112_000

@@ -124,43 +124,74 @@ kf_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   }
 }
 
-// dx = [dx_in +] r*g - x*r^3*mean(g*x) with g = dy*w;  dw partial = sum_rows dy*x*r (per block, fp32).
-// dx_in (optional) is the gradient arriving over the residual connection; it may alias dx.
-// The first NORM_CACHE*NORM_THREADS vectors of a row (D <= 8192) stay in registers between the two passes.
+// RMSNorm backward in two streaming passes (dw first, so that dx may overwrite dy in place):
+//   kf_rmsnorm_bwd_dw   dw partial[chunk][d] = sum over the chunk's rows of dy * x * rstd   (column-parallel, fp32)
+//   kf_rmsnorm_bwd_dx   dx = [dx_in +] r*g - x*r^3*mean(g*x) with g = dy*w                   (one block per row)
+// Both keep many rows in flight per SM (few registers, no accumulators that live across rows), which is what lets
+// them run at memory speed; the earlier single kernel carried the dw accumulators through the row loop and was
+// latency bound.  dx_in (optional) is the gradient arriving over the residual connection; it may alias dx.
+__global__ void __launch_bounds__(256)
+kf_rmsnorm_bwd_dw(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                  const float* __restrict__ rstd, float* __restrict__ partial, int rows, int D, int rows_per_chunk) {
+  const int nvec = D >> 3;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= nvec) return;
+  const int r0 = blockIdx.y * rows_per_chunk;
+  const int r1 = min(rows, r0 + rows_per_chunk);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int row = r0;
+  for (; row + 4 <= r1; row += 4) {  // four rows in flight per thread
+    F8 g[4], a[4];
+    float r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      g[u] = load8(dy + size_t(row + u) * D + v * 8);
+      a[u] = load8(x + size_t(row + u) * D + v * 8);
+      r[u] = rstd[row + u];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += g[u].v[i] * a[u].v[i] * r[u];
+  }
+  for (; row < r1; ++row) {
+    const F8 g = load8(dy + size_t(row) * D + v * 8), a = load8(x + size_t(row) * D + v * 8);
+    const float r = rstd[row];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += g.v[i] * a.v[i] * r;
+  }
+  float* out = partial + size_t(blockIdx.y) * D + v * 8;
+  *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  *reinterpret_cast<float4*>(out + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+constexpr int BWD_CACHE = 2;  // vectors of 8 per thread kept between the two passes over a row (D <= 4096)
+
 __global__ void __launch_bounds__(NORM_THREADS)
-kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-               const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-               __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int D,
-               const __nv_bfloat16* __restrict__ dx_in) {
+kf_rmsnorm_bwd_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                  const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                  __nv_bfloat16* __restrict__ dx, int rows, int D, const __nv_bfloat16* __restrict__ dx_in) {
   __shared__ float red[40];
   const int nvec = D >> 3;
-  constexpr int CACHED = NORM_CACHE * NORM_THREADS;
-  F8 dw_acc[NORM_CACHE];
-#pragma unroll
-  for (int c = 0; c < NORM_CACHE; ++c)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) dw_acc[c].v[i] = 0.f;
-  float* my_partial = dw_partial + size_t(blockIdx.x) * D;
-  // columns beyond the register cache accumulate straight into this block's partial row
-  for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) my_partial[v * 8 + i] = 0.f;
-
+  constexpr int CACHED = BWD_CACHE * NORM_THREADS;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16* xr = x + size_t(row) * D;
     const __nv_bfloat16* dyr = dy + size_t(row) * D;
     const float r = rstd[row];
     float dot = 0.f;
-    F8 xc[NORM_CACHE], dc[NORM_CACHE];
+    F8 xc[BWD_CACHE], gc[BWD_CACHE];  // gc holds dy * w
 #pragma unroll
-    for (int c = 0; c < NORM_CACHE; ++c) {
+    for (int c = 0; c < BWD_CACHE; ++c) {
       const int v = threadIdx.x + c * NORM_THREADS;
       if (v < nvec) {
         xc[c] = load8(xr + v * 8);
-        dc[c] = load8(dyr + v * 8);
+        gc[c] = load8(dyr + v * 8);
         const F8 ww = load8(w + v * 8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dot += dc[c].v[i] * ww.v[i] * xc[c].v[i];
+        for (int i = 0; i < 8; ++i) {
+          gc[c].v[i] *= ww.v[i];
+          dot += gc[c].v[i] * xc[c].v[i];
+        }
       }
     }
     for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
@@ -172,21 +203,20 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
     __nv_bfloat16* dxr = dx + size_t(row) * D;
     const __nv_bfloat16* dir = dx_in ? dx_in + size_t(row) * D : nullptr;
 #pragma unroll
-    for (int c = 0; c < NORM_CACHE; ++c) {
+    for (int c = 0; c < BWD_CACHE; ++c) {
       const int v = threadIdx.x + c * NORM_THREADS;
       if (v < nvec) {
-        const F8 ww = load8(w + v * 8);
         F8 o;
         if (dir) o = load8(dir + v * 8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float d = r * dc[c].v[i] * ww.v[i] - xc[c].v[i] * coef;
+          const float d = r * gc[c].v[i] - xc[c].v[i] * coef;
           o.v[i] = dir ? o.v[i] + d : d;
-          dw_acc[c].v[i] += dc[c].v[i] * xc[c].v[i] * r;
         }
         store8(dxr + v * 8, o);
       }
     }
+    // beyond the register cache: every element is re-read and then written by the same thread, so dx may alias dy
     for (int v = threadIdx.x + CACHED; v < nvec; v += NORM_THREADS) {
       const F8 a = load8(xr + v * 8), g = load8(dyr + v * 8), ww = load8(w + v * 8);
       F8 o;
@@ -195,17 +225,9 @@ kf_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __rest
       for (int i = 0; i < 8; ++i) {
         const float d = r * g.v[i] * ww.v[i] - a.v[i] * coef;
         o.v[i] = dir ? o.v[i] + d : d;
-        my_partial[v * 8 + i] += g.v[i] * a.v[i] * r;
       }
       store8(dxr + v * 8, o);
     }
-  }
-#pragma unroll
-  for (int c = 0; c < NORM_CACHE; ++c) {
-    const int v = threadIdx.x + c * NORM_THREADS;
-    if (v < nvec)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) my_partial[v * 8 + i] = dw_acc[c].v[i];
   }
 }
 
@@ -527,19 +549,25 @@ int kf_rmsnorm_fwd_bf16(const void* x, const void* w, void* y, void* rstd, int r
 }
 
 // Number of fp32 partial rows rmsnorm_bwd writes (the workspace must hold nblocks * D floats).
-int kf_rmsnorm_bwd_blocks(int rows) { return rows < 148 * 2 ? rows : 148 * 2; }
+int kf_rmsnorm_bwd_blocks(int rows) { return rows < 148 ? (rows < 1 ? 1 : rows) : 148; }
 
 int kf_rmsnorm_bwd_bf16(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
                         void* dw_partial, void* dw_bf16, void* dw_f32, int rows, int D, const void* dx_in,
                         void* stream) {
   using namespace kf;
   if (D % 8) return 1;
-  const int nb = kf_rmsnorm_bwd_blocks(rows);
-  kf_rmsnorm_bwd<<<nb, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+  cudaStream_t st = (cudaStream_t)stream;
+  const int chunks = kf_rmsnorm_bwd_blocks(rows);
+  const int rows_per_chunk = (rows + chunks - 1) / chunks;
+  const int nvec = D / 8;
+  // dw first: the dx pass may overwrite dy
+  kf_rmsnorm_bwd_dw<<<dim3((nvec + 255) / 256, chunks), 256, 0, st>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const float*)rstd, (float*)dw_partial, rows, D, rows_per_chunk);
+  kf_colsum_partials<<<(D + 255) / 256, 256, 0, st>>>((const float*)dw_partial, (__nv_bfloat16*)dw_bf16,
+                                                      (float*)dw_f32, chunks, D);
+  kf_rmsnorm_bwd_dx<<<rows < 148 * 8 ? rows : 148 * 8, NORM_THREADS, 0, st>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)rstd,
-      (__nv_bfloat16*)dx, (float*)dw_partial, rows, D, (const __nv_bfloat16*)dx_in);
-  kf_colsum_partials<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-      (const float*)dw_partial, (__nv_bfloat16*)dw_bf16, (float*)dw_f32, nb, D);
+      (__nv_bfloat16*)dx, rows, D, (const __nv_bfloat16*)dx_in);
   KF_LAUNCH_CHECK();
 }
 
