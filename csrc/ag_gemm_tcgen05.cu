@@ -67,6 +67,7 @@ __device__ __forceinline__ TileRef tile_ref(int t, int rank, int tp, int mb_per_
   return x;
 }
 
+template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 kf_ag_gemm_tcgen05(const __grid_constant__ CUtensorMap map_local, const __grid_constant__ CUtensorMap map_gather,
                    const __grid_constant__ CUtensorMap map_b, Peers peers, const __nv_bfloat16* __restrict__ x_shard,
@@ -132,7 +133,13 @@ kf_ag_gemm_tcgen05(const __grid_constant__ CUtensorMap map_local, const __grid_c
           const uint32_t a_dst = smem_base + s * STAGE_BYTES;
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           tma_load_2d(a_dst, ma, full_bar(s), kb * BK, arow);
-          tma_load_2d(a_dst + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, tr.nb * BN);
+          if (!B_MN) {
+            tma_load_2d(a_dst + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, tr.nb * BN);
+          } else {  // B stored [K][N] (output dim contiguous): 64-column boxes
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(a_dst + A_STAGE_BYTES + c * (64 * BK * 2), &map_b, full_bar(s), tr.nb * BN + 64 * c, kb * BK);
+          }
         }
       }
       for (int j = max(0, it - STAGES); j < it; ++j)
@@ -140,7 +147,7 @@ kf_ag_gemm_tcgen05(const __grid_constant__ CUtensorMap map_local, const __grid_c
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, false);
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
       int it = 0, tile_iter = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
@@ -156,7 +163,9 @@ kf_ag_gemm_tcgen05(const __grid_constant__ CUtensorMap map_local, const __grid_c
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             tc_mma_f16(d_tmem, umma_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024),
-                       umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024), idesc, (kb | k) != 0);
+                       B_MN ? umma_desc_sw128(b_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                            : umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024),
+                       idesc, (kb | k) != 0);
           tc_commit(empty_bar(s));
         }
         if (ok) tc_commit(tfull_bar(acc));
@@ -254,7 +263,7 @@ extern "C" {
 // Cross-rank waits are bounded and report through the status word.
 int kf_ag_gemm_bf16(const void* x_shard, const void* w, const long long* gather_ptrs, const long long* flag_ptrs, void* y,
                     int T, int N, int K, int S, long long ldx, long long ldw, long long ldy, int tp, int rank,
-                    int call_no, int num_sms, void* stream) {
+                    int call_no, int b_mn, int num_sms, void* stream) {
   using namespace kf;
   using namespace kf::ag;
   if (tp < 1 || tp > MAX_PEERS || T % tp || S % tp || ((S / tp) % BM) || (T % S) || (K % (8 * K_SLICES)) || (ldx & 7) ||
@@ -265,24 +274,39 @@ int kf_ag_gemm_bf16(const void* x_shard, const void* w, const long long* gather_
   if (rc) return 100 + rc;
   rc = make_map_2d_bf16(&mg, reinterpret_cast<const void*>(gather_ptrs[rank]), uint64_t(2) * T, K, K, BK, BM);
   if (rc) return 150 + rc;
-  rc = make_map_2d_bf16(&mb, w, N, K, ldw, BK, BN);
+  // b_mn: w is stored [K][N] (N contiguous; K must be a multiple of 64), else [N][K]
+  if (b_mn && (K % BK)) return 5;
+  rc = b_mn ? make_map_2d_bf16(&mb, w, K, N, ldw, 64, BK) : make_map_2d_bf16(&mb, w, N, K, ldw, BK, BN);
   if (rc) return 200 + rc;
   Peers peers;
   for (int i = 0; i < MAX_PEERS; ++i) {
     peers.gather[i] = i < tp ? reinterpret_cast<void*>(gather_ptrs[i]) : nullptr;
     peers.flags[i] = i < tp ? reinterpret_cast<int*>(flag_ptrs[i]) : nullptr;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kf_ag_gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
   const int tiles = (T / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kf_ag_gemm_tcgen05<<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(
-      ml, mg, mb, peers, reinterpret_cast<const __nv_bfloat16*>(x_shard), ldx, reinterpret_cast<__nv_bfloat16*>(y), ldy, T,
-      N, K, S, tp, rank, call_no, reinterpret_cast<int*>(kf_status_device_ptr()));
+  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
+  auto xs = reinterpret_cast<const __nv_bfloat16*>(x_shard);
+  auto yp = reinterpret_cast<__nv_bfloat16*>(y);
+  if (b_mn) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_ag_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_ag_gemm_tcgen05<true><<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(ml, mg, mb, peers, xs, ldx, yp, ldy, T, N, K, S, tp,
+                                                                          rank, call_no, status);
+  } else {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_ag_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_ag_gemm_tcgen05<false><<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(ml, mg, mb, peers, xs, ldx, yp, ldy, T, N, K, S, tp,
+                                                                           rank, call_no, status);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

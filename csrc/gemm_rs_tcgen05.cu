@@ -68,6 +68,7 @@ __device__ __forceinline__ TileRef tile_ref(int t, int rank, int tp, int mb_per_
   return x;
 }
 
+template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 kf_gemm_rs_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Peers peers,
                    __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual, int T, int D, int K,
@@ -119,7 +120,13 @@ kf_gemm_rs_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t a_dst = smem_base + s * STAGE_BYTES;
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, tr.row0);
-          tma_load_2d(a_dst + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, tr.nb * BN);
+          if (!B_MN) {
+            tma_load_2d(a_dst + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, tr.nb * BN);
+          } else {  // B stored [K][D] (output dim contiguous): 64-column boxes
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(a_dst + A_STAGE_BYTES + c * (64 * BK * 2), &map_b, full_bar(s), tr.nb * BN + 64 * c, kb * BK);
+          }
         }
       }
       for (int j = max(0, it - STAGES); j < it; ++j)
@@ -127,7 +134,7 @@ kf_gemm_rs_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, false);
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
       int it = 0, tile_iter = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
@@ -143,7 +150,9 @@ kf_gemm_rs_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             tc_mma_f16(d_tmem, umma_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024),
-                       umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024), idesc, (kb | k) != 0);
+                       B_MN ? umma_desc_sw128(b_src + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                            : umma_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024),
+                       idesc, (kb | k) != 0);
           tc_commit(empty_bar(s));
         }
         if (ok) tc_commit(tfull_bar(acc));
@@ -264,31 +273,46 @@ extern "C" {
 // tile counters) is bounded and reports through the status word.
 int kf_gemm_rs_bf16(const void* x, const void* w, const long long* stage_ptrs, const long long* flag_ptrs, void* out,
                     const void* residual, int T, int D, int K, int S, long long lda, long long ldb, int tp, int rank,
-                    int call_no, int num_sms, void* stream) {
+                    int call_no, int b_mn, int num_sms, void* stream) {
   using namespace kf;
   using namespace kf::rs;
   if (tp < 1 || tp > MAX_PEERS || T % tp || S % tp || ((S / tp) % BM) || (T % S) || (D & 7) || (lda & 7) || (ldb & 7)) return 5;
   CUtensorMap ma, mb;
   int rc = make_map_2d_bf16(&ma, x, T, K, lda, BK, BM);
   if (rc) return 100 + rc;
-  rc = make_map_2d_bf16(&mb, w, D, K, ldb, BK, BN);
+  // b_mn: w is stored [K][D] (D contiguous; K must be a multiple of 64), else [D][K]
+  if (b_mn && (K % BK)) return 5;
+  rc = b_mn ? make_map_2d_bf16(&mb, w, K, D, ldb, 64, BK) : make_map_2d_bf16(&mb, w, D, K, ldb, BK, BN);
   if (rc) return 200 + rc;
   Peers peers;
   for (int i = 0; i < MAX_PEERS; ++i) {
     peers.stage[i] = i < tp ? reinterpret_cast<void*>(stage_ptrs[i]) : nullptr;
     peers.flags[i] = i < tp ? reinterpret_cast<int*>(flag_ptrs[i]) : nullptr;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kf_gemm_rs_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
   const int tiles = (T / BM) * ((D + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kf_gemm_rs_tcgen05<<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(
-      ma, mb, peers, reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(residual), T, D, K, S,
-      tp, rank, call_no, reinterpret_cast<int*>(kf_status_device_ptr()));
+  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
+  auto out_p = reinterpret_cast<__nv_bfloat16*>(out);
+  auto res_p = reinterpret_cast<const __nv_bfloat16*>(residual);
+  if (b_mn) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_gemm_rs_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_gemm_rs_tcgen05<true><<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(ma, mb, peers, out_p, res_p, T, D, K, S, tp, rank,
+                                                                          call_no, status);
+  } else {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kf_gemm_rs_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e != cudaSuccess) return 300 + (int)e;
+      attr_set = true;
+    }
+    kf_gemm_rs_tcgen05<false><<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(ma, mb, peers, out_p, res_p, T, D, K, S, tp, rank,
+                                                                           call_no, status);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

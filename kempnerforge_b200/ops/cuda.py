@@ -73,8 +73,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_moe_combine_bf16": [vp, vp, vp, i, i, i, vp, vp],
         "kf_moe_combine_bwd_bf16": [vp, vp, vp, vp, i, i, i, vp, vp, vp],
         "kf_grouped_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
-        "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, vp],
-        "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, vp],
+        "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
+        "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
         "kf_attn_fwd2_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
@@ -547,32 +547,35 @@ def grouped_gemm_supported(a: torch.Tensor, b: torch.Tensor, b_mn: bool) -> bool
             and a.stride(0) % 8 == 0 and b.is_contiguous())
 
 
-def all_gather_gemm(x_shard: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[T, N] = gather over the ranks of ``ctx`` (along the sequence) of x_shard[T/tp, K], times w[N, K]ᵀ; the shard
-    is pushed to the peers by copy warps of the GEMM kernel itself.  ``ctx`` is a ``comm.fused_tp.AgGemmContext``."""
+def all_gather_gemm(x_shard: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None,
+                    w_kn: bool = False) -> torch.Tensor:
+    """out[T, N] = gather over the ranks of ``ctx`` (along the sequence) of x_shard[T/tp, K], times the weight: w is
+    (N, K) or, with ``w_kn``, (K, N) (the layout the input-gradient GEMM of a row-parallel Linear needs).  The shard is
+    pushed to the peers by copy warps of the GEMM kernel itself.  ``ctx`` is a ``comm.fused_tp.AgGemmContext``."""
     tl, k = x_shard.shape
     t = tl * ctx.world
-    n = w.shape[0]
-    assert x_shard.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == k
+    n = w.shape[1] if w_kn else w.shape[0]
+    assert x_shard.stride(1) == 1 and w.stride(1) == 1 and (w.shape[0] if w_kn else w.shape[1]) == k
     if out is None:
         out = torch.empty((t, n), dtype=torch.bfloat16, device=x_shard.device)
     ctx.reserve(t, k)
     _check(
         lib().kf_ag_gemm_bf16(x_shard.data_ptr(), w.data_ptr(), ctx.stage_ptrs, ctx.flag_ptrs, out.data_ptr(), t, n, k,
                               seq_len, x_shard.stride(0), w.stride(0), out.stride(0), ctx.world, ctx.rank, ctx.next_call(),
-                              sm_count(), _stream()),
+                              int(w_kn), sm_count(), _stream()),
         "kf_ag_gemm_bf16",
     )
     return out
 
 
 def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None,
-                        residual: torch.Tensor | None = None) -> torch.Tensor:
-    """out[T/tp, D] = reduce-scatter over the ranks of ``ctx`` of x2[T, K_local] @ w[D, K_local]ᵀ (+ residual), with the
-    tiles pushed to their owners from the GEMM epilogue.  ``ctx`` is a ``comm.fused_tp.GemmRSContext``."""
+                        residual: torch.Tensor | None = None, w_kn: bool = False) -> torch.Tensor:
+    """out[T/tp, D] = reduce-scatter over the ranks of ``ctx`` of x2[T, K_local] times the weight (+ residual): w is
+    (D, K_local) or, with ``w_kn``, (K_local, D) (the input-gradient GEMM of a column-parallel Linear).  Tiles are pushed
+    to their owners from the GEMM epilogue.  ``ctx`` is a ``comm.fused_tp.GemmRSContext``."""
     t, k = x2.shape
-    d = w.shape[0]
-    assert x2.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == k
+    d = w.shape[1] if w_kn else w.shape[0]
+    assert x2.stride(1) == 1 and w.stride(1) == 1 and (w.shape[0] if w_kn else w.shape[1]) == k
     tl = t // ctx.world
     if out is None:
         out = torch.empty((tl, d), dtype=torch.bfloat16, device=x2.device)
@@ -580,7 +583,7 @@ def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, ou
     _check(
         lib().kf_gemm_rs_bf16(x2.data_ptr(), w.data_ptr(), ctx.stage_ptrs, ctx.flag_ptrs, out.data_ptr(),
                               residual.data_ptr() if residual is not None else None, t, d, k, seq_len, x2.stride(0),
-                              w.stride(0), ctx.world, ctx.rank, ctx.next_call(), sm_count(), _stream()),
+                              w.stride(0), ctx.world, ctx.rank, ctx.next_call(), int(w_kn), sm_count(), _stream()),
         "kf_gemm_rs_bf16",
     )
     return out

@@ -205,8 +205,8 @@ class TPContext:
 
 
 class _FusedColumnLinearFn(torch.autograd.Function):
-    """y = gather_seq(x) @ [W_0; W_1; ...]ᵀ with the gather inside the GEMM kernel.  The backward uses library
-    collectives: reduce-scatter of the input gradient, all-gather of the input for the weight gradient."""
+    """y = gather_seq(x) @ [W_0; W_1; ...]ᵀ with the gather inside the GEMM kernel.  Backward: the input gradient is a
+    GEMM whose epilogue reduce-scatters (``kf_gemm_rs``); the weight gradient all-gathers the input with the library."""
 
     @staticmethod
     def forward(ctx, x, tp, *weights):
@@ -238,8 +238,14 @@ class _FusedColumnLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = None
         if ctx.needs_input_grad[0]:
-            dx_full = kc.gemm(dy2, w, a_kmajor=True, b_kmajor=False).view(b, s_local * tp.size, k)
-            dx = _reduce_scatter_dim(dx_full, 1, tp.group)
+            n_local = w.shape[0]
+            if n_local % 64 == 0 and k % 8 == 0:
+                # dx_partial = dy @ W reduced over the ranks and scattered along the sequence inside the GEMM
+                dx = kc.gemm_reduce_scatter(dy2, w, tp._context("rs", dy2.shape[0], k, dy2.device), s_local * tp.size,
+                                            w_kn=True).view(b, s_local, k)
+            else:
+                dx_full = kc.gemm(dy2, w, a_kmajor=True, b_kmajor=False).view(b, s_local * tp.size, k)
+                dx = _reduce_scatter_dim(dx_full, 1, tp.group)
         wgrads = [None] * len(weights)
         if any(ctx.needs_input_grad[2:]):
             x_full = _all_gather_dim(x2.view(b, s_local, k), 1, tp.group).reshape(-1, k)
@@ -248,8 +254,9 @@ class _FusedColumnLinearFn(torch.autograd.Function):
 
 
 class _FusedRowLinearFn(torch.autograd.Function):
-    """out = reduce_scatter_seq(x @ Wᵀ) with the tiles pushed to their owners from the GEMM epilogue.  The backward
-    all-gathers the output gradient with the library and runs plain GEMMs."""
+    """out = reduce_scatter_seq(x @ Wᵀ) with the tiles pushed to their owners from the GEMM epilogue.  Backward: the
+    input gradient gathers the output gradient inside its GEMM (``kf_ag_gemm``); the weight gradient uses a library
+    all-gather and a plain GEMM."""
 
     @staticmethod
     def forward(ctx, x, tp, weight):
@@ -272,9 +279,23 @@ class _FusedRowLinearFn(torch.autograd.Function):
 
         x2, weight = ctx.saved_tensors
         tp, (b, s, k, d) = ctx.tp, ctx.dims
-        dy_full = _all_gather_dim(dy, 1, tp.group).reshape(b * s, d)
-        dx = kc.gemm(dy_full, weight, a_kmajor=True, b_kmajor=False).view(b, s, k) if ctx.needs_input_grad[0] else None
-        (gw,) = F._linear_weight_grads(kc, dy_full, x2, [weight], [ctx.needs_input_grad[2]])
+        dx = None
+        dy_full = None
+        if ctx.needs_input_grad[0]:
+            if d % 64 == 0 and k % 8 == 0:
+                # dx = gather_seq(dy) @ W with the gather inside the GEMM (W read with its input dim contiguous)
+                dy2 = dy.reshape(-1, d)
+                if not dy2.is_contiguous():
+                    dy2 = dy2.contiguous()
+                dx = kc.all_gather_gemm(dy2, weight, tp._context("ag", b * s, d, dy.device), s, w_kn=True).view(b, s, k)
+            else:
+                dy_full = _all_gather_dim(dy, 1, tp.group).reshape(b * s, d)
+                dx = kc.gemm(dy_full, weight, a_kmajor=True, b_kmajor=False).view(b, s, k)
+        gw = None
+        if ctx.needs_input_grad[2]:
+            if dy_full is None:
+                dy_full = _all_gather_dim(dy, 1, tp.group).reshape(b * s, d)
+            (gw,) = F._linear_weight_grads(kc, dy_full, x2, [weight], [True])
         return dx, None, gw
 
 

@@ -85,7 +85,7 @@ dist.init_process_group("nccl")
 from kempnerforge_b200.comm.fused_tp import GemmRSContext
 from kempnerforge_b200.ops import cuda as K
 dev = torch.device("cuda")
-B, S, D, Kl = 2, 128 * world * 2, 768, 320
+B, S, D, Kl = 2, 128 * world * 2, 768, 320  # Kl is a multiple of 64 (needed by the (K, D) layout)
 T = B * S
 ctx = GemmRSContext(dist.group.WORLD, dev, T, D)
 errs = []
@@ -94,7 +94,10 @@ for call in range(5):
     x = torch.randn(T, Kl, device=dev, dtype=torch.bfloat16, generator=g)
     w = torch.randn(D, Kl, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
     res = torch.randn(T // world, D, device=dev, dtype=torch.bfloat16, generator=g) if call % 2 else None
-    out = K.gemm_reduce_scatter(x, w, ctx, S, residual=res)
+    if call % 2 == 0:
+        out = K.gemm_reduce_scatter(x, w, ctx, S, residual=res)
+    else:  # the same product with the weight stored (K, D): the layout of the input-gradient GEMM
+        out = K.gemm_reduce_scatter(x, w.t().contiguous(), ctx, S, residual=res, w_kn=True)
     full = (x.float() @ w.float().t())
     dist.all_reduce(full)
     mine = full.view(B, world, S // world, D)[:, rank].reshape(T // world, D)
@@ -150,7 +153,10 @@ for call in range(5):
     g = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
     xs = torch.randn(T // world, Kd, device=dev, dtype=torch.bfloat16, generator=g)
     w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
-    out = K.all_gather_gemm(xs, w, ctx, S)
+    if call % 2 == 0:
+        out = K.all_gather_gemm(xs, w, ctx, S)
+    else:
+        out = K.all_gather_gemm(xs, w.t().contiguous(), ctx, S, w_kn=True)
     parts = [torch.empty_like(xs) for _ in range(world)]
     dist.all_gather(parts, xs)
     full = torch.stack([p.view(B, S // world, Kd) for p in parts], dim=1).reshape(T, Kd)
