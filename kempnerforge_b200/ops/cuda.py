@@ -73,6 +73,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_moe_combine_bf16": [vp, vp, vp, i, i, i, vp, vp],
         "kf_moe_combine_bwd_bf16": [vp, vp, vp, vp, i, i, i, vp, vp, vp],
         "kf_grouped_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
+        "kf_grouped_wgrad_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, vp],
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
@@ -545,6 +546,28 @@ def grouped_gemm_supported(a: torch.Tensor, b: torch.Tensor, b_mn: bool) -> bool
     n = b.shape[2] if b_mn else b.shape[1]
     return (b.shape[0] <= 256 and k % 8 == 0 and n % 8 == 0 and (not b_mn or k % 64 == 0) and a.stride(1) == 1
             and a.stride(0) % 8 == 0 and b.is_contiguous())
+
+
+def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """Per-expert ``a_e^T @ b_e`` over the ragged row ranges ``offsets[e]:offsets[e+1]``: (E, a.shape[1], b.shape[1])
+    in bf16.  The weight gradient of :func:`grouped_gemm`; experts without rows get zeros."""
+    rows, m = a.shape
+    n = b.shape[1]
+    e = offsets.numel() - 1
+    assert b.shape[0] == rows and a.stride(1) == 1 and b.stride(1) == 1 and offsets.dtype == torch.int32
+    out = torch.empty((e, m, n), dtype=torch.bfloat16, device=a.device)
+    _check(lib().kf_grouped_wgrad_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), rows, e, m, n,
+                                       a.stride(0), b.stride(0), sm_count(), _stream()), "kf_grouped_wgrad_bf16")
+    return out
+
+
+def grouped_wgrad_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    if os.environ.get("KF_GROUPED_WGRAD", "0") != "1":
+        return False
+    if getattr(lib(), "kf_grouped_wgrad_bf16", None) is None or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        return False
+    return (a.shape[0] > 0 and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and a.stride(1) == 1 and b.stride(1) == 1
+            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0)
 
 
 def all_gather_gemm(x_shard: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, out: torch.Tensor | None = None,

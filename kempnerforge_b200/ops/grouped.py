@@ -28,8 +28,8 @@ def stack_expert_weights(weights: list[torch.Tensor]) -> torch.Tensor:
 
 
 class _GroupedLinearFn(torch.autograd.Function):
-    """Ragged grouped Linear on the tcgen05 grouped GEMM: forward and input gradient native, weight gradient
-    (a reduction over each expert's ragged token range) through ``torch._grouped_mm``."""
+    """Ragged grouped Linear on the tcgen05 grouped GEMMs: forward, input gradient and weight gradient (a reduction
+    over each expert's ragged token range, its tail rows masked inside the kernel)."""
 
     @staticmethod
     def forward(ctx, x, w, offsets, layout):
@@ -50,11 +50,11 @@ class _GroupedLinearFn(torch.autograd.Function):
             # 'nk': W_e is (N, K): dx = dy @ W_e reads W with the output dim (K) contiguous; 'kn': W_e is (K, N): dx = dy @ W_e^T
             dx = kc.grouped_gemm(dy, w, offsets, b_mn=(layout == "nk"))
         if ctx.needs_input_grad[1]:
-            offs = offsets[1:]
-            if layout == "kn":
-                dw = torch._grouped_mm(x.t(), dy, offs=offs)      # (E, K, N)
+            a, b = (x, dy) if layout == "kn" else (dy, x)         # (E, K, N) or (E, N, K)
+            if kc.grouped_wgrad_supported(a, b):
+                dw = kc.grouped_wgrad(a, b, offsets)
             else:
-                dw = torch._grouped_mm(dy.t(), x, offs=offs)      # (E, N, K)
+                dw = torch._grouped_mm(a.t(), b, offs=offsets[1:])
         return dx, dw, None, None
 
 

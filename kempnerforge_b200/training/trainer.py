@@ -79,6 +79,15 @@ class SyntheticTokens:
         self.batches_yielded = state.get("batches_yielded", 0)
 
 
+def phase_weights(phase, names: list[str], sources) -> list[float]:
+    """Mixture weights of a training phase in dataset order: the phase's value for a dataset it names, the
+    configured weight otherwise (scripts/train.py:613-632, 904-915 of the reference)."""
+    configured = [src.weight for src in sources]
+    if len(configured) != len(names):
+        configured = [1.0] * len(names)
+    return [float(phase.dataset_weights.get(name, w)) for name, w in zip(names, configured)]
+
+
 class Trainer:
     def __init__(self, config: JobConfig, hooks: list | None = None, model=None, dataloader=None,
                  init_dist: bool = True, transport: str | None = None) -> None:
@@ -315,8 +324,10 @@ class Trainer:
                 ph = self.phases[new_idx]
                 log.info("Entering data phase %d at step %d (lr_scale=%s)", new_idx, self.step, ph.lr_scale)
                 sampler = getattr(self.dataloader, "sampler", None)
-                if ph.dataset_weights and hasattr(sampler, "update_weights"):
-                    sampler.update_weights(ph.dataset_weights)
+                names = getattr(getattr(self.dataloader, "dataset", None), "dataset_names", None)
+                if ph.dataset_weights and names and hasattr(sampler, "update_weights"):
+                    sampler.update_weights(phase_weights(ph, names, self.config.data.datasets),
+                                           self.config.data.mix_temperature)
                     self._data_iter = None
 
     # ------------------------------------------------------------------ full run

@@ -474,6 +474,28 @@ def test_grouped_gemm_forward_backward(native_lib, counts, layout):
     _close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [1000, 24], [0, 0, 513], [64, 63, 65]])
+def test_grouped_wgrad_matches_per_expert_products(native_lib, counts):
+    """Ragged reduction ranges: rows of the next expert, and NaN rows past the last expert, must not leak in."""
+    torch.manual_seed(0)
+    m, n = 200, 328
+    rows = sum(counts)
+    pad = 70
+    a = _rand(rows + pad, m)
+    b = _rand(rows + pad, n)
+    a[rows:] = float("nan")
+    b[rows:] = float("nan")
+    offsets = torch.zeros(len(counts) + 1, dtype=torch.int32, device="cuda")
+    offsets[1:] = torch.tensor(counts, device="cuda").cumsum(0)
+    got = native_lib.grouped_wgrad(a, b, offsets)
+    assert native_lib.read_status() == 0
+    start = 0
+    for e, c in enumerate(counts):
+        want = a[start:start + c].float().t() @ b[start:start + c].float()
+        _close(got[e], want, rtol=3e-2, atol=3e-2)
+        start += c
+
+
 # --------------------------------------------------------------------------- MoE routing / sort / gather / combine
 @pytest.mark.parametrize("sigmoid", [False, True])
 @pytest.mark.parametrize("shape", [(64, 8, 2), (1000, 64, 6), (333, 160, 8)])
