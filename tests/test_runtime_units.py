@@ -1,0 +1,194 @@
+"""Collective deadlines with a fake work handle, seeding rules, memory-map lifetime, GPU health probe on CPU,
+environment checker.
+
+Mirrors tests/unit/test_collective_timeouts.py, test_distributed_seed.py, test_dataset_mmap_cleanup.py and
+test_check_env.py of the reference (failures are produced on the host: a fake of the failing call).
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import random
+import sys
+from datetime import timedelta
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+
+from kempnerforge_b200.data.dataset import MemoryMappedDataset
+from kempnerforge_b200.parallel import setup as kf_setup
+from kempnerforge_b200.resilience import health
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+class _Work:
+    def __init__(self, result=True, raises=None):
+        self.result, self.raises, self.seen = result, raises, None
+
+    def wait(self, timeout=None):
+        self.seen = timeout
+        if self.raises:
+            raise self.raises
+        return self.result
+
+
+def _fake_group(monkeypatch, work, world=2):
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: world)
+    monkeypatch.setattr(dist, "get_backend", lambda group=None: "gloo")
+
+    def all_reduce(t, group=None, async_op=False):
+        t.fill_(world)
+        return work
+
+    monkeypatch.setattr(dist, "all_reduce", all_reduce)
+    monkeypatch.setattr(dist, "barrier", lambda group=None, async_op=False: work)
+
+
+# --------------------------------------------------------------------------- deadlines
+def test_health_check_passes_the_deadline_to_wait(monkeypatch):
+    w = _Work(True)
+    _fake_group(monkeypatch, w)
+    assert health.check_nccl_health(timeout_sec=2.5) is True
+    assert w.seen == timedelta(seconds=2.5)
+
+
+def test_health_check_false_when_wait_times_out_or_raises(monkeypatch):
+    _fake_group(monkeypatch, _Work(False))
+    assert health.check_nccl_health(timeout_sec=0.1) is False
+    _fake_group(monkeypatch, _Work(raises=RuntimeError("peer went away")))
+    assert health.check_nccl_health(timeout_sec=0.1) is False
+
+
+def test_health_check_false_on_a_wrong_sum(monkeypatch):
+    w = _Work(True)
+    _fake_group(monkeypatch, w, world=2)
+    monkeypatch.setattr(dist, "all_reduce", lambda t, group=None, async_op=False: (t.fill_(1.0), w)[1])
+    assert health.check_nccl_health(timeout_sec=0.1) is False
+
+
+def test_health_check_true_without_a_process_group(monkeypatch):
+    monkeypatch.setattr(dist, "is_initialized", lambda: False)
+    assert health.check_nccl_health() is True
+
+
+def test_barrier_with_timeout_raises_with_the_reason(monkeypatch):
+    w = _Work(False)
+    _fake_group(monkeypatch, w)
+    with pytest.raises(RuntimeError, match="timed out after 0.25"):
+        kf_setup.barrier_with_timeout(0.25)
+    assert w.seen == timedelta(seconds=0.25)
+    _fake_group(monkeypatch, _Work(True))
+    kf_setup.barrier_with_timeout(0.25)  # returns normally
+
+
+def test_gpu_health_probe_never_raises_on_cpu(monkeypatch):
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    out = health.check_gpu_health()
+    assert out["healthy"] is False and "CUDA" in out["error"]
+    assert health.check_native_kernel_status() == 0
+
+
+# --------------------------------------------------------------------------- seeding
+def _draws():
+    return random.random(), float(np.random.rand()), float(torch.rand(1))
+
+
+def test_set_seed_covers_python_numpy_and_torch():
+    kf_setup.set_seed(123)
+    a = _draws()
+    kf_setup.set_seed(123)
+    assert _draws() == a
+    kf_setup.set_seed(124)
+    b = _draws()
+    assert all(x != y for x, y in zip(a, b))
+
+
+def test_set_seed_differs_per_pipeline_stage_only():
+    kf_setup.set_seed(7, pp_rank=0)
+    a = _draws()
+    kf_setup.set_seed(7, pp_rank=1)
+    b = _draws()
+    assert a != b
+    kf_setup.set_seed(8, pp_rank=0)  # seed + pp_rank is what counts
+    assert _draws() == b
+
+
+# --------------------------------------------------------------------------- memory maps
+def _write_shards(d: Path, n=3, tokens=64):
+    for i in range(n):
+        np.save(d / f"s{i}.npy", np.arange(tokens, dtype=np.uint16) + i)
+
+
+def test_mmap_dataset_close_is_idempotent(tmp_path):
+    _write_shards(tmp_path)
+    ds = MemoryMappedDataset(str(tmp_path), seq_len=16)
+    assert len(ds) == 12 and len(ds._maps) == 3
+    ds.close()
+    assert ds._maps == []
+    ds.close()
+
+
+def test_mmap_dataset_releases_earlier_maps_when_a_later_file_is_bad(tmp_path, monkeypatch):
+    _write_shards(tmp_path)
+    opened, closed = [], []
+    real_load = np.load
+
+    def load(path, *a, **k):
+        if path.endswith("s2.npy"):
+            raise OSError("truncated shard")
+        arr = real_load(path, *a, **k)
+        opened.append(arr)
+        return arr
+
+    monkeypatch.setattr(np, "load", load)
+    real_close = MemoryMappedDataset.close
+
+    def close(self):
+        closed.append(len(self._maps))
+        real_close(self)
+
+    monkeypatch.setattr(MemoryMappedDataset, "close", close)
+    with pytest.raises(OSError, match="truncated"):
+        MemoryMappedDataset(str(tmp_path), seq_len=16)
+    assert len(opened) == 2 and closed and closed[0] == 2
+
+
+def test_mmap_dataset_bin_files_and_missing_dir(tmp_path):
+    (np.arange(40, dtype=np.uint16)).tofile(tmp_path / "a.bin")       # 80 bytes -> divisible by 4 -> read as uint32
+    ds = MemoryMappedDataset(str(tmp_path), seq_len=5, file_pattern="*.bin")
+    assert len(ds) == 4
+    ds.close()
+    with pytest.raises(FileNotFoundError):
+        MemoryMappedDataset(str(tmp_path), seq_len=5, file_pattern="*.none")
+
+
+# --------------------------------------------------------------------------- environment checker
+def _check_env():
+    spec = importlib.util.spec_from_file_location("kf_check_env", ROOT / "scripts" / "check_env.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["kf_check_env"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_check_env_sections_report_without_a_gpu(tmp_path):
+    ce = _check_env()
+    for fn in (ce.check_python, ce.check_torch, ce.check_native, ce.check_gpus, ce.check_slurm, ce.check_layout,
+               ce.check_optional):
+        out = fn()
+        assert isinstance(out, dict) and out
+    fs = ce.check_filesystem(str(tmp_path))
+    assert isinstance(fs, dict)
+    assert isinstance(ce.check_filesystem(None), dict)
+
+
+def test_check_env_main_returns_an_exit_code(capsys):
+    ce = _check_env()
+    rc = ce.main([])
+    out = capsys.readouterr().out
+    assert rc in (0, 1) and "python" in out.lower() and "torch" in out.lower()
