@@ -13,6 +13,7 @@
 // kempnerforge/distributed/parallel.py:125-174): e4m3 for activations and weights, e5m2 for gradients.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include "tile_math.h"
 #include <cuda_fp8.h>
 
 namespace kf {
@@ -47,14 +48,8 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
       : "memory");
 }
 
-__device__ __forceinline__ void tile_coord(int t, int m_blocks, int n_blocks, int& tm, int& tn) {
-  const int per_group = GROUP_M * n_blocks;
-  const int g = t / per_group;
-  const int first_m = g * GROUP_M;
-  const int rows = min(GROUP_M, m_blocks - first_m);
-  const int r = t - g * per_group;
-  tm = first_m + r % rows;
-  tn = r / rows;
+__device__ __forceinline__ void tile_coord(int t, int m_blocks, int n_blocks, int& tile_m, int& tile_n) {
+  tilemath::raster(t, m_blocks, n_blocks, GROUP_M, tile_m, tile_n);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)

@@ -17,6 +17,7 @@
 // kempnerforge/model/mlp.py:26, kempnerforge/model/embedding.py:51) and their backward.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include "tile_math.h"
 
 namespace kf {
 
@@ -38,12 +39,9 @@ struct TileCoord {
 };
 
 __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_blocks) {
-  const int per_group = GROUP_M * n_blocks;
-  const int g = t / per_group;
-  const int first_m = g * GROUP_M;
-  const int rows = min(GROUP_M, m_blocks - first_m);
-  const int r = t - g * per_group;
-  return {first_m + r % rows, r / rows};
+  TileCoord tc;
+  tilemath::raster(t, m_blocks, n_blocks, GROUP_M, tc.m, tc.n);
+  return tc;
 }
 
 template <bool A_MN, bool B_MN, typename OutT>

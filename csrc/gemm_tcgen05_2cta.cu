@@ -16,6 +16,7 @@
 // TMA loads carry no cluster multicast; every CTA fetches its own operands.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include "tile_math.h"
 
 namespace kf2 {
 
@@ -94,12 +95,9 @@ struct TileCoord {
   int m, n;
 };
 __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_blocks) {
-  const int per_group = GROUP_M * n_blocks;
-  const int g = t / per_group;
-  const int first_m = g * GROUP_M;
-  const int rows = min(GROUP_M, m_blocks - first_m);
-  const int r = t - g * per_group;
-  return {first_m + r % rows, r / rows};
+  TileCoord tc;
+  tilemath::raster(t, m_blocks, n_blocks, GROUP_M, tc.m, tc.n);
+  return tc;
 }
 
 // SWIGLU != 0 (bf16, K-major operands only): B is the stacked [gate ; up] weight of a SwiGLU MLP with F = N rows

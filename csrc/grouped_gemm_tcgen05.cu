@@ -16,6 +16,7 @@
 // (kempnerforge/model/moe.py:20-145).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include "tile_math.h"
 
 namespace kf {
 namespace grp {
@@ -26,26 +27,10 @@ constexpr int THREADS = 192, TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 256;
 constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + (MAX_EXPERTS + 1) * 4;
 
-struct Tile {
-  int e, row0, valid, nb;
-};
+using Tile = tilemath::GroupedTile;
 
-// tile_start[e] = number of 128-row tiles of experts 0..e-1 (tile_start[E] = total)
 __device__ __forceinline__ Tile decode(int t, int n_blocks, const int* tile_start, const int* offsets, int E) {
-  const int nb = t % n_blocks;
-  const int tm = t / n_blocks;
-  int lo = 0, hi = E;  // largest e with tile_start[e] <= tm
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (tile_start[mid] <= tm) lo = mid; else hi = mid;
-  }
-  Tile x;
-  x.e = lo;
-  const int mb = tm - tile_start[lo];
-  x.row0 = offsets[lo] + mb * BM;
-  x.valid = min(BM, offsets[lo + 1] - x.row0);
-  x.nb = nb;
-  return x;
+  return tilemath::grouped_decode(t, n_blocks, tile_start, offsets, E, BM);
 }
 
 template <bool B_MN>
@@ -77,12 +62,7 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
-    int acc = 0;
-    for (int e = 0; e < E; ++e) {
-      tile_start[e] = acc;
-      acc += (offsets[e + 1] - offsets[e] + BM - 1) / BM;
-    }
-    tile_start[E] = acc;
+    tilemath::grouped_tile_starts(offsets, E, BM, tile_start);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();

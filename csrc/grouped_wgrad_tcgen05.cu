@@ -17,6 +17,7 @@
 // call of the reference (kempnerforge/model/moe.py:20-145).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include "tile_math.h"
 
 namespace kf {
 namespace gwg {
@@ -28,20 +29,10 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int THREADS = 192, TMEM_COLS = 512;
 constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
 
-struct Tile {
-  int e, m0, n0, row0, rows;
-};
+using Tile = tilemath::WgradTile;
 
 __device__ __forceinline__ Tile decode(int t, int m_blocks, int n_blocks, const int* offsets) {
-  Tile x;
-  const int per_e = m_blocks * n_blocks;
-  x.e = t / per_e;
-  const int r = t - x.e * per_e;
-  x.m0 = (r / n_blocks) * BM;
-  x.n0 = (r % n_blocks) * BN;
-  x.row0 = offsets[x.e];
-  x.rows = offsets[x.e + 1] - x.row0;
-  return x;
+  return tilemath::wgrad_decode(t, m_blocks, n_blocks, BM, BN, offsets);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -121,10 +112,9 @@ kf_grouped_wgrad_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid
         const int valid = tl.rows - kb * BK;
         if (valid < BK) {
           // rows valid..63 of every 64-column block belong to another expert (or to nobody): zero them
-          const int per_block = (BK - valid) * 8;  // 16-byte chunks
-          for (int i = lane; i < per_block * (STAGE_BYTES / BLOCK_BYTES); i += 32) {
-            const int blk = i / per_block, j = i - blk * per_block;
-            const uint32_t addr = a_src + blk * BLOCK_BYTES + valid * 128 + j * 16;
+          constexpr int BLOCKS = STAGE_BYTES / BLOCK_BYTES;
+          for (int i = lane; i < tilemath::tail_chunks(valid, BK, BLOCKS); i += 32) {
+            const uint32_t addr = a_src + tilemath::tail_chunk_offset(i, valid, BK, BLOCK_BYTES);
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
           }
           fence_async_smem();

@@ -548,14 +548,16 @@ def grouped_gemm_supported(a: torch.Tensor, b: torch.Tensor, b_mn: bool) -> bool
             and a.stride(0) % 8 == 0 and b.is_contiguous())
 
 
-def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Per-expert ``a_e^T @ b_e`` over the ragged row ranges ``offsets[e]:offsets[e+1]``: (E, a.shape[1], b.shape[1])
     in bf16.  The weight gradient of :func:`grouped_gemm`; experts without rows get zeros."""
     rows, m = a.shape
     n = b.shape[1]
     e = offsets.numel() - 1
     assert b.shape[0] == rows and a.stride(1) == 1 and b.stride(1) == 1 and offsets.dtype == torch.int32
-    out = torch.empty((e, m, n), dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.empty((e, m, n), dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (e, m, n) and out.is_contiguous() and out.dtype == torch.bfloat16
     _check(lib().kf_grouped_wgrad_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), rows, e, m, n,
                                        a.stride(0), b.stride(0), sm_count(), _stream()), "kf_grouped_wgrad_bf16")
     return out

@@ -496,6 +496,79 @@ def test_grouped_wgrad_matches_per_expert_products(native_lib, counts):
         start += c
 
 
+# --------------------------------------------------------------------------- memory safety without a sanitizer
+_SENTINEL = 12288.0  # exactly representable in bf16
+
+
+def _guarded(shape, dtype=torch.bfloat16, pad=4096):
+    """A tensor of ``shape`` carved out of a larger buffer whose margins hold a sentinel value."""
+    n = 1
+    for d in shape:
+        n *= d
+    flat = torch.full((n + 2 * pad,), _SENTINEL, dtype=dtype, device="cuda")
+    return flat, flat[pad:pad + n].view(*shape)
+
+
+def _margins_intact(flat, n, pad=4096):
+    return bool((flat[:pad] == _SENTINEL).all()) and bool((flat[pad + n:] == _SENTINEL).all())
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (130, 264, 72), (257, 520, 200), (1000, 136, 4096)])
+def test_gemm_ragged_shapes_stay_inside_their_output_and_repeat_bit_exactly(native_lib, mode, m, n, k):
+    torch.manual_seed(0)
+    a, b = _rand(m, k), _rand(n, k)
+    flat, out = _guarded((m, n))
+    native_lib.gemm(a, b, out=out, mode=mode)
+    assert native_lib.read_status() == 0 and _margins_intact(flat, m * n)
+    _close(out, a.float() @ b.float().t())
+    again = native_lib.gemm(a, b, mode=mode)
+    assert torch.equal(out, again)            # fixed reduction order: a difference would mean a race
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 300, 77, 130, 1], [0, 0, 513], [1]])
+def test_grouped_kernels_stay_inside_their_outputs_and_repeat_bit_exactly(native_lib, counts):
+    torch.manual_seed(0)
+    e, k, n = len(counts), 192, 328
+    rows = sum(counts)
+    x, w, g = _rand(rows, k), _rand(e, n, k, scale=0.05), _rand(rows, n)
+    offsets = torch.zeros(e + 1, dtype=torch.int32, device="cuda")
+    offsets[1:] = torch.tensor(counts, device="cuda").cumsum(0)
+    flat_y, y = _guarded((rows, n))
+    native_lib.grouped_gemm(x, w, offsets, b_mn=False, out=y)
+    flat_w, dw = _guarded((e, n, k))
+    native_lib.grouped_wgrad(g, x, offsets, out=dw)
+    assert native_lib.read_status() == 0
+    assert _margins_intact(flat_y, rows * n) and _margins_intact(flat_w, e * n * k)
+    assert torch.equal(y, native_lib.grouped_gemm(x, w, offsets, b_mn=False))
+    assert torch.equal(dw, native_lib.grouped_wgrad(g, x, offsets))
+    assert not torch.isnan(dw.float()).any() and not (dw == _SENTINEL).any()
+
+
+def test_row_kernels_stay_inside_their_outputs_and_repeat_bit_exactly(native_lib):
+    torch.manual_seed(0)
+    rows, d = 1003, 4096
+    x, w, dy = _rand(rows, d), _rand(d), _rand(rows, d)
+    y, rstd = native_lib.rmsnorm_fwd(x, w, 1e-5)
+    y2, rstd2 = native_lib.rmsnorm_fwd(x, w, 1e-5)
+    assert torch.equal(y, y2) and torch.equal(rstd, rstd2)
+    flat, dx = _guarded((rows, d))
+    dx1, dw1 = native_lib.rmsnorm_bwd(dy, x, w, rstd, out=dx)
+    dx2, dw2 = native_lib.rmsnorm_bwd(dy, x, w, rstd)
+    assert _margins_intact(flat, rows * d) and native_lib.read_status() == 0
+    assert torch.equal(dw1, dw2) and torch.equal(dx1, dx2)
+    gu = _rand(rows, 2 * 1408)
+    assert torch.equal(native_lib.swiglu_fwd(gu), native_lib.swiglu_fwd(gu))
+
+
+def test_attention_forward_repeats_bit_exactly(native_lib):
+    torch.manual_seed(0)
+    q, k, v = _rand(1, 384, 8, 128), _rand(1, 384, 2, 128), _rand(1, 384, 2, 128)
+    o1, l1 = native_lib.attn_fwd(q, k, v, True, None, 128 ** -0.5)
+    o2, l2 = native_lib.attn_fwd(q, k, v, True, None, 128 ** -0.5)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2) and native_lib.read_status() == 0
+
+
 # --------------------------------------------------------------------------- MoE routing / sort / gather / combine
 @pytest.mark.parametrize("sigmoid", [False, True])
 @pytest.mark.parametrize("shape", [(64, 8, 2), (1000, 64, 6), (333, 160, 8)])
