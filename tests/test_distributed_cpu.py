@@ -83,10 +83,10 @@ def _single_process_reference(model_cfg, batches_per_step, steps=2, accum=1):
 
 
 # ------------------------------------------------------------------ workers
-def _dp_worker(rank, world, model_cfg, steps):
+def _dp_worker(rank, world, model_cfg, steps, dims=None):
     from kempnerforge_b200.training.trainer import Trainer
 
-    t = Trainer(_job(model_cfg, {"dp_shard": world}))
+    t = Trainer(_job(model_cfg, dims or {"dp_shard": world}))
     data = _batches(world * steps)
     traj = [t.train_step([data[s * world + rank]]) for s in range(steps)]
     return traj, {n: p.detach().clone() for n, p in t.model.named_parameters()}
@@ -159,6 +159,20 @@ def test_sharded_data_parallel_matches_single_process(world):
         assert _close(mean_loss, ref_traj[s]["loss"])
         assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
     for r in results:  # every rank ends with the same, correct weights
+        for n, p in r[1].items():
+            assert torch.allclose(p, ref_params[n], atol=2e-5), n
+
+
+def test_hybrid_sharded_data_parallel_matches_single_process():
+    """dp_replicate 2 x dp_shard 2: gradients are averaged over all four ranks and every rank ends with the same weights."""
+    steps, world = 2, 4
+    data = _batches(world * steps)
+    ref_traj, ref_params = _single_process_reference(TINY, [data[s * world : (s + 1) * world] for s in range(steps)])
+    results = run_ranks(_dp_worker, world, TINY, steps, {"dp_replicate": 2, "dp_shard": 2})
+    for s in range(steps):
+        assert _close(sum(r[0][s]["loss"] for r in results) / world, ref_traj[s]["loss"])
+        assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
+    for r in results:
         for n, p in r[1].items():
             assert torch.allclose(p, ref_params[n], atol=2e-5), n
 
