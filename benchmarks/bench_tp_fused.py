@@ -2,7 +2,10 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/bench_tp_fused.py
 """
-import os, sys, torch, json
+import os
+import sys
+
+import torch
 import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])

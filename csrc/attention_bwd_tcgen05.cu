@@ -41,8 +41,11 @@ constexpr int Q_TILE_BYTES = BLK_Q * HD * 2;    // 16 KB: two blocks of [64 rows
 constexpr int Q_BLOCK_BYTES = BLK_Q * 128;      // 8 KB
 constexpr int DS_BYTES = BLK_K * BLK_Q * 2;     // 16 KB: [128 key rows x 128 B]
 constexpr int STAGES = 3;  // Q_i / dO_i ring: a tile is loaded one whole iteration before its scores are issued
+constexpr int AUX_BYTES = 2048;  // barriers, row statistics, doc ids
 constexpr size_t SMEM = 2 * size_t(KV_TILE_BYTES) + STAGES * 2 * size_t(Q_TILE_BYTES) + 2 * DS_BYTES + 1024 /*align*/ +
-                        2048 /*barriers, row statistics, doc ids*/;
+                        AUX_BYTES;
+constexpr int DQ_STAGE_BYTES = BLK_Q * HD * 4;  // 32 KB: one dQ tile [64 queries][128] fp32 for the bulk reduction
+constexpr size_t SMEM_DQ_TMA = SMEM + DQ_STAGE_BYTES;
 
 __device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -72,11 +75,21 @@ __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
+// fp32 tile in shared memory (row-major, the tensor map's box) added to global memory by the TMA unit
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+               "r"(x), "r"(y), "r"(smem_src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <bool CAUSAL, bool HAS_DOC>
 __global__ void __launch_bounds__(THREADS, 1)
 kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                    const float* __restrict__ LSE, const float* __restrict__ Dsum, const int* __restrict__ doc_ids,
+                    const __grid_constant__ CUtensorMap map_dq, int dq_tma, const float* __restrict__ LSE, const float* __restrict__ Dsum, const int* __restrict__ doc_ids,
                     float* __restrict__ dQacc, __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV, int Sq,
                     int Sk, int H, int group, long long lddk, long long lddv, float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -101,6 +114,7 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_gen + 128);
   float* stat_smem = reinterpret_cast<float*>(bar_gen + 256);       // [2][lse2 | D][64]
   int* docq_smem = reinterpret_cast<int*>(bar_gen + 256 + 1024);    // [2][64]
+  const uint32_t dq_stage = bar_base + AUX_BYTES;                   // only allocated when dq_tma
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -372,6 +386,7 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int quarter = warp & 3;
     const int d = quarter * 32 + lane;  // head-dim index = TMEM lane of dQ^T
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const bool elected = threadIdx.x == 192;  // issues, commits and waits for the bulk reductions
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int hq = hk * group + it / n_i;
@@ -385,13 +400,29 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);  // the values are in registers: the next dQ^T may be computed
-      if (ok) {
+      if (dq_tma) {
+        // transpose through shared memory into the [query][head dim] tile the tensor map describes, then one
+        // bulk reduction adds the whole tile; rows past the end of the tensor are clipped by the TMA unit, rows
+        // of padding queries hold exact zeros
+        if (elected) bulk_wait_read_all();  // the previous reduction has read the staging tile
+        group_sync(2, 128);
+#pragma unroll
+        for (int c = 0; c < BLK_Q; ++c)
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(dq_stage + uint32_t(c * HD + d) * 4u), "r"(v[c]) : "memory");
+        fence_async_smem();
+        group_sync(2, 128);
+        if (elected && ok) {
+          tma_reduce_add_2d(&map_dq, dq_stage, hq * HD, b * Sq + q0);
+          bulk_commit();
+        }
+      } else if (ok) {
         float* base = dQacc + ((size_t(b) * Sq + q0) * H + hq) * HD + d;
 #pragma unroll
         for (int c = 0; c < BLK_Q; ++c)
           if (q0 + c < Sq) red_add_f32(base + size_t(c) * H * HD, __uint_as_float(v[c]));
       }
     }
+    if (dq_tma && elected) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -447,7 +478,36 @@ __global__ void kf_f32_to_bf16_rows(const float* __restrict__ src, __nv_bfloat16
 
 extern "C" void* kf_status_device_ptr();
 
+namespace kf {
+namespace attnb {
+static int g_dq_mode = 0;  // 0: red.global per element, 1: bulk tensor reduction from shared memory
+
+// fp32 [rows][cols] row-major -> tensor map with an unswizzled (box_cols x box_rows) box
+inline int make_map_2d_f32_plain(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                                 uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 4};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+}  // namespace attnb
+}  // namespace kf
+
 extern "C" {
+
+// How the backward kernel adds its dQ tiles to the fp32 accumulator: 0 = red.global per element (default),
+// 1 = one bulk tensor reduction per tile.  Returns the previous mode.
+int kf_attn_bwd_dq_mode(int mode) {
+  const int prev = kf::attnb::g_dq_mode;
+  if (mode == 0 || mode == 1) kf::attnb::g_dq_mode = mode;
+  return prev;
+}
 
 // Backward attention (head dim 128).  q / k / v / o / do: rows (b * S + s) with pitches ld*, heads side by
 // side; lse: fp32 [B][H][Sq] from the forward; dsum: fp32 scratch [B][H][Sq]; dq_acc: fp32 scratch
@@ -473,6 +533,11 @@ int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o,
   if (rc) return 250 + rc;
   rc = make_map_2d_bf16(&mdo, d_o, uint64_t(B) * Sq, uint64_t(H) * hd, lddo, 64, BLK_Q);
   if (rc) return 270 + rc;
+  const int dq_tma = g_dq_mode;
+  CUtensorMap mdq;
+  rc = make_map_2d_f32_plain(&mdq, dq_acc, uint64_t(B) * Sq, uint64_t(H) * hd, HD, BLK_Q);
+  if (rc) return 280 + rc;
+  const size_t smem_bytes = dq_tma ? SMEM_DQ_TMA : SMEM;
   // pre-pass: D = rowsum(dO * O); zero the fp32 dQ accumulator
   {
     const long long rows = (long long)B * Sq * H;
@@ -491,11 +556,11 @@ int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o,
     auto kern = kf_attn_bwd_tcgen05<C_, D_>;                                                                       \
     static bool attr_set = false;                                                                                  \
     if (!attr_set) {                                                                                               \
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DQ_TMA);   \
       if (e != cudaSuccess) return 300 + (int)e;                                                                   \
       attr_set = true;                                                                                             \
     }                                                                                                              \
-    kern<<<grid, THREADS, SMEM, st>>>(mq, mk, mv, mdo, reinterpret_cast<const float*>(lse),                        \
+    kern<<<grid, THREADS, smem_bytes, st>>>(mq, mk, mv, mdo, mdq, dq_tma, reinterpret_cast<const float*>(lse),     \
                                       reinterpret_cast<const float*>(dsum), reinterpret_cast<const int*>(doc),     \
                                       reinterpret_cast<float*>(dq_acc), reinterpret_cast<__nv_bfloat16*>(dk),      \
                                       reinterpret_cast<__nv_bfloat16*>(dv), Sq, Sk, H, H / Hkv, lddk, lddv, scale, \

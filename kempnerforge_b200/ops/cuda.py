@@ -35,6 +35,8 @@ def lib() -> ctypes.CDLL:
             )
         _lib = ctypes.CDLL(str(LIB_PATH))
         _declare(_lib)
+        if os.environ.get("KF_ATTN_BWD_DQ", "") == "tma" and hasattr(_lib, "kf_attn_bwd_dq_mode"):
+            _lib.kf_attn_bwd_dq_mode(1)
     return _lib
 
 
@@ -77,6 +79,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
+        "kf_attn_bwd_dq_mode": [i],
         "kf_attn_fwd2_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
@@ -612,6 +615,13 @@ def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, ou
         "kf_gemm_rs_bf16",
     )
     return out
+
+
+def attn_bwd_dq_mode(mode: int) -> int:
+    """How the attention backward adds its dQ tiles to the fp32 accumulator: 0 = one ``red.global`` per element,
+    1 = one bulk tensor reduction (TMA) per tile staged in shared memory.  Returns the previous mode.  The default
+    comes from ``KF_ATTN_BWD_DQ`` (``tma`` selects 1)."""
+    return int(lib().kf_attn_bwd_dq_mode(int(mode)))
 
 
 def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=None, dk=None, dv=None):

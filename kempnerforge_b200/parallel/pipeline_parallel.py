@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import torch
 import torch.distributed as dist
-from torch import nn
 
 from kempnerforge_b200.models.modality import ModalityContext
 from kempnerforge_b200.models.transformer import Transformer

@@ -20,8 +20,6 @@ final checkpoints, log strings ``Starting training: step=``, ``Training complete
 
 from __future__ import annotations
 
-import math
-import time
 from collections.abc import Iterator
 from typing import Any
 

@@ -396,9 +396,17 @@ def _attn_reference_grads(q, k, v, dout, causal, doc=None):
     return out.detach(), qf.grad, kf_.grad, vf.grad
 
 
+@pytest.fixture(params=[0, 1], ids=["dq_red", "dq_bulk_reduce"])
+def dq_mode(native_lib, request):
+    """Both ways the backward kernel accumulates dQ: per-element reductions and one bulk tensor reduction per tile."""
+    prev = native_lib.attn_bwd_dq_mode(request.param)
+    yield request.param
+    native_lib.attn_bwd_dq_mode(prev)
+
+
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 384, 4, 1), (2, 200, 2, 2), (1, 1024, 8, 2)])
-def test_attention_backward_matches_fp32_reference(native_lib, shape, causal):
+def test_attention_backward_matches_fp32_reference(native_lib, shape, causal, dq_mode):
     b, s, h, hkv = shape
     hd = 128
     q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=11)
@@ -413,7 +421,7 @@ def test_attention_backward_matches_fp32_reference(native_lib, shape, causal):
         assert rel < 2e-2, (name, rel.item())
 
 
-def test_attention_backward_document_mask_into_fused_gradient(native_lib):
+def test_attention_backward_document_mask_into_fused_gradient(native_lib, dq_mode):
     b, s, h, hkv, hd = 2, 512, 4, 2, 128
     q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=13)
     cuts = torch.tensor([[0, 100, 130, 400], [0, 256, 300, 301]], device="cuda")
