@@ -3,8 +3,8 @@
     python benchmarks/ncu_targets.py gemm                      # plain run first (must exit 0), then:
     ncu --set full --clock-control none -k regex:kf_gemm -s 2 -c 1 -o prof python benchmarks/ncu_targets.py gemm
 
-Targets: gemm (CTA-pair tiling, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu, grouped, attn_fwd, attn_bwd, rmsnorm_bwd,
-adamw.  Inputs are larger than the 126 MB L2 where the kernel is memory bound.
+Targets: gemm (CTA-pair tiling, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu, grouped, grouped_wgrad, attn_fwd, attn_bwd
+(attn_bwd_bulk: dQ by bulk tensor reductions), rmsnorm_bwd, adamw.  Inputs are larger than the 126 MB L2 where the kernel is memory bound.
 """
 
 from __future__ import annotations
@@ -40,7 +40,14 @@ def main() -> int:
         x = torch.randn(int(counts.sum()), 2048, device=dev, dtype=bf)
         w = torch.randn(8, 2048, 5632, device=dev, dtype=bf) * 0.02
         fn = lambda: K.grouped_gemm(x, w, offsets, b_mn=True)  # noqa: E731
-    elif target in ("attn_fwd", "attn_bwd"):
+    elif target == "grouped_wgrad":
+        counts = torch.tensor([4000, 5000, 3000, 4384, 4100, 3900, 4200, 4184], device=dev)
+        offsets = torch.zeros(9, dtype=torch.int32, device=dev)
+        offsets[1:] = counts.cumsum(0)
+        x = torch.randn(int(counts.sum()), 2048, device=dev, dtype=bf)
+        dy = torch.randn(int(counts.sum()), 5632, device=dev, dtype=bf)
+        fn = lambda: K.grouped_wgrad(x, dy, offsets)  # noqa: E731
+    elif target in ("attn_fwd", "attn_bwd", "attn_bwd_bulk"):
         b, s, h, hkv, hd = 2, 4096, 32, 8, 128
         qkv = torch.randn(b, s, h + 2 * hkv, hd, device=dev, dtype=bf)
         q, k, v = qkv[:, :, :h], qkv[:, :, h:h + hkv], qkv[:, :, h + hkv:]
@@ -48,6 +55,7 @@ def main() -> int:
         if target == "attn_fwd":
             fn = lambda: K.attn_fwd(q, k, v, True, None, sc)  # noqa: E731
         else:
+            K.attn_bwd_dq_mode(1 if target == "attn_bwd_bulk" else 0)
             out, lse = K.attn_fwd(q, k, v, True, None, sc)
             dout = torch.randn_like(out)
             fn = lambda: K.attn_bwd(dout, q, k, v, out, lse, True, None, sc)  # noqa: E731
