@@ -285,6 +285,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // The driver entry point is resolved at run time so that the library links without libcuda.
 inline EncodeTiledFn encode_tiled_fn() {
+  // cuTensorMapEncodeTiled is a driver call: it needs a context current on the calling thread, and a thread that
+  // has not yet made a runtime call (an autograd worker whose first native call builds a tensor map) has none.
+  // cudaFree(0) binds the current device's primary context; once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -567,7 +567,7 @@ def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, out: 
 
 
 def grouped_wgrad_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
-    if os.environ.get("KF_GROUPED_WGRAD", "0") != "1":
+    if os.environ.get("KF_GROUPED_WGRAD", "1") == "0":  # escape hatch: weight gradients through torch._grouped_mm
         return False
     if getattr(lib(), "kf_grouped_wgrad_bf16", None) is None or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         return False
