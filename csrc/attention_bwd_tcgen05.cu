@@ -119,9 +119,12 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_kv_tiles = gridDim.x;
-  const int kt = CAUSAL ? blockIdx.x : (n_kv_tiles - 1 - blockIdx.x);  // causal: early key tiles see most queries
-  const int hk = blockIdx.y, b = blockIdx.z;
+  // grid: x = (batch, KV head), y = key tile.  Blocks are handed out x-fastest, so with a causal mask all the
+  // heaviest key tiles (the earliest: every query sees them) start first and the lightest ones fill the tail.
+  const int n_kv_tiles = gridDim.y;
+  const int kt = CAUSAL ? blockIdx.y : (n_kv_tiles - 1 - blockIdx.y);
+  const int Hkv_ = H / group;
+  const int hk = blockIdx.x % Hkv_, b = blockIdx.x / Hkv_;
   const int k0 = kt * BLK_K;
   const int n_q_tiles = (Sq + BLK_Q - 1) / BLK_Q;
   const int i_start = CAUSAL ? min(n_q_tiles, k0 / BLK_Q) : 0;
@@ -551,7 +554,7 @@ int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o,
     if (e != cudaSuccess) return 400 + (int)e;
   }
   int* status = reinterpret_cast<int*>(kf_status_device_ptr());
-  dim3 grid((Sk + BLK_K - 1) / BLK_K, Hkv, B);
+  dim3 grid(Hkv * B, (Sk + BLK_K - 1) / BLK_K);
 #define KF_BWD_LAUNCH(C_, D_)                                                                                      \
   {                                                                                                                \
     auto kern = kf_attn_bwd_tcgen05<C_, D_>;                                                                       \
