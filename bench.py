@@ -41,7 +41,17 @@ MODELS = {
     "moe_8x": dict(dim=2048, n_layers=24, n_heads=16, n_kv_heads=16, vocab_size=102400, ffn_hidden_dim=5632,
                    max_seq_len=4096, rope_theta=500000.0, num_experts=8, moe_top_k=2, moe_router="softmax_topk",
                    moe_packed_experts=True),
-    # small shape for quick functional checks of this script (not a benchmark number)
+    # fine-grained MoE with DeepSeek-V3-style routing: 64 routed experts of 1408 (top-6) + 2 shared, sigmoid router with
+    # bias balancing and router z-loss, first layer dense (hidden 10944)
+    "moe_fine": dict(dim=2048, n_layers=24, n_heads=16, n_kv_heads=16, vocab_size=102400, ffn_hidden_dim=10944,
+                     max_seq_len=4096, rope_theta=500000.0, num_experts=64, moe_top_k=6, moe_router="sigmoid_topk",
+                     moe_shared_experts=2, moe_router_z_loss_weight=1e-3, moe_first_k_dense=1,
+                     moe_expert_ffn_multiplier=1408.0 / 10944.0, moe_packed_experts=True),
+    # small shapes for quick functional checks of this script (not benchmark numbers)
+    "tiny_moe": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536,
+                     max_seq_len=512, rope_theta=500000.0, num_experts=8, moe_top_k=2, moe_router="sigmoid_topk",
+                     moe_shared_experts=1, moe_router_z_loss_weight=1e-3, moe_first_k_dense=1,
+                     moe_expert_ffn_multiplier=0.25, moe_packed_experts=True),
     "tiny": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536,
                  max_seq_len=512, rope_theta=500000.0),
 }
@@ -60,6 +70,10 @@ def parse_args():
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (data parallel over the rest)")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree")
     ap.add_argument("--ep-in-dp", action="store_true", help="experts sharded over the data-parallel ranks (ours only)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (1F1B over --micro-batches)")
+    ap.add_argument("--micro-batches", type=int, default=1, help="micro-batches per optimizer step (gradient accumulation)")
+    ap.add_argument("--fp8", action="store_true", help="float8 Linear layers (tensorwise scaling)")
+    ap.add_argument("--optimizer", default="adamw", choices=("adamw", "muon"))
     return ap.parse_args()
 
 
@@ -67,15 +81,20 @@ def mesh_dims(args, world: int) -> tuple[dict, int, str]:
     """[distributed] fields, number of distinct batches per step, and a label such as "tp2xdp4"."""
     if args.ep > 1 and args.ep_in_dp:
         return {"ep": args.ep, "ep_in_dp": True, "dp_shard": world}, world, f"ep{args.ep}-in-dp{world}"
-    dp = world // (args.tp * args.ep)
+    dp = world // (args.tp * args.ep * args.pp)
     dims = {"dp_shard": dp}
     label = f"dp{dp}"
+    if args.pp > 1:
+        dims["pp"] = args.pp
+        dims["pp_schedule"] = "1f1b"
     if args.tp > 1:
         dims["tp"] = args.tp
         label = f"tp{args.tp}x" + label
     if args.ep > 1:
         dims["ep"] = args.ep
         label = f"ep{args.ep}x" + label
+    if args.pp > 1:
+        label = f"pp{args.pp}x" + label
     return dims, dp, label
 
 
@@ -170,10 +189,10 @@ def run_ours(args) -> dict:
     seq = args.seq_len or shape["max_seq_len"]
     cfg = config_from_dict({
         "model": shape,
-        "train": {"batch_size": args.batch_size, "seq_len": seq, "max_steps": 1000, "grad_accum_steps": 1,
-                  "mixed_precision": "bf16", "activation_checkpointing": "full", "compile_model": False,
-                  "grad_clip_norm": 1.0, "seed": 0},
-        "optimizer": {"name": "adamw", "lr": 3e-4, "weight_decay": 0.1, "fused": True},
+        "train": {"batch_size": args.batch_size, "seq_len": seq, "max_steps": 1000,
+                  "grad_accum_steps": args.micro_batches, "mixed_precision": "fp8" if args.fp8 else "bf16",
+                  "activation_checkpointing": "full", "compile_model": False, "grad_clip_norm": 1.0, "seed": 0},
+        "optimizer": {"name": args.optimizer, "lr": 3e-4, "weight_decay": 0.1, "fused": True},
         "scheduler": {"name": "cosine", "warmup_steps": 10},
         "distributed": mesh_dims(args, world)[0],
         "metrics": {"log_interval": 1000},
@@ -185,29 +204,36 @@ def run_ours(args) -> dict:
     vocab = shape["vocab_size"]
     gen = torch.Generator().manual_seed(1234 + trainer.dp_rank)  # ranks of one TP / EP group share their batch
 
-    def host_batch():
+    def host_micro():
         tok = torch.randint(0, vocab, (args.batch_size, seq + 1), generator=gen)
         return {"input_ids": tok[:, :-1].contiguous().pin_memory(), "labels": tok[:, 1:].contiguous().pin_memory()}
 
+    def host_batch():  # one optimizer step: --micro-batches micro-batches
+        return [host_micro() for _ in range(args.micro_batches)]
+
+    def on_device(step_batches):
+        return [{k: v.to(dev) for k, v in mb.items()} for mb in step_batches]
+
     # a different random batch for every step, so nothing can be memorised
-    warm = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(args.warmup)]
-    dev_batches = [{k: v.to(dev) for k, v in host_batch().items()} for _ in range(args.steps)]
+    warm = [on_device(host_batch()) for _ in range(args.warmup)]
+    dev_batches = [on_device(host_batch()) for _ in range(args.steps)]
     for b in warm:
-        trainer.train_step([b])
+        trainer.train_step(b)
     status = kcuda.read_status()
     if status != 0:
         raise RuntimeError(f"native kernel wait status {status} during warm-up")
 
     sampler = ClockSampler(local)
     launches0 = kcuda.LAUNCH_COUNT
-    ms, wall, last = timed_region(torch, dist, world, lambda i: trainer.train_step([dev_batches[i]]), args.steps)
+    ms, wall, last = timed_region(torch, dist, world, lambda i: trainer.train_step(dev_batches[i]), args.steps)
     launches = kcuda.LAUNCH_COUNT - launches0
     clocks = sampler.stop()
 
     host_batches = [host_batch() for _ in range(args.steps)]
-    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    h2d = sum(v.numel() * v.element_size() for mb in host_batches[0] for v in mb.values())
     ms_e2e, _, last_e2e = timed_region(torch, dist, world,
-                                       lambda i: trainer.train_step([host_batches[i]]), args.steps)
+                                       lambda i: trainer.train_step(host_batches[i]), args.steps)
+    n_batches *= args.micro_batches
     tokens_per_step = args.batch_size * seq * n_batches
     value = tokens_per_step / (ms / 1e3)
     e2e = tokens_per_step / (ms_e2e / 1e3)
@@ -225,9 +251,12 @@ def run_ours(args) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": (value / base) if (base and args.model == "llama3_8b" and mesh_label == f"dp{world}") else None,
-        "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
+        "dtype": "fp8 (E4M3 / E5M2 linear layers, bf16 elsewhere)" if args.fp8 else "bf16",
+        "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
         "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
-                   "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused",
+                   "parallelism": mesh_label, "activation_checkpointing": "full",
+                   "optimizer": "adamw_fused" if args.optimizer == "adamw" else "muon (Newton-Schulz 5) + adamw",
+                   "micro_batches": args.micro_batches,
                    "l2": "working set (>60 GB) far exceeds L2; no flush needed"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
@@ -272,6 +301,11 @@ def run_reference(args) -> dict:
     ]
     if args.ep_in_dp:
         return {"impl": "reference", "unavailable": "the reference cannot shard experts over its data-parallel ranks"}
+    if args.fp8:
+        return {"impl": "reference", "unavailable": "the reference's float8 path needs torchao, which is not installed"}
+    if args.pp > 1 or args.micro_batches > 1 or args.optimizer != "adamw" or shape.get("moe_first_k_dense"):
+        return {"impl": "reference", "unavailable": "this harness drives the reference's plain text step only "
+                "(no pipeline schedule / accumulation / Muon; moe_first_k_dense does not exist in the reference)"}
     dims, n_batches, mesh_label = mesh_dims(args, world)
     overrides += [f"--distributed.{k}={v}" for k, v in dims.items()]
     if shape.get("num_experts"):
