@@ -81,6 +81,7 @@ class SigmoidTopKRouter(nn.Module):
         self.bias_schedule = bias_schedule
         self._step = 0
         self._max_steps = 1
+        self._bias_fifo: list[torch.Tensor] = []  # biases used by checkpointed forward passes awaiting recomputation
         self.expert_bias = nn.Parameter(torch.zeros(num_experts))
         self.register_buffer("expert_ema", torch.full((num_experts,), 1.0 / num_experts))
         self.aux_loss = torch.tensor(0.0)
@@ -90,6 +91,7 @@ class SigmoidTopKRouter(nn.Module):
     def set_step(self, step: int, max_steps: int) -> None:
         self._step = step
         self._max_steps = max(1, max_steps)
+        self._bias_fifo.clear()  # every backward of the previous step has run
 
     def _effective_bias_rate(self) -> float:
         t = self._step / self._max_steps
@@ -100,23 +102,44 @@ class SigmoidTopKRouter(nn.Module):
         }.get(self.bias_schedule, 1.0)
         return self.bias_update_rate * shape
 
+    def _bias_for_this_pass(self) -> tuple[torch.Tensor, bool]:
+        """The balancing bias this pass routes with, and whether this pass may update the router's state.
+
+        Inside an activation-checkpointed block the forward runs twice.  The first pass records the bias it
+        used (it nudges the parameter right afterwards); the recomputation routes with that recorded value, so
+        both passes pick the same experts, and leaves the moving average and the bias alone.  First-in first-out
+        matches every schedule in which backward passes run in the order of their forward passes (plain
+        accumulation, GPipe, 1F1B)."""
+        from kempnerforge_b200.models import recompute
+
+        ph = recompute.phase()
+        if ph == "forward" and self.training:
+            self._bias_fifo.append(self.expert_bias.detach().clone())
+            return self.expert_bias, True
+        if ph == "recompute" and self._bias_fifo:
+            used = self._bias_fifo.pop(0)
+            # same value as in the first pass, gradient still reaches the parameter
+            return self.expert_bias + (used - self.expert_bias).detach(), False
+        return self.expert_bias, ph != "recompute"
+
     def forward(self, x: torch.Tensor):
         logits = self.gate(x)
         from kempnerforge_b200.ops import moe_ops
 
+        bias, may_update = self._bias_for_this_pass()
         native = moe_ops.native_ok(logits, self.num_experts, self.top_k)
         if native:
-            weights, indices, counts, smean, z = moe_ops.route(logits, self.expert_bias, True, self.top_k)
+            weights, indices, counts, smean, z = moe_ops.route(logits, bias, True, self.top_k)
             weights = weights.to(x.dtype)
         else:
-            scores = torch.sigmoid(logits.float() + self.expert_bias.float())
+            scores = torch.sigmoid(logits.float() + bias.float())
             weights, indices = torch.topk(scores, self.top_k, dim=-1)
             weights = (weights / weights.sum(dim=-1, keepdim=True)).to(x.dtype)
             counts = _counts(indices, self.num_experts)
             smean = None
         self.expert_counts = counts.detach()
         util = counts / (x.shape[0] * self.top_k + 1e-8)
-        if self.training:
+        if self.training and may_update:
             with torch.no_grad():
                 self.expert_ema.lerp_(util.to(self.expert_ema.dtype), 1.0 - self.ema_decay)
                 nudge = self._effective_bias_rate() * (1.0 / self.num_experts - self.expert_ema.float())

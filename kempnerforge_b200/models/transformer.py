@@ -24,6 +24,8 @@ import torch
 from torch import nn
 from torch.utils.checkpoint import checkpoint
 
+from kempnerforge_b200.models.recompute import checkpoint_contexts
+
 from kempnerforge_b200.config.registry import registry
 from kempnerforge_b200.config.sections import ModelConfig
 from kempnerforge_b200.models.attention import Attention, KVCache
@@ -79,7 +81,8 @@ class TransformerBlock(nn.Module):
     def _body(self, x, cos, sin, kv_cache, doc_ids, key_padding_mask):
         if self.ac_mode == "selective" and self.training and torch.is_grad_enabled() and kv_cache is None:
             attn = checkpoint(
-                self._attn_branch, x, cos, sin, None, doc_ids, key_padding_mask, use_reentrant=False
+                self._attn_branch, x, cos, sin, None, doc_ids, key_padding_mask, use_reentrant=False,
+                context_fn=checkpoint_contexts,
             )
         else:
             attn = self._attn_branch(x, cos, sin, kv_cache, doc_ids, key_padding_mask)
@@ -95,7 +98,8 @@ class TransformerBlock(nn.Module):
                 return fused_block.dense_block(self, x, rope_cos, rope_sin)
         if self.ac_mode == "full" and self.training and torch.is_grad_enabled() and kv_cache is None:
             return checkpoint(
-                self._body, x, rope_cos, rope_sin, None, doc_ids, key_padding_mask, use_reentrant=False
+                self._body, x, rope_cos, rope_sin, None, doc_ids, key_padding_mask, use_reentrant=False,
+                context_fn=checkpoint_contexts,
             )
         return self._body(x, rope_cos, rope_sin, kv_cache, doc_ids, key_padding_mask)
 

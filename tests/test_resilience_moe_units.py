@@ -296,3 +296,38 @@ def test_expert_parallel_config_rules():
         DistributedConfig(ep=3).resolve(8)
     with pytest.raises(ValueError):
         DistributedConfig(ep=0)
+
+
+@pytest.mark.parametrize("accum", [1, 3])
+def test_sigmoid_router_is_consistent_under_activation_checkpointing(accum):
+    """The balancing bias moves in every forward pass; the recomputation of a checkpointed block must route with
+    the bias its first pass used, update nothing, and give the gradients of an un-checkpointed run."""
+    from kempnerforge_b200.parallel.parallel import apply_ac
+
+    def run(mode):
+        torch.manual_seed(11)
+        m = Transformer(_moe_cfg(moe_router="sigmoid_topk", num_experts=8, moe_top_k=2, n_layers=3))
+        for r in (mod for mod in m.modules() if isinstance(mod, SigmoidTopKRouter)):
+            r.bias_update_rate = 0.5          # large nudges: a second update would visibly change the routing
+        apply_ac(m, mode)
+        m.train()
+        g = torch.Generator().manual_seed(3)
+        m.set_moe_step(0, 10)
+        losses = []
+        for _ in range(accum):               # forward/backward pairs, as in gradient accumulation
+            ids = torch.randint(0, 64, (2, 16), generator=g)
+            loss = m.compute_loss(ids, ids)
+            loss.backward()
+            losses.append(float(loss))
+        grads = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+        state = {n: b.clone() for n, b in m.named_buffers() if "expert_ema" in n}
+        bias = {n: p.detach().clone() for n, p in m.named_parameters() if n.endswith("expert_bias")}
+        return losses, grads, state, bias
+
+    plain, ckpt = run("none"), run("full")
+    assert plain[0] == pytest.approx(ckpt[0], rel=1e-6)
+    for n in plain[1]:
+        assert torch.allclose(plain[1][n], ckpt[1][n], atol=1e-5, rtol=1e-4), n
+    for part in (2, 3):                       # moving averages and biases were updated once per forward, not twice
+        for n in plain[part]:
+            assert torch.allclose(plain[part][n], ckpt[part][n], atol=1e-7), n
