@@ -244,8 +244,12 @@ def _build_sf(param_groups, config: OptimizerConfig):
 def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
     """Quintic Newton-Schulz orthogonalisation (fp32 in, fp32 out).
 
-    On CUDA the three matrix products of every iteration run as bf16 tcgen05 GEMMs
-    with fp32 accumulation; elsewhere in plain fp32.
+    On CUDA every iteration is three bf16 tcgen05 GEMMs with fp32 accumulation.  The Gram matrix is always taken
+    on the short side: X' = (aI + bA + cA^2) X with A = X X^T for a wide X, and X' = X (aI + bA + cA^2) with
+    A = X^T X for a tall one.  Both are the same polynomial in X (X X^T X = X (X^T X)), so the result is the one the
+    un-transposed formulation gives, at min(m, n)^2 max(m, n) instead of max(m, n)^2 min(m, n) flops per product;
+    the ``a X`` term rides on the diagonal of the polynomial, so the last GEMM writes the next iterate directly.
+    Elsewhere (CPU, odd shapes) the plain fp32 formulation runs.
     """
     if g.is_cuda and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0 and min(g.shape) >= 64:
         from kempnerforge_b200.ops import cuda as kcuda
@@ -254,13 +258,18 @@ def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
             a, b, c = ref.NS_COEFFS
             x = g.float()
             x = (x / (x.norm() + 1e-7)).to(torch.bfloat16).contiguous()
+            tall = x.shape[0] > x.shape[1]
+            n = min(x.shape)
+            eye_a = torch.zeros(n, n, dtype=torch.float32, device=x.device)
+            eye_a.diagonal().fill_(a)
             for _ in range(steps):
-                gram = kcuda.gemm(x, x, a_kmajor=True, b_kmajor=True, out_dtype=torch.float32)  # X Xᵀ
-                gram_bf = gram.to(torch.bfloat16)
-                poly = kcuda.gemm(gram_bf, gram_bf, a_kmajor=True, b_kmajor=True, out_dtype=torch.float32)
-                poly = (b * gram + c * poly).to(torch.bfloat16)
-                upd = kcuda.gemm(poly, x, a_kmajor=True, b_kmajor=False, out_dtype=torch.float32)  # B X
-                x = (a * x.float() + upd).to(torch.bfloat16)
+                if tall:   # A = X^T X  (n x n): both operands read with the reduction index slow
+                    gram = kcuda.gemm(x, x, a_kmajor=False, b_kmajor=False)
+                else:      # A = X X^T  (m x m)
+                    gram = kcuda.gemm(x, x)
+                sq = kcuda.gemm(gram, gram, out_dtype=torch.float32)                    # A^2 (A is symmetric)
+                poly = (eye_a + b * gram.float() + c * sq).to(torch.bfloat16)           # aI + bA + cA^2, symmetric
+                x = kcuda.gemm(x, poly) if tall else kcuda.gemm(poly, x, b_kmajor=False)
             return x.float()
     return ref.newton_schulz(g, steps)
 

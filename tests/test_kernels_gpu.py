@@ -504,6 +504,23 @@ def test_grouped_wgrad_matches_per_expert_products(native_lib, counts):
         start += c
 
 
+# --------------------------------------------------------------------------- Newton-Schulz on the tensor cores
+@pytest.mark.parametrize("shape", [(256, 256), (128, 512), (512, 128), (1024, 384), (64, 4096)])
+def test_newton_schulz_matches_the_fp32_formulation_for_wide_and_tall_matrices(native_lib, shape):
+    from kempnerforge_b200.ops import ref
+    from kempnerforge_b200.training.optimizer import newton_schulz
+
+    torch.manual_seed(0)
+    g = torch.randn(*shape, device="cuda")
+    got = newton_schulz(g, 5)
+    want = ref.newton_schulz(g, 5)          # un-transposed fp32 reference (Gram on the row side)
+    assert got.shape == want.shape and got.dtype == torch.float32 and native_lib.read_status() == 0
+    rel = ((got - want).norm() / want.norm()).item()
+    assert rel < 3e-2, rel
+    sv = torch.linalg.svdvals(got)
+    assert sv.max() < 1.3 and sv.min() > 0.4
+
+
 # --------------------------------------------------------------------------- memory safety without a sanitizer
 _SENTINEL = 12288.0  # exactly representable in bf16
 
