@@ -91,28 +91,44 @@ def scaled_mm(a8, b8, sa, sb, a_e5m2=False, b_e5m2=False, out=None, accumulate=F
     return out
 
 
+def quantized_weight(weights, want_t: bool):
+    """(scale, row-major fp8, transposed fp8 or None) of the weights stacked along the output dimension.
+
+    The quantised copies are kept on the first weight tensor and reused until a weight is modified in place (the
+    tensors' version counters change on every optimizer step), so the micro-batches, the recomputation and the
+    backward pass of one step quantise each weight once instead of once per use."""
+    from kempnerforge_b200.ops import functional as F
+
+    versions = tuple(w._version for w in weights) + tuple(w.data_ptr() for w in weights)
+    holder = weights[0]
+    cached = getattr(holder, "_kf_fp8_cache", None)
+    if cached is None or cached[0] != versions:
+        sw, w8, _ = quantize(F._stack_weight_rows(weights).detach())
+        cached = [versions, sw, w8, None]
+        holder._kf_fp8_cache = cached
+    if want_t and cached[3] is None:
+        cached[3] = quantize(F._stack_weight_rows(weights).detach(), want_row=False, want_t=True, scale=cached[1])[2]
+    return cached[1], cached[2], cached[3]
+
+
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, *weights):
-        from kempnerforge_b200.ops import functional as F
-
-        w = F._stack_weight_rows(weights)
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         sx, x8, _ = quantize(x2)
-        sw, w8, _ = quantize(w)
+        sw, w8, _ = quantized_weight(weights, want_t=False)
         y = scaled_mm(x8, w8, sx, sw)
         ctx.save_for_backward(x2, sx, sw, *weights)
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y.view(*x.shape[:-1], w8.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
         from kempnerforge_b200.ops import functional as F
 
         x2, sx, sw, *weights = ctx.saved_tensors
-        w = F._stack_weight_rows(weights)
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
@@ -121,7 +137,7 @@ class _Fp8LinearFn(torch.autograd.Function):
         sg, g8, g8t = quantize(dy2, e5m2=True, want_row=need_dx, want_t=need_dw)
         dx = None
         if need_dx:
-            _, _, w8t = quantize(w, want_row=False, want_t=True, scale=sw)          # (K, N)
+            _, _, w8t = quantized_weight(weights, want_t=True)                      # (K, N)
             dx = scaled_mm(g8, w8t, sg, sw, a_e5m2=True).view(ctx.x_shape)
         wgrads = [None] * len(weights)
         if need_dw:
