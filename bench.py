@@ -291,6 +291,18 @@ def run_reference(args) -> dict:
 
     rank, local, world = dist_env()
     shape = MODELS[args.model]
+    if args.ep_in_dp:
+        return {"impl": "reference", "unavailable": "the reference cannot shard experts over its data-parallel ranks"}
+    if args.fp8:
+        return {"impl": "reference", "unavailable": "the reference's float8 path needs torchao, which is not installed"}
+    if args.pp > 1 or args.micro_batches > 1 or args.optimizer != "adamw":
+        return {"impl": "reference", "unavailable": "this harness drives the reference's plain text step only "
+                "(no pipeline schedule / accumulation / Muon)"}
+    notes = []
+    if shape.get("moe_first_k_dense"):
+        # the reference can only place MoE layers by frequency: every layer becomes an MoE layer there
+        shape = {k: v for k, v in shape.items() if k != "moe_first_k_dense"}
+        notes.append("reference has no moe_first_k_dense: all layers are MoE layers in this arm")
     seq = args.seq_len or shape["max_seq_len"]
     overrides = [f"--model.{k}={v}" for k, v in shape.items()] + [
         f"--train.batch_size={args.batch_size}", f"--train.seq_len={seq}", "--train.max_steps=1000",
@@ -299,13 +311,6 @@ def run_reference(args) -> dict:
         "--optimizer.name=adamw", "--optimizer.lr=3e-4", "--optimizer.weight_decay=0.1", "--optimizer.fused=true",
         "--scheduler.name=cosine", "--scheduler.warmup_steps=10",
     ]
-    if args.ep_in_dp:
-        return {"impl": "reference", "unavailable": "the reference cannot shard experts over its data-parallel ranks"}
-    if args.fp8:
-        return {"impl": "reference", "unavailable": "the reference's float8 path needs torchao, which is not installed"}
-    if args.pp > 1 or args.micro_batches > 1 or args.optimizer != "adamw" or shape.get("moe_first_k_dense"):
-        return {"impl": "reference", "unavailable": "this harness drives the reference's plain text step only "
-                "(no pipeline schedule / accumulation / Muon; moe_first_k_dense does not exist in the reference)"}
     dims, n_batches, mesh_label = mesh_dims(args, world)
     overrides += [f"--distributed.{k}={v}" for k, v in dims.items()]
     if shape.get("num_experts"):
@@ -365,7 +370,7 @@ def run_reference(args) -> dict:
         "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "reference",
         "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
                    "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused",
-                   "compile_model": not shape.get("num_experts")},
+                   "compile_model": not shape.get("num_experts"), "notes": notes},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
