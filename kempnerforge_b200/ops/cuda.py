@@ -651,9 +651,15 @@ def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=No
 
 
 # --------------------------------------------------------------------------- fused communication kernels
-def symm_rs_norm(buf, lo: int, n: int, sumsq_out: torch.Tensor, accumulate: bool, max_blocks: int = 296) -> None:
+SYMM_RS_BLOCKS = int(os.environ.get("KF_SYMM_RS_BLOCKS", "296"))        # grid cap of the fused reduce-scatter kernel
+SYMM_ADAMW_BLOCKS = int(os.environ.get("KF_SYMM_ADAMW_BLOCKS", "592"))  # grid cap of the fused AdamW + publication kernel
+
+
+def symm_rs_norm(buf, lo: int, n: int, sumsq_out: torch.Tensor, accumulate: bool, max_blocks: int | None = None) -> None:
     """Average this rank's shard [lo, lo+n) of a symmetric gradient buffer over all ranks (in place, own copy)
-    and add the squared norm of the result to ``sumsq_out[0]``."""
+    and add the squared norm of the result to ``sumsq_out[0]``.  The kernel runs beside the backward GEMMs on a side
+    stream; ``max_blocks`` (default ``KF_SYMM_RS_BLOCKS``) bounds how many SMs it shares with them."""
+    max_blocks = SYMM_RS_BLOCKS if max_blocks is None else max_blocks
     partial = torch.empty(1024, dtype=torch.float32, device=buf.tensor.device)
     _check(
         lib().kf_symm_rs_norm_bf16(buf.peer_ptrs, buf.multicast_ptr, buf.world, buf.rank, lo, n, partial.data_ptr(),
@@ -663,8 +669,9 @@ def symm_rs_norm(buf, lo: int, n: int, sumsq_out: torch.Tensor, accumulate: bool
 
 
 def symm_adamw_bcast(param_buf, grad_shard, m, v, lo: int, n: int, n_decay_global: int, lr, beta1, beta2, eps, wd,
-                     step: int, grad_scale=None, skip=None, max_blocks: int = 592) -> None:
+                     step: int, grad_scale=None, skip=None, max_blocks: int | None = None) -> None:
     """AdamW on the shard [lo, lo+n) and store of the new parameters into every rank's parameter buffer."""
+    max_blocks = SYMM_ADAMW_BLOCKS if max_blocks is None else max_blocks
     bc1 = 1.0 - beta1**step
     bc2_sqrt = math.sqrt(1.0 - beta2**step)
     _check(
