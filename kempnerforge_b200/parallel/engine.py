@@ -24,6 +24,8 @@ pre-clip norm is returned.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -54,6 +56,8 @@ class DataParallelEngine:
         self.symmetric = transport == "symmetric" and self.world > 1 and self.groups[0].grad_symm is not None
         self._comm_stream = torch.cuda.Stream() if (self.symmetric and dev.type == "cuda") else None
         self._sq_from_reduce = False
+        self._root_groups: list[int] = []
+        self._published_per_group = False
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
         if self.world > 1:
@@ -91,6 +95,7 @@ class DataParallelEngine:
             break
         # everything that no block hook covers is waited for when the model itself is entered
         root = [i for i in range(len(self.groups)) if i not in covered]
+        self._root_groups = root
         self._handles.append(self.model.register_forward_pre_hook(lambda m, a: self.wait_params(root)))
         for name in ("forward_hidden", "compute_loss"):
             fn = getattr(self.model, name, None)
@@ -271,9 +276,42 @@ class DataParallelEngine:
             lo, hi = g.shard_range
             g.grad[lo:hi].mul_(self.grad_scale.to(g.grad.dtype))
 
+    def publish_on_side_stream(self, flat_groups) -> bool:
+        """True when the optimizer should hand its fused update + publication kernels to
+        :meth:`publish_in_forward_order` (symmetric transport on a GPU, every unit in a symmetric buffer)."""
+        if not (self.symmetric and self._comm_stream is not None and self._handles):
+            return False
+        if os.environ.get("KF_DP_OVERLAP_PUBLISH", "1") == "0":
+            return False
+        return (len(flat_groups) == len(self.groups) and all(a is b for a, b in zip(flat_groups, self.groups))
+                and all(getattr(g, "param_symm", None) is not None and g.param.numel() > 0 for g in self.groups))
+
+    def publish_in_forward_order(self, launch) -> None:
+        """Run ``launch(unit)`` (sharded optimizer update that stores the new parameters on every rank) for every
+        unit on the communication stream: root unit first (the embedding is needed first), then the blocks in
+        order.  Each launch is followed by that unit's cross-rank barrier (all ranks' stores into this rank's copy
+        are complete) and an event; a unit's next forward waits for its own event (``wait_params``), so the update
+        of the later blocks overlaps the forward pass of the earlier ones."""
+        order = list(self._root_groups) + [i for i in range(len(self.groups)) if i not in set(self._root_groups)]
+        ready = torch.cuda.Event()
+        ready.record()  # gradients reduced, clipping scale and skip flag final
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ready)
+            for i in order:
+                g = self.groups[i]
+                launch(g)
+                g.param_symm.barrier()
+                done = torch.cuda.Event()
+                done.record()
+                self._gather_work[i] = _EventWork(done)
+        self._published_per_group = True
+
     def after_optimizer_step(self) -> None:
         """Publish the updated shards so that every rank holds the full new parameters.  On GPUs the
         all-gathers are asynchronous and each block waits for its own only when its next forward starts."""
+        if self.symmetric and self._published_per_group:
+            self._published_per_group = False  # every unit carries its own barrier + event
+            return
         if self.symmetric:
             # the optimizer kernel already stored the new parameters on every rank; one barrier makes sure all
             # ranks' stores (and their reads of our gradients) are complete before the next step touches them

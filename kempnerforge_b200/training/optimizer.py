@@ -75,6 +75,21 @@ class FusedAdamW(torch.optim.AdamW):
         b1, b2 = self.param_groups[0]["betas"]
         eps = self.param_groups[0]["eps"]
         wd = max(g["weight_decay"] for g in self.param_groups)
+        eng = getattr(self, "_engine", None)
+        if eng is not None and eng.publish_on_side_stream(self._flat_groups):
+            # sharded update + publication of every unit on the communication stream, in the order the next forward
+            # pass needs them; each unit's forward waits for its own publication only
+            def launch(fg):
+                fg.step_count += 1
+                p, g, m, v = fg.optimizer_views()
+                lo, hi = fg.shard_range
+                kcuda.symm_adamw_bcast(fg.param_symm, g, m, v, lo, hi - lo, fg.n_decay, lr, b1, b2, eps, wd,
+                                       fg.step_count, self.grad_scale, self.skip_flag)
+
+            for fg in self._flat_groups:
+                fg.step_tensor.fill_(float(fg.step_count + 1))
+            eng.publish_in_forward_order(launch)
+            return loss
         for fg in self._flat_groups:
             fg.step_count += 1
             fg.step_tensor.fill_(float(fg.step_count))
@@ -398,4 +413,5 @@ def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.op
     flat = getattr(model, "_kf_flat_groups", None)
     if flat and isinstance(opt, FusedAdamW):
         opt.attach_flat_groups(flat)
+        opt._engine = getattr(model, "_kf_engine", None)
     return opt
