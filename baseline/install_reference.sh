@@ -5,10 +5,11 @@
 # pure-Python project contains exactly this directory.
 set -u
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:-${KF_REFERENCE_ROOT:-$here/../../reference}}"   # the reference checkout: argument, KF_REFERENCE_ROOT, or beside this repository
+wheels="${KF_WHEELHOUSE:-/opt/wheelhouse}"
 target="$here/_ref"
 mkdir -p "$target"
-if python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --no-deps --target "$target" "$ref" \
+if python -m pip install --no-index --no-build-isolation --find-links "$wheels" --no-deps --target "$target" "$ref" \
      > "$here/_ref_pip.log" 2>&1; then
   echo "pip install ok" | tee "$target/INSTALL_METHOD"
 else

@@ -30,7 +30,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-H200_PUBLISHED_TOKS = {1: 10471.0, 2: 18728.0, 4: 38983.0}  # reference, H200, FSDP rows
+H200_PUBLISHED_TOKS = {1: 10471.0, 2: 18728.0, 4: 38983.0}  # tokens/s the reference publishes for H200 (its FSDP rows), by GPU count
 MODELS = {
     "llama3_8b": dict(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256,
                       ffn_hidden_dim=14336, max_seq_len=4096, rope_theta=500000.0),
