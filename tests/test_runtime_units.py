@@ -192,3 +192,41 @@ def test_check_env_main_returns_an_exit_code(capsys):
     rc = ce.main([])
     out = capsys.readouterr().out
     assert rc in (0, 1) and "python" in out.lower() and "torch" in out.lower()
+
+
+# --------------------------------------------------------------------------- activation-checkpoint phases
+def test_checkpoint_phase_contexts_nest_and_reset():
+    from torch.utils.checkpoint import checkpoint
+
+    from kempnerforge_b200.models import recompute
+
+    assert recompute.phase() is None
+    fwd, rec = recompute.checkpoint_contexts()
+    with fwd:
+        assert recompute.phase() == "forward"
+        with rec:
+            assert recompute.phase() == "recompute"
+        assert recompute.phase() == "forward"
+    assert recompute.phase() is None
+    seen = []
+
+    def body(x):
+        seen.append(recompute.phase())
+        return x.sin() * x          # saves tensors, so the backward pass has to recompute the region
+
+    x = torch.ones(3, requires_grad=True)
+    y = checkpoint(body, x, use_reentrant=False, context_fn=recompute.checkpoint_contexts)
+    y.sum().backward()
+    assert seen == ["forward", "recompute"] and recompute.phase() is None
+
+
+def test_side_stream_publication_is_off_without_the_symmetric_transport():
+    from kempnerforge_b200.models.transformer import Transformer
+    from kempnerforge_b200.config.sections import ModelConfig
+    from kempnerforge_b200.parallel.engine import DataParallelEngine
+
+    m = Transformer(ModelConfig(dim=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, ffn_hidden_dim=48, max_seq_len=16))
+    eng = DataParallelEngine(m, None, transport="collective")
+    assert eng.publish_on_side_stream(eng.groups) is False
+    eng.after_optimizer_step()      # single process: nothing to publish, nothing raises
+    eng.release()
