@@ -94,3 +94,14 @@ def test_sigterm_writes_emergency_checkpoint_and_resumes(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     steps = _steps_logged(r.stdout + r.stderr)
     assert steps and min(steps) == last_step + 1, (last_step, steps)
+
+
+def test_sigmoid_moe_with_full_activation_checkpointing_trains(tmp_path):
+    """DeepSeek-style routing (bias balancing, shared expert, first layer dense) under full recomputation: the
+    recomputed blocks must route exactly as their first pass did, or the run stops with a shape mismatch."""
+    r = _train([f"--checkpoint.dir={tmp_path / 'ck'}", "--checkpoint.interval=1000", "--train.max_steps=6",
+                "--model.num_experts=4", "--model.moe_top_k=2", "--model.moe_router=sigmoid_topk",
+                "--model.moe_shared_experts=1", "--model.moe_first_k_dense=1", "--model.moe_router_z_loss_weight=0.001",
+                "--train.activation_checkpointing=full"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert 6 in _steps_logged(r.stdout + r.stderr)
