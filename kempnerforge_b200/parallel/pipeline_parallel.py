@@ -67,6 +67,31 @@ def get_pp_mesh(mesh):
     return mesh["pp"] if mesh is not None and "pp" in (mesh.mesh_dim_names or ()) else None
 
 
+_STAGE_GROUPS: dict[int, object] = {}
+
+
+def stage_process_group(mesh):
+    """The process group of all ranks that hold the same pipeline stage as this rank (its data- / tensor-parallel
+    peers); checkpoints of a stage are coordinated inside it.  Every rank creates every stage's group, in stage
+    order, the first time this is called for a mesh."""
+    import torch.distributed as dist
+
+    names = tuple(mesh.mesh_dim_names or ())
+    if "pp" not in names:
+        return None
+    key = id(mesh)
+    if key not in _STAGE_GROUPS:
+        grid = mesh.mesh.movedim(names.index("pp"), 0)
+        mine = None
+        for stage in range(grid.shape[0]):
+            ranks = sorted(int(r) for r in grid[stage].flatten().tolist())
+            group = dist.new_group(ranks)
+            if dist.get_rank() in ranks:
+                mine = group
+        _STAGE_GROUPS[key] = mine
+    return _STAGE_GROUPS[key]
+
+
 def get_pp_rank(mesh) -> int:
     return mesh_dim(mesh, "pp")[2]
 

@@ -334,8 +334,14 @@ class Trainer:
         from kempnerforge_b200.resilience import resolve_resume_path
 
         cfg = self.config.checkpoint
+        stage_group = None
+        if self.pp_size > 1 and self.mesh is not None:
+            # each pipeline stage writes and reads its own sub-directory, coordinated among the ranks of that stage
+            from kempnerforge_b200.parallel.pipeline_parallel import stage_process_group
+
+            stage_group = stage_process_group(self.mesh)
         self.ckpt = CheckpointManager(cfg, self.model, self.optimizer, pp_rank=self.pp_rank if self.pp_size > 1 else None,
-                                      process_group=None)
+                                      process_group=stage_group)
         resume = cfg.load_path or resolve_resume_path(cfg.dir)
         if resume:
             exclude = list(cfg.exclude_from_loading) or None

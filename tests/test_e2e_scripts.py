@@ -105,3 +105,30 @@ def test_sigmoid_moe_with_full_activation_checkpointing_trains(tmp_path):
                 "--train.activation_checkpointing=full"])
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert 6 in _steps_logged(r.stdout + r.stderr)
+
+
+def _torchrun(nproc, args, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "scripts", "train.py"),
+           os.path.join(ROOT, "configs", "train", "debug.toml"), *TINY, *args]
+    env = _env()
+    env.pop("MASTER_ADDR", None)
+    return subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=300, cwd=ROOT)
+
+
+@pytest.mark.parametrize("dims", [["--distributed.dp_shard=2"], ["--distributed.tp=2", "--distributed.dp_shard=1"],
+                                  ["--distributed.pp=2", "--distributed.dp_shard=1", "--train.grad_accum_steps=2"]],
+                         ids=["dp2", "tp2", "pp2"])
+def test_two_rank_runs_through_the_launcher_and_resume(tmp_path, dims):
+    """`torchrun scripts/train.py` on two gloo ranks for every parallel mode: trains, writes one checkpoint that both
+    ranks contribute to, and a second launch resumes from it."""
+    ckpt = str(tmp_path / "ckpt")
+    port = 29800 + (hash(tuple(dims)) % 100)
+    r = _torchrun(2, [f"--checkpoint.dir={ckpt}", "--checkpoint.interval=3", "--train.max_steps=3", *dims], port)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert 3 in _steps_logged(r.stdout + r.stderr)
+    assert os.path.isdir(os.path.join(ckpt, "step_3"))
+    r2 = _torchrun(2, [f"--checkpoint.dir={ckpt}", "--checkpoint.interval=100", "--train.max_steps=5", *dims], port + 1)
+    assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
+    steps = _steps_logged(r2.stdout + r2.stderr)
+    assert steps and min(steps) >= 4 and max(steps) == 5, steps
