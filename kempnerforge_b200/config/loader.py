@@ -93,6 +93,10 @@ def _convert(value: Any, annot: Any, where: str) -> Any:
         if issubclass(annot, enum.Enum):
             if isinstance(value, annot):
                 return value
+            if value is None:  # "--scheduler.name=none" reaches here as None: an enum may have a member of that name
+                for member in annot:
+                    if str(member.value).lower() in ("none", "null"):
+                        return member
             try:
                 return annot(value)
             except ValueError:

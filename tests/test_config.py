@@ -241,3 +241,8 @@ def test_reference_import_paths_resolve():
     from kempnerforge_b200.models.transformer import Transformer as T2
 
     assert M2 is ModelConfig and Transformer is T2 and c2 is clip_grad_norm_
+
+
+def test_cli_none_reaches_enum_members_and_optional_fields():
+    cfg = load_config(None, ["--scheduler.name=none", "--checkpoint.load_path=None", "--scheduler.decay_steps=null"])
+    assert str(cfg.scheduler.name) == "none" and cfg.scheduler.decay_steps is None

@@ -116,9 +116,24 @@ def _torchrun(nproc, args, port):
     return subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=300, cwd=ROOT)
 
 
-@pytest.mark.parametrize("dims", [["--distributed.dp_shard=2"], ["--distributed.tp=2", "--distributed.dp_shard=1"],
-                                  ["--distributed.pp=2", "--distributed.dp_shard=1", "--train.grad_accum_steps=2"]],
-                         ids=["dp2", "tp2", "pp2"])
+_MOE = ["--model.num_experts=4", "--model.moe_top_k=2"]
+
+
+@pytest.mark.parametrize("dims", [
+    ["--distributed.dp_shard=2"],
+    ["--distributed.tp=2", "--distributed.dp_shard=1"],
+    ["--distributed.pp=2", "--distributed.dp_shard=1", "--train.grad_accum_steps=2"],
+    ["--distributed.ep=2", "--distributed.dp_shard=1", *_MOE],
+    ["--distributed.ep=2", "--distributed.ep_in_dp=true", "--distributed.dp_shard=2", *_MOE, "--model.moe_packed_experts=true"],
+    ["--distributed.dp_shard=2", "--optimizer.name=muon"],
+    ["--distributed.dp_shard=2", "--optimizer.name=schedule_free_adamw", "--scheduler.name=none"],
+    ["--distributed.dp_shard=2", "--checkpoint.async_mode=async"],
+    ["--distributed.dp_shard=2", "--train.mixed_precision=bf16", "--train.activation_checkpointing=selective"],
+    ["--distributed.dp_shard=2", "--train.mixed_precision=fp8", "--train.activation_checkpointing=full"],
+    ["--distributed.dp_shard=2", "--optimizer.name=lion", "--train.grad_accum_steps=2", "--scheduler.name=wsd",
+     "--scheduler.stable_steps=2"],
+], ids=["dp2", "tp2", "pp2", "ep2", "ep2_in_dp", "dp2_muon", "dp2_schedule_free", "dp2_async_ckpt", "dp2_bf16_selective_ac",
+        "dp2_fp8", "dp2_lion_accum_wsd"])
 def test_two_rank_runs_through_the_launcher_and_resume(tmp_path, dims):
     """`torchrun scripts/train.py` on two gloo ranks for every parallel mode: trains, writes one checkpoint that both
     ranks contribute to, and a second launch resumes from it."""
