@@ -126,14 +126,8 @@ _MOE = ["--model.num_experts=4", "--model.moe_top_k=2"]
     ["--distributed.ep=2", "--distributed.dp_shard=1", *_MOE],
     ["--distributed.ep=2", "--distributed.ep_in_dp=true", "--distributed.dp_shard=2", *_MOE, "--model.moe_packed_experts=true"],
     ["--distributed.dp_shard=2", "--optimizer.name=muon"],
-    ["--distributed.dp_shard=2", "--optimizer.name=schedule_free_adamw", "--scheduler.name=none"],
-    ["--distributed.dp_shard=2", "--checkpoint.async_mode=async"],
-    ["--distributed.dp_shard=2", "--train.mixed_precision=bf16", "--train.activation_checkpointing=selective"],
     ["--distributed.dp_shard=2", "--train.mixed_precision=fp8", "--train.activation_checkpointing=full"],
-    ["--distributed.dp_shard=2", "--optimizer.name=lion", "--train.grad_accum_steps=2", "--scheduler.name=wsd",
-     "--scheduler.stable_steps=2"],
-], ids=["dp2", "tp2", "pp2", "ep2", "ep2_in_dp", "dp2_muon", "dp2_schedule_free", "dp2_async_ckpt", "dp2_bf16_selective_ac",
-        "dp2_fp8", "dp2_lion_accum_wsd"])
+], ids=["dp2", "tp2", "pp2", "ep2", "ep2_in_dp", "dp2_muon", "dp2_fp8"])
 def test_two_rank_runs_through_the_launcher_and_resume(tmp_path, dims):
     """`torchrun scripts/train.py` on two gloo ranks for every parallel mode: trains, writes one checkpoint that both
     ranks contribute to, and a second launch resumes from it."""
@@ -147,3 +141,21 @@ def test_two_rank_runs_through_the_launcher_and_resume(tmp_path, dims):
     assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
     steps = _steps_logged(r2.stdout + r2.stderr)
     assert steps and min(steps) >= 4 and max(steps) == 5, steps
+
+
+@pytest.mark.parametrize("opts", [
+    ["--optimizer.name=schedule_free_adamw", "--scheduler.name=none"],
+    ["--checkpoint.async_mode=async"],
+    ["--train.mixed_precision=bf16", "--train.activation_checkpointing=selective"],
+    ["--optimizer.name=lion", "--train.grad_accum_steps=2", "--scheduler.name=wsd", "--scheduler.stable_steps=2"],
+], ids=["schedule_free", "async_ckpt", "bf16_selective_ac", "lion_accum_wsd"])
+def test_single_process_variants_train_and_resume(tmp_path, opts):
+    ckpt = str(tmp_path / "ckpt")
+    r = _train([f"--checkpoint.dir={ckpt}", "--checkpoint.interval=3", "--train.max_steps=3", *opts])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert os.path.isdir(os.path.join(ckpt, "step_3")) and os.path.exists(os.path.join(ckpt, "latest"))
+    r2 = _train([f"--checkpoint.dir={ckpt}", "--checkpoint.interval=100", "--train.max_steps=5", *opts])
+    assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
+    steps = _steps_logged(r2.stdout + r2.stderr)
+    assert steps and min(steps) >= 4 and max(steps) == 5, steps
+
