@@ -141,6 +141,23 @@ def test_two_rank_runs_through_the_launcher_and_resume(tmp_path, dims):
     assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
     steps = _steps_logged(r2.stdout + r2.stderr)
     assert steps and min(steps) >= 4 and max(steps) == 5, steps
+    if any(d.startswith("--distributed.pp=") for d in dims):
+        # every stage wrote a complete sub-checkpoint; the converter merges them into one model
+        step_dir = os.path.join(ckpt, "step_5")
+        for stage in ("pp0", "pp1"):
+            assert os.path.exists(os.path.join(step_dir, stage, ".metadata"))
+            assert os.path.exists(os.path.join(step_dir, stage, "train_state.pt"))
+        cfg = tmp_path / "model.toml"
+        cfg.write_text("[model]\ndim = 64\nn_layers = 2\nn_heads = 4\nn_kv_heads = 2\nvocab_size = 256\nmax_seq_len = 64\n")
+        conv = subprocess.run([sys.executable, os.path.join(ROOT, "scripts", "convert_checkpoint.py"), "--config", str(cfg),
+                               "to-hf", step_dir, str(tmp_path / "hf")], capture_output=True, text=True, env=_env(),
+                              timeout=300, cwd=ROOT)
+        assert conv.returncode == 0, conv.stderr[-2000:]
+        from safetensors.torch import load_file
+
+        names = set(load_file(str(tmp_path / "hf" / "model.safetensors")))
+        assert {"model.embed_tokens.weight", "lm_head.weight", "model.layers.0.mlp.down_proj.weight",
+                "model.layers.1.mlp.down_proj.weight"} <= names
 
 
 @pytest.mark.parametrize("opts", [
