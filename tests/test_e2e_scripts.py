@@ -176,3 +176,40 @@ def test_single_process_variants_train_and_resume(tmp_path, opts):
     steps = _steps_logged(r2.stdout + r2.stderr)
     assert steps and min(steps) >= 4 and max(steps) == 5, steps
 
+
+
+def test_mixture_with_a_training_phase_through_the_training_script(tmp_path):
+    """Two token sources mixed 3:1, an annealing phase at step 3 that flips the weights and halves the LR."""
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    for name in ("web", "code"):
+        d = tmp_path / name
+        d.mkdir()
+        np.save(d / "shard.npy", rng.integers(0, 256, size=33 * 40, dtype=np.uint16))
+    cfg = tmp_path / "mix.toml"
+    cfg.write_text(f"""
+[[data.datasets]]
+path = "{tmp_path / 'web'}"
+name = "web"
+weight = 3.0
+[[data.datasets]]
+path = "{tmp_path / 'code'}"
+name = "code"
+weight = 1.0
+[[data.phases]]
+start_step = 3
+lr_scale = 0.5
+dataset_weights = {{ web = 1.0, code = 3.0 }}
+""")
+    cmd = [sys.executable, os.path.join(ROOT, "scripts", "train.py"), str(cfg), *TINY, "--train.max_steps=5",
+           "--data.num_workers=0", f"--checkpoint.dir={tmp_path / 'ck'}", "--checkpoint.interval=1000",
+           "--scheduler.name=constant"]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=_env(), timeout=300, cwd=ROOT)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert 5 in _steps_logged(out) and "Entering data phase 0 at step 3" in out
+    import re
+
+    lrs = {int(s): float(v) for s, v in re.findall(r"\[step (\d+)\].*?lr=([0-9.e+-]+)", out)}
+    assert lrs[2] == pytest.approx(1e-3) and lrs[5] == pytest.approx(5e-4)
