@@ -413,6 +413,8 @@ class CheckpointManager:
             materialize_optimizer_state(self.model, self.optimizer)
             state["optimizer"] = _optimizer_template(self.model, self.optimizer)
         if state:
+            if "optimizer" in state:
+                self._drop_unsaved_group_fields(state["optimizer"], self._dcp_dir(step_dir))
             dcp.load(state, checkpoint_id=str(self._dcp_dir(step_dir)), process_group=self.process_group)
             if "model" in state:
                 load_model_state_dict(self.model, state["model"])
@@ -426,6 +428,21 @@ class CheckpointManager:
         step, tokens, extra = restore_train_state(train_state, scheduler, dataloader)
         log.info("Checkpoint loaded: %s (step=%d)", step_dir, step)
         return step, tokens, extra
+
+    @staticmethod
+    def _drop_unsaved_group_fields(opt_state: dict, dcp_dir: Path) -> None:
+        """Hyper-parameter fields of the live param groups that the checkpoint does not contain (for instance
+        ``initial_lr``, which only exists once a scheduler has been attached) keep their current values instead of
+        failing the load."""
+        try:
+            saved = set(dcp.FileSystemReader(str(dcp_dir)).read_metadata().state_dict_metadata)
+        except Exception:  # unreadable metadata is reported by dcp.load itself
+            return
+        for i, group in enumerate(opt_state.get("param_groups", [])):
+            for key in [k for k in group if k != "params"]:
+                if f"optimizer.param_groups.{i}.{key}" not in saved:
+                    log.info("checkpoint has no optimizer.param_groups.%d.%s; keeping the current value", i, key)
+                    del group[key]
 
     @staticmethod
     def _step_from_name(step_dir: Path) -> int:
