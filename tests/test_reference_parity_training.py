@@ -1,0 +1,92 @@
+"""The CPU plumbing configuration (dim 256, 4 layers, 4 / 2 heads, SwiGLU 688, vocab 1024, batch 4 x 128, AdamW
+3e-4 / (0.9, 0.95) / wd 0.1, cosine with 5 warm-up steps, 20 steps) trained here and with the unmodified reference
+library from ``baseline/_ref``: same initial weights, same token stream, step-by-step loss and gradient-norm
+parity, then identical weights after a checkpoint round trip.  Skipped when the reference is not installed."""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+pytestmark = pytest.mark.skipif(not (REF / "kempnerforge").is_dir(), reason="reference package not installed")
+
+PRESET = str(ROOT / "configs" / "train" / "cpu_plumbing.toml")
+
+
+def _batches(n, vocab=1024, batch=4, seq=128):
+    g = torch.Generator().manual_seed(0)
+    out = []
+    for _ in range(n):
+        tok = torch.randint(0, vocab, (batch, seq + 1), generator=g)
+        out.append((tok[:, :-1].contiguous(), tok[:, 1:].contiguous()))     # labels = inputs shifted by one
+    return out
+
+
+def _reference_run(batches, init_out: dict):
+    if str(REF) not in sys.path:
+        sys.path.insert(0, str(REF))
+    from kempnerforge.config.loader import load_config
+    from kempnerforge.distributed.utils import clip_grad_norm_
+    from kempnerforge.model.transformer import Transformer
+    from kempnerforge.training.loss import build_loss_fn
+    from kempnerforge.training.optimizer import build_optimizer
+    from kempnerforge.training.scheduler import build_scheduler
+
+    cfg = load_config(PRESET, [])
+    torch.manual_seed(0)
+    model = Transformer(cfg.model)
+    init_out.update({k: v.detach().clone() for k, v in model.state_dict().items()})
+    opt = build_optimizer(model, cfg.optimizer)
+    sched = build_scheduler(opt, cfg.scheduler, max_steps=cfg.train.max_steps)
+    loss_fn = build_loss_fn(cfg.train)
+    traj = []
+    for ids, labels in batches:          # the reference's text step: forward, loss, backward, clip, step, schedule
+        loss = loss_fn(model(ids), labels)
+        loss.backward()
+        norm = clip_grad_norm_(model, cfg.train.grad_clip_norm)
+        lr = opt.param_groups[0]["lr"]
+        opt.step()
+        sched.step()
+        opt.zero_grad()
+        traj.append((float(loss), float(norm), lr))
+    return traj, {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def test_twenty_steps_match_the_reference_and_survive_a_checkpoint_round_trip(tmp_path, monkeypatch):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.training.trainer import Trainer
+
+    batches = _batches(20)
+    init: dict = {}
+    ref_traj, ref_final = _reference_run(batches, init)
+
+    cfg = load_config(PRESET, [f"--checkpoint.dir={tmp_path / 'ck'}", "--metrics.log_interval=1000"])
+    t = Trainer(cfg, init_dist=False)
+    assert set(t.model.state_dict()) == set(init)
+    t.model.load_state_dict(init)                                     # same starting point as the reference
+    t.setup_checkpointing()
+    ours = []
+    for i, (ids, labels) in enumerate(batches):
+        if i == 10:                                                   # save, rebuild everything, resume
+            t.step = 10
+            t.save_checkpoint()
+            t.ckpt.wait()
+            t = Trainer(cfg, init_dist=False)
+            t.setup_checkpointing()
+            assert t.step == 10
+        out = t.train_step([{"input_ids": ids, "labels": labels}])
+        ours.append((out["loss"], out["grad_norm"], out["lr"]))
+    for step, (a, b) in enumerate(zip(ours, ref_traj)):
+        assert a[0] == pytest.approx(b[0], rel=2e-4, abs=2e-4), ("loss", step, a, b)
+        assert a[1] == pytest.approx(b[1], rel=2e-3, abs=2e-4), ("grad norm", step, a, b)
+        assert a[2] == pytest.approx(b[2], rel=1e-6, abs=1e-12), ("lr", step, a, b)
+    assert ours[0][2] == 0.0 and ours[-1][0] < ours[0][0]              # first step at lr 0, then the loss moves
+    final = t.model.state_dict()
+    worst = max((final[k] - ref_final[k]).abs().max().item() for k in ref_final)
+    assert worst < 5e-4, worst
