@@ -27,7 +27,7 @@ def _batches(n, vocab=1024, batch=4, seq=128):
     return out
 
 
-def _reference_run(batches, init_out: dict):
+def _reference_run(batches, init_out: dict, overrides=()):
     if str(REF) not in sys.path:
         sys.path.insert(0, str(REF))
     from kempnerforge.config.loader import load_config
@@ -37,9 +37,10 @@ def _reference_run(batches, init_out: dict):
     from kempnerforge.training.optimizer import build_optimizer
     from kempnerforge.training.scheduler import build_scheduler
 
-    cfg = load_config(PRESET, [])
+    cfg = load_config(PRESET, list(overrides))
     torch.manual_seed(0)
     model = Transformer(cfg.model)
+    mc = cfg.model
     init_out.update({k: v.detach().clone() for k, v in model.state_dict().items()})
     opt = build_optimizer(model, cfg.optimizer)
     sched = build_scheduler(opt, cfg.scheduler, max_steps=cfg.train.max_steps)
@@ -47,6 +48,10 @@ def _reference_run(batches, init_out: dict):
     traj = []
     for ids, labels in batches:          # the reference's text step: forward, loss, backward, clip, step, schedule
         loss = loss_fn(model(ids), labels)
+        if mc.num_experts > 0:           # the auxiliary terms the reference's training script adds for MoE models
+            loss = loss + mc.moe_aux_loss_weight * model.get_moe_aux_loss()
+            if mc.moe_router_z_loss_weight > 0:
+                loss = loss + mc.moe_router_z_loss_weight * model.get_moe_router_z_loss()
         loss.backward()
         norm = clip_grad_norm_(model, cfg.train.grad_clip_norm)
         lr = opt.param_groups[0]["lr"]
@@ -90,3 +95,67 @@ def test_twenty_steps_match_the_reference_and_survive_a_checkpoint_round_trip(tm
     final = t.model.state_dict()
     worst = max((final[k] - ref_final[k]).abs().max().item() for k in ref_final)
     assert worst < 5e-4, worst
+
+
+@pytest.mark.parametrize("router_overrides", [
+    ["--model.moe_router=softmax_topk", "--model.moe_aux_loss_weight=0.01", "--model.moe_router_z_loss_weight=0.001"],
+    ["--model.moe_router=sigmoid_topk", "--model.moe_shared_experts=1", "--model.moe_router_z_loss_weight=0.001"],
+], ids=["softmax_top2", "sigmoid_bias_balanced"])
+def test_moe_steps_match_the_reference(monkeypatch, router_overrides):
+    """Mixture-of-experts variant of the same run (4 experts, top-2): routing, auxiliary losses, the sigmoid router's
+    bias nudging and moving average follow the reference step by step."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.training.trainer import Trainer
+
+    overrides = ["--model.num_experts=4", "--model.moe_top_k=2", "--model.n_layers=2", "--train.max_steps=8",
+                 *router_overrides]
+    batches = _batches(8)
+    init: dict = {}
+    ref_traj, ref_final = _reference_run(batches, init, overrides)
+    cfg = load_config(PRESET, overrides + ["--metrics.log_interval=1000"])
+    t = Trainer(cfg, init_dist=False)
+    assert set(t.model.state_dict()) == set(init)
+    t.model.load_state_dict(init)
+    for step, ((ids, labels), want) in enumerate(zip(batches, ref_traj)):
+        out = t.train_step([{"input_ids": ids, "labels": labels}])
+        t.step += 1
+        assert out["loss"] == pytest.approx(want[0], rel=3e-4, abs=3e-4), ("loss", step, out, want)
+        assert out["grad_norm"] == pytest.approx(want[1], rel=5e-3, abs=5e-4), ("grad norm", step, out, want)
+    final = t.model.state_dict()
+    worst = max((final[k].float() - ref_final[k].float()).abs().max().item() for k in ref_final)
+    assert worst < 1e-3, worst
+
+
+@pytest.mark.parametrize("opt_overrides", [
+    ["--optimizer.name=muon", "--optimizer.lr=0.02"],
+    ["--optimizer.name=lion", "--optimizer.lr=1e-4"],
+    ["--optimizer.name=schedule_free_adamw", "--optimizer.lr=1e-3", "--scheduler.name=none",
+     "--optimizer.schedule_free_warmup_steps=3"],
+], ids=["muon", "lion", "schedule_free"])
+def test_other_optimizers_match_the_reference(monkeypatch, opt_overrides):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.training.trainer import Trainer
+
+    overrides = ["--model.n_layers=2", "--train.max_steps=6", *opt_overrides]
+    batches = _batches(6)
+    init: dict = {}
+    ref_traj, ref_final = _reference_run(batches, init, overrides)
+    cfg = load_config(PRESET, overrides + ["--metrics.log_interval=1000"])
+    t = Trainer(cfg, init_dist=False)
+    t.model.load_state_dict(init)
+    for step, ((ids, labels), want) in enumerate(zip(batches, ref_traj)):
+        out = t.train_step([{"input_ids": ids, "labels": labels}])
+        t.step += 1
+        assert out["loss"] == pytest.approx(want[0], rel=5e-4, abs=5e-4), ("loss", step, out, want)
+    final = t.model.state_dict()
+    keys = list(ref_final)
+    if "muon" in " ".join(opt_overrides):
+        # The reference's Muon does not override zero_grad, so `optimizer.zero_grad()` in its training loop never
+        # clears the gradients of the parameters its inner AdamW owns (1-D tensors): they accumulate from step to
+        # step there.  This framework clears them; the matrices Muon itself updates are compared.
+        keys = [k for k in keys if ref_final[k].dim() >= 2]
+    worst = max((final[k].float() - ref_final[k].float()).abs().max().item() for k in keys)
+    assert worst < 2e-3, worst
+
