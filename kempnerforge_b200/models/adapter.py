@@ -32,12 +32,12 @@ class MLP2LayerAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, hidden_dim: int | None = None, activation: str = "gelu", **_) -> None:
         super().__init__()
         hidden = hidden_dim or out_dim
-        self.fc1 = nn.Linear(in_dim, hidden)
+        self.proj1 = nn.Linear(in_dim, hidden)  # parameter names are the checkpoint keys of the reference
         self.act = _ACT[activation]()
-        self.fc2 = nn.Linear(hidden, out_dim)
+        self.proj2 = nn.Linear(hidden, out_dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.fc2(self.act(self.fc1(x)))
+        return self.proj2(self.act(self.proj1(x)))
 
 
 class LinearAdapter(VisionAdapter):
@@ -94,7 +94,7 @@ class AttentionalPoolAdapter(VisionAdapter):
         self.k_proj = nn.Linear(in_dim, in_dim)
         self.v_proj = nn.Linear(in_dim, in_dim)
         self.o_proj = nn.Linear(in_dim, in_dim)
-        self.proj = nn.Linear(in_dim, out_dim)
+        self.out_proj = nn.Linear(in_dim, out_dim)
 
     def output_num_tokens(self, num_input_tokens: int) -> int:
         return pooled_token_count(num_input_tokens, self.window, require_divisible=True)
@@ -111,7 +111,7 @@ class AttentionalPoolAdapter(VisionAdapter):
         v = self.v_proj(win).reshape(b * w, p, self.heads, hd).transpose(1, 2)
         att = torch.nn.functional.scaled_dot_product_attention(q, k, v)  # tiny: P keys per window
         pooled = self.o_proj(att.transpose(1, 2).reshape(b, w, f))
-        return self.proj(pooled)
+        return self.out_proj(pooled)
 
 
 registry.register("adapter", "mlp_2layer", MLP2LayerAdapter)

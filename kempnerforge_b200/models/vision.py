@@ -29,13 +29,15 @@ class RandomVisionEncoder(VisionEncoder):
         # a fixed random projection of coarse image statistics: deterministic per image, different across images
         gen = torch.Generator().manual_seed(1234)
         self.register_buffer("basis", torch.randn(3 * 16, num_tokens * feature_dim, generator=gen) / 7.0, persistent=False)
-        self.anchor = nn.Parameter(torch.zeros(1))  # lets ``.parameters()`` / dtype queries work
+        # no parameters and nothing in the state dict (like the reference's stub): a non-persistent buffer carries
+        # the module's device and dtype
+        self.register_buffer("_anchor", torch.zeros(1), persistent=False)
 
     def forward(self, pixel_values: torch.Tensor) -> torch.Tensor:
         b = pixel_values.shape[0]
         coarse = torch.nn.functional.adaptive_avg_pool2d(pixel_values.float(), 4).reshape(b, -1)
         feats = torch.tanh(coarse @ self.basis.float()).reshape(b, self.num_tokens, self.feature_dim)
-        return feats.to(self.anchor.dtype) + 0.0 * self.anchor
+        return feats.to(self._anchor.dtype)
 
 
 class HFVisionEncoder(VisionEncoder):

@@ -1,0 +1,137 @@
+"""Model-level parity with the unmodified reference (``baseline/_ref``) on CPU: identical parameter names and, with the
+same weights, identical outputs for the vision-language wrappers (all four architectures), the adapters, MoE variants
+and greedy decoding.  Skipped when the reference is not installed."""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+pytestmark = pytest.mark.skipif(not (REF / "kempnerforge").is_dir(), reason="reference package not installed")
+
+BASE = ["--model.dim=64", "--model.n_layers=4", "--model.n_heads=4", "--model.n_kv_heads=2", "--model.vocab_size=128",
+        "--model.max_seq_len=64", "--model.ffn_hidden_dim=128", "--train.seq_len=32", "--train.batch_size=2",
+        "--train.compile_model=false"]
+
+
+def _ref_path():
+    if str(REF) not in sys.path:
+        sys.path.insert(0, str(REF))
+
+
+def _open_zero_gates(state):
+    """Zero-initialised projections hide whole branches; give them values so the comparison exercises every path."""
+    g = torch.Generator().manual_seed(5)
+    for v in state.values():
+        if v.dim() == 2 and torch.count_nonzero(v) == 0:
+            v.copy_(torch.randn(v.shape, generator=g) * 0.05)
+
+
+@pytest.mark.parametrize("arch", ["joint_decoder", "cross_attention", "mot", "moma"])
+def test_vlm_wrappers_share_names_and_logits_with_the_reference(arch, monkeypatch):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.model.vlm import build_vlm_wrapper as ref_build
+
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.models.vlm import build_vlm_wrapper
+
+    ov = BASE + ["--vision_encoder.type=random", "--vision_encoder.feature_dim=32", "--vision_encoder.num_tokens=4",
+                 "--adapter.type=mlp_2layer", f"--vlm.arch={arch}", "--vlm.max_text_len=12"]
+    if arch == "cross_attention":
+        ov.append("--vlm.cross_attention_every_n_layers=2")
+    if arch == "moma":
+        ov.append("--vlm.moma_gumbel_noise=false")
+    rc = ref_load(None, ov)
+    torch.manual_seed(0)
+    ref = ref_build(rc.model, rc.vision_encoder, rc.adapter, rc.vlm)
+    c = load_config(None, ov)
+    ours = build_vlm_wrapper(c.model, c.vision_encoder, c.adapter, c.vlm)
+    assert set(ours.state_dict()) == set(ref.state_dict())
+    state = {k: v.clone() for k, v in ref.state_dict().items()}
+    _open_zero_gates(state)
+    ref.load_state_dict(state)
+    ours.load_state_dict(state)
+    ours.vision_encoder = ref.vision_encoder          # the stub encoders draw different features: share one
+    pixels, ids = torch.rand(2, 3, 16, 16), torch.randint(1, 128, (2, 10))
+    ref.eval(), ours.eval()
+    with torch.no_grad():
+        want = ref(pixels, ids)
+        want = want[0] if isinstance(want, tuple) else want
+        got = ours(pixels, ids)[0]
+    assert got.shape == want.shape == (2, 10, 128)
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max().item()
+
+
+@pytest.mark.parametrize("kind,tokens", [("mlp_2layer", 16), ("linear", 16), ("avgpool", 16), ("attentional_pool", 16)])
+def test_adapters_share_names_and_outputs_with_the_reference(kind, tokens):
+    _ref_path()
+    from kempnerforge.config.adapter import AdapterConfig as RefAdapterConfig
+    from kempnerforge.model.adapter import build_adapter as ref_build
+
+    from kempnerforge_b200.config.vlm import AdapterConfig
+    from kempnerforge_b200.models.adapter import build_adapter
+
+    torch.manual_seed(0)
+    ref = ref_build(RefAdapterConfig(type=kind, pool_window=2, pool_heads=4), in_dim=32, out_dim=48)
+    ours = build_adapter(AdapterConfig(type=kind, pool_window=2, pool_heads=4), in_dim=32, out_dim=48)
+    assert set(ours.state_dict()) == set(ref.state_dict())
+    ours.load_state_dict(ref.state_dict())
+    x = torch.randn(2, tokens, 32)
+    with torch.no_grad():
+        want, got = ref(x), ours(x)
+    assert got.shape == want.shape and torch.allclose(got, want, atol=1e-5)
+    assert ours.output_num_tokens(tokens) == want.shape[1]
+
+
+@pytest.mark.parametrize("extra", [
+    [],
+    ["--model.qk_norm=true", "--model.tie_embeddings=true"],
+    ["--model.num_experts=4", "--model.moe_top_k=2", "--model.moe_frequency=2"],
+    ["--model.num_experts=4", "--model.moe_top_k=2", "--model.moe_packed_experts=true", "--model.moe_shared_experts=1"],
+    ["--model.num_experts=4", "--model.moe_top_k=2", "--model.moe_router=sigmoid_topk", "--model.moe_capacity_factor=1.0"],
+    ["--model.activation=gelu", "--model.norm_type=layernorm"],
+], ids=["dense", "qk_norm_tied", "moe_every_other", "moe_packed_shared", "moe_sigmoid_capacity", "gelu_layernorm"])
+def test_transformer_variants_share_names_and_logits_with_the_reference(extra):
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.model.transformer import Transformer as RefTransformer
+
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.models.transformer import Transformer
+
+    torch.manual_seed(0)
+    ref = RefTransformer(ref_load(None, BASE + extra).model)
+    ours = Transformer(load_config(None, BASE + extra).model)
+    assert set(ours.state_dict()) == set(ref.state_dict())
+    ours.load_state_dict(ref.state_dict())
+    ids = torch.randint(0, 128, (2, 12))
+    ref.eval(), ours.eval()
+    with torch.no_grad():
+        assert torch.allclose(ours(ids), ref(ids), atol=2e-5)
+
+
+def test_greedy_decoding_matches_the_reference():
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.model.generate import generate as ref_generate
+    from kempnerforge.model.transformer import Transformer as RefTransformer
+
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.models.generate import generate
+    from kempnerforge_b200.models.transformer import Transformer
+
+    torch.manual_seed(0)
+    ref = RefTransformer(ref_load(None, BASE).model)
+    ours = Transformer(load_config(None, BASE).model)
+    ours.load_state_dict(ref.state_dict())
+    prompt = torch.randint(0, 128, (2, 5))
+    want = ref_generate(ref, prompt, max_new_tokens=12, temperature=0.0)
+    got = generate(ours, prompt, max_new_tokens=12, temperature=0.0)
+    assert torch.equal(got, want)
