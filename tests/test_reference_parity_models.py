@@ -135,3 +135,79 @@ def test_greedy_decoding_matches_the_reference():
     want = ref_generate(ref, prompt, max_new_tokens=12, temperature=0.0)
     got = generate(ours, prompt, max_new_tokens=12, temperature=0.0)
     assert torch.equal(got, want)
+
+
+# --------------------------------------------------------------------------- configuration surface
+def _norm(v):
+    import dataclasses
+    import enum
+
+    if isinstance(v, enum.Enum):
+        return str(v.value)
+    if dataclasses.is_dataclass(v):
+        return {f.name: _norm(getattr(v, f.name)) for f in dataclasses.fields(v)}
+    if isinstance(v, (list, tuple)):
+        return [_norm(x) for x in v]
+    if isinstance(v, dict):
+        return {k: _norm(x) for k, x in v.items()}
+    return v
+
+
+def test_every_reference_preset_parses_to_the_same_values():
+    """Each TOML preset shipped by the reference, read by both loaders: every field the reference defines exists here
+    with the same value (this framework may define more), and the derived model quantities agree."""
+    import glob
+    import os
+
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+
+    from kempnerforge_b200.config import load_config
+
+    root = os.environ.get("KF_REFERENCE_ROOT") or str(ROOT.parent / "reference")
+    presets = sorted(glob.glob(os.path.join(root, "configs", "train", "*.toml")))
+    if not presets:
+        pytest.skip("reference presets not available")
+    for path in presets:
+        name = os.path.basename(path)
+        ref_cfg, cfg = ref_load(path), load_config(path)
+        want, got = _norm(ref_cfg), _norm(cfg)
+        for section, fields in want.items():
+            if fields is None:
+                assert got.get(section) is None, (name, section)
+                continue
+            assert got.get(section) is not None, (name, section)
+            for key, value in fields.items():
+                assert key in got[section], (name, section, key)
+                assert got[section][key] == value, (name, section, key, value, got[section][key])
+        rm, m = ref_cfg.model, cfg.model
+        assert (m.head_dim, m.computed_ffn_hidden_dim, m.is_moe) == (rm.head_dim, rm.computed_ffn_hidden_dim, rm.is_moe), name
+        assert m.num_params_estimate == rm.num_params_estimate, name
+        assert cfg.train.param_dtype == ref_cfg.train.param_dtype and cfg.train.is_fp8 == ref_cfg.train.is_fp8, name
+
+
+@pytest.mark.parametrize("name,kw", [("cosine", {}), ("linear", {}), ("constant", {}), ("rex", {"rex_alpha": 2.0}),
+                                     ("wsd", {"stable_steps": 30, "wsd_decay_type": "sqrt"}),
+                                     ("wsd", {"stable_steps": 10, "wsd_decay_type": "linear", "decay_steps": 40})])
+def test_schedules_match_the_reference_at_every_step(name, kw):
+    _ref_path()
+    from kempnerforge.config.scheduler import SchedulerConfig as RefSchedulerConfig
+    from kempnerforge.training.scheduler import build_scheduler as ref_build
+
+    from kempnerforge_b200.config.sections import SchedulerConfig
+    from kempnerforge_b200.training.scheduler import build_scheduler
+
+    def lrs(build, cfg):
+        p = torch.nn.Parameter(torch.zeros(1))
+        opt = torch.optim.SGD([p], lr=1.0)
+        sched = build(opt, cfg, 100)
+        out = []
+        for _ in range(110):
+            out.append(opt.param_groups[0]["lr"])
+            opt.step()
+            sched.step()
+        return out
+
+    want = lrs(ref_build, RefSchedulerConfig(name=name, warmup_steps=7, min_lr_ratio=0.1, **kw))
+    got = lrs(build_scheduler, SchedulerConfig(name=name, warmup_steps=7, min_lr_ratio=0.1, **kw))
+    assert got == pytest.approx(want, abs=1e-9)
