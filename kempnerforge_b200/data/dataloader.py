@@ -17,7 +17,14 @@ from torch.utils.data import DataLoader, Dataset, Sampler
 class StatefulDataLoader:
     def __init__(self, dataset: Dataset, batch_size: int, sampler: Sampler | None = None, num_workers: int = 0,
                  pin_memory: bool = False, prefetch_factor: int | None = 2, drop_last: bool = True,
-                 collate_fn=None) -> None:
+                 collate_fn=None, config=None) -> None:
+        """Worker settings are given one by one, or as ``config=DataConfig`` (the reference's calling convention,
+        kempnerforge/data/dataloader.py:53-64); a ``DataConfig`` passed as the fourth positional argument works too."""
+        if config is None and not isinstance(num_workers, int):
+            config, num_workers = num_workers, 0
+        if config is not None:
+            num_workers, pin_memory = int(config.num_workers), bool(config.pin_memory)
+            prefetch_factor = config.prefetch_factor
         self.dataset, self.batch_size, self.sampler = dataset, batch_size, sampler
         kwargs = dict(batch_size=batch_size, sampler=sampler, num_workers=num_workers,
                       pin_memory=pin_memory and torch.cuda.is_available(), drop_last=drop_last,

@@ -211,3 +211,65 @@ def test_schedules_match_the_reference_at_every_step(name, kw):
     want = lrs(ref_build, RefSchedulerConfig(name=name, warmup_steps=7, min_lr_ratio=0.1, **kw))
     got = lrs(build_scheduler, SchedulerConfig(name=name, warmup_steps=7, min_lr_ratio=0.1, **kw))
     assert got == pytest.approx(want, abs=1e-9)
+
+
+# --------------------------------------------------------------------------- data pipeline
+def test_token_datasets_and_samplers_yield_the_reference_streams(tmp_path):
+    """Same shards -> same samples; same seeds -> the same index order from both samplers (so a data-loader position
+    saved by one implementation resumes at the same sample in the other); same packed outputs."""
+    import numpy as np
+
+    _ref_path()
+    from kempnerforge.data.dataset import MemoryMappedDataset as RefDataset
+    from kempnerforge.data.dataset import _compute_packed_output as ref_pack
+    from kempnerforge.data.sampler import DistributedSampler as RefSampler
+    from kempnerforge.data.sampler import MixtureSampler as RefMixture
+
+    from kempnerforge_b200.data.dataset import MemoryMappedDataset, compute_packed_output
+    from kempnerforge_b200.data.sampler import DistributedSampler, MixtureSampler
+
+    np.save(tmp_path / "a.npy", np.arange(1000, dtype=np.uint16))
+    np.save(tmp_path / "b.npy", np.arange(2000, 2700, dtype=np.uint16))
+    ref_ds, ds = RefDataset(str(tmp_path), 33), MemoryMappedDataset(str(tmp_path), 33)
+    assert len(ds) == len(ref_ds) == 51
+    for i in range(len(ds)):
+        assert torch.equal(ds[i]["input_ids"], ref_ds[i]["input_ids"]) and torch.equal(ds[i]["labels"], ref_ds[i]["labels"])
+    for kw in (dict(num_replicas=4, rank=1, shuffle=True, seed=3, drop_last=True),
+               dict(num_replicas=3, rank=2, shuffle=True, seed=0, drop_last=False),
+               dict(num_replicas=2, rank=0, shuffle=False, seed=0, drop_last=True)):
+        a, b = RefSampler(ref_ds, **kw), DistributedSampler(ds, **kw)
+        for epoch in (0, 2):
+            a.set_epoch(epoch), b.set_epoch(epoch)
+            assert list(a) == list(b), (kw, epoch)
+        a.set_skip(5), b.set_skip(5)
+        assert list(a) == list(b)
+        assert a.state_dict() == b.state_dict()
+    for cum, kw in (([0, 400, 1000], dict(weights=[3.0, 1.0], num_replicas=2, rank=1, seed=4, temperature=1.0)),
+                    ([0, 100, 700, 1000], dict(weights=[1.0, 5.0, 2.0], num_replicas=1, rank=0, seed=0, temperature=2.0))):
+        a, b = RefMixture(cum, **kw), MixtureSampler(cum, **kw)
+        a.set_epoch(1), b.set_epoch(1)
+        assert list(a) == list(b)
+        new = [1.0] * len(kw["weights"])
+        a.update_weights(new), b.update_weights(new)
+        assert list(a) == list(b)
+    window = np.array([5, 6, 0, 7, 8, 9, 0, 0, 3, 4], dtype=np.int64)
+    want, got = ref_pack(window, 0), compute_packed_output(window, 0)
+    assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
+
+
+def test_stateful_loader_accepts_the_reference_calling_convention(tmp_path):
+    import numpy as np
+
+    from kempnerforge_b200.config.sections import DataConfig
+    from kempnerforge_b200.data.dataloader import StatefulDataLoader
+    from kempnerforge_b200.data.dataset import MemoryMappedDataset
+    from kempnerforge_b200.data.sampler import DistributedSampler
+
+    np.save(tmp_path / "a.npy", np.arange(660, dtype=np.uint16))
+    ds = MemoryMappedDataset(str(tmp_path), 33)
+    cfg = DataConfig(num_workers=0, pin_memory=False)
+    for loader in (StatefulDataLoader(ds, 4, DistributedSampler(ds, 1, 0, seed=1), config=cfg),
+                   StatefulDataLoader(ds, 4, DistributedSampler(ds, 1, 0, seed=1), cfg)):
+        batches = list(loader)
+        assert len(batches) == 5 and batches[0]["input_ids"].shape == (4, 32)
+        assert {"epoch"} <= set(loader.state_dict())
