@@ -273,3 +273,40 @@ def test_stateful_loader_accepts_the_reference_calling_convention(tmp_path):
         batches = list(loader)
         assert len(batches) == 5 and batches[0]["input_ids"].shape == (4, 32)
         assert {"epoch"} <= set(loader.state_dict())
+
+
+def test_loader_positions_are_interchangeable_with_the_reference(tmp_path):
+    """A data-loader state captured mid-epoch by either implementation resumes at the same batch in the other."""
+    import numpy as np
+
+    _ref_path()
+    from kempnerforge.config.data import DataConfig as RefDataConfig
+    from kempnerforge.data.dataloader import StatefulDataLoader as RefLoader
+    from kempnerforge.data.dataset import MemoryMappedDataset as RefDataset
+    from kempnerforge.data.sampler import DistributedSampler as RefSampler
+
+    from kempnerforge_b200.data.dataloader import StatefulDataLoader
+    from kempnerforge_b200.data.dataset import MemoryMappedDataset
+    from kempnerforge_b200.data.sampler import DistributedSampler
+
+    np.save(tmp_path / "a.npy", np.arange(3300, dtype=np.uint16))
+    ref_ds, ds = RefDataset(str(tmp_path), 33), MemoryMappedDataset(str(tmp_path), 33)
+
+    def ref_loader():
+        return RefLoader(ref_ds, 4, RefSampler(ref_ds, 1, 0, seed=1), RefDataConfig(num_workers=0, pin_memory=False))
+
+    def our_loader():
+        return StatefulDataLoader(ds, 4, DistributedSampler(ds, 1, 0, seed=1), 0, False, None, True)
+
+    a, b = ref_loader(), our_loader()
+    ia, ib = iter(a), iter(b)
+    for _ in range(7):
+        assert torch.equal(next(ia)["input_ids"], next(ib)["input_ids"])
+    sa, sb = a.state_dict(), b.state_dict()
+    assert {k: sb[k] for k in sa} == sa                       # same keys and values (ours may add more)
+    resumed_here, resumed_there = our_loader(), ref_loader()
+    resumed_here.load_state_dict(sa)
+    resumed_there.load_state_dict(sb)
+    want = next(ia)["input_ids"]
+    assert torch.equal(next(iter(resumed_here))["input_ids"], want)
+    assert torch.equal(next(iter(resumed_there))["input_ids"], want)
