@@ -97,8 +97,29 @@ def format_metrics(step: int, metrics: dict) -> str:
             parts.append(f"mem={val}")
         elif key == "step_time":
             parts.append(f"step_time={val:.2f}s")
-        elif isinstance(val, float):
-            parts.append(f"{key}={val:.4g}")
         else:
-            parts.append(f"{key}={val}")
+            parts.append(f"{key}={format_number(val)}")
     return f"[step {step}] " + " | ".join(parts)
+
+
+def format_number(val) -> str:
+    """Compact rendering of a metric value, same rules as the reference's log lines (kempnerforge/metrics/logger.py:
+    120-140): integers (and whole floats from 1000 up) as 12.3k / 4.5M / 1.2B, tiny or huge floats in scientific
+    notation, other floats with four decimals, anything else through ``str``."""
+    if isinstance(val, bool) or not isinstance(val, (int, float)):
+        return str(val)
+    if isinstance(val, int) or (val == int(val) and abs(val) >= 1000 if val == val and abs(val) != float("inf") else False):
+        n = int(val)
+        mag = abs(n)
+        if mag >= 1_000_000_000:
+            return f"{n / 1e9:.1f}B"
+        if mag >= 1_000_000:
+            return f"{n / 1e6:.1f}M"
+        if mag >= 1_000:
+            return f"{n / 1e3:.0f}k" if mag % 1000 == 0 else f"{n / 1e3:.1f}k"
+        return str(n)
+    if val != val or abs(val) == float("inf"):
+        return str(val)
+    if abs(val) < 0.01 or abs(val) >= 1e6:
+        return f"{val:.2e}"
+    return f"{val:.4f}"

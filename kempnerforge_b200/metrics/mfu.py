@@ -70,7 +70,7 @@ def active_params(model_config) -> int:
             shared = 0
             if c.moe_shared_experts > 0:  # one shared MLP runs (optionally widened)
                 shared = 3 * d * he * (c.moe_shared_experts if c.moe_shared_expert_widen else 1)
-            total += attn + c.moe_top_k * 3 * d * he + shared + d * c.num_experts
+            total += attn + c.moe_top_k * 3 * d * he + shared  # the router GEMM is left out, as in the reference's formula
         else:
             total += attn + 3 * d * c.computed_ffn_hidden_dim
     return total + c.vocab_size * d  # output head

@@ -310,3 +310,61 @@ def test_loader_positions_are_interchangeable_with_the_reference(tmp_path):
     want = next(ia)["input_ids"]
     assert torch.equal(next(iter(resumed_here))["input_ids"], want)
     assert torch.equal(next(iter(resumed_there))["input_ids"], want)
+
+
+# --------------------------------------------------------------------------- metrics, losses, log lines
+@pytest.mark.parametrize("extra", [[], ["--model.num_experts=8", "--model.moe_top_k=2"],
+                                   ["--model.num_experts=16", "--model.moe_top_k=4", "--model.moe_frequency=2"]],
+                         ids=["dense", "moe_top2", "moe_top4_every_other"])
+def test_flop_estimates_match_the_reference(extra):
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.metrics.mfu import compute_mfu as ref_mfu
+    from kempnerforge.metrics.mfu import estimate_model_flops_per_token as ref_flops
+
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.metrics.mfu import compute_mfu, estimate_model_flops_per_token
+
+    a, b = ref_load(None, extra).model, load_config(None, extra).model
+    for seq in (2048, 8192):
+        assert estimate_model_flops_per_token(b, seq) == ref_flops(a, seq)
+    assert compute_mfu(b, 1e5, 8, 2048, peak_tflops=989.0) == pytest.approx(ref_mfu(a, 1e5, 8, 989.0, 2048), rel=1e-9)
+
+
+def test_flop_estimate_counts_the_experts_that_run():
+    """Where the reference's estimate departs from the executed work it is not followed: it charges every expert at the
+    dense FFN width and multiplies the shared MLP by ``moe_shared_experts`` although one MLP is built."""
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.metrics.mfu import estimate_model_flops_per_token as ref_flops
+
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.metrics.mfu import estimate_model_flops_per_token
+
+    for extra in (["--model.num_experts=8", "--model.moe_top_k=2", "--model.moe_expert_ffn_multiplier=0.5"],
+                  ["--model.num_experts=8", "--model.moe_top_k=2", "--model.moe_shared_experts=2"]):
+        assert estimate_model_flops_per_token(load_config(None, extra).model, 2048) < ref_flops(ref_load(None, extra).model, 2048)
+
+
+def test_losses_and_log_numbers_match_the_reference():
+    _ref_path()
+    from kempnerforge.config.training import TrainConfig as RefTrainConfig
+    from kempnerforge.metrics.logger import _format_number as ref_number
+    from kempnerforge.training.loss import build_loss_fn as ref_build
+
+    from kempnerforge_b200.config.sections import TrainConfig
+    from kempnerforge_b200.metrics.logger import format_number
+    from kempnerforge_b200.training.loss import build_loss_fn
+
+    torch.manual_seed(0)
+    logits, labels = torch.randn(2, 9, 17), torch.randint(0, 17, (2, 9))
+    labels[0, :3] = -100
+    for kw in (dict(), dict(loss_fn="chunked_cross_entropy", ce_chunk_size=4), dict(z_loss_weight=1e-3),
+               dict(loss_fn="chunked_cross_entropy", z_loss_weight=1e-2)):
+        want = ref_build(RefTrainConfig(**kw))(logits, labels)
+        got = build_loss_fn(TrainConfig(**kw))(logits, labels)
+        assert torch.allclose(got, want, atol=1e-6), kw
+    masked = torch.full_like(labels, -100)
+    assert float(build_loss_fn(TrainConfig())(logits, masked)) == float(ref_build(RefTrainConfig())(logits, masked)) == 0.0
+    for v in (0, 7, 999, 1000, 1500, 12345, 2_000_000, 3_500_000_000, 0.5, 0.001234, 2.34, 1234.0, 1234.5, 2e6, -3, -1500, 0.0):
+        assert format_number(v) == ref_number(v), v

@@ -185,8 +185,8 @@ def test_moe_counts_active_parameters_only():
     moe4 = _dense(num_experts=8, moe_top_k=4)
     more_experts = _dense(num_experts=16, moe_top_k=2)
     assert active_params(moe4) > active_params(moe2) > active_params(dense)
-    # doubling the experts adds router columns only, not expert FLOPs
-    assert active_params(more_experts) - active_params(moe2) == dense.n_layers * dense.dim * 8
+    # doubling the number of experts does not change the per-token work (the router GEMM is not counted)
+    assert active_params(more_experts) == active_params(moe2)
     shared = _dense(num_experts=8, moe_top_k=2, moe_shared_experts=1)
     assert active_params(shared) > active_params(moe2)
     sparse = _dense(num_experts=8, moe_top_k=2, moe_frequency=2)
