@@ -368,3 +368,32 @@ def test_losses_and_log_numbers_match_the_reference():
     assert float(build_loss_fn(TrainConfig())(logits, masked)) == float(ref_build(RefTrainConfig())(logits, masked)) == 0.0
     for v in (0, 7, 999, 1000, 1500, 12345, 2_000_000, 3_500_000_000, 0.5, 0.001234, 2.34, 1234.0, 1234.5, 2e6, -3, -1500, 0.0):
         assert format_number(v) == ref_number(v), v
+
+
+# --------------------------------------------------------------------------- vision-language data
+def test_vlm_text_encoding_collation_and_frame_sampling_match_the_reference():
+    _ref_path()
+    sys.path.insert(0, str(ROOT / "tests"))
+    from kempnerforge.data import video_io as ref_video
+    from kempnerforge.data import vlm_dataset as ref_vlm
+    from test_vlm_data import ToyTokenizer
+
+    from kempnerforge_b200.data import video_io, vlm_dataset
+
+    tok = ToyTokenizer()
+    for prompt, text in ((None, "w1 w2 w3"), ("w9 w8", " ".join(f"w{i}" for i in range(1, 13))), ("w4", "w5"), ("", "w1")):
+        want = ref_vlm._tokenize_and_mask(tok, text, 10, prompt)
+        got = vlm_dataset.encode_text(tok, text, 10, prompt)
+        assert all(torch.equal(a, b) for a, b in zip(got, want)), (prompt, text)
+    samples = []
+    for n in (3, 10, 7):
+        ids = torch.arange(1, n + 1)
+        samples.append({"pixel_values": torch.rand(3, 8, 8), "input_ids": ids, "labels": ids.clone()})
+    want = ref_vlm.VLMCollator(pad_id=0, max_text_len=10)(samples)
+    got = vlm_dataset.VLMCollator(pad_id=0, max_text_len=10)(samples)
+    assert set(got) == set(want)
+    assert all(torch.equal(got[k], want[k]) for k in want)
+    for duration in (0.0, 0.5, 3.0, 20.0, 1000.0):
+        a = ref_video.sample_timestamps(duration, 2.0, 4, 8)
+        b = video_io.sample_timestamps(duration, 2.0, 4, 8)
+        assert b == pytest.approx(a, abs=1e-9), duration
