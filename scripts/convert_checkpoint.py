@@ -3,10 +3,12 @@
 
     python scripts/convert_checkpoint.py to-hf   <dcp_step_dir> <hf_dir> --config cfg.toml [--dtype bfloat16]
     python scripts/convert_checkpoint.py from-hf <hf_dir> <dcp_step_dir> --config cfg.toml
+    python scripts/convert_checkpoint.py dcp-to-hf --dcp-dir <dcp_step_dir> --hf-dir <hf_dir> --config cfg.toml [--dtype bfloat16]
+    python scripts/convert_checkpoint.py hf-to-dcp --hf-dir <hf_dir> --dcp-dir <dcp_step_dir> --config cfg.toml
 
 ``to-hf`` merges per-stage ``pp*/`` sub-directories of a pipeline-parallel checkpoint, renames the keys,
 casts to the export dtype and writes ``model.safetensors`` (or ``pytorch_model.bin``) plus ``config.json``.
-Same CLI contract and key maps as the reference's scripts/convert_checkpoint.py:48-310.
+The sub-command forms are the reference's command line (scripts/convert_checkpoint.py:48-310); the key maps are the same.
 """
 
 from __future__ import annotations
@@ -88,7 +90,8 @@ def build_hf_config(mc, dtype: str = "bfloat16") -> dict:
         "torch_dtype": dtype,
     }
     if mc.is_moe:
-        cfg.update(num_local_experts=mc.num_experts, num_experts_per_tok=mc.moe_top_k)
+        cfg.update(num_local_experts=mc.num_experts, num_experts_per_tok=mc.moe_top_k,
+                   router_aux_loss_coef=mc.moe_aux_loss_weight)
     return cfg
 
 
@@ -159,18 +162,32 @@ def hf_to_dcp(hf_dir: str, dcp_dir: str, model_config) -> None:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[1])
-    ap.add_argument("direction", choices=["to-hf", "from-hf"])
-    ap.add_argument("src")
-    ap.add_argument("dst")
-    ap.add_argument("--config", required=True)
-    ap.add_argument("--dtype", default=None)
-    args, overrides = ap.parse_known_args(argv)
-    cfg = load_config(args.config, overrides)
-    if args.direction == "to-hf":
-        dcp_to_hf(args.src, args.dst, cfg.model, args.dtype or cfg.checkpoint.export_dtype)
+    if argv and argv[0] in ("dcp-to-hf", "hf-to-dcp"):
+        # the reference's command line: sub-commands with named directories
+        ap.add_argument("direction", choices=["dcp-to-hf", "hf-to-dcp"])
+        ap.add_argument("--dcp-dir", required=True, help="DCP checkpoint directory")
+        ap.add_argument("--hf-dir", required=True, help="HuggingFace directory")
+        ap.add_argument("--config", required=True, help="TOML config file")
+        ap.add_argument("--dtype", default=None, choices=["float32", "bfloat16", "float16"])
+        args, overrides = ap.parse_known_args(argv)
+        to_hf = args.direction == "dcp-to-hf"
+        src, dst = (args.dcp_dir, args.hf_dir) if to_hf else (args.hf_dir, args.dcp_dir)
     else:
-        hf_to_dcp(args.src, args.dst, cfg.model)
+        ap.add_argument("direction", choices=["to-hf", "from-hf"])
+        ap.add_argument("src")
+        ap.add_argument("dst")
+        ap.add_argument("--config", required=True)
+        ap.add_argument("--dtype", default=None)
+        args, overrides = ap.parse_known_args(argv)
+        to_hf = args.direction == "to-hf"
+        src, dst = args.src, args.dst
+    cfg = load_config(args.config, overrides)
+    if to_hf:
+        dcp_to_hf(src, dst, cfg.model, args.dtype or cfg.checkpoint.export_dtype)
+    else:
+        hf_to_dcp(src, dst, cfg.model)
     return 0
 
 

@@ -397,3 +397,51 @@ def test_vlm_text_encoding_collation_and_frame_sampling_match_the_reference():
         a = ref_video.sample_timestamps(duration, 2.0, 4, 8)
         b = video_io.sample_timestamps(duration, 2.0, 4, 8)
         assert b == pytest.approx(a, abs=1e-9), duration
+
+
+def test_checkpoint_converter_writes_what_the_reference_converter_writes(tmp_path, monkeypatch):
+    """Both converters export the same DCP checkpoint (MoE with a shared expert) to HuggingFace format: same tensor
+    names, same values, same model description; the reference's sub-command syntax is accepted here too."""
+    import importlib.util
+    import json
+    import os
+
+    ref_root = os.environ.get("KF_REFERENCE_ROOT") or str(ROOT.parent / "reference")
+    ref_script = Path(ref_root) / "scripts" / "convert_checkpoint.py"
+    if not ref_script.exists():
+        pytest.skip("reference scripts not available")
+    _ref_path()
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    from safetensors.torch import load_file
+
+    from kempnerforge_b200.checkpoint import CheckpointManager
+    from kempnerforge_b200.config import load_config
+    from kempnerforge_b200.models.transformer import Transformer
+    from kempnerforge_b200.training.optimizer import build_optimizer
+
+    cfg_file = tmp_path / "m.toml"
+    cfg_file.write_text("\n".join(["[model]", "dim = 64", "n_layers = 2", "n_heads = 4", "n_kv_heads = 2", "vocab_size = 256",
+                                   "max_seq_len = 64", "num_experts = 4", "moe_top_k = 2", "moe_shared_experts = 1", ""]))
+    cfg = load_config(str(cfg_file), [f"--checkpoint.dir={tmp_path / 'ck'}"])
+    torch.manual_seed(0)
+    model = Transformer(cfg.model)
+    CheckpointManager(cfg.checkpoint, model, build_optimizer(model, cfg.optimizer)).save(step=1)
+
+    def run(script, out):
+        spec = importlib.util.spec_from_file_location(f"conv_{out.name}", script)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        argv = ["dcp-to-hf", "--dcp-dir", str(tmp_path / "ck" / "step_1"), "--hf-dir", str(out), "--config", str(cfg_file),
+                "--dtype", "float32"]
+        monkeypatch.setattr(sys, "argv", [str(script), *argv])
+        rc = mod.main() if script == ref_script else mod.main(argv)
+        assert rc in (0, None)
+
+    run(ROOT / "scripts" / "convert_checkpoint.py", tmp_path / "ours")
+    run(ref_script, tmp_path / "ref")
+    ours, ref = load_file(str(tmp_path / "ours" / "model.safetensors")), load_file(str(tmp_path / "ref" / "model.safetensors"))
+    assert set(ours) == set(ref) and all(torch.equal(ours[k], ref[k]) for k in ref)
+    a, b = json.loads((tmp_path / "ours" / "config.json").read_text()), json.loads((tmp_path / "ref" / "config.json").read_text())
+    for key, value in b.items():
+        if key != "torch_dtype":        # the reference always writes bfloat16 there, whatever dtype was exported
+            assert a[key] == value, key
