@@ -21,15 +21,20 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("config")
-    ap.add_argument("--checkpoint", required=True)
-    ap.add_argument("--tasks", required=True)
+    ap.add_argument("config", nargs="?", default=None)
+    ap.add_argument("--config", dest="config_opt", default=None, help="TOML config (the reference's spelling of the positional)")
+    ap.add_argument("--checkpoint", default=None, help="DCP checkpoint directory (converted to HuggingFace format first)")
+    ap.add_argument("--hf-model", default=None, help="already converted HuggingFace directory (skips the conversion)")
+    ap.add_argument("--tasks", default="hellaswag,arc_easy,arc_challenge,winogrande,piqa,boolq")
     ap.add_argument("--tokenizer", default=None)
     ap.add_argument("--batch-size", default="auto")
     ap.add_argument("--limit", type=float, default=None)
     ap.add_argument("--num-fewshot", type=int, default=None)
     ap.add_argument("--output", default=None)
     args, overrides = ap.parse_known_args(argv)
+    args.config = args.config or args.config_opt
+    if not args.hf_model and not (args.checkpoint and args.config):
+        ap.error("give --hf-model, or --checkpoint together with a config")
     try:
         import lm_eval
     except ImportError:
@@ -39,15 +44,19 @@ def main(argv=None) -> int:
 
     from kempnerforge_b200.config import load_config
 
-    cfg = load_config(args.config, overrides)
-    tokenizer = args.tokenizer or cfg.data.tokenizer_path
+    cfg = load_config(args.config, overrides) if args.config else None
+    tokenizer = args.tokenizer or (cfg.data.tokenizer_path if cfg else None) or args.hf_model
     if not tokenizer:
         print("a tokenizer is required (--tokenizer or data.tokenizer_path)", file=sys.stderr)
         return 2
+    export_dtype = cfg.checkpoint.export_dtype if cfg else "bfloat16"
     with tempfile.TemporaryDirectory(prefix="kf_hf_") as tmp:
-        dcp_to_hf(os.path.realpath(args.checkpoint), tmp, cfg.model, cfg.checkpoint.export_dtype)
+        if args.hf_model:
+            tmp = args.hf_model
+        else:
+            dcp_to_hf(os.path.realpath(args.checkpoint), tmp, cfg.model, export_dtype)
         results = lm_eval.simple_evaluate(
-            model="hf", model_args=f"pretrained={tmp},tokenizer={tokenizer},dtype={cfg.checkpoint.export_dtype}",
+            model="hf", model_args=f"pretrained={tmp},tokenizer={tokenizer},dtype={export_dtype}",
             tasks=[t.strip() for t in args.tasks.split(",") if t.strip()], batch_size=args.batch_size,
             limit=args.limit, num_fewshot=args.num_fewshot)
     summary = results.get("results", {})

@@ -41,16 +41,21 @@ def main(argv=None) -> int:
     ap.add_argument("config")
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--prompt", default=None)
-    ap.add_argument("--max-new-tokens", type=int, default=64)
+    # spellings with underscores are the reference's command line (scripts/generate.py:88-147)
+    ap.add_argument("--max-new-tokens", "--max_tokens", dest="max_new_tokens", type=int, default=64)
     ap.add_argument("--temperature", type=float, default=0.8)
-    ap.add_argument("--top-k", type=int, default=0)
-    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--top-k", "--top_k", dest="top_k", type=int, default=0)
+    ap.add_argument("--top-p", "--top_p", dest="top_p", type=float, default=1.0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--interactive", action="store_true")
+    ap.add_argument("--device", default=None, help="default: cuda when available")
+    ap.add_argument("--dtype", default=None, choices=["float32", "bfloat16", "float16"])
     args, overrides = ap.parse_known_args(argv)
     cfg = load_config(args.config, overrides)
-    device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    device = torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu"))
     model = load_model(cfg, args.checkpoint, device)
+    if args.dtype:
+        model = model.to(getattr(torch, args.dtype))
     tok = None
     if cfg.data.tokenizer_path:
         from transformers import AutoTokenizer

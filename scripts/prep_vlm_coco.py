@@ -31,23 +31,10 @@ def iter_official(ann: dict):
         yield names[a["image_id"]], a["caption"].strip()
 
 
-def main(argv=None) -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--annotations", required=True)
-    ap.add_argument("--images", required=True)
-    ap.add_argument("--out", required=True)
-    ap.add_argument("--split", default="train")
-    ap.add_argument("--prompt", default="")
-    ap.add_argument("--max-samples", type=int, default=0)
-    args = ap.parse_args(argv)
-    try:
-        import datasets
-    except ImportError:
-        print("the `datasets` package is required", file=sys.stderr)
-        return 2
-    ann = json.loads(Path(args.annotations).read_text())
-    pairs = iter_karpathy(ann, args.split) if "sentences" in (ann["images"][0] if ann.get("images") else {}) else iter_official(ann)
-    root = Path(args.images)
+def _build_split(datasets, ann_path: Path, root: Path, split: str, prompt: str, limit: int):
+    ann = json.loads(ann_path.read_text())
+    first = ann["images"][0] if ann.get("images") else {}
+    pairs = iter_karpathy(ann, split) if "sentences" in first else iter_official(ann)
     rows = {"image": [], "text": [], "prompt": []}
     missing = 0
     for rel, text in pairs:
@@ -57,13 +44,54 @@ def main(argv=None) -> int:
             continue
         rows["image"].append(str(path))
         rows["text"].append(text)
-        rows["prompt"].append(args.prompt)
-        if args.max_samples and len(rows["text"]) >= args.max_samples:
+        rows["prompt"].append(prompt)
+        if limit and len(rows["text"]) >= limit:
             break
     if not rows["text"]:
+        return None, missing
+    return datasets.Dataset.from_dict(rows).cast_column("image", datasets.Image()), missing
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    # --caption-json / --image-root / --num-samples / --all-splits are the reference's spellings
+    ap.add_argument("--annotations", "--caption-json", dest="annotations", required=True)
+    ap.add_argument("--images", "--image-root", dest="images", required=True)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--split", default="train")
+    ap.add_argument("--prompt", default="")
+    ap.add_argument("--max-samples", "--num-samples", dest="max_samples", type=int, default=0, help="per-split cap, 0 = all")
+    ap.add_argument("--all-splits", action="store_true",
+                    help="read coco_karpathy_{train,val,test}.json beside --annotations and save a DatasetDict")
+    args = ap.parse_args(argv)
+    try:
+        import datasets
+    except ImportError:
+        print("the `datasets` package is required", file=sys.stderr)
+        return 2
+    root = Path(args.images)
+    if args.all_splits:
+        base = Path(args.annotations)
+        folder = base if base.is_dir() else base.parent
+        parts = {}
+        for split in ("train", "val", "test"):
+            path = folder / f"coco_karpathy_{split}.json"
+            if not path.exists():
+                continue
+            ds, missing = _build_split(datasets, path, root, split, args.prompt, args.max_samples)
+            if ds is not None:
+                parts[split] = ds
+                print(f"{split}: {len(ds)} samples ({missing} images missing)")
+        if not parts:
+            print("no coco_karpathy_{train,val,test}.json with usable pairs found", file=sys.stderr)
+            return 1
+        datasets.DatasetDict(parts).save_to_disk(args.out)
+        print(f"wrote splits {sorted(parts)} to {args.out}")
+        return 0
+    ds, missing = _build_split(datasets, Path(args.annotations), root, args.split, args.prompt, args.max_samples)
+    if ds is None:
         print("no (image, caption) pairs found", file=sys.stderr)
         return 1
-    ds = datasets.Dataset.from_dict(rows).cast_column("image", datasets.Image())
     ds.save_to_disk(args.out)
     print(f"wrote {len(ds)} samples to {args.out} ({missing} images missing)")
     return 0

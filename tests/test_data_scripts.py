@@ -78,3 +78,38 @@ def test_coco_converter_writes_a_dataset_of_existing_images(tmp_path):
 
     ds = datasets.load_from_disk(str(tmp_path / "hf"))
     assert len(ds) == 1 and ds[0]["text"] == "a square" and ds[0]["prompt"] == "Describe:"
+
+
+def test_coco_converter_reference_spellings_and_all_splits(tmp_path):
+    pytest.importorskip("datasets")
+    from PIL import Image
+
+    coco = _load("prep_vlm_coco")
+    img_dir = tmp_path / "images"
+    img_dir.mkdir()
+    Image.new("RGB", (8, 8)).save(img_dir / "x.jpg")
+    for split in ("train", "val"):
+        ann = {"images": [{"split": split, "filepath": "", "filename": "x.jpg", "sentences": [{"raw": f"{split} caption"}]}]}
+        (tmp_path / f"coco_karpathy_{split}.json").write_text(json.dumps(ann))
+    rc = coco.main(["--caption-json", str(tmp_path / "coco_karpathy_train.json"), "--image-root", str(img_dir),
+                    "--out", str(tmp_path / "hf"), "--num-samples", "5", "--all-splits"])
+    assert rc == 0
+    import datasets
+
+    dd = datasets.load_from_disk(str(tmp_path / "hf"))
+    assert sorted(dd) == ["train", "val"] and dd["val"][0]["text"] == "val caption"
+
+
+def test_script_command_lines_accept_the_reference_spellings(capsys):
+    gen = _load("generate")
+    with pytest.raises(SystemExit):
+        gen.main(["--help"])
+    text = capsys.readouterr().out
+    for flag in ("--max_tokens", "--top_k", "--top_p", "--device", "--dtype"):
+        assert flag in text, flag
+    harness = _load("eval_harness")
+    with pytest.raises(SystemExit):
+        harness.main(["--help"])
+    text = capsys.readouterr().out
+    for flag in ("--config", "--hf-model", "--checkpoint", "--tasks", "--num-fewshot"):
+        assert flag in text, flag
