@@ -230,3 +230,94 @@ def test_side_stream_publication_is_off_without_the_symmetric_transport():
     assert eng.publish_on_side_stream(eng.groups) is False
     eng.after_optimizer_step()      # single process: nothing to publish, nothing raises
     eng.release()
+
+
+# --------------------------------------------------------------------------- check_env: requirement tags and --init
+def _check_env():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("kf_check_env", Path(__file__).resolve().parents[1] / "scripts" / "check_env.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_check_env_requirement_tags(monkeypatch, tmp_path):
+    ce = _check_env()
+    assert ce.parse_requires(" gpu, slurm ,,hf") == ["gpu", "slurm", "hf"]
+    assert ce.parse_requires(None) == []
+    monkeypatch.delenv("WANDB_API_KEY", raising=False)
+    monkeypatch.delenv("HF_TOKEN", raising=False)
+    monkeypatch.delenv("HUGGING_FACE_HUB_TOKEN", raising=False)
+    out = ce.run_requirements(["wandb", "hf", "nonsense"], {})
+    assert [r["status"] for r in out.values()] == ["miss", "miss", "miss"]
+    assert "unknown" in out["nonsense"]["message"]
+    monkeypatch.setenv("WANDB_API_KEY", "k")
+    monkeypatch.setenv("HUGGING_FACE_HUB_TOKEN", "t")
+    out = ce.run_requirements(["wandb", "hf"], {})
+    assert [r["status"] for r in out.values()] == ["ok", "ok"]
+    text = ce.format_requirements({"hf": {"status": "miss", "message": "no token", "fix": "export HF_TOKEN"}})
+    assert "[MISS]" in text and "fix: export HF_TOKEN" in text
+
+
+def test_check_env_slurm_and_multi_node_rules(monkeypatch, tmp_path):
+    ce = _check_env()
+    monkeypatch.setattr(ce.shutil, "which", lambda name: None)
+    assert ce.require_slurm({})["status"] == "miss"
+    monkeypatch.setattr(ce.shutil, "which", lambda name: "/usr/bin/" + name)
+    monkeypatch.delenv("SLURM_ACCOUNT", raising=False)
+    monkeypatch.delenv("SLURM_QOS", raising=False)
+    assert ce.require_slurm({"slurm": {"require_account": True}})["status"] == "miss"
+    assert ce.require_slurm({"slurm": {"require_account": False}})["status"] == "ok"
+    assert ce.require_slurm({"slurm": {"account": "lab", "require_qos": True}})["status"] == "miss"
+    assert ce.require_slurm({"slurm": {"account": "lab", "qos": "high", "require_qos": True}})["status"] == "ok"
+    # multi-node: needs a configuration, a shared root that exists, and the repository under it
+    assert ce.require_multi_node({})["status"] == "miss"
+    assert ce.require_multi_node({"network": {"shared_fs_root": ""}})["status"] == "miss"
+    assert ce.require_multi_node({"network": {"shared_fs_root": str(tmp_path / "absent")}})["status"] == "miss"
+    assert ce.require_multi_node({"network": {"shared_fs_root": str(tmp_path)}})["status"] == "miss"  # repo elsewhere
+    root = str(ce.ROOT.parent)
+    assert ce.require_multi_node({"network": {"shared_fs_root": root}})["status"] == "warn"
+    cfg = {"network": {"shared_fs_root": root}, "paths": {"checkpoints_root": str(tmp_path)}}
+    assert ce.require_multi_node(cfg)["status"] == "miss"
+    cfg["paths"]["checkpoints_root"] = str(ce.ROOT / "checkpoints")
+    assert ce.require_multi_node(cfg)["status"] == "warn"
+
+
+def test_check_env_init_writes_the_cluster_schema_and_refuses_to_overwrite(monkeypatch, tmp_path, capsys):
+    import tomllib
+
+    ce = _check_env()
+    target = tmp_path / "cluster.toml"
+    monkeypatch.setenv("SLURM_PARTITION", "gpu_part")
+    argv = ["--init", "--non-interactive", "--cluster-config", str(target), "--slurm-account", "lab", "--require-qos", "true",
+            "--slurm-nodes", "4", "--shared-fs-root", "/shared", "--wandb-entity", "team"]
+    assert ce.main(argv) == 0
+    cfg = tomllib.loads(target.read_text())
+    assert set(cfg) == {"cluster", "slurm", "network", "paths", "credentials"}
+    assert cfg["slurm"]["account"] == "lab" and cfg["slurm"]["partition"] == "gpu_part"
+    assert cfg["slurm"]["require_qos"] is True and cfg["slurm"]["require_account"] is True
+    assert cfg["slurm"]["default_nodes"] == 4 and cfg["slurm"]["default_gpus_per_node"] == 8
+    assert cfg["network"] == {"ib_interface": "auto", "shared_fs_root": "/shared"}
+    assert cfg["credentials"]["wandb_entity"] == "team"
+    assert ce.load_cluster_config(target) == cfg
+    capsys.readouterr()
+    assert ce.main(argv) == 1 and "exists" in capsys.readouterr().err
+    assert ce.main(argv + ["--force", "--slurm-account", "other"]) == 0
+    assert tomllib.loads(target.read_text())["slurm"]["account"] == "other"
+
+
+def test_check_env_exit_code_follows_required_misses(monkeypatch, capsys):
+    import json as _json
+
+    ce = _check_env()
+    monkeypatch.delenv("HF_TOKEN", raising=False)
+    monkeypatch.delenv("HUGGING_FACE_HUB_TOKEN", raising=False)
+    assert ce.main(["--requires", "hf", "--json"]) == 1
+    report = _json.loads(capsys.readouterr().out)
+    assert report["requires"]["hf"]["status"] == "miss"
+    monkeypatch.setenv("HF_TOKEN", "x")
+    assert ce.main(["--requires", "hf"]) == 0
+    assert "[OK  ] hf" in capsys.readouterr().out
+    with pytest.raises(SystemExit):
+        ce.main(["--non-interactive"])
