@@ -66,5 +66,10 @@ class AsyncCheckpointer:
             self._future = None
 
     @property
+    def is_pending(self) -> bool:
+        """True from ``save`` until ``wait`` has collected the result (whether or not the write has finished)."""
+        return self._future is not None
+
+    @property
     def pending(self) -> bool:
         return self._future is not None and not self._future.done()

@@ -209,15 +209,17 @@ def config_from_dict(tree: dict[str, Any]) -> JobConfig:
     return _build_dataclass(JobConfig, tree, "job")
 
 
+def load_toml(path: str | Path) -> dict[str, Any]:
+    p = Path(path)
+    if not p.is_file():
+        raise FileNotFoundError(f"Config file not found: {p}")
+    with p.open("rb") as fh:
+        return tomllib.load(fh)
+
+
 def load_config(path: str | Path | None = None, cli_args: list[str] | None = None) -> JobConfig:
     """Defaults, overlaid by the TOML preset at ``path``, overlaid by ``cli_args``."""
-    tree: dict[str, Any] = {}
-    if path is not None:
-        p = Path(path)
-        if not p.is_file():
-            raise FileNotFoundError(f"Config file not found: {p}")
-        with p.open("rb") as fh:
-            tree = tomllib.load(fh)
+    tree: dict[str, Any] = load_toml(path) if path is not None else {}
     if cli_args:
         tree = _deep_merge(tree, parse_cli_overrides(list(cli_args)))
     return config_from_dict(tree)

@@ -27,6 +27,12 @@ class VisionAdapter(nn.Module):
     def output_num_tokens(self, num_input_tokens: int) -> int:
         return num_input_tokens
 
+    def reset_parameters(self) -> None:
+        """Re-run the default initialisation of every Linear (after ``to_empty`` on a meta-device build)."""
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                m.reset_parameters()
+
 
 class MLP2LayerAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, hidden_dim: int | None = None, activation: str = "gelu", **_) -> None:
@@ -71,14 +77,20 @@ def _to_windows(x: torch.Tensor, window: int):
 class AvgPoolAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, pool_window: int = 2, **_) -> None:
         super().__init__()
-        self.window = pool_window
+        if pool_window <= 0:
+            raise ValueError(f"pool_window must be positive (got {pool_window})")
+        self.window = self.pool_window = pool_window
         self.proj = nn.Linear(in_dim, out_dim)
 
     def output_num_tokens(self, num_input_tokens: int) -> int:
         return pooled_token_count(num_input_tokens, self.window)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        win, valid = _to_windows(x, self.window)
+    def forward(self, x: torch.Tensor, pool_window: int | None = None) -> torch.Tensor:
+        """``pool_window`` overrides the configured window for this call (the projection is shared)."""
+        window = self.window if pool_window is None else pool_window
+        if window <= 0:
+            raise ValueError(f"pool_window must be positive (got {window})")
+        win, valid = _to_windows(x, window)
         w = valid.to(x.dtype)[None, :, :, None]
         pooled = (win * w).sum(dim=2) / w.sum(dim=2).clamp_min(1)
         return self.proj(pooled)
@@ -89,7 +101,10 @@ class AttentionalPoolAdapter(VisionAdapter):
         super().__init__()
         if in_dim % pool_heads:
             raise ValueError(f"feature dim {in_dim} is not divisible by pool_heads {pool_heads}")
+        if pool_window <= 0:
+            raise ValueError(f"pool_window must be positive (got {pool_window})")
         self.window, self.heads = pool_window, pool_heads
+        self.pool_window, self.pool_heads, self.head_dim = pool_window, pool_heads, in_dim // pool_heads
         self.q_proj = nn.Linear(in_dim, in_dim)
         self.k_proj = nn.Linear(in_dim, in_dim)
         self.v_proj = nn.Linear(in_dim, in_dim)
@@ -99,11 +114,15 @@ class AttentionalPoolAdapter(VisionAdapter):
     def output_num_tokens(self, num_input_tokens: int) -> int:
         return pooled_token_count(num_input_tokens, self.window, require_divisible=True)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, pool_window: int | None = None) -> torch.Tensor:
+        """``pool_window`` overrides the configured window for this call (images 2x2, video 3x3 share the weights)."""
+        window = self.window if pool_window is None else pool_window
+        if window <= 0:
+            raise ValueError(f"pool_window must be positive (got {window})")
         side = math.isqrt(x.shape[1])
-        if side % self.window:
-            raise ValueError(f"token grid side {side} is not divisible by pool_window {self.window}")
-        win, _ = _to_windows(x, self.window)  # (B, W, P, F)
+        if side % window:
+            raise ValueError(f"token grid side {side} is not divisible by pool_window {window}")
+        win, _ = _to_windows(x, window)  # (B, W, P, F)
         b, w, p, f = win.shape
         hd = f // self.heads
         q = self.q_proj(win.mean(dim=2)).reshape(b * w, 1, self.heads, hd).transpose(1, 2)

@@ -17,17 +17,36 @@ import torch
 from torch import nn
 
 
+class _MissingModule(KeyError, ValueError):
+    """Raised for an unknown module name; both a KeyError (a lookup failed) and a ValueError (a bad argument)."""
+
+
 class ActivationStore:
-    def __init__(self, model: nn.Module, layer_names: list[str], detach_to_cpu: bool = True) -> None:
+    """Hooks are live from construction; ``disable()`` / ``enable()`` (or leaving the ``with`` block) remove and
+    re-install them.  ``layers=`` is accepted as another spelling of ``layer_names``."""
+
+    def __init__(self, model: nn.Module, layer_names: list[str] | None = None, detach_to_cpu: bool = True, *,
+                 layers: list[str] | None = None) -> None:
         self.model = model
-        self.layer_names = list(layer_names)
+        self.layer_names = list(layer_names if layer_names is not None else (layers or []))
         self.to_cpu = detach_to_cpu
         self.activations: dict[str, list[torch.Tensor]] = defaultdict(list)
         self._handles = []
-        modules = dict(model.named_modules())
+        self._on = False
+        self.enable()
+
+    @property
+    def enabled(self) -> bool:
+        return self._on
+
+    def enable(self) -> None:
+        """Install the forward hooks (no-op while they are installed)."""
+        if self._on:
+            return
+        modules = dict(self.model.named_modules())
         missing = [n for n in self.layer_names if n not in modules]
         if missing:
-            raise KeyError(f"modules not found: {missing}; e.g. {sorted(modules)[:8]}")
+            raise _MissingModule(f"modules not found: {missing}; e.g. {sorted(modules)[:8]}")
         for name in self.layer_names:
             self._handles.append(modules[name].register_forward_hook(self._make_hook(name)))
             # make sure the parents of a hooked module run their ordinary (op-by-op) forward
@@ -36,6 +55,7 @@ class ActivationStore:
                 parent = modules.get(".".join(parts[:i]))
                 if parent is not None and hasattr(parent, "ac_mode"):
                     self._handles.append(parent.register_forward_hook(lambda *a: None))
+        self._on = True
 
     def _make_hook(self, name: str):
         def hook(module, inputs, output):
@@ -61,6 +81,9 @@ class ActivationStore:
         for h in self._handles:
             h.remove()
         self._handles = []
+        self._on = False
+
+    disable = remove
 
     def __enter__(self):
         return self
@@ -71,14 +94,26 @@ class ActivationStore:
 
 @torch.no_grad()
 def extract_representations(model: nn.Module, batches, layer_names: list[str], device=None,
+                            batch_size: int | None = None, max_samples: int | None = None,
                             pool: str | None = None) -> dict[str, torch.Tensor]:
-    """Run ``model`` over an iterable of token batches; returns {layer: (N, ...) tensor}.  ``pool`` may be
-    None, "mean" (over the sequence) or "last" (final position)."""
+    """Run ``model`` over token batches; returns {layer: (N, ...) tensor} on the host.
+
+    ``batches`` is an iterable of batches (tensors or dicts with ``input_ids``) or, with ``batch_size`` given or a
+    ``torch.utils.data.Dataset`` passed, a map-style dataset of samples that is batched here in order.
+    ``max_samples`` stops after that many samples and trims the result to it.  ``pool`` may be None, "mean" (over the
+    sequence) or "last" (final position)."""
+    from torch.utils.data import DataLoader, Dataset
+
+    if batch_size is not None or isinstance(batches, Dataset):
+        batches = DataLoader(batches, batch_size=batch_size or 32, shuffle=False)
     was_training = model.training
     model.eval()
     out: dict[str, list[torch.Tensor]] = defaultdict(list)
+    seen = 0
     with ActivationStore(model, layer_names) as store:
         for batch in batches:
+            if max_samples is not None and seen >= max_samples:
+                break
             tokens = batch["input_ids"] if isinstance(batch, dict) else batch
             if device is not None:
                 tokens = tokens.to(device)
@@ -91,10 +126,18 @@ def extract_representations(model: nn.Module, batches, layer_names: list[str], d
                 elif pool == "last":
                     act = act[:, -1]
                 out[name].append(act)
+            seen += tokens.shape[0]
     if was_training:
         model.train()
-    return {k: torch.cat(v, dim=0) for k, v in out.items()}
+    return {k: torch.cat(v, dim=0)[:max_samples] for k, v in out.items()}
 
 
-def save_activations(activations: dict[str, torch.Tensor], path: str) -> None:
-    np.savez(path, **{k.replace(".", "__"): v.float().numpy() for k, v in activations.items()})
+def save_activations(activations: dict[str, torch.Tensor], path) -> None:
+    """One ``.npz`` (the suffix is added when missing, parent folders are created) keyed by the module names."""
+    from pathlib import Path
+
+    path = Path(path)
+    if path.suffix != ".npz":
+        path = path.with_suffix(".npz")
+    path.parent.mkdir(parents=True, exist_ok=True)
+    np.savez(str(path), **{k: v.float().numpy() for k, v in activations.items()})

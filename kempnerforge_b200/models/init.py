@@ -21,7 +21,10 @@ from torch import nn
 _RESIDUAL_SUFFIXES = ("o_proj.weight", "down_proj.weight", "down_w")
 
 
-def init_weights(model: nn.Module, n_layers: int, init_std: float = 0.02) -> None:
+def init_weights(model: nn.Module, n_layers, init_std: float = 0.02) -> None:
+    """``n_layers`` is the layer count, or a model config carrying ``n_layers`` and ``init_std``."""
+    if not isinstance(n_layers, int):
+        n_layers, init_std = n_layers.n_layers, getattr(n_layers, "init_std", init_std)
     scaled = init_std / math.sqrt(2 * max(1, n_layers))
     with torch.no_grad():
         for name, p in model.named_parameters():

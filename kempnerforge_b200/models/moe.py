@@ -30,6 +30,36 @@ from kempnerforge_b200.models.router import build_router
 from kempnerforge_b200.ops import grouped
 
 
+def _counts_tensor(tokens_per_expert, device) -> torch.Tensor:
+    if torch.is_tensor(tokens_per_expert):
+        return tokens_per_expert.to(device=device, dtype=torch.int64)
+    return torch.tensor(list(tokens_per_expert), dtype=torch.int64, device=device)
+
+
+def grouped_expert_forward(x_sorted: torch.Tensor, tokens_per_expert, experts) -> torch.Tensor:
+    """Expert FFNs over rows sorted by expert, for a list of expert modules (``gate_proj``/``up_proj``/``down_proj``
+    Linears, or ``up_proj``/``down_proj`` plus ``act``).  ``tokens_per_expert`` is a list or a device tensor of row
+    counts in expert order.  Parity: kempnerforge/model/moe.py:20-83."""
+    experts = list(experts.values()) if isinstance(experts, nn.ModuleDict) else list(experts)
+    if x_sorted.shape[0] == 0:
+        return torch.zeros_like(x_sorted)
+    swiglu = hasattr(experts[0], "gate_proj")
+    stack = lambda name: grouped.stack_expert_weights([getattr(e, name).weight for e in experts])  # noqa: E731
+    return grouped.grouped_ffn(x_sorted, _counts_tensor(tokens_per_expert, x_sorted.device),
+                               stack("gate_proj") if swiglu else None, stack("up_proj"), stack("down_proj"), "nk",
+                               None if swiglu else experts[0].act)
+
+
+def grouped_expert_forward_packed(x_sorted: torch.Tensor, tokens_per_expert, up_w: torch.Tensor, down_w: torch.Tensor,
+                                  gate_w: torch.Tensor | None, activation) -> torch.Tensor:
+    """Same over packed weights ``up_w``/``gate_w`` (E, dim, hidden) and ``down_w`` (E, hidden, dim); ``activation``
+    is used when ``gate_w`` is None.  Parity: kempnerforge/model/moe.py:86-145."""
+    if x_sorted.shape[0] == 0:
+        return torch.zeros_like(x_sorted)
+    return grouped.grouped_ffn(x_sorted, _counts_tensor(tokens_per_expert, x_sorted.device), gate_w, up_w, down_w, "kn",
+                               None if gate_w is not None else activation)
+
+
 def apply_capacity(weights: torch.Tensor, indices: torch.Tensor, num_experts: int, capacity_factor: float):
     """Zero the routing weight of tokens beyond each expert's per-slot capacity (device only)."""
     t, k = indices.shape

@@ -17,6 +17,8 @@ Parity: kempnerforge/model/vlm.py:56-470.
 
 from __future__ import annotations
 
+from typing import Protocol, runtime_checkable
+
 import torch
 from torch import nn
 
@@ -57,6 +59,17 @@ def prefix_key_padding_mask(frame_mask, num_visual_tokens: int, input_ids: torch
         return None
     text = torch.ones(input_ids.shape, dtype=torch.bool, device=vmask.device)
     return torch.cat([vmask, text], dim=1)
+
+
+@runtime_checkable
+class ModalityStrategy(Protocol):
+    """What a registered modality strategy provides.  Strategies hold no parameters and are not sub-modules of
+    the wrapper, so they are neither sharded nor checkpointed.  Parity: kempnerforge/model/vlm.py:56-74."""
+
+    def prepare(self, wrapper, pixel_values: torch.Tensor, input_ids: torch.Tensor,
+                frame_mask: torch.Tensor | None = None) -> ModalityContext: ...
+
+    def num_image_tokens(self, wrapper) -> int: ...
 
 
 class _PrefixStrategy:

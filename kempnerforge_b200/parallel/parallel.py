@@ -13,6 +13,8 @@ Parity: kempnerforge/distributed/parallel.py:5-10,72-122,125-174,250-302,499-597
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import os
 
 import logging
@@ -99,6 +101,21 @@ def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, **_) -> Da
     return DataParallelEngine(model, pg, transport=transport, allocator=allocator)
 
 
+@dataclass(frozen=True)
+class MixedPrecisionPolicy:
+    """What the data-parallel engine does with dtypes: parameters and activations in ``param_dtype``, gradient
+    reduction and optimizer state in ``reduce_dtype`` (fp32), module inputs cast to ``param_dtype``."""
+
+    param_dtype: torch.dtype = torch.bfloat16
+    reduce_dtype: torch.dtype = torch.float32
+    cast_forward_inputs: bool = True
+
+
+def default_mp_policy(param_dtype: torch.dtype = torch.bfloat16) -> MixedPrecisionPolicy:
+    """Parity: kempnerforge/distributed/parallel.py:72-88."""
+    return MixedPrecisionPolicy(param_dtype=param_dtype)
+
+
 def build_parallel_model(
     model_config,
     device: torch.device,
@@ -111,9 +128,30 @@ def build_parallel_model(
     transport: str | None = None,
     vlm_config=None,
     ep_in_dp: bool = False,
+    vision_config=None,
+    adapter_config=None,
+    mp_policy: MixedPrecisionPolicy | None = None,
+    frames_per_clip: int = 1,
     **model_kwargs,
 ) -> nn.Module:
-    """Build the registered model and apply TP -> EP -> FP8 -> AC -> sharded DP."""
+    """Build the registered model and apply TP -> EP -> FP8 -> AC -> sharded DP.
+
+    ``mp_policy`` (see ``default_mp_policy``) overrides ``param_dtype``.  With ``vision_config`` and ``adapter_config``
+    given as well as ``vlm_config`` the result is the vision-language wrapper of ``build_parallel_vlm``.
+    """
+    if mp_policy is not None:
+        if mp_policy.reduce_dtype != torch.float32:
+            raise ValueError("gradients are reduced in fp32; other reduce dtypes are not supported")
+        param_dtype = mp_policy.param_dtype
+    if vision_config is not None:
+        if vlm_config is None or adapter_config is None:
+            raise ValueError("a vision-language model needs vision_config, adapter_config and vlm_config together")
+        from types import SimpleNamespace
+
+        job = SimpleNamespace(model=model_config, vision_encoder=vision_config, adapter=adapter_config, vlm=vlm_config,
+                              video=SimpleNamespace(max_frames=frames_per_clip) if frames_per_clip != 1 else None,
+                              train=SimpleNamespace(param_dtype=param_dtype, activation_checkpointing=ac_mode))
+        return build_parallel_vlm(job, device, device_mesh, transport=transport)
     builder = registry.get("model", model_config.model_type)
     with torch.device(device):  # parameters are drawn on the target device (fp32), then cast
         model = builder(model_config, **({"vlm_config": vlm_config} if vlm_config is not None else {}), **model_kwargs)

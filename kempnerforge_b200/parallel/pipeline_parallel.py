@@ -53,6 +53,15 @@ class PipelineStageModule(Transformer):
             return self.forward_hidden(x, doc_ids=doc_ids)
         return self.forward_hidden(None, modality=ModalityContext(inputs_embeds=x), doc_ids=doc_ids)
 
+    def init_weights_and_freqs(self) -> None:
+        """(Re-)draw this stage's weights and build its rotary tables, e.g. after ``to_empty`` on a meta build."""
+        from kempnerforge_b200.models.init import init_weights
+
+        device = next(self.parameters()).device
+        init_weights(self, self.config)
+        self._rope_cos = None
+        self.rope_tables(device, 0, 1)
+
     def stage_loss(self, hidden: torch.Tensor, labels: torch.Tensor, z_loss_weight: float = 0.0) -> torch.Tensor:
         from kempnerforge_b200.ops import functional as F
 
@@ -61,6 +70,18 @@ class PipelineStageModule(Transformer):
 
 def build_stage_module(model_config, pp_rank: int, pp_size: int) -> PipelineStageModule:
     return PipelineStageModule(model_config, pp_rank, pp_size)
+
+
+def build_pipeline_stage(stage_module: PipelineStageModule, device_mesh, device: torch.device, batch_size: int = 0,
+                         seq_len: int = 0, param_dtype: torch.dtype = torch.bfloat16, schedule: str = "1f1b"):
+    """A runnable stage (``PipelineRunner``) for a stage module: moves it to ``device`` / ``param_dtype`` and binds the
+    pipeline process group of ``device_mesh``.  Activation shapes are taken from the first micro-batch, so
+    ``batch_size`` and ``seq_len`` are accepted only for call compatibility.
+    Parity: kempnerforge/distributed/pipeline_parallel.py:259-306."""
+    pp_mesh = get_pp_mesh(device_mesh)
+    stage_module.to(device=device, dtype=param_dtype)
+    stage_module.rope_tables(device, 0, 1)
+    return PipelineRunner(stage_module, pp_mesh.get_group() if pp_mesh is not None else None, schedule)
 
 
 def get_pp_mesh(mesh):

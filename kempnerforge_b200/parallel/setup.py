@@ -41,6 +41,10 @@ def get_world_info() -> tuple[int, int, int]:
     return 0, 0, 1
 
 
+def is_rank_zero() -> bool:
+    return get_world_info()[0] == 0
+
+
 def _detect_ib_interface() -> str | None:
     try:
         out = subprocess.run(["ip", "-br", "addr"], capture_output=True, text=True, timeout=5).stdout

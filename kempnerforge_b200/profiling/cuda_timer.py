@@ -60,9 +60,38 @@ class CUDATimer:
 
 
 class CUDATimerCollection:
-    def __init__(self, enabled: bool = True) -> None:
+    """Named timers.  ``CUDATimerCollection(["forward", "backward"], enabled=...)`` pre-declares regions for the
+    ``start(region)`` / ``stop(region)`` / ``elapsed_ms(region)`` / ``elapsed_all()`` calls (latest interval of each
+    region, 0.0 when it never ran); ``timer(name)`` context managers and ``summary()`` accumulate every interval."""
+
+    def __init__(self, regions: list[str] | bool | None = None, enabled: bool = True) -> None:
+        if isinstance(regions, bool):          # CUDATimerCollection(False)
+            regions, enabled = None, regions
         self.enabled = enabled
+        self.regions = list(regions or [])
         self._timers: dict[str, CUDATimer] = defaultdict(CUDATimer)
+        if enabled:
+            for name in self.regions:
+                self._timers[name].name = name
+
+    def start(self, region: str) -> None:
+        if self.enabled:
+            self._timers[region].start()
+
+    def stop(self, region: str) -> None:
+        if self.enabled:
+            self._timers[region].stop()
+
+    def elapsed_ms(self, region: str) -> float:
+        """Milliseconds of the region's most recent start/stop interval (synchronises); 0.0 if disabled or never run."""
+        if not self.enabled or region not in self._timers:
+            return 0.0
+        ms = self._timers[region].elapsed_ms()
+        return ms[-1] if ms else 0.0
+
+    def elapsed_all(self) -> dict[str, float]:
+        names = list(dict.fromkeys([*self.regions, *self._timers]))
+        return {name: self.elapsed_ms(name) for name in names}
 
     def timer(self, name: str):
         if not self.enabled:

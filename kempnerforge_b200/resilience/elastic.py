@@ -30,6 +30,10 @@ class SLURMInfo:
     array_task_id: str | None = None
     partition: str | None = None
 
+    @property
+    def is_requeued(self) -> bool:
+        return self.restart_count > 0
+
 
 def get_slurm_info() -> SLURMInfo | None:
     env = os.environ

@@ -62,6 +62,10 @@ class ShutdownHandler:
     def should_shutdown(self) -> bool:
         return self._requested.is_set()
 
+    @property
+    def shutdown_requested(self) -> bool:
+        return self._requested.is_set()
+
     def request(self) -> None:
         """Programmatic equivalent of receiving a signal (used by tests and hooks)."""
         self._on_signal(signal.SIGUSR1, None)

@@ -34,6 +34,10 @@ def chunked_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, chunk_size
     return total / (lab != IGNORE_INDEX).sum().clamp_min(1).float()
 
 
+cross_entropy_loss = cross_entropy
+chunked_cross_entropy_loss = chunked_cross_entropy
+
+
 def z_loss(logits: torch.Tensor, weight: float = 1e-4) -> torch.Tensor:
     """weight * mean(logsumexp(logits)^2) over all positions."""
     return weight * torch.logsumexp(logits.float(), dim=-1).pow(2).mean()

@@ -43,7 +43,7 @@ def test_activation_store_and_extract_representations(tmp_path):
     path = str(tmp_path / "acts.npz")
     save_activations(reps, path)
     loaded = np.load(path)
-    assert set(loaded.files) == {"layers__0__attention", "layers__1__mlp", "norm"}
+    assert set(loaded.files) == {"layers.0.attention", "layers.1.mlp", "norm"}
 
 
 # ------------------------------------------------------------------ sampling

@@ -87,7 +87,7 @@ def test_extract_representations_pooling_modes_and_save(tmp_path):
     path.parent.mkdir()
     save_activations(full, str(path))
     loaded = np.load(str(path) + ".npz")
-    assert set(loaded.files) == {"layers__1", "norm"} and loaded["norm"].shape == (6, 6, 32)
+    assert set(loaded.files) == {"layers.1", "norm"} and loaded["norm"].shape == (6, 6, 32)
 
 
 # --------------------------------------------------------------------------- training hooks
@@ -289,3 +289,33 @@ def test_optimizer_config_rules():
         build_optimizer(nn.Linear(2, 2), OptimizerConfig(name="sgd_with_hats"))
     opt = build_optimizer(nn.Linear(2, 2), OptimizerConfig(name="adamw", betas=(0.8, 0.9), eps=1e-6))
     assert opt.param_groups[0]["betas"] == (0.8, 0.9) and opt.param_groups[0]["eps"] == 1e-6
+
+
+def test_activation_store_enable_disable_and_dataset_extraction(tmp_path):
+    m = _model()
+    store = ActivationStore(m, layers=["norm"])
+    assert store.enabled and store.layer_names == ["norm"]
+    store.disable()
+    assert not store.enabled
+    tokens = torch.randint(0, 40, (2, 5))
+    m(tokens)
+    assert store.get("norm") == []            # nothing captured while disabled
+    store.enable()
+    store.enable()                            # idempotent
+    m(tokens)
+    assert store.get("norm").shape[0] == 2
+    store.disable()
+    with pytest.raises(ValueError):
+        ActivationStore(m, layers=["nope"])
+
+    class Samples(torch.utils.data.Dataset):
+        def __len__(self):
+            return 7
+
+        def __getitem__(self, i):
+            return {"input_ids": torch.full((5,), i % 40, dtype=torch.long)}
+
+    reps = extract_representations(m, Samples(), ["norm"], torch.device("cpu"), batch_size=3, max_samples=5)
+    assert reps["norm"].shape[0] == 5
+    everything = extract_representations(m, Samples(), ["norm"], batch_size=4)
+    assert everything["norm"].shape[0] == 7 and torch.equal(everything["norm"][:5], reps["norm"])

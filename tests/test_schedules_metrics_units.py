@@ -333,3 +333,44 @@ def test_get_logger_namespaces_and_format_metrics():
     for piece in ("loss=2.3457", "lr=3.00e-04", "grad_norm=0.812", "tok/s=12,346", "mfu=41.2%", "mem=10.1/180GB",
                   "step_time=0.53s", "count=7", "tag=x"):
         assert piece in line, piece
+
+
+# --------------------------------------------------------------------------- region timers / interval memory reports
+def test_timer_collection_region_calls_and_disabled_mode():
+    from kempnerforge_b200.profiling.cuda_timer import CUDATimerCollection
+
+    timers = CUDATimerCollection(["forward", "backward", "never"], enabled=True)
+    timers.start("forward")
+    sum(range(1000))
+    timers.stop("forward")
+    timers.start("backward")
+    timers.stop("backward")
+    all_ms = timers.elapsed_all()
+    assert list(all_ms) == ["forward", "backward", "never"] and all_ms["never"] == 0.0
+    assert all_ms["forward"] >= 0.0 and timers.elapsed_ms("forward") == all_ms["forward"]
+    with timers.timer("extra"):
+        pass
+    assert "extra" in timers.elapsed_all() and timers.summary()["forward"]["count"] == 1
+    off = CUDATimerCollection(["forward"], enabled=False)
+    off.start("forward")
+    off.stop("forward")
+    assert off.elapsed_ms("forward") == 0.0 and off.elapsed_all() == {"forward": 0.0} and not off.enabled
+    assert CUDATimerCollection(False).enabled is False and CUDATimerCollection().enabled is True
+
+
+def test_memory_monitor_interval_report_without_a_gpu(caplog):
+    import logging
+
+    from kempnerforge_b200.metrics.memory import (DeviceMemoryMonitor, format_memory_stats, get_memory_utilization,
+                                                  reset_peak_memory)
+
+    assert get_memory_utilization() == 0.0 or 0.0 < get_memory_utilization() <= 1.0
+    text = format_memory_stats()
+    assert text.startswith("GPU mem: ") and "GB total (" in text
+    reset_peak_memory()
+    mon = DeviceMemoryMonitor(snapshot_step=3, snapshot_dir="unused_dir")
+    with caplog.at_level(logging.INFO):
+        stats = mon.report(3)
+    assert {"allocated_gb", "peak_gb", "reserved_gb", "total_gb", "mem_utilization"} <= set(stats)
+    assert "[step 3] GPU mem:" in caplog.text and mon._snapshot_taken
+    assert DeviceMemoryMonitor(None, "somewhere").snapshot_dir == "somewhere"
