@@ -243,8 +243,8 @@ def run_ours(args) -> dict:
             peaks = json.load(fh)
     except OSError:
         pass
-    mfu_nominal = compute_mfu(cfg.model, value, world, seq, 2250.0)
-    mfu_measured = compute_mfu(cfg.model, value, world, seq, peaks.get("bf16_tflops", 1590.0))
+    mfu_nominal = compute_mfu(cfg.model, value, world, 2250.0, seq)
+    mfu_measured = compute_mfu(cfg.model, value, world, peaks.get("bf16_tflops", 1590.0), seq)
     base = H200_PUBLISHED_TOKS.get(world)
     return {
         "metric": f"{args.model}_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,

@@ -217,8 +217,10 @@ def load_toml(path: str | Path) -> dict[str, Any]:
         return tomllib.load(fh)
 
 
-def load_config(path: str | Path | None = None, cli_args: list[str] | None = None) -> JobConfig:
-    """Defaults, overlaid by the TOML preset at ``path``, overlaid by ``cli_args``."""
+def load_config(path: str | Path | None = None, cli_args: list[str] | None = None, *,
+                config_path: str | Path | None = None) -> JobConfig:
+    """Defaults, overlaid by the TOML preset at ``path`` (also ``config_path=``), overlaid by ``cli_args``."""
+    path = path if path is not None else config_path
     tree: dict[str, Any] = load_toml(path) if path is not None else {}
     if cli_args:
         tree = _deep_merge(tree, parse_cli_overrides(list(cli_args)))

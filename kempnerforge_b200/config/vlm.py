@@ -38,10 +38,10 @@ def _patterns(**extra: list[str]) -> dict[str, list[str]]:
     return out
 
 
-def pooled_token_count(num_tokens: int, window: int, require_divisible: bool = False) -> int:
-    """Tokens left after pooling a square grid of ``num_tokens`` with a ``window``² kernel."""
-    side = math.isqrt(num_tokens)
-    _require(side * side == num_tokens, f"pooling adapters need a square token grid (got {num_tokens})")
+def pooled_token_count(num_input_tokens: int, window: int, require_divisible: bool = False) -> int:
+    """Tokens left after pooling a square grid of ``num_input_tokens`` with a ``window``² kernel."""
+    side = math.isqrt(num_input_tokens)
+    _require(side * side == num_input_tokens, f"pooling adapters need a square token grid (got {num_input_tokens})")
     if require_divisible:
         _require(side % window == 0, f"token grid side {side} is not divisible by pool_window {window}")
     out_side = -(-side // window)

@@ -30,10 +30,10 @@ def _one_dataset(config, path: str = "", hf_name: str = "", hf_config: str = "",
         eos = _eos_id(config) if dc.pack_sequences else None
         return MemoryMappedDataset(path, window, dc.file_pattern, dc.pack_sequences, eos)
     if dc.hf_streaming:
-        return StreamingHuggingFaceDataset(hf_name, window, dc.tokenizer_path, hf_config or None,
+        return StreamingHuggingFaceDataset(hf_name, tc.seq_len, dc.tokenizer_path, hf_config or None,
                                            dc.hf_dataset_split, dc.hf_dataset_text_field, rank, world,
-                                           dc.pack_sequences)
-    return HuggingFaceDataset(hf_name, window, dc.tokenizer_path, hf_config or None, dc.hf_dataset_split,
+                                           dc.pack_sequences, seed=tc.effective_data_seed)
+    return HuggingFaceDataset(hf_name, tc.seq_len, dc.tokenizer_path, hf_config or None, dc.hf_dataset_split,
                               dc.hf_dataset_text_field, dc.pack_sequences)
 
 

@@ -90,7 +90,7 @@ class MemoryMappedDataset(Dataset):
         return {"input_ids": tok[:-1], "labels": tok[1:]}
 
     def state_dict(self) -> dict:
-        return {"epoch": self._epoch}
+        return {"epoch": self._epoch, "total_samples": len(self)}
 
     def load_state_dict(self, state: dict) -> None:
         self._epoch = state.get("epoch", 0)
@@ -112,6 +112,14 @@ class MemoryMappedDataset(Dataset):
             pass
 
 
+def _encode_plain(tokenizer, text: str) -> list[int]:
+    """Token ids of ``text`` without BOS / EOS or other special tokens (the packer adds EOS itself)."""
+    try:
+        return list(tokenizer.encode(text, add_special_tokens=False))
+    except TypeError:  # minimal tokenizers without the keyword
+        return list(tokenizer.encode(text))
+
+
 def _pack_token_stream(stream, seq_len: int) -> list[np.ndarray]:
     """Cut a stream of token lists into windows of exactly ``seq_len`` tokens (the tail is dropped)."""
     out, buf = [], []
@@ -124,19 +132,25 @@ def _pack_token_stream(stream, seq_len: int) -> list[np.ndarray]:
 
 
 class HuggingFaceDataset(Dataset):
-    """Eagerly tokenised + packed text dataset (small corpora, tests, quick experiments)."""
+    """Eagerly tokenised + packed text dataset (small corpora, tests, quick experiments).
+
+    ``seq_len`` is the training sequence length: documents are tokenised without special tokens, joined with EOS
+    (id 0 when the tokenizer has none) and cut into windows of ``seq_len + 1`` tokens, so a sample's ``input_ids``
+    and ``labels`` are ``seq_len`` long.  Documents that tokenise to nothing are skipped.
+    """
 
     def __init__(self, dataset_name: str, seq_len: int, tokenizer_path: str, dataset_config: str | None = None,
                  split: str = "train", text_field: str = "text", pack_sequences: bool = False,
                  raw_dataset=None, tokenizer=None) -> None:
         self.seq_len = seq_len
         self._pack = pack_sequences
+        self._sample_idx = 0
         if tokenizer is None:
             from transformers import AutoTokenizer
 
             tokenizer = AutoTokenizer.from_pretrained(tokenizer_path)
         self.tokenizer = tokenizer
-        self._eos = tokenizer.eos_token_id
+        self._eos = tokenizer.eos_token_id or 0
         if raw_dataset is None:
             import datasets
 
@@ -144,15 +158,13 @@ class HuggingFaceDataset(Dataset):
 
         def stream():
             for row in raw_dataset:
-                text = row[text_field]
-                if not text or not text.strip():
+                ids = _encode_plain(tokenizer, row[text_field] or "")
+                if not ids:
                     continue
-                ids = list(tokenizer.encode(text))
-                if self._eos is not None:
-                    ids.append(self._eos)
+                ids.append(self._eos)
                 yield ids
 
-        self._samples = _pack_token_stream(stream(), seq_len)
+        self._samples = _pack_token_stream(stream(), seq_len + 1)
         self._epoch = 0
         log.info("HuggingFaceDataset %s: %d samples of %d tokens", dataset_name, len(self._samples), seq_len)
 
@@ -161,24 +173,33 @@ class HuggingFaceDataset(Dataset):
 
     def __getitem__(self, idx: int) -> dict[str, torch.Tensor]:
         window = self._samples[idx]
-        if self._pack and self._eos is not None:
+        if self._pack:
             return compute_packed_output(window, self._eos)
         tok = torch.from_numpy(window)
         return {"input_ids": tok[:-1], "labels": tok[1:]}
 
     def state_dict(self) -> dict:
-        return {"epoch": self._epoch, "num_samples": len(self._samples)}
+        return {"epoch": self._epoch, "sample_idx": self._sample_idx, "total_sequences": len(self._samples)}
 
     def load_state_dict(self, state: dict) -> None:
         self._epoch = state.get("epoch", 0)
+        self._sample_idx = state.get("sample_idx", 0)
 
 
 class StreamingHuggingFaceDataset(IterableDataset):
-    """Lazily tokenised stream; rank r takes documents r, r + world, ...; resumable by document count."""
+    """Lazily tokenised stream; rank r takes documents r, r + world, ...; resumable by this rank's document count.
+
+    ``seq_len`` is the training sequence length (windows of ``seq_len + 1`` tokens, as in ``HuggingFaceDataset``).
+    A Hugging Face stream is shuffled through a ``shuffle_buffer_size`` buffer seeded with ``seed + epoch``, so every
+    epoch has its own order and a resumed run sees the order of the run it continues.
+    Parity: kempnerforge/data/dataset.py:322-468.
+    """
 
     def __init__(self, dataset_name: str, seq_len: int, tokenizer_path: str, dataset_config: str | None = None,
                  split: str = "train", text_field: str = "text", rank: int = 0, world_size: int = 1,
-                 pack_sequences: bool = False, raw_stream=None, tokenizer=None) -> None:
+                 pack_sequences: bool = False, raw_stream=None, tokenizer=None, seed: int = 42,
+                 shuffle_buffer_size: int = 10000) -> None:
+        self.seed, self.shuffle_buffer_size = seed, shuffle_buffer_size
         self.dataset_name, self.dataset_config, self.split = dataset_name, dataset_config, split
         self.seq_len, self.text_field = seq_len, text_field
         self.tokenizer_path = tokenizer_path
@@ -202,11 +223,15 @@ class StreamingHuggingFaceDataset(IterableDataset):
             return self._raw_stream
         import datasets
 
-        return datasets.load_dataset(self.dataset_name, self.dataset_config, split=self.split, streaming=True)
+        ds = datasets.load_dataset(self.dataset_name, self.dataset_config, split=self.split, streaming=True)
+        if self.shuffle_buffer_size > 0:
+            ds = ds.shuffle(seed=self.seed + self._epoch, buffer_size=self.shuffle_buffer_size)
+        return ds
 
     def __iter__(self):
         tok = self._ensure_tokenizer()
-        eos = tok.eos_token_id
+        eos = tok.eos_token_id or 0
+        window_len = self.seq_len + 1
         info = torch.utils.data.get_worker_info()
         n_workers, wid = (info.num_workers, info.id) if info is not None else (1, 0)
         stride = self.world_size * n_workers
@@ -219,29 +244,29 @@ class StreamingHuggingFaceDataset(IterableDataset):
             seen += 1
             if seen <= self._skip_docs:
                 continue
-            text = row[self.text_field]
             self._docs_consumed = seen
-            if not text or not text.strip():
+            ids = _encode_plain(tok, row[self.text_field] or "")
+            if not ids:
                 continue
-            buf.extend(tok.encode(text))
-            if eos is not None:
-                buf.append(eos)
-            while len(buf) >= self.seq_len:
-                window = np.asarray(buf[: self.seq_len], dtype=np.int64)
-                buf = buf[self.seq_len :]
-                if self._pack and eos is not None:
+            buf.extend(ids)
+            buf.append(eos)
+            while len(buf) >= window_len:
+                window = np.asarray(buf[:window_len], dtype=np.int64)
+                buf = buf[window_len:]
+                if self._pack:
                     yield compute_packed_output(window, eos)
                 else:
                     t = torch.from_numpy(window)
                     yield {"input_ids": t[:-1], "labels": t[1:]}
         self._skip_docs = 0
+        self._docs_consumed = 0
         self._epoch += 1
 
     def state_dict(self) -> dict:
-        return {"docs_consumed": self._docs_consumed, "epoch": self._epoch}
+        return {"epoch": self._epoch, "rank_docs_consumed": self._docs_consumed}
 
     def load_state_dict(self, state: dict) -> None:
-        self._skip_docs = state.get("docs_consumed", 0)
+        self._skip_docs = state.get("rank_docs_consumed", state.get("docs_consumed", 0))
         self._docs_consumed = self._skip_docs
         self._epoch = state.get("epoch", 0)
 
@@ -279,9 +304,14 @@ class MixtureDataset(Dataset):
         return sample
 
     def state_dict(self) -> dict:
-        return {"datasets": [d.state_dict() if hasattr(d, "state_dict") else {} for d in self._datasets]}
+        return {f"dataset_{i}": d.state_dict() for i, d in enumerate(self._datasets) if hasattr(d, "state_dict")}
 
     def load_state_dict(self, state: dict) -> None:
-        for d, s in zip(self._datasets, state.get("datasets", [])):
-            if hasattr(d, "load_state_dict"):
-                d.load_state_dict(s)
+        legacy = state.get("datasets")          # list form written by earlier checkpoints of this package
+        for i, d in enumerate(self._datasets):
+            if not hasattr(d, "load_state_dict"):
+                continue
+            if f"dataset_{i}" in state:
+                d.load_state_dict(state[f"dataset_{i}"])
+            elif legacy is not None and i < len(legacy):
+                d.load_state_dict(legacy[i])

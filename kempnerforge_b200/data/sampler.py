@@ -39,8 +39,13 @@ def _replica_info(num_replicas, rank):
 
 
 class DistributedSampler(Sampler[int]):
-    def __init__(self, dataset_size, num_replicas: int | None = None, rank: int | None = None,
-                 shuffle: bool = True, seed: int = 0, drop_last: bool = True) -> None:
+    def __init__(self, dataset_size=None, num_replicas: int | None = None, rank: int | None = None,
+                 shuffle: bool = True, seed: int = 0, drop_last: bool = True, *, dataset=None) -> None:
+        """The first argument is a sample count or a sized dataset (also accepted as ``dataset=``)."""
+        if dataset_size is None:
+            if dataset is None:
+                raise TypeError("DistributedSampler needs a dataset or its size")
+            dataset_size = dataset
         self.dataset_size = dataset_size if isinstance(dataset_size, int) else len(dataset_size)
         self.num_replicas, self.rank = _replica_info(num_replicas, rank)
         self.shuffle, self.seed, self.drop_last = shuffle, seed, drop_last

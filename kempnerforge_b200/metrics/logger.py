@@ -72,8 +72,10 @@ def setup_logging(level: int | str = logging.INFO, all_ranks: bool = False) -> N
         _configured = True
 
 
-def get_logger(name: str = "kempnerforge_b200") -> logging.Logger:
-    setup_logging()
+def get_logger(name: str = "kempnerforge_b200", rank_zero_only: bool = True) -> logging.Logger:
+    """``rank_zero_only=False`` on the call that first configures logging lets every rank print."""
+    if not _configured:
+        setup_logging(all_ranks=not rank_zero_only)
     if not name.startswith("kempnerforge_b200"):
         name = f"kempnerforge_b200.{name}"
     return logging.getLogger(name)

@@ -76,13 +76,20 @@ def active_params(model_config) -> int:
     return total + c.vocab_size * d  # output head
 
 
-def estimate_model_flops_per_token(model_config, seq_len: int) -> float:
-    return 6.0 * active_params(model_config) + 12.0 * model_config.n_layers * model_config.dim * seq_len
+def estimate_model_flops_per_token(config, seq_len: int | None = None) -> float:
+    seq_len = config.max_seq_len if seq_len is None else seq_len
+    return 6.0 * active_params(config) + 12.0 * config.n_layers * config.dim * seq_len
 
 
-def compute_mfu(model_config, tokens_per_sec: float, num_gpus: int = 1, seq_len: int = 2048,
-                peak_tflops: float | None = None) -> float:
-    """Utilisation in [0, 1] of ``num_gpus`` GPUs at ``tokens_per_sec`` (whole job)."""
-    peak = peak_tflops if peak_tflops is not None else get_gpu_peak_tflops()
-    achieved = estimate_model_flops_per_token(model_config, seq_len) * tokens_per_sec / max(1, num_gpus)
-    return achieved / (peak * 1e12)
+def compute_mfu(config, tokens_per_sec: float, num_gpus: int = 1, gpu_peak_tflops: float | None = None,
+                seq_len: int | None = None, *, peak_tflops: float | None = None) -> float:
+    """Utilisation in [0, 1] of ``num_gpus`` GPUs at ``tokens_per_sec`` (whole job).  ``gpu_peak_tflops`` (also
+    spelled ``peak_tflops``) is per GPU and detected when omitted; ``seq_len`` defaults to the model's maximum.
+    Parity: kempnerforge/metrics/mfu.py:150-180."""
+    peak = gpu_peak_tflops if gpu_peak_tflops is not None else peak_tflops
+    if peak is None:
+        peak = get_gpu_peak_tflops()
+    if not peak or not num_gpus:
+        return 0.0
+    seq = seq_len if seq_len is not None else config.max_seq_len
+    return estimate_model_flops_per_token(config, seq) * tokens_per_sec / (peak * 1e12 * num_gpus)

@@ -12,6 +12,7 @@ unsynchronised host clock.
 
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 
@@ -40,7 +41,10 @@ class StepMetrics:
 
 
 class WandBBackend:
-    def __init__(self, project: str, run_name: str | None, run_id: str = "", config: dict | None = None) -> None:
+    def __init__(self, project, run_name: str | None = None, run_id: str = "", config: dict | None = None) -> None:
+        """``project`` is a project name, or a metrics config carrying ``wandb_project / wandb_run_name / wandb_run_id``."""
+        if hasattr(project, "wandb_project"):
+            project, run_name, run_id = project.wandb_project, project.wandb_run_name, project.wandb_run_id
         import wandb
 
         self._wandb = wandb
@@ -55,7 +59,9 @@ class WandBBackend:
 
 
 class TensorBoardBackend:
-    def __init__(self, log_dir: str) -> None:
+    def __init__(self, log_dir) -> None:
+        """``log_dir`` is a directory, or a metrics config carrying ``tensorboard_dir``."""
+        log_dir = getattr(log_dir, "tensorboard_dir", log_dir)
         from torch.utils.tensorboard import SummaryWriter
 
         self.writer = SummaryWriter(log_dir)
@@ -70,11 +76,22 @@ class TensorBoardBackend:
 
 
 class MetricsTracker:
-    def __init__(self, config, model_config=None, num_gpus: int = 1, seq_len: int = 2048, rank: int = 0,
-                 peak_tflops: float | None = None) -> None:
+    def __init__(self, config, model_config=None, num_gpus: int | None = None, seq_len: int = 2048, rank: int = 0,
+                 peak_tflops: float | None = None, *, gpu_peak_tflops: float | None = None) -> None:
+        """``config`` is the metrics section; a whole job config works too (``MetricsTracker(job, num_gpus)``), in which
+        case the model section, the sequence length and the calling process's rank are taken from it / the environment."""
+        if hasattr(config, "metrics") and hasattr(config, "model"):
+            job = config
+            if isinstance(model_config, int):          # MetricsTracker(job, num_gpus[, gpu_peak_tflops])
+                if num_gpus is not None and peak_tflops is None:
+                    peak_tflops = float(num_gpus)
+                num_gpus = model_config
+            config, model_config, seq_len = job.metrics, job.model, job.train.seq_len
+            rank = int(os.environ.get("RANK", rank))
+        peak_tflops = peak_tflops if peak_tflops is not None else gpu_peak_tflops
         self.config = config
         self.model_config = model_config
-        self.num_gpus = num_gpus
+        self.num_gpus = 1 if num_gpus is None else num_gpus
         self.seq_len = seq_len
         self.rank = rank
         self.backends: list = []
@@ -137,7 +154,7 @@ class MetricsTracker:
             return None
         mfu = 0.0
         if self.model_config is not None:
-            mfu = compute_mfu(self.model_config, tps, self.num_gpus, self.seq_len, self.peak_tflops)
+            mfu = compute_mfu(self.model_config, tps, self.num_gpus, self.peak_tflops, self.seq_len)
         mem = get_memory_stats()
         m = StepMetrics(step, loss, grad_norm, lr, tps, mfu, dt, mem["peak_gb"], mem["total_gb"],
                         self._smoothed_loss, self._smoothed_tps)

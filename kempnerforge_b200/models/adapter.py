@@ -139,5 +139,5 @@ registry.register("adapter", "avgpool", AvgPoolAdapter)
 registry.register("adapter", "attentional_pool", AttentionalPoolAdapter)
 
 
-def build_adapter(config, in_dim: int, out_dim: int) -> VisionAdapter:
-    return registry.get("adapter", config.type)(in_dim, out_dim, **config.extra_kwargs())
+def build_adapter(adapter_config, in_dim: int, out_dim: int) -> VisionAdapter:
+    return registry.get("adapter", adapter_config.type)(in_dim, out_dim, **adapter_config.extra_kwargs())

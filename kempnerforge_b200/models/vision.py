@@ -23,11 +23,11 @@ class VisionEncoder(nn.Module):
 
 
 class RandomVisionEncoder(VisionEncoder):
-    def __init__(self, num_tokens: int = 16, feature_dim: int = 768) -> None:
+    def __init__(self, num_tokens: int = 16, feature_dim: int = 768, seed: int = 0) -> None:
         super().__init__()
         self.num_tokens, self.feature_dim = num_tokens, feature_dim
         # a fixed random projection of coarse image statistics: deterministic per image, different across images
-        gen = torch.Generator().manual_seed(1234)
+        gen = torch.Generator().manual_seed(1234 + seed)
         self.register_buffer("basis", torch.randn(3 * 16, num_tokens * feature_dim, generator=gen) / 7.0, persistent=False)
         # no parameters and nothing in the state dict (like the reference's stub): a non-persistent buffer carries
         # the module's device and dtype

@@ -115,8 +115,8 @@ class CrossAttentionStrategy:
         return 0
 
 
-def build_modality_strategy(vlm_config):
-    return registry.get("modality_strategy", vlm_config.arch)()
+def build_modality_strategy(vlm):
+    return registry.get("modality_strategy", vlm.arch)()
 
 
 class VLMWrapper(nn.Module):

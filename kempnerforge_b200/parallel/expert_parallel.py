@@ -160,9 +160,22 @@ def _ep_forward_peer_memory(x_flat, weights, indices, moe, ctx) -> torch.Tensor:
     return moe_ops.combine_rows(y_sorted, weights, row_of_slot, slot_of_row)
 
 
-def apply_expert_parallel(model: nn.Module, ep_group, ep_in_dp: bool = False) -> int:
-    """Keep only this rank's experts in every MoE layer and record the EP context on the layer."""
+def apply_expert_parallel(model: nn.Module, ep_group=None, ep_in_dp: bool = False, *, device_mesh=None) -> int:
+    """Keep only this rank's experts in every MoE layer and record the EP context on the layer.
+
+    ``ep_group`` is the expert-parallel process group; a device mesh (positionally or as ``device_mesh=``) is resolved
+    to its ``ep`` dimension (``dp_shard`` with ``ep_in_dp``), and a mesh without one leaves the model unchanged.
+    """
+    from torch.distributed.device_mesh import DeviceMesh
+
     from kempnerforge_b200.models.moe import MoEMLP
+
+    if device_mesh is not None or isinstance(ep_group, DeviceMesh):
+        ep_group, size = ep_group_for(device_mesh if device_mesh is not None else ep_group, ep_in_dp)
+        if size <= 1:
+            return 0
+    elif ep_group is None:
+        return 0
 
     ep = dist.get_world_size(ep_group)
     rank = dist.get_rank(ep_group)

@@ -30,18 +30,18 @@ from kempnerforge_b200.parallel.setup import mesh_dim
 log = logging.getLogger(__name__)
 
 
-def get_dp_mesh(mesh):
-    """The data-parallel sub-mesh: 1-D ``dp_shard`` or 2-D ``(dp_replicate, dp_shard)``; None if absent."""
-    if mesh is None:
+def get_dp_mesh(device_mesh):
+    """The data-parallel sub-device_mesh: 1-D ``dp_shard`` or 2-D ``(dp_replicate, dp_shard)``; None if absent."""
+    if device_mesh is None:
         return None
-    names = mesh.mesh_dim_names or ()
+    names = device_mesh.mesh_dim_names or ()
     has_rep, has_shard = "dp_replicate" in names, "dp_shard" in names
     if has_rep and has_shard:
-        return mesh["dp_replicate", "dp_shard"]
+        return device_mesh["dp_replicate", "dp_shard"]
     if has_shard:
-        return mesh["dp_shard"]
+        return device_mesh["dp_shard"]
     if has_rep:
-        return mesh["dp_replicate"]
+        return device_mesh["dp_replicate"]
     return None
 
 

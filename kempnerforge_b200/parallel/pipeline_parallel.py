@@ -68,8 +68,8 @@ class PipelineStageModule(Transformer):
         return F.linear_cross_entropy(hidden, self.output_head.proj.weight, labels, z_loss_weight)
 
 
-def build_stage_module(model_config, pp_rank: int, pp_size: int) -> PipelineStageModule:
-    return PipelineStageModule(model_config, pp_rank, pp_size)
+def build_stage_module(config, pp_rank: int, pp_size: int) -> PipelineStageModule:
+    return PipelineStageModule(config, pp_rank, pp_size)
 
 
 def build_pipeline_stage(stage_module: PipelineStageModule, device_mesh, device: torch.device, batch_size: int = 0,
@@ -84,8 +84,8 @@ def build_pipeline_stage(stage_module: PipelineStageModule, device_mesh, device:
     return PipelineRunner(stage_module, pp_mesh.get_group() if pp_mesh is not None else None, schedule)
 
 
-def get_pp_mesh(mesh):
-    return mesh["pp"] if mesh is not None and "pp" in (mesh.mesh_dim_names or ()) else None
+def get_pp_mesh(device_mesh):
+    return device_mesh["pp"] if device_mesh is not None and "pp" in (device_mesh.mesh_dim_names or ()) else None
 
 
 _STAGE_GROUPS: dict[int, object] = {}
@@ -113,12 +113,12 @@ def stage_process_group(mesh):
     return _STAGE_GROUPS[key]
 
 
-def get_pp_rank(mesh) -> int:
-    return mesh_dim(mesh, "pp")[2]
+def get_pp_rank(device_mesh) -> int:
+    return mesh_dim(device_mesh, "pp")[2]
 
 
-def get_pp_size(mesh) -> int:
-    return mesh_dim(mesh, "pp")[1]
+def get_pp_size(device_mesh) -> int:
+    return mesh_dim(device_mesh, "pp")[1]
 
 
 # --------------------------------------------------------------------------- schedules

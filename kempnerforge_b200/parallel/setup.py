@@ -177,19 +177,19 @@ def mesh_dim(mesh: DeviceMesh | None, name: str):
     return sub.get_group(), sub.size(), sub.get_local_rank()
 
 
-def has_dp_mesh(mesh: DeviceMesh | None) -> bool:
-    return mesh is not None and any(n in (mesh.mesh_dim_names or ()) for n in ("dp_shard", "dp_replicate"))
+def has_dp_mesh(device_mesh: DeviceMesh | None) -> bool:
+    return device_mesh is not None and any(n in (device_mesh.mesh_dim_names or ()) for n in ("dp_shard", "dp_replicate"))
 
 
-def get_dp_info(mesh: DeviceMesh | None) -> tuple[int, int]:
+def get_dp_info(device_mesh: DeviceMesh | None) -> tuple[int, int]:
     """(dp_rank, dp_size) for data loading: only dp_replicate x dp_shard count, never tp / pp / ep."""
-    if mesh is None:
+    if device_mesh is None:
         return 0, 1
-    names = mesh.mesh_dim_names or ()
+    names = device_mesh.mesh_dim_names or ()
     rank, size = 0, 1
     for n in ("dp_replicate", "dp_shard"):
         if n in names:
-            sub = mesh[n]
+            sub = device_mesh[n]
             rank = rank * sub.size() + sub.get_local_rank()
             size *= sub.size()
     return rank, size

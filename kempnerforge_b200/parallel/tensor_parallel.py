@@ -327,14 +327,14 @@ def build_block_tp_plan(block: nn.Module) -> dict[str, str]:
 _build_block_tp_plan = build_block_tp_plan
 
 
-def get_tp_mesh(mesh):
-    if mesh is None or "tp" not in (mesh.mesh_dim_names or ()):
+def get_tp_mesh(device_mesh):
+    if device_mesh is None or "tp" not in (device_mesh.mesh_dim_names or ()):
         return None
-    return mesh["tp"]
+    return device_mesh["tp"]
 
 
-def apply_tensor_parallel(model: nn.Module, mesh, sequence_parallel: bool | None = None) -> TPContext | None:
-    group, size, _ = mesh_dim(mesh, "tp")
+def apply_tensor_parallel(model: nn.Module, device_mesh, sequence_parallel: bool | None = None) -> TPContext | None:
+    group, size, _ = mesh_dim(device_mesh, "tp")
     if size <= 1:
         return None
     cfg = getattr(model, "config", None)

@@ -13,7 +13,11 @@ import torch
 import torch.distributed as dist
 
 
-def should_build_eval_dataloader(config) -> bool:
+def should_build_eval_dataloader(config, is_vlm: bool | None = None):
+    """``should_build_eval_dataloader(job_config)`` -> bool.  The flag form ``(eval_enabled, is_vlm)`` returns
+    ``(build, warn_that_vlm_eval_is_skipped)`` (kempnerforge/training/eval.py:25-40)."""
+    if isinstance(config, bool):
+        return (False, True) if config and is_vlm else (config, False)
     ec = config.eval
     if not ec.enabled or getattr(config, "is_vlm", False):
         return False
@@ -28,19 +32,35 @@ def build_eval_dataloader(config, dp_rank: int = 0, dp_size: int = 1):
     if ec.dataset_path:
         ds = MemoryMappedDataset(ec.dataset_path, window, ec.file_pattern)
     else:
-        ds = HuggingFaceDataset(ec.hf_dataset_name, window, dc.tokenizer_path, ec.hf_dataset_config,
+        ds = HuggingFaceDataset(ec.hf_dataset_name, tc.seq_len, dc.tokenizer_path, ec.hf_dataset_config,
                                 ec.hf_dataset_split, dc.hf_dataset_text_field)
     sampler = DistributedSampler(len(ds), dp_size, dp_rank, shuffle=False, seed=0, drop_last=True)
     return StatefulDataLoader(ds, tc.batch_size, sampler, 0, False, None, True)
 
 
 @torch.no_grad()
-def run_eval(model, dataloader, config, device, pipeline=None) -> dict[str, float]:
+def run_eval(model, dataloader, config, device, pipeline=None, *, eval_steps: int | None = None, pp_schedule=None,
+             **_) -> dict[str, float]:
+    """Mean loss and perplexity over ``config.eval.steps`` batches (the loader restarts when it runs out).
+
+    ``config`` may instead be a loss function ``(logits, labels) -> scalar``, with the number of batches as the next
+    positional argument or ``eval_steps=`` and a pipeline runner as ``pp_schedule=``
+    (kempnerforge/training/eval.py:43-130).
+    """
+    loss_fn = None
+    if callable(config) and not hasattr(config, "eval"):
+        loss_fn = config
+        if isinstance(pipeline, int):
+            eval_steps, pipeline = pipeline, None
+        pipeline = pipeline if pipeline is not None else pp_schedule
+        if eval_steps is None:
+            raise TypeError("run_eval with a loss function needs eval_steps")
+    steps = eval_steps if eval_steps is not None else config.eval.steps
     was_training = model.training
     model.eval()
     total = torch.zeros(2, dtype=torch.float64, device=device)
     it = iter(dataloader)
-    for _ in range(config.eval.steps):
+    for _ in range(steps):
         try:
             batch = next(it)
         except StopIteration:
@@ -52,6 +72,8 @@ def run_eval(model, dataloader, config, device, pipeline=None) -> dict[str, floa
         ids, labels = batch["input_ids"].to(device), batch["labels"].to(device)
         if pipeline is not None:
             loss = pipeline.eval_loss(ids, labels)
+        elif loss_fn is not None:
+            loss = loss_fn(model(ids), labels)
         elif hasattr(model, "compute_loss"):
             loss = model.compute_loss(ids, labels, doc_ids=batch.get("doc_ids"))
         else:

@@ -28,7 +28,9 @@ def freeze_params(model: nn.Module, patterns: Iterable[str], frozen: bool = True
     return hit
 
 
-def apply_freeze_specs(model: nn.Module, specs, module_patterns: dict[str, list[str]]) -> dict[str, int]:
+def apply_freeze_specs(model: nn.Module, specs, module_patterns: dict[str, list[str]] | None = None, *,
+                       pattern_map: dict[str, list[str]] | None = None) -> dict[str, int]:
+    module_patterns = module_patterns if module_patterns is not None else (pattern_map or {})
     counts = {}
     for spec in specs:
         if spec.module not in module_patterns:
@@ -45,15 +47,26 @@ def canonical_freeze_meta(specs) -> list[dict]:
     return [{"module": k, "frozen": latest[k]} for k in sorted(latest)]
 
 
-def effective_freeze(vlm_config, step: int):
-    """Static freeze list overlaid by every schedule stage whose start_step <= step."""
-    if vlm_config is None:
+def effective_freeze(vlm_config, step=None, schedule=None, valid_modules=None):
+    """Static freeze list overlaid by every schedule stage whose start_step <= step (later stages win per module).
+
+    Two call forms: ``effective_freeze(vlm_config, step)`` and ``effective_freeze(step, base, schedule,
+    valid_modules=None)`` with explicit lists; the latter raises ValueError for a module key outside
+    ``valid_modules``.  Parity: kempnerforge/training/freeze.py:91-140.
+    """
+    if isinstance(vlm_config, int) and not isinstance(vlm_config, bool):
+        step, base, stages = vlm_config, list(step or []), list(schedule or [])
+    elif vlm_config is None:
         return []
-    specs = list(vlm_config.freeze)
-    for stage in vlm_config.freeze_schedule:
+    else:
+        base, stages = list(vlm_config.freeze), list(vlm_config.freeze_schedule)
+    applied = [("base", spec) for spec in base]
+    for stage in sorted(stages, key=lambda s: s.start_step):
         if stage.start_step <= step:
-            specs.extend(stage.specs)
+            applied.extend((f"stage at step {stage.start_step}", spec) for spec in stage.specs)
     latest = {}
-    for spec in specs:
+    for where, spec in applied:
+        if valid_modules is not None and spec.module not in valid_modules:
+            raise ValueError(f"freeze module {spec.module!r} (from {where}) is not one of {sorted(valid_modules)}")
         latest[spec.module] = spec
     return [latest[k] for k in sorted(latest)]

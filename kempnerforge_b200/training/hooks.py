@@ -31,7 +31,7 @@ class TrainingHook:
 
     def on_step_end(self, ctx: StepContext) -> None: ...
 
-    def on_eval_end(self, eval_metrics: dict[str, float], step: int) -> None: ...
+    def on_eval_end(self, metrics: dict[str, float], step: int) -> None: ...
 
     def on_checkpoint_save(self, step: int, path: str) -> None: ...
 
@@ -55,8 +55,8 @@ class HookRunner:
     def on_step_end(self, ctx: StepContext) -> None:
         self._each("on_step_end", ctx)
 
-    def on_eval_end(self, eval_metrics: dict[str, float], step: int) -> None:
-        self._each("on_eval_end", eval_metrics, step)
+    def on_eval_end(self, metrics: dict[str, float], step: int) -> None:
+        self._each("on_eval_end", metrics, step)
 
     def on_checkpoint_save(self, step: int, path: str) -> None:
         self._each("on_checkpoint_save", step, path)

@@ -47,14 +47,14 @@ registry.register("loss", "cross_entropy", cross_entropy)
 registry.register("loss", "chunked_cross_entropy", chunked_cross_entropy)
 
 
-def build_loss_fn(train_config) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
-    name = train_config.loss_fn
+def build_loss_fn(config) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
+    name = config.loss_fn
     base = registry.get("loss", name)
     if name == "chunked_cross_entropy":
-        chunk = train_config.ce_chunk_size or 4096
+        chunk = config.ce_chunk_size or 4096
         inner = base
         base = lambda lg, lb: inner(lg, lb, chunk_size=chunk)  # noqa: E731
-    zw = train_config.z_loss_weight
+    zw = config.z_loss_weight
     if zw > 0:
         return lambda lg, lb: base(lg, lb) + z_loss(lg, zw)
     return base

@@ -135,9 +135,26 @@ def test_mixture_dataset_indexing():
         MixtureDataset([], [])
     with pytest.raises(ValueError):
         MixtureDataset([_Const(1, 0)], ["a", "b"])
-    state = ds.state_dict()
-    ds.load_state_dict(state)
-    assert len(state["datasets"]) == 3
+    assert ds.state_dict() == {}                      # sub-datasets without state contribute nothing
+
+    class _Stateful(_Const):
+        epoch = 0
+
+        def state_dict(self):
+            return {"epoch": self.epoch}
+
+        def load_state_dict(self, state):
+            self.epoch = state["epoch"]
+
+    mixed = MixtureDataset([_Stateful(2, 0), _Const(2, 1), _Stateful(2, 2)], ["a", "b", "c"])
+    mixed._datasets[2].epoch = 4
+    state = mixed.state_dict()
+    assert state == {"dataset_0": {"epoch": 0}, "dataset_2": {"epoch": 4}}
+    fresh = MixtureDataset([_Stateful(2, 0), _Const(2, 1), _Stateful(2, 2)], ["a", "b", "c"])
+    fresh.load_state_dict(state)
+    assert fresh._datasets[2].epoch == 4
+    fresh.load_state_dict({"datasets": [{"epoch": 9}, {}, {"epoch": 1}]})      # list form of older checkpoints
+    assert fresh._datasets[0].epoch == 9 and fresh._datasets[2].epoch == 1
 
 
 # --------------------------------------------------------------------------- mixture sampler

@@ -128,3 +128,59 @@ def test_stage_module_reinitialises_and_init_weights_accepts_a_config():
     torch.manual_seed(1)
     init_weights(lin, cfg.n_layers, cfg.init_std)
     assert torch.equal(a, lin[0].weight)
+
+
+def test_positional_orders_shared_with_other_callers():
+    from kempnerforge_b200.config import JobConfig
+    from kempnerforge_b200.data.sampler import DistributedSampler
+    from kempnerforge_b200.metrics.mfu import compute_mfu, estimate_model_flops_per_token
+    from kempnerforge_b200.metrics.tracker import MetricsTracker
+
+    cfg = ModelConfig(dim=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, ffn_hidden_dim=48, max_seq_len=16)
+    # (config, tokens/s, gpus, peak TFLOP/s per GPU, sequence length)
+    a = compute_mfu(cfg, 1e6, 2, 100.0, 8)
+    assert a == pytest.approx(estimate_model_flops_per_token(cfg, 8) * 1e6 / (2 * 100e12))
+    assert compute_mfu(cfg, 1e6, 2, 100.0) == pytest.approx(estimate_model_flops_per_token(cfg) * 1e6 / 200e12)
+    assert compute_mfu(cfg, 1e6, 0, 100.0) == 0.0 and compute_mfu(cfg, 1e6, 1, 0.0) == 0.0
+    data = list(range(10))
+    s1, s2 = DistributedSampler(data, 2, 0, shuffle=False), DistributedSampler(dataset=data, num_replicas=2, rank=0, shuffle=False)
+    assert list(s1) == list(s2) == list(DistributedSampler(10, 2, 0, shuffle=False))
+    with pytest.raises(TypeError):
+        DistributedSampler()
+    job = JobConfig()
+    job.model = cfg
+    t = MetricsTracker(job, 4, 123.0)
+    assert (t.num_gpus, t.peak_tflops, t.seq_len, t.model_config) == (4, 123.0, job.train.seq_len, cfg)
+    t2 = MetricsTracker(job.metrics, cfg, 4, 64, 0, 123.0)
+    assert (t2.num_gpus, t2.peak_tflops, t2.seq_len) == (4, 123.0, 64)
+    assert MetricsTracker(job, num_gpus=2, gpu_peak_tflops=50.0).peak_tflops == 50.0
+
+
+def test_freeze_and_eval_helpers_accept_explicit_lists_and_flags():
+    from kempnerforge_b200.config.vlm import FreezeSpec, FreezeStage
+    from kempnerforge_b200.training.eval import run_eval, should_build_eval_dataloader
+    from kempnerforge_b200.training.freeze import effective_freeze
+
+    base = [FreezeSpec("vision_encoder", True), FreezeSpec("adapter", False)]
+    sched = [FreezeStage(start_step=10, specs=(FreezeSpec("vision_encoder", False),)),
+             FreezeStage(start_step=5, specs=(FreezeSpec("adapter", True),))]
+    at = lambda step: {s.module: s.frozen for s in effective_freeze(step, base, sched)}  # noqa: E731
+    assert at(0) == {"vision_encoder": True, "adapter": False}
+    assert at(7) == {"vision_encoder": True, "adapter": True}
+    assert at(10) == {"vision_encoder": False, "adapter": True}
+    with pytest.raises(ValueError):
+        effective_freeze(0, base, sched, valid_modules={"adapter"})
+    assert should_build_eval_dataloader(True, True) == (False, True)
+    assert should_build_eval_dataloader(True, False) == (True, False)
+    assert should_build_eval_dataloader(False, True) == (False, False)
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Embedding(16, 8), nn.Linear(8, 16))
+    batches = [{"input_ids": torch.randint(0, 16, (2, 4)), "labels": torch.randint(0, 16, (2, 4))} for _ in range(2)]
+    loss_fn = lambda logits, labels: nn.functional.cross_entropy(logits.flatten(0, 1), labels.flatten())  # noqa: E731
+    out = run_eval(model, batches, loss_fn, torch.device("cpu"), 3)
+    want = sum(float(loss_fn(model(b["input_ids"]), b["labels"])) for b in (batches[0], batches[1], batches[0])) / 3
+    assert out["eval/loss"] == pytest.approx(want, rel=1e-5) and out["eval/perplexity"] > 1.0
+    assert run_eval(model, batches, loss_fn, torch.device("cpu"), eval_steps=3) == out
+    with pytest.raises(TypeError):
+        run_eval(model, batches, loss_fn, torch.device("cpu"))

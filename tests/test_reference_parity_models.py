@@ -328,7 +328,7 @@ def test_flop_estimates_match_the_reference(extra):
     a, b = ref_load(None, extra).model, load_config(None, extra).model
     for seq in (2048, 8192):
         assert estimate_model_flops_per_token(b, seq) == ref_flops(a, seq)
-    assert compute_mfu(b, 1e5, 8, 2048, peak_tflops=989.0) == pytest.approx(ref_mfu(a, 1e5, 8, 989.0, 2048), rel=1e-9)
+    assert compute_mfu(b, 1e5, 8, 989.0, 2048) == pytest.approx(ref_mfu(a, 1e5, 8, 989.0, 2048), rel=1e-9)
 
 
 def test_flop_estimate_counts_the_experts_that_run():
@@ -445,3 +445,67 @@ def test_checkpoint_converter_writes_what_the_reference_converter_writes(tmp_pat
     for key, value in b.items():
         if key != "torch_dtype":        # the reference always writes bfloat16 there, whatever dtype was exported
             assert a[key] == value, key
+
+
+def test_hf_text_datasets_yield_the_reference_samples_and_state(monkeypatch):
+    """With the same documents and tokenizer, the eager and the streaming text datasets cut the same windows (no special
+    tokens, EOS between documents, seq_len + 1 tokens per window), shard documents over ranks the same way, and save
+    interchangeable positions."""
+    import datasets as hf_datasets
+    import transformers
+
+    _ref_path()
+    from kempnerforge.data.dataset import HuggingFaceDataset as RefEager
+    from kempnerforge.data.dataset import StreamingHuggingFaceDataset as RefStream
+
+    from kempnerforge_b200.data.dataset import HuggingFaceDataset, StreamingHuggingFaceDataset
+
+    class Tok:
+        eos_token_id = 3
+
+        def encode(self, text, add_special_tokens=True):
+            ids = [10 + (sum(map(ord, w)) % 80) for w in text.split()]
+            return ([1] + ids) if add_special_tokens and ids else ids      # BOS only when special tokens are requested
+
+    class Stream(list):
+        def shuffle(self, seed, buffer_size):
+            order = torch.randperm(len(self), generator=torch.Generator().manual_seed(seed)).tolist()
+            return Stream(self[i] for i in order)
+
+    docs = Stream({"text": " ".join(f"w{i}x{j}" for j in range(3 + i % 9))} for i in range(60))
+    docs.insert(7, {"text": ""})
+    monkeypatch.setattr(hf_datasets, "load_dataset", lambda *a, **k: docs)
+    monkeypatch.setattr(transformers.AutoTokenizer, "from_pretrained", classmethod(lambda cls, *a, **k: Tok()))
+
+    for pack in (False, True):
+        ref = RefEager(dataset_name="toy", split="train", text_field="text", seq_len=16, tokenizer_path="t", pack_sequences=pack)
+        mine = HuggingFaceDataset(dataset_name="toy", split="train", text_field="text", seq_len=16, tokenizer_path="t",
+                                  pack_sequences=pack)
+        assert len(ref) == len(mine) > 5
+        for i in range(len(ref)):
+            a, b = ref[i], mine[i]
+            assert set(a) == set(b)
+            for k in a:
+                assert torch.equal(a[k], b[k]), (pack, i, k)
+        assert set(ref.state_dict()) == set(mine.state_dict())
+        assert ref.state_dict()["total_sequences"] == mine.state_dict()["total_sequences"]
+
+    for rank, world in ((0, 1), (1, 3)):
+        kw = dict(dataset_name="toy", split="train", text_field="text", seq_len=12, tokenizer_path="t", rank=rank,
+                  world_size=world, seed=5, shuffle_buffer_size=16)
+        ref, mine = RefStream(**kw), StreamingHuggingFaceDataset(**kw)
+        ra, ma = iter(ref), iter(mine)
+        for _ in range(4):
+            a, b = next(ra), next(ma)
+            assert torch.equal(a["input_ids"], b["input_ids"]) and torch.equal(a["labels"], b["labels"])
+        assert ref.state_dict() == mine.state_dict()
+        # a position saved by one resumes at the same sample in the other, in both directions
+        resumed_mine, resumed_ref = StreamingHuggingFaceDataset(**kw), RefStream(**kw)
+        resumed_mine.load_state_dict(ref.state_dict())
+        resumed_ref.load_state_dict(mine.state_dict())
+        x, y = next(iter(resumed_mine)), next(iter(resumed_ref))
+        assert torch.equal(x["input_ids"], y["input_ids"])
+        rest_ref, rest_mine = list(ra), list(ma)
+        assert len(rest_ref) == len(rest_mine)
+        assert all(torch.equal(a["input_ids"], b["input_ids"]) for a, b in zip(rest_ref, rest_mine))
+        assert ref.state_dict() == mine.state_dict() and mine.state_dict()["epoch"] == 1

@@ -172,11 +172,11 @@ def test_llama_7b_flops_are_about_six_times_its_parameters():
 def test_compute_mfu_arithmetic():
     c = _dense()
     per_tok = estimate_model_flops_per_token(c, 128)
-    assert compute_mfu(c, 0.0, 1, 128, peak_tflops=100.0) == 0.0
-    one = compute_mfu(c, 1e6, 1, 128, peak_tflops=100.0)
+    assert compute_mfu(c, 0.0, 1, seq_len=128, peak_tflops=100.0) == 0.0
+    one = compute_mfu(c, 1e6, 1, seq_len=128, peak_tflops=100.0)
     assert one == pytest.approx(per_tok * 1e6 / 100e12)
-    assert compute_mfu(c, 1e6, 4, 128, peak_tflops=100.0) == pytest.approx(one / 4)
-    assert compute_mfu(c, 1e6, 1, 128, peak_tflops=200.0) == pytest.approx(one / 2)
+    assert compute_mfu(c, 1e6, 4, seq_len=128, peak_tflops=100.0) == pytest.approx(one / 4)
+    assert compute_mfu(c, 1e6, 1, seq_len=128, peak_tflops=200.0) == pytest.approx(one / 2)
 
 
 def test_moe_counts_active_parameters_only():

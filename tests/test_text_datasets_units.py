@@ -46,7 +46,7 @@ def test_mmap_windows_lengths_and_boundaries(shard_dir):
     other = MemoryMappedDataset(str(shard_dir), seq_len=10)
     assert len(other) == 17
     ds.load_state_dict({"epoch": 3})
-    assert ds.state_dict() == {"epoch": 3}
+    assert ds.state_dict() == {"epoch": 3, "total_samples": len(ds)}
     with pytest.raises(FileNotFoundError):
         MemoryMappedDataset(str(shard_dir), seq_len=8, file_pattern="*.tokens")
     with pytest.raises(ValueError):
@@ -97,19 +97,19 @@ def test_stateful_loader_iterates_counts_and_rolls_epochs(shard_dir):
 # --------------------------------------------------------------------------- Hugging Face datasets on an in-memory corpus
 def test_hf_dataset_packs_documents_into_fixed_windows():
     docs = _docs(20, 9) + [{"text": ""}, {"text": "   "}]            # empty documents are skipped
-    ds = HuggingFaceDataset("toy", 16, "", raw_dataset=docs, tokenizer=_Tok())
+    ds = HuggingFaceDataset("toy", 15, "", raw_dataset=docs, tokenizer=_Tok())          # windows of 15 + 1 tokens
     assert len(ds) == (20 * 10) // 16
     s = ds[0]
     assert s["input_ids"].shape == s["labels"].shape == (15,) and torch.equal(s["labels"][:-1], s["input_ids"][1:])
     stream = torch.cat([torch.cat([ds[i]["input_ids"], ds[i]["labels"][-1:]]) for i in range(len(ds))])
     assert int((stream == 0).sum()) >= 12                           # document ends (EOS) are inside the stream
-    assert ds.state_dict()["num_samples"] == len(ds)
-    ds.load_state_dict({"epoch": 2})
-    assert ds.state_dict()["epoch"] == 2
+    assert ds.state_dict() == {"epoch": 0, "sample_idx": 0, "total_sequences": len(ds)}
+    ds.load_state_dict({"epoch": 2, "sample_idx": 5})
+    assert ds.state_dict()["epoch"] == 2 and ds.state_dict()["sample_idx"] == 5
 
 
 def test_hf_dataset_packed_output_carries_document_ids():
-    ds = HuggingFaceDataset("toy", 16, "", raw_dataset=_docs(10, 5), tokenizer=_Tok(), pack_sequences=True)
+    ds = HuggingFaceDataset("toy", 15, "", raw_dataset=_docs(10, 5), tokenizer=_Tok(), pack_sequences=True)
     s = ds[0]
     assert {"input_ids", "labels", "doc_ids"} <= set(s)
     assert s["doc_ids"].shape == s["input_ids"].shape and int(s["doc_ids"].max()) >= 1
@@ -119,23 +119,23 @@ def test_hf_dataset_packed_output_carries_document_ids():
 
 def test_streaming_dataset_shards_by_document_and_resumes():
     docs = _docs(40, 7)
-    full = list(StreamingHuggingFaceDataset("toy", 8, "", raw_stream=docs, tokenizer=_Tok()))
+    full = list(StreamingHuggingFaceDataset("toy", 7, "", raw_stream=docs, tokenizer=_Tok()))
     assert len(full) == (40 * 8) // 8 and full[0]["input_ids"].shape == (7,)
-    r0 = list(StreamingHuggingFaceDataset("toy", 8, "", raw_stream=docs, tokenizer=_Tok(), rank=0, world_size=2))
-    r1 = list(StreamingHuggingFaceDataset("toy", 8, "", raw_stream=docs, tokenizer=_Tok(), rank=1, world_size=2))
+    r0 = list(StreamingHuggingFaceDataset("toy", 7, "", raw_stream=docs, tokenizer=_Tok(), rank=0, world_size=2))
+    r1 = list(StreamingHuggingFaceDataset("toy", 7, "", raw_stream=docs, tokenizer=_Tok(), rank=1, world_size=2))
     assert len(r0) == len(r1) == 20
     assert not any(torch.equal(a["input_ids"], b["input_ids"]) for a, b in zip(r0, r1))
     with_empty = [{"text": ""}] + docs
-    assert len(list(StreamingHuggingFaceDataset("toy", 8, "", raw_stream=with_empty, tokenizer=_Tok()))) == 40
-    ds = StreamingHuggingFaceDataset("toy", 8, "", raw_stream=docs, tokenizer=_Tok())
+    assert len(list(StreamingHuggingFaceDataset("toy", 7, "", raw_stream=with_empty, tokenizer=_Tok()))) == 40
+    ds = StreamingHuggingFaceDataset("toy", 7, "", raw_stream=docs, tokenizer=_Tok())
     it = iter(ds)
     head = [next(it) for _ in range(10)]
     state = ds.state_dict()
-    assert state["docs_consumed"] == 10
-    resumed = StreamingHuggingFaceDataset("toy", 8, "", raw_stream=docs, tokenizer=_Tok())
+    assert state == {"epoch": 0, "rank_docs_consumed": 10}
+    resumed = StreamingHuggingFaceDataset("toy", 7, "", raw_stream=docs, tokenizer=_Tok())
     resumed.load_state_dict(state)
     tail = list(resumed)
     assert len(head) + len(tail) == len(full)
     assert torch.equal(tail[0]["input_ids"], full[10]["input_ids"])
-    packed = next(iter(StreamingHuggingFaceDataset("toy", 16, "", raw_stream=docs, tokenizer=_Tok(), pack_sequences=True)))
+    packed = next(iter(StreamingHuggingFaceDataset("toy", 15, "", raw_stream=docs, tokenizer=_Tok(), pack_sequences=True)))
     assert "doc_ids" in packed
