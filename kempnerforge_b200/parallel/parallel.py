@@ -69,7 +69,7 @@ def apply_ac(model: nn.Module, mode: str = "full") -> None:
 
 
 def apply_float8(model: nn.Module, enable_fsdp_float8_all_gather: bool = True) -> int:
-    """Switch the dense Linear call sites to block-scaled fp8 GEMMs; experts, shared experts and routers
+    """Switch the dense Linear call sites to tensor-wise scaled fp8 GEMMs; experts, shared experts and routers
     keep bf16 (same module filter as the reference).  Returns the number of converted modules."""
     from kempnerforge_b200.ops import fp8
 

@@ -256,11 +256,16 @@ class Trainer:
         self._loss_acc.zero_()
         if self.config.model.is_moe and hasattr(self.model, "set_moe_step"):
             self.model.set_moe_step(self.step, tc.max_steps)
+        per_dataset = self._dataset_metrics_wanted()
+        self._dataset_stats = {} if per_dataset else None
         for micro in range(accum):
             batch = batches[micro] if batches is not None else self.next_batch()
             batch = _to_device(batch, self.device)
             with maybe_no_sync(self.model, micro, accum):
-                loss = self.micro_loss(batch)
+                if per_dataset and "dataset_idx" in batch:
+                    loss = self._micro_loss_with_dataset_stats(batch)
+                else:
+                    loss = self.micro_loss(batch)
                 (loss / accum).backward()
             self._loss_acc[0] += loss.detach().float() / accum
         if self.engine is not None:
@@ -405,6 +410,9 @@ class Trainer:
             self.hook_runner.on_step_end(ctx)
             if ctx.metrics:
                 self.tracker.log_extra(ctx.metrics, self.step)
+            ds_metrics = self._dataset_metrics()
+            if ds_metrics:
+                self.tracker.log_eval(ds_metrics, self.step)
             if any(getattr(h, "should_stop", False) for h in self.hook_runner.hooks):
                 stop_reason = "hook"
                 log.info("a training hook asked to stop at step %d", self.step)
@@ -442,6 +450,56 @@ class Trainer:
         self.tracker.close()
         self.shutdown.unregister()
         return {**last, "step": self.step, "tokens_seen": self.tokens_seen, "stop_reason": stop_reason}
+
+    # ------------------------------------------------------------------ per-dataset metrics of mixture runs
+    def _mixture_names(self) -> list[str] | None:
+        return getattr(getattr(self.dataloader, "dataset", None), "dataset_names", None)
+
+    def _dataset_metrics_wanted(self) -> bool:
+        """True on the steps whose metrics are logged, for a dataset mixture, outside pipeline / vocabulary-parallel
+        runs (there the final hidden states and the head are not on one rank)."""
+        nxt = self.step + 1
+        if not (nxt % self.config.metrics.log_interval == 0 or nxt == 1):
+            return False
+        model = self.model
+        return (self._mixture_names() is not None and self.pipeline is None and getattr(model, "norm", None) is not None
+                and getattr(getattr(model, "output_head", None), "tp", None) is None)
+
+    def _micro_loss_with_dataset_stats(self, batch) -> torch.Tensor:
+        """The ordinary micro-batch loss; also records, per source dataset of the mixture, the mean loss of its rows
+        and their token count (kempnerforge scripts/train.py:822-839 computes the same from the logits).  The final
+        hidden states are captured by a forward hook and pushed through the head once more without gradients, in
+        chunks, so the training path itself is unchanged."""
+        from kempnerforge_b200.ops import functional as F
+
+        captured = []
+        handle = self.model.norm.register_forward_hook(lambda _m, _i, out: captured.append(out.detach()))
+        try:
+            loss = self.micro_loss(batch)
+        finally:
+            handle.remove()
+        if captured:
+            hidden, labels, ds_idx = captured[0], batch["labels"], batch["dataset_idx"]
+            weight = self.model.output_head.proj.weight
+            seq = labels.shape[1]
+            with torch.no_grad():
+                for i, name in enumerate(self._mixture_names()):
+                    rows = ds_idx == i
+                    n_rows = int(rows.sum())
+                    if n_rows == 0:
+                        continue
+                    ds_loss = F.linear_cross_entropy(hidden[rows], weight, labels[rows])
+                    acc = self._dataset_stats.setdefault(name, [0.0, 0, 0])
+                    acc[0] += float(ds_loss)
+                    acc[1] += 1
+                    acc[2] += n_rows * seq
+        return loss
+
+    def _dataset_metrics(self) -> dict[str, float]:
+        stats = getattr(self, "_dataset_stats", None) or {}
+        out = {f"loss/{name}": total / max(1, count) for name, (total, count, _) in stats.items()}
+        out.update({f"data/{name}/tokens": float(tokens) for name, (_, _, tokens) in stats.items()})
+        return out
 
     # ------------------------------------------------------------------ helpers
     def _moe_metrics(self) -> dict[str, float] | None:

@@ -213,3 +213,13 @@ dataset_weights = {{ web = 1.0, code = 3.0 }}
 
     lrs = {int(s): float(v) for s, v in re.findall(r"\[step (\d+)\].*?lr=([0-9.e+-]+)", out)}
     assert lrs[2] == pytest.approx(1e-3) and lrs[5] == pytest.approx(5e-4)
+    # per-source metrics on the logged steps: a loss near ln(vocab) and a token count for every source that was drawn
+    per_source = re.findall(r"\[step (\d+)\] (?=.*loss/)(.*)", out)
+    assert per_source, out[-2000:]
+    seen = set()
+    for _, line in per_source:
+        for name, value in re.findall(r"loss/(\w+)=([0-9.]+)", line):
+            seen.add(name)
+            assert 3.0 < float(value) < 8.0
+        assert re.search(r"data/(web|code)/tokens=", line)
+    assert seen == {"web", "code"}
