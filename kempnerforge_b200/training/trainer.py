@@ -258,6 +258,7 @@ class Trainer:
             self.model.set_moe_step(self.step, tc.max_steps)
         per_dataset = self._dataset_metrics_wanted()
         self._dataset_stats = {} if per_dataset else None
+        self._text_tokens = None
         for micro in range(accum):
             batch = batches[micro] if batches is not None else self.next_batch()
             batch = _to_device(batch, self.device)
@@ -267,6 +268,9 @@ class Trainer:
                 else:
                     loss = self.micro_loss(batch)
                 (loss / accum).backward()
+            if "pixel_values" in batch and self._logs_next_step():
+                n = (self._vlm_target_labels(batch["labels"]) != -100).sum()
+                self._text_tokens = n if self._text_tokens is None else self._text_tokens + n
             self._loss_acc[0] += loss.detach().float() / accum
         if self.engine is not None:
             self.engine.finish_backward()
@@ -410,7 +414,7 @@ class Trainer:
             self.hook_runner.on_step_end(ctx)
             if ctx.metrics:
                 self.tracker.log_extra(ctx.metrics, self.step)
-            ds_metrics = self._dataset_metrics()
+            ds_metrics = {**self._text_token_metrics(), **self._dataset_metrics()}
             if ds_metrics:
                 self.tracker.log_eval(ds_metrics, self.step)
             if any(getattr(h, "should_stop", False) for h in self.hook_runner.hooks):
@@ -455,11 +459,29 @@ class Trainer:
     def _mixture_names(self) -> list[str] | None:
         return getattr(getattr(self.dataloader, "dataset", None), "dataset_names", None)
 
+    def _logs_next_step(self) -> bool:
+        nxt = self.step + 1
+        return nxt % self.config.metrics.log_interval == 0 or nxt == 1
+
+    def _vlm_target_labels(self, labels: torch.Tensor) -> torch.Tensor:
+        """The label positions the vision-language wrapper scores (all but the first when it shifts them)."""
+        return labels[:, 1:] if getattr(self.model, "shift_labels", True) else labels
+
+    def _text_token_metrics(self) -> dict[str, float]:
+        """``data/text_tokens_trained``: text positions that carried a loss in the logged step, summed over ranks
+        (image prefix, padding and masked prompt tokens excluded); vision-language runs only."""
+        n = getattr(self, "_text_tokens", None)
+        if n is None:
+            return {}
+        n = n.to(torch.int64).reshape(1)
+        if self.world_size > 1 and dist.is_initialized():
+            dist.all_reduce(n)
+        return {"data/text_tokens_trained": float(n.item())}
+
     def _dataset_metrics_wanted(self) -> bool:
         """True on the steps whose metrics are logged, for a dataset mixture, outside pipeline / vocabulary-parallel
         runs (there the final hidden states and the head are not on one rank)."""
-        nxt = self.step + 1
-        if not (nxt % self.config.metrics.log_interval == 0 or nxt == 1):
+        if not self._logs_next_step():
             return False
         model = self.model
         return (self._mixture_names() is not None and self.pipeline is None and getattr(model, "norm", None) is not None

@@ -74,3 +74,17 @@ def test_freeze_schedule_transition_keeps_moments():
     t.train_step()
     assert not torch.equal(w0, t.model.transformer.layers["0"].mlp.down_proj.weight)  # now it trains
     assert adapter_p.requires_grad
+
+
+def test_vlm_run_reports_the_text_tokens_of_logged_steps():
+    cfg = _cfg()
+    loader = _loader(cfg)
+    t = Trainer(cfg, init_dist=False, dataloader=loader)
+    first = next(iter(_loader(cfg)))
+    expected = int((first["labels"][:, 1:] != -100).sum())
+    assert 0 < expected < first["labels"].numel()
+    t.train_step()                                  # the step that becomes step 1 is a logged step
+    assert t._text_token_metrics() == {"data/text_tokens_trained": float(expected)}
+    t.step = 1
+    t.train_step()                                  # step 2 with log_interval=100: nothing is counted
+    assert t._text_token_metrics() == {}
