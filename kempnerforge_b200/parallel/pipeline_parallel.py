@@ -23,8 +23,9 @@ from kempnerforge_b200.models.transformer import Transformer
 from kempnerforge_b200.parallel.setup import mesh_dim
 
 
-def compute_layer_assignment(n_layers: int, pp_size: int) -> list[list[int]]:
-    """Layer indices of every stage: even split, the first ``n_layers % pp_size`` stages get one more."""
+def compute_layer_assignment(n_layers: int, pp_size: int) -> list[tuple[int, int]]:
+    """``(start, end)`` layer range of every stage, end exclusive: an even split in which the first
+    ``n_layers % pp_size`` stages get one more.  Parity: kempnerforge/distributed/pipeline_parallel.py:77-112."""
     if pp_size <= 0:
         raise ValueError("pp_size must be positive")
     if n_layers < pp_size:
@@ -33,7 +34,7 @@ def compute_layer_assignment(n_layers: int, pp_size: int) -> list[list[int]]:
     out, start = [], 0
     for s in range(pp_size):
         n = base + (1 if s < extra else 0)
-        out.append(list(range(start, start + n)))
+        out.append((start, start + n))
         start += n
     return out
 
@@ -41,8 +42,17 @@ def compute_layer_assignment(n_layers: int, pp_size: int) -> list[list[int]]:
 class PipelineStageModule(Transformer):
     """The slice of the transformer owned by one pipeline stage."""
 
-    def __init__(self, config, pp_rank: int, pp_size: int) -> None:
-        layers = compute_layer_assignment(config.n_layers, pp_size)[pp_rank]
+    def __init__(self, config, pp_rank: int | None = None, pp_size: int | None = None,
+                 layer_range: tuple[int, int] | None = None, *, stage_id: int | None = None,
+                 num_stages: int | None = None) -> None:
+        """Stage ``pp_rank`` of ``pp_size`` (also spelled ``stage_id`` / ``num_stages``); ``layer_range = (start, end)``
+        overrides the balanced layer assignment."""
+        pp_rank = stage_id if pp_rank is None else pp_rank
+        pp_size = num_stages if pp_size is None else pp_size
+        if pp_rank is None or pp_size is None:
+            raise TypeError("PipelineStageModule needs the stage index and the number of stages")
+        layers = list(range(*(layer_range if layer_range is not None
+                              else compute_layer_assignment(config.n_layers, pp_size)[pp_rank])))
         super().__init__(config, layer_ids=layers, with_embedding=pp_rank == 0, with_head=pp_rank == pp_size - 1)
         self.pp_rank, self.pp_size = pp_rank, pp_size
         self.is_first, self.is_last = pp_rank == 0, pp_rank == pp_size - 1
@@ -303,6 +313,11 @@ def build_pipeline(config, device: torch.device, mesh, transport: str | None = N
     return PipelineRunner(module, group, str(config.distributed.pp_schedule))
 
 
-def build_pipeline_schedule(runner: PipelineRunner, n_microbatches: int, schedule: str = "1f1b") -> list[tuple[str, int]]:
-    """The slot list this rank will execute (exposed for inspection and tests)."""
+def build_pipeline_schedule(runner: PipelineRunner, n_microbatches: int, loss_fn=None,
+                            schedule: str = "1f1b") -> list[tuple[str, int]]:
+    """The slot list this rank will execute (exposed for inspection and tests).  ``loss_fn`` is accepted for call
+    compatibility (the last stage computes its loss with the fused head + cross-entropy); a schedule name in its
+    place is understood too."""
+    if isinstance(loss_fn, str):
+        schedule = loss_fn
     return schedule_order(schedule, runner.rank, runner.size, n_microbatches)

@@ -184,3 +184,16 @@ def test_freeze_and_eval_helpers_accept_explicit_lists_and_flags():
     assert run_eval(model, batches, loss_fn, torch.device("cpu"), eval_steps=3) == out
     with pytest.raises(TypeError):
         run_eval(model, batches, loss_fn, torch.device("cpu"))
+
+
+def test_pipeline_stage_spellings():
+    from kempnerforge_b200.parallel.pipeline_parallel import PipelineStageModule, compute_layer_assignment
+
+    cfg = ModelConfig(dim=32, n_layers=6, n_heads=4, n_kv_heads=2, vocab_size=64, ffn_hidden_dim=48, max_seq_len=16)
+    a = PipelineStageModule(cfg, 1, 3)
+    b = PipelineStageModule(cfg, stage_id=1, num_stages=3)
+    assert list(a.layers.keys()) == list(b.layers.keys()) == [str(i) for i in range(*compute_layer_assignment(6, 3)[1])]
+    c = PipelineStageModule(cfg, 0, 2, (0, 5))
+    assert list(c.layers.keys()) == ["0", "1", "2", "3", "4"] and c.is_first and not c.is_last
+    with pytest.raises(TypeError):
+        PipelineStageModule(cfg)

@@ -201,8 +201,8 @@ def test_eval_loader_is_built_only_for_text_runs_with_a_source():
                                        (7, 2, [4, 3])])
 def test_layer_assignment(n, pp, want):
     out = compute_layer_assignment(n, pp)
-    assert [len(s) for s in out] == want
-    assert [i for s in out for i in s] == list(range(n))
+    assert [end - start for start, end in out] == want
+    assert [i for start, end in out for i in range(start, end)] == list(range(n))
 
 
 def test_layer_assignment_rejects_too_many_stages():
