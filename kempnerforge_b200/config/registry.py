@@ -35,6 +35,9 @@ _KNOWN_CATEGORIES: dict[str, str] = {
 }
 
 
+_UNSET: Any = object()
+
+
 class Registry:
     """Two-level dictionary ``category -> name -> object`` with duplicate protection."""
 
@@ -42,9 +45,9 @@ class Registry:
         self._tables: dict[str, dict[str, Any]] = {}
 
     # -- generic surface -------------------------------------------------
-    def register(self, category: str, name: str, obj: Any = None) -> Any:
+    def register(self, category: str, name: str, obj: Any = _UNSET) -> Any:
         """Register ``obj``; with ``obj`` omitted acts as a decorator factory."""
-        if obj is None:
+        if obj is _UNSET:
             return lambda o: self.register(category, name, o)
         table = self._tables.setdefault(category, {})
         if name in table:

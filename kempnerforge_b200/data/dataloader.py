@@ -25,6 +25,10 @@ class StatefulDataLoader:
         if config is not None:
             num_workers, pin_memory = int(config.num_workers), bool(config.pin_memory)
             prefetch_factor = config.prefetch_factor
+        if sampler is None and not isinstance(dataset, torch.utils.data.IterableDataset):
+            from kempnerforge_b200.data.sampler import DistributedSampler
+
+            sampler = DistributedSampler(dataset)        # rank / world from the environment, seeded shuffle
         self.dataset, self.batch_size, self.sampler = dataset, batch_size, sampler
         kwargs = dict(batch_size=batch_size, sampler=sampler, num_workers=num_workers,
                       pin_memory=pin_memory and torch.cuda.is_available(), drop_last=drop_last,

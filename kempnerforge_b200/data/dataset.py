@@ -77,10 +77,8 @@ class MemoryMappedDataset(Dataset):
         return int(self._bounds[-1])
 
     def __getitem__(self, idx: int) -> dict[str, torch.Tensor]:
-        if idx < 0:
-            idx += len(self)
         if not 0 <= idx < len(self):
-            raise IndexError(idx)
+            raise IndexError(f"Index {idx} out of range [0, {len(self)})")
         f = int(np.searchsorted(self._bounds, idx, side="right") - 1)
         lo = (idx - int(self._bounds[f])) * self.seq_len
         window = np.asarray(self._maps[f][lo : lo + self.seq_len])

@@ -34,9 +34,17 @@ class VisionAdapter(nn.Module):
                 m.reset_parameters()
 
 
+def _check_dims(kind: str, in_dim: int, out_dim: int) -> None:
+    if in_dim <= 0 or out_dim <= 0:
+        raise ValueError(f"{kind} in_dim and out_dim must be positive (got {in_dim}, {out_dim})")
+
+
 class MLP2LayerAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, hidden_dim: int | None = None, activation: str = "gelu", **_) -> None:
         super().__init__()
+        _check_dims("MLP2LayerAdapter", in_dim, out_dim)
+        if activation not in _ACT:
+            raise ValueError(f"Unknown adapter activation {activation!r}; known: {sorted(_ACT)}")
         hidden = hidden_dim or out_dim
         self.proj1 = nn.Linear(in_dim, hidden)  # parameter names are the checkpoint keys of the reference
         self.act = _ACT[activation]()
@@ -49,6 +57,7 @@ class MLP2LayerAdapter(VisionAdapter):
 class LinearAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, **_) -> None:
         super().__init__()
+        _check_dims("LinearAdapter", in_dim, out_dim)
         self.proj = nn.Linear(in_dim, out_dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -77,6 +86,7 @@ def _to_windows(x: torch.Tensor, window: int):
 class AvgPoolAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, pool_window: int = 2, **_) -> None:
         super().__init__()
+        _check_dims("AvgPoolAdapter", in_dim, out_dim)
         if pool_window <= 0:
             raise ValueError(f"pool_window must be positive (got {pool_window})")
         self.window = self.pool_window = pool_window
@@ -99,6 +109,7 @@ class AvgPoolAdapter(VisionAdapter):
 class AttentionalPoolAdapter(VisionAdapter):
     def __init__(self, in_dim: int, out_dim: int, pool_window: int = 2, pool_heads: int = 16, **_) -> None:
         super().__init__()
+        _check_dims("AttentionalPoolAdapter", in_dim, out_dim)
         if in_dim % pool_heads:
             raise ValueError(f"feature dim {in_dim} is not divisible by pool_heads {pool_heads}")
         if pool_window <= 0:

@@ -15,9 +15,9 @@ from kempnerforge_b200.models.attention import KVCache
 
 def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
            generator: torch.Generator | None = None) -> torch.Tensor:
-    """logits (batch, vocab) -> token ids (batch, 1)."""
+    """logits (batch, vocab) -> token ids (batch,); greedy at temperature 0."""
     if temperature <= 0:
-        return logits.argmax(dim=-1, keepdim=True)
+        return logits.argmax(dim=-1)
     logits = logits.float() / temperature
     if top_k and top_k > 0:
         k = min(top_k, logits.shape[-1])
@@ -31,7 +31,7 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
         sorted_logits = sorted_logits.masked_fill(drop, float("-inf"))
         logits = torch.full_like(logits, float("-inf")).scatter(-1, order, sorted_logits)
     probs = torch.softmax(logits, dim=-1)
-    return torch.multinomial(probs, 1, generator=generator)
+    return torch.multinomial(probs, 1, generator=generator).squeeze(-1)
 
 
 @torch.no_grad()
@@ -39,8 +39,11 @@ def generate(model, prompt_tokens: torch.Tensor, max_new_tokens: int, temperatur
              top_p: float = 1.0, eos_token_id: int | None = None, generator: torch.Generator | None = None) -> torch.Tensor:
     cfg = model.config
     b, plen = prompt_tokens.shape
-    total = min(cfg.max_seq_len, plen + max_new_tokens)
-    if plen >= total:
+    total = plen + max_new_tokens
+    if total > cfg.max_seq_len:
+        raise ValueError(f"prompt ({plen}) + max_new_tokens ({max_new_tokens}) = {total} exceeds model max_seq_len "
+                         f"({cfg.max_seq_len})")
+    if max_new_tokens <= 0:
         return prompt_tokens
     param = next(model.parameters())
     hd = cfg.head_dim
@@ -52,7 +55,7 @@ def generate(model, prompt_tokens: torch.Tensor, max_new_tokens: int, temperatur
     out = prompt_tokens
     done = torch.zeros(b, dtype=torch.bool, device=prompt_tokens.device)
     for _ in range(total - plen):
-        nxt = sample(logits[:, -1], temperature, top_k, top_p, generator)
+        nxt = sample(logits[:, -1], temperature, top_k, top_p, generator)[:, None]
         if eos_token_id is not None:
             nxt = torch.where(done[:, None], torch.full_like(nxt, eos_token_id), nxt)
             done |= nxt.squeeze(-1) == eos_token_id

@@ -140,4 +140,9 @@ def save_activations(activations: dict[str, torch.Tensor], path) -> None:
     if path.suffix != ".npz":
         path = path.with_suffix(".npz")
     path.parent.mkdir(parents=True, exist_ok=True)
-    np.savez(str(path), **{k: v.float().numpy() for k, v in activations.items()})
+    def as_array(v):
+        if isinstance(v, (list, tuple)):          # an ActivationStore's per-pass lists
+            v = torch.cat(list(v), dim=0)
+        return v.float().numpy()
+
+    np.savez(str(path), **{k: as_array(v) for k, v in activations.items() if not isinstance(v, (list, tuple)) or len(v)})

@@ -152,10 +152,8 @@ def mot_warm_start_from_text_stack(model: nn.Module, text_state: dict[str, torch
                     raise KeyError(f"{name} (from {key}) not found in the MoT model")
                 continue
             local = dst.to_local() if hasattr(dst, "to_local") else dst
-            if local.shape != value.shape:
-                if strict:
-                    raise ValueError(f"shape mismatch for {name}: {tuple(local.shape)} vs {tuple(value.shape)}")
-                continue
+            if local.shape != value.shape:        # never skipped silently: the source is the wrong architecture
+                raise ValueError(f"shape mismatch for {name}: {tuple(local.shape)} vs {tuple(value.shape)}")
             local.copy_(value.to(local.dtype))
             copied += 1
     log.info("MoT warm start: copied %d tensors", copied)

@@ -124,6 +124,12 @@ class Transformer(nn.Module):
         if arch == "mot":
             from kempnerforge_b200.models.mot import MoTBlock
 
+            text_kv = config.n_kv_heads if config.n_kv_heads is not None else config.n_heads
+            if hasattr(vlm_config, "resolved_image_heads"):
+                img_heads, img_kv = vlm_config.resolved_image_heads(config.n_heads, text_kv)
+                if img_heads != config.n_heads or img_kv != text_kv:
+                    raise ValueError("MoT requires equal head counts across modalities (one global attention): image "
+                                     f"{img_heads}/{img_kv} vs text {config.n_heads}/{text_kv}")
             self._mot_modalities = tuple(vlm_config.mot_modalities)
             self._mot_n_image = num_image_tokens
             for i in range(config.n_layers):

@@ -63,13 +63,20 @@ def _build_random(path: str = "", num_tokens: int | None = None, feature_dim: in
     return RandomVisionEncoder(num_tokens or 16, feature_dim or 768)
 
 
+def _require_path(path: str, kind: str) -> None:
+    if not path:
+        raise ValueError(f"vision_encoder_path must be set for the {kind} encoder (a Hugging Face model id or directory)")
+
+
 @registry.register("vision_encoder", "siglip2")
 def _build_siglip2(path: str, num_tokens: int | None = None, feature_dim: int | None = None):
+    _require_path(path, "siglip2")
     return HFVisionEncoder(path, drop_cls=False, num_tokens=num_tokens, feature_dim=feature_dim)
 
 
 @registry.register("vision_encoder", "clip")
 def _build_clip(path: str, num_tokens: int | None = None, feature_dim: int | None = None):
+    _require_path(path, "clip")
     return HFVisionEncoder(path, drop_cls=True, num_tokens=num_tokens, feature_dim=feature_dim)
 
 

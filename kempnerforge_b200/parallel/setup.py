@@ -72,13 +72,19 @@ def _set_nccl_env() -> None:
         env["TORCH_NCCL_ASYNC_ERROR_HANDLING"] = "1"
 
 
-def barrier_with_timeout(timeout_sec: float = 60.0, group=None) -> None:
-    """A barrier that raises instead of hanging when a rank never arrives."""
-    work = dist.barrier(group=group, async_op=True)
+def barrier_with_timeout(timeout_sec: float = 60.0, group=None, reason: str = "") -> None:
+    """A barrier that raises RuntimeError instead of hanging when a rank never arrives; ``reason`` names the caller
+    in the message (a timeout surfaces either as a False return or as an exception from the wait)."""
+    what = f"barrier ({reason})" if reason else "barrier"
+    work = dist.barrier(async_op=True) if group is None else dist.barrier(group=group, async_op=True)
     if work is None:
         return
-    if not work.wait(timeout=timedelta(seconds=timeout_sec)):
-        raise RuntimeError(f"barrier timed out after {timeout_sec}s")
+    try:
+        arrived = work.wait(timeout=timedelta(seconds=timeout_sec))
+    except RuntimeError as exc:
+        raise RuntimeError(f"{what} failed after at most {timeout_sec}s: {exc}") from exc
+    if arrived is False:
+        raise RuntimeError(f"{what} timed out after {timeout_sec}s")
 
 
 _barrier_with_timeout = barrier_with_timeout

@@ -25,10 +25,14 @@ class SLURMInfo:
     job_name: str | None = None
     node_list: str | None = None
     num_nodes: int = 1
-    tasks_per_node: int = 1
+    ntasks_per_node: int = 1
     restart_count: int = 0
     array_task_id: str | None = None
     partition: str | None = None
+
+    @property
+    def tasks_per_node(self) -> int:
+        return self.ntasks_per_node
 
     @property
     def is_requeued(self) -> bool:
@@ -52,8 +56,8 @@ def get_slurm_info() -> SLURMInfo | None:
         job_id=env["SLURM_JOB_ID"],
         job_name=env.get("SLURM_JOB_NAME"),
         node_list=env.get("SLURM_JOB_NODELIST"),
-        num_nodes=_int("SLURM_JOB_NUM_NODES", 1),
-        tasks_per_node=int(m.group()) if m else 1,
+        num_nodes=_int("SLURM_JOB_NUM_NODES", _int("SLURM_NNODES", 1)),
+        ntasks_per_node=int(m.group()) if m else 1,
         restart_count=_int("SLURM_RESTART_COUNT", 0),
         array_task_id=env.get("SLURM_ARRAY_TASK_ID"),
         partition=env.get("SLURM_JOB_PARTITION"),

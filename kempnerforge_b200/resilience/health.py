@@ -97,17 +97,21 @@ class NaNDetector:
 
 def check_gpu_health(device: int | None = None) -> dict:
     """Tiny compute + allocation probe of the current GPU; never raises."""
-    out = {"healthy": False, "device": None, "error": None}
-    if not torch.cuda.is_available():
+    out = {"healthy": False, "device": None, "error": None, "cuda_available": torch.cuda.is_available(),
+           "device_accessible": False, "compute_ok": False, "memory_ok": False}
+    if not out["cuda_available"]:
         out["error"] = "CUDA not available"
         return out
     try:
         dev = torch.cuda.current_device() if device is None else device
         out["device"] = torch.cuda.get_device_name(dev)
+        out["device_accessible"] = True
         a = torch.ones(256, device=f"cuda:{dev}")
         ok = float((a + a).sum().item()) == 512.0
+        out["compute_ok"] = ok
         buf = torch.empty(1 << 20, dtype=torch.uint8, device=f"cuda:{dev}")
         del buf
+        out["memory_ok"] = True
         out["memory_allocated_gb"] = torch.cuda.memory_allocated(dev) / 1024**3
         out["healthy"] = ok
         if not ok:

@@ -66,7 +66,10 @@ def main(argv=None) -> int:
     def run(prompt: str) -> str:
         ids = tok.encode(prompt) if tok else [int(t) for t in prompt.split()]
         x = torch.tensor([ids], device=device)
-        out = generate(model, x, args.max_new_tokens, args.temperature, args.top_k, args.top_p,
+        room = cfg.model.max_seq_len - len(ids)
+        if room <= 0:
+            raise SystemExit(f"the prompt has {len(ids)} tokens; the model's context is {cfg.model.max_seq_len}")
+        out = generate(model, x, min(args.max_new_tokens, room), args.temperature, args.top_k, args.top_p,
                        eos_token_id=tok.eos_token_id if tok else None,
                        generator=None if device.type == "cuda" else gen)
         new = out[0].tolist()

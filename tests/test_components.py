@@ -53,9 +53,9 @@ def test_sample_temperature_top_k_top_p():
     logits = torch.tensor([[0.0, 5.0, 1.0, 4.0], [3.0, 0.0, 0.0, 0.0]])
     assert sample(logits, temperature=0.0).squeeze(-1).tolist() == [1, 0]
     g = torch.Generator().manual_seed(0)
-    picks = torch.cat([sample(logits, temperature=1.0, top_k=2, generator=g) for _ in range(200)], dim=1)
+    picks = torch.stack([sample(logits, temperature=1.0, top_k=2, generator=g) for _ in range(200)], dim=1)
     assert set(picks[0].tolist()) <= {1, 3} and set(picks[1].tolist()) <= {0, 1, 2, 3}
-    nucleus = torch.cat([sample(logits, temperature=1.0, top_p=0.5, generator=g) for _ in range(200)], dim=1)
+    nucleus = torch.stack([sample(logits, temperature=1.0, top_p=0.5, generator=g) for _ in range(200)], dim=1)
     assert set(nucleus[0].tolist()) == {1}       # the top token alone carries > 0.5 of the mass
     assert set(nucleus[1].tolist()) == {0}
 

@@ -48,7 +48,7 @@ def test_kv_cache_updates_incrementally_and_overflows_loudly():
 
 def test_sampling_rules():
     logits = torch.tensor([[0.0, 1.0, 5.0, 2.0], [3.0, 0.0, 0.0, 0.0]])
-    assert sample(logits, temperature=0.0).tolist() == [[2], [0]]
+    assert sample(logits, temperature=0.0).tolist() == [2, 0]
     g = torch.Generator().manual_seed(0)
     draws = torch.cat([sample(logits[:1], 1.0, top_k=2, generator=g) for _ in range(200)])
     assert set(draws.flatten().tolist()) <= {2, 3}
@@ -58,7 +58,7 @@ def test_sampling_rules():
     assert len(set(hot.flatten().tolist())) == 4       # a high temperature flattens the distribution
     cold = torch.cat([sample(logits[:1], 0.05, generator=g) for _ in range(100)])
     assert set(cold.flatten().tolist()) == {2}
-    assert sample(logits, 1.0, generator=g).shape == (2, 1)
+    assert sample(logits, 1.0, generator=g).shape == (2,)
 
 
 def test_generate_contract():
@@ -74,7 +74,8 @@ def test_generate_contract():
     generate(m, prompt, 2, temperature=0.0)
     assert not m.training                                                          # an eval model stays in eval
     assert torch.equal(generate(m, prompt, 0), prompt)
-    assert generate(m, prompt, 1000, temperature=0.0).shape[1] == m.config.max_seq_len   # clipped to the context
+    with pytest.raises(ValueError, match="exceeds model max_seq_len"):                 # never silently clipped
+        generate(m, prompt, 1000, temperature=0.0)
 
 
 def test_generate_stops_at_eos_and_pads_finished_rows():

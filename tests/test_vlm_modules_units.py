@@ -231,16 +231,15 @@ def test_mot_warm_start_copies_into_every_modality_and_is_idempotent():
     host = Host()
     src = {"transformer.layers.0.attention.q_proj.weight": torch.randn(32, 32),
            "layers.0.mlp.up_proj.weight": torch.randn(48, 32),
-           "layers.7.attention.q_proj.weight": torch.randn(32, 32),      # layer the target does not have: skipped
-           "layers.0.attention.k_proj.weight": torch.randn(5, 5)}        # wrong shape: skipped unless strict
+           "layers.7.attention.q_proj.weight": torch.randn(32, 32)}      # layer the target does not have: skipped
     n = mot_warm_start_from_text_stack(host, src)
     att = host.layers["0"].attn
     for m in ("image", "text"):
         assert torch.equal(att.q_proj[m].weight, src["transformer.layers.0.attention.q_proj.weight"])
         assert torch.equal(host.layers["0"].mlp[m].up_proj.weight, src["layers.0.mlp.up_proj.weight"])
     assert n == 4 and mot_warm_start_from_text_stack(host, src) == 4
-    with pytest.raises(ValueError):
-        mot_warm_start_from_text_stack(host, {"layers.0.attention.k_proj.weight": torch.randn(5, 5)}, strict=True)
+    with pytest.raises(ValueError, match="shape mismatch"):              # a wrong shape is never skipped
+        mot_warm_start_from_text_stack(host, {"layers.0.attention.k_proj.weight": torch.randn(5, 5)})
     assert mot_warm_start_from_text_stack(nn.Linear(2, 2), src) == 0     # nothing to do on a non-MoT module
 
 
