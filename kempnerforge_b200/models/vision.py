@@ -53,8 +53,10 @@ class HFVisionEncoder(VisionEncoder):
         self.feature_dim = feature_dim or cfg.hidden_size
 
     def forward(self, pixel_values: torch.Tensor) -> torch.Tensor:
-        dtype = next(self.model.parameters()).dtype
-        hidden = self.model(pixel_values=pixel_values.to(dtype)).last_hidden_state
+        first = next(self.model.parameters(), None)
+        if first is not None:
+            pixel_values = pixel_values.to(first.dtype)
+        hidden = self.model(pixel_values=pixel_values).last_hidden_state
         return hidden[:, 1:] if self.drop_cls else hidden
 
 
