@@ -1,0 +1,118 @@
+"""One native kernel on one workload, timed with CUDA events (median of ``--iters`` launches after ``--warmup``,
+L2 flushed between launches).  Each workload is small enough (a few hundred MB, a handful of launches) to be the
+subject of a profiler capture as well:
+
+    python benchmarks/single_kernel.py gemm
+    python benchmarks/single_kernel.py attn_bwd --dq-mode red --iters 5
+
+Workloads (Llama-3-8B shapes unless noted): gemm (CTA-pair tiles, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu,
+gemm_rope (QKV projection with the rotary embedding in the epilogue), grouped / grouped_wgrad (8 experts,
+dim 2048 x 5632), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
+rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit).  Prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def build(target: str, K, args):
+    """(callable, flops, bytes) of the workload."""
+    dev, bf = "cuda", torch.bfloat16
+    if target in ("gemm", "gemm_1cta"):
+        a = torch.randn(8192, 4096, device=dev, dtype=bf)
+        w = torch.randn(6144, 4096, device=dev, dtype=bf) * 0.02
+        out = torch.empty(8192, 6144, device=dev, dtype=bf)
+        return (lambda: K.gemm(a, w, out=out, mode=1 if target == "gemm_1cta" else 2)), 2 * 8192 * 6144 * 4096, 0
+    if target == "gemm_swiglu":
+        a = torch.randn(8192, 4096, device=dev, dtype=bf)
+        w = torch.randn(2 * 14336, 4096, device=dev, dtype=bf) * 0.02
+        return (lambda: K.gemm_swiglu(a, w, want_gu=True)), 2 * 8192 * 28672 * 4096, 0
+    if target == "gemm_rope":
+        s, h, hkv, hd = 4096, 32, 8, 128
+        a = torch.randn(2 * s, 4096, device=dev, dtype=bf)
+        w = torch.randn((h + 2 * hkv) * hd, 4096, device=dev, dtype=bf) * 0.02
+        ang = torch.outer(torch.arange(s, device=dev).float(), 500000.0 ** (-torch.arange(0, hd, 2, device=dev).float() / hd))
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        out = torch.empty(2 * s, w.shape[0], device=dev, dtype=bf)
+        return (lambda: K.gemm(a, w, out=out, rope=(cos, sin, s, (h + hkv) * hd, hd))), 2 * 8192 * 6144 * 4096, 0
+    if target in ("grouped", "grouped_wgrad"):
+        counts = torch.tensor([4000, 5000, 3000, 4384, 4100, 3900, 4200, 4184], device=dev)
+        offsets = torch.zeros(9, dtype=torch.int32, device=dev)
+        offsets[1:] = counts.cumsum(0)
+        rows = int(counts.sum())
+        x = torch.randn(rows, 2048, device=dev, dtype=bf)
+        if target == "grouped":
+            w = torch.randn(8, 2048, 5632, device=dev, dtype=bf) * 0.02
+            return (lambda: K.grouped_gemm(x, w, offsets, b_mn=True)), 2 * rows * 2048 * 5632, 0
+        dy = torch.randn(rows, 5632, device=dev, dtype=bf)
+        return (lambda: K.grouped_wgrad(x, dy, offsets)), 2 * rows * 2048 * 5632, 0
+    if target in ("attn_fwd", "attn_bwd"):
+        b, s, h, hkv, hd = 2, 4096, 32, 8, 128
+        qkv = torch.randn(b, s, h + 2 * hkv, hd, device=dev, dtype=bf)
+        q, k, v = qkv[:, :, :h], qkv[:, :, h:h + hkv], qkv[:, :, h + hkv:]
+        sc = 1 / math.sqrt(hd)
+        fwd_flops = 4 * b * h * s * s * hd // 2
+        if target == "attn_fwd":
+            return (lambda: K.attn_fwd(q, k, v, True, None, sc)), fwd_flops, 0
+        K.attn_bwd_dq_mode(0 if args.dq_mode == "red" else 1)
+        out, lse = K.attn_fwd(q, k, v, True, None, sc)
+        dout = torch.randn_like(out)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :h], dqkv[:, :, h:h + hkv], dqkv[:, :, h + hkv:]
+        return (lambda: K.attn_bwd(dout, q, k, v, out, lse, True, None, sc, dq=dq, dk=dk, dv=dv)), fwd_flops * 5 // 2, 0
+    if target == "rmsnorm_bwd":
+        x = torch.randn(16384, 4096, device=dev, dtype=bf)
+        w = torch.ones(4096, device=dev, dtype=bf)
+        _, rstd = K.rmsnorm_fwd(x, w, 1e-5)
+        dy = torch.randn_like(x)
+        return (lambda: K.rmsnorm_bwd(dy, x, w, rstd, residual_grad=dy)), 0, 4 * x.numel() * 2
+    if target == "adamw":
+        n = 218_112_000
+        p, g = torch.randn(n, device=dev, dtype=bf), torch.randn(n, device=dev, dtype=bf)
+        m, v2 = torch.zeros(n, device=dev, dtype=bf), torch.zeros(n, device=dev, dtype=bf)
+        return (lambda: K.adamw_flat(p, g, m, v2, n, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1)), 0, 7 * n * 2
+    raise SystemExit(f"unknown workload {target!r}")
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("target")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--dq-mode", choices=("red", "bulk"), default="bulk")
+    ap.add_argument("--no-flush", action="store_true", help="do not write a 256 MB buffer between launches")
+    args = ap.parse_args()
+    from kempnerforge_b200.ops import cuda as K
+
+    fn, flops, nbytes = build(args.target, K, args)
+    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(args.warmup):
+        fn()
+    times = []
+    for _ in range(args.iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    ms = sorted(times)[len(times) // 2]
+    status = K.read_status()
+    print(json.dumps({"workload": args.target, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1) if flops else None,
+                      "gbs": round(nbytes / ms / 1e6, 1) if nbytes else None, "iters": args.iters, "status_word": status}))
+    return 0 if status == 0 else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

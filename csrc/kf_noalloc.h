@@ -28,6 +28,8 @@ extern "C" {
 // calls that overlap on the GPU (different streams) race on it — serialise them.  The first call on each
 // device does the set-up (it looks the array's device address up with cudaGetSymbolAddress): make that
 // first call before any stream capture begins.  Nothing is claimed here about use inside a capture.
+// Host threads: the per-device address is cached without a lock, so the first call on a device must not
+// run concurrently with another host thread's call on that device; later calls may come from any thread.
 int kf_sumsq_noalloc(const void* x, long long n, int dt, void* out, int accumulate, void* stream);
 
 #ifdef __cplusplus

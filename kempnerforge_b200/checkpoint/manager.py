@@ -117,13 +117,38 @@ def _param_fqns(model) -> dict[int, str]:
     return {id(p): n for n, p in _unwrap(model).named_parameters(remove_duplicate=False)}
 
 
+def _dp_row_mesh(model, engine):
+    """The 1-D data-parallel mesh over which flat moment shards can be described as row shards, or None.
+
+    Flat shards cut parameters at arbitrary elements, which no sharded-tensor placement can express.  When the
+    engine's group is exactly the ``dp_shard`` mesh dimension, every rank instead keeps rows [r*R/N, (r+1)*R/N) of
+    each parameter's moments and hands them to the checkpoint layer as ``Shard(0)`` over that mesh: the layout the
+    reference's FSDP2 optimizer state has (kempnerforge/checkpoint/state.py, DTensor shards over ``dp_shard``), with
+    1/N of the moments per rank instead of a full copy on every rank."""
+    if engine is None or engine.world <= 1:
+        return None
+    mesh = getattr(_unwrap(model), "_kf_mesh", None)
+    names = (mesh.mesh_dim_names or ()) if mesh is not None else ()
+    if "dp_shard" not in names or mesh["dp_shard"].size() != engine.world:
+        return None
+    return mesh["dp_shard"]
+
+
+def _rows_of(full: torch.Tensor, shape, rank: int, world: int) -> torch.Tensor:
+    rows = shape[0] // world
+    return full.view(shape)[rank * rows : (rank + 1) * rows].clone()
+
+
 def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
-    """{"state": {fqn: {...}}, "param_groups": [{"params": [fqn...], ...}]} with whole tensors."""
+    """{"state": {fqn: {...}}, "param_groups": [{"params": [fqn...], ...}]}; flat moments of a data-parallel run
+    appear as row shards over the ``dp_shard`` mesh (one unit is assembled at a time, then cut and released)."""
     fqn_of = _param_fqns(model)
     engine = getattr(_unwrap(model), "_kf_engine", None)
     opts = [optimizer] + ([optimizer.inner_adam] if getattr(optimizer, "inner_adam", None) is not None else [])
     state: dict[str, dict] = {}
     groups = []
+    row_mesh = _dp_row_mesh(model, engine)
+    specs = _shard_specs(model) if row_mesh is not None else {}
     for opt in opts:
         flat_groups = getattr(opt, "_flat_groups", None) or []
         flat_param_ids = set()
@@ -134,11 +159,20 @@ def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
                 m_full, v_full = fg.exp_avg, fg.exp_avg_sq
             for p, off in zip(fg.params, fg.offsets):
                 flat_param_ids.add(id(p))
-                state[fqn_of[id(p)]] = {
-                    "step": fg.step_tensor.detach().clone().cpu(),
-                    "exp_avg": m_full[off : off + p.numel()].view(p.shape),
-                    "exp_avg_sq": v_full[off : off + p.numel()].view(p.shape),
-                }
+                fqn = fqn_of[id(p)]
+                m_p, v_p = m_full[off : off + p.numel()], v_full[off : off + p.numel()]
+                if (row_mesh is not None and not fg.local and fqn not in specs and p.dim() >= 1
+                        and p.shape[0] % engine.world == 0 and p.shape[0] >= engine.world):
+                    from torch.distributed.tensor import DTensor, Shard
+
+                    m_p = DTensor.from_local(_rows_of(m_p, p.shape, engine.rank, engine.world), row_mesh, [Shard(0)], run_check=False)
+                    v_p = DTensor.from_local(_rows_of(v_p, p.shape, engine.rank, engine.world), row_mesh, [Shard(0)], run_check=False)
+                else:
+                    m_p, v_p = m_p.view(p.shape), v_p.view(p.shape)
+                    if m_full is not fg.exp_avg:  # do not keep the whole gathered unit alive through a view
+                        m_p, v_p = m_p.clone(), v_p.clone()
+                state[fqn] = {"step": fg.step_tensor.detach().clone().cpu(), "exp_avg": m_p, "exp_avg_sq": v_p}
+            del m_full, v_full
         for p, st in opt.state.items():
             if id(p) in flat_param_ids or id(p) not in fqn_of:
                 continue
@@ -163,9 +197,18 @@ def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
     return {"state": state, "param_groups": groups}
 
 
+def _whole(v, model_sharded: bool):
+    """A loaded state tensor as this rank needs it: the local part of a tensor- / expert-parallel shard (the
+    parameter itself is sharded that way), the whole tensor for row shards of a data-parallel moment, else itself."""
+    if not hasattr(v, "to_local"):
+        return v
+    return v.to_local() if model_sharded else v.full_tensor()
+
+
 def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
     """Inverse of ``optimizer_state_dict`` for tensors that were loaded in place (flat views) or into copies."""
-    loaded = {**loaded, "state": {fqn: {k: to_local(v) for k, v in entry.items()}
+    specs = _shard_specs(model)
+    loaded = {**loaded, "state": {fqn: {k: _whole(v, fqn in specs) for k, v in entry.items()}
                                   for fqn, entry in loaded["state"].items()}}
     name_to_param = dict(_unwrap(model).named_parameters(remove_duplicate=False))
     engine = getattr(_unwrap(model), "_kf_engine", None)
@@ -323,8 +366,10 @@ class CheckpointManager:
         self._drain_pending_finalize()
         if self._is_writer() or (self.pp_rank is not None and self.group_rank == 0):
             train_state = build_train_state(step, tokens_seen, scheduler, dataloader, extra)
-            target = dcp_dir if self.pp_rank is not None else step_dir
-            torch.save(train_state, target / "train_state.pt")
+            if self._is_writer():  # the reference's layout: one train state per step, written by rank 0
+                torch.save(train_state, step_dir / "train_state.pt")
+            if self.pp_rank is not None and self.group_rank == 0:  # plus one per stage (its own RNG / loader state)
+                torch.save(train_state, dcp_dir / "train_state.pt")
         if self._is_writer():
             meta = {"step": step, "tokens_seen": tokens_seen}
             if extra and "vlm_freeze" in extra:
@@ -389,8 +434,14 @@ class CheckpointManager:
         return None
 
     def load(self, path=None, scheduler=None, dataloader=None, exclude_keys: list[str] | None = None,
-             vlm_freeze_expected: list[dict] | None = None) -> tuple[int, int, dict]:
-        """Restore model / optimizer / train state; returns (step, tokens_seen, extras) — (0, 0, {}) if nothing found."""
+             vlm_freeze_expected: list[dict] | None = None, allow_fallback: bool | None = None) -> tuple[int, int, dict]:
+        """Restore model / optimizer / train state; returns (step, tokens_seen, extras) — (0, 0, {}) if nothing found.
+
+        An incomplete checkpoint (tensor data without ``.metadata``) is replaced by the newest complete one only on
+        auto-resume (``allow_fallback``; default: no explicit ``path`` and no ``checkpoint.load_path``).  An explicit
+        path is honoured as given and fails loudly, like the reference; rank 0 decides and the others follow."""
+        if allow_fallback is None:
+            allow_fallback = not path and not self.config.load_path
         step_dir = self._resolve_load_path(path)
         exists = step_dir is not None
         if self._dist and dist.get_world_size() > 1:  # rank 0's view of the filesystem is authoritative
@@ -400,12 +451,19 @@ class CheckpointManager:
         if not exists:
             log.info("no checkpoint found under %s; starting from scratch", self.dir)
             return 0, 0, {}
-        step_dir = self._resolve_dcp_load_dir(step_dir)
-        if step_dir is None:
-            log.warning("no complete checkpoint available; starting from scratch")
-            return 0, 0, {}
-        self._check_freeze_metadata(step_dir, vlm_freeze_expected)
         exclude = set(exclude_keys or [])
+        wants_tensors = not {"model", "optimizer"} <= exclude
+        if wants_tensors and allow_fallback:
+            chosen = self._resolve_dcp_load_dir(step_dir)
+            if self._dist and dist.get_world_size() > 1:
+                box = [str(chosen) if chosen is not None else ""]
+                dist.broadcast_object_list(box, src=0, group=self._sync_group)
+                chosen = Path(box[0]) if box[0] else None
+            if chosen is None:
+                log.warning("no complete checkpoint available; starting from scratch")
+                return 0, 0, {}
+            step_dir = chosen
+        self._check_freeze_metadata(step_dir, vlm_freeze_expected)
         state: dict[str, Any] = {}
         if "model" not in exclude:
             state["model"] = model_state_dict(self.model)
@@ -453,6 +511,10 @@ class CheckpointManager:
 
     def _load_train_state(self, step_dir: Path) -> dict | None:
         target = (self._dcp_dir(step_dir) if self.pp_rank is not None else step_dir) / "train_state.pt"
+        if self.pp_rank is not None and not target.exists() and (step_dir / "train_state.pt").exists():
+            # a checkpoint in the reference's layout: one train state for all stages
+            log.info("no per-stage train state in %s; reading %s", target.parent, step_dir / "train_state.pt")
+            target = step_dir / "train_state.pt"
         multi = self._dist and dist.get_world_size() > 1 and self.pp_rank is None
         state = None
         if not multi or self.rank == 0:

@@ -58,6 +58,9 @@ class DataParallelEngine:
         self._sq_from_reduce = False
         self._root_groups: list[int] = []
         self._published_per_group = False
+        # True when the optimizer steps on whole parameters (Lion, Schedule-Free AdamW, Muon) instead of the flat
+        # shards: every rank then needs the *whole* averaged gradient, not only its shard (set by build_optimizer)
+        self.full_grads = False
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
         if self.world > 1:
@@ -144,6 +147,8 @@ class DataParallelEngine:
         if self.symmetric and g.grad_symm is not None:
             return self._reduce_one_symmetric(g, async_op)
         if g.grad.is_cuda and "nccl" in str(dist.get_backend(self.pg)):
+            if self.full_grads:
+                return dist.all_reduce(g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
             lo, hi = g.shard_range
             return dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
         work = dist.all_reduce(g.grad, group=self.pg, async_op=async_op)
@@ -166,6 +171,11 @@ class DataParallelEngine:
         def launch():
             g.grad_symm.barrier()
             kcuda.symm_rs_norm(g.grad_symm, lo, hi - lo, self._sq3[slot : slot + 1], accumulate=True)
+            if self.full_grads:
+                # whole-parameter optimizers: every rank also needs the other shards of the averaged gradient
+                g.grad_symm.barrier()  # every rank has finished reading the un-averaged values of this range
+                kcuda.symm_gather(g.grad_symm, lo, hi - lo)
+                g.grad_symm.barrier()
 
         if not async_op or self._comm_stream is None:
             launch()
@@ -273,7 +283,7 @@ class DataParallelEngine:
     def apply_grad_scale(self) -> None:
         """Multiply the (shard) gradients by ``grad_scale``; only needed for optimizers that do not fuse it."""
         for g in self.groups:
-            lo, hi = g.shard_range
+            lo, hi = (0, g.numel) if self.full_grads else g.shard_range
             g.grad[lo:hi].mul_(self.grad_scale.to(g.grad.dtype))
 
     def publish_on_side_stream(self, flat_groups) -> bool:

@@ -414,4 +414,8 @@ def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.op
     if flat and isinstance(opt, FusedAdamW):
         opt.attach_flat_groups(flat)
         opt._engine = getattr(model, "_kf_engine", None)
+    elif getattr(model, "_kf_engine", None) is not None:
+        # whole-parameter optimizers read every element of ``p.grad``: the engine must leave the complete averaged
+        # gradient on every rank, not only the local shard of each flat buffer
+        model._kf_engine.full_grads = True
     return opt

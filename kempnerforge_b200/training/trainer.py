@@ -294,8 +294,9 @@ class Trainer:
             self.optimizer.step()
             if self.engine is not None:
                 self.engine.after_optimizer_step()
-        self.scheduler.step()
-        self._apply_phase_lr()
+            # a skipped (non-finite) step advances neither the optimizer nor the schedule, like the reference's loop
+            self.scheduler.step()
+            self._apply_phase_lr()
         if self.engine is not None:
             self.engine.zero_grad()
         self.optimizer.zero_grad(set_to_none=True)
@@ -354,8 +355,22 @@ class Trainer:
         resume = cfg.load_path or resolve_resume_path(cfg.dir)
         if resume:
             exclude = list(cfg.exclude_from_loading) or None
+            freeze_expected = None
+            vlm = self.config.vlm
+            if vlm is not None:
+                # The trainable set at the saved step may differ from the one the model was built with (step 0):
+                # move to the saved step's freeze stage first, so the flat groups and the optimizer template hold
+                # exactly the parameters whose moments the checkpoint carries; then compare the freeze metadata.
+                from kempnerforge_b200.training.freeze import canonical_freeze_meta, effective_freeze
+
+                probe = self.ckpt.peek_saved_step(resume) or 0
+                freeze_expected = canonical_freeze_meta(effective_freeze(vlm, probe))
+                if vlm.freeze_schedule and probe > 0:
+                    self.step = probe
+                    self._maybe_advance_freeze_stage()
             self.step, self.tokens_seen, extra = self.ckpt.load(
-                path=resume, scheduler=self.scheduler, dataloader=self.dataloader, exclude_keys=exclude)
+                path=resume, scheduler=self.scheduler, dataloader=self.dataloader, exclude_keys=exclude,
+                vlm_freeze_expected=freeze_expected, allow_fallback=not cfg.load_path)
             self.config.metrics.wandb_run_id = extra.get("wandb_run_id", self.config.metrics.wandb_run_id)
             log.info("Resumed from %s at step=%d", resume, self.step)
 
@@ -363,6 +378,10 @@ class Trainer:
         if self.ckpt is None:
             return
         extra = {"phase_idx": self.phase_idx, "wandb_run_id": self.tracker.wandb_run_id}
+        if self.config.vlm is not None:
+            from kempnerforge_b200.training.freeze import canonical_freeze_meta, effective_freeze
+
+            extra["vlm_freeze"] = canonical_freeze_meta(effective_freeze(self.config.vlm, self.step))
         path = self.ckpt.save(self.step, self.tokens_seen, scheduler=self.scheduler, dataloader=self.dataloader,
                               extra=extra)
         self.hook_runner.on_checkpoint_save(self.step, str(path))

@@ -13,6 +13,11 @@ cd "$REPO"
 if [[ "$LOCAL_RANK" == "0" ]]; then
     python -c "from kempnerforge_b200.ops.build import build; build()"
 else
-    until [[ -f kempnerforge_b200/lib/build.stamp ]]; do sleep 1; done
+    # bounded: if local rank 0's build fails there will never be a stamp, and the job must end, not hang
+    for _ in $(seq 1 "${KF_BUILD_WAIT_SEC:-900}"); do
+        [[ -f kempnerforge_b200/lib/build.stamp ]] && break
+        sleep 1
+    done
+    [[ -f kempnerforge_b200/lib/build.stamp ]] || { echo "native library was not built on this node" >&2; exit 1; }
 fi
 exec python scripts/train.py "$@"

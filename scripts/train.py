@@ -15,28 +15,7 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from kempnerforge_b200.config import load_config  # noqa: E402
-from kempnerforge_b200.metrics.logger import get_logger  # noqa: E402
-from kempnerforge_b200.parallel.setup import destroy_distributed  # noqa: E402
-from kempnerforge_b200.resilience import log_job_info  # noqa: E402
-from kempnerforge_b200.training.trainer import Trainer  # noqa: E402
-
-
-def main(argv: list[str] | None = None) -> int:
-    argv = list(sys.argv[1:] if argv is None else argv)
-    path = None
-    if argv and not argv[0].startswith("--"):
-        path = argv.pop(0)
-    config = load_config(path, argv)
-    log = get_logger("train")
-    log_job_info()
-    trainer = Trainer(config)
-    try:
-        result = trainer.fit()
-    finally:
-        destroy_distributed()
-    return 0 if result.get("stop_reason") in (None, "signal") else 1
-
+from kempnerforge_b200.cli import train as main  # noqa: E402
 
 if __name__ == "__main__":
     sys.exit(main())

@@ -125,6 +125,39 @@ def test_incomplete_checkpoint_falls_back(tmp_path):
     assert empty == (0, 0, {})
 
 
+def test_explicit_path_is_honoured_and_train_state_only_load_needs_no_tensors(tmp_path):
+    """Fallback to an older checkpoint is for auto-resume only; an explicit path fails loudly.  A load that wants
+    only the train state does not look at the tensor data."""
+    cfg = CheckpointConfig(dir=str(tmp_path))
+    model, opt, sched = _setup()
+    _step(model, opt, sched, 0)
+    CheckpointManager(cfg, model, opt).save(1, tokens_seen=7, scheduler=sched)
+    broken = tmp_path / "step_2"
+    broken.mkdir()
+    with pytest.raises(BaseException):   # torch's CheckpointException derives from BaseException
+        CheckpointManager(cfg, *_setup()[:2]).load(path=str(broken))
+    for f in (tmp_path / "step_1").glob("*.distcp"):
+        f.unlink()
+    (tmp_path / "step_1" / ".metadata").unlink()
+    step, tokens, _ = CheckpointManager(cfg, *_setup()[:2]).load(path=str(tmp_path / "step_1"),
+                                                                exclude_keys=["model", "optimizer"])
+    assert (step, tokens) == (1, 7)
+
+
+def test_pipeline_stage_reads_the_step_level_train_state(tmp_path):
+    """With pipeline parallelism rank 0 writes ``step_N/train_state.pt`` (the reference's layout) beside the per-stage
+    copies, and a stage without its own copy falls back to it."""
+    cfg = CheckpointConfig(dir=str(tmp_path))
+    model, opt, sched = _setup()
+    _step(model, opt, sched, 0)
+    CheckpointManager(cfg, model, opt, pp_rank=0).save(1, tokens_seen=11, scheduler=sched, extra={"wandb_run_id": "abc"})
+    assert (tmp_path / "step_1" / "train_state.pt").exists() and (tmp_path / "step_1" / "pp0" / "train_state.pt").exists()
+    (tmp_path / "step_1" / "pp0" / "train_state.pt").unlink()          # what a reference-written checkpoint looks like
+    model2, opt2, sched2 = _setup(seed=5)
+    step, tokens, extra = CheckpointManager(cfg, model2, opt2, pp_rank=0).load(scheduler=sched2)
+    assert (step, tokens, extra.get("wandb_run_id")) == (1, 11, "abc") and sched2.last_epoch == sched.last_epoch
+
+
 def test_exclude_optimizer_and_dataloader_stash(tmp_path):
     cfg = CheckpointConfig(dir=str(tmp_path))
     model, opt, sched = _setup()

@@ -293,6 +293,59 @@ def test_tensor_parallel_checkpoint_round_trip_and_reshard(tmp_path):
         assert torch.equal(p.detach(), full[name]), name
 
 
+def _dp_ckpt_worker(rank, world, ckpt_dir):
+    """Sharded data parallelism: the moments reach the checkpoint as row shards (1/N per rank), and come back."""
+    from kempnerforge_b200.checkpoint import CheckpointManager
+    from kempnerforge_b200.checkpoint.manager import optimizer_state_dict
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(TINY, {"dp_shard": world})
+    cfg.checkpoint.dir = ckpt_dir
+    t = Trainer(cfg)
+    data = _batches(3 * world)
+    for s in range(2):
+        t.train_step([data[s * world + rank]])
+    t.step = 2
+    mgr = CheckpointManager(cfg.checkpoint, t.model, t.optimizer)
+    sd = optimizer_state_dict(t.model, t.optimizer)["state"]
+    n_row_sharded = sum(1 for v in sd.values() if hasattr(v["exp_avg"], "to_local"))
+    local_numel = sum(v["exp_avg"].to_local().numel() if hasattr(v["exp_avg"], "to_local") else v["exp_avg"].numel()
+                      for v in sd.values())
+    want_m = {k: (v["exp_avg"].full_tensor() if hasattr(v["exp_avg"], "full_tensor") else v["exp_avg"]).clone()
+              for k, v in sd.items()}
+    mgr.save(2, tokens_seen=64, scheduler=t.scheduler)
+    mgr.wait()
+    want_w = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    t.train_step([data[2 * world + rank]])
+    mgr.load(scheduler=t.scheduler)
+    sd2 = optimizer_state_dict(t.model, t.optimizer)["state"]
+    got_m = {k: (v["exp_avg"].full_tensor() if hasattr(v["exp_avg"], "full_tensor") else v["exp_avg"]) for k, v in sd2.items()}
+    same_w = all(torch.equal(want_w[n], p.detach()) for n, p in t.model.named_parameters())
+    same_m = all(torch.equal(want_m[k], got_m[k]) for k in want_m)
+    total = sum(p.numel() for p in t.model.parameters())
+    return n_row_sharded, local_numel, total, same_w, same_m, want_m
+
+
+def test_data_parallel_moments_are_saved_as_row_shards_and_reload_anywhere(tmp_path):
+    from kempnerforge_b200.checkpoint import CheckpointManager
+    from kempnerforge_b200.checkpoint.manager import optimizer_state_dict
+    from kempnerforge_b200.training.trainer import Trainer
+
+    ckpt = str(tmp_path / "ckpt")
+    results = run_ranks(_dp_ckpt_worker, 2, ckpt)
+    for n_rows, local_numel, total, same_w, same_m, _ in results:
+        assert n_rows > 0 and local_numel < 0.6 * total      # about half of the moments per rank, not a full copy
+        assert same_w and same_m
+    # a single process reads the same files back whole
+    cfg = _job(TINY, {})
+    cfg.checkpoint.dir = ckpt
+    single = Trainer(cfg, init_dist=False)
+    CheckpointManager(cfg.checkpoint, single.model, single.optimizer).load(scheduler=single.scheduler)
+    got = optimizer_state_dict(single.model, single.optimizer)["state"]
+    for k, want in results[0][5].items():
+        assert torch.equal(got[k]["exp_avg"], want), k
+
+
 # ------------------------------------------------------------------ combined meshes
 def _tp_dp_worker(rank, world, model_cfg, steps):
     """tp = 2 inside, sharded data parallelism across: ranks (0, 1) and (2, 3) are the two TP groups."""

@@ -29,6 +29,8 @@ def _loader(cfg, n=8):
     tok = ToyTokenizer()
     rows = [{"image": Image.new("RGB", (8, 8), color=(i * 20 % 255, 10, 200)), "text": f"w{i} w{i + 1} w{i + 2} end"}
             for i in range(n)]
+    for r in rows:      # the toy vocabulary grows in encounter order: fix it, so two loaders tokenise alike
+        tok(r["text"])
     ds = HuggingFaceVLMDataset("toy", "train", "image", "text", "", cfg.vlm.max_text_len, image_size=8, rows=rows,
                                tokenizer=tok)
     return build_vlm_dataloader(cfg, dataset=ds, tokenizer=tok)
@@ -88,3 +90,47 @@ def test_vlm_run_reports_the_text_tokens_of_logged_steps():
     t.step = 1
     t.train_step()                                  # step 2 with log_interval=100: nothing is counted
     assert t._text_token_metrics() == {}
+
+
+def test_resume_after_a_freeze_stage_boundary_is_bit_exact(tmp_path):
+    """A checkpoint written after the transformer thawed carries moments for parameters that are frozen at step 0.
+    The resuming trainer has to move to the saved step's freeze stage before loading; it then continues exactly
+    like the run that never stopped, and the checkpoint's metadata records the freeze set-up."""
+    import json
+
+    def make():
+        cfg = _cfg("joint_decoder",
+                   freeze=[{"module": "vision_encoder", "frozen": True}, {"module": "transformer", "frozen": True}],
+                   freeze_schedule=[{"start_step": 2, "specs": [{"module": "transformer", "frozen": False}]}])
+        cfg.checkpoint.dir = str(tmp_path / "ckpt")
+        cfg.checkpoint.async_mode = "disabled"
+        return cfg
+
+    def run(t, n):
+        out = []
+        for _ in range(n):
+            t._maybe_advance_freeze_stage()
+            out.append(t.train_step()["loss"])
+            t.step += 1
+        return out
+
+    cfg = make()
+    a = Trainer(cfg, init_dist=False, dataloader=_loader(cfg, n=16))
+    a.setup_checkpointing()
+    run(a, 3)                                           # steps 0, 1 frozen; step 2 trains the transformer
+    a.save_checkpoint()
+    a.ckpt.wait()
+    meta = json.loads((tmp_path / "ckpt" / "step_3" / "metadata.json").read_text())
+    assert {"module": "transformer", "frozen": False} in meta["vlm_freeze"]
+    tail_a = run(a, 2)
+
+    cfg_b = make()
+    b = Trainer(cfg_b, init_dist=False, dataloader=_loader(cfg_b, n=16))
+    assert not any(n.startswith("transformer.") for n, p in b.model.named_parameters() if p.requires_grad)
+    b.setup_checkpointing()
+    assert b.step == 3
+    assert any(n.startswith("transformer.") for n, p in b.model.named_parameters() if p.requires_grad)
+    tail_b = run(b, 2)
+    assert tail_a == tail_b
+    for (n1, p1), (n2, p2) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2), n1

@@ -64,6 +64,29 @@ def test_noalloc_sumsq_matches_regular_entry_point_twice(dtype, dt):
         assert abs(got.item() - 2 * want.item()) <= 1e-5 * abs(want.item())
 
 
+def test_noalloc_sumsq_unaligned_bf16_view_and_empty_input():
+    """A bf16 view that starts one element into its allocation is only 2-byte aligned (the scalar path of the
+    kernel); a length that is not a multiple of 8 exercises the tail; an empty input must give 0."""
+    lib = _load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(1)
+    stream = torch.cuda.current_stream().cuda_stream
+    base = torch.randn(70_003, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    for _ in range(2):
+        x = base[1:]                                        # odd element offset, n % 8 != 0
+        assert x.data_ptr() % 16 != 0 and x.numel() % 8 != 0
+        got = torch.full((1,), -1.0, dtype=torch.float32, device=dev)
+        assert lib.kf_sumsq_noalloc(x.data_ptr(), x.numel(), 0, got.data_ptr(), 0, stream) == 0
+        want = _reference(lib, x, 0)
+        torch.cuda.synchronize()
+        exact = (x.double() ** 2).sum().item()
+        assert torch.allclose(got, want, rtol=1e-6, atol=0.0) and abs(got.item() - exact) <= 1e-4 * exact
+        empty = torch.full((1,), 5.0, dtype=torch.float32, device=dev)
+        assert lib.kf_sumsq_noalloc(x.data_ptr(), 0, 0, empty.data_ptr(), 0, stream) == 0
+        torch.cuda.synchronize()
+        assert empty.item() == 0.0
+
+
 def test_noalloc_sumsq_rejects_oversize_and_bad_dtype():
     lib = _load()
     out = torch.zeros(1, dtype=torch.float32, device="cuda")
