@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O,
                      float* __restrict__ LSE, const int* __restrict__ doc_ids, int Sq, int Sk, int H, int group,
-                     long long ldo, float scale_log2, int* status) {
+                     long long ldo, float scale_log2, int* status, int n_super, int n_batch) {
   using C = Cfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -72,9 +72,13 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_super = gridDim.x;
-  const int qs = n_super - 1 - blockIdx.x;  // longest causal rows first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid, query super-tile slowest: blocks are handed out in index order, so with a causal mask ALL the longest
+  // rows (of every head and batch entry) start first and the short ones fill the tail of the last wave; the heads
+  // of one KV group are neighbours and share their K / V tiles in L2
+  const int n_hb = H * n_batch;
+  const int qs = CAUSAL ? n_super - 1 - int(blockIdx.x) / n_hb : int(blockIdx.x) / n_hb;
+  const int hb = int(blockIdx.x) % n_hb;
+  const int h = hb % H, b = hb / H;
   const int hk = h / group;
   const int m0 = qs * 2 * BLK_M;
   const int kv_all = (Sk + BLK_N - 1) / BLK_N;
@@ -368,9 +372,10 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     if (e != cudaSuccess) return 300 + (int)e;
     attr_set = true;
   }
-  dim3 grid((Sq + 2 * BLK_M - 1) / (2 * BLK_M), H, B);
+  const int n_super = (Sq + 2 * BLK_M - 1) / (2 * BLK_M);
+  dim3 grid((unsigned)(n_super * H * B));
   kern<<<grid, THREADS, Cfg<HD>::SMEM, stream>>>(mq, mk, mv, reinterpret_cast<__nv_bfloat16*>(O), LSE, doc, Sq, Sk, H,
-                                                 H / Hkv, ldo, scale * 1.4426950408889634f, status);
+                                                 H / Hkv, ldo, scale * 1.4426950408889634f, status, n_super, B);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

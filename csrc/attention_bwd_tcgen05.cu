@@ -92,7 +92,8 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const __grid_constant__ CUtensorMap map_dq, int dq_tma, const float* __restrict__ LSE, const float* __restrict__ Dsum, const int* __restrict__ doc_ids,
                     float* __restrict__ dQacc, __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV, int Sq,
-                    int Sk, int H, int group, long long lddk, long long lddv, float scale, int* status) {
+                    int Sk, int H, int group, long long lddk, long long lddv, float scale, int* status,
+                    const float* __restrict__ cosT, const float* __restrict__ sinT) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -307,12 +308,16 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const bool tile_masked = HAS_DOC || (CAUSAL && q0 < k0 + BLK_K - 1) || (k0 + BLK_K > Sk) || (q0 + BLK_Q > Sq);
       uint32_t pk[BLK_Q / 2], dsk[BLK_Q / 2];
 #pragma unroll
-      for (int i = 0; i < BLK_Q / 2; ++i) {
-        float p[2], ds[2];
+      for (int i4 = 0; i4 < BLK_Q / 4; ++i4) {
+        // four queries per step: their lse / D come as two 16-byte broadcast reads instead of eight 4-byte ones
+        const float4 l4 = *reinterpret_cast<const float4*>(stat + 4 * i4);
+        const float4 d4 = *reinterpret_cast<const float4*>(stat + 64 + 4 * i4);
+        const float lse4[4] = {l4.x, l4.y, l4.z, l4.w}, dd4[4] = {d4.x, d4.y, d4.z, d4.w};
+        float p[4], ds[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int c = 2 * i + e;
-          float pe = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -stat[c]));
+        for (int e = 0; e < 4; ++e) {
+          const int c = 4 * i4 + e;
+          float pe = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -lse4[e]));
           if (tile_masked) {
             const int qpos = q0 + c;
             bool vis = kpos < Sk && qpos < Sq;
@@ -321,10 +326,12 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             pe = vis ? pe : 0.f;
           }
           p[e] = pe;
-          ds[e] = pe * (__uint_as_float(dp[c]) - stat[64 + c]) * scale;
+          ds[e] = pe * (__uint_as_float(dp[c]) - dd4[e]) * scale;
         }
-        pk[i] = pack_bf16(p[0], p[1]);
-        dsk[i] = pack_bf16(ds[0], ds[1]);
+        pk[2 * i4] = pack_bf16(p[0], p[1]);
+        pk[2 * i4 + 1] = pack_bf16(p[2], p[3]);
+        dsk[2 * i4] = pack_bf16(ds[0], ds[1]);
+        dsk[2 * i4 + 1] = pack_bf16(ds[2], ds[3]);
       }
       // P^T over the start of S^T (every score of this row is in registers)
       {
@@ -354,10 +361,43 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     // ---- epilogue: dK / dV accumulators -> bf16 rows of the key tile
     if (ok && n_iter > 0 && !mbar_wait(final_bar, 0, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
+    if (ok && cosT != nullptr && n_iter > 0) {
+      // dK leaves through the inverse rotary embedding (the forward rotated K after the projection): columns
+      // (i, i + 64) of a head are a pair, the angle is that of the key's position
+      tc_fence_after();
+      __nv_bfloat16* dst = dK + (size_t(b) * Sk + kpos) * lddk + size_t(hk) * HD;
+      const float* cr = cosT + size_t(min(kpos, Sk - 1)) * (HD / 2);
+      const float* sr = sinT + size_t(min(kpos, Sk - 1)) * (HD / 2);
+#pragma unroll 1
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t lo[32], hi[32];
+        tmem_ld_32x32_at(t_lane + DK_COL + c * 32, lo);
+        tmem_ld_32x32_at(t_lane + DK_COL + HD / 2 + c * 32, hi);
+        tmem_ld_wait();
+        if (kpos < Sk) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float a[8], bb[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float cv = cr[c * 32 + 8 * i + e], sv2 = sr[c * 32 + 8 * i + e];
+              const float x = __uint_as_float(lo[8 * i + e]), y = __uint_as_float(hi[8 * i + e]);
+              a[e] = x * cv + y * sv2;
+              bb[e] = y * cv - x * sv2;
+            }
+            uint4 w0, w1;
+            w0.x = pack_bf16(a[0], a[1]); w0.y = pack_bf16(a[2], a[3]); w0.z = pack_bf16(a[4], a[5]); w0.w = pack_bf16(a[6], a[7]);
+            w1.x = pack_bf16(bb[0], bb[1]); w1.y = pack_bf16(bb[2], bb[3]); w1.z = pack_bf16(bb[4], bb[5]); w1.w = pack_bf16(bb[6], bb[7]);
+            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = w0;
+            *reinterpret_cast<uint4*>(dst + HD / 2 + c * 32 + 8 * i) = w1;
+          }
+        }
+      }
+    }
     if (ok) {
       tc_fence_after();
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      for (int which = 0; which < ((cosT != nullptr && n_iter > 0) ? 1 : 2); ++which) {
         __nv_bfloat16* dst = which == 0 ? dV + (size_t(b) * Sk + kpos) * lddv + size_t(hk) * HD
                                         : dK + (size_t(b) * Sk + kpos) * lddk + size_t(hk) * HD;
         const uint32_t col0 = which == 0 ? DV_COL : DK_COL;
@@ -477,6 +517,31 @@ __global__ void kf_f32_to_bf16_rows(const float* __restrict__ src, __nv_bfloat16
   }
 }
 
+// fp32 dQ [rows][H * 128] -> bf16 rows with pitch ld, through the inverse rotary embedding of position (row % S)
+__global__ void kf_dq_finish_rope(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int H,
+                                  long long ld, const float* __restrict__ cosT, const float* __restrict__ sinT, int S) {
+  constexpr int HALF = HD / 2;
+  const long long n4 = rows * H * (HALF / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const int j = (i % (HALF / 4)) * 4;
+    const long long rh = i / (HALF / 4);
+    const int h = rh % H;
+    const long long r = rh / H;
+    const int pos = r % S;
+    const float4 a = *reinterpret_cast<const float4*>(src + (r * H + h) * HD + j);
+    const float4 b = *reinterpret_cast<const float4*>(src + (r * H + h) * HD + HALF + j);
+    const float4 c = *reinterpret_cast<const float4*>(cosT + size_t(pos) * HALF + j);
+    const float4 s = *reinterpret_cast<const float4*>(sinT + size_t(pos) * HALF + j);
+    uint2 lo, hi;
+    lo.x = pack_bf16(a.x * c.x + b.x * s.x, a.y * c.y + b.y * s.y);
+    lo.y = pack_bf16(a.z * c.z + b.z * s.z, a.w * c.w + b.w * s.w);
+    hi.x = pack_bf16(b.x * c.x - a.x * s.x, b.y * c.y - a.y * s.y);
+    hi.y = pack_bf16(b.z * c.z - a.z * s.z, b.w * c.w - a.w * s.w);
+    *reinterpret_cast<uint2*>(dst + r * ld + h * HD + j) = lo;
+    *reinterpret_cast<uint2*>(dst + r * ld + h * HD + HALF + j) = hi;
+  }
+}
+
 }  // namespace attnb
 }  // namespace kf
 
@@ -517,11 +582,14 @@ int kf_attn_bwd_dq_mode(int mode) {
 // side; lse: fp32 [B][H][Sq] from the forward; dsum: fp32 scratch [B][H][Sq]; dq_acc: fp32 scratch
 // [B][Sq][H][128] (zeroed here); dq / dk / dv: bf16 outputs with pitches lddq / lddk / lddv (they may be
 // slices of one fused gradient buffer).  doc: optional int32 [B][S].  Requires Sq == Sk when causal or doc.
-int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
-                     void* dsum, void* dq_acc, void* dq, void* dk, void* dv, const void* doc, int B, int Sq, int Sk,
-                     int H, int Hkv, int hd, long long ldq, long long ldk, long long ldv, long long ldo,
-                     long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
-                     void* stream) {
+// kf_attn_bwd_rope_bf16: the same, and dq / dk additionally pass through the inverse rotary embedding (cosT / sinT:
+// fp32 [Sq][64], position = index inside the sequence), i.e. they are gradients with respect to the un-rotated
+// projections when q / k were rotated after the projection.  Null tables = no rotation.
+int kf_attn_bwd_rope_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
+                          void* dsum, void* dq_acc, void* dq, void* dk, void* dv, const void* doc, int B, int Sq, int Sk,
+                          int H, int Hkv, int hd, long long ldq, long long ldk, long long ldv, long long ldo,
+                          long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
+                          const void* cosT, const void* sinT, void* stream) {
   using namespace kf;
   using namespace kf::attnb;
   if (hd != HD || Hkv <= 0 || H % Hkv != 0) return 3;
@@ -568,7 +636,8 @@ int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o,
                                       reinterpret_cast<const float*>(dsum), reinterpret_cast<const int*>(doc),     \
                                       reinterpret_cast<float*>(dq_acc), reinterpret_cast<__nv_bfloat16*>(dk),      \
                                       reinterpret_cast<__nv_bfloat16*>(dv), Sq, Sk, H, H / Hkv, lddk, lddv, scale, \
-                                      status);                                                                     \
+                                      status, reinterpret_cast<const float*>(cosT),                                \
+                                      reinterpret_cast<const float*>(sinT));                                       \
   }
   if (doc) {
     if (causal) KF_BWD_LAUNCH(true, true) else KF_BWD_LAUNCH(false, true)
@@ -579,11 +648,25 @@ int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o,
   {
     const long long rows = (long long)B * Sq;
     const int cols = H * hd;
-    kf_f32_to_bf16_rows<<<1184, 256, 0, st>>>(reinterpret_cast<const float*>(dq_acc),
-                                              reinterpret_cast<__nv_bfloat16*>(dq), rows, cols, lddq);
+    if (cosT)
+      kf_dq_finish_rope<<<1184, 256, 0, st>>>(reinterpret_cast<const float*>(dq_acc), reinterpret_cast<__nv_bfloat16*>(dq),
+                                              rows, H, lddq, reinterpret_cast<const float*>(cosT),
+                                              reinterpret_cast<const float*>(sinT), Sq);
+    else
+      kf_f32_to_bf16_rows<<<1184, 256, 0, st>>>(reinterpret_cast<const float*>(dq_acc),
+                                                reinterpret_cast<__nv_bfloat16*>(dq), rows, cols, lddq);
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+int kf_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
+                     void* dsum, void* dq_acc, void* dq, void* dk, void* dv, const void* doc, int B, int Sq, int Sk,
+                     int H, int Hkv, int hd, long long ldq, long long ldk, long long ldv, long long ldo,
+                     long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
+                     void* stream) {
+  return kf_attn_bwd_rope_bf16(q, k, v, o, d_o, lse, dsum, dq_acc, dq, dk, dv, doc, B, Sq, Sk, H, Hkv, hd, ldq, ldk, ldv,
+                               ldo, lddo, lddq, lddk, lddv, scale, causal, nullptr, nullptr, stream);
 }
 
 }  // extern "C"

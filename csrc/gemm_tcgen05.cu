@@ -255,7 +255,23 @@ int launch_gemm_swiglu_2cta(const void* A, const void* W, void* H, void* GU, int
                             int ldgu, int num_sms, cudaStream_t stream, int* status);
 }
 
+namespace kf2 {
+int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                          const float* cosT, const float* sinT, int S, int rope_cols, int hd, int num_sms,
+                          cudaStream_t stream, int* status);
+}
+
 extern "C" {
+
+// Fused Q | K | V projection with the rotary embedding in the epilogue: out[M, N] = x W^T, then every head of `hd`
+// columns inside the first `rope_cols` columns is rotated by the angle of position (row % S); cos / sin are fp32
+// [S][hd / 2].  N and rope_cols multiples of hd (64, 128 or 256); pitches in elements, multiples of 8.
+int kf_gemm_rope_bf16(const void* x, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldc,
+                      const void* cosT, const void* sinT, int S, int rope_cols, int hd, int num_sms, void* stream) {
+  if ((lda & 7) || (ldw & 7) || (ldc & 7)) return 5;
+  return kf2::launch_gemm_rope_2cta(x, w, out, M, N, K, lda, ldw, ldc, (const float*)cosT, (const float*)sinT, S,
+                                    rope_cols, hd, num_sms, (cudaStream_t)stream, kf::status_ptr());
+}
 
 // SwiGLU up-projection in one kernel: h[M, F] = silu(x Wg^T) * (x Wu^T), W = [Wg ; Wu] stacked as [2F][K] (K contiguous).
 // gu (optional, [M, 2F]) receives the bf16 pre-activations (gate | up) for the backward pass.  F must be a multiple of

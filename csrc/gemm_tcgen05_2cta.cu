@@ -105,11 +105,22 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
 // the peer), so every CTA's accumulator holds gate in columns 0..127 and up in columns 128..255 for the same 128
 // hidden units; the epilogue writes h = silu(gate) * up to C[M, F] and, when R is given, the pre-activations to
 // R[M, 2F] (gate | up) for the backward pass.
+//
+// SWIGLU == 2 (bf16, K-major operands only): rotary position embedding in the epilogue of a fused Q | K | V
+// projection.  Output columns [0, rope.cols) are heads of `rope.hd` columns that get rotated (pairs (i, i + hd/2)
+// with the angle of position `row % rope.S`), the remaining columns (V) are stored as they are.  The rotation is
+// applied to the fp32 accumulators, so q and k are rounded to bf16 once.
+struct RopeArgs {
+  const float* cosT;  // [S][hd / 2]
+  const float* sinT;
+  int S, cols, hd;
+};
+
 template <bool A_MN, bool B_MN, typename OutT, int SWIGLU = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ C, const OutT* __restrict__ R, int M, int N, int K, int ldc, int ldr,
-                          int accumulate, int* status) {
+                          int accumulate, int* status, RopeArgs rope) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -128,7 +139,7 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int m_blocks = (M + TILE_M - 1) / TILE_M;
-  const int n_blocks = SWIGLU ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
+  const int n_blocks = SWIGLU == 1 ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (K + BK - 1) / BK;
 
@@ -164,8 +175,8 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
         const int m0 = tc.m * TILE_M + int(rank) * CTA_M;
-        const int n0 = SWIGLU ? tc.n * HALF_N + int(rank) * N  // leader: gate rows, peer: the matching up rows
-                              : tc.n * TILE_N + int(rank) * HALF_N;
+        const int n0 = SWIGLU == 1 ? tc.n * HALF_N + int(rank) * N  // leader: gate rows, peer: the matching up rows
+                                   : tc.n * TILE_N + int(rank) * HALF_N;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -246,7 +257,48 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       tc_fence_after();
       const int row = tc.m * TILE_M + int(rank) * CTA_M + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TILE_N;
-      if constexpr (SWIGLU != 0) {
+      if constexpr (SWIGLU == 2) {
+        const int col0 = tc.n * TILE_N;
+        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(C) + size_t(row) * ldc + col0;
+        const int half_chunks = rope.hd >> 6;       // 32-column chunks in half a head
+        const int head_chunks = rope.hd >> 5;
+        const int pos = row % rope.S;
+        const float* cos_row = rope.cosT + size_t(pos) * (rope.hd >> 1);
+        const float* sin_row = rope.sinT + size_t(pos) * (rope.hd >> 1);
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          const int hc = c % head_chunks;           // chunk index inside its head
+          if (hc >= half_chunks) continue;          // second halves are written together with their partners
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_row + c * 32, lo);
+          tmem_ld_32x32(t_row + (c + half_chunks) * 32, hi);
+          tmem_ld_wait();
+          const int col = col0 + c * 32;
+          if (row < M && col < N) {
+            if (col < rope.cols) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                const float4 cs = *reinterpret_cast<const float4*>(cos_row + hc * 32 + v * 4);
+                const float4 sn = *reinterpret_cast<const float4*>(sin_row + hc * 32 + v * 4);
+                const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float a = __uint_as_float(lo[v * 4 + i]), b = __uint_as_float(hi[v * 4 + i]);
+                  lo[v * 4 + i] = __float_as_uint(a * cv[i] - b * sv[i]);
+                  hi[v * 4 + i] = __float_as_uint(b * cv[i] + a * sv[i]);
+                }
+              }
+            }
+            store_chunk<__nv_bfloat16>(c_row + c * 32, lo, 32, false, nullptr);
+            store_chunk<__nv_bfloat16>(c_row + (c + half_chunks) * 32, hi, 32, false, nullptr);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) arrive_on_cta(tempty_bar(acc), 0);
+        continue;
+      }
+      if constexpr (SWIGLU == 1) {
         const int h0 = tc.n * HALF_N;  // first hidden unit of this tile
         __nv_bfloat16* h_row = reinterpret_cast<__nv_bfloat16*>(C) + size_t(row) * ldc + h0;
         __nv_bfloat16* gu_row = R ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(R)) + size_t(row) * ldr + h0
@@ -325,7 +377,7 @@ static int launch(const void* A, const void* B, void* C, const void* R, int M, i
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<OutT*>(C),
                                                    reinterpret_cast<const OutT*>(R), M, N, K, ldc, ldr, accumulate,
-                                                   status);
+                                                   status, RopeArgs{nullptr, nullptr, 1, 0, 64});
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -349,7 +401,35 @@ int launch_gemm_swiglu_2cta(const void* A, const void* W, void* H, void* GU, int
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(H),
-                                                   reinterpret_cast<const __nv_bfloat16*>(GU), M, F, K, ldh, ldgu, 0, status);
+                                                   reinterpret_cast<const __nv_bfloat16*>(GU), M, F, K, ldh, ldgu, 0, status,
+                                                   RopeArgs{nullptr, nullptr, 1, 0, 64});
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// qkv[M, N] = x W^T with the rotary embedding applied to the first `rope_cols` output columns (heads of `hd` columns,
+// position = row % S).  N and rope_cols must be multiples of hd; hd in {64, 128, 256}; tables fp32 [S][hd / 2].
+int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                          const float* cosT, const float* sinT, int S, int rope_cols, int hd, int num_sms,
+                          cudaStream_t stream, int* status) {
+  if ((hd != 64 && hd != 128 && hd != 256) || N % hd || rope_cols % hd || rope_cols > N || S <= 0) return 6;
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, A, M, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = make_map_2d_bf16(&mb, W, N, K, ldw, BK, HALF_N);
+  if (rc) return 200 + rc;
+  auto kern = kf_gemm_bf16_tcgen05_2cta<false, false, __nv_bfloat16, 2>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C), nullptr, M, N, K, ldc, 0, 0,
+                                                   status, RopeArgs{cosT, sinT, S, rope_cols, hd});
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -49,6 +49,7 @@ def _declare(L: ctypes.CDLL) -> None:
     sigs = {
         "kf_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, i, i, vp],
         "kf_gemm_swiglu_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp],
+        "kf_gemm_rope_bf16": [vp, vp, vp, i, i, i, i, i, i, vp, vp, i, i, i, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
         "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
@@ -79,6 +80,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, i, vp],
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
+        "kf_attn_bwd_rope_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp, vp, vp],
         "kf_attn_bwd_dq_mode": [i],
         "kf_attn_fwd2_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
@@ -173,8 +175,13 @@ def gemm(
     out_dtype: torch.dtype | None = None,
     residual: torch.Tensor | None = None,
     mode: int | None = None,
+    rope: tuple | None = None,
 ) -> torch.Tensor:
     """out[M,N] = A * Bᵀ (+ out if ``accumulate``) (+ ``residual``) on the tcgen05 tensor cores.
+
+    ``rope = (cos, sin, seq_len, rope_cols, head_dim)``: rotary position embedding in the epilogue (fused Q | K | V
+    projection): the heads inside the first ``rope_cols`` output columns are rotated by the angle of position
+    ``row % seq_len``; ``cos`` / ``sin`` are fp32 (seq_len, head_dim / 2).  Needs K-major operands, bf16 output.
 
     ``mode``: None/0 = automatic, 1 = single-CTA 128x256 tiles, 2 = CTA pairs (cta_group::2) on 256x256 tiles.
 
@@ -198,6 +205,15 @@ def gemm(
         raise NativeKernelError(
             f"gemm operands must have 16-byte aligned bases and row pitches (lda={lda}, ldb={ldb}, ldc={ldc})"
         )
+    if rope is not None:
+        cos, sin, seq_len, rope_cols, hd = rope
+        assert a_kmajor and b_kmajor and not out_f32 and not accumulate and residual is None
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape[-1] == hd // 2 and cos.numel() >= seq_len * (hd // 2) and M % seq_len == 0
+        code = lib().kf_gemm_rope_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, cos.data_ptr(),
+                                       sin.data_ptr(), int(seq_len), int(rope_cols), int(hd), sm_count(), _stream())
+        _check(code, "kf_gemm_rope_bf16")
+        return out
     ldr = 0
     if residual is not None:
         assert residual.shape == (M, N) and residual.dtype == out.dtype and residual.stride(1) == 1
@@ -397,9 +413,10 @@ def gemm_fp8(a8: torch.Tensor, b8: torch.Tensor, sa: torch.Tensor, sb: torch.Ten
 
 # --------------------------------------------------------------------------- attention
 def attn_policy() -> str:
-    """``KF_ATTN``: "native" = tcgen05 kernels wherever they apply; "library" = never; "auto" (default) =
-    native for gradient-free attention (evaluation, generation), the library kernel inside training."""
-    return os.environ.get("KF_ATTN", "auto")
+    """``KF_ATTN``: "native" (default) = the tcgen05 kernels wherever they apply (training blocks included; shapes
+    they do not cover fall back to the library call); "library" = never."""
+    v = os.environ.get("KF_ATTN", "native")
+    return "native" if v == "auto" else v
 
 
 def _attn_rows_ok(t: torch.Tensor) -> bool:
@@ -624,9 +641,17 @@ def attn_bwd_dq_mode(mode: int) -> int:
     return int(lib().kf_attn_bwd_dq_mode(int(mode)))
 
 
-def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=None, dk=None, dv=None):
+def gemm_rope_supported(x2: torch.Tensor, w: torch.Tensor, hd: int) -> bool:
+    """The rotary epilogue lives in the CTA-pair kernel: bf16, head dim 64 / 128 / 256, whole heads per weight."""
+    return (getattr(lib(), "kf_gemm_rope_bf16", None) is not None and hd in (64, 128, 256) and w.shape[0] % hd == 0
+            and x2.dtype == torch.bfloat16 and x2.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=None, dk=None, dv=None, rope=None):
     """Gradients of ``attn_fwd``.  ``dq`` / ``dk`` / ``dv`` may be preallocated (strided) destinations, e.g. the
-    three head ranges of one fused projection gradient; otherwise contiguous tensors are returned."""
+    three head ranges of one fused projection gradient; otherwise contiguous tensors are returned.
+    ``rope = (cos, sin)`` (fp32 (S, 64)): dq and dk leave through the inverse rotary embedding, i.e. they are the
+    gradients of the un-rotated projections when q and k were rotated after the projection."""
     b, sq, h, hd = q.shape
     sk, hkv = k.shape[1], k.shape[2]
     if dout.stride(-1) != 1 or dout.stride(2) != hd or (b > 1 and dout.stride(0) != sq * dout.stride(1)):
@@ -639,13 +664,20 @@ def attn_bwd(dout, q, k, v, out, lse, causal: bool, doc_ids, scale: float, dq=No
     dsum = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
     dq_acc = torch.empty((b, sq, h, hd), dtype=torch.float32, device=q.device)
     doc = doc_ids.to(torch.int32).contiguous() if doc_ids is not None else None
+    cos = sin = None
+    if rope is not None:
+        cos, sin = rope
+        assert sq == sk and cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape[-1] == hd // 2 and cos.numel() >= sq * (hd // 2)
     _check(
-        lib().kf_attn_bwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                               dsum.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                               doc.data_ptr() if doc is not None else None, b, sq, sk, h, hkv, hd, q.stride(1),
-                               k.stride(1), v.stride(1), out.stride(1), dout.stride(1), dq.stride(1), dk.stride(1),
-                               dv.stride(1), float(scale), int(causal), _stream()),
-        "kf_attn_bwd_bf16",
+        lib().kf_attn_bwd_rope_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                    lse.data_ptr(), dsum.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                    dv.data_ptr(), doc.data_ptr() if doc is not None else None, b, sq, sk, h, hkv, hd,
+                                    q.stride(1), k.stride(1), v.stride(1), out.stride(1), dout.stride(1), dq.stride(1),
+                                    dk.stride(1), dv.stride(1), float(scale), int(causal),
+                                    cos.data_ptr() if cos is not None else None,
+                                    sin.data_ptr() if sin is not None else None, _stream()),
+        "kf_attn_bwd_rope_bf16",
     )
     return dq, dk, dv
 

@@ -1,7 +1,8 @@
 """One autograd node for a whole dense transformer block on the native kernels.
 
-Forward:  x -> RMSNorm -> fused QKV GEMM -> RoPE -> attention -> O GEMM -> +x
-            -> RMSNorm -> fused gate|up GEMM -> SwiGLU -> down GEMM -> +residual
+Forward:  x -> RMSNorm -> fused QKV GEMM (rotary embedding in its epilogue) -> tcgen05 flash attention
+            -> O GEMM (+x in its epilogue) -> RMSNorm -> fused gate|up GEMM (SwiGLU in its epilogue)
+            -> down GEMM (+residual in its epilogue)
 With ``recompute=True`` (full activation checkpointing) only the block input is kept; backward
 re-runs the forward *except the down projection* (its output is not needed for any gradient),
 which removes one of the four large GEMMs from the recomputation.  Without recomputation the
@@ -9,7 +10,14 @@ intermediates are kept and backward starts immediately.
 
 Backward is written out by hand: every weight-gradient GEMM writes (or accumulates) straight
 into the parameter's flat gradient buffer, the two residual-gradient additions are folded into
-the RMSNorm backward kernel, and no autograd graph is built for the block's interior.
+the RMSNorm backward kernel, and no autograd graph is built for the block's interior.  The
+attention backward writes dq | dk | dv into the three head ranges of ONE fused gradient buffer and
+applies the inverse rotary embedding on the way out (dq in its fp32 -> bf16 pass, dk in its
+epilogue), so neither a copy nor a separate rotary pass exists in either direction.
+
+``KF_AC_KEEP_ATTN=1`` additionally keeps each block's attention output and log-sum-exp (66 MB per
+block at the 8B shape) so that the recomputation skips the attention forward; the default keeps
+only the block input, which is what "full" checkpointing means in the reference.
 
 Semantics are those of kempnerforge/model/transformer.py:82-103 with the activation
 checkpointing of kempnerforge/distributed/parallel.py:90-122.
@@ -18,6 +26,7 @@ checkpointing of kempnerforge/distributed/parallel.py:90-122.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -66,7 +75,7 @@ def _norm_wgrad(weight, dw):
 def _attention_fwd(q, k, v, causal, scale, need_ctx: bool = True):
     """(out, ctx) with ctx holding what the backward needs (None when ``need_ctx`` is False: the
     first forward of a recomputed block only wants the output)."""
-    if kc.attn_policy() == "native" and kc.attn_supported(q, k, v, causal, needs_grad=need_ctx):
+    if kc.attn_policy() == "native" and kc.attn_supported(q, k, v, causal, needs_grad=True):
         out, lse = kc.attn_fwd(q, k, v, causal, None, scale)
         return out, ("native", lse)
     if not need_ctx:
@@ -90,6 +99,15 @@ def _attention_bwd(dout, q, k, v, out, actx, causal, scale):
     return torch.autograd.grad(o, (ql, kl, vl), dout)
 
 
+def _rope_fused(n1, w_qkv, cos, sin, s: int, hd: int) -> bool:
+    """The rotary epilogue of the CTA-pair GEMM applies: fp32 (S, hd / 2) tables, whole sequences per row block,
+    and a problem large enough for that kernel (small ones keep the separate in-place pass)."""
+    return (os.environ.get("KF_ROPE_EPILOGUE", "1") != "0" and cos.dtype == torch.float32 and cos.is_contiguous()
+            and sin.is_contiguous() and cos.dim() == 2 and cos.shape[0] >= s and cos.shape[1] == hd // 2
+            and n1.shape[0] % s == 0 and n1.shape[0] >= 256 and w_qkv.shape[0] % 256 == 0
+            and kc.gemm_rope_supported(n1, w_qkv, hd))
+
+
 class DenseBlockFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin, wn1, wq, wk, wv, wo, wn2, wg, wu, wd, eps, head_dim, recompute):
@@ -99,29 +117,43 @@ class DenseBlockFn(torch.autograd.Function):
             x2 = x2.contiguous()
         ctx.meta = (b, s, d, eps, head_dim, recompute)
         ctx.weights = (wn1, wq, wk, wv, wo, wn2, wg, wu, wd)
-        inter = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=True, keep=not recompute)
+        keep_attn = recompute and os.environ.get("KF_AC_KEEP_ATTN", "0") == "1"
+        inter = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=True, keep=not recompute,
+                                          keep_attn=keep_attn)
         y = inter.pop("y")
+        ctx.attn_saved = None
         if recompute:
             ctx.save_for_backward(x2, cos, sin)
             ctx.inter = None
+            if keep_attn and inter.get("actx") is not None and inter["actx"][0] == "native":
+                ctx.attn_saved = (inter["attn2"], inter["actx"])
         else:
             ctx.save_for_backward(x2, cos, sin)
             ctx.inter = inter
         return y.view(b, s, d)
 
     @staticmethod
-    def _run_forward(x2, cos, sin, weights, meta, need_output: bool, keep: bool) -> dict:
+    def _run_forward(x2, cos, sin, weights, meta, need_output: bool, keep: bool, keep_attn: bool = False,
+                     attn_saved=None) -> dict:
         wn1, wq, wk, wv, wo, wn2, wg, wu, wd = weights
         b, s, d, eps, hd, _ = meta
         h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
         n1, rstd1 = kc.rmsnorm_fwd(x2, wn1, eps)
-        qkv = kc.gemm(n1, kc.stack_rows([wq, wk, wv]))
-        qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
-        kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)  # in place: each element is read and written by one thread
+        w_qkv = kc.stack_rows([wq, wk, wv])
+        if _rope_fused(n1, w_qkv, cos, sin, s, hd):
+            qkv = kc.gemm(n1, w_qkv, rope=(cos, sin, s, (h + hkv) * hd, hd), mode=2)  # rotation in the GEMM epilogue
+            qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+        else:
+            qkv = kc.gemm(n1, w_qkv)
+            qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+            kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)  # in place: each element is read and written by one thread
         q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
         scale = 1.0 / math.sqrt(hd)
-        attn, actx = _attention_fwd(q, k, v, True, scale, need_ctx=keep)
-        attn2 = attn.reshape(b * s, h * hd)
+        if attn_saved is not None:       # kept from the first forward: the recomputation skips the attention kernel
+            attn2, actx = attn_saved
+        else:
+            attn, actx = _attention_fwd(q, k, v, True, scale, need_ctx=keep or keep_attn)
+            attn2 = attn.reshape(b * s, h * hd)
         h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
         n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)
         w_gu = kc.stack_rows([wg, wu])
@@ -137,6 +169,8 @@ class DenseBlockFn(torch.autograd.Function):
             out["y"] = y
         if keep:
             out.update(n1=n1, rstd1=rstd1, qkv4=qkv4, attn2=attn2, actx=actx, h1=h1, n2=n2, rstd2=rstd2, gu=gu, hmid=hmid)
+        elif keep_attn:
+            out.update(attn2=attn2, actx=actx)
         return out
 
     @staticmethod
@@ -146,7 +180,9 @@ class DenseBlockFn(torch.autograd.Function):
         wn1, wq, wk, wv, wo, wn2, wg, wu, wd = ctx.weights
         it = ctx.inter
         if it is None:
-            it = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=False, keep=True)
+            it = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=False, keep=True,
+                                           attn_saved=ctx.attn_saved)
+            ctx.attn_saved = None
         dy2 = dy.reshape(b * s, d)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
@@ -166,13 +202,22 @@ class DenseBlockFn(torch.autograd.Function):
         qkv4 = it["qkv4"]
         q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
         attn = it["attn2"].view(b, s, h, hd)
-        dq, dk, dv = _attention_bwd(dattn.view(b, s, h, hd), q, k, v, attn, it["actx"], True, 1.0 / math.sqrt(hd))
         dqkv4 = torch.empty_like(qkv4)
-        dqkv4[:, :, :h].copy_(dq)
-        dqkv4[:, :, h : h + hkv].copy_(dk)
-        dqkv4[:, :, h + hkv :].copy_(dv)
-        del dq, dk, dv
-        kc.rope(dqkv4, cos, sin, h + hkv, inverse=True, out=dqkv4)
+        if it["actx"][0] == "native":
+            # dq | dk | dv land in their head ranges of the fused gradient, already through the inverse rotation
+            fused_rope = hd == 128 and cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+            kc.attn_bwd(dattn.view(b, s, h, hd), q, k, v, attn, it["actx"][1], True, None, 1.0 / math.sqrt(hd),
+                        dq=dqkv4[:, :, :h], dk=dqkv4[:, :, h : h + hkv], dv=dqkv4[:, :, h + hkv :],
+                        rope=(cos, sin) if fused_rope else None)
+            if not fused_rope:
+                kc.rope(dqkv4, cos, sin, h + hkv, inverse=True, out=dqkv4)
+        else:
+            dq, dk, dv = _attention_bwd(dattn.view(b, s, h, hd), q, k, v, attn, it["actx"], True, 1.0 / math.sqrt(hd))
+            dqkv4[:, :, :h].copy_(dq)
+            dqkv4[:, :, h : h + hkv].copy_(dk)
+            dqkv4[:, :, h + hkv :].copy_(dv)
+            del dq, dk, dv
+            kc.rope(dqkv4, cos, sin, h + hkv, inverse=True, out=dqkv4)
         dqkv = dqkv4.view(b * s, (h + 2 * hkv) * hd)
         dn1 = kc.gemm(dqkv, kc.stack_rows([wq, wk, wv]), a_kmajor=True, b_kmajor=False)
         g_wq, g_wk, g_wv = _wgrad(dqkv, it["n1"], [wq, wk, wv])

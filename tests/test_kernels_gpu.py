@@ -794,3 +794,48 @@ def test_attention_forward_single_tile_kernel(native_lib, monkeypatch, shape, ca
     want = ref.attention(q.float(), k.float(), v.float(), causal=causal)
     assert native_lib.read_status() == 0
     assert (out.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("shape", [(2, 128, 4, 2, 128, 256), (1, 512, 8, 2, 128, 520), (2, 256, 4, 4, 64, 128)])
+def test_gemm_rope_epilogue_matches_projection_then_rotation(native_lib, shape):
+    """Fused Q | K | V projection with the rotary embedding in the GEMM epilogue against an fp32 product followed by
+    the reference rotation; the V columns must come out un-rotated."""
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hkv, hd, k = shape
+    n = (h + 2 * hkv) * hd
+    x, w = _rand(b * s, k), _rand(n, k) * 0.1
+    cos, sin = ref.rope_tables(hd, s, 500000.0, device=DEV)
+    cos, sin = cos[:s].contiguous(), sin[:s].contiguous()
+    got = native_lib.gemm(x, w, rope=(cos, sin, s, (h + hkv) * hd, hd), mode=2)
+    assert native_lib.read_status() == 0
+    full = (x.float() @ w.float().t()).view(b, s, h + 2 * hkv, hd)
+    want = torch.cat([ref.apply_rope(full[:, :, : h + hkv], cos, sin), full[:, :, h + hkv:]], dim=2).reshape(b * s, n)
+    _close(got, want, rtol=2e-2, atol=2e-2)
+    plain = native_lib.gemm(x, w, mode=2)
+    assert torch.equal(got.view(b, s, -1, hd)[:, :, h + hkv:], plain.view(b, s, -1, hd)[:, :, h + hkv:])
+
+
+@pytest.mark.parametrize("shape", [(2, 256, 4, 2), (1, 384, 4, 1), (2, 200, 2, 2)])
+def test_attention_backward_with_inverse_rotary_epilogue(native_lib, shape):
+    """dq / dk through the inverse rotary embedding inside the backward (dq in its fp32 -> bf16 pass, dk in the kernel
+    epilogue) against the plain backward followed by the separate inverse rotation; dv is unchanged."""
+    from kempnerforge_b200.ops import ref
+
+    b, s, h, hkv = shape
+    hd = 128
+    q, k, v = _attn_inputs(b, s, h, hkv, hd, seed=17)
+    dout = _rand(b, s, h, hd)
+    scale = 1.0 / math.sqrt(hd)
+    cos, sin = ref.rope_tables(hd, s, 500000.0, device=DEV)
+    cos, sin = cos[:s].contiguous(), sin[:s].contiguous()
+    out, lse = native_lib.attn_fwd(q, k, v, True, None, scale)
+    dqkv = torch.zeros(b, s, h + 2 * hkv, hd, device="cuda", dtype=torch.bfloat16)
+    native_lib.attn_bwd(dout, q, k, v, out, lse, True, None, scale, dq=dqkv[:, :, :h], dk=dqkv[:, :, h:h + hkv],
+                        dv=dqkv[:, :, h + hkv:], rope=(cos, sin))
+    assert native_lib.read_status() == 0
+    _, rq, rk, rv = _attn_reference_grads(q, k, v, dout, True)
+    want = torch.cat([ref.apply_rope(rq, cos, -sin), ref.apply_rope(rk, cos, -sin), rv], dim=2)
+    for name, lo, hi in (("dq", 0, h), ("dk", h, h + hkv), ("dv", h + hkv, h + 2 * hkv)):
+        rel = (dqkv[:, :, lo:hi].float() - want[:, :, lo:hi]).norm() / want[:, :, lo:hi].norm()
+        assert rel < 2e-2, (name, rel.item())
