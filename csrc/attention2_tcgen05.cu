@@ -16,6 +16,7 @@
 // Masks, lazy rescaling and outputs are those of the single-tile kernel in attention_tcgen05.cu, which remains the
 // path for short sequences.  Replaces F.scaled_dot_product_attention (kempnerforge/model/attention.py:227-231).
 #include "attention_common.cuh"
+#include <stdlib.h>
 
 namespace kf {
 namespace attn2 {
@@ -41,7 +42,9 @@ __device__ __forceinline__ void tile_group_sync(int tile) {
   asm volatile("bar.sync %0, 128;" ::"r"(tile + 1) : "memory");
 }
 
-template <int HD, bool CAUSAL, bool HAS_DOC>
+// POLY: how many of every 16 pairs of exponentials are evaluated by exp2_poly2 on the FMA pipe (0 = all on the
+// special-function unit).
+template <int HD, bool CAUSAL, bool HAS_DOC, int POLY>
 __global__ void __launch_bounds__(THREADS, 1)
 kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O,
@@ -307,9 +310,14 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int i = 0; i < 16; ++i) {
           const uint64_t x2 = ffma2(pack2(__uint_as_float(sv[c * 32 + 2 * i]), __uint_as_float(sv[c * 32 + 2 * i + 1])),
                                     scale2, neg_m2);
-          float x0, x1;
+          float x0, x1, e0, e1;
           unpack2(x2, x0, x1);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          if (POLY > 0 && ((i * POLY) & 15) < POLY) {
+            exp2_poly2(x0, x1, e0, e1);
+          } else {
+            e0 = fast_exp2(x0);
+            e1 = fast_exp2(x1);
+          }
           lsum[i & 3] = fadd2(lsum[i & 3], pack2(e0, e1));
           pk[i] = pack_bf16(e0, e1);
         }
@@ -362,10 +370,10 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 }
 
-template <int HD, bool CAUSAL, bool HAS_DOC>
+template <int HD, bool CAUSAL, bool HAS_DOC, int POLY = 0>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* LSE, const int* doc,
                   int B, int Sq, int Sk, int H, int Hkv, long long ldo, float scale, int* status, cudaStream_t stream) {
-  auto kern = kf_attn_fwd2_tcgen05<HD, CAUSAL, HAS_DOC>;
+  auto kern = kf_attn_fwd2_tcgen05<HD, CAUSAL, HAS_DOC, POLY>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<HD>::SMEM);
@@ -408,6 +416,26 @@ int kf_attn_fwd2_bf16(const void* q, const void* k, const void* v, void* o, void
   float* L = reinterpret_cast<float*>(lse);
   const int* D = reinterpret_cast<const int*>(doc);
 #define KF_ATTN2_LAUNCH(HD_, C_, D_) return launch<HD_, C_, D_>(mq, mk, mv, o, L, D, B, Sq, Sk, H, Hkv, ldo, scale, status, st)
+#define KF_ATTN2_POLY(C_, P_) return launch<128, C_, false, P_>(mq, mk, mv, o, L, D, B, Sq, Sk, H, Hkv, ldo, scale, status, st)
+  if (hd == 128 && !doc) {
+    // share of the exponentials on the FMA pipe (of 16): KF_ATTN_EXP_POLY = 0 (default), 4, 6 or 8.  On the 8B
+    // shape the variants measured 0.307 / 0.313 / 0.313 / 0.320 ms: the two-tile kernel is paced by the per-tile
+    // softmax -> MMA chain, not by the special-function unit, so the extra FMA-pipe instructions do not pay here.
+    static int poly = -1;
+    if (poly < 0) {
+      const char* e = getenv("KF_ATTN_EXP_POLY");
+      poly = e ? atoi(e) : 0;
+    }
+    if (causal) {
+      if (poly == 4) KF_ATTN2_POLY(true, 4);
+      if (poly == 6) KF_ATTN2_POLY(true, 6);
+      if (poly == 8) KF_ATTN2_POLY(true, 8);
+    } else {
+      if (poly == 4) KF_ATTN2_POLY(false, 4);
+      if (poly == 6) KF_ATTN2_POLY(false, 6);
+      if (poly == 8) KF_ATTN2_POLY(false, 8);
+    }
+  }
   if (hd == 128) {
     if (doc) { if (causal) KF_ATTN2_LAUNCH(128, true, true); else KF_ATTN2_LAUNCH(128, false, true); }
     if (causal) KF_ATTN2_LAUNCH(128, true, false); else KF_ATTN2_LAUNCH(128, false, false);
@@ -416,6 +444,7 @@ int kf_attn_fwd2_bf16(const void* q, const void* k, const void* v, void* o, void
     if (causal) KF_ATTN2_LAUNCH(64, true, false); else KF_ATTN2_LAUNCH(64, false, false);
   }
 #undef KF_ATTN2_LAUNCH
+#undef KF_ATTN2_POLY
 }
 
 }  // extern "C"

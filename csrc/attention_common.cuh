@@ -63,5 +63,28 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+// 2^x for two values on the FMA pipe instead of the special-function unit: x = j + f with j = round(x) and
+// f in [-0.5, 0.5], 2^f by a minimax cubic (relative error 7.5e-5, far below the bf16 rounding of the
+// probabilities), then j is added to the exponent field.  Inputs below -126 (masked scores are -inf) flush to ~0.
+// The special-function unit evaluates 16 exponentials per clock and SM, which is less than the tensor cores can
+// consume for a 128-wide head; moving a share of them here balances the two pipes.
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& e0, float& e1) {
+  constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const uint64_t x = pack2(x0, x1);
+  const uint64_t t = fadd2(x, pack2(MAGIC, MAGIC));
+  const uint64_t j = fadd2(t, pack2(-MAGIC, -MAGIC));
+  const uint64_t f = ffma2(j, pack2(-1.f, -1.f), x);
+  uint64_t p = ffma2(pack2(0.05517973f, 0.05517973f), f, pack2(0.24260947f, 0.24260947f));
+  p = ffma2(p, f, pack2(0.69325984f, 0.69325984f));
+  p = ffma2(p, f, pack2(0.99992818f, 0.99992818f));
+  float p0, p1, t0, t1;
+  unpack2(p, p0, p1);
+  unpack2(t, t0, t1);
+  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 }  // namespace attn
 }  // namespace kf
