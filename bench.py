@@ -74,6 +74,8 @@ def parse_args():
     ap.add_argument("--micro-batches", type=int, default=1, help="micro-batches per optimizer step (gradient accumulation)")
     ap.add_argument("--fp8", action="store_true", help="float8 Linear layers (tensorwise scaling)")
     ap.add_argument("--optimizer", default="adamw", choices=("adamw", "muon"))
+    ap.add_argument("--param-sharding", default="resident", choices=("auto", "resident", "sharded"),
+                    help="data-parallel memory plan (ours only): whole parameters on every rank, or ZeRO-3")
     return ap.parse_args()
 
 
@@ -194,7 +196,7 @@ def run_ours(args) -> dict:
                   "activation_checkpointing": "full", "compile_model": False, "grad_clip_norm": 1.0, "seed": 0},
         "optimizer": {"name": args.optimizer, "lr": 3e-4, "weight_decay": 0.1, "fused": True},
         "scheduler": {"name": "cosine", "warmup_steps": 10},
-        "distributed": mesh_dims(args, world)[0],
+        "distributed": {**mesh_dims(args, world)[0], "param_sharding": args.param_sharding},
         "metrics": {"log_interval": 1000},
         "data": {"pin_memory": True},
     })
@@ -255,9 +257,10 @@ def run_ours(args) -> dict:
         "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
         "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
                    "parallelism": mesh_label, "activation_checkpointing": "full",
-                   "optimizer": "adamw_fused" if args.optimizer == "adamw" else "muon (Newton-Schulz 5) + adamw",
-                   "micro_batches": args.micro_batches,
-                   "l2": "working set (>60 GB) far exceeds L2; no flush needed"},
+                   "optimizer": "adamw_fused" if args.optimizer == "adamw" else "muon (Newton-Schulz 5) + adamw"},
+        "notes": {"micro_batches": args.micro_batches, "l2": "working set (>60 GB) far exceeds L2; no flush needed",
+                  "param_sharding": type(trainer.engine).__name__ if trainer.engine is not None else None,
+                  "engine_memory_gb": (trainer.engine.memory_report() if hasattr(trainer.engine, "memory_report") else None)},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 12},
@@ -265,7 +268,15 @@ def run_ours(args) -> dict:
         "mfu_of_nominal_2250": mfu_nominal, "mfu_of_measured_cublas": mfu_measured,
         "loss": last["loss"] if last else None, "wall_s_timed": wall,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+        "device_mem_used_gb": device_mem_used_gb(torch),
     }
+
+
+def device_mem_used_gb(torch) -> float:
+    """Memory in use on this GPU as the driver sees it (total - free): includes symmetric-memory buffers, which the
+    caching allocator's statistics do not count."""
+    free, total = torch.cuda.mem_get_info()
+    return (total - free) / 2**30
 
 
 # --------------------------------------------------------------------------- reference framework
@@ -369,13 +380,14 @@ def run_reference(args) -> dict:
         "scaling": "weak", "vs_baseline": (value / base) if (base and args.model == "llama3_8b" and mesh_label == f"dp{world}") else None,
         "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "reference",
         "config": {"model": args.model, "global_batch": args.batch_size * n_batches, "seq_len": seq,
-                   "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused",
-                   "compile_model": not shape.get("num_experts"), "notes": notes},
+                   "parallelism": mesh_label, "activation_checkpointing": "full", "optimizer": "adamw_fused"},
+        "notes": {"compile_model": not shape.get("num_experts"), "remarks": notes},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": 0, "loss": last["loss"] if last else None, "wall_s_timed": wall,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+        "device_mem_used_gb": device_mem_used_gb(torch),
     }
 
 

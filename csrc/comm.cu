@@ -172,6 +172,109 @@ __global__ void kf_symm_gather(PeerPtrs bufs, void* mc_buf, int world, int rank,
   }
 }
 
+// ---- sharded parameters (every rank keeps 1/world of each parameter) ---------------------------------------
+// A unit's parameters are laid out one after another ("full layout"); parameter i occupies full[i] .. full[i] +
+// len[i] and is cut into `world` equal contiguous pieces; rank r keeps piece r of every parameter, packed in the
+// same order ("shard layout": the piece of parameter i starts at full[i] / world).  SegTable describes a subset
+// of the parameters: where the segment starts in the destination / source full-layout buffer (`full`), its total
+// length, and where its piece starts inside a rank's shard.  All values are multiples of 8 elements.
+constexpr int MAX_SEGS = 16;
+struct SegTable {
+  long long full[MAX_SEGS];
+  long long len[MAX_SEGS];
+  long long shard[MAX_SEGS];
+  long long vec_start[MAX_SEGS + 1];  // prefix sums of len / 8 (gather) or len / world / 8 (reduce)
+  int n;
+};
+
+__device__ __forceinline__ int seg_of(const SegTable& t, long long v) {
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < MAX_SEGS; ++i)
+    if (i < t.n && v >= t.vec_start[i]) s = i;
+  return s;
+}
+
+// All-gather of the listed parameters into a local full-layout buffer by plain peer loads (own piece: local loads).
+// Nothing waits for another GPU; the peers' shards must not change while the kernel runs.
+__global__ void __launch_bounds__(256)
+kf_symm_pull(PeerPtrs shards, int world, SegTable t, __nv_bfloat16* __restrict__ dst) {
+  const long long nvec = t.vec_start[t.n];
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const int s = seg_of(t, v);
+    const long long e = (v - t.vec_start[s]) * 8;   // element inside the parameter
+    const long long piece = t.len[s] / world;
+    const int owner = int(e / piece);
+    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[owner]) + t.shard[s] +
+                                                    (e - owner * piece));
+    *reinterpret_cast<uint4*>(dst + t.full[s] + e) = u;
+  }
+}
+
+// Reduce-scatter of full-layout gradient buffers into the shard layout: this rank sums ITS piece of every listed
+// parameter over all ranks' buffers (peer loads, fixed order, fp32), scales by 1 / world and writes (or adds to)
+// its gradient shard.  mc_grads != null: one multimem.ld_reduce through NVSwitch instead of `world` loads.
+__global__ void __launch_bounds__(512)
+kf_symm_rs_shard(PeerPtrs grads, const void* mc_grads, int world, int rank, SegTable t, float inv_world,
+                 __nv_bfloat16* __restrict__ shard_grad, int accumulate) {
+  const long long nvec = t.vec_start[t.n];
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const int s = seg_of(t, v);
+    const long long local = (v - t.vec_start[s]) * 8;        // element inside this rank's piece
+    const long long piece = t.len[s] / world;
+    const long long src = t.full[s] + rank * piece + local;  // element inside a full-layout buffer
+    float acc[8];
+    if (mc_grads) {
+      ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grads) + src, acc);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + src);
+        float2 f;
+        f = unpack_bf16(u.x); acc[0] += f.x; acc[1] += f.y;
+        f = unpack_bf16(u.y); acc[2] += f.x; acc[3] += f.y;
+        f = unpack_bf16(u.z); acc[4] += f.x; acc[5] += f.y;
+        f = unpack_bf16(u.w); acc[6] += f.x; acc[7] += f.y;
+      }
+    }
+    __nv_bfloat16* out = shard_grad + t.shard[s] + local;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= inv_world;
+    if (accumulate) {
+      const uint4 old = *reinterpret_cast<const uint4*>(out);
+      float2 f;
+      f = unpack_bf16(old.x); acc[0] += f.x; acc[1] += f.y;
+      f = unpack_bf16(old.y); acc[2] += f.x; acc[3] += f.y;
+      f = unpack_bf16(old.z); acc[4] += f.x; acc[5] += f.y;
+      f = unpack_bf16(old.w); acc[6] += f.x; acc[7] += f.y;
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]);
+    o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out) = o;
+  }
+}
+
+static inline int fill_seg_table(SegTable& t, int n, const long long* full, const long long* len, const long long* shard,
+                                 int world, bool per_piece) {
+  if (n < 1 || n > MAX_SEGS) return 1;
+  t.n = n;
+  long long acc = 0;
+  for (int i = 0; i < n; ++i) {
+    if ((full[i] & 7) || (shard[i] & 7) || (len[i] % (8LL * world))) return 2;
+    t.full[i] = full[i];
+    t.len[i] = len[i];
+    t.shard[i] = shard[i];
+    t.vec_start[i] = acc;
+    acc += (per_piece ? len[i] / world : len[i]) / 8;
+  }
+  for (int i = n; i <= MAX_SEGS; ++i) t.vec_start[i] = acc;
+  return 0;
+}
+
 static inline PeerPtrs make_ptrs(const long long* ptrs, int world) {
   PeerPtrs pp;
   for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
@@ -210,6 +313,40 @@ int kf_symm_adamw_bcast_bf16(const long long* peer_param_ptrs, void* mc_param, i
       make_ptrs(peer_param_ptrs, world), mc_param, world, rank, (const __nv_bfloat16*)grad, (__nv_bfloat16*)m,
       (__nv_bfloat16*)v, lo, n, n_decay_global, lr, b1, b2, eps, wd, bc1, bc2_sqrt, (const float*)grad_scale,
       (const int*)skip);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// dst[full[i] .. + len[i]) = parameter i assembled from every rank's piece at shard_ptrs[r] + shard[i].
+int kf_symm_pull_bf16(const long long* shard_ptrs, int world, int n_seg, const long long* full, const long long* len,
+                      const long long* shard, void* dst, int max_blocks, void* stream) {
+  using namespace kf;
+  if (world < 1 || world > MAX_PEERS) return 1;
+  SegTable t;
+  int rc = fill_seg_table(t, n_seg, full, len, shard, world, false);
+  if (rc) return 10 + rc;
+  const long long nvec = t.vec_start[t.n];
+  long long want = (nvec + 255) / 256;
+  int nb = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  kf_symm_pull<<<nb, 256, 0, (cudaStream_t)stream>>>(make_ptrs(shard_ptrs, world), world, t, (__nv_bfloat16*)dst);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// shard_grad[shard[i] .. + len[i] / world) (+)= mean over ranks of grad buffers [full[i] + rank * len[i] / world ..).
+int kf_symm_rs_shard_bf16(const long long* grad_ptrs, const void* mc_grads, int world, int rank, int n_seg,
+                          const long long* full, const long long* len, const long long* shard, void* shard_grad,
+                          int accumulate, int max_blocks, void* stream) {
+  using namespace kf;
+  if (world < 1 || world > MAX_PEERS) return 1;
+  SegTable t;
+  int rc = fill_seg_table(t, n_seg, full, len, shard, world, true);
+  if (rc) return 10 + rc;
+  const long long nvec = t.vec_start[t.n];
+  long long want = (nvec + 511) / 512;
+  int nb = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  kf_symm_rs_shard<<<nb, 512, 0, (cudaStream_t)stream>>>(make_ptrs(grad_ptrs, world), mc_grads, world, rank, t,
+                                                         1.f / world, (__nv_bfloat16*)shard_grad, accumulate);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

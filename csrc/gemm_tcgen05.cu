@@ -261,7 +261,31 @@ int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, i
                           cudaStream_t stream, int* status);
 }
 
+namespace kf2 {
+int launch_gemm_gather_2cta(int epi, const void* A, void* C, const void* R, int M, int N, int K, int lda, int ldc, int ldr,
+                            const long long* peers, int world, int rank, int n_seg, const long long* seg_rows,
+                            const long long* seg_src, void* stage, int* flags, const float* cosT, const float* sinT,
+                            int S, int rope_cols, int hd, int num_sms, cudaStream_t stream, int* status);
+}
+
 extern "C" {
+
+// GEMM whose weight operand is gathered from the data-parallel ranks' parameter shards by the same kernel
+// (sharded parameters: rank r keeps piece r of every weight).  out = x W^T with W = the row stack of `n_seg`
+// weights (seg_rows[i] rows of K elements); piece r of weight i is at shard_ptrs[r] + seg_src[i] (elements).
+// epi 0: (+ residual R); epi 1: SwiGLU over [gate ; up] (N = hidden size F, out = h, R = optional pre-activations
+// [M, 2F]); epi 2: rotary embedding on the first rope_cols columns.  `stage` (rows x K bf16) receives the assembled
+// operand and stays valid afterwards; `flags`: rows / 128 + 1 ints of scratch.  K % 128 == 0, rows % 128 == 0,
+// every piece a multiple of 16384 elements.
+int kf_gemm_gather_bf16(int epi, const void* x, void* out, const void* R, int M, int N, int K, int lda, int ldc, int ldr,
+                        const long long* shard_ptrs, int world, int rank, int n_seg, const long long* seg_rows,
+                        const long long* seg_src, void* stage, void* flags, const void* cosT, const void* sinT, int S,
+                        int rope_cols, int hd, int num_sms, void* stream) {
+  if ((lda & 7) || (ldc & 7) || (R && (ldr & 7))) return 5;
+  return kf2::launch_gemm_gather_2cta(epi, x, out, R, M, N, K, lda, ldc, ldr, shard_ptrs, world, rank, n_seg, seg_rows,
+                                      seg_src, stage, (int*)flags, (const float*)cosT, (const float*)sinT, S, rope_cols,
+                                      hd, num_sms, (cudaStream_t)stream, kf::status_ptr());
+}
 
 // Fused Q | K | V projection with the rotary embedding in the epilogue: out[M, N] = x W^T, then every head of `hd`
 // columns inside the first `rope_cols` columns is rotated by the angle of position (row % S); cos / sin are fp32

@@ -33,6 +33,7 @@ constexpr int A_BYTES = CTA_M * BK * 2;   // 16 KB
 constexpr int B_BYTES = HALF_N * BK * 2;  // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
+constexpr int THREADS_GATHER = 320;  // + four copy warps (6..9) in the weight-gathering variant
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
@@ -91,6 +92,34 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
 }
 
+// ---- weight-gathering variant (sharded data parallelism: every rank keeps 1/world of each weight's rows) ------
+// The B operand of the GEMM is a weight (or a row stack of weights: q | k | v, gate | up) that is NOT resident: each
+// of its segments is cut into `world` equal contiguous pieces, piece r living in rank r's parameter shard.  The
+// kernel's copy warps pull the pieces over NVLink (plain peer loads; the local piece by local loads) into a staging
+// copy of the operand in this GPU's memory, chunk by chunk in the order in which the tiles will consume them (own
+// rows first), and bump one counter per 128-row block; the TMA producer of a tile waits (bounded) for the counter
+// of the row block it is about to load, so the transfer of later rows overlaps the math on earlier ones.  Nothing
+// in here waits for another GPU: peers only have to keep their shards unchanged while the kernel runs.
+constexpr int GATHER_CHUNK_ELEMS = 16384;  // 32 KB per copy step of one CTA's copy warps
+constexpr int GATHER_MAX_SEG = 4;
+constexpr int GATHER_GROUP_N = 4;          // column tiles that share one sweep over the row tiles
+struct GatherArgs {
+  const __nv_bfloat16* peer[8];            // every rank's parameter shard (this unit)
+  __nv_bfloat16* stage;                    // local staging copy of the whole operand ([rows][K], rows contiguous)
+  int* flags;                              // [row blocks] counters + [1] work counter, zeroed before the launch
+  long long seg_dst[GATHER_MAX_SEG];       // first element of the segment inside the operand
+  long long seg_len[GATHER_MAX_SEG];       // elements of the segment (all ranks together)
+  long long seg_src[GATHER_MAX_SEG];       // first element of the segment's piece inside a rank's shard
+  int n_seg, world;
+  int chunks_per_rb;                       // chunks per 128-row block = K / 128
+  int total_chunks, row_blocks;
+  int n_tile_start;                        // rotation of the column-tile order: the tile that holds own rows
+};
+
+__device__ __forceinline__ void red_release_gpu_add(int* addr, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
 struct TileCoord {
   int m, n;
 };
@@ -116,11 +145,11 @@ struct RopeArgs {
   int S, cols, hd;
 };
 
-template <bool A_MN, bool B_MN, typename OutT, int SWIGLU = 0>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+template <bool A_MN, bool B_MN, typename OutT, int SWIGLU = 0, bool GATHER = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? THREADS_GATHER : THREADS, 1)
 kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ C, const OutT* __restrict__ R, int M, int N, int K, int ldc, int ldr,
-                          int accumulate, int* status, RopeArgs rope) {
+                          int accumulate, int* status, RopeArgs rope, const __grid_constant__ GatherArgs ga) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -142,6 +171,20 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
   const int n_blocks = SWIGLU == 1 ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (K + BK - 1) / BK;
+  // gathering variant: column tiles are the slow index (a weight row block is consumed completely soon after it
+  // arrived), rotated so that the tile holding this rank's own rows comes first
+  auto tile_at = [&](int t) {
+    TileCoord tc;
+    if constexpr (GATHER) {
+      int nr;
+      tilemath::raster(t, n_blocks, m_blocks, GATHER_GROUP_N, nr, tc.m);
+      tc.n = nr + ga.n_tile_start;
+      if (tc.n >= n_blocks) tc.n -= n_blocks;
+    } else {
+      tc = tile_coord(t, m_blocks, n_blocks);
+    }
+    return tc;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -173,10 +216,17 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       int it = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+        const TileCoord tc = tile_at(t);
         const int m0 = tc.m * TILE_M + int(rank) * CTA_M;
         const int n0 = SWIGLU == 1 ? tc.n * HALF_N + int(rank) * N  // leader: gate rows, peer: the matching up rows
                                    : tc.n * TILE_N + int(rank) * HALF_N;
+        if constexpr (GATHER) {
+          // the 128 weight rows this CTA loads must have landed in the staging copy
+          if (n0 < N * (SWIGLU == 1 ? 2 : 1)) {
+            if (!flag_wait_ge(ga.flags + n0 / HALF_N, ga.chunks_per_rb, status)) { ok = false; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> this thread's TMA reads
+          }
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -244,13 +294,13 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
                    : "memory");
       mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     const int quarter = warp & 3;
     int tile_iter = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_iter) {
-      const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+      const TileCoord tc = tile_at(t);
       const int acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1;
       if (!mbar_wait(tfull_bar(acc), acc_ph, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
@@ -348,6 +398,59 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
     }
   }
 
+  else if constexpr (GATHER) {
+    // ------------------------------------------------------------ copy warps 6..9: pull weight chunks into the staging copy
+    const int c_tid = threadIdx.x - 192;  // 0..127
+    volatile int* claim = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot - smem_u32(smem_raw)) + 8);
+    int* work = ga.flags + ga.row_blocks;
+    const int f_blocks = SWIGLU == 1 ? N / HALF_N : 0;  // row blocks of the gate half (SwiGLU operand: [gate ; up])
+    while (true) {
+      if (c_tid == 0) *claim = atomicAdd(work, 1);
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      const int c = *claim;
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (c >= ga.total_chunks) break;
+      // claimed position -> chunk, in the order in which the tiles consume the row blocks
+      int rb, j;
+      if constexpr (SWIGLU == 1) {
+        const int per_tile = 2 * ga.chunks_per_rb;
+        int n = c / per_tile + ga.n_tile_start;
+        if (n >= f_blocks) n -= f_blocks;
+        const int rem = c % per_tile;
+        rb = n + (rem / ga.chunks_per_rb) * f_blocks;
+        j = rem % ga.chunks_per_rb;
+      } else {
+        int q = c + 2 * ga.n_tile_start * ga.chunks_per_rb;
+        if (q >= ga.total_chunks) q -= ga.total_chunks;
+        rb = q / ga.chunks_per_rb;
+        j = q - rb * ga.chunks_per_rb;
+      }
+      const long long d = (long long)(rb * ga.chunks_per_rb + j) * GATHER_CHUNK_ELEMS;  // element inside the operand
+      int sg = 0;
+#pragma unroll
+      for (int i = 1; i < GATHER_MAX_SEG; ++i)
+        if (i < ga.n_seg && d >= ga.seg_dst[i]) sg = i;
+      const long long in_seg = d - ga.seg_dst[sg];
+      const long long piece = ga.seg_len[sg] / ga.world;
+      const int owner = int(in_seg / piece);
+      const __nv_bfloat16* src = ga.peer[owner] + ga.seg_src[sg] + (in_seg - owner * piece);
+      __nv_bfloat16* dst = ga.stage + d;
+      // 2048 vectors of 16 bytes over 128 threads: eight loads in flight per thread before the first store
+      constexpr int UNROLL = 8;
+#pragma unroll 1
+      for (int i0 = c_tid; i0 < GATHER_CHUNK_ELEMS / 8; i0 += 128 * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) v[u] = *reinterpret_cast<const uint4*>(src + size_t(i0 + u * 128) * 8);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) *reinterpret_cast<uint4*>(dst + size_t(i0 + u * 128) * 8) = v[u];
+      }
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (c_tid == 0) red_release_gpu_add(ga.flags + rb, 1);
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's shared memory / tensor memory stay valid until both CTAs are done
@@ -377,7 +480,7 @@ static int launch(const void* A, const void* B, void* C, const void* R, int M, i
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<OutT*>(C),
                                                    reinterpret_cast<const OutT*>(R), M, N, K, ldc, ldr, accumulate,
-                                                   status, RopeArgs{nullptr, nullptr, 1, 0, 64});
+                                                   status, RopeArgs{nullptr, nullptr, 1, 0, 64}, GatherArgs{});
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -402,7 +505,7 @@ int launch_gemm_swiglu_2cta(const void* A, const void* W, void* H, void* GU, int
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(H),
                                                    reinterpret_cast<const __nv_bfloat16*>(GU), M, F, K, ldh, ldgu, 0, status,
-                                                   RopeArgs{nullptr, nullptr, 1, 0, 64});
+                                                   RopeArgs{nullptr, nullptr, 1, 0, 64}, GatherArgs{});
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -429,7 +532,70 @@ int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, i
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C), nullptr, M, N, K, ldc, 0, 0,
-                                                   status, RopeArgs{cosT, sinT, S, rope_cols, hd});
+                                                   status, RopeArgs{cosT, sinT, S, rope_cols, hd}, GatherArgs{});
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// Weight-gathering GEMM (see GatherArgs).  epi: 0 = C = A W^T (+ R), 1 = SwiGLU (W = [gate ; up], C = h, R = optional
+// pre-activations), 2 = rotary epilogue.  W is described by `n_seg` segments (seg_rows[i] rows of K elements each,
+// stacked in this order); segment i's piece of rank r is seg_rows[i] * K / world contiguous elements at
+// peers[r] + seg_src[i].  `stage` receives the whole operand; `flags` needs rows / 128 + 1 ints.
+int launch_gemm_gather_2cta(int epi, const void* A, void* C, const void* R, int M, int N, int K, int lda, int ldc, int ldr,
+                            const long long* peers, int world, int rank, int n_seg, const long long* seg_rows,
+                            const long long* seg_src, void* stage, int* flags, const float* cosT, const float* sinT,
+                            int S, int rope_cols, int hd, int num_sms, cudaStream_t stream, int* status) {
+  if (world < 1 || world > 8 || n_seg < 1 || n_seg > GATHER_MAX_SEG || (K % 128)) return 6;
+  GatherArgs ga{};
+  long long rows = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    ga.seg_dst[i] = rows * K;
+    ga.seg_len[i] = seg_rows[i] * K;
+    ga.seg_src[i] = seg_src[i];
+    if ((ga.seg_len[i] % world) || ((ga.seg_len[i] / world) % GATHER_CHUNK_ELEMS) || (seg_src[i] & 7)) return 7;
+    rows += seg_rows[i];
+  }
+  const long long want_rows = epi == 1 ? 2LL * N : N;
+  if (rows != want_rows || (rows % HALF_N)) return 8;
+  if (epi == 1 && (n_seg != 2 || seg_rows[0] != N)) return 8;
+  for (int r = 0; r < 8; ++r) ga.peer[r] = r < world ? reinterpret_cast<const __nv_bfloat16*>(peers[r]) : nullptr;
+  ga.stage = reinterpret_cast<__nv_bfloat16*>(stage);
+  ga.flags = flags;
+  ga.n_seg = n_seg;
+  ga.world = world;
+  ga.chunks_per_rb = K / 128;
+  ga.row_blocks = int(rows / HALF_N);
+  ga.total_chunks = ga.row_blocks * ga.chunks_per_rb;
+  const long long own_row = seg_rows[0] / world * rank;
+  ga.n_tile_start = int(own_row / (epi == 1 ? HALF_N : TILE_N));
+  cudaError_t me = cudaMemsetAsync(flags, 0, sizeof(int) * (ga.row_blocks + 1), stream);
+  if (me != cudaSuccess) return 350 + (int)me;
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, A, M, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = make_map_2d_bf16(&mb, stage, rows, K, K, BK, HALF_N);
+  if (rc) return 200 + rc;
+  const int n_tiles_n = epi == 1 ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * n_tiles_n;
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  RopeArgs ra{cosT, sinT, S > 0 ? S : 1, rope_cols, hd > 0 ? hd : 64};
+  if (epi == 2 && ((hd != 64 && hd != 128 && hd != 256) || N % hd || rope_cols % hd || rope_cols > N || S <= 0)) return 6;
+#define KF2_GATHER_LAUNCH(EPI_)                                                                                      \
+  {                                                                                                                  \
+    auto kern = kf_gemm_bf16_tcgen05_2cta<false, false, __nv_bfloat16, EPI_, true>;                                  \
+    static bool attr_set = false;                                                                                    \
+    if (!attr_set) {                                                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);      \
+      if (e != cudaSuccess) return 300 + (int)e;                                                                     \
+      attr_set = true;                                                                                               \
+    }                                                                                                                \
+    kern<<<pairs * 2, THREADS_GATHER, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),             \
+                                                            reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr, \
+                                                            0, status, ra, ga);                                      \
+  }
+  if (epi == 0) KF2_GATHER_LAUNCH(0) else if (epi == 1) KF2_GATHER_LAUNCH(1) else if (epi == 2) KF2_GATHER_LAUNCH(2) else return 6;
+#undef KF2_GATHER_LAUNCH
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -101,6 +101,22 @@ def model_state_dict(model) -> dict[str, torch.Tensor]:
     if engine is not None and hasattr(engine, "wait_all"):
         engine.wait_all()  # parameters being published asynchronously must have landed
     sd = dict(_unwrap(model).state_dict())
+    if engine is not None and getattr(engine, "sharded_groups", None):
+        # ZeRO-3 units: ``state_dict`` sees staging memory; the truth is in the shards
+        row_mesh = _dp_row_mesh(model, engine)
+        names = {id(p): n for n, p in _unwrap(model).named_parameters(remove_duplicate=False)}
+        for g in engine.sharded_groups:
+            for i, p in enumerate(g.params):
+                name = names[id(p)]
+                if name not in sd:
+                    continue
+                if row_mesh is not None and _row_shardable(g, i, p):
+                    from torch.distributed.tensor import DTensor, Shard
+
+                    local = g.piece_of(p).view(p.shape[0] // g.world, *p.shape[1:])
+                    sd[name] = DTensor.from_local(local, row_mesh, [Shard(0)], run_check=False)
+                else:
+                    sd[name] = engine.full_parameter(p)
     meshes = _shard_meshes(model)
     if meshes:
         for name, spec in _shard_specs(model).items():
@@ -109,7 +125,30 @@ def model_state_dict(model) -> dict[str, torch.Tensor]:
     return sd
 
 
+def _row_shardable(g, i: int, p) -> bool:
+    """The piece of parameter i of a sharded unit is exactly rows [r * R / N, (r + 1) * R / N) of the parameter."""
+    return p.dim() >= 1 and g.padded[i] == p.numel() and p.shape[0] % g.world == 0
+
+
 def load_model_state_dict(model, loaded: dict[str, Any]) -> None:
+    engine = getattr(_unwrap(model), "_kf_engine", None)
+    if engine is not None and getattr(engine, "sharded_groups", None):
+        loaded = dict(loaded)
+        names = {id(p): n for n, p in _unwrap(model).named_parameters(remove_duplicate=False)}
+        for g in engine.sharded_groups:
+            for i, p in enumerate(g.params):
+                v = loaded.pop(names[id(p)], None)
+                if v is None:
+                    continue
+                if hasattr(v, "to_local") and _row_shardable(g, i, p):
+                    g.piece_of(p).copy_(v.to_local().reshape(-1))
+                else:
+                    engine.load_full_parameter(p, v.full_tensor() if hasattr(v, "full_tensor") else v)
+            g.valid = set()
+        engine._stage_owner = None
+        if not engine.shared_staging:
+            for g in engine.sharded_groups:
+                engine.acquire(g, everything=True)
     _unwrap(model).load_state_dict({k: to_local(v) for k, v in loaded.items()}, strict=False)
 
 
@@ -153,6 +192,24 @@ def optimizer_state_dict(model, optimizer) -> dict[str, Any]:
         flat_groups = getattr(opt, "_flat_groups", None) or []
         flat_param_ids = set()
         for fg in flat_groups:
+            if getattr(fg, "sharded", False):
+                for i, p in enumerate(fg.params):
+                    flat_param_ids.add(id(p))
+                    lo, hi = fg.offsets[i] // fg.world, (fg.offsets[i] + fg.padded[i]) // fg.world
+                    entry = {"step": fg.step_tensor.detach().clone().cpu()}
+                    for key, buf in (("exp_avg", fg.exp_avg), ("exp_avg_sq", fg.exp_avg_sq)):
+                        piece = buf[lo:hi]
+                        if row_mesh is not None and _row_shardable(fg, i, p):
+                            from torch.distributed.tensor import DTensor, Shard
+
+                            entry[key] = DTensor.from_local(piece.view(p.shape[0] // fg.world, *p.shape[1:]), row_mesh,
+                                                            [Shard(0)], run_check=False)
+                        else:
+                            full = torch.empty(fg.padded[i], dtype=buf.dtype, device=buf.device)
+                            dist.all_gather_into_tensor(full, piece.contiguous(), group=engine.pg)
+                            entry[key] = full[: p.numel()].view(p.shape).clone()
+                    state[fqn_of[id(p)]] = entry
+                continue
             if engine is not None and engine.world > 1:
                 m_full, v_full = engine.full_optimizer_state(fg)
             else:
@@ -208,7 +265,15 @@ def _whole(v, model_sharded: bool):
 def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
     """Inverse of ``optimizer_state_dict`` for tensors that were loaded in place (flat views) or into copies."""
     specs = _shard_specs(model)
-    loaded = {**loaded, "state": {fqn: {k: _whole(v, fqn in specs) for k, v in entry.items()}
+    # moments of ZeRO-3 units stay row shards (the local rows go straight into the shard-layout buffers)
+    keep_rows = set()
+    eng0 = getattr(_unwrap(model), "_kf_engine", None)
+    if eng0 is not None and getattr(eng0, "sharded_groups", None):
+        fq = _param_fqns(model)
+        keep_rows = {fq[id(p)] for g in eng0.sharded_groups for i, p in enumerate(g.params) if _row_shardable(g, i, p)}
+    loaded = {**loaded, "state": {fqn: {k: (to_local(v) if fqn in keep_rows and k in ("exp_avg", "exp_avg_sq") and
+                                            hasattr(v, "to_local") else _whole(v, fqn in specs))
+                                        for k, v in entry.items()}
                                   for fqn, entry in loaded["state"].items()}}
     name_to_param = dict(_unwrap(model).named_parameters(remove_duplicate=False))
     engine = getattr(_unwrap(model), "_kf_engine", None)
@@ -216,6 +281,29 @@ def load_optimizer_state_dict(model, optimizer, loaded: dict[str, Any]) -> None:
     handled = set()
     for opt in opts:
         for fg in getattr(opt, "_flat_groups", None) or []:
+            if getattr(fg, "sharded", False):
+                fqn_of = _param_fqns(model)
+                step = None
+                for i, p in enumerate(fg.params):
+                    entry = loaded["state"].get(fqn_of[id(p)])
+                    handled.add(fqn_of[id(p)])
+                    if entry is None:
+                        continue
+                    piece = fg.padded[i] // fg.world
+                    lo = fg.offsets[i] // fg.world
+                    for key, buf in (("exp_avg", fg.exp_avg), ("exp_avg_sq", fg.exp_avg_sq)):
+                        flat = entry[key].reshape(-1)
+                        if flat.numel() == piece and piece != p.numel():   # this rank's rows of a row-sharded moment
+                            buf[lo : lo + piece].copy_(flat)
+                            continue
+                        a, b = fg.rank * piece, min((fg.rank + 1) * piece, flat.numel())   # a whole tensor
+                        buf[lo : lo + piece].zero_()
+                        if b > a:
+                            buf[lo : lo + b - a].copy_(flat[a:b])
+                    step = entry.get("step", step)
+                if step is not None:
+                    fg.load_step(int(float(step)))
+                continue
             full_m = torch.zeros(fg.numel, dtype=fg.exp_avg.dtype, device=fg.exp_avg.device)
             full_v = torch.zeros_like(full_m)
             step = None

@@ -312,6 +312,10 @@ class DistributedConfig:
     # extension: EP ranks live inside the data-parallel dimension (each EP rank
     # routes its own tokens) instead of multiplying the world size.
     ep_in_dp: bool = False
+    # extension: memory plan of the data-parallel engine.  "resident" keeps whole parameters and gradients on every
+    # rank (optimizer state sharded); "sharded" is ZeRO-3 (1/N of parameters, gradients and state per rank, weights
+    # gathered inside the GEMMs that read them); "auto" picks "sharded" only when "resident" would not fit.
+    param_sharding: str = "auto"
 
     def __post_init__(self) -> None:
         _require(self.dp_shard == -1 or self.dp_shard > 0, "dp_shard must be -1 (auto) or positive")

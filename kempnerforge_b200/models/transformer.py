@@ -96,6 +96,12 @@ class TransformerBlock(nn.Module):
 
             if F.use_native(x) and fused_block.dense_block_supported(self, x, kv_cache, doc_ids, key_padding_mask):
                 return fused_block.dense_block(self, x, rope_cos, rope_sin)
+        unit = getattr(self.attention.q_proj.weight, "_kf_flat", None)
+        if unit is not None and getattr(unit, "sharded", False) and unit.engine.shared_staging:
+            if torch.is_grad_enabled() and x.requires_grad:
+                raise RuntimeError("sharded parameters (ZeRO-3) train through the fused dense block only; this call "
+                                   "(masks, caches, hooks or an unsupported dtype) needs the resident engine")
+            unit.engine.acquire(unit, everything=True)  # gradient-free paths read whole parameters
         if self.ac_mode == "full" and self.training and torch.is_grad_enabled() and kv_cache is None:
             return checkpoint(
                 self._body, x, rope_cos, rope_sin, None, doc_ids, key_padding_mask, use_reentrant=False,

@@ -87,6 +87,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
         "kf_symm_adamw_bcast_bf16": [vp, vp, i, i, vp, vp, vp, ll, ll, ll, f, f, f, f, f, f, f, vp, vp, i, vp],
         "kf_symm_gather_bf16": [vp, vp, i, i, ll, ll, i, vp],
+        "kf_symm_pull_bf16": [vp, i, i, vp, vp, vp, vp, i, vp],
+        "kf_symm_rs_shard_bf16": [vp, vp, i, i, i, vp, vp, vp, vp, i, i, vp],
+        "kf_gemm_gather_bf16": [i, vp, vp, vp, i, i, i, i, i, i, vp, i, i, i, vp, vp, vp, vp, vp, vp, i, i, i, i, vp],
         "kf_read_status": [],
         "kf_clear_status": [],
         "kf_status_device_ptr": [],
@@ -719,3 +722,60 @@ def symm_adamw_bcast(param_buf, grad_shard, m, v, lo: int, n: int, n_decay_globa
 def symm_gather(buf, lo: int, n: int, max_blocks: int = 592) -> None:
     _check(lib().kf_symm_gather_bf16(buf.peer_ptrs, buf.multicast_ptr, buf.world, buf.rank, lo, n, max_blocks, _stream()),
            "kf_symm_gather_bf16")
+
+
+# --------------------------------------------------------------------------- sharded parameters (ZeRO-3)
+def _ll_array(values):
+    return (ctypes.c_longlong * len(values))(*[int(v) for v in values])
+
+
+def symm_pull(shard_buf, full_offsets, lengths, shard_offsets, dst: torch.Tensor, max_blocks: int = 592) -> None:
+    """All-gather of up to 16 parameters of a sharded unit into the full-layout buffer ``dst``: parameter i
+    (``lengths[i]`` elements, cut into ``world`` equal pieces) is assembled at ``dst[full_offsets[i]:]`` from every
+    rank's piece at ``shard_offsets[i]`` of its shard (``shard_buf``: the symmetric shard buffer)."""
+    _check(lib().kf_symm_pull_bf16(shard_buf.peer_ptrs, shard_buf.world, len(lengths), _ll_array(full_offsets),
+                                   _ll_array(lengths), _ll_array(shard_offsets), dst.data_ptr(), max_blocks, _stream()),
+           "kf_symm_pull_bf16")
+
+
+def symm_rs_shard(grad_buf, full_offsets, lengths, shard_offsets, shard_grad: torch.Tensor, accumulate: bool,
+                  max_blocks: int | None = None) -> None:
+    """Reduce-scatter of full-layout gradient staging buffers (``grad_buf``: symmetric) into this rank's gradient
+    shard: the mean over ranks of this rank's piece of every listed parameter is written (or added) to
+    ``shard_grad[shard_offsets[i]:]``."""
+    max_blocks = SYMM_RS_BLOCKS if max_blocks is None else max_blocks
+    _check(lib().kf_symm_rs_shard_bf16(grad_buf.peer_ptrs, grad_buf.multicast_ptr, grad_buf.world, grad_buf.rank,
+                                       len(lengths), _ll_array(full_offsets), _ll_array(lengths), _ll_array(shard_offsets),
+                                       shard_grad.data_ptr(), int(accumulate), max_blocks, _stream()),
+           "kf_symm_rs_shard_bf16")
+
+
+def gemm_gather(x2: torch.Tensor, plan: dict, n: int, *, epi: int = 0, residual: torch.Tensor | None = None,
+                rope: tuple | None = None, want_gu: bool = True):
+    """GEMM whose weight operand is gathered from the data-parallel ranks' parameter shards inside the kernel.
+
+    ``plan`` comes from ``ShardedDataParallelEngine.gather_plan`` (shard buffer, segment rows / shard offsets, the
+    staging view that receives the operand, scratch flags).  ``epi`` 0: ``x W^T (+ residual)`` -> (M, n);
+    1: SwiGLU over W = [gate ; up] with hidden size ``n`` -> (h (M, n), gu (M, 2n) or None); 2: rotary epilogue
+    (``rope`` as in :func:`gemm`) -> (M, n).  Afterwards the staging view holds the whole weight."""
+    m, k = x2.shape
+    symm = plan["symm"]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x2.device)
+    r_ptr, ldr, gu = None, 0, None
+    if epi == 1 and want_gu:
+        gu = torch.empty((m, 2 * n), dtype=torch.bfloat16, device=x2.device)
+        r_ptr, ldr = gu.data_ptr(), 2 * n
+    elif epi == 0 and residual is not None:
+        assert residual.shape == (m, n) and residual.stride(1) == 1
+        r_ptr, ldr = residual.data_ptr(), residual.stride(0)
+    cos_p = sin_p = None
+    s_len = rope_cols = hd = 0
+    if epi == 2:
+        cos, sin, s_len, rope_cols, hd = rope
+        cos_p, sin_p = cos.data_ptr(), sin.data_ptr()
+    code = lib().kf_gemm_gather_bf16(
+        epi, x2.data_ptr(), out.data_ptr(), r_ptr, m, n, k, x2.stride(0), n, ldr, symm.peer_ptrs, symm.world, symm.rank,
+        len(plan["seg_rows"]), _ll_array(plan["seg_rows"]), _ll_array(plan["seg_src"]), plan["stage"].data_ptr(),
+        plan["flags"].data_ptr(), cos_p, sin_p, int(s_len), int(rope_cols), int(hd), sm_count(), _stream())
+    _check(code, "kf_gemm_gather_bf16")
+    return (out, gu) if epi == 1 else out

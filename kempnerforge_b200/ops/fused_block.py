@@ -99,6 +99,30 @@ def _attention_bwd(dout, q, k, v, out, actx, causal, scale):
     return torch.autograd.grad(o, (ql, kl, vl), dout)
 
 
+def _sharded_unit(w):
+    """The sharded flat unit (ZeRO-3) that owns parameter ``w``, or None."""
+    g = getattr(w, "_kf_flat", None)
+    return g if g is not None and getattr(g, "sharded", False) else None
+
+
+def _gather_plan(g, key: str, weights, x2):
+    """Plan for the weight-gathering GEMM when the unit is sharded, the weights are not yet in the staging buffer
+    and the shapes fit the kernel; otherwise the weights are made valid by a plain pull and None is returned."""
+    if g is None:
+        return None
+    eng = g.engine
+    if eng._stage_owner is not g:
+        eng.acquire(g)
+    if key in g.valid or "all" in g.valid:
+        return None
+    plan = eng.gather_plan(g, weights, x2.shape[1]) if (x2.shape[0] >= 256 and x2.stride(0) % 8 == 0) else None
+    if plan is None:
+        eng.ensure(g, key, weights)
+        return None
+    g.valid.add(key)  # the kernel launched next leaves the whole operand in the staging buffer
+    return plan
+
+
 def _rope_fused(n1, w_qkv, cos, sin, s: int, hd: int) -> bool:
     """The rotary epilogue of the CTA-pair GEMM applies: fp32 (S, hd / 2) tables, whole sequences per row block,
     and a problem large enough for that kernel (small ones keep the separate in-place pass)."""
@@ -138,9 +162,20 @@ class DenseBlockFn(torch.autograd.Function):
         wn1, wq, wk, wv, wo, wn2, wg, wu, wd = weights
         b, s, d, eps, hd, _ = meta
         h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        unit = _sharded_unit(wq)
+        if unit is not None and unit.engine._stage_owner is not unit:
+            unit.engine.acquire(unit)   # norm weights are pulled here; matrices by the GEMMs that read them
         n1, rstd1 = kc.rmsnorm_fwd(x2, wn1, eps)
         w_qkv = kc.stack_rows([wq, wk, wv])
-        if _rope_fused(n1, w_qkv, cos, sin, s, hd):
+        rope_ok = _rope_fused(n1, w_qkv, cos, sin, s, hd)
+        plan = _gather_plan(unit, "qkv", [wq, wk, wv], n1)
+        if plan is not None:
+            qkv = kc.gemm_gather(n1, plan, w_qkv.shape[0], epi=2 if rope_ok else 0,
+                                 rope=(cos, sin, s, (h + hkv) * hd, hd) if rope_ok else None)
+            qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+            if not rope_ok:
+                kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)
+        elif rope_ok:
             qkv = kc.gemm(n1, w_qkv, rope=(cos, sin, s, (h + hkv) * hd, hd), mode=2)  # rotation in the GEMM epilogue
             qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
         else:
@@ -154,10 +189,19 @@ class DenseBlockFn(torch.autograd.Function):
         else:
             attn, actx = _attention_fwd(q, k, v, True, scale, need_ctx=keep or keep_attn)
             attn2 = attn.reshape(b * s, h * hd)
-        h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
+        plan = _gather_plan(unit, "o", [wo], attn2)
+        if plan is not None:
+            h1 = kc.gemm_gather(attn2, plan, wo.shape[0], epi=0, residual=x2)
+        else:
+            h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
         n2, rstd2 = kc.rmsnorm_fwd(h1, wn2, eps)
         w_gu = kc.stack_rows([wg, wu])
-        if kc.gemm_swiglu_supported(n2, w_gu):
+        plan = _gather_plan(unit, "gu", [wg, wu], n2) if kc.gemm_swiglu_supported(n2, w_gu) else None
+        if plan is None and unit is not None:
+            unit.engine.ensure(unit, "gu", [wg, wu])
+        if plan is not None:
+            hmid, gu = kc.gemm_gather(n2, plan, wg.shape[0], epi=1, want_gu=keep)
+        elif kc.gemm_swiglu_supported(n2, w_gu):
             # activation in the GEMM epilogue; the pre-activations are written only when the backward will need them
             hmid, gu = kc.gemm_swiglu(n2, w_gu, want_gu=keep)
         else:
@@ -165,7 +209,11 @@ class DenseBlockFn(torch.autograd.Function):
             hmid = kc.swiglu_fwd(gu)
         out = {}
         if need_output:
-            y = kc.gemm(hmid, wd, residual=h1)
+            plan = _gather_plan(unit, "d", [wd], hmid)
+            if plan is not None:
+                y = kc.gemm_gather(hmid, plan, wd.shape[0], epi=0, residual=h1)
+            else:
+                y = kc.gemm(hmid, wd, residual=h1)
             out["y"] = y
         if keep:
             out.update(n1=n1, rstd1=rstd1, qkv4=qkv4, attn2=attn2, actx=actx, h1=h1, n2=n2, rstd2=rstd2, gu=gu, hmid=hmid)
@@ -178,6 +226,9 @@ class DenseBlockFn(torch.autograd.Function):
         x2, cos, sin = ctx.saved_tensors
         b, s, d, eps, hd, recompute = ctx.meta
         wn1, wq, wk, wv, wo, wn2, wg, wu, wd = ctx.weights
+        unit = _sharded_unit(wq)
+        if unit is not None:
+            unit.engine.prepare_backward(unit)  # parameter staging is ours again; gradient staging slot is free
         it = ctx.inter
         if it is None:
             it = DenseBlockFn._run_forward(x2, cos, sin, ctx.weights, ctx.meta, need_output=False, keep=True,
@@ -187,6 +238,12 @@ class DenseBlockFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        if unit is not None:  # whatever the recomputation did not gather (the down projection; everything without AC)
+            eng = unit.engine
+            eng.ensure(unit, "d", [wd])
+            eng.ensure(unit, "gu", [wg, wu])
+            eng.ensure(unit, "o", [wo])
+            eng.ensure(unit, "qkv", [wq, wk, wv])
         # ---- feed-forward branch
         dhmid = kc.gemm(dy2, wd, a_kmajor=True, b_kmajor=False)
         (g_wd,) = _wgrad(dy2, it["hmid"], [wd])

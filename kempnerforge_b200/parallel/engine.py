@@ -40,7 +40,8 @@ class DataParallelEngine:
         self.world = dist.get_world_size(process_group) if process_group is not None else 1
         self.rank = dist.get_rank(process_group) if process_group is not None else 0
         self.transport = transport
-        self.groups: list[FlatParamGroup] = flatten_model(model, self.world, self.rank, allocator)
+        self.groups: list[FlatParamGroup] = flatten_model(model, self.world, self.rank, allocator,
+                                                          shard_blocks=bool(getattr(self, "shard_blocks", False)))
         self.requires_sync = True
         dev = self.groups[0].device
         self.device = dev
@@ -53,7 +54,8 @@ class DataParallelEngine:
         self._group_of_module: dict[int, int] = {}
         self._handles: list = []   # forward pre-hooks installed on the model
         self._wrapped: list[str] = []  # model methods replaced by waiting wrappers
-        self.symmetric = transport == "symmetric" and self.world > 1 and self.groups[0].grad_symm is not None
+        self.symmetric = transport == "symmetric" and self.world > 1 and any(
+            getattr(g, "grad_symm", None) is not None or getattr(g, "shard_symm", None) is not None for g in self.groups)
         self._comm_stream = torch.cuda.Stream() if (self.symmetric and dev.type == "cuda") else None
         self._sq_from_reduce = False
         self._root_groups: list[int] = []

@@ -44,8 +44,17 @@ class FlatParamGroup:
         rank: int = 0,
         allocator: Callable[[int, torch.dtype, torch.device], torch.Tensor] | None = None,
         local: bool = False,
+        sharded: bool = False,
     ) -> None:
+        """``sharded=True`` (ZeRO-3): this rank keeps only piece ``rank`` of every parameter (``self.shard``, the
+        pieces packed in parameter order) plus the matching gradient shard and moments; the whole parameters and
+        gradients exist only in staging buffers that the engine binds with :meth:`bind` and that are shared by all
+        units.  Every parameter is padded to a multiple of ``8 * world`` elements so that all pieces are 16-byte
+        aligned and equally long — per-parameter dim-0 sharding like ``fully_shard`` of the reference
+        (kempnerforge/distributed/parallel.py:250-302), which keeps every rank's NVLink egress equal when a weight
+        is gathered."""
         self.name = name
+        self.sharded = bool(sharded) and world > 1 and not local
         # a "local" group holds parameters that exist only on this rank (expert-parallel experts inside the
         # data-parallel group): it is neither reduced nor sharded across the data-parallel ranks
         self.local = local
@@ -60,7 +69,7 @@ class FlatParamGroup:
         if any(p.dtype != self.dtype or p.device != self.device for _, p in items):
             raise ValueError(f"flat group {name!r} mixes dtypes or devices")
         elem = torch.empty((), dtype=self.dtype).element_size()
-        align = max(1, ALIGN_BYTES // elem)
+        align = max(1, ALIGN_BYTES // elem) * (world if self.sharded else 1)
         decay = [(n, p) for n, p in items if _should_decay(n, p)]
         rest = [(n, p) for n, p in items if not _should_decay(n, p)]
         # tensor-parallel shards first: their squared norm has to be summed over the TP group, while the
@@ -88,6 +97,9 @@ class FlatParamGroup:
         self.numel = -(-off // chunk) * chunk
         self.shard_numel = self.numel // world
         alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
+        if self.sharded:
+            self._init_sharded(alloc, allocator is not None)
+            return
         self.param = alloc(self.numel, self.dtype, self.device)
         self.grad = alloc(self.numel, self.dtype, self.device)
         # symmetric-memory descriptors of the two buffers (None with an ordinary allocator)
@@ -110,6 +122,59 @@ class FlatParamGroup:
                 p._kf_grad_live = False
                 p._kf_flat = self
 
+    # ------------------------------------------------------------------ sharded parameters (ZeRO-3)
+    def _init_sharded(self, alloc, symmetric: bool) -> None:
+        w, r = self.world, self.rank
+        # padded length of every parameter = distance to the next offset
+        ends = self.offsets[1:] + [self.numel]
+        self.padded = [e - o for o, e in zip(self.offsets, ends)]
+        self.shard = alloc(self.shard_numel, self.dtype, self.device)          # this rank's piece of every parameter
+        self.grad_shard = torch.zeros(self.shard_numel, dtype=self.dtype, device=self.device)
+        self.grad_shard_live = False
+        self.shard_symm = None
+        if symmetric:
+            from kempnerforge_b200.comm import symmetric as symm
+
+            self.shard_symm = symm.lookup(self.shard)
+        self.param = self.grad = None        # whole buffers exist only while bound to staging
+        self.param_symm = self.grad_symm = None
+        self.grad_stage_symm = None
+        self.valid: set = set()              # which parts of the bound parameter staging hold this unit's current values
+        self.engine = None
+        self.exp_avg = self.exp_avg_sq = None
+        self.step_tensor = torch.zeros((), dtype=torch.float32)
+        self.step_count = 0
+        with torch.no_grad():
+            for p, o, n in zip(self.params, self.offsets, self.padded):
+                piece = n // w
+                flat = p.data.reshape(-1)
+                lo, hi = r * piece, min((r + 1) * piece, flat.numel())
+                dst = self.shard[o // w : o // w + piece]
+                dst.zero_()
+                if hi > lo:
+                    dst[: hi - lo].copy_(flat[lo:hi])
+                p._kf_flat = self
+                p._kf_grad_live = False
+
+    def piece_of(self, p) -> torch.Tensor:
+        """This rank's piece of parameter ``p`` inside the shard (1-D, padded length / world)."""
+        i = next(k for k, q in enumerate(self.params) if q is p)
+        return self.shard[self.offsets[i] // self.world : (self.offsets[i] + self.padded[i]) // self.world]
+
+    def index_of(self, p) -> int:
+        return next(k for k, q in enumerate(self.params) if q is p)
+
+    def bind(self, param_stage: torch.Tensor, grad_stage: torch.Tensor | None, grad_stage_symm=None) -> None:
+        """Point the unit's parameters (and gradient slots) at staging buffers.  The contents are whatever the
+        staging holds: the engine pulls the current values before they are read."""
+        self.param = param_stage[: self.numel]
+        self.grad = grad_stage[: self.numel] if grad_stage is not None else None
+        self.grad_stage_symm = grad_stage_symm
+        for p, o in zip(self.params, self.offsets):
+            p.data = self.param[o : o + p.numel()].view(p.shape)
+            if self.grad is not None:
+                p._kf_grad = self.grad[o : o + p.numel()].view(p.shape)
+
     # ------------------------------------------------------------------ shards
     @property
     def shard_range(self) -> tuple[int, int]:
@@ -119,17 +184,23 @@ class FlatParamGroup:
     @property
     def n_decay_local(self) -> int:
         """Number of leading elements of the local shard that receive weight decay."""
+        if self.sharded:
+            return self.n_decay // self.world
         lo, hi = self.shard_range
         return max(0, min(self.n_decay, hi) - lo)
 
     def optimizer_views(self):
         """(param shard, grad shard, exp_avg, exp_avg_sq) for the local rank."""
+        if self.sharded:
+            return self.shard, self.grad_shard, self.exp_avg, self.exp_avg_sq
         lo, hi = self.shard_range
         return self.param[lo:hi], self.grad[lo:hi], self.exp_avg, self.exp_avg_sq
 
     # ------------------------------------------------------------------ gradients
     def zero_grad(self) -> None:
         """Forget accumulated gradients; the buffer itself is overwritten by the next backward."""
+        if self.sharded:
+            self.grad_shard_live = False
         for p in self.params:
             p._kf_grad_live = False
             p.grad = None
@@ -137,6 +208,8 @@ class FlatParamGroup:
     def finalize_grads(self) -> None:
         """Make the flat buffer hold every gradient: fold in autograd-produced ``.grad`` tensors, zero
         the slots nothing wrote, and point ``.grad`` at the flat views."""
+        if self.sharded and getattr(self.engine, "shared_staging", True):
+            return  # gradients went through the shared staging buffer and were reduced into the shard block by block
         with torch.no_grad():
             for p in self.params:
                 slot = p._kf_grad
@@ -188,7 +261,8 @@ def group_module_params(module: nn.Module, prefix: str = "") -> list[tuple[str, 
     return out
 
 
-def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=None) -> list[FlatParamGroup]:
+def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=None,
+                  shard_blocks: bool = False) -> list[FlatParamGroup]:
     """One flat group per transformer block plus a root group for everything else.
 
     Returns the groups in forward order (root group last) and records them on the model.
@@ -207,7 +281,8 @@ def flatten_model(model: nn.Module, world: int = 1, rank: int = 0, allocator=Non
         shared = [(n, p) for n, p in items if not is_local(p)]
         mine = [(n, p) for n, p in items if is_local(p)]
         if shared:
-            groups.append(FlatParamGroup(name, shared, world, rank, allocator))
+            groups.append(FlatParamGroup(name, shared, world, rank, allocator,
+                                         sharded=shard_blocks and name != "root" and not name.startswith("root.")))
         if mine:
             groups.append(FlatParamGroup(name + ".experts", mine, world, rank, None if ep_local else allocator, local=ep_local))
             groups[-1].ep_sharded = True

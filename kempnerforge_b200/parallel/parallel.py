@@ -76,8 +76,44 @@ def apply_float8(model: nn.Module, enable_fsdp_float8_all_gather: bool = True) -
     return fp8.convert_model(model, skip=("experts", "shared_expert", "router"))
 
 
-def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, **_) -> DataParallelEngine:
-    """Flatten the model's parameters per block and shard optimizer state over the data-parallel group."""
+def _wants_sharded_params(model: nn.Module, world: int, mode: str | None) -> bool:
+    """``resident``: every rank keeps whole parameters and gradients (fastest; 4 bytes per parameter per GPU);
+    ``sharded``: ZeRO-3, 1/N of everything per rank; ``auto`` (default): sharded only when the resident plan would
+    take more than half of the GPU's memory."""
+    mode = (mode or os.environ.get("KF_DP_PARAM_SHARDING", "auto")).lower()
+    if world <= 1 or mode == "resident":
+        return False
+    if mode == "sharded":
+        return True
+    if not torch.cuda.is_available():
+        return False
+    n = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    resident_bytes = 4 * n + 4 * n // world
+    return resident_bytes > 0.5 * torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+
+
+def _sharded_params_supported(model: nn.Module) -> str | None:
+    """None when the model can train with sharded parameters, else the reason it cannot."""
+    if getattr(model, "tp", None) is not None or getattr(model, "ep_group", None) is not None:
+        return "tensor- or expert-parallel models keep the resident engine"
+    layers = None
+    for mod in model.modules():
+        if isinstance(getattr(mod, "layers", None), nn.ModuleDict):
+            layers = mod.layers
+            break
+    if layers is None:
+        return "no block stack"
+    for block in layers.values():
+        if type(getattr(block, "mlp", None)).__name__ != "SwiGLUMLP" or getattr(block, "fp8", False):
+            return "only dense bf16 SwiGLU blocks (the fused block path) are supported"
+    return None
+
+
+def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, reshard_after_forward: bool | None = None,
+                param_sharding: str | None = None, **_) -> DataParallelEngine:
+    """Flatten the model's parameters per block and shard optimizer state — and, in the ``sharded`` plan, parameters
+    and gradients too (``reshard_after_forward`` semantics of kempnerforge/distributed/parallel.py:250-302) — over
+    the data-parallel group."""
     pg = dp_process_group(mesh)
     allocator = None
     if transport is None:
@@ -98,6 +134,30 @@ def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, **_) -> Da
         except Exception as e:  # noqa: BLE001  symmetric memory is optional: fall back, loudly
             log.warning("symmetric-memory transport unavailable (%s); using library collectives", e)
             transport, allocator = "collective", None
+    world = torch.distributed.get_world_size(pg) if pg is not None else 1
+    if reshard_after_forward is False and param_sharding is None:
+        param_sharding = "resident"
+    if _wants_sharded_params(model, world, param_sharding):
+        why = _sharded_params_supported(model)
+        if why is None:
+            from kempnerforge_b200.parallel.zero3 import ShardedDataParallelEngine
+
+            if allocator is None and torch.cuda.is_available() and pg is not None and world > 1 \
+                    and "nccl" in str(torch.distributed.get_backend(pg)) \
+                    and int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) == int(os.environ.get("WORLD_SIZE", "1") or 1) \
+                    and os.environ.get("KF_DP_TRANSPORT", "auto") != "collective":
+                # the sharded engine's kernels work on any mesh whose data-parallel group sits on one NVLink domain
+                try:
+                    from kempnerforge_b200.comm import symmetric
+
+                    allocator = symmetric.make_allocator(pg)
+                    allocator(16, torch.bfloat16, torch.device("cuda", torch.cuda.current_device()))
+                except Exception as e:  # noqa: BLE001
+                    log.warning("symmetric memory unavailable for the sharded engine (%s); using library collectives", e)
+                    allocator = None
+            log.info("data parallelism: sharded parameters (ZeRO-3) over %d ranks", world)
+            return ShardedDataParallelEngine(model, pg, transport=transport, allocator=allocator)
+        log.warning("sharded parameters requested but not available: %s", why)
     return DataParallelEngine(model, pg, transport=transport, allocator=allocator)
 
 
@@ -132,6 +192,7 @@ def build_parallel_model(
     adapter_config=None,
     mp_policy: MixedPrecisionPolicy | None = None,
     frames_per_clip: int = 1,
+    param_sharding: str | None = None,
     **model_kwargs,
 ) -> nn.Module:
     """Build the registered model and apply TP -> EP -> FP8 -> AC -> sharded DP.
@@ -175,7 +236,7 @@ def build_parallel_model(
         apply_float8(model)
     if ac_mode and str(ac_mode) != "none":
         apply_ac(model, str(ac_mode))
-    apply_fsdp2(model, device_mesh, transport=transport)
+    apply_fsdp2(model, device_mesh, transport=transport, param_sharding=param_sharding)
     if compile_model:
         log.info("compile_model is accepted for preset compatibility; this build has no tracing compiler")
     return model

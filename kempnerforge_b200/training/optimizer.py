@@ -414,6 +414,9 @@ def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.op
     if flat and isinstance(opt, FusedAdamW):
         opt.attach_flat_groups(flat)
         opt._engine = getattr(model, "_kf_engine", None)
+    elif getattr(getattr(model, "_kf_engine", None), "shard_blocks", False):
+        raise ValueError(f"optimizer {config.name!r} steps on whole parameters; sharded parameters (ZeRO-3) need adamw "
+                         "(set distributed param sharding to 'resident' for the other optimizers)")
     elif getattr(model, "_kf_engine", None) is not None:
         # whole-parameter optimizers read every element of ``p.grad``: the engine must leave the complete averaged
         # gradient on every rank, not only the local shard of each flat buffer

@@ -129,6 +129,7 @@ class Trainer:
                 ac_mode=str(tc.activation_checkpointing), param_dtype=tc.param_dtype,
                 fp8=tc.is_fp8, compile_model=False, transport=transport,
                 ep_in_dp=config.distributed.ep_in_dp and config.distributed.ep > 1,
+                param_sharding=getattr(config.distributed, "param_sharding", None),
             )
         self.engine = getattr(self.model, "_kf_engine", None)
         self.optimizer = build_optimizer(self.model, config.optimizer)

@@ -163,6 +163,67 @@ def test_sharded_data_parallel_matches_single_process(world):
             assert torch.allclose(p, ref_params[n], atol=2e-5), n
 
 
+def _zero3_worker(rank, world, model_cfg, steps, ckpt_dir):
+    """Sharded parameters (ZeRO-3): every rank keeps 1/world of each block; same trajectory as one process."""
+    from kempnerforge_b200.checkpoint import CheckpointManager
+    from kempnerforge_b200.parallel.zero3 import ShardedDataParallelEngine
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {"dp_shard": world, "param_sharding": "sharded"})
+    cfg.checkpoint.dir = ckpt_dir
+    t = Trainer(cfg)
+    assert isinstance(t.engine, ShardedDataParallelEngine) and len(t.engine.sharded_groups) == model_cfg["n_layers"]
+    shard_elems = sum(g.shard.numel() for g in t.engine.sharded_groups)
+    full_elems = sum(g.numel for g in t.engine.sharded_groups)
+    data = _batches(world * (steps + 1))
+    traj = [t.train_step([data[s * world + rank]]) for s in range(steps)]
+    whole = {n: (t.engine.full_parameter(p) if getattr(getattr(p, "_kf_flat", None), "sharded", False) else p.detach()).clone()
+             for n, p in t.model.named_parameters()}
+    # checkpoint round trip: save, move on, load, the shards are back
+    t.step = steps
+    mgr = CheckpointManager(cfg.checkpoint, t.model, t.optimizer)
+    mgr.save(steps, tokens_seen=1, scheduler=t.scheduler)
+    mgr.wait()
+    shards_then = [g.shard.clone() for g in t.engine.sharded_groups]
+    m_then = [g.exp_avg.clone() for g in t.engine.sharded_groups]
+    t.train_step([data[steps * world + rank]])
+    mgr.load(scheduler=t.scheduler)
+    same = all(torch.equal(a, g.shard) for a, g in zip(shards_then, t.engine.sharded_groups)) and \
+        all(torch.equal(a, g.exp_avg) for a, g in zip(m_then, t.engine.sharded_groups))
+    # evaluation reads whole parameters through the staging copies
+    with torch.no_grad():
+        loss_eval = float(t.model.compute_loss(data[0]["input_ids"], data[0]["labels"]))
+    return traj, whole, shard_elems * world, full_elems, same, loss_eval
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_parameters_match_single_process_and_round_trip_checkpoints(world, tmp_path):
+    steps = 2
+    data = _batches(world * (steps + 1))
+    ref_traj, ref_params = _single_process_reference(TINY, [data[s * world : (s + 1) * world] for s in range(steps)])
+    ckpt = str(tmp_path / "ckpt")
+    results = run_ranks(_zero3_worker, world, TINY, steps, ckpt)
+    for s in range(steps):
+        assert _close(sum(r[0][s]["loss"] for r in results) / world, ref_traj[s]["loss"])
+        assert _close(results[0][0][s]["grad_norm"], ref_traj[s]["grad_norm"], 1e-3)
+    for traj, whole, shard_total, full_total, same, loss_eval in results:
+        assert shard_total == full_total and same and loss_eval == loss_eval
+        # dividing by 3 rounds differently from the single-process mean, and AdamW's normalised step amplifies that
+        # (the resident engine shows the same 4e-3 at world 3)
+        for n, p in whole.items():
+            assert torch.allclose(p, ref_params[n], atol=2e-5 if world == 2 else 5e-3), n
+    # one process (resident parameters) reads the sharded run's checkpoint
+    from kempnerforge_b200.checkpoint import CheckpointManager
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(TINY, {})
+    cfg.checkpoint.dir = ckpt
+    single = Trainer(cfg, init_dist=False)
+    CheckpointManager(cfg.checkpoint, single.model, single.optimizer).load(scheduler=single.scheduler)
+    for n, p in single.model.named_parameters():
+        assert torch.allclose(p.detach(), results[0][1][n], atol=0), n
+
+
 def test_hybrid_sharded_data_parallel_matches_single_process():
     """dp_replicate 2 x dp_shard 2: gradients are averaged over all four ranks and every rank ends with the same weights."""
     steps, world = 2, 4

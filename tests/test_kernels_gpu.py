@@ -839,3 +839,104 @@ def test_attention_backward_with_inverse_rotary_epilogue(native_lib, shape):
     for name, lo, hi in (("dq", 0, h), ("dk", h, h + hkv), ("dv", h + hkv, h + 2 * hkv)):
         rel = (dqkv[:, :, lo:hi].float() - want[:, :, lo:hi]).norm() / want[:, :, lo:hi].norm()
         assert rel < 2e-2, (name, rel.item())
+
+
+class _FakePeers:
+    """Stands in for a symmetric-memory buffer: the 'ranks' are separate tensors on this one GPU, which is all the
+    gathering kernels need (they only ever load from the pointers they are given and never wait for a peer)."""
+
+    def __init__(self, tensors, rank):
+        import ctypes
+
+        self.tensors = tensors
+        self.world, self.rank = len(tensors), rank
+        ptrs = [t.data_ptr() for t in tensors] + [0] * (8 - len(tensors))
+        self.peer_ptrs = (ctypes.c_longlong * 8)(*ptrs)
+        self.multicast_ptr = None
+
+
+def _shards_of(weights, world):
+    """Per-rank shard buffers holding piece r of every weight, packed in order; returns (shards, shard offsets)."""
+    offs, acc = [], 0
+    for w in weights:
+        offs.append(acc)
+        acc += w.numel() // world
+    shards = []
+    for r in range(world):
+        sh = torch.empty(acc, device=DEV, dtype=torch.bfloat16)
+        for w, o in zip(weights, offs):
+            piece = w.numel() // world
+            sh[o:o + piece] = w.reshape(-1)[r * piece:(r + 1) * piece]
+        shards.append(sh)
+    return shards, offs
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 5)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_gemm_with_gathered_weight_operand(native_lib, world, rank, epi):
+    """The weight-gathering GEMM against the plain kernels on the assembled weight: plain (+ residual), SwiGLU and
+    rotary epilogues; the staging buffer must hold the whole operand afterwards."""
+    from kempnerforge_b200.ops import ref
+
+    torch.manual_seed(world * 10 + rank)
+    m, k = 512, 512
+    if epi == 1:
+        rows = [1024, 1024]          # gate, up
+    elif epi == 2:
+        rows = [1024, 256, 256]      # q, k, v (head dim 128: 8 / 2 / 2 heads)
+    else:
+        rows = [1024]
+    weights = [_rand(r, k) * 0.1 for r in rows]
+    x = _rand(m, k)
+    shards, offs = _shards_of(weights, world)
+    total_rows = sum(rows)
+    stage = torch.full((total_rows * k,), float("nan"), device=DEV, dtype=torch.bfloat16)
+    flags = torch.zeros(256, dtype=torch.int32, device=DEV)
+    plan = {"symm": _FakePeers(shards, rank), "seg_rows": rows, "seg_src": offs, "stage": stage, "flags": flags}
+    w_full = torch.cat(weights, dim=0)
+    if epi == 0:
+        res = _rand(m, total_rows)
+        got = native_lib.gemm_gather(x, plan, total_rows, epi=0, residual=res)
+        want = native_lib.gemm(x, w_full, residual=res, mode=2)
+        assert torch.equal(got, want)
+    elif epi == 1:
+        h, gu = native_lib.gemm_gather(x, plan, rows[0], epi=1, want_gu=True)
+        h2, gu2 = native_lib.gemm_swiglu(x, w_full, want_gu=True)
+        assert torch.equal(h, h2) and torch.equal(gu, gu2)
+    else:
+        s, hd = 256, 128
+        cos, sin = ref.rope_tables(hd, s, 500000.0, device=DEV)
+        cos, sin = cos[:s].contiguous(), sin[:s].contiguous()
+        rope = (cos, sin, s, rows[0] + rows[1], hd)
+        got = native_lib.gemm_gather(x, plan, total_rows, epi=2, rope=rope)
+        want = native_lib.gemm(x, w_full, rope=rope, mode=2)
+        assert torch.equal(got, want)
+    assert native_lib.read_status() == 0
+    assert torch.equal(stage.view(total_rows, k), w_full)
+
+
+def test_symm_pull_and_shard_reduce_scatter_kernels(native_lib):
+    """Pull (all-gather of pieces into the full layout) and the reduce-scatter of full-layout gradients into the
+    shard layout, with the ranks emulated as separate buffers on one GPU."""
+    world = 4
+    lens = [4096 * 8, 64 * world, 1024 * world]          # a matrix, a tiny vector, another tensor
+    full_off, acc = [], 0
+    for n in lens:
+        full_off.append(acc)
+        acc += n
+    params = [_rand(n) for n in lens]
+    shards, offs = _shards_of(params, world)
+    dst = torch.zeros(acc, device=DEV, dtype=torch.bfloat16)
+    native_lib.symm_pull(_FakePeers(shards, 1), full_off, lens, offs, dst)
+    assert torch.equal(dst, torch.cat(params))
+    # gradients: every "rank" has a full-layout buffer; rank r ends with the mean of its pieces
+    grads = [_rand(acc) for _ in range(world)]
+    mean = torch.stack([g.float() for g in grads]).mean(0)
+    for rank in range(world):
+        out = torch.zeros(acc // world, device=DEV, dtype=torch.bfloat16)
+        native_lib.symm_rs_shard(_FakePeers(grads, rank), full_off, lens, offs, out, accumulate=False)
+        want = torch.cat([mean[o + rank * (n // world): o + (rank + 1) * (n // world)] for o, n in zip(full_off, lens)])
+        _close(out, want, rtol=1e-2, atol=1e-2)
+        native_lib.symm_rs_shard(_FakePeers(grads, rank), full_off, lens, offs, out, accumulate=True)
+        _close(out, 2 * want, rtol=2e-2, atol=2e-2)
+    assert native_lib.read_status() == 0

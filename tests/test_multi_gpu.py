@@ -21,7 +21,8 @@ cfg = config_from_dict({
     "model": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536, max_seq_len=256),
     "train": dict(batch_size=2, seq_len=256, max_steps=10, mixed_precision="bf16", activation_checkpointing="full", seed=0),
     "optimizer": dict(lr=1e-3), "scheduler": dict(warmup_steps=0, name="constant"),
-    "distributed": dict(dp_shard=world), "metrics": dict(log_interval=1000)})
+    "distributed": dict(dp_shard=world, param_sharding=os.environ.get("KF_TEST_PARAM_SHARDING") or "resident"),
+    "metrics": dict(log_interval=1000)})
 t = Trainer(cfg, transport=os.environ.get("KF_TRANSPORT") or None)
 g = torch.Generator().manual_seed(100 + rank)
 out = []
@@ -29,23 +30,29 @@ for step in range(4):
     tok = torch.randint(0, 4096, (2, 257), generator=g)
     out.append(t.train_step([{"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}]))
 t.engine.wait_all()
-flat = torch.cat([p.detach().float().flatten() for p in t.model.parameters()])
+def whole(p):
+    g = getattr(p, "_kf_flat", None)
+    return t.engine.full_parameter(p) if g is not None and getattr(g, "sharded", False) else p.detach()
+flat = torch.cat([whole(p).float().flatten() for p in t.model.parameters()])
+mem = t.engine.memory_report() if hasattr(t.engine, "memory_report") else {}
 digest = torch.stack([flat.sum(), flat.abs().sum(), flat.pow(2).sum()])
 gathered = [torch.zeros_like(digest) for _ in range(world)]
 torch.distributed.all_gather(gathered, digest)
 if rank == 0:
     same = all(torch.equal(gathered[0], x) for x in gathered)
-    print("RESULT " + json.dumps({"losses": [o["loss"] for o in out], "norms": [o["grad_norm"] for o in out], "replicas_identical": same}))
+    print("RESULT " + json.dumps({"losses": [o["loss"] for o in out], "norms": [o["grad_norm"] for o in out], "replicas_identical": same,
+                                  "digest": [float(x) for x in digest], "engine": type(t.engine).__name__, "mem": mem,
+                                  "status": __import__("kempnerforge_b200.ops.cuda", fromlist=["x"]).read_status()}))
 torch.distributed.destroy_process_group()
 '''
 
 
-def _run(world: int, transport: str = "", multimem: bool = True, tmp_dir: str = "/tmp"):
+def _run(world: int, transport: str = "", multimem: bool = True, tmp_dir: str = "/tmp", sharding: str = "resident"):
     script = os.path.join(tmp_dir, f"kf_multi_gpu_worker_{os.getpid()}.py")
     with open(script, "w") as f:
         f.write(WORKER)
     env = dict(os.environ, KF_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KF_TRANSPORT=transport,
-               KF_SYMM_MULTIMEM="1" if multimem else "0")
+               KF_SYMM_MULTIMEM="1" if multimem else "0", KF_TEST_PARAM_SHARDING=sharding)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29631", script]
     res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
@@ -73,6 +80,23 @@ def test_symmetric_transport_matches_collectives(multimem):
         assert abs(a - b) < 5e-2, (base["losses"], fused["losses"])
     for a, b in zip(base["norms"], fused["norms"]):
         assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (base["norms"], fused["norms"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("transport", ["symmetric", "collective"])
+def test_sharded_parameters_match_resident_parameters(transport):
+    """ZeRO-3 (weights gathered inside the GEMMs that read them, gradients reduce-scattered into shards) against the
+    resident engine on the same data: same losses, gradient norms and final parameters."""
+    base = _run(2, transport="collective")
+    z3 = _run(2, transport=transport, multimem=False, sharding="sharded")
+    assert z3["engine"] == "ShardedDataParallelEngine" and z3["status"] == 0
+    for a, b in zip(base["losses"], z3["losses"]):
+        assert abs(a - b) < 5e-2, (base["losses"], z3["losses"])
+    for a, b in zip(base["norms"], z3["norms"]):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (base["norms"], z3["norms"])
+    for a, b in zip(base["digest"], z3["digest"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (base["digest"], z3["digest"])
+    assert z3["mem"]["param_shards"] > 0
 
 
 GEMM_RS_WORKER = r'''
