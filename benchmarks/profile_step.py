@@ -25,11 +25,42 @@ SHAPES = {
 }
 
 
+def stream_report(prof, n_gaps: int) -> list[str]:
+    """Busy time per CUDA stream and the longest idle gaps of the busiest one (what the compute stream waited for)."""
+    try:
+        events = prof.profiler.kineto_results.events()
+    except AttributeError:
+        return []
+    per_stream: dict[int, list] = {}
+    for e in events:
+        if str(e.device_type()).endswith("CUDA") and e.duration_ns() > 0 and "Memcpy" not in e.name() and "Memset" not in e.name():
+            per_stream.setdefault(e.device_resource_id(), []).append((e.start_ns(), e.start_ns() + e.duration_ns(), e.name()))
+    if not per_stream:
+        return []
+    out = ["", "streams (busy ms, kernels):"]
+    busiest, best = None, -1
+    for sid, evs in per_stream.items():
+        busy = sum(b - a for a, b, _ in evs) / 1e6
+        out.append(f"  stream {sid}: {busy:8.2f} ms in {len(evs)} kernels")
+        if busy > best:
+            busiest, best = sid, busy
+    evs = sorted(per_stream[busiest])
+    span = (evs[-1][1] - evs[0][0]) / 1e6
+    gaps = sorted(((evs[i + 1][0] - evs[i][1], evs[i][2], evs[i + 1][2]) for i in range(len(evs) - 1)), reverse=True)
+    idle = sum(g[0] for g in gaps if g[0] > 0) / 1e6
+    out.append(f"busiest stream {busiest}: span {span:.2f} ms, idle inside the span {idle:.2f} ms; longest gaps:")
+    for g, before, after in gaps[:n_gaps]:
+        out.append(f"  {g / 1e6:7.3f} ms between {before[:60]} -> {after[:60]}")
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama3_8b", choices=sorted(SHAPES))
     ap.add_argument("--out", default=None)
     ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--param-sharding", default="resident", choices=("auto", "resident", "sharded"))
+    ap.add_argument("--gaps", type=int, default=12, help="list this many of the longest idle gaps of the busiest stream")
     args = ap.parse_args()
     from kempnerforge_b200.config import config_from_dict
     from kempnerforge_b200.training.trainer import Trainer
@@ -40,7 +71,8 @@ def main() -> int:
                             "train": {"batch_size": 2, "seq_len": seq, "max_steps": 100, "mixed_precision": "bf16",
                                       "activation_checkpointing": "full", "seed": 0},
                             "scheduler": {"warmup_steps": 10}, "metrics": {"log_interval": 1000},
-                            "distributed": {"dp_shard": int(os.environ.get("WORLD_SIZE", "1"))}})
+                            "distributed": {"dp_shard": int(os.environ.get("WORLD_SIZE", "1")),
+                                            "param_sharding": args.param_sharding}})
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     trainer = Trainer(cfg, init_dist=world > 1)
 
@@ -69,6 +101,7 @@ def main() -> int:
     lines = [f"ranks {world}; profiled step {step_ms:.1f} ms on the stream clock (with profiler overhead); "
              f"total device kernel time {total / 1e3:.1f} ms (kernels on different streams overlap)"]
     lines += [f"{us / 1e3:9.2f} ms {100 * us / total:5.1f}% x{n:5d} {key[:110]}" for us, n, key in rows[: args.top]]
+    lines += stream_report(prof, args.gaps)
     text = "\n".join(lines)
     if rank == 0:
         print(text)

@@ -413,6 +413,78 @@ kf_ce_fwd_bwd(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------ vocabulary-parallel cross entropy
+// The vocabulary dimension of the logits is sharded over the tensor-parallel ranks (this rank holds columns
+// [vocab_start, vocab_start + V)).  Phase 1 produces, per row, the local maximum, the local sum of exponentials
+// relative to that maximum and the logit of the label when the label lives on this rank; the ranks then exchange
+// those three numbers per row (one MAX and one SUM all-reduce of (T,) vectors) and phase 2 turns the logits into
+// their gradient in place, given the global log-sum-exp.  No (T, V) temporary, no host read.
+__global__ void __launch_bounds__(CE_THREADS)
+kf_ce_vp_stats(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels, long long vocab_start,
+               float* __restrict__ row_max, float* __restrict__ row_sum, float* __restrict__ row_picked, int V, int ld) {
+  __shared__ float red[40];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + size_t(row) * ld;
+  const int nvec = V >> 3;
+  float mx = -INFINITY, sum = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    F8 t = load8(lr + v * 8);
+    float m2 = mx;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m2 = fmaxf(m2, t.v[i]);
+    float s2 = sum * __expf(mx - m2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s2 += __expf(t.v[i] - m2);
+    mx = m2;
+    sum = s2;
+  }
+  for (int j = nvec * 8 + threadIdx.x; j < V; j += CE_THREADS) {
+    const float t = __bfloat162float(lr[j]);
+    const float m2 = fmaxf(mx, t);
+    sum = sum * __expf(mx - m2) + __expf(t - m2);
+    mx = m2;
+  }
+  const float gmax = block_max(mx, red);
+  const float gsum = block_sum(mx == -INFINITY ? 0.f : sum * __expf(mx - gmax), red);
+  if (threadIdx.x == 0) {
+    const long long local = labels[row] - vocab_start;
+    row_max[row] = gmax;
+    row_sum[row] = gsum;
+    row_picked[row] = (local >= 0 && local < V) ? __bfloat162float(lr[local]) : 0.f;
+  }
+}
+
+// logits <- d loss / d logits = upstream * inv_n * (softmax * (1 + 2 z lse) - onehot) for rows with a valid label.
+__global__ void __launch_bounds__(CE_THREADS)
+kf_ce_vp_bwd(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels, long long vocab_start,
+             const float* __restrict__ lse_rows, const float* __restrict__ inv_n_ptr, const float* __restrict__ upstream,
+             float z_w, int V, int ld) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + size_t(row) * ld;
+  const long long label = labels[row];
+  const bool valid = label >= 0;
+  const long long local = label - vocab_start;
+  const float lse = lse_rows[row];
+  const float scale = valid ? (*inv_n_ptr) * (upstream ? *upstream : 1.f) : 0.f;
+  const float gscale = scale * (1.f + 2.f * z_w * lse);
+  const int nvec = V >> 3;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    F8 t = load8(lr + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float g = __expf(t.v[i] - lse) * gscale;
+      if (v * 8 + i == local) g -= scale;
+      t.v[i] = g;
+    }
+    store8(lr + v * 8, t);
+  }
+  for (int j = nvec * 8 + threadIdx.x; j < V; j += CE_THREADS) {
+    float g = __expf(__bfloat162float(lr[j]) - lse) * gscale;
+    if (j == local) g -= scale;
+    lr[j] = __float2bfloat16(g);
+  }
+}
+
 // ------------------------------------------------------------------ fused AdamW on flat buffers
 template <typename T>
 __device__ __forceinline__ float to_f(T v);
@@ -623,6 +695,26 @@ int kf_ce_fwd_bwd_bf16(void* logits, const void* labels, void* row_nll, void* ro
   kf_ce_fwd_bwd<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)logits, (const long long*)labels, (float*)row_nll, (float*)row_lse2,
       (const float*)inv_n, z_w, V, ld);
+  KF_LAUNCH_CHECK();
+}
+
+int kf_ce_vp_stats_bf16(const void* logits, const void* labels, long long vocab_start, void* row_max, void* row_sum,
+                        void* row_picked, int rows, int V, int ld, void* stream) {
+  using namespace kf;
+  if (ld % 8) return 1;
+  kf_ce_vp_stats<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, (const long long*)labels,
+                                                                vocab_start, (float*)row_max, (float*)row_sum,
+                                                                (float*)row_picked, V, ld);
+  KF_LAUNCH_CHECK();
+}
+
+int kf_ce_vp_bwd_bf16(void* logits, const void* labels, long long vocab_start, const void* lse, const void* inv_n,
+                      const void* upstream, float z_w, int rows, int V, int ld, void* stream) {
+  using namespace kf;
+  if (ld % 8) return 1;
+  kf_ce_vp_bwd<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, (const long long*)labels,
+                                                              vocab_start, (const float*)lse, (const float*)inv_n,
+                                                              (const float*)upstream, z_w, V, ld);
   KF_LAUNCH_CHECK();
 }
 

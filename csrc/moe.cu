@@ -507,3 +507,51 @@ int kf_ep_move_bf16(const void* window, void* compact, const void* table, const 
 }
 
 }  // extern "C"
+
+
+// ------------------------------------------------------------------ expert capacity
+// keep[t, j] = 1 when token t is among the first `cap` tokens (in sequence order) that slot j routes to its expert,
+// else 0: the per-(slot, expert) capacity rule of the reference (kempnerforge/model/moe.py:148-185), evaluated on
+// the device without data-dependent shapes.  One block per (slot, expert) scans the token column with a block-wide
+// prefix count; the result does not depend on scheduling.
+namespace kf {
+namespace moe {
+constexpr int CAP_THREADS = 256;
+__global__ void __launch_bounds__(CAP_THREADS)
+kf_moe_capacity_mask(const long long* __restrict__ indices, int T, int k, int cap, float* __restrict__ keep) {
+  __shared__ int warp_tot[CAP_THREADS / 32];
+  __shared__ int base;
+  const int j = blockIdx.x % k, e = blockIdx.x / k;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) base = 0;
+  __syncthreads();
+  for (int t0 = 0; t0 < T; t0 += CAP_THREADS) {
+    const int t = t0 + threadIdx.x;
+    const bool hit = t < T && indices[size_t(t) * k + j] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    const int before_in_warp = __popc(m & ((1u << lane) - 1u));
+    if (lane == 0) warp_tot[warp] = __popc(m);
+    __syncthreads();
+    int before = base + before_in_warp;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (hit) keep[size_t(t) * k + j] = before < cap ? 1.f : 0.f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < CAP_THREADS / 32; ++w) tot += warp_tot[w];
+      base += tot;
+    }
+    __syncthreads();
+  }
+}
+}  // namespace moe
+}  // namespace kf
+
+extern "C" int kf_moe_capacity_mask(const void* indices, int T, int k, int E, int cap, void* keep, void* stream) {
+  using namespace kf::moe;
+  if (T <= 0 || k <= 0 || E <= 0) return 0;
+  kf_moe_capacity_mask<<<E * k, CAP_THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(indices), T, k,
+                                                                         cap, reinterpret_cast<float*>(keep));
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : 400 + (int)err;
+}

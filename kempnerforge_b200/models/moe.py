@@ -64,6 +64,13 @@ def apply_capacity(weights: torch.Tensor, indices: torch.Tensor, num_experts: in
     """Zero the routing weight of tokens beyond each expert's per-slot capacity (device only)."""
     t, k = indices.shape
     cap = max(1, math.ceil(t * k / num_experts * capacity_factor))
+    if indices.is_cuda and indices.dtype == torch.int64:
+        from kempnerforge_b200.ops import cuda as kc
+        from kempnerforge_b200.ops import functional as _F
+
+        if kc.available() and not _F._FORCE_REF and getattr(kc.lib(), "kf_moe_capacity_mask", None) is not None:
+            keep = kc.moe_capacity_mask(indices.contiguous(), num_experts, cap)   # one kernel, no (T, k, E) one-hot
+            return weights * keep.to(weights.dtype), indices
     onehot = torch.nn.functional.one_hot(indices, num_experts)  # (T, k, E)
     rank = (onehot.cumsum(dim=0) * onehot).sum(dim=-1) - 1  # arrival order within (slot, expert)
     keep = rank < cap

@@ -59,6 +59,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_embedding_fwd_bf16": [vp, vp, vp, ll, i, i, vp],
         "kf_embedding_bwd_bf16": [vp, vp, vp, ll, i, i, vp],
         "kf_ce_fwd_bwd_bf16": [vp, vp, vp, vp, vp, f, i, i, i, vp],
+        "kf_ce_vp_stats_bf16": [vp, vp, ll, vp, vp, vp, i, i, i, vp],
+        "kf_ce_vp_bwd_bf16": [vp, vp, ll, vp, vp, vp, f, i, i, i, vp],
         "kf_adamw_flat": [vp, vp, vp, vp, ll, ll, f, f, f, f, f, f, f, vp, vp, i, i, i, vp],
         "kf_sumsq": [vp, ll, i, vp, vp, i, vp],
         "kf_test_flag_timeout": [vp, i, ll],
@@ -72,6 +74,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_ep_move_bf16": [vp, vp, vp, vp, vp, i, i, i, ll, i, vp, vp],
         "kf_router_topk": [vp, i, vp, i, i, i, i, vp, vp, vp, vp, vp, vp],
         "kf_moe_sort": [vp, i, i, vp, vp, vp, vp, vp],
+        "kf_moe_capacity_mask": [vp, i, i, i, i, vp, vp],
         "kf_moe_gather_bf16": [vp, vp, i, i, i, vp, vp],
         "kf_moe_combine_bf16": [vp, vp, vp, i, i, i, vp, vp],
         "kf_moe_combine_bwd_bf16": [vp, vp, vp, vp, i, i, i, vp, vp, vp],
@@ -506,6 +509,16 @@ def router_topk(logits: torch.Tensor, bias: torch.Tensor | None, sigmoid: bool, 
     return w, idx, acc[:e], acc[e:2 * e], acc[2 * e:]
 
 
+def moe_capacity_mask(indices: torch.Tensor, num_experts: int, cap: int) -> torch.Tensor:
+    """fp32 (T, k) mask: 1 for the first ``cap`` tokens (sequence order) of every (slot, expert) pair, else 0."""
+    t, k = indices.shape
+    assert indices.dtype == torch.int64 and indices.is_contiguous()
+    keep = torch.empty((t, k), dtype=torch.float32, device=indices.device)
+    _check(lib().kf_moe_capacity_mask(indices.data_ptr(), t, k, num_experts, int(cap), keep.data_ptr(), _stream()),
+           "kf_moe_capacity_mask")
+    return keep
+
+
 def moe_sort(indices: torch.Tensor, num_experts: int):
     """Stable sort of the (token, k) assignments by expert: (offsets int32 (E + 1), row_of_slot int32, slot_of_row int32)."""
     flat = indices.reshape(-1)
@@ -722,6 +735,29 @@ def symm_adamw_bcast(param_buf, grad_shard, m, v, lo: int, n: int, n_decay_globa
 def symm_gather(buf, lo: int, n: int, max_blocks: int = 592) -> None:
     _check(lib().kf_symm_gather_bf16(buf.peer_ptrs, buf.multicast_ptr, buf.world, buf.rank, lo, n, max_blocks, _stream()),
            "kf_symm_gather_bf16")
+
+
+# --------------------------------------------------------------------------- vocabulary-parallel cross entropy
+def ce_vp_stats(logits: torch.Tensor, labels: torch.Tensor, vocab_start: int):
+    """Per row of this rank's vocabulary shard (T, V_local) bf16: (max, sum of exp relative to that max, logit of the
+    label if the label is in [vocab_start, vocab_start + V_local) else 0), three fp32 (T,) vectors."""
+    t, v = logits.shape
+    out = torch.empty((3, t), dtype=torch.float32, device=logits.device)
+    _check(lib().kf_ce_vp_stats_bf16(logits.data_ptr(), labels.data_ptr(), int(vocab_start), out[0].data_ptr(),
+                                     out[1].data_ptr(), out[2].data_ptr(), t, v, logits.stride(0), _stream()),
+           "kf_ce_vp_stats_bf16")
+    return out[0], out[1], out[2]
+
+
+def ce_vp_bwd(logits: torch.Tensor, labels: torch.Tensor, vocab_start: int, lse: torch.Tensor, inv_n: torch.Tensor,
+              upstream: torch.Tensor | None, z_weight: float) -> torch.Tensor:
+    """In place: logits <- gradient of the mean (over valid rows) cross entropy (+ z-loss) given the global
+    log-sum-exp ``lse`` (T,); ``inv_n`` and ``upstream`` are device scalars."""
+    t, v = logits.shape
+    _check(lib().kf_ce_vp_bwd_bf16(logits.data_ptr(), labels.data_ptr(), int(vocab_start), lse.data_ptr(), inv_n.data_ptr(),
+                                   upstream.data_ptr() if upstream is not None else None, float(z_weight), t, v,
+                                   logits.stride(0), _stream()), "kf_ce_vp_bwd_bf16")
+    return logits
 
 
 # --------------------------------------------------------------------------- sharded parameters (ZeRO-3)

@@ -386,6 +386,28 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, labels, vocab_start, group, z_weight):
+        ctx.native = False
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(-1) == 1 and logits.stride(0) % 8 == 0:
+            from kempnerforge_b200.ops import cuda as kc
+            from kempnerforge_b200.ops import functional as _F
+
+            if kc.available() and not _F._FORCE_REF and getattr(kc.lib(), "kf_ce_vp_stats_bf16", None) is not None:
+                # kernels: per-row (max, sum exp, picked) of the local shard; two (T,) all-reduces; gradient in place
+                labels = labels.contiguous()
+                row_max, row_sum, picked = kc.ce_vp_stats(logits, labels, vocab_start)
+                gmax = row_max.clone()
+                dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+                both = torch.stack([row_sum * torch.exp(row_max - gmax), picked])
+                dist.all_reduce(both, group=group)
+                lse = gmax + torch.log(both[0])
+                valid = labels != -100
+                n = valid.sum().clamp_min(1).float()
+                zero = torch.zeros_like(lse)
+                nll = torch.where(valid, lse - both[1], zero).sum() / n
+                z = torch.where(valid, lse * lse, zero).sum() / n
+                ctx.native, ctx.z_weight, ctx.vocab_start = True, z_weight, vocab_start
+                ctx.save_for_backward(logits, labels, lse, (1.0 / n).reshape(1))
+                return nll + z_weight * z
         lf = logits.float()
         local_max = lf.max(dim=-1).values
         gmax = local_max.clone()
@@ -409,10 +431,17 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
+        if ctx.native:
+            from kempnerforge_b200.ops import cuda as kc
+
+            logits, labels, lse, inv_n = ctx.saved_tensors
+            # the logits feed nothing but this loss: their storage becomes the gradient
+            grad = kc.ce_vp_bwd(logits, labels, ctx.vocab_start, lse, inv_n, g.reshape(1).float().contiguous(), ctx.z_weight)
+            return grad, None, None, None, None
         probs, local_label, mine, valid, lse, n = ctx.saved_tensors
         grad = probs * (1.0 + 2.0 * ctx.z_weight * lse)[:, None]
-        rows = torch.nonzero(mine, as_tuple=False).squeeze(-1)
-        grad[rows, local_label[rows]] -= 1.0
+        # subtract the one-hot without a data-dependent shape (no host read): rows whose label lives elsewhere add 0
+        grad.scatter_add_(1, local_label.clamp(0, grad.shape[1] - 1)[:, None], -mine.to(grad.dtype)[:, None])
         grad = grad * (valid.float() / n)[:, None] * g
         return grad.to(probs.dtype), None, None, None, None
 

@@ -309,6 +309,9 @@ class Muon(torch.optim.Optimizer):
         self._initial_adam_lr = adam_lr
         has_adam = any(len(g["params"]) for g in adam_params)
         self._adam = FusedAdamW(adam_params, lr=adam_lr, betas=adam_betas, eps=adam_eps) if has_adam else None
+        # data-parallel group over which the Newton-Schulz work is divided (set by build_optimizer; None = every rank
+        # orthogonalises every matrix, like the reference)
+        self.dp_group = None
         super().__init__(muon_params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay, ns_steps=ns_steps))
 
     @property
@@ -338,6 +341,13 @@ class Muon(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        import torch.distributed as dist
+
+        dp = self.dp_group
+        world = dist.get_world_size(dp) if dp is not None else 1
+        rank = dist.get_rank(dp) if dp is not None else 0
+        pending = []   # (work handle) of parameter broadcasts in flight
+        k = 0          # running index of non-empty matrices: matrix k is orthogonalised by data-parallel rank k % world
         for group in self.param_groups:
             lr, mu, wd, ns = group["lr"], group["momentum"], group["weight_decay"], group["ns_steps"]
             for p in group["params"]:
@@ -347,14 +357,23 @@ class Muon(torch.optim.Optimizer):
                 if "momentum_buffer" not in st:
                     st["momentum_buffer"] = torch.zeros_like(p.grad)
                 pl, gl, buf = _local(p), _local(p.grad), _local(st["momentum_buffer"])
-                buf.mul_(mu).add_(gl)
+                buf.mul_(mu).add_(gl)   # every rank keeps every momentum buffer (the gradients are identical)
                 if buf.numel() == 0:
                     continue
-                mat = buf.reshape(buf.shape[0], -1)
-                upd = newton_schulz(mat.float(), ns).mul_(math.sqrt(max(1.0, mat.shape[0] / mat.shape[1])))
-                if wd > 0:
-                    pl.mul_(1.0 - lr * wd)
-                pl.add_(upd.to(pl.dtype).view_as(pl), alpha=-lr)
+                owner = k % world
+                k += 1
+                if owner == rank:
+                    mat = buf.reshape(buf.shape[0], -1)
+                    upd = newton_schulz(mat.float(), ns).mul_(math.sqrt(max(1.0, mat.shape[0] / mat.shape[1])))
+                    if wd > 0:
+                        pl.mul_(1.0 - lr * wd)
+                    pl.add_(upd.to(pl.dtype).view_as(pl), alpha=-lr)
+                if world > 1:
+                    # the owner's new values replace everybody's copy; the transfer overlaps the next matrices' math
+                    src = dist.get_global_rank(dp, owner)
+                    pending.append(dist.broadcast(pl if pl.is_contiguous() else pl.data, src=src, group=dp, async_op=True))
+        for work in pending:
+            work.wait()
         if self._adam is not None:
             if self._initial_lr > 0:
                 ratio = self.param_groups[0]["lr"] / self._initial_lr
@@ -421,4 +440,6 @@ def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.op
         # whole-parameter optimizers read every element of ``p.grad``: the engine must leave the complete averaged
         # gradient on every rank, not only the local shard of each flat buffer
         model._kf_engine.full_grads = True
+        if isinstance(opt, Muon) and model._kf_engine.world > 1:
+            opt.dp_group = model._kf_engine.pg   # divide the Newton-Schulz work over the data-parallel ranks
     return opt

@@ -224,6 +224,48 @@ def test_sharded_parameters_match_single_process_and_round_trip_checkpoints(worl
         assert torch.allclose(p.detach(), results[0][1][n], atol=0), n
 
 
+def _dp_opt_worker(rank, world, model_cfg, steps, opt_name):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {"dp_shard": world})
+    cfg.optimizer.name = opt_name
+    t = Trainer(cfg)
+    data = _batches(world * steps)
+    traj = [t.train_step([data[s * world + rank]]) for s in range(steps)]
+    state = {}
+    for p, st in t.optimizer.state.items():
+        for k_, v in st.items():
+            if torch.is_tensor(v) and v.dim() > 0:
+                state.setdefault(k_, []).append(v.detach().float().flatten())
+    digest = {k_: torch.cat(v) for k_, v in state.items()}
+    return traj, {n: p.detach().clone() for n, p in t.model.named_parameters()}, digest
+
+
+@pytest.mark.parametrize("opt_name", ["lion", "muon", "schedule_free_adamw"])
+def test_whole_parameter_optimizers_under_data_parallelism_match_single_process(opt_name):
+    """Lion / Muon / Schedule-Free step on whole parameters: every rank must see the whole averaged gradient (not
+    only its shard), end with identical weights and state, and — for Muon — may divide the Newton-Schulz work."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    steps, world = 2, 2
+    data = _batches(world * steps)
+    cfg = _job(TINY, {}, grad_accum_steps=world)
+    cfg.optimizer.name = opt_name
+    single = Trainer(cfg, init_dist=False)
+    torch.save(single.model.state_dict(), INIT_FILE)
+    ref_traj = [single.train_step(list(data[s * world:(s + 1) * world])) for s in range(steps)]
+    ref_params = {n: p.detach().clone() for n, p in single.model.named_parameters()}
+    results = run_ranks(_dp_opt_worker, world, TINY, steps, opt_name)
+    for s in range(steps):
+        assert _close(sum(r[0][s]["loss"] for r in results) / world, ref_traj[s]["loss"])
+    tol = 2e-3 if opt_name == "lion" else 5e-4     # Lion moves every weight by +-lr: one flipped sign is 2 lr
+    for r in results:
+        for n, p in r[1].items():
+            assert torch.allclose(p, ref_params[n], atol=tol), (n, float((p - ref_params[n]).abs().max()))
+    for k_ in results[0][2]:
+        assert torch.equal(results[0][2][k_], results[1][2][k_]), k_      # identical optimizer state on every rank
+
+
 def test_hybrid_sharded_data_parallel_matches_single_process():
     """dp_replicate 2 x dp_shard 2: gradients are averaged over all four ranks and every rank ends with the same weights."""
     steps, world = 2, 4

@@ -940,3 +940,57 @@ def test_symm_pull_and_shard_reduce_scatter_kernels(native_lib):
         native_lib.symm_rs_shard(_FakePeers(grads, rank), full_off, lens, offs, out, accumulate=True)
         _close(out, 2 * want, rtol=2e-2, atol=2e-2)
     assert native_lib.read_status() == 0
+
+
+@pytest.mark.parametrize("z_w", [0.0, 1e-3])
+def test_vocab_parallel_cross_entropy_kernels_match_full_cross_entropy(native_lib, z_w):
+    """Two vocabulary shards handled by the two-phase kernels (statistics -> exchange -> gradient in place), combined
+    the way the ranks combine them, against the fp32 cross entropy over the whole vocabulary."""
+    torch.manual_seed(3)
+    t, v, tp = 300, 1000, 2
+    vl = v // tp
+    logits = (_rand(t, v) * 4).contiguous()
+    labels = torch.randint(0, v, (t,), device=DEV)
+    labels[::7] = -100
+    shards = [logits[:, r * vl:(r + 1) * vl].contiguous() for r in range(tp)]
+    stats = [native_lib.ce_vp_stats(s, labels, r * vl) for r, s in enumerate(shards)]
+    gmax = torch.stack([s[0] for s in stats]).max(0).values
+    sumexp = sum(s[1] * torch.exp(s[0] - gmax) for s in stats)
+    picked = sum(s[2] for s in stats)
+    lse = gmax + torch.log(sumexp)
+    valid = labels != -100
+    n = valid.sum().float()
+    loss = (torch.where(valid, lse - picked, torch.zeros_like(lse)).sum() + z_w * torch.where(valid, lse * lse, torch.zeros_like(lse)).sum()) / n
+    lf = logits.float().requires_grad_(True)
+    lse_ref = torch.logsumexp(lf, -1)
+    ref = torch.nn.functional.cross_entropy(lf, labels, ignore_index=-100) + z_w * (lse_ref[valid] ** 2).sum() / n
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * abs(ref.item())
+    up = torch.full((1,), 0.5, device=DEV)
+    for r, s in enumerate(shards):
+        g = native_lib.ce_vp_bwd(s, labels, r * vl, lse, (1.0 / n).reshape(1), up, z_w)
+        want = 0.5 * lf.grad[:, r * vl:(r + 1) * vl]
+        assert (g.float() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("shape", [(1000, 2, 8, 1.0), (4096, 6, 64, 1.25), (77, 1, 4, 0.5)])
+def test_moe_capacity_mask_kernel_matches_the_reference_rule(native_lib, shape):
+    """First `cap` tokens in sequence order of every (slot, expert) pair keep their weight (the rule of the
+    reference's Python loops), evaluated by one kernel."""
+    import math
+
+    from kempnerforge_b200.models.moe import apply_capacity
+
+    t, k, e, cf = shape
+    torch.manual_seed(t)
+    idx = torch.randint(0, e, (t, k), device=DEV)
+    w = torch.rand(t, k, device=DEV)
+    got, _ = apply_capacity(w, idx, e, cf)
+    cap = max(1, math.ceil(t * k / e * cf))
+    want = w.clone().cpu()
+    ic = idx.cpu()
+    for j in range(k):
+        for ex in range(e):
+            rows = (ic[:, j] == ex).nonzero(as_tuple=True)[0]
+            want[rows[cap:], j] = 0.0
+    assert torch.equal(got.cpu(), want)
