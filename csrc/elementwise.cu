@@ -295,9 +295,12 @@ __global__ void kf_swiglu_fwd(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
   }
 }
 
+// rows_ptr (optional, device int): only the first min(rows, *rows_ptr) rows are touched (ragged expert activations
+// whose buffers are sized by an upper bound known on the host).
 __global__ void kf_swiglu_bwd(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
-                              __nv_bfloat16* __restrict__ dgu, long long rows, int H) {
+                              __nv_bfloat16* __restrict__ dgu, long long rows, int H, const int* __restrict__ rows_ptr) {
   const int vec = H >> 3;
+  if (rows_ptr) rows = min(rows, (long long)*rows_ptr);
   const long long total = rows * vec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -666,7 +669,16 @@ int kf_swiglu_bwd_bf16(const void* dh, const void* gu, void* dgu, long long rows
   using namespace kf;
   if (H % 8) return 1;
   kf_swiglu_bwd<<<grid_for(rows * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, rows, H);
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, rows, H, nullptr);
+  KF_LAUNCH_CHECK();
+}
+
+int kf_swiglu_bwd_ragged_bf16(const void* dh, const void* gu, void* dgu, long long rows_bound, const void* rows_ptr, int H,
+                              void* stream) {
+  using namespace kf;
+  if (H % 8) return 1;
+  kf_swiglu_bwd<<<grid_for(rows_bound * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, rows_bound, H, (const int*)rows_ptr);
   KF_LAUNCH_CHECK();
 }
 

@@ -33,11 +33,16 @@ __device__ __forceinline__ Tile decode(int t, int n_blocks, const int* tile_star
   return tilemath::grouped_decode(t, n_blocks, tile_start, offsets, E, BM);
 }
 
-template <bool B_MN>
+// SWIGLU: the expert feed-forward's first half in one kernel.  Two weight operands (gate: map_b, up: map_b2) of N = F
+// hidden units each; a tile covers 128 hidden units and its accumulator holds [gate 128 | up 128]; the epilogue writes
+// h = silu(gate) * up to C[rows, F] and, when GU is given, the bf16 pre-activations to GU[rows, 2F] (gate | up) for the
+// backward pass.  ACCUMULATE (plain variant): C += A * op(B_e) (the two input-gradient products of gate and up).
+template <bool B_MN, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        __nv_bfloat16* __restrict__ C, const int* __restrict__ offsets, int E, int N, int K,
-                        long long ldc, int* status) {
+                        const __grid_constant__ CUtensorMap map_b2, __nv_bfloat16* __restrict__ C,
+                        __nv_bfloat16* __restrict__ GU, const int* __restrict__ offsets, int E, int N, int K,
+                        long long ldc, long long ldgu, int accumulate, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -52,7 +57,8 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
   int* tile_start = reinterpret_cast<int*>(bar_gen + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_blocks = (N + BN - 1) / BN;
+  constexpr int TN = SWIGLU ? BN / 2 : BN;  // output columns (hidden units) per tile
+  const int n_blocks = (N + TN - 1) / TN;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -62,6 +68,7 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (SWIGLU) tma_prefetch_desc(&map_b2);
     tilemath::grouped_tile_starts(offsets, E, BM, tile_start);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -83,7 +90,19 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
           const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_STAGE_BYTES;
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, tl.row0);
-          if (!B_MN) {
+          if constexpr (SWIGLU) {
+            if (!B_MN) {  // rows 0..127 of the B tile: gate weights, rows 128..255: the matching up weights
+              tma_load_2d(b_dst, &map_b, full_bar(s), kb * BK, tl.e * N + tl.nb * TN);
+              tma_load_2d(b_dst + TN * BK * 2, &map_b2, full_bar(s), kb * BK, tl.e * N + tl.nb * TN);
+            } else {
+#pragma unroll
+              for (int c = 0; c < TN / 64; ++c) {
+                tma_load_2d(b_dst + c * (64 * BK * 2), &map_b, full_bar(s), tl.nb * TN + 64 * c, tl.e * K + kb * BK);
+                tma_load_2d(b_dst + (TN / 64 + c) * (64 * BK * 2), &map_b2, full_bar(s), tl.nb * TN + 64 * c,
+                            tl.e * K + kb * BK);
+              }
+            }
+          } else if (!B_MN) {
             tma_load_2d(b_dst, &map_b, full_bar(s), kb * BK, tl.e * N + tl.nb * BN);
           } else {
 #pragma unroll
@@ -133,16 +152,42 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (!mbar_wait(tfull_bar(acc), (tile_iter >> 1) & 1, status, KF_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int r = quarter * 32 + lane;
-      const int col0 = tl.nb * BN;
+      const int col0 = tl.nb * TN;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       __nv_bfloat16* c_row = C + size_t(tl.row0 + r) * ldc + col0;
+      if constexpr (SWIGLU) {
+        __nv_bfloat16* gu_row = GU ? GU + size_t(tl.row0 + r) * ldgu + col0 : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
-        tmem_ld_wait();
-        const int valid_cols = min(32, N - (col0 + c * 32));
-        if (r < tl.valid && valid_cols > 0) store_chunk<__nv_bfloat16>(c_row + c * 32, v, valid_cols, false, nullptr);
+        for (int c = 0; c < TN / 32; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c * 32, g);
+          tmem_ld_32x32(t_row + TN + c * 32, u);
+          tmem_ld_wait();
+          const int valid_cols = min(32, N - (col0 + c * 32));
+          if (r < tl.valid && valid_cols > 0) {
+            if (gu_row) {
+              store_chunk<__nv_bfloat16>(gu_row + c * 32, g, valid_cols, false, nullptr);
+              store_chunk<__nv_bfloat16>(gu_row + N + c * 32, u, valid_cols, false, nullptr);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {  // the activation sees the bf16 pre-activations, like the two-kernel path
+              const float gf = __bfloat162float(__float2bfloat16(__uint_as_float(g[i])));
+              const float uf = __bfloat162float(__float2bfloat16(__uint_as_float(u[i])));
+              g[i] = __float_as_uint(gf / (1.f + __expf(-gf)) * uf);
+            }
+            store_chunk<__nv_bfloat16>(c_row + c * 32, g, valid_cols, false, nullptr);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const int valid_cols = min(32, N - (col0 + c * 32));
+          if (r < tl.valid && valid_cols > 0)
+            store_chunk<__nv_bfloat16>(c_row + c * 32, v, valid_cols, accumulate != 0, nullptr);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -160,13 +205,35 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
 
 extern "C" void* kf_status_device_ptr();
 
+namespace kf {
+namespace grp {
+template <bool B_MN, bool SWIGLU>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* C, void* GU, const void* offsets,
+                  int E, int N, int K, long long ldc, long long ldgu, int accumulate, int grid, cudaStream_t st) {
+  auto kern = kf_grouped_gemm_tcgen05<B_MN, SWIGLU>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
+  kern<<<grid, THREADS, SMEM, st>>>(ma, mb, mb2, reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<__nv_bfloat16*>(GU),
+                                    reinterpret_cast<const int*>(offsets), E, N, K, ldc, ldgu, accumulate, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+}  // namespace grp
+}  // namespace kf
+
 extern "C" {
 
-// C[rows, N] = grouped A[rows, K] x B_e.  offsets: int32[E + 1] on the device (offsets[0] = 0, offsets[E] <= rows).
+// C[rows, N] (+)= grouped A[rows, K] x B_e.  offsets: int32[E + 1] on the device (offsets[0] = 0, offsets[E] <= rows;
+// rows past offsets[E] are neither read nor written, so C may be sized by an upper bound known on the host).
 //   b_mn == 0: B is [E][N][K] (K contiguous);  b_mn == 1: B is [E][K][N] (N contiguous; K must be a multiple of 64).
-//   lda / ldc in elements (multiples of 8); B is dense.  E <= 256.
-int kf_grouped_gemm_bf16(const void* A, const void* B, void* C, const void* offsets, int rows, int E, int N, int K,
-                         long long lda, long long ldc, int b_mn, int num_sms, void* stream) {
+//   lda / ldc in elements (multiples of 8); B is dense.  E <= 256.  accumulate != 0: add to C.
+int kf_grouped_gemm_acc_bf16(const void* A, const void* B, void* C, const void* offsets, int rows, int E, int N, int K,
+                             long long lda, long long ldc, int b_mn, int accumulate, int num_sms, void* stream) {
   using namespace kf;
   using namespace kf::grp;
   if (E < 1 || E > MAX_EXPERTS || (lda & 7) || (ldc & 7) || (K & 7) || (N & 7) || (b_mn && (K % BK))) return 5;
@@ -176,31 +243,44 @@ int kf_grouped_gemm_bf16(const void* A, const void* B, void* C, const void* offs
   if (rc) return 100 + rc;
   rc = b_mn ? make_map_2d_bf16(&mb, B, uint64_t(E) * K, N, N, 64, BK) : make_map_2d_bf16(&mb, B, uint64_t(E) * N, K, K, BK, BN);
   if (rc) return 200 + rc;
-  int* status = reinterpret_cast<int*>(kf_status_device_ptr());
   const int upper = ((rows + BM - 1) / BM + E) * ((N + BN - 1) / BN);  // at most one partial tile per expert
   const int grid = upper < num_sms ? upper : num_sms;
   cudaStream_t st = (cudaStream_t)stream;
+  return b_mn ? launch<true, false>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, grid, st)
+              : launch<false, false>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, grid, st);
+}
+
+int kf_grouped_gemm_bf16(const void* A, const void* B, void* C, const void* offsets, int rows, int E, int N, int K,
+                         long long lda, long long ldc, int b_mn, int num_sms, void* stream) {
+  return kf_grouped_gemm_acc_bf16(A, B, C, offsets, rows, E, N, K, lda, ldc, b_mn, 0, num_sms, stream);
+}
+
+// H[rows, F] = silu(A x Wg_e) * (A x Wu_e) per expert; GU (optional, [rows, 2F]) receives the pre-activations
+// (gate | up).  Wg / Wu: [E][F][K] (b_mn == 0) or [E][K][F] (b_mn == 1).  F, K multiples of 8 (64 for K when b_mn).
+int kf_grouped_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* H, void* GU, const void* offsets, int rows,
+                           int E, int F, int K, long long lda, long long ldh, long long ldgu, int b_mn, int num_sms,
+                           void* stream) {
+  using namespace kf;
+  using namespace kf::grp;
+  if (E < 1 || E > MAX_EXPERTS || (lda & 7) || (ldh & 7) || (GU && (ldgu & 7)) || (K & 7) || (F & 7) || (b_mn && (K % BK)))
+    return 5;
+  if (rows <= 0) return 0;
+  CUtensorMap ma, mg, mu;
+  int rc = make_map_2d_bf16(&ma, A, rows, K, lda, BK, BM);
+  if (rc) return 100 + rc;
   if (b_mn) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(kf_grouped_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-      if (e != cudaSuccess) return 300 + (int)e;
-      attr_set = true;
-    }
-    kf_grouped_gemm_tcgen05<true><<<grid, THREADS, SMEM, st>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),
-                                                              reinterpret_cast<const int*>(offsets), E, N, K, ldc, status);
+    rc = make_map_2d_bf16(&mg, Wg, uint64_t(E) * K, F, F, 64, BK);
+    if (!rc) rc = make_map_2d_bf16(&mu, Wu, uint64_t(E) * K, F, F, 64, BK);
   } else {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(kf_grouped_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-      if (e != cudaSuccess) return 300 + (int)e;
-      attr_set = true;
-    }
-    kf_grouped_gemm_tcgen05<false><<<grid, THREADS, SMEM, st>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),
-                                                               reinterpret_cast<const int*>(offsets), E, N, K, ldc, status);
+    rc = make_map_2d_bf16(&mg, Wg, uint64_t(E) * F, K, K, BK, BN / 2);
+    if (!rc) rc = make_map_2d_bf16(&mu, Wu, uint64_t(E) * F, K, K, BK, BN / 2);
   }
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : 400 + (int)e;
+  if (rc) return 200 + rc;
+  const int upper = ((rows + BM - 1) / BM + E) * ((F + BN / 2 - 1) / (BN / 2));
+  const int grid = upper < num_sms ? upper : num_sms;
+  cudaStream_t st = (cudaStream_t)stream;
+  return b_mn ? launch<true, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, grid, st)
+              : launch<false, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, grid, st);
 }
 
 }  // extern "C"

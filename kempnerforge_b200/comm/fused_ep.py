@@ -7,13 +7,16 @@ Two primitives, each one peer-store pass plus one bounded barrier on the stream:
 * ``return_rows``: compact rows -> back on the source rank, in the source's sorted order.
 
 The backward of one is the other.  Receive windows hold ``cap`` rows per source (the most a source can send: all of
-its tokens x top_k), so nothing is ever sized from data on the host; the only host read is the total number of rows a
-rank received, needed to allocate the expert activations exactly.
+its tokens x top_k), so nothing is ever sized from data on the host.  The expert activations are allocated for the same
+bound (``ep * cap`` rows; ``KF_EP_EXACT_ROWS=1`` restores the exact allocation at the price of one 4-byte host read per
+layer): the grouped kernels and the move kernels take their row ranges from device-side offsets, so the unused tail of
+those buffers is never read or written and no step of the exchange waits for the host.
 """
 
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -57,8 +60,9 @@ class EPContext:
         kc._check(kc.lib().kf_ep_layout(table.data_ptr(), self.ep, self.n_local, offsets_l.data_ptr(),
                                         chunk_dst.data_ptr(), chunk_src.data_ptr(), total.data_ptr(), kc._stream()),
                   "kf_ep_layout")
+        exact = os.environ.get("KF_EP_EXACT_ROWS", "0") == "1"
         return {"table": table, "offsets_l": offsets_l, "chunk_dst": chunk_dst, "chunk_src": chunk_src,
-                "total": int(total.item())}  # the one host read: how many rows this rank's experts received
+                "total": int(total.item()) if exact else self.ep * self.cap}  # rows to allocate (exact or the bound)
 
     def compact(self, lay: dict, cols: int) -> torch.Tensor:
         out = torch.empty((lay["total"], cols), dtype=torch.bfloat16, device=self.table.tensor.device)

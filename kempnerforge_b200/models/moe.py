@@ -136,10 +136,11 @@ class MoEMLP(nn.Module):
         ex = self.experts
         return list(ex.values()) if isinstance(ex, nn.ModuleDict) else list(ex)
 
-    def run_experts(self, x_sorted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
-        """Grouped expert FFN over rows already sorted by (local) expert."""
+    def run_experts(self, x_sorted: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor | None = None) -> torch.Tensor:
+        """Grouped expert FFN over rows already sorted by (local) expert.  ``offsets`` (int32 (E + 1), device): the
+        row ranges when they are already known; ``x_sorted`` may then be longer than ``offsets[-1]``."""
         gate, up, down, layout = self.expert_weights()
-        return grouped.grouped_ffn(x_sorted, counts, gate, up, down, layout, self._activation())
+        return grouped.grouped_ffn(x_sorted, counts, gate, up, down, layout, self._activation(), offsets=offsets)
 
     def _local_forward(self, x_flat, weights, indices):
         t, k = indices.shape
@@ -151,7 +152,7 @@ class MoEMLP(nn.Module):
             offsets, row_of_slot, slot_of_row = moe_ops.sort_by_expert(indices, self.num_experts)
             counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
             x_sorted = moe_ops.gather_rows(x_flat, slot_of_row, row_of_slot, k)
-            y = self.run_experts(x_sorted, counts)
+            y = self.run_experts(x_sorted, counts, offsets=offsets)
             return moe_ops.combine_rows(y, weights, row_of_slot, slot_of_row)
         flat_e = indices.reshape(-1)
         order = torch.argsort(flat_e, stable=True)

@@ -79,6 +79,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_moe_combine_bf16": [vp, vp, vp, i, i, i, vp, vp],
         "kf_moe_combine_bwd_bf16": [vp, vp, vp, vp, i, i, i, vp, vp, vp],
         "kf_grouped_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
+        "kf_grouped_gemm_acc_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, vp],
+        "kf_grouped_swiglu_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp],
+        "kf_swiglu_bwd_ragged_bf16": [vp, vp, vp, ll, vp, i, vp],
         "kf_grouped_wgrad_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, vp],
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
         "kf_gemm_rs_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, i, i, vp],
@@ -559,9 +562,43 @@ def moe_combine_bwd(dout: torch.Tensor, y: torch.Tensor, slot_of_row: torch.Tens
     return dy, dw
 
 
-def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, b_mn: bool, out: torch.Tensor | None = None):
+def grouped_swiglu(a: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, offsets: torch.Tensor, b_mn: bool,
+                   want_gu: bool = True):
+    """(h, gu): h = silu(a @ Wg_e) * (a @ Wu_e) over the ragged expert row ranges in ONE grouped GEMM (activation in
+    its epilogue); ``gu`` (rows, 2F) keeps the bf16 pre-activations (gate | up) when ``want_gu``.  Weights (E, F, K)
+    or, with ``b_mn``, (E, K, F).  Rows past ``offsets[E]`` are left untouched."""
+    rows, k = a.shape
+    e = wg.shape[0]
+    f = wg.shape[2] if b_mn else wg.shape[1]
+    assert wg.shape == wu.shape and wg.is_contiguous() and wu.is_contiguous() and a.stride(1) == 1
+    h = torch.empty((rows, f), dtype=torch.bfloat16, device=a.device)
+    gu = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device=a.device) if want_gu else None
+    _check(lib().kf_grouped_swiglu_bf16(a.data_ptr(), wg.data_ptr(), wu.data_ptr(), h.data_ptr(),
+                                        gu.data_ptr() if gu is not None else None, offsets.data_ptr(), rows, e, f, k,
+                                        a.stride(0), f, 2 * f, int(b_mn), sm_count(), _stream()), "kf_grouped_swiglu_bf16")
+    return h, gu
+
+
+def grouped_swiglu_supported(a: torch.Tensor, wg: torch.Tensor, b_mn: bool) -> bool:
+    return getattr(lib(), "kf_grouped_swiglu_bf16", None) is not None and grouped_gemm_supported(a, wg, b_mn) \
+        and not os.environ.get("KF_DISABLE_GROUPED_SWIGLU")
+
+
+def swiglu_bwd_ragged(dh: torch.Tensor, gu: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """dgu (rows, 2F) of h = silu(gate) * up for the rows below ``offsets[-1]`` (a device int; later rows untouched)."""
+    rows, f = dh.shape
+    assert gu.shape == (rows, 2 * f) and dh.is_contiguous() and gu.is_contiguous()
+    dgu = torch.empty_like(gu)
+    _check(lib().kf_swiglu_bwd_ragged_bf16(dh.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, offsets[-1:].data_ptr(), f,
+                                           _stream()), "kf_swiglu_bwd_ragged_bf16")
+    return dgu
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, b_mn: bool, out: torch.Tensor | None = None,
+                 accumulate: bool = False):
     """Ragged grouped GEMM: rows ``offsets[e]:offsets[e+1]`` of ``a`` (rows, K) are multiplied by expert e's matrix.
-    ``b`` is (E, N, K) when ``b_mn`` is False and (E, K, N) when True; ``offsets`` is int32 (E + 1) on the device."""
+    ``b`` is (E, N, K) when ``b_mn`` is False and (E, K, N) when True; ``offsets`` is int32 (E + 1) on the device.
+    ``accumulate``: add to ``out``."""
     rows, k = a.shape
     e = b.shape[0]
     n = b.shape[2] if b_mn else b.shape[1]
@@ -569,9 +606,9 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, b_mn: 
     assert offsets.dtype == torch.int32 and offsets.numel() == e + 1
     if out is None:
         out = torch.empty((rows, n), dtype=torch.bfloat16, device=a.device)
-    _check(lib().kf_grouped_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), rows, e, n, k,
-                                      a.stride(0), out.stride(0), int(b_mn), sm_count(), _stream()),
-           "kf_grouped_gemm_bf16")
+    _check(lib().kf_grouped_gemm_acc_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), rows, e, n, k,
+                                          a.stride(0), out.stride(0), int(b_mn), int(accumulate), sm_count(), _stream()),
+           "kf_grouped_gemm_acc_bf16")
     return out
 
 

@@ -58,6 +58,42 @@ class _GroupedLinearFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+class _GroupedSwiGLUFn(torch.autograd.Function):
+    """silu(x @ Wg_e) * (x @ Wu_e) over ragged expert rows: one grouped GEMM with the activation in its epilogue
+    forward; backward = one ragged SwiGLU-gradient kernel, two input-gradient grouped GEMMs (the second accumulating
+    into the first's output) and two ragged weight-gradient reductions over the strided halves of d[gate | up].
+    Nothing reads a row count on the host: buffers may be sized by an upper bound, ``offsets`` bounds the work."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu, offsets, layout):
+        kc = _cuda_binding
+        h, gu = kc.grouped_swiglu(x, wg, wu, offsets, b_mn=(layout == "kn"), want_gu=True)
+        ctx.save_for_backward(x, wg, wu, offsets, gu)
+        ctx.layout = layout
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        kc = _cuda_binding
+        x, wg, wu, offsets, gu = ctx.saved_tensors
+        layout = ctx.layout
+        f = dh.shape[1]
+        dgu = kc.swiglu_bwd_ragged(dh.contiguous(), gu, offsets)
+        dgate, dup = dgu[:, :f], dgu[:, f:]
+        dx = dwg = dwu = None
+        if ctx.needs_input_grad[0]:
+            dx = kc.grouped_gemm(dgate, wg, offsets, b_mn=(layout == "nk"))
+            kc.grouped_gemm(dup, wu, offsets, b_mn=(layout == "nk"), out=dx, accumulate=True)
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            def wgrad(d):
+                a, b = (x, d) if layout == "kn" else (d, x)
+                if kc.grouped_wgrad_supported(a, b):
+                    return kc.grouped_wgrad(a, b, offsets)
+                return torch._grouped_mm(a.contiguous().t(), b.contiguous(), offs=offsets[1:])
+            dwg, dwu = wgrad(dgate), wgrad(dup)
+        return dx, dwg, dwu, None, None
+
+
 def _native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
     from kempnerforge_b200.ops import functional as _F
 
@@ -94,8 +130,26 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, layou
     return out
 
 
-def grouped_ffn(x_sorted, counts, gate_w, up_w, down_w, layout: str, activation=None) -> torch.Tensor:
-    """Expert feed-forward over expert-sorted rows: SwiGLU when ``gate_w`` is given, else act(up) -> down."""
+def offsets_of(counts: torch.Tensor) -> torch.Tensor:
+    off = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
+    off[1:] = counts.cumsum(0)
+    return off
+
+
+def grouped_ffn(x_sorted, counts, gate_w, up_w, down_w, layout: str, activation=None, offsets=None) -> torch.Tensor:
+    """Expert feed-forward over expert-sorted rows: SwiGLU when ``gate_w`` is given, else act(up) -> down.
+    ``offsets`` (int32 (E + 1) on the device) may be passed instead of being derived from ``counts``; ``x_sorted`` may
+    then have more rows than ``offsets[-1]`` (the extra rows are ignored)."""
+    if (gate_w is not None and _native_ok(x_sorted, up_w, layout) and _native_ok(x_sorted, gate_w, layout)
+            and _cuda_binding.grouped_swiglu_supported(x_sorted, gate_w, layout == "kn")):
+        f = up_w.shape[2] if layout == "kn" else up_w.shape[1]
+        down_ok = down_w.dim() == 3 and down_w.is_contiguous() and _cuda_binding.grouped_gemm_supported(
+            torch.empty((0, f), dtype=x_sorted.dtype, device=x_sorted.device), down_w, layout == "kn")
+        if down_ok and (layout != "nk" or (down_w.shape[1] % 64 == 0)):
+            off = offsets if offsets is not None else offsets_of(counts)
+            xs = x_sorted if x_sorted.is_contiguous() else x_sorted.contiguous()
+            hidden = _GroupedSwiGLUFn.apply(xs, gate_w, up_w, off, layout)
+            return _GroupedLinearFn.apply(hidden, down_w, off, layout)
     up = grouped_linear(x_sorted, up_w, counts, layout)
     if gate_w is not None:
         hidden = F.silu(grouped_linear(x_sorted, gate_w, counts, layout)) * up

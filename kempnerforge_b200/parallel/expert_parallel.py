@@ -155,7 +155,7 @@ def _ep_forward_peer_memory(x_flat, weights, indices, moe, ctx) -> torch.Tensor:
     offsets_g, row_of_slot, slot_of_row = moe_ops.sort_by_expert(indices, e_global)
     x_c, offsets_l, lay = fused_ep.dispatch(x_flat, slot_of_row, row_of_slot, k, offsets_g, ctx)
     counts_l = (offsets_l[1:] - offsets_l[:-1]).to(torch.int64)
-    y_c = moe.run_experts(x_c, counts_l)
+    y_c = moe.run_experts(x_c, counts_l, offsets=offsets_l)
     y_sorted = fused_ep.return_rows(y_c, offsets_g, t * k, lay, ctx)
     return moe_ops.combine_rows(y_sorted, weights, row_of_slot, slot_of_row)
 

@@ -994,3 +994,49 @@ def test_moe_capacity_mask_kernel_matches_the_reference_rule(native_lib, shape):
             rows = (ic[:, j] == ex).nonzero(as_tuple=True)[0]
             want[rows[cap:], j] = 0.0
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("counts,extra", [([128, 128, 128, 128], 0), ([5, 0, 300, 77, 130, 1], 0), ([1000, 24], 200), ([0, 0, 513], 64)])
+def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, extra, monkeypatch):
+    """Expert feed-forward (gate / up grouped GEMM with the SwiGLU epilogue, ragged SwiGLU gradient, accumulating
+    input-gradient GEMMs) against an fp32 per-expert reference.  ``extra`` rows beyond the last expert stand for a
+    buffer sized by an upper bound: they must be ignored.  No row count may be read on the host."""
+    from kempnerforge_b200.ops import grouped
+
+    torch.manual_seed(1)
+    e, d, f = len(counts), 192, 256
+    rows = sum(counts)
+    x = _rand(rows + extra, d)
+    x[rows:] = float("nan")
+    x.requires_grad_(True)
+    shape_in, shape_out = ((e, d, f), (e, f, d)) if layout == "kn" else ((e, f, d), (e, d, f))
+    wg, wu = (_rand(*shape_in, scale=0.05).requires_grad_(True) for _ in range(2))
+    wd = _rand(*shape_out, scale=0.05).requires_grad_(True)
+    cnt = torch.tensor(counts, device="cuda")
+    off = grouped.offsets_of(cnt)
+
+    def boom(*a, **k):
+        raise AssertionError("host read inside the expert feed-forward")
+
+    monkeypatch.setattr(torch.Tensor, "item", boom)
+    monkeypatch.setattr(torch.Tensor, "tolist", boom)
+    y = grouped.grouped_ffn(x, cnt, wg, wu, wd, layout, offsets=off)
+    g = _rand(rows + extra, d)
+    y.backward(g)
+    monkeypatch.undo()
+    assert native_lib.read_status() == 0
+    xf = x.detach()[:rows].float().requires_grad_(True)
+    wgf, wuf, wdf = (w.detach().float().requires_grad_(True) for w in (wg, wu, wd))
+    outs, start = [], 0
+    for i, c in enumerate(counts):
+        t = (lambda w: w[i] if layout == "kn" else w[i].t())
+        xe = xf[start:start + c]
+        outs.append((torch.nn.functional.silu(xe @ t(wgf)) * (xe @ t(wuf))) @ t(wdf))
+        start += c
+    want = torch.cat(outs)
+    want.backward(g[:rows].float())
+    _close(y[:rows], want, rtol=3e-2, atol=3e-2)
+    _close(x.grad[:rows], xf.grad, rtol=3e-2, atol=3e-2)
+    for got, ref_w in ((wg, wgf), (wu, wuf), (wd, wdf)):
+        _close(got.grad, ref_w.grad, rtol=4e-2, atol=4e-2)

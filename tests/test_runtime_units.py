@@ -321,3 +321,14 @@ def test_check_env_exit_code_follows_required_misses(monkeypatch, capsys):
     assert "[OK  ] hf" in capsys.readouterr().out
     with pytest.raises(SystemExit):
         ce.main(["--non-interactive"])
+
+
+def test_codebase_map_is_in_sync_with_the_source():
+    """``codebase-map.json`` is generated from the source tree; a stale file fails here."""
+    import subprocess
+    import sys as _sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([_sys.executable, str(root / "scripts" / "build_codebase_map.py"), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
