@@ -68,6 +68,7 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
   auto pv_done = [&](int tile) { return bar_base + 8u * (13 + tile); };
   const uint32_t drain_bar = bar_base + 8u * 15;
   auto o_final = [&](int tile) { return bar_base + 8u * (16 + tile); };  // every MMA of the tile has retired
+  auto p_half = [&](int tile) { return bar_base + 8u * (19 + tile); };   // first 64 keys of P are in tensor memory
   const uint32_t tmem_slot = bar_base + 8u * 18;
   uint8_t* bar_generic = smem_raw + (smem_base - smem_u32(smem_raw)) + C::N_TILES_SMEM * C::TILE_BYTES;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * 18);
@@ -99,6 +100,7 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(v_empty(i), 1);
       mbar_init(s_full(i), 1);
       mbar_init(p_full(i), 4);
+      mbar_init(p_half(i), 4);
       mbar_init(pv_done(i), 1);
       mbar_init(o_final(i), 1);
     }
@@ -193,15 +195,23 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
         bool k_next_ready = false;
         for (int tile = 0; tile < 2 && ok; ++tile) {
           if (j >= n_of[tile]) continue;
-          if (!mbar_wait(p_full(tile), j & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          // O_tile += P_tile V_j : A = P from tensor memory, B = V with the head dim contiguous (MN-major).  The
+          // softmax warps hand P over in two halves: the products over the first 64 keys run while the
+          // exponentials of the last 64 are still being computed.
+          if (!mbar_wait(p_half(tile), j & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
           if (!mbar_wait(v_full(st), (j >> 1) & 1, status, KF_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          // O_tile += P_tile V_j : A = P from tensor memory, B = V with the head dim contiguous (MN-major)
 #pragma unroll
-          for (int kk = 0; kk < BLK_N / 16; ++kk)
+          for (int kk = 0; kk < BLK_N / 32; ++kk)
             tc_mma_f16_ts(o_col(tile), s_col(tile) + kk * 8,
                           umma_desc_sw128(v_smem + st * C::TILE_BYTES + kk * 2048, C::BLOCK_BYTES, 1024), idesc_o,
                           (j | kk) != 0);
+          if (!mbar_wait(p_full(tile), j & 1, status, KF_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = BLK_N / 32; kk < BLK_N / 16; ++kk)
+            tc_mma_f16_ts(o_col(tile), s_col(tile) + kk * 8,
+                          umma_desc_sw128(v_smem + st * C::TILE_BYTES + kk * 2048, C::BLOCK_BYTES, 1024), idesc_o, 1u);
           tc_commit(pv_done(tile));
           if (j + 1 == n_of[tile]) tc_commit(o_final(tile));  // a phase of its own: cannot be mistaken for an earlier tile
           // the next score tile of this query tile follows at once (its buffer's P was read by the MMAs just issued)
@@ -322,6 +332,12 @@ kf_attn_fwd2_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_con
           pk[i] = pack_bf16(e0, e1);
         }
         tmem_st_32x16(t_s + c * 16, pk);
+        if (c == 1) {  // the first 64 keys are in place: the MMA warp may start O += P V on them
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_half(tile));
+        }
       }
       {
         float a0, a1;

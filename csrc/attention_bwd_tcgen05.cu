@@ -12,11 +12,15 @@
 //   dK  += dS^T Q_i                      (A from smem, 128 x 128 accumulator)
 //   dQ_i^T = K^T dS                      (128 head-dim rows x 64 queries; added to an fp32 dQ by a bulk reduction)
 //
-//   warp 0   : TMA producer (K, V once; Q_i / dO_i ring of three stages)
-//   warp 1   : MMA issuer
-//   warps 2-5: softmax (one thread per key row) and the final dK / dV store
-//   warps 6-9: dQ reduction (TMEM -> shared-memory tile -> one cp.reduce.async.bulk.tensor add per tile;
-//              or, as a fallback mode, red.global.add.f32 per element)
+//   warp 0     : TMA producer (K, V once; Q_i / dO_i ring of three stages)
+//   warp 1     : MMA issuer
+//   warps 2-5  : softmax of queries 0..31 of the tile (one thread per key row) and the final dK / dV store
+//   warps 10-13: softmax of queries 32..63 (the same key rows): two warps per scheduler hide each other's
+//                exp2 / conversion latencies, and 32 scores + 32 dP per thread leave registers for instruction-level
+//                parallelism (with 64 + 64 per thread the P / dS arithmetic was latency bound: 2400 of the 4100
+//                cycles of an iteration)
+//   warps 6-9  : dQ reduction (TMEM -> shared-memory tile -> one cp.reduce.async.bulk.tensor add per tile;
+//                or, as a fallback mode, red.global.add.f32 per element)
 //
 // D_i = rowsum(dO_i * O_i) comes from a small pre-pass; a post-pass converts the fp32 dQ to bf16.
 // Replaces the backward of F.scaled_dot_product_attention (kempnerforge/model/attention.py:227-231) for the
@@ -29,7 +33,7 @@ namespace attnb {
 constexpr int HD = 128;
 constexpr int BLK_K = 128;  // keys per CTA
 constexpr int BLK_Q = 64;   // queries per iteration
-constexpr int THREADS = 320;
+constexpr int THREADS = 448;
 constexpr int TMEM_COLS = 512;
 constexpr int ST_COL = 0;     // S^T buffers 0 / 1 (fp32, 64 cols each); P^T (bf16 pairs, 32 cols) aliases each start
 constexpr int DPT_COL = 128;  // dP^T (fp32, 64 cols)
@@ -140,10 +144,10 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(stage_free(st), 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 4);
+    mbar_init(ds_ready, 8);
     mbar_init(mma_done, 1);
     mbar_init(dq_free, 4);
-    mbar_init(sdp_taken, 4);
+    mbar_init(sdp_taken, 8);
     mbar_init(final_bar, 1);
     mbar_init(ds_free(0), 1);
     mbar_init(ds_free(1), 1);
@@ -266,63 +270,74 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_wait(drain_bar, 0, status, KF_ERR_WAIT_DRAIN);
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------ softmax warps: one thread per key row
+  } else if (warp < 6 || warp >= 10) {
+    // ------------------------------------------------------------ softmax warps: one thread per (key row, half of the queries)
+    constexpr int HQ = BLK_Q / 2;             // queries per thread
+    const int half = warp >= 10 ? 1 : 0;
     const int quarter = warp & 3;
     const int r_local = quarter * 32 + lane;  // key row of this thread
     const int kpos = k0 + r_local;
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
-    const int t128 = threadIdx.x - 64;        // 0..127 inside the softmax group
+    const int t128 = half == 0 ? threadIdx.x - 64 : 128;   // the first group's 128 threads fetch the row statistics
     int doc_k = 0;
     if (HAS_DOC) doc_k = kpos < Sk ? doc_ids[size_t(b) * Sk + kpos] : -2;
     bool ok = true;
+    // statistics of the 64 queries of iteration `t` (lse in log2 units for threads 0..63, D for 64..127), fetched one
+    // iteration ahead so that the global-memory latency hides under the arithmetic of the current tile
+    auto fetch_stat = [&](int t) -> float {
+      if (t128 >= 128 || t >= n_iter) return 0.f;
+      const int hq_t = hk * group + t / n_i;
+      const int qq = (i_start + t % n_i) * BLK_Q + (t128 & 63);
+      const size_t idx = (size_t(b) * H + hq_t) * Sq + qq;
+      if (t128 < 64) return qq < Sq ? LSE[idx] * 1.4426950408889634f : INFINITY;  // +inf -> P = 0 for padding rows
+      return qq < Sq ? Dsum[idx] : 0.f;
+    };
+    float stat_next = fetch_stat(0);
     for (int it = 0; it < n_iter; ++it) {
       const int hq = hk * group + it / n_i;
       const int q0 = (i_start + it % n_i) * BLK_Q;
-      // row statistics of the 64 queries: lse (in log2 units) and D, shared through smem
       float* stat = stat_smem + (it & 1) * 128;
       int* dq_doc = docq_smem + (it & 1) * 64;
-      {
-        const int qq = q0 + (t128 & 63);
-        const size_t idx = (size_t(b) * H + hq) * Sq + qq;
-        if (t128 < 64) {
-          stat[t128] = qq < Sq ? LSE[idx] * 1.4426950408889634f : INFINITY;  // +inf -> P = 0 for padding rows
-          if (HAS_DOC) dq_doc[t128] = qq < Sq ? doc_ids[size_t(b) * Sq + qq] : -1;
-        } else {
-          stat[t128] = qq < Sq ? Dsum[idx] : 0.f;
+      if (t128 < 128) {
+        stat[t128] = stat_next;
+        if (HAS_DOC && t128 < 64) {
+          const int qq = q0 + t128;
+          dq_doc[t128] = qq < Sq ? doc_ids[size_t(b) * Sq + qq] : -1;
         }
       }
-      group_sync(1, 128);
+      group_sync(1, 256);
+      stat_next = fetch_stat(it + 1);
       if (ok && !mbar_wait(sdp_full, it & 1, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
       tc_fence_after();
       const uint32_t t_s = t_lane + ST_COL + (it & 1) * BLK_Q;
-      uint32_t sv[BLK_Q], dp[BLK_Q];
-      tmem_ld_32x32_at(t_s, sv);
-      tmem_ld_32x32_at(t_s + 32, sv + 32);
-      tmem_ld_32x32_at(t_lane + DPT_COL, dp);
-      tmem_ld_32x32_at(t_lane + DPT_COL + 32, dp + 32);
+      uint32_t sv[HQ], dp[HQ];
+      tmem_ld_32x32_at(t_s + half * HQ, sv);
+      tmem_ld_32x32_at(t_lane + DPT_COL + half * HQ, dp);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(sdp_taken);  // dP^T is in registers: the next tile's dP^T may be computed
+      // P^T overwrites the first 32 columns of S^T: nobody may store before both warps of a key-row quarter have
+      // loaded their scores
+      group_sync(3, 256);
       const bool tile_masked = HAS_DOC || (CAUSAL && q0 < k0 + BLK_K - 1) || (k0 + BLK_K > Sk) || (q0 + BLK_Q > Sq);
-      uint32_t pk[BLK_Q / 2], dsk[BLK_Q / 2];
+      uint32_t pk[HQ / 2], dsk[HQ / 2];
 #pragma unroll
-      for (int i4 = 0; i4 < BLK_Q / 4; ++i4) {
+      for (int i4 = 0; i4 < HQ / 4; ++i4) {
         // four queries per step: their lse / D come as two 16-byte broadcast reads instead of eight 4-byte ones
-        const float4 l4 = *reinterpret_cast<const float4*>(stat + 4 * i4);
-        const float4 d4 = *reinterpret_cast<const float4*>(stat + 64 + 4 * i4);
+        const float4 l4 = *reinterpret_cast<const float4*>(stat + half * HQ + 4 * i4);
+        const float4 d4 = *reinterpret_cast<const float4*>(stat + 64 + half * HQ + 4 * i4);
         const float lse4[4] = {l4.x, l4.y, l4.z, l4.w}, dd4[4] = {d4.x, d4.y, d4.z, d4.w};
         float p[4], ds[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int c = 4 * i4 + e;
+          const int c = 4 * i4 + e;           // index inside this thread's half
           float pe = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -lse4[e]));
           if (tile_masked) {
-            const int qpos = q0 + c;
+            const int qpos = q0 + half * HQ + c;
             bool vis = kpos < Sk && qpos < Sq;
             if (CAUSAL) vis = vis && kpos <= qpos;
-            if (HAS_DOC) vis = vis && dq_doc[c] == doc_k;
+            if (HAS_DOC) vis = vis && dq_doc[half * HQ + c] == doc_k;
             pe = vis ? pe : 0.f;
           }
           p[e] = pe;
@@ -333,14 +348,8 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         dsk[2 * i4] = pack_bf16(ds[0], ds[1]);
         dsk[2 * i4 + 1] = pack_bf16(ds[2], ds[3]);
       }
-      // P^T over the start of S^T (every score of this row is in registers)
-      {
-        uint32_t lo[16], hi[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
-        tmem_st_32x16(t_s, lo);
-        tmem_st_32x16(t_s + 16, hi);
-      }
+      // P^T over the start of S^T (bf16 pairs: 16 columns per 32 queries)
+      tmem_st_32x16(t_s + half * (HQ / 2), pk);
       // dS^T into shared memory, 128B-swizzled rows (16-byte chunk c of row r lives at chunk c ^ (r % 8));
       // the previous iteration's dK / dQ MMAs must have finished reading it
       // (two buffers: the MMAs of iteration it-2 were the last readers of this one)
@@ -348,9 +357,9 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       {
         uint8_t* row_ptr = ds_gen + (it & 1) * DS_BYTES + r_local * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {   // this thread's 32 queries = four 16-byte chunks of the row
           uint4 w = make_uint4(dsk[4 * c], dsk[4 * c + 1], dsk[4 * c + 2], dsk[4 * c + 3]);
-          *reinterpret_cast<uint4*>(row_ptr + ((c ^ (r_local & 7)) << 4)) = w;
+          *reinterpret_cast<uint4*>(row_ptr + (((half * 4 + c) ^ (r_local & 7)) << 4)) = w;
         }
       }
       fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
@@ -359,7 +368,8 @@ kf_attn_bwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
     }
-    // ---- epilogue: dK / dV accumulators -> bf16 rows of the key tile
+    // ---- epilogue: dK / dV accumulators -> bf16 rows of the key tile (first softmax group: one thread per key row)
+    if (half != 0) ok = false;
     if (ok && n_iter > 0 && !mbar_wait(final_bar, 0, status, KF_ERR_WAIT_TMEM_FULL)) ok = false;
     if (ok && cosT != nullptr && n_iter > 0) {
       // dK leaves through the inverse rotary embedding (the forward rotated K after the projection): columns

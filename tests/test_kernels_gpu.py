@@ -947,7 +947,7 @@ def test_vocab_parallel_cross_entropy_kernels_match_full_cross_entropy(native_li
     """Two vocabulary shards handled by the two-phase kernels (statistics -> exchange -> gradient in place), combined
     the way the ranks combine them, against the fp32 cross entropy over the whole vocabulary."""
     torch.manual_seed(3)
-    t, v, tp = 300, 1000, 2
+    t, v, tp = 300, 1024, 2
     vl = v // tp
     logits = (_rand(t, v) * 4).contiguous()
     labels = torch.randint(0, v, (t,), device=DEV)
