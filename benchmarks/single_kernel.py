@@ -8,7 +8,10 @@ subject of a profiler capture as well:
 Workloads (Llama-3-8B shapes unless noted): gemm (CTA-pair tiles, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu,
 gemm_rope (QKV projection with the rotary embedding in the epilogue), grouped / grouped_wgrad (8 experts,
 dim 2048 x 5632), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
-rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit).  Prints one JSON line.
+rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_gather (QKV projection whose weight is gathered
+inside the kernel from 8 parameter shards; on one GPU the shards are 8 local buffers, so the kernel and its copy
+warps run exactly as in a job but the "peer" loads stay on this GPU), symm_pull, symm_rs_shard (one block unit, 8
+emulated ranks).  Prints one JSON line.
 """
 
 from __future__ import annotations
@@ -69,6 +72,39 @@ def build(target: str, K, args):
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = dqkv[:, :, :h], dqkv[:, :, h:h + hkv], dqkv[:, :, h + hkv:]
         return (lambda: K.attn_bwd(dout, q, k, v, out, lse, True, None, sc, dq=dq, dk=dk, dv=dv)), fwd_flops * 5 // 2, 0
+    if target in ("gemm_gather", "symm_pull", "symm_rs_shard"):
+        import ctypes
+
+        class Peers:   # stands in for a symmetric-memory buffer: eight local tensors play the eight ranks
+            def __init__(self, tensors, rank):
+                self.world, self.rank, self.multicast_ptr = len(tensors), rank, None
+                self.peer_ptrs = (ctypes.c_longlong * 8)(*[t.data_ptr() for t in tensors])
+                self.keep = tensors
+
+        world = 8
+        if target == "gemm_gather":
+            s_len, h, hkv, hd, k = 4096, 32, 8, 128, 4096
+            rows = [h * hd, hkv * hd, hkv * hd]
+            a = torch.randn(2 * s_len, k, device=dev, dtype=bf)
+            offs, acc = [], 0
+            for r in rows:
+                offs.append(acc)
+                acc += r * k // world
+            shards = [torch.randn(acc, device=dev, dtype=bf) * 0.02 for _ in range(world)]
+            ang = torch.outer(torch.arange(s_len, device=dev).float(), 500000.0 ** (-torch.arange(0, hd, 2, device=dev).float() / hd))
+            cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+            plan = {"symm": Peers(shards, 3), "seg_rows": rows, "seg_src": offs,
+                    "stage": torch.empty(sum(rows) * k, device=dev, dtype=bf), "flags": torch.zeros(256, dtype=torch.int32, device=dev)}
+            rope = (cos, sin, s_len, (h + hkv) * hd, hd)
+            return (lambda: K.gemm_gather(a, plan, sum(rows), epi=2, rope=rope)), 2 * 8192 * 6144 * 4096, 0
+        unit = 218_103_808
+        if target == "symm_pull":
+            shards = [torch.randn(unit // world, device=dev, dtype=bf) for _ in range(world)]
+            dst = torch.empty(unit, device=dev, dtype=bf)
+            return (lambda: K.symm_pull(Peers(shards, 3), [0], [unit], [0], dst)), 0, 2 * unit * 2
+        grads = [torch.randn(unit, device=dev, dtype=bf) for _ in range(world)]
+        out = torch.empty(unit // world, device=dev, dtype=bf)
+        return (lambda: K.symm_rs_shard(Peers(grads, 3), [0], [unit], [0], out, False)), 0, (world + 1) * (unit // world) * 2
     if target == "rmsnorm_bwd":
         x = torch.randn(16384, 4096, device=dev, dtype=bf)
         w = torch.ones(4096, device=dev, dtype=bf)
