@@ -18,6 +18,7 @@
 namespace kf {
 
 constexpr int MAX_PEERS = 8;
+constexpr int RS_UNROLL = 4;  // 16-byte vectors per thread and step in the peer-load kernels
 struct PeerPtrs {
   void* p[MAX_PEERS];
 };
@@ -65,37 +66,59 @@ kf_symm_rs_norm(PeerPtrs grads, const void* mc_grad, int world, int rank, long l
   const long long nvec = n >> 3;
   __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(grads.p[rank]) + lo;
   float ss = 0.f;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    float acc[8];
+  // RS_UNROLL vectors per thread and step, every rank's loads of a step issued before the first use: NVLink loads
+  // take microseconds, so the bytes in flight per thread set the bandwidth
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * RS_UNROLL) {
+    float acc[RS_UNROLL][8];
     if (mc_grad) {
-      ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grad) + lo + i * 8, acc);
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grad) + lo + i * 8, acc[u]);
+      }
     } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int u = 0; u < RS_UNROLL; ++u)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
       for (int r = 0; r < world; ++r) {  // fixed order: bit-identical results on every run
-        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + lo + i * 8);
-        float2 f;
-        f = unpack_bf16(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16(u.w); acc[6] += f.x; acc[7] += f.y;
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + lo;
+        uint4 v[RS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          v[u] = i < nvec ? *reinterpret_cast<const uint4*>(src + i * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u) {
+          float2 f;
+          f = unpack_bf16(v[u].x); acc[u][0] += f.x; acc[u][1] += f.y;
+          f = unpack_bf16(v[u].y); acc[u][2] += f.x; acc[u][3] += f.y;
+          f = unpack_bf16(v[u].z); acc[u][4] += f.x; acc[u][5] += f.y;
+          f = unpack_bf16(v[u].w); acc[u][6] += f.x; acc[u][7] += f.y;
+        }
       }
     }
-    uint4 o;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] *= inv_world;
-    o.x = pack_bf16(acc[0], acc[1]);
-    o.y = pack_bf16(acc[2], acc[3]);
-    o.z = pack_bf16(acc[4], acc[5]);
-    o.w = pack_bf16(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(mine + i * 8) = o;
-    // the norm is taken of the values the optimizer will read (after rounding to bf16)
-    float2 f;
-    f = unpack_bf16(o.x); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16(o.y); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16(o.z); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16(o.w); ss += f.x * f.x + f.y * f.y;
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      uint4 o;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[u][k] *= inv_world;
+      o.x = pack_bf16(acc[u][0], acc[u][1]);
+      o.y = pack_bf16(acc[u][2], acc[u][3]);
+      o.z = pack_bf16(acc[u][4], acc[u][5]);
+      o.w = pack_bf16(acc[u][6], acc[u][7]);
+      *reinterpret_cast<uint4*>(mine + i * 8) = o;
+      // the norm is taken of the values the optimizer will read (after rounding to bf16)
+      float2 f;
+      f = unpack_bf16(o.x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(o.y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(o.z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(o.w); ss += f.x * f.x + f.y * f.y;
+    }
   }
   const float total = block_sum_f(ss, red);
   if (threadIdx.x == 0) partial[blockIdx.x] = total;
@@ -200,14 +223,27 @@ __device__ __forceinline__ int seg_of(const SegTable& t, long long v) {
 __global__ void __launch_bounds__(256)
 kf_symm_pull(PeerPtrs shards, int world, SegTable t, __nv_bfloat16* __restrict__ dst) {
   const long long nvec = t.vec_start[t.n];
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-    const int s = seg_of(t, v);
-    const long long e = (v - t.vec_start[s]) * 8;   // element inside the parameter
-    const long long piece = t.len[s] / world;
-    const int owner = int(e / piece);
-    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[owner]) + t.shard[s] +
-                                                    (e - owner * piece));
-    *reinterpret_cast<uint4*>(dst + t.full[s] + e) = u;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * RS_UNROLL) {
+    uint4 q[RS_UNROLL];
+    long long dsti[RS_UNROLL];
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      const long long v = v0 + u * stride;
+      dsti[u] = -1;
+      if (v < nvec) {
+        const int s = seg_of(t, v);
+        const long long e = (v - t.vec_start[s]) * 8;   // element inside the parameter
+        const long long piece = t.len[s] / world;
+        const int owner = int(e / piece);
+        q[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[owner]) + t.shard[s] +
+                                               (e - owner * piece));
+        dsti[u] = t.full[s] + e;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u)
+      if (dsti[u] >= 0) *reinterpret_cast<uint4*>(dst + dsti[u]) = q[u];
   }
 }
 
@@ -218,43 +254,68 @@ __global__ void __launch_bounds__(512)
 kf_symm_rs_shard(PeerPtrs grads, const void* mc_grads, int world, int rank, SegTable t, float inv_world,
                  __nv_bfloat16* __restrict__ shard_grad, int accumulate) {
   const long long nvec = t.vec_start[t.n];
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-    const int s = seg_of(t, v);
-    const long long local = (v - t.vec_start[s]) * 8;        // element inside this rank's piece
-    const long long piece = t.len[s] / world;
-    const long long src = t.full[s] + rank * piece + local;  // element inside a full-layout buffer
-    float acc[8];
-    if (mc_grads) {
-      ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grads) + src, acc);
-    } else {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * RS_UNROLL) {
+    long long src[RS_UNROLL], dsti[RS_UNROLL];
+    float acc[RS_UNROLL][8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      for (int r = 0; r < world; ++r) {
-        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + src);
-        float2 f;
-        f = unpack_bf16(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16(u.w); acc[6] += f.x; acc[7] += f.y;
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      const long long v = v0 + u * stride;
+      src[u] = -1;
+      if (v < nvec) {
+        const int s = seg_of(t, v);
+        const long long local = (v - t.vec_start[s]) * 8;        // element inside this rank's piece
+        const long long piece = t.len[s] / world;
+        src[u] = t.full[s] + rank * piece + local;                // element inside a full-layout buffer
+        dsti[u] = t.shard[s] + local;
       }
     }
-    __nv_bfloat16* out = shard_grad + t.shard[s] + local;
+    if (mc_grads) {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] *= inv_world;
-    if (accumulate) {
-      const uint4 old = *reinterpret_cast<const uint4*>(out);
-      float2 f;
-      f = unpack_bf16(old.x); acc[0] += f.x; acc[1] += f.y;
-      f = unpack_bf16(old.y); acc[2] += f.x; acc[3] += f.y;
-      f = unpack_bf16(old.z); acc[4] += f.x; acc[5] += f.y;
-      f = unpack_bf16(old.w); acc[6] += f.x; acc[7] += f.y;
+      for (int u = 0; u < RS_UNROLL; ++u)
+        if (src[u] >= 0) ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_grads) + src[u], acc[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(grads.p[r]);
+        uint4 q[RS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u)
+          q[u] = src[u] >= 0 ? *reinterpret_cast<const uint4*>(base + src[u]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u) {
+          float2 f;
+          f = unpack_bf16(q[u].x); acc[u][0] += f.x; acc[u][1] += f.y;
+          f = unpack_bf16(q[u].y); acc[u][2] += f.x; acc[u][3] += f.y;
+          f = unpack_bf16(q[u].z); acc[u][4] += f.x; acc[u][5] += f.y;
+          f = unpack_bf16(q[u].w); acc[u][6] += f.x; acc[u][7] += f.y;
+        }
+      }
     }
-    uint4 o;
-    o.x = pack_bf16(acc[0], acc[1]);
-    o.y = pack_bf16(acc[2], acc[3]);
-    o.z = pack_bf16(acc[4], acc[5]);
-    o.w = pack_bf16(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(out) = o;
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      if (src[u] < 0) continue;
+      __nv_bfloat16* out = shard_grad + dsti[u];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[u][k] *= inv_world;
+      if (accumulate) {
+        const uint4 old = *reinterpret_cast<const uint4*>(out);
+        float2 f;
+        f = unpack_bf16(old.x); acc[u][0] += f.x; acc[u][1] += f.y;
+        f = unpack_bf16(old.y); acc[u][2] += f.x; acc[u][3] += f.y;
+        f = unpack_bf16(old.z); acc[u][4] += f.x; acc[u][5] += f.y;
+        f = unpack_bf16(old.w); acc[u][6] += f.x; acc[u][7] += f.y;
+      }
+      uint4 o;
+      o.x = pack_bf16(acc[u][0], acc[u][1]);
+      o.y = pack_bf16(acc[u][2], acc[u][3]);
+      o.z = pack_bf16(acc[u][4], acc[u][5]);
+      o.w = pack_bf16(acc[u][6], acc[u][7]);
+      *reinterpret_cast<uint4*>(out) = o;
+    }
   }
 }
 

@@ -63,6 +63,8 @@ class DataParallelEngine:
         # True when the optimizer steps on whole parameters (Lion, Schedule-Free AdamW, Muon) instead of the flat
         # shards: every rank then needs the *whole* averaged gradient, not only its shard (set by build_optimizer)
         self.full_grads = False
+        # library-collective path: reduce gradients in fp32 (KF_DP_REDUCE_DTYPE=bf16 trades that for half the traffic)
+        self.reduce_fp32 = os.environ.get("KF_DP_REDUCE_DTYPE", "fp32").lower() in ("fp32", "float32")
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
         if self.world > 1:
@@ -141,8 +143,18 @@ class DataParallelEngine:
                 getattr(p, "_kf_grad_live", False) and (p.grad is None or p.grad.data_ptr() == p._kf_grad.data_ptr())
                 for p in g.params
             )
-            if ready and getattr(self.model, "tp", None) is None and getattr(self.model, "ep_group", None) is None:
-                self._reduce_work[i] = self._reduce_one(g, async_op=True)
+            if not ready:
+                continue
+            tp = getattr(self.model, "tp", None)
+            if tp is not None:  # gradients that only saw part of the tokens are summed over the TP group first
+                from kempnerforge_b200.parallel.tensor_parallel import sync_partial_grads_of
+
+                sync_partial_grads_of(g.params, tp)
+            ep_group = getattr(self.model, "ep_group", None)
+            if ep_group is not None and not getattr(self.model, "ep_in_dp", False) and g.ep_sharded:
+                g.grad.div_(dist.get_world_size(ep_group))  # shared-batch EP: every expert saw each token once per peer
+                g._kf_ep_scaled = True
+            self._reduce_work[i] = self._reduce_one(g, async_op=True)
         return None
 
     def _reduce_one(self, g: FlatParamGroup, async_op: bool = False):
@@ -152,6 +164,16 @@ class DataParallelEngine:
             if self.full_grads:
                 return dist.all_reduce(g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
             lo, hi = g.shard_range
+            if self.reduce_fp32 and g.grad.dtype != torch.float32:
+                # the sum over ranks is taken in fp32 and rounded once (what the peer-memory kernels do, and the
+                # reduce_dtype of the mixed-precision policy); costs a transient fp32 copy of one unit
+                wide = g.grad.float()
+                out = torch.empty(hi - lo, dtype=torch.float32, device=g.grad.device)
+                work = dist.reduce_scatter_tensor(out, wide, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
+                if async_op:
+                    return _CopyAfterWork(work, out, g.grad[lo:hi], wide)
+                g.grad[lo:hi].copy_(out)
+                return None
             return dist.reduce_scatter_tensor(g.grad[lo:hi], g.grad, op=dist.ReduceOp.AVG, group=self.pg, async_op=async_op)
         work = dist.all_reduce(g.grad, group=self.pg, async_op=async_op)
         if async_op:
@@ -208,7 +230,7 @@ class DataParallelEngine:
             # EP peers route the *same* batch, so every expert saw each token once per peer: undo that factor
             ep = dist.get_world_size(ep_group)
             for g in self.groups:
-                if g.ep_sharded:
+                if g.ep_sharded and not getattr(g, "_kf_ep_scaled", False):
                     g.grad.div_(ep)
         if self.world > 1 and self.requires_sync:
             self._reduce_gradients()
@@ -370,6 +392,10 @@ class DataParallelEngine:
     def zero_grad(self) -> None:
         for g in self.groups:
             g.zero_grad()
+            g._kf_ep_scaled = False
+            for p in g.params:
+                if getattr(p, "_kf_tp_synced", False):
+                    p._kf_tp_synced = False
         self._reduced = False
 
     # ------------------------------------------------------------------ checkpoint helpers
@@ -398,6 +424,18 @@ class _EventWork:
 
     def wait(self) -> None:
         torch.cuda.current_stream().wait_event(self.event)
+
+
+class _CopyAfterWork:
+    """Handle of an asynchronous reduction into a wide buffer whose result is then rounded into the gradient shard."""
+
+    def __init__(self, work, src: torch.Tensor, dst: torch.Tensor, keep) -> None:
+        self.work, self.src, self.dst, self.keep = work, src, dst, keep
+
+    def wait(self) -> None:
+        self.work.wait()
+        self.dst.copy_(self.src)
+        self.keep = None
 
 
 class _ScaledWork:

@@ -121,7 +121,10 @@ def apply_fsdp2(model: nn.Module, mesh, transport: str | None = None, reshard_af
     if transport == "auto":
         # our peer-memory kernels when the job is plain data parallelism on GPUs of one NVLink domain;
         # library collectives otherwise (other mesh dimensions, CPU, several nodes)
-        pure_dp = mesh is not None and all(mesh_dim(mesh, d)[1] <= 1 for d in ("tp", "ep", "pp", "dp_replicate"))
+        # other mesh dimensions do not matter to the data-parallel transport (it lives on the dp sub-group); replicas of
+        # a hybrid mesh are one flattened group.  KF_DP_SYMM_MIXED=0 restricts it to pure data parallelism.
+        mixed_ok = os.environ.get("KF_DP_SYMM_MIXED", "1") != "0"
+        pure_dp = mesh is not None and (mixed_ok or all(mesh_dim(mesh, d)[1] <= 1 for d in ("tp", "ep", "pp", "dp_replicate")))
         one_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) == int(os.environ.get("WORLD_SIZE", "1") or 1)
         on_gpu = torch.cuda.is_available() and pg is not None and "nccl" in str(torch.distributed.get_backend(pg))
         transport = "symmetric" if (pure_dp and one_node and on_gpu and torch.distributed.get_world_size(pg) > 1) else "collective"

@@ -373,10 +373,21 @@ def sync_partial_grads(model: nn.Module) -> None:
     if ctx is None:
         return
     for p in model.parameters():
-        if getattr(p, "_kf_tp_partial_grad", False):
+        if getattr(p, "_kf_tp_partial_grad", False) and not getattr(p, "_kf_tp_synced", False):
             g = getattr(p, "_kf_grad", None) if getattr(p, "_kf_grad_live", False) else p.grad
             if g is not None:
                 dist.all_reduce(g, group=ctx.group)
+
+
+def sync_partial_grads_of(params, ctx) -> None:
+    """The same for one block's parameters, as soon as its backward has finished (so that the block's data-parallel
+    reduction can start while the rest of the backward runs); marks them so the end-of-backward pass skips them."""
+    for p in params:
+        if getattr(p, "_kf_tp_partial_grad", False) and not getattr(p, "_kf_tp_synced", False):
+            g = getattr(p, "_kf_grad", None) if getattr(p, "_kf_grad_live", False) else p.grad
+            if g is not None:
+                dist.all_reduce(g, group=ctx.group)
+                p._kf_tp_synced = True
 
 
 # --------------------------------------------------------------------------- vocabulary-parallel loss
