@@ -207,14 +207,14 @@ struct SegTable {
   long long len[MAX_SEGS];
   long long shard[MAX_SEGS];
   long long vec_start[MAX_SEGS + 1];  // prefix sums of len / 8 (gather) or len / world / 8 (reduce)
+  long long piece[MAX_SEGS];          // len / world
   int n;
 };
 
 __device__ __forceinline__ int seg_of(const SegTable& t, long long v) {
   int s = 0;
-#pragma unroll
-  for (int i = 1; i < MAX_SEGS; ++i)
-    if (i < t.n && v >= t.vec_start[i]) s = i;
+  for (int i = 1; i < t.n; ++i)
+    if (v >= t.vec_start[i]) s = i;
   return s;
 }
 
@@ -234,7 +234,7 @@ kf_symm_pull(PeerPtrs shards, int world, SegTable t, __nv_bfloat16* __restrict__
       if (v < nvec) {
         const int s = seg_of(t, v);
         const long long e = (v - t.vec_start[s]) * 8;   // element inside the parameter
-        const long long piece = t.len[s] / world;
+        const long long piece = t.piece[s];
         const int owner = int(e / piece);
         q[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[owner]) + t.shard[s] +
                                                (e - owner * piece));
@@ -265,8 +265,7 @@ kf_symm_rs_shard(PeerPtrs grads, const void* mc_grads, int world, int rank, SegT
       if (v < nvec) {
         const int s = seg_of(t, v);
         const long long local = (v - t.vec_start[s]) * 8;        // element inside this rank's piece
-        const long long piece = t.len[s] / world;
-        src[u] = t.full[s] + rank * piece + local;                // element inside a full-layout buffer
+        src[u] = t.full[s] + rank * t.piece[s] + local;           // element inside a full-layout buffer
         dsti[u] = t.shard[s] + local;
       }
     }
@@ -329,6 +328,7 @@ static inline int fill_seg_table(SegTable& t, int n, const long long* full, cons
     t.full[i] = full[i];
     t.len[i] = len[i];
     t.shard[i] = shard[i];
+    t.piece[i] = len[i] / world;
     t.vec_start[i] = acc;
     acc += (per_piece ? len[i] / world : len[i]) / 8;
   }

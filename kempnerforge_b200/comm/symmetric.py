@@ -7,7 +7,8 @@ copies.  Our kernels take those addresses directly (``kempnerforge_b200.ops.cuda
 
 Ordering between ranks is a signal-pad barrier on the stream (``SymmBuffer.barrier``); it is bounded by a
 timeout, so a rank that never arrives produces an error instead of a hang.  ``KF_SYMM_MULTIMEM=0`` keeps the
-kernels on plain peer loads / stores (the mode used by fault-handling tests).
+kernels on plain peer loads / stores (the mode used by fault-handling tests), ``1`` forces the multicast
+instructions, the default ``auto`` uses them from four ranks on.
 """
 
 from __future__ import annotations
@@ -34,7 +35,11 @@ class SymmBuffer:
         self.rank = self.handle.rank
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.peer_ptrs = (ctypes.c_longlong * 8)(*(ptrs + [0] * (8 - len(ptrs))))
-        use_mc = os.environ.get("KF_SYMM_MULTIMEM", "1") != "0"
+        # NVSwitch multicast (multimem.ld_reduce / multimem.st) pays once the in-switch reduction / fan-out saves bytes on
+        # this GPU's links: with two ranks it saves nothing and measured 1.8x slower than plain peer loads / stores
+        # (0.685 vs 0.375 ms for one block's reduce-scatter), so "auto" uses it from four ranks on
+        mode = os.environ.get("KF_SYMM_MULTIMEM", "auto")
+        use_mc = mode == "1" or (mode == "auto" and self.world >= 4)
         mc = int(self.handle.multicast_ptr) if use_mc and getattr(self.handle, "multicast_ptr", 0) else 0
         self.multicast_ptr = mc or None
 
