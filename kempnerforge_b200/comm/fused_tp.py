@@ -5,6 +5,18 @@ the GEMM epilogue of every rank stores finished tiles into the owner's staging s
 per-tile counter; the owner sums the slices once a tile's counter shows all contributions.  The buffers are
 sized for the largest (T, D) seen and shared by every row-parallel Linear of the model (calls are serialised
 on the stream; staging and counters alternate by call parity).
+
+Why two parities are enough (no fence between call n and call n + 2).  A rank writes into a peer's parity-p buffer
+only from inside its own call n (n = p mod 2).  For rank A to *start* call n + 2 it has finished call n + 1 on its
+stream, and its call n + 1 could only finish after it had received every peer's contribution to call n + 1 (the
+all-gather GEMM consumes every owner's rows; the reduce-scatter GEMM sums every source's tiles, each behind a
+bounded counter wait).  Peer B issues its contribution to call n + 1 from its own call n + 1 kernel, which is ordered
+on B's stream after B's call n kernel — the last reader of B's parity-p buffer of call n.  Hence
+"B finished reading parity p of call n"  happens-before  "B contributes to n + 1"  happens-before  "A finishes n + 1"
+happens-before  "A overwrites B's parity p in call n + 2".  The argument needs (i) every call of a context to involve
+every rank of the group, (ii) calls of one context to be issued on one stream per rank in the same order on all ranks
+— both hold for the layers of a tensor-parallel model — and (iii) the counters to be monotonic (they are: the expected
+value is derived from the call number), so a stale counter can never satisfy a later call.
 """
 
 from __future__ import annotations
