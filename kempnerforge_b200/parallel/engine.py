@@ -67,6 +67,13 @@ class DataParallelEngine:
         self.reduce_fp32 = os.environ.get("KF_DP_REDUCE_DTYPE", "fp32").lower() in ("fp32", "float32")
         model._kf_engine = self
         model.set_requires_gradient_sync = self.set_requires_gradient_sync
+        # One GPU: the flat AdamW of a step (bound by memory bandwidth) runs on a side stream, unit by unit in forward
+        # order, under the next step's forward pass (bound by the tensor cores); a block waits for its own unit only.
+        self.overlap_update = (self.world == 1 and dev.type == "cuda" and not getattr(self, "shard_blocks", False)
+                               and os.environ.get("KF_DP_OVERLAP_UPDATE", "1") != "0")
+        if self.overlap_update:
+            self._comm_stream = torch.cuda.Stream()
+            self._install_overlap_hooks()
         if self.world > 1:
             self.broadcast_parameters()
             self._install_overlap_hooks()
@@ -313,12 +320,14 @@ class DataParallelEngine:
     def publish_on_side_stream(self, flat_groups) -> bool:
         """True when the optimizer should hand its fused update + publication kernels to
         :meth:`publish_in_forward_order` (symmetric transport on a GPU, every unit in a symmetric buffer)."""
-        if not (self.symmetric and self._comm_stream is not None and self._handles):
+        if self._comm_stream is None or not self._handles:
             return False
-        if os.environ.get("KF_DP_OVERLAP_PUBLISH", "1") == "0":
+        same = len(flat_groups) == len(self.groups) and all(a is b for a, b in zip(flat_groups, self.groups))
+        if self.overlap_update:
+            return same and all(g.param.numel() > 0 for g in self.groups)
+        if not self.symmetric or os.environ.get("KF_DP_OVERLAP_PUBLISH", "1") == "0":
             return False
-        return (len(flat_groups) == len(self.groups) and all(a is b for a, b in zip(flat_groups, self.groups))
-                and all(getattr(g, "param_symm", None) is not None and g.param.numel() > 0 for g in self.groups))
+        return same and all(getattr(g, "param_symm", None) is not None and g.param.numel() > 0 for g in self.groups)
 
     def publish_in_forward_order(self, launch) -> None:
         """Run ``launch(unit)`` (sharded optimizer update that stores the new parameters on every rank) for every
@@ -334,7 +343,8 @@ class DataParallelEngine:
             for i in order:
                 g = self.groups[i]
                 launch(g)
-                g.param_symm.barrier()
+                if self.world > 1:
+                    g.param_symm.barrier()
                 done = torch.cuda.Event()
                 done.record()
                 self._gather_work[i] = _EventWork(done)
@@ -343,8 +353,8 @@ class DataParallelEngine:
     def after_optimizer_step(self) -> None:
         """Publish the updated shards so that every rank holds the full new parameters.  On GPUs the
         all-gathers are asynchronous and each block waits for its own only when its next forward starts."""
-        if self.symmetric and self._published_per_group:
-            self._published_per_group = False  # every unit carries its own barrier + event
+        if self._published_per_group:
+            self._published_per_group = False  # every unit carries its own (barrier +) event
             return
         if self.symmetric:
             # the optimizer kernel already stored the new parameters on every rank; one barrier makes sure all

@@ -82,9 +82,13 @@ class FusedAdamW(torch.optim.AdamW):
             def launch(fg):
                 fg.step_count += 1
                 p, g, m, v = fg.optimizer_views()
-                lo, hi = fg.shard_range
-                kcuda.symm_adamw_bcast(fg.param_symm, g, m, v, lo, hi - lo, fg.n_decay, lr, b1, b2, eps, wd,
-                                       fg.step_count, self.grad_scale, self.skip_flag)
+                if fg.world > 1:
+                    lo, hi = fg.shard_range
+                    kcuda.symm_adamw_bcast(fg.param_symm, g, m, v, lo, hi - lo, fg.n_decay, lr, b1, b2, eps, wd,
+                                           fg.step_count, self.grad_scale, self.skip_flag)
+                else:  # one GPU: the same ordering, without publication
+                    kcuda.adamw_flat(p, g, m, v, fg.n_decay_local, lr, b1, b2, eps, wd, fg.step_count,
+                                     self.grad_scale, self.skip_flag)
 
             for fg in self._flat_groups:
                 fg.step_tensor.fill_(float(fg.step_count + 1))
