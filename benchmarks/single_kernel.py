@@ -6,7 +6,8 @@ subject of a profiler capture as well:
     python benchmarks/single_kernel.py attn_bwd --dq-mode red --iters 5
 
 Workloads (Llama-3-8B shapes unless noted): gemm (CTA-pair tiles, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu,
-gemm_rope (QKV projection with the rotary embedding in the epilogue), grouped / grouped_wgrad (8 experts,
+gemm_rope (QKV projection with the rotary embedding in the epilogue), gemm_fp8 (tensorwise-scaled e4m3, same shape),
+fp8_cast (abs-max + cast of the 8192 x 4096 activation, row-major + transposed), grouped / grouped_wgrad (8 experts,
 dim 2048 x 5632), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
 rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_gather (QKV projection whose weight is gathered
 inside the kernel from 8 parameter shards; on one GPU the shards are 8 local buffers, so the kernel and its copy
@@ -35,6 +36,18 @@ def build(target: str, K, args):
         w = torch.randn(6144, 4096, device=dev, dtype=bf) * 0.02
         out = torch.empty(8192, 6144, device=dev, dtype=bf)
         return (lambda: K.gemm(a, w, out=out, mode=1 if target == "gemm_1cta" else 2)), 2 * 8192 * 6144 * 4096, 0
+    if target in ("gemm_fp8", "fp8_cast"):
+        a = torch.randn(8192, 4096, device=dev, dtype=bf)
+        w = torch.randn(6144, 4096, device=dev, dtype=bf) * 0.02
+        if target == "fp8_cast":   # abs-max + cast of the activation, row-major and transposed copies
+            def cast():
+                sc = K.fp8_scale(a)
+                return K.fp8_cast(a, sc, False, True, True)
+            return cast, 0, a.numel() * (2 + 2 + 1 + 1)
+        sa, sw = K.fp8_scale(a), K.fp8_scale(w)
+        a8, _ = K.fp8_cast(a, sa, False, True, False)
+        w8, _ = K.fp8_cast(w, sw, False, True, False)
+        return (lambda: K.gemm_fp8(a8, w8, sa, sw)), 2 * 8192 * 6144 * 4096, 0
     if target == "gemm_swiglu":
         a = torch.randn(8192, 4096, device=dev, dtype=bf)
         w = torch.randn(2 * 14336, 4096, device=dev, dtype=bf) * 0.02

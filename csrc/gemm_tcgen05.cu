@@ -262,6 +262,11 @@ int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, i
 }
 
 namespace kf2 {
+int launch_gemm_swiglu_bwd_2cta(const void* DY, const void* W, const void* GU, void* DGU, int M, int F, int K, int lda,
+                                int ldw, int ldgu, int num_sms, cudaStream_t stream, int* status);
+}
+
+namespace kf2 {
 int launch_gemm_gather_2cta(int epi, const void* A, void* C, const void* R, int M, int N, int K, int lda, int ldc, int ldr,
                             const long long* peers, int world, int rank, int n_seg, const long long* seg_rows,
                             const long long* seg_src, void* stage, int* flags, const float* cosT, const float* sinT,
@@ -269,6 +274,16 @@ int launch_gemm_gather_2cta(int epi, const void* A, void* C, const void* R, int 
 }
 
 extern "C" {
+
+// Input gradient of a SwiGLU MLP's down projection fused with the SwiGLU gradient: dgu[M, 2F] (d gate | d up) from
+// dy[M, K], the down weight w[K][F] (its stored layout) and the saved pre-activations gu[M, 2F]; dh is never written.
+// dgu may alias gu.  Pitches in elements, multiples of 8; K % 64 == 0.
+int kf_gemm_swiglu_bwd_bf16(const void* dy, const void* w, const void* gu, void* dgu, int M, int F, int K, int lda, int ldw,
+                            int ldgu, int num_sms, void* stream) {
+  if ((lda & 7) || (ldw & 7) || (ldgu & 7) || (F & 7) || (K % 64)) return 5;
+  return kf2::launch_gemm_swiglu_bwd_2cta(dy, w, gu, dgu, M, F, K, lda, ldw, ldgu, num_sms, (cudaStream_t)stream,
+                                          kf::status_ptr());
+}
 
 // GEMM whose weight operand is gathered from the data-parallel ranks' parameter shards by the same kernel
 // (sharded parameters: rank r keeps piece r of every weight).  out = x W^T with W = the row stack of `n_seg`

@@ -307,6 +307,47 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
       tc_fence_after();
       const int row = tc.m * TILE_M + int(rank) * CTA_M + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TILE_N;
+      if constexpr (SWIGLU == 3) {
+        // SwiGLU backward in the epilogue of the down projection's input-gradient GEMM: the accumulator is
+        // dh[rows, F] (never written); R = the saved pre-activations [rows, 2F] (gate | up), C = d[gate | up]
+        // [rows, 2F] (may be the same buffer: every element is read and written by one thread).
+        const int col0 = tc.n * TILE_N;
+        const __nv_bfloat16* gu_row = reinterpret_cast<const __nv_bfloat16*>(R) + size_t(row) * ldr + col0;
+        __nv_bfloat16* d_row = reinterpret_cast<__nv_bfloat16*>(C) + size_t(row) * ldc + col0;
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const int valid = min(32, N - (col0 + c * 32));
+          if (row < M && valid > 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (q * 8 >= valid) break;
+              const uint4 gq = *reinterpret_cast<const uint4*>(gu_row + c * 32 + q * 8);
+              const uint4 uq = *reinterpret_cast<const uint4*>(gu_row + N + c * 32 + q * 8);
+              const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+              uint32_t dg[4], du[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g2 = unpack_bf16(gw[e]), u2 = unpack_bf16(uw[e]);
+                // the gradient of the hidden activation is rounded to bf16 first, like the two-kernel path
+                const float d0 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e])));
+                const float d1 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e + 1])));
+                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                du[e] = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
+                dg[e] = pack_bf16(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+              }
+              *reinterpret_cast<uint4*>(d_row + c * 32 + q * 8) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+              *reinterpret_cast<uint4*>(d_row + N + c * 32 + q * 8) = make_uint4(du[0], du[1], du[2], du[3]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) arrive_on_cta(tempty_bar(acc), 0);
+        continue;
+      }
       if constexpr (SWIGLU == 2) {
         const int col0 = tc.n * TILE_N;
         __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(C) + size_t(row) * ldc + col0;
@@ -596,6 +637,32 @@ int launch_gemm_gather_2cta(int epi, const void* A, void* C, const void* R, int 
   }
   if (epi == 0) KF2_GATHER_LAUNCH(0) else if (epi == 1) KF2_GATHER_LAUNCH(1) else if (epi == 2) KF2_GATHER_LAUNCH(2) else return 6;
 #undef KF2_GATHER_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// d[gate | up][M, 2F] = SwiGLU'(gu) * (dy[M, K] x W[K, F]) with W stored [K][F] (F contiguous: the down projection's
+// weight read for its input gradient); gu and dgu may be the same buffer.  F % 8 == 0, K % 64 == 0.
+int launch_gemm_swiglu_bwd_2cta(const void* DY, const void* W, const void* GU, void* DGU, int M, int F, int K, int lda,
+                                int ldw, int ldgu, int num_sms, cudaStream_t stream, int* status) {
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, DY, M, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = make_map_2d_bf16(&mb, W, K, F, ldw, 64, BK);
+  if (rc) return 200 + rc;
+  auto kern = kf_gemm_bf16_tcgen05_2cta<false, true, __nv_bfloat16, 3>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * ((F + TILE_N - 1) / TILE_N);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(DGU),
+                                                   reinterpret_cast<const __nv_bfloat16*>(GU), M, F, K, ldgu, ldgu, 0, status,
+                                                   RopeArgs{nullptr, nullptr, 1, 0, 64}, GatherArgs{});
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -48,21 +48,61 @@ class SymmBuffer:
         self.handle.barrier(channel=channel, timeout_ms=BARRIER_TIMEOUT_MS)
 
 
-_REGISTRY: dict[int, SymmBuffer] = {}
+class SymmSlice:
+    """A sub-range of an arena: the same interface as :class:`SymmBuffer` (tensor, peer addresses, multicast address,
+    barrier), with every address advanced by the slice's byte offset.  Barriers of a slice use the arena's signal pad
+    on the slice's channel."""
+
+    def __init__(self, arena: SymmBuffer, byte_offset: int, numel: int, dtype: torch.dtype, channel: int) -> None:
+        elem = torch.empty((), dtype=dtype).element_size()
+        raw = arena.tensor.view(torch.uint8)[byte_offset : byte_offset + numel * elem]
+        self.tensor = raw.view(dtype)
+        self.arena, self.world, self.rank, self.channel = arena, arena.world, arena.rank, channel
+        ptrs = [int(arena.peer_ptrs[i]) + byte_offset if i < arena.world else 0 for i in range(8)]
+        self.peer_ptrs = (ctypes.c_longlong * 8)(*ptrs)
+        self.multicast_ptr = (arena.multicast_ptr + byte_offset) if arena.multicast_ptr else None
+        self.handle = arena.handle
+
+    def barrier(self, channel: int | None = None) -> None:
+        self.arena.barrier(self.channel if channel is None else channel)
 
 
-def lookup(t: torch.Tensor) -> SymmBuffer | None:
+_REGISTRY: dict[int, object] = {}
+
+
+def lookup(t: torch.Tensor):
     return _REGISTRY.get(t.data_ptr())
 
 
+ARENA_ALIGN = 256
+ARENA_MIN_BYTES = int(os.environ.get("KF_SYMM_ARENA_MIN_MB", "256")) << 20
+ARENA_MAX_BYTES = int(os.environ.get("KF_SYMM_ARENA_MAX_MB", "8192")) << 20
+
+
 def make_allocator(group):
-    """Allocator for ``FlatParamGroup``: flat buffers are placed in symmetric memory of ``group``."""
+    """Allocator for ``FlatParamGroup``: flat buffers are placed in symmetric memory of ``group``.
+
+    Buffers are carved out of a few large arenas (each one rendezvous: 256 MB first, doubling up to 8 GB, or as large
+    as a single request needs) instead of one rendezvous per buffer: a 32-block model needs a handful of exchanges of
+    peer addresses at start-up, not 66.  Requests alternate between two barrier channels (parameters / gradients are
+    allocated alternately), so the two kinds never share a signal slot."""
     if group is None:
         group = dist.group.WORLD
+    state = {"arena": None, "used": 0, "next": ARENA_MIN_BYTES, "count": 0}
 
     def alloc(numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
-        buf = SymmBuffer(numel, dtype, device, group)
-        _REGISTRY[buf.tensor.data_ptr()] = buf
-        return buf.tensor
+        elem = torch.empty((), dtype=dtype).element_size()
+        need = -(-numel * elem // ARENA_ALIGN) * ARENA_ALIGN
+        arena = state["arena"]
+        if arena is None or state["used"] + need > arena.tensor.numel():
+            size = max(need, min(state["next"], ARENA_MAX_BYTES))
+            state["next"] = min(2 * size, ARENA_MAX_BYTES)
+            arena = state["arena"] = SymmBuffer(size, torch.uint8, device, group)
+            state["used"] = 0
+        piece = SymmSlice(arena, state["used"], numel, dtype, channel=state["count"] % 2)
+        state["used"] += need
+        state["count"] += 1
+        _REGISTRY[piece.tensor.data_ptr()] = piece
+        return piece.tensor
 
     return alloc

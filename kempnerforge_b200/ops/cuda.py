@@ -50,6 +50,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, i, i, vp],
         "kf_gemm_swiglu_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp],
         "kf_gemm_rope_bf16": [vp, vp, vp, i, i, i, i, i, i, vp, vp, i, i, i, i, vp],
+        "kf_gemm_swiglu_bwd_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
         "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
@@ -372,6 +373,26 @@ def gemm_swiglu(x2: torch.Tensor, w_gate_up: torch.Tensor, want_gu: bool = True)
                                      m, f, k, x2.stride(0), w_gate_up.stride(0), f, 2 * f, sm_count(), _stream()),
            "kf_gemm_swiglu_bf16")
     return h, gu
+
+
+def gemm_swiglu_bwd(dy2: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    """d[gate | up] (M, 2F), written over ``gu``: the input-gradient GEMM of the down projection (``dy2`` (M, K) times
+    ``w_down`` (K, F) as stored) with the SwiGLU gradient in its epilogue; the gradient of the hidden activation is
+    never written to memory."""
+    m, k = dy2.shape
+    f = w_down.shape[1]
+    assert w_down.shape[0] == k and gu.shape == (m, 2 * f) and gu.is_contiguous() and w_down.stride(1) == 1
+    _check(lib().kf_gemm_swiglu_bwd_bf16(dy2.data_ptr(), w_down.data_ptr(), gu.data_ptr(), gu.data_ptr(), m, f, k,
+                                         dy2.stride(0), w_down.stride(0), 2 * f, sm_count(), _stream()),
+           "kf_gemm_swiglu_bwd_bf16")
+    return gu
+
+
+def gemm_swiglu_bwd_supported(dy2: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor | None) -> bool:
+    return (gu is not None and getattr(lib(), "kf_gemm_swiglu_bwd_bf16", None) is not None
+            and not os.environ.get("KF_DISABLE_SWIGLU_EPILOGUE") and os.environ.get("KF_SWIGLU_BWD_EPILOGUE", "1") == "1" and dy2.shape[0] >= 256 and dy2.shape[1] % 64 == 0
+            and w_down.shape[1] % 256 == 0 and dy2.stride(0) % 8 == 0 and w_down.stride(0) % 8 == 0 and gu.is_contiguous()
+            and dy2.dtype == torch.bfloat16)
 
 
 def gemm_swiglu_supported(x2: torch.Tensor, w_gate_up: torch.Tensor) -> bool:

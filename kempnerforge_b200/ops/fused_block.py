@@ -245,10 +245,13 @@ class DenseBlockFn(torch.autograd.Function):
             eng.ensure(unit, "o", [wo])
             eng.ensure(unit, "qkv", [wq, wk, wv])
         # ---- feed-forward branch
-        dhmid = kc.gemm(dy2, wd, a_kmajor=True, b_kmajor=False)
         (g_wd,) = _wgrad(dy2, it["hmid"], [wd])
-        dgu = kc.swiglu_bwd(dhmid, it["gu"], out=it["gu"])  # gu is dead after this; reuse its storage
-        del dhmid
+        if kc.gemm_swiglu_bwd_supported(dy2, wd, it["gu"]):
+            dgu = kc.gemm_swiglu_bwd(dy2, wd, it["gu"])  # SwiGLU gradient in the GEMM epilogue, written over gu
+        else:
+            dhmid = kc.gemm(dy2, wd, a_kmajor=True, b_kmajor=False)
+            dgu = kc.swiglu_bwd(dhmid, it["gu"], out=it["gu"])  # gu is dead after this; reuse its storage
+            del dhmid
         dn2 = kc.gemm(dgu, kc.stack_rows([wg, wu]), a_kmajor=True, b_kmajor=False)
         g_wg, g_wu = _wgrad(dgu, it["n2"], [wg, wu])
         dh1, dwn2 = kc.rmsnorm_bwd(dn2, it["h1"], wn2, it["rstd2"], residual_grad=dy2, out=dn2)

@@ -1040,3 +1040,16 @@ def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, ext
     _close(x.grad[:rows], xf.grad, rtol=3e-2, atol=3e-2)
     for got, ref_w in ((wg, wgf), (wu, wuf), (wd, wdf)):
         _close(got.grad, ref_w.grad, rtol=4e-2, atol=4e-2)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 128), (512, 1536, 512), (1000, 768, 320)])
+def test_gemm_swiglu_backward_epilogue_matches_two_kernel_path(native_lib, shape):
+    """Input-gradient GEMM of the down projection with the SwiGLU gradient in its epilogue against the plain GEMM
+    followed by the element-wise kernel (same roundings: bit-identical)."""
+    m, f, k = shape
+    dy, wd = _rand(m, k), _rand(k, f) * 0.1
+    gu = _rand(m, 2 * f)
+    want = native_lib.swiglu_bwd(native_lib.gemm(dy, wd, a_kmajor=True, b_kmajor=False, mode=2), gu.clone())
+    got = native_lib.gemm_swiglu_bwd(dy, wd, gu.clone())
+    assert native_lib.read_status() == 0
+    assert torch.equal(got, want)
