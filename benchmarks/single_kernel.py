@@ -9,7 +9,9 @@ Workloads (Llama-3-8B shapes unless noted): gemm (CTA-pair tiles, 8192 x 6144 x 
 gemm_rope (QKV projection with the rotary embedding in the epilogue), gemm_fp8 (tensorwise-scaled e4m3, same shape),
 fp8_cast (abs-max + cast of the 8192 x 4096 activation, row-major + transposed), grouped / grouped_wgrad (8 experts,
 dim 2048 x 5632), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
-rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_gather (QKV projection whose weight is gathered
+rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_symm / gemm_symm_plain (Gram matrix of a 4096 x 14336
+weight from its upper-triangle tiles, and the plain GEMM it replaces; both report the full product's flops), muon_ns
+(five Newton-Schulz iterations of that weight); gemm_gather (QKV projection whose weight is gathered
 inside the kernel from 8 parameter shards; on one GPU the shards are 8 local buffers, so the kernel and its copy
 warps run exactly as in a job but the "peer" loads stay on this GPU), symm_pull, symm_rs_shard (one block unit, 8
 emulated ranks).  Prints one JSON line.
@@ -118,6 +120,14 @@ def build(target: str, K, args):
         grads = [torch.randn(unit, device=dev, dtype=bf) for _ in range(world)]
         out = torch.empty(unit // world, device=dev, dtype=bf)
         return (lambda: K.symm_rs_shard(Peers(grads, 3), [0], [unit], [0], out, False)), 0, (world + 1) * (unit // world) * 2
+    if target in ("gemm_symm", "gemm_symm_plain", "muon_ns"):
+        x = torch.randn(4096, 14336, device=dev, dtype=bf) * 0.01     # an MLP weight: Gram matrix on the short side
+        if target == "muon_ns":   # five Newton-Schulz iterations of one MLP weight
+            from kempnerforge_b200.training.optimizer import _newton_schulz_native
+            return (lambda: _newton_schulz_native(x, 5)), 5 * (2 * 2 * 4096 * 4096 * 14336 + 2 * 4096 ** 3), 0
+        if target == "gemm_symm_plain":
+            return (lambda: K.gemm(x, x, mode=2)), 2 * 4096 * 4096 * 14336, 0
+        return (lambda: K.gemm_symm(x)), 2 * 4096 * 4096 * 14336, 0   # flops of the full product: what it replaces
     if target == "rmsnorm_bwd":
         x = torch.randn(16384, 4096, device=dev, dtype=bf)
         w = torch.ones(4096, device=dev, dtype=bf)

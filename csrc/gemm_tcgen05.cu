@@ -262,6 +262,11 @@ int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, i
 }
 
 namespace kf2 {
+int launch_gemm_symm_2cta(int x_mn, const void* X, void* C, const void* R, int n, int K, int ldx, int ldc, int ldr,
+                          float alpha, float beta, float diag, int num_sms, cudaStream_t stream, int* status);
+}
+
+namespace kf2 {
 int launch_gemm_swiglu_bwd_2cta(const void* DY, const void* W, const void* GU, void* DGU, int M, int F, int K, int lda,
                                 int ldw, int ldgu, int num_sms, cudaStream_t stream, int* status);
 }
@@ -283,6 +288,17 @@ int kf_gemm_swiglu_bwd_bf16(const void* dy, const void* w, const void* gu, void*
   if ((lda & 7) || (ldw & 7) || (ldgu & 7) || (F & 7) || (K % 64)) return 5;
   return kf2::launch_gemm_swiglu_bwd_2cta(dy, w, gu, dgu, M, F, K, lda, ldw, ldgu, num_sms, (cudaStream_t)stream,
                                           kf::status_ptr());
+}
+
+// Symmetric product with a polynomial epilogue (the Gram matrix and the quintic of Muon's Newton-Schulz iteration):
+// c[n, n] = alpha * x x^T + beta * r + diag * I for x[n][K] (x_mn == 0) or alpha * x^T x + ... for x[K][n] (x_mn != 0).
+// Only the tiles on and above the diagonal are computed, the rest is their transposed copy.  r (optional) must be
+// symmetric; c must alias neither x nor r.  n % 8 == 0; pitches in elements, multiples of 8.
+int kf_gemm_symm_bf16(int x_mn, const void* x, void* c, const void* r, int n, int K, int ldx, int ldc, int ldr, float alpha,
+                      float beta, float diag, int num_sms, void* stream) {
+  if ((ldx & 7) || (ldc & 7) || (r && (ldr & 7)) || c == x || c == r) return 5;
+  return kf2::launch_gemm_symm_2cta(x_mn, x, c, r, n, K, ldx, ldc, ldr, alpha, beta, diag, num_sms, (cudaStream_t)stream,
+                                    kf::status_ptr());
 }
 
 // GEMM whose weight operand is gathered from the data-parallel ranks' parameter shards by the same kernel

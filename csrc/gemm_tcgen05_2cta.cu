@@ -139,10 +139,16 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
 // projection.  Output columns [0, rope.cols) are heads of `rope.hd` columns that get rotated (pairs (i, i + hd/2)
 // with the angle of position `row % rope.S`), the remaining columns (V) are stored as they are.  The rotation is
 // applied to the fp32 accumulators, so q and k are rounded to bf16 once.
+//
+// SWIGLU == 4 (bf16 output, A and B the same matrix X): symmetric product  C = alpha * X X^T + beta * R + diag * I
+// (or X^T X with MN-major operands), N = M.  Only the tiles on and above the diagonal are computed; every tile
+// above the diagonal is stored twice, as it is and transposed, so C comes out exactly symmetric at about half the
+// tensor-core work.  R must be symmetric as well (it is read at the untransposed position only).
 struct RopeArgs {
   const float* cosT;  // [S][hd / 2]
   const float* sinT;
   int S, cols, hd;
+  float alpha, beta, diag;  // SWIGLU == 4 only
 };
 
 template <bool A_MN, bool B_MN, typename OutT, int SWIGLU = 0, bool GATHER = false>
@@ -169,13 +175,21 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
   const int num_pairs = gridDim.x >> 1;
   const int m_blocks = (M + TILE_M - 1) / TILE_M;
   const int n_blocks = SWIGLU == 1 ? (N + HALF_N - 1) / HALF_N : (N + TILE_N - 1) / TILE_N;
-  const int num_tiles = m_blocks * n_blocks;
+  const int num_tiles = SWIGLU == 4 ? m_blocks * (m_blocks + 1) / 2 : m_blocks * n_blocks;
   const int k_blocks = (K + BK - 1) / BK;
   // gathering variant: column tiles are the slow index (a weight row block is consumed completely soon after it
   // arrived), rotated so that the tile holding this rank's own rows comes first
   auto tile_at = [&](int t) {
     TileCoord tc;
-    if constexpr (GATHER) {
+    if constexpr (SWIGLU == 4) {  // upper triangle, row by row: consecutive tiles share their A rows
+      int m = 0, rest = t;
+      while (rest >= m_blocks - m) {
+        rest -= m_blocks - m;
+        ++m;
+      }
+      tc.m = m;
+      tc.n = m + rest;
+    } else if constexpr (GATHER) {
       int nr;
       tilemath::raster(t, n_blocks, m_blocks, GATHER_GROUP_N, nr, tc.m);
       tc.n = nr + ga.n_tile_start;
@@ -340,6 +354,56 @@ kf_gemm_bf16_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __gri
               }
               *reinterpret_cast<uint4*>(d_row + c * 32 + q * 8) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
               *reinterpret_cast<uint4*>(d_row + N + c * 32 + q * 8) = make_uint4(du[0], du[1], du[2], du[3]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) arrive_on_cta(tempty_bar(acc), 0);
+        continue;
+      }
+      if constexpr (SWIGLU == 4) {
+        const int col0 = tc.n * TILE_N;
+        const bool mirror = tc.n != tc.m;
+        __nv_bfloat16* c_out = reinterpret_cast<__nv_bfloat16*>(C);
+        __nv_bfloat16* c_row = c_out + size_t(row) * ldc + col0;
+        const __nv_bfloat16* r_row = R ? reinterpret_cast<const __nv_bfloat16*>(R) + size_t(row) * ldr + col0 : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const int col = col0 + c * 32;
+          const int valid = min(32, N - col);
+          if (row < M && valid > 0) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = rope.alpha * __uint_as_float(v[q * 8 + i]);
+              if (r_row && q * 8 < valid) {
+                const uint4 old = *reinterpret_cast<const uint4*>(r_row + c * 32 + q * 8);
+                const float2 a = unpack_bf16(old.x), b = unpack_bf16(old.y), cc = unpack_bf16(old.z), d = unpack_bf16(old.w);
+                f[0] += rope.beta * a.x; f[1] += rope.beta * a.y; f[2] += rope.beta * b.x; f[3] += rope.beta * b.y;
+                f[4] += rope.beta * cc.x; f[5] += rope.beta * cc.y; f[6] += rope.beta * d.x; f[7] += rope.beta * d.y;
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (col + q * 8 + i == row) f[i] += rope.diag;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) packed[q * 4 + i] = pack_bf16(f[2 * i], f[2 * i + 1]);
+              if (q * 8 < valid)
+                *reinterpret_cast<uint4*>(c_row + c * 32 + q * 8) =
+                    make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+            }
+            if (mirror) {
+              // transposed copy: for a fixed column the 32 lanes of the warp write 32 consecutive elements
+              unsigned short* t_col = reinterpret_cast<unsigned short*>(c_out) + size_t(col) * ldc + row;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid)
+                  t_col[size_t(i) * ldc] = (unsigned short)((i & 1) ? (packed[i >> 1] >> 16) : (packed[i >> 1] & 0xffffu));
             }
           }
         }
@@ -574,6 +638,41 @@ int launch_gemm_rope_2cta(const void* A, const void* W, void* C, int M, int N, i
   if (tiles < pairs) pairs = tiles;
   kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C), nullptr, M, N, K, ldc, 0, 0,
                                                    status, RopeArgs{cosT, sinT, S, rope_cols, hd}, GatherArgs{});
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// Symmetric product with a polynomial epilogue: C[n, n] = alpha * X X^T + beta * R + diag * I for X[n][K] (K-major,
+// x_mn == 0), or alpha * X^T X + ... for X[K][n] (x_mn != 0).  R (optional) must be symmetric; C must not alias X or R
+// (the transposed stores of one tile land in the rows another tile may still be reading).  n % 8 == 0.
+int launch_gemm_symm_2cta(int x_mn, const void* X, void* C, const void* R, int n, int K, int ldx, int ldc, int ldr,
+                          float alpha, float beta, float diag, int num_sms, cudaStream_t stream, int* status) {
+  if ((n & 7) || n <= 0 || K <= 0) return 6;
+  CUtensorMap ma, mb;
+  int rc = x_mn ? make_map_2d_bf16(&ma, X, K, n, ldx, 64, BK) : make_map_2d_bf16(&ma, X, n, K, ldx, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = x_mn ? make_map_2d_bf16(&mb, X, K, n, ldx, 64, BK) : make_map_2d_bf16(&mb, X, n, K, ldx, BK, HALF_N);
+  if (rc) return 200 + rc;
+  const int nb = (n + TILE_M - 1) / TILE_M;
+  const int tiles = nb * (nb + 1) / 2;
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  const RopeArgs ra{nullptr, nullptr, 1, 0, 64, alpha, beta, diag};
+#define KF2_SYMM_LAUNCH(MN_)                                                                                         \
+  {                                                                                                                  \
+    auto kern = kf_gemm_bf16_tcgen05_2cta<MN_, MN_, __nv_bfloat16, 4>;                                               \
+    static bool attr_set = false;                                                                                    \
+    if (!attr_set) {                                                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);      \
+      if (e != cudaSuccess) return 300 + (int)e;                                                                     \
+      attr_set = true;                                                                                               \
+    }                                                                                                                \
+    kern<<<pairs * 2, THREADS, SMEM_BYTES, stream>>>(ma, mb, reinterpret_cast<__nv_bfloat16*>(C),                    \
+                                                     reinterpret_cast<const __nv_bfloat16*>(R), n, n, K, ldc, ldr, 0, \
+                                                     status, ra, GatherArgs{});                                      \
+  }
+  if (x_mn) KF2_SYMM_LAUNCH(true) else KF2_SYMM_LAUNCH(false)
+#undef KF2_SYMM_LAUNCH
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -51,6 +51,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_gemm_swiglu_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp],
         "kf_gemm_rope_bf16": [vp, vp, vp, i, i, i, i, i, i, vp, vp, i, i, i, i, vp],
         "kf_gemm_swiglu_bwd_bf16": [vp, vp, vp, vp, i, i, i, i, i, i, i, vp],
+        "kf_gemm_symm_bf16": [i, vp, vp, vp, i, i, i, i, i, f, f, f, i, vp],
         "kf_rmsnorm_fwd_bf16": [vp, vp, vp, vp, i, i, f, vp],
         "kf_rmsnorm_bwd_blocks": [i],
         "kf_rmsnorm_bwd_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp],
@@ -386,6 +387,30 @@ def gemm_swiglu_bwd(dy2: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor) -
                                          dy2.stride(0), w_down.stride(0), 2 * f, sm_count(), _stream()),
            "kf_gemm_swiglu_bwd_bf16")
     return gu
+
+
+def gemm_symm(x: torch.Tensor, tall: bool = False, residual: torch.Tensor | None = None, alpha: float = 1.0,
+              beta: float = 0.0, diag: float = 0.0) -> torch.Tensor:
+    """bf16 (n, n) = alpha * x xᵀ + beta * residual + diag * I for x (n, K), or alpha * xᵀ x + ... for ``tall`` x (K, n).
+
+    Only the tiles on and above the diagonal go through the tensor cores; the kernel stores each of them a second time
+    transposed, so the result is exactly symmetric.  ``residual`` must be symmetric."""
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    n, k = (x.shape[1], x.shape[0]) if tall else x.shape
+    out = torch.empty((n, n), dtype=torch.bfloat16, device=x.device)
+    if residual is not None:
+        assert residual.shape == (n, n) and residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+    _check(lib().kf_gemm_symm_bf16(int(tall), x.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                   n, k, x.stride(0), n, residual.stride(0) if residual is not None else 0, float(alpha),
+                                   float(beta), float(diag), sm_count(), _stream()), "kf_gemm_symm_bf16")
+    return out
+
+
+def gemm_symm_supported(x: torch.Tensor, tall: bool = False) -> bool:
+    n, k = (x.shape[1], x.shape[0]) if tall else x.shape
+    return (getattr(lib(), "kf_gemm_symm_bf16", None) is not None and os.environ.get("KF_GEMM_SYMM", "1") == "1"
+            and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and n % 8 == 0 and n >= 256
+            and k % 64 == 0)
 
 
 def gemm_swiglu_bwd_supported(dy2: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor | None) -> bool:

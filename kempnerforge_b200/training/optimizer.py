@@ -260,8 +260,43 @@ def _build_sf(param_groups, config: OptimizerConfig):
 
 
 # --------------------------------------------------------------------------- Muon
+def _newton_schulz_native(g: torch.Tensor, steps: int) -> torch.Tensor | None:
+    """bf16 result of the iteration on the tcgen05 kernels, or None when the shape / device is not served.
+
+    Per iteration: the Gram matrix A on the short side as a symmetric product (upper-triangle tiles only), the quintic
+    aI + bA + cA^2 as a second symmetric product whose epilogue adds bA and the diagonal, and one GEMM that applies the
+    polynomial to X; no elementwise pass in between.  The input may be bf16 or fp32; it is normalised in one pass.
+    """
+    if not (g.is_cuda and g.dim() == 2 and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0 and min(g.shape) >= 64):
+        return None
+    from kempnerforge_b200.ops import cuda as kcuda
+
+    if not kcuda.available():
+        return None
+    a, b, c = ref.NS_COEFFS
+    inv = 1.0 / (torch.linalg.vector_norm(g, dtype=torch.float32) + 1e-7)
+    x = (g * inv).to(torch.bfloat16).contiguous()
+    tall = x.shape[0] > x.shape[1]
+    n = min(x.shape)
+    symm = kcuda.gemm_symm_supported(x, tall)
+    eye_a = None
+    for _ in range(steps):
+        if symm:
+            gram = kcuda.gemm_symm(x, tall)                                         # A = X X^T or X^T X, symmetric
+            poly = kcuda.gemm_symm(gram, False, residual=gram, alpha=c, beta=b, diag=a)   # aI + bA + cA^2
+        else:
+            if eye_a is None:
+                eye_a = torch.zeros(n, n, dtype=torch.float32, device=x.device)
+                eye_a.diagonal().fill_(a)
+            gram = kcuda.gemm(x, x, a_kmajor=False, b_kmajor=False) if tall else kcuda.gemm(x, x)
+            sq = kcuda.gemm(gram, gram, out_dtype=torch.float32)
+            poly = (eye_a + b * gram.float() + c * sq).to(torch.bfloat16)
+        x = kcuda.gemm(x, poly) if tall else kcuda.gemm(poly, x, b_kmajor=False)
+    return x
+
+
 def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
-    """Quintic Newton-Schulz orthogonalisation (fp32 in, fp32 out).
+    """Quintic Newton-Schulz orthogonalisation (fp32 out).
 
     On CUDA every iteration is three bf16 tcgen05 GEMMs with fp32 accumulation.  The Gram matrix is always taken
     on the short side: X' = (aI + bA + cA^2) X with A = X X^T for a wide X, and X' = X (aI + bA + cA^2) with
@@ -270,27 +305,8 @@ def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
     the ``a X`` term rides on the diagonal of the polynomial, so the last GEMM writes the next iterate directly.
     Elsewhere (CPU, odd shapes) the plain fp32 formulation runs.
     """
-    if g.is_cuda and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0 and min(g.shape) >= 64:
-        from kempnerforge_b200.ops import cuda as kcuda
-
-        if kcuda.available():
-            a, b, c = ref.NS_COEFFS
-            x = g.float()
-            x = (x / (x.norm() + 1e-7)).to(torch.bfloat16).contiguous()
-            tall = x.shape[0] > x.shape[1]
-            n = min(x.shape)
-            eye_a = torch.zeros(n, n, dtype=torch.float32, device=x.device)
-            eye_a.diagonal().fill_(a)
-            for _ in range(steps):
-                if tall:   # A = X^T X  (n x n): both operands read with the reduction index slow
-                    gram = kcuda.gemm(x, x, a_kmajor=False, b_kmajor=False)
-                else:      # A = X X^T  (m x m)
-                    gram = kcuda.gemm(x, x)
-                sq = kcuda.gemm(gram, gram, out_dtype=torch.float32)                    # A^2 (A is symmetric)
-                poly = (eye_a + b * gram.float() + c * sq).to(torch.bfloat16)           # aI + bA + cA^2, symmetric
-                x = kcuda.gemm(x, poly) if tall else kcuda.gemm(poly, x, b_kmajor=False)
-            return x.float()
-    return ref.newton_schulz(g, steps)
+    x = _newton_schulz_native(g, steps)
+    return x.float() if x is not None else ref.newton_schulz(g, steps)
 
 
 _newton_schulz = newton_schulz
@@ -368,10 +384,15 @@ class Muon(torch.optim.Optimizer):
                 k += 1
                 if owner == rank:
                     mat = buf.reshape(buf.shape[0], -1)
-                    upd = newton_schulz(mat.float(), ns).mul_(math.sqrt(max(1.0, mat.shape[0] / mat.shape[1])))
+                    shape_scale = math.sqrt(max(1.0, mat.shape[0] / mat.shape[1]))
                     if wd > 0:
                         pl.mul_(1.0 - lr * wd)
-                    pl.add_(upd.to(pl.dtype).view_as(pl), alpha=-lr)
+                    upd = _newton_schulz_native(mat, ns)
+                    if upd is not None:   # bf16 iterate straight into the parameter: one pass, one rounding
+                        pl.add_(upd.view_as(pl), alpha=-lr * shape_scale)
+                    else:
+                        upd = newton_schulz(mat.float(), ns).mul_(shape_scale)
+                        pl.add_(upd.to(pl.dtype).view_as(pl), alpha=-lr)
                 if world > 1:
                     # the owner's new values replace everybody's copy; the transfer overlaps the next matrices' math
                     src = dist.get_global_rank(dp, owner)

@@ -1053,3 +1053,41 @@ def test_gemm_swiglu_backward_epilogue_matches_two_kernel_path(native_lib, shape
     got = native_lib.gemm_swiglu_bwd(dy, wd, gu.clone())
     assert native_lib.read_status() == 0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("shape,tall", [((256, 512), False), ((768, 320), False), ((1000, 1024), False),
+                                        ((512, 256), True), ((2048, 520), True)])
+def test_symmetric_product_matches_fp32_reference(native_lib, shape, tall):
+    """alpha * X X^T + beta * R + diag * I (and the X^T X form) computed from the upper-triangle tiles only: against
+    the fp32 product, exactly symmetric, and (without a polynomial) equal to the plain GEMM bit for bit."""
+    x = _rand(*shape)
+    n = shape[1] if tall else shape[0]
+    xf = x.float()
+    prod = xf.t() @ xf if tall else xf @ xf.t()
+    got = native_lib.gemm_symm(x, tall)
+    assert native_lib.read_status() == 0
+    assert torch.equal(got, got.t())
+    assert torch.allclose(got.float(), prod, rtol=8e-3, atol=0.05)   # bf16 rounding of an fp32 accumulation
+    plain = native_lib.gemm(x, x, a_kmajor=False, b_kmajor=False, mode=2) if tall else native_lib.gemm(x, x, mode=2)
+    assert torch.equal(torch.triu(got), torch.triu(plain))
+    r = got
+    poly = native_lib.gemm_symm(x, tall, residual=r, alpha=0.5, beta=-1.25, diag=3.0)
+    want = 0.5 * prod - 1.25 * r.float() + 3.0 * torch.eye(n, device=x.device)
+    assert torch.equal(poly, poly.t())
+    assert torch.allclose(poly.float(), want, rtol=8e-3, atol=0.05)
+
+
+def test_newton_schulz_on_symmetric_products_matches_fp32_iteration(native_lib):
+    """The native Newton-Schulz iteration (symmetric Gram product, polynomial in the epilogue of the second product)
+    against the plain fp32 formulation, wide and tall."""
+    from kempnerforge_b200.ops import reference as ref
+    from kempnerforge_b200.training.optimizer import _newton_schulz_native
+
+    for shape in ((512, 1536), (1024, 256)):
+        g = torch.randn(*shape, device="cuda")
+        got = _newton_schulz_native(g.to(torch.bfloat16), 5)
+        assert got is not None and got.dtype == torch.bfloat16
+        want = ref.newton_schulz(g.to(torch.bfloat16).float(), 5)
+        err = (got.float() - want).norm() / want.norm()
+        assert err < 5e-2, err
+    assert native_lib.read_status() == 0
