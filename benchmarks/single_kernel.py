@@ -7,8 +7,8 @@ subject of a profiler capture as well:
 
 Workloads (Llama-3-8B shapes unless noted): gemm (CTA-pair tiles, 8192 x 6144 x 4096), gemm_1cta, gemm_swiglu,
 gemm_rope (QKV projection with the rotary embedding in the epilogue), gemm_fp8 (tensorwise-scaled e4m3, same shape),
-fp8_cast (abs-max + cast of the 8192 x 4096 activation, row-major + transposed), grouped / grouped_wgrad (8 experts,
-dim 2048 x 5632), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
+fp8_cast (abs-max + cast of the 8192 x 4096 activation, row-major + transposed), grouped / grouped_swiglu / grouped_wgrad (8 experts,
+dim 2048 x 5632; ``grouped_single`` / ``grouped_swiglu_single``: the single-CTA tiling instead of CTA pairs), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
 rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_symm / gemm_symm_plain (Gram matrix of a 4096 x 14336
 weight from its upper-triangle tiles, and the plain GEMM it replaces; both report the full product's flops), muon_ns
 (five Newton-Schulz iterations of that weight); gemm_gather (QKV projection whose weight is gathered
@@ -62,7 +62,10 @@ def build(target: str, K, args):
         cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
         out = torch.empty(2 * s, w.shape[0], device=dev, dtype=bf)
         return (lambda: K.gemm(a, w, out=out, rope=(cos, sin, s, (h + hkv) * hd, hd))), 2 * 8192 * 6144 * 4096, 0
-    if target in ("grouped", "grouped_wgrad"):
+    if target in ("grouped", "grouped_wgrad", "grouped_single", "grouped_swiglu", "grouped_swiglu_single"):
+        if target.endswith("_single"):
+            K.grouped_pair_mode(0)
+            target = target[:-7]
         counts = torch.tensor([4000, 5000, 3000, 4384, 4100, 3900, 4200, 4184], device=dev)
         offsets = torch.zeros(9, dtype=torch.int32, device=dev)
         offsets[1:] = counts.cumsum(0)
@@ -71,6 +74,10 @@ def build(target: str, K, args):
         if target == "grouped":
             w = torch.randn(8, 2048, 5632, device=dev, dtype=bf) * 0.02
             return (lambda: K.grouped_gemm(x, w, offsets, b_mn=True)), 2 * rows * 2048 * 5632, 0
+        if target == "grouped_swiglu":
+            wg = torch.randn(8, 2048, 5632, device=dev, dtype=bf) * 0.02
+            wu = torch.randn(8, 2048, 5632, device=dev, dtype=bf) * 0.02
+            return (lambda: K.grouped_swiglu(x, wg, wu, offsets, b_mn=True, want_gu=True)), 2 * 2 * rows * 2048 * 5632, 0
         dy = torch.randn(rows, 5632, device=dev, dtype=bf)
         return (lambda: K.grouped_wgrad(x, dy, offsets)), 2 * rows * 2048 * 5632, 0
     if target in ("attn_fwd", "attn_bwd"):

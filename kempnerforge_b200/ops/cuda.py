@@ -37,6 +37,8 @@ def lib() -> ctypes.CDLL:
         _declare(_lib)
         if os.environ.get("KF_ATTN_BWD_DQ", "") == "red" and hasattr(_lib, "kf_attn_bwd_dq_mode"):
             _lib.kf_attn_bwd_dq_mode(0)
+        if os.environ.get("KF_GROUPED_PAIR", "1") == "0" and hasattr(_lib, "kf_grouped_pair_mode"):
+            _lib.kf_grouped_pair_mode(0)
     return _lib
 
 
@@ -90,6 +92,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_attn_bwd_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp],
         "kf_attn_bwd_rope_bf16": [vp] * 12 + [i] * 6 + [ll] * 8 + [f, i, vp, vp, vp],
         "kf_attn_bwd_dq_mode": [i],
+        "kf_grouped_pair_mode": [i],
         "kf_attn_fwd2_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_attn_fwd_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ll, ll, ll, ll, f, i, vp],
         "kf_symm_rs_norm_bf16": [vp, vp, i, i, ll, ll, vp, vp, i, i, vp],
@@ -731,6 +734,11 @@ def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, ctx, seq_len: int, ou
         "kf_gemm_rs_bf16",
     )
     return out
+
+
+def grouped_pair_mode(mode: int) -> None:
+    """1: the ragged grouped GEMMs run on CTA-pair tiles (default); 0: single-CTA 128 x 256 tiles."""
+    lib().kf_grouped_pair_mode(int(mode))
 
 
 def attn_bwd_dq_mode(mode: int) -> int:

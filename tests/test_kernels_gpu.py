@@ -454,9 +454,17 @@ def test_attention_autograd_function_native_policy(native_lib, monkeypatch):
 
 
 # --------------------------------------------------------------------------- ragged grouped GEMM (MoE experts)
+@pytest.fixture(params=["pair", "single"])
+def grouped_tiles(request, native_lib):
+    """Runs a grouped-GEMM test on both tilings: CTA pairs (256-row tiles, the default) and single-CTA 128 x 256."""
+    native_lib.grouped_pair_mode(1 if request.param == "pair" else 0)
+    yield request.param
+    native_lib.grouped_pair_mode(1)
+
+
 @pytest.mark.parametrize("layout", ["kn", "nk"])
 @pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [1000, 24], [0, 0, 513]])
-def test_grouped_gemm_forward_backward(native_lib, counts, layout):
+def test_grouped_gemm_forward_backward(native_lib, counts, layout, grouped_tiles):
     from kempnerforge_b200.ops import grouped
 
     torch.manual_seed(0)
@@ -553,8 +561,8 @@ def test_gemm_ragged_shapes_stay_inside_their_output_and_repeat_bit_exactly(nati
     assert torch.equal(out, again)            # fixed reduction order: a difference would mean a race
 
 
-@pytest.mark.parametrize("counts", [[5, 0, 300, 77, 130, 1], [0, 0, 513], [1]])
-def test_grouped_kernels_stay_inside_their_outputs_and_repeat_bit_exactly(native_lib, counts):
+@pytest.mark.parametrize("counts", [[5, 0, 300, 77, 130, 1], [0, 0, 513], [1], [257, 255, 0, 700]])
+def test_grouped_kernels_stay_inside_their_outputs_and_repeat_bit_exactly(native_lib, counts, grouped_tiles):
     torch.manual_seed(0)
     e, k, n = len(counts), 192, 328
     rows = sum(counts)
@@ -998,7 +1006,7 @@ def test_moe_capacity_mask_kernel_matches_the_reference_rule(native_lib, shape):
 
 @pytest.mark.parametrize("layout", ["kn", "nk"])
 @pytest.mark.parametrize("counts,extra", [([128, 128, 128, 128], 0), ([5, 0, 300, 77, 130, 1], 0), ([1000, 24], 200), ([0, 0, 513], 64)])
-def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, extra, monkeypatch):
+def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, extra, monkeypatch, grouped_tiles):
     """Expert feed-forward (gate / up grouped GEMM with the SwiGLU epilogue, ragged SwiGLU gradient, accumulating
     input-gradient GEMMs) against an fp32 per-expert reference.  ``extra`` rows beyond the last expert stand for a
     buffer sized by an upper bound: they must be ignored.  No row count may be read on the host."""
@@ -1080,7 +1088,7 @@ def test_symmetric_product_matches_fp32_reference(native_lib, shape, tall):
 def test_newton_schulz_on_symmetric_products_matches_fp32_iteration(native_lib):
     """The native Newton-Schulz iteration (symmetric Gram product, polynomial in the epilogue of the second product)
     against the plain fp32 formulation, wide and tall."""
-    from kempnerforge_b200.ops import reference as ref
+    from kempnerforge_b200.ops import ref
     from kempnerforge_b200.training.optimizer import _newton_schulz_native
 
     for shape in ((512, 1536), (1024, 256)):
