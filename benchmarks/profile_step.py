@@ -1,6 +1,6 @@
 """Per-kernel device time of one training step of the Llama-3-8B-shape benchmark (torch profiler, CUDA activities).
 
-    python benchmarks/profile_step.py [--out step_profile.txt] [--model llama3_8b|tiny]
+    python benchmarks/profile_step.py [--out step_profile.txt] [--model llama3_8b|moe_8x|moe_fine|tiny] [--batch-size 2]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/profile_step.py
         (sharded data parallel over the ranks; rank 0 reports its own kernels and the gaps between them)
 
@@ -22,6 +22,14 @@ SHAPES = {
     "llama3_8b": dict(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256, ffn_hidden_dim=14336,
                       max_seq_len=4096, rope_theta=500000.0),
     "tiny": dict(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=4096, ffn_hidden_dim=1536, max_seq_len=512),
+    # the mixture-of-experts benchmark models of bench.py, all experts on this rank unless launched with several ranks
+    "moe_8x": dict(dim=2048, n_layers=24, n_heads=16, n_kv_heads=16, vocab_size=102400, ffn_hidden_dim=5632,
+                   max_seq_len=4096, rope_theta=500000.0, num_experts=8, moe_top_k=2, moe_router="softmax_topk",
+                   moe_packed_experts=True),
+    "moe_fine": dict(dim=2048, n_layers=24, n_heads=16, n_kv_heads=16, vocab_size=102400, ffn_hidden_dim=10944,
+                     max_seq_len=4096, rope_theta=500000.0, num_experts=64, moe_top_k=6, moe_router="sigmoid_topk",
+                     moe_shared_experts=2, moe_router_z_loss_weight=1e-3, moe_first_k_dense=1,
+                     moe_expert_ffn_multiplier=1408.0 / 10944.0, moe_packed_experts=True),
 }
 
 
@@ -59,6 +67,7 @@ def main() -> int:
     ap.add_argument("--model", default="llama3_8b", choices=sorted(SHAPES))
     ap.add_argument("--out", default=None)
     ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--batch-size", type=int, default=2)
     ap.add_argument("--param-sharding", default="resident", choices=("auto", "resident", "sharded"))
     ap.add_argument("--gaps", type=int, default=12, help="list this many of the longest idle gaps of the busiest stream")
     args = ap.parse_args()
@@ -68,7 +77,7 @@ def main() -> int:
     shape = SHAPES[args.model]
     seq = shape["max_seq_len"]
     cfg = config_from_dict({"model": shape,
-                            "train": {"batch_size": 2, "seq_len": seq, "max_steps": 100, "mixed_precision": "bf16",
+                            "train": {"batch_size": args.batch_size, "seq_len": seq, "max_steps": 100, "mixed_precision": "bf16",
                                       "activation_checkpointing": "full", "seed": 0},
                             "scheduler": {"warmup_steps": 10}, "metrics": {"log_interval": 1000},
                             "distributed": {"dp_shard": int(os.environ.get("WORLD_SIZE", "1")),
@@ -77,7 +86,7 @@ def main() -> int:
     trainer = Trainer(cfg, init_dist=world > 1)
 
     def batch():
-        tok = torch.randint(0, shape["vocab_size"], (2, seq + 1), device="cuda")
+        tok = torch.randint(0, shape["vocab_size"], (args.batch_size, seq + 1), device="cuda")
         return {"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
 
     for _ in range(3):

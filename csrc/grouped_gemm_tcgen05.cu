@@ -236,12 +236,13 @@ int launch_grouped_swiglu_2cta(const void* A, const void* Wg, const void* Wu, vo
 }  // namespace grp2
 }  // namespace kf
 
-// 1 (default): CTA-pair tiles (256 rows per tile) when the call has at least 256 rows; 0: single-CTA 128 x 256 tiles.
-static int g_grouped_pair_mode = 1;
+// 1 (default): CTA-pair tiles (256 x 256; forward / input gradient when the call has at least 256 rows); 0: single-CTA
+// 128 x 256 tiles.
+int kf_grouped_pair_mode_value = 1;  // read by grouped_wgrad_tcgen05.cu as well
 
 extern "C" {
 
-void kf_grouped_pair_mode(int mode) { g_grouped_pair_mode = mode; }
+void kf_grouped_pair_mode(int mode) { kf_grouped_pair_mode_value = mode; }
 
 // C[rows, N] (+)= grouped A[rows, K] x B_e.  offsets: int32[E + 1] on the device (offsets[0] = 0, offsets[E] <= rows;
 // rows past offsets[E] are neither read nor written, so C may be sized by an upper bound known on the host).
@@ -253,7 +254,7 @@ int kf_grouped_gemm_acc_bf16(const void* A, const void* B, void* C, const void* 
   using namespace kf::grp;
   if (E < 1 || E > MAX_EXPERTS || (lda & 7) || (ldc & 7) || (K & 7) || (N & 7) || (b_mn && (K % BK))) return 5;
   if (rows <= 0) return 0;
-  if (g_grouped_pair_mode && rows >= 256 && num_sms >= 2)
+  if (kf_grouped_pair_mode_value && rows >= 256 && num_sms >= 2)
     return grp2::launch_grouped_gemm_2cta(A, B, C, offsets, rows, E, N, K, lda, ldc, b_mn, accumulate, num_sms,
                                           (cudaStream_t)stream, reinterpret_cast<int*>(kf_status_device_ptr()));
   CUtensorMap ma, mb;
@@ -283,7 +284,7 @@ int kf_grouped_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* 
   if (E < 1 || E > MAX_EXPERTS || (lda & 7) || (ldh & 7) || (GU && (ldgu & 7)) || (K & 7) || (F & 7) || (b_mn && (K % BK)))
     return 5;
   if (rows <= 0) return 0;
-  if (g_grouped_pair_mode && rows >= 256 && num_sms >= 2)
+  if (kf_grouped_pair_mode_value && rows >= 256 && num_sms >= 2)
     return grp2::launch_grouped_swiglu_2cta(A, Wg, Wu, H, GU, offsets, rows, E, F, K, lda, ldh, ldgu, b_mn, num_sms,
                                             (cudaStream_t)stream, reinterpret_cast<int*>(kf_status_device_ptr()));
   CUtensorMap ma, mg, mu;

@@ -178,6 +178,14 @@ kf_grouped_wgrad_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid
 }  // namespace kf
 
 extern "C" void* kf_status_device_ptr();
+extern int kf_grouped_pair_mode_value;
+
+namespace kf {
+namespace gwg2 {
+int launch_grouped_wgrad_2cta(const void* A, const void* B, void* Out, const void* offsets, int rows, int E, int M, int N,
+                              long long lda, long long ldb, int num_sms, cudaStream_t stream, int* status);
+}
+}  // namespace kf
 
 extern "C" {
 
@@ -188,6 +196,9 @@ int kf_grouped_wgrad_bf16(const void* A, const void* B, void* Out, const void* o
   using namespace kf;
   using namespace kf::gwg;
   if (E < 1 || (lda & 7) || (ldb & 7) || (M & 7) || (N & 7) || rows < 1) return 5;
+  if (kf_grouped_pair_mode_value && num_sms >= 2)
+    return gwg2::launch_grouped_wgrad_2cta(A, B, Out, offsets, rows, E, M, N, lda, ldb, num_sms, (cudaStream_t)stream,
+                                           reinterpret_cast<int*>(kf_status_device_ptr()));
   CUtensorMap ma, mb;
   int rc = make_map_2d_bf16(&ma, A, rows, M, lda, 64, BK);
   if (rc) return 100 + rc;

@@ -62,5 +62,29 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
 }
 
+// Bounded wait on a barrier of this CTA whose arrivals come from the other CTA of the pair (cluster-scope acquire).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0x3ff) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > KF_WAIT_CYCLES) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 }  // namespace pairops
 }  // namespace kf

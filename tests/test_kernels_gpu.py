@@ -490,8 +490,8 @@ def test_grouped_gemm_forward_backward(native_lib, counts, layout, grouped_tiles
     _close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [1000, 24], [0, 0, 513], [64, 63, 65]])
-def test_grouped_wgrad_matches_per_expert_products(native_lib, counts):
+@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [1000, 24], [0, 0, 513], [64, 63, 65], [449, 1, 15, 16, 17]])
+def test_grouped_wgrad_matches_per_expert_products(native_lib, counts, grouped_tiles):
     """Ragged reduction ranges: rows of the next expert, and NaN rows past the last expert, must not leak in."""
     torch.manual_seed(0)
     m, n = 200, 328
