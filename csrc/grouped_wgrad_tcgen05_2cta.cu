@@ -7,14 +7,18 @@
 // and [n0 + 128 r, + 128) of B (both MN-major: the reduction index is the slow one in memory), 32 KB per CTA and
 // k-block instead of the 48 KB of the 128 x 256 single-CTA tile.
 //
-// The ragged tail: the last 64-row block of an expert usually runs into the next expert's rows.  Every CTA zeroes
-// those rows of ITS OWN shared-memory stage, so the hand-over differs from the dense pair kernel:
-//   full[s]    per CTA: the CTA's own TMA bytes (each CTA arms and waits its own barrier)
-//   ready[s]   leader only: the peer's MMA warp arrives here (remote, release) once its stage has landed and its
-//              tail is zeroed and fenced towards the async proxy; the leader's issuing thread waits for it
-//              (cluster-scope acquire) after handling its own stage, then issues the 256 x 256 x 16 MMAs
-//   empty[s]   both CTAs: released by the leader's tcgen05.commit, multicast to the pair
-//   tfull[a] / tempty[a]: as in gemm_tcgen05_2cta.cu (8 epilogue-warp arrivals on the leader)
+// The ragged tail: the last 64-row block of an expert usually runs into the next expert's rows, and every CTA has to
+// zero those rows of ITS OWN shared-memory stage before the MMAs read it.  Two hand-over protocols therefore:
+//   full 64-row blocks   as in gemm_tcgen05_2cta.cu: both CTAs' TMA bytes are counted on the leader's full[s]
+//   the tail block       (at most one per tile) each CTA's loads complete on its own full[s]; the peer's MMA warp waits
+//                        for it, zeroes its tail rows, fences them towards the async proxy and arrives (remote,
+//                        release) on the leader's ready[s]; the leader does the same with its own stage and its
+//                        issuing thread then waits for ready[s] (cluster-scope acquire) before the MMAs
+//   empty[s]             both CTAs: released by the leader's tcgen05.commit, multicast to the pair
+//   tfull[a] / tempty[a] as in gemm_tcgen05_2cta.cu (8 epilogue-warp arrivals on the leader)
+// The peer's full[s] and the leader's ready[s] complete one phase per TAIL use of stage s only; both sides keep one
+// parity bit per stage for them.  (Relaying every block through the peer's warp was measured 2.4x slower than the
+// single-CTA kernel.)
 // All waits are bounded; TMA loads carry no cluster multicast.
 //
 // Replaces the per-expert weight-gradient products that autograd derives for the padded `torch._grouped_mm`
@@ -88,9 +92,9 @@ kf_grouped_wgrad_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const _
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer (one per CTA, own barrier)
+    // ------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
-      int it = 0;
+      int it = 0, peer_tails = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         const Tile tl = tilemath::wgrad_decode(t, m_blocks, n_blocks, TILE_M, TILE_N, offsets);
@@ -101,31 +105,70 @@ kf_grouped_wgrad_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const _
           if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, status, KF_ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
           const int row = tl.row0 + kb * BK;
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          if (tl.rows - kb * BK < BK) {
+            // tail block: every CTA's bytes complete on its own barrier (its MMA warp zeroes the foreign rows)
+            mbar_expect_tx(full_bar(s), STAGE_BYTES);
 #pragma unroll
-          for (int c = 0; c < CTA_M / 64; ++c) tma_load_2d(a_dst + c * BLOCK_BYTES, &map_a, full_bar(s), m0 + 64 * c, row);
+            for (int c = 0; c < CTA_M / 64; ++c) tma_load_2d(a_dst + c * BLOCK_BYTES, &map_a, full_bar(s), m0 + 64 * c, row);
 #pragma unroll
-          for (int c = 0; c < HALF_N / 64; ++c) tma_load_2d(b_dst + c * BLOCK_BYTES, &map_b, full_bar(s), n0 + 64 * c, row);
+            for (int c = 0; c < HALF_N / 64; ++c) tma_load_2d(b_dst + c * BLOCK_BYTES, &map_b, full_bar(s), n0 + 64 * c, row);
+            if (!leader) ++peer_tails;
+          } else {
+            const uint32_t lead_full = full_bar(s) & PEER_BIT_MASK;
+            if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+#pragma unroll
+            for (int c = 0; c < CTA_M / 64; ++c) tma_load_2d_pair(a_dst + c * BLOCK_BYTES, &map_a, lead_full, m0 + 64 * c, row);
+#pragma unroll
+            for (int c = 0; c < HALF_N / 64; ++c) tma_load_2d_pair(b_dst + c * BLOCK_BYTES, &map_b, lead_full, n0 + 64 * c, row);
+          }
         }
       }
-      for (int j = max(0, it - STAGES); j < it; ++j)
-        mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
+      // Copies into this CTA's shared memory are complete once the stages they filled were consumed (empty flipped)
+      // or, on the error path, once the barrier that counts them flipped.
+      if (leader)
+        for (int j = max(0, it - STAGES); j < it; ++j)
+          mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, KF_ERR_WAIT_DRAIN);
+      (void)peer_tails;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ stage preparation (both CTAs) + MMA issue (leader)
-    // the whole warp walks the loop (the tail rows of a stage are zeroed by all lanes)
+    // the whole warp walks the loop (the tail rows of a stage are zeroed by all lanes); the peer's warp only acts on
+    // tail blocks
     constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, TILE_N, true, true);
     int it = 0, tile_iter = 0;
+    uint32_t tail_parity = 0;  // bit s: parity of the next tail use of stage s (peer: its full[s]; leader: ready[s])
     bool ok = true;
+    auto zero_tail = [&](uint32_t a_src, int valid) {
+      // rows valid..63 of every 64-column block belong to another expert (or to nobody)
+      constexpr int BLOCKS = STAGE_BYTES / BLOCK_BYTES;
+      for (int i = lane; i < tilemath::tail_chunks(valid, BK, BLOCKS); i += 32) {
+        const uint32_t addr = a_src + tilemath::tail_chunk_offset(i, valid, BK, BLOCK_BYTES);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+      }
+      fence_async_smem();
+      __syncwarp();
+    };
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_iter) {
       const Tile tl = tilemath::wgrad_decode(t, m_blocks, n_blocks, TILE_M, TILE_N, offsets);
       const int k_blocks = (tl.rows + BK - 1) / BK;
       const int acc = tile_iter & 1;
-      if (leader) {
-        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), ((tile_iter >> 1) & 1) ^ 1, status, KF_ERR_WAIT_TMEM_EMPTY));
-        if (!ok) break;
-        tc_fence_after();
+      if (!leader) {
+        // peer: only the tail block (the last one, when the expert's row count is not a multiple of 64)
+        const int valid = tl.rows - (k_blocks - 1) * BK;
+        if (k_blocks > 0 && valid < BK) {
+          const int s = (it + k_blocks - 1) % STAGES;
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), (tail_parity >> s) & 1, status, KF_ERR_WAIT_FULL));
+          if (!ok) break;
+          tail_parity ^= 1u << s;
+          zero_tail(smem_base + s * STAGE_BYTES, valid);
+          if (lane == 0) arrive_on_cta(ready_bar(s), 0);  // this CTA's half of the stage is in place
+        }
+        it += k_blocks;
+        continue;
       }
+      ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), ((tile_iter >> 1) & 1) ^ 1, status, KF_ERR_WAIT_TMEM_EMPTY));
+      if (!ok) break;
+      tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * TILE_N;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % STAGES;
@@ -134,35 +177,26 @@ kf_grouped_wgrad_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const _
         if (!ok) break;
         const uint32_t a_src = smem_base + s * STAGE_BYTES, b_src = a_src + A_BYTES;
         const int valid = tl.rows - kb * BK;
-        if (valid < BK) {
-          // rows valid..63 of every 64-column block belong to another expert (or to nobody): zero them
-          constexpr int BLOCKS = STAGE_BYTES / BLOCK_BYTES;
-          for (int i = lane; i < tilemath::tail_chunks(valid, BK, BLOCKS); i += 32) {
-            const uint32_t addr = a_src + tilemath::tail_chunk_offset(i, valid, BK, BLOCK_BYTES);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
-          }
-          fence_async_smem();
-        }
-        __syncwarp();
+        const bool tail = valid < BK;
+        if (tail) zero_tail(a_src, valid);
         if (lane == 0) {
-          if (!leader) {
-            arrive_on_cta(ready_bar(s), 0);  // this CTA's half of the stage is in place
-          } else {
-            if (!mbar_wait_cluster(ready_bar(s), ph, status, KF_ERR_WAIT_FULL)) ok = false;
-            if (ok) {
-              tc_fence_after();
+          if (tail && !mbar_wait_cluster(ready_bar(s), (tail_parity >> s) & 1, status, KF_ERR_WAIT_FULL)) ok = false;
+          if (ok) {
+            tc_fence_after();
 #pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                mma_pair_f16(d_tmem, umma_desc_sw128(a_src + k * (UMMA_K * 128), BLOCK_BYTES, 1024),
-                             umma_desc_sw128(b_src + k * (UMMA_K * 128), BLOCK_BYTES, 1024), idesc, (kb | k) != 0);
-              commit_pair(empty_bar(s));
-            }
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              mma_pair_f16(d_tmem, umma_desc_sw128(a_src + k * (UMMA_K * 128), BLOCK_BYTES, 1024),
+                           umma_desc_sw128(b_src + k * (UMMA_K * 128), BLOCK_BYTES, 1024), idesc, (kb | k) != 0);
+            commit_pair(empty_bar(s));
           }
         }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
+        if (tail) {
+          tail_parity ^= 1u << s;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
       }
-      if (ok && leader && lane == 0) commit_pair(tfull_bar(acc));
+      if (ok && lane == 0) commit_pair(tfull_bar(acc));
     }
     if (leader && lane == 0) {
       // every MMA must have retired before either CTA gives up its shared or tensor memory
