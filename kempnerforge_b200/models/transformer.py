@@ -85,6 +85,14 @@ class TransformerBlock(nn.Module):
                 context_fn=checkpoint_contexts,
             )
         else:
+            if x.is_cuda and not _FUSED_BLOCK_OFF and F.use_native(x):
+                from kempnerforge_b200.ops import fused_block
+
+                if fused_block.attn_half_supported(self, x, kv_cache, doc_ids, key_padding_mask):
+                    # blocks the whole-block node does not cover (mixture-of-experts layers): the attention
+                    # sub-layer as one node, residual included
+                    x = fused_block.attn_half(self, x, cos, sin)
+                    return x + self.mlp(self.mlp_norm(x))
             attn = self._attn_branch(x, cos, sin, kv_cache, doc_ids, key_padding_mask)
         x = x + attn
         return x + self.mlp(self.mlp_norm(x))

@@ -287,6 +287,106 @@ class DenseBlockFn(torch.autograd.Function):
         return (dx.view(b, s, d), None, None, g_wn1, g_wq, g_wk, g_wv, g_wo, g_wn2, g_wg, g_wu, g_wd, None, None, None)
 
 
+class AttnHalfFn(torch.autograd.Function):
+    """x + Attention(RMSNorm(x)) as one autograd node: the first half of a block whose second half is not the plain
+    SwiGLU MLP (mixture-of-experts layers).  Same kernels as the dense block: rotary embedding in the QKV GEMM
+    epilogue, tcgen05 flash attention, the residual in the O GEMM epilogue; backward with dq | dk | dv written through
+    the inverse rotation into one fused gradient and the residual gradient folded into the RMSNorm backward.
+
+    Everything the backward needs goes through ``save_for_backward``, so an enclosing non-reentrant
+    ``torch.utils.checkpoint`` (full activation checkpointing of the block) drops and recomputes it like any other op.
+    Parity: kempnerforge/model/transformer.py:82-103 (attention sub-layer)."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, wn1, wq, wk, wv, wo, eps, hd):
+        b, s, d = x.shape
+        x2 = x.reshape(b * s, d)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        n1, rstd1 = kc.rmsnorm_fwd(x2, wn1, eps)
+        w_qkv = kc.stack_rows([wq, wk, wv])
+        fused_rope = _rope_fused(n1, w_qkv, cos, sin, s, hd)
+        if fused_rope:
+            qkv = kc.gemm(n1, w_qkv, rope=(cos, sin, s, (h + hkv) * hd, hd), mode=2)
+            qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+        else:
+            qkv = kc.gemm(n1, w_qkv)
+            qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+            kc.rope(qkv4, cos, sin, h + hkv, inverse=False, out=qkv4)
+        q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
+        attn, lse = kc.attn_fwd(q, k, v, True, None, 1.0 / math.sqrt(hd))
+        attn2 = attn.reshape(b * s, h * hd)
+        h1 = kc.gemm(attn2, wo, residual=x2)  # residual add in the GEMM epilogue
+        ctx.save_for_backward(x2, cos, sin, n1, rstd1, qkv, attn2, lse)
+        ctx.weights = (wn1, wq, wk, wv, wo)
+        ctx.meta = (b, s, d, hd)
+        return h1.view(b, s, d)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, cos, sin, n1, rstd1, qkv, attn2, lse = ctx.saved_tensors
+        wn1, wq, wk, wv, wo = ctx.weights
+        b, s, d, hd = ctx.meta
+        h, hkv = wq.shape[0] // hd, wk.shape[0] // hd
+        dh1 = dh.reshape(b * s, d)
+        if not dh1.is_contiguous():
+            dh1 = dh1.contiguous()
+        dattn = kc.gemm(dh1, wo, a_kmajor=True, b_kmajor=False)
+        (g_wo,) = _wgrad(dh1, attn2, [wo])
+        qkv4 = qkv.view(b, s, h + 2 * hkv, hd)
+        q, k, v = qkv4[:, :, :h], qkv4[:, :, h : h + hkv], qkv4[:, :, h + hkv :]
+        dqkv4 = torch.empty_like(qkv4)
+        fused_rope = hd == 128 and cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        kc.attn_bwd(dattn.view(b, s, h, hd), q, k, v, attn2.view(b, s, h, hd), lse, True, None, 1.0 / math.sqrt(hd),
+                    dq=dqkv4[:, :, :h], dk=dqkv4[:, :, h : h + hkv], dv=dqkv4[:, :, h + hkv :],
+                    rope=(cos, sin) if fused_rope else None)
+        if not fused_rope:
+            kc.rope(dqkv4, cos, sin, h + hkv, inverse=True, out=dqkv4)
+        dqkv = dqkv4.view(b * s, (h + 2 * hkv) * hd)
+        dn1 = kc.gemm(dqkv, kc.stack_rows([wq, wk, wv]), a_kmajor=True, b_kmajor=False)
+        g_wq, g_wk, g_wv = _wgrad(dqkv, n1, [wq, wk, wv])
+        dx, dwn1 = kc.rmsnorm_bwd(dn1, x2, wn1, rstd1, residual_grad=dh1, out=dn1)
+        g_wn1 = _norm_wgrad(wn1, dwn1)
+        return dx.view(b, s, d), None, None, g_wn1, g_wq, g_wk, g_wv, g_wo, None, None
+
+
+def attn_half_supported(block, x, kv_cache, doc_ids, key_padding_mask) -> bool:
+    """The fused attention sub-layer covers bf16 causal self-attention with head dim 128 on a GPU, without masks,
+    caches, q/k norms, tensor parallelism, fp8 or hooks; the feed-forward half of the block may be anything."""
+    att = block.attention
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and kv_cache is None and doc_ids is None
+            and key_padding_mask is None and torch.is_grad_enabled()):
+        return False
+    if os.environ.get("KF_DISABLE_FUSED_ATTN_HALF"):
+        return False
+    unit = getattr(att.q_proj.weight, "_kf_flat", None)
+    return (
+        getattr(att, "tp", None) is None
+        and att.q_norm is None
+        and not att.capture_attention_weights
+        and type(block.attention_norm).__name__ == "RMSNorm"
+        and not getattr(block, "fp8", False)
+        and not getattr(block, "_kf_fp8_block", False)
+        and not (unit is not None and getattr(unit, "sharded", False))
+        and att.head_dim == 128
+        and x.shape[-1] % 8 == 0
+        and x.shape[0] * x.shape[1] >= 128
+        and kc.attn_policy() == "native"
+        and getattr(kc.lib(), "kf_attn_bwd_bf16", None) is not None
+        and att.q_proj.weight.dtype == torch.bfloat16
+        and not block._forward_hooks
+        and not att._forward_hooks
+        and not block.attention_norm._forward_hooks
+    )
+
+
+def attn_half(block, x, cos, sin):
+    att = block.attention
+    return AttnHalfFn.apply(x, cos, sin, block.attention_norm.weight, att.q_proj.weight, att.k_proj.weight,
+                            att.v_proj.weight, att.o_proj.weight, block.attention_norm.eps, att.head_dim)
+
+
 def dense_block_supported(block, x, kv_cache, doc_ids, key_padding_mask) -> bool:
     """The fused node covers the plain dense pre-norm SwiGLU block in bf16 on a GPU."""
     att, mlp = block.attention, block.mlp

@@ -270,6 +270,63 @@ def test_fused_dense_block_matches_op_by_op_path(native_lib, ac):
         assert (p.grad.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6) < 0.05, n
 
 
+@pytest.mark.parametrize("ac", ["none", "full"])
+def test_fused_attention_sublayer_of_moe_blocks_matches_op_by_op_path(native_lib, ac, monkeypatch):
+    """Mixture-of-experts blocks run their attention sub-layer (norm, QKV + rotary, attention, O + residual) as one
+    autograd node; losses and every gradient must agree with the op-by-op path, with and without activation
+    checkpointing around the block, and with gradients deposited into flat buffers."""
+    from kempnerforge_b200.config import ModelConfig
+    from kempnerforge_b200.models import Transformer
+    from kempnerforge_b200.ops import fused_block
+    from kempnerforge_b200.parallel.flat import flatten_model
+
+    torch.manual_seed(0)
+    cfg = ModelConfig(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, max_seq_len=256, ffn_hidden_dim=1024,
+                      num_experts=4, moe_top_k=2, moe_packed_experts=True)
+    model = Transformer(cfg).to(device=DEV, dtype=torch.bfloat16)
+    for blk in model.layers.values():
+        blk.ac_mode = ac
+    tok = torch.randint(0, 1024, (2, 257), device=DEV)
+    calls = {"n": 0}
+    real = fused_block.attn_half
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(fused_block, "attn_half", counted)
+    results = {}
+    for fused in (True, False):
+        if fused:
+            monkeypatch.delenv("KF_DISABLE_FUSED_ATTN_HALF", raising=False)
+        else:
+            monkeypatch.setenv("KF_DISABLE_FUSED_ATTN_HALF", "1")
+        model.zero_grad()
+        model.train()
+        before = calls["n"]
+        loss = model.compute_loss(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        assert (calls["n"] > before) == fused
+        results[fused] = (loss.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None})
+    assert native_lib.read_status() == 0
+    assert abs(results[True][0] - results[False][0]) < 2e-2
+    assert results[True][1].keys() == results[False][1].keys()
+    # relative to the norm: a token whose top-k choice flips under bf16 noise changes single rows, not the whole gradient
+    for n, g in results[False][1].items():
+        assert ((results[True][1][n] - g).norm() / (g.norm() + 1e-12)).item() < 0.05, n
+    monkeypatch.delenv("KF_DISABLE_FUSED_ATTN_HALF", raising=False)
+    flatten_model(model)
+    for p in model.parameters():
+        p.grad = None
+    model.compute_loss(tok[:, :-1], tok[:, 1:]).backward()
+    for g in model._kf_flat_groups:
+        g.finalize_grads()
+    for n, p in model.named_parameters():
+        if n in results[False][1]:
+            ref = results[False][1][n]
+            assert ((p.grad.float() - ref).norm() / (ref.norm() + 1e-12)).item() < 0.05, n
+
+
 # --------------------------------------------------------------------------- attention (tcgen05)
 def _attn_inputs(b, s, h, hkv, hd, fused=True, seed=0):
     g = torch.Generator(device="cuda").manual_seed(seed)
