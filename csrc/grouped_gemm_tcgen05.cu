@@ -233,6 +233,9 @@ int launch_grouped_gemm_2cta(const void* A, const void* B, void* C, const void* 
 int launch_grouped_swiglu_2cta(const void* A, const void* Wg, const void* Wu, void* H, void* GU, const void* offsets, int rows,
                                int E, int F, int K, long long lda, long long ldh, long long ldgu, int b_mn, int num_sms,
                                cudaStream_t st, int* status);
+int launch_grouped_swiglu_bwd_2cta(const void* DY, const void* W, const void* GU, void* DGU, const void* offsets, int rows,
+                                   int E, int F, int K, long long lda, long long ldgu, int b_mn, int num_sms, cudaStream_t st,
+                                   int* status);
 }  // namespace grp2
 }  // namespace kf
 
@@ -303,6 +306,19 @@ int kf_grouped_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* 
   cudaStream_t st = (cudaStream_t)stream;
   return b_mn ? launch<true, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, grid, st)
               : launch<false, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, grid, st);
+}
+
+// d[gate | up] of an expert feed-forward from the output gradient: DGU[rows, 2F] (may alias GU) = SwiGLU'(GU) applied to
+// dh = DY[rows, K] x W_e, with dh living only in tensor memory.  W: the down weights, [E][F][K] (b_mn == 0) or
+// [E][K][F] (b_mn == 1).  F, K multiples of 8 (64 for K when b_mn); pitches multiples of 8.  CTA-pair tiles only.
+int kf_grouped_swiglu_bwd_bf16(const void* DY, const void* W, const void* GU, void* DGU, const void* offsets, int rows, int E,
+                               int F, int K, long long lda, long long ldgu, int b_mn, int num_sms, void* stream) {
+  using namespace kf;
+  if (E < 1 || E > grp::MAX_EXPERTS || (lda & 7) || (ldgu & 7) || (K & 7) || (F & 7) || (b_mn && (K % grp::BK)) || num_sms < 2)
+    return 5;
+  if (rows <= 0) return 0;
+  return grp2::launch_grouped_swiglu_bwd_2cta(DY, W, GU, DGU, offsets, rows, E, F, K, lda, ldgu, b_mn, num_sms,
+                                              (cudaStream_t)stream, reinterpret_cast<int*>(kf_status_device_ptr()));
 }
 
 }  // extern "C"

@@ -14,6 +14,8 @@
 // the leader CTA loads their gate weights and the peer the matching up weights, so every CTA's accumulator holds
 // [gate 128 | up 128] for its 128 rows; the epilogue writes h = silu(gate) * up and optionally the pre-activations.
 //
+// EPI == 2: SwiGLU backward in the epilogue of the down projection's input-gradient product (see the launcher).
+//
 // Synchronisation as in gemm_tcgen05_2cta.cu (all waits bounded); TMA loads carry no cluster multicast.
 // Replaces the padded torch._grouped_mm calls of the reference (kempnerforge/model/moe.py:20-145).
 #include "common.cuh"
@@ -34,7 +36,7 @@ constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + (MAX_EXPERTS
 
 using Tile = tilemath::GroupedTile;
 
-template <bool B_MN, bool SWIGLU>
+template <bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_b2, __nv_bfloat16* __restrict__ C,
@@ -58,6 +60,7 @@ kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  constexpr bool SWIGLU = EPI == 1;
   constexpr int TN = SWIGLU ? HALF_N : TILE_N;  // output columns (hidden units) per tile
   const int n_blocks = (N + TN - 1) / TN;
   const int k_blocks = (K + BK - 1) / BK;
@@ -173,7 +176,41 @@ kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __
       const int col0 = tl.nb * TN;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TILE_N;
       __nv_bfloat16* c_row = C + size_t(tl.row0 + r) * ldc + col0;
-      if constexpr (SWIGLU) {
+      if constexpr (EPI == 2) {
+        // SwiGLU backward: the accumulator is dh[rows, F] (never written); GU = the saved pre-activations [rows, 2F]
+        // (gate | up), C = d[gate | up] [rows, 2F] (may be the same buffer: every element is read and written by one
+        // thread)
+        const __nv_bfloat16* gu_row = GU + size_t(tl.row0 + r) * ldgu + col0;
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const int valid_cols = min(32, N - (col0 + c * 32));
+          if (r < tl.valid && valid_cols > 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (q * 8 >= valid_cols) break;
+              const uint4 gq = *reinterpret_cast<const uint4*>(gu_row + c * 32 + q * 8);
+              const uint4 uq = *reinterpret_cast<const uint4*>(gu_row + N + c * 32 + q * 8);
+              const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+              uint32_t dg[4], du[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g2 = unpack_bf16(gw[e]), u2 = unpack_bf16(uw[e]);
+                // the gradient of the hidden activation is rounded to bf16 first, like the two-kernel path
+                const float d0 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e])));
+                const float d1 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e + 1])));
+                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                du[e] = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
+                dg[e] = pack_bf16(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+              }
+              *reinterpret_cast<uint4*>(c_row + c * 32 + q * 8) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+              *reinterpret_cast<uint4*>(c_row + N + c * 32 + q * 8) = make_uint4(du[0], du[1], du[2], du[3]);
+            }
+          }
+        }
+      } else if constexpr (SWIGLU) {
         __nv_bfloat16* gu_row = GU ? GU + size_t(tl.row0 + r) * ldgu + col0 : nullptr;
 #pragma unroll 1
         for (int c = 0; c < TN / 32; ++c) {
@@ -222,10 +259,10 @@ kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __
   }
 }
 
-template <bool B_MN, bool SWIGLU>
+template <bool B_MN, int EPI>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* C, void* GU, const void* offsets,
                   int E, int N, int K, long long ldc, long long ldgu, int accumulate, int pairs, cudaStream_t st, int* status) {
-  auto kern = kf_grouped_gemm_tcgen05_2cta<B_MN, SWIGLU>;
+  auto kern = kf_grouped_gemm_tcgen05_2cta<B_MN, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
@@ -249,8 +286,8 @@ int launch_grouped_gemm_2cta(const void* A, const void* B, void* C, const void* 
   const int upper = ((rows + TILE_M - 1) / TILE_M + E) * ((N + TILE_N - 1) / TILE_N);  // at most one partial tile per expert
   int pairs = num_sms / 2;
   if (upper < pairs) pairs = upper;
-  return b_mn ? launch<true, false>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, pairs, st, status)
-              : launch<false, false>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, pairs, st, status);
+  return b_mn ? launch<true, 0>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, pairs, st, status)
+              : launch<false, 0>(ma, mb, mb, C, nullptr, offsets, E, N, K, ldc, 0, accumulate, pairs, st, status);
 }
 
 int launch_grouped_swiglu_2cta(const void* A, const void* Wg, const void* Wu, void* H, void* GU, const void* offsets, int rows,
@@ -270,8 +307,26 @@ int launch_grouped_swiglu_2cta(const void* A, const void* Wg, const void* Wu, vo
   const int upper = ((rows + TILE_M - 1) / TILE_M + E) * ((F + HALF_N - 1) / HALF_N);
   int pairs = num_sms / 2;
   if (upper < pairs) pairs = upper;
-  return b_mn ? launch<true, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, pairs, st, status)
-              : launch<false, true>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, pairs, st, status);
+  return b_mn ? launch<true, 1>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, pairs, st, status)
+              : launch<false, 1>(ma, mg, mu, H, GU, offsets, E, F, K, ldh, ldgu, 0, pairs, st, status);
+}
+
+// d[gate | up] (rows x 2F, may alias GU) from dy (rows x K) and the down weights: W [E][F][K] (b_mn == 0: K
+// contiguous) or [E][K][F] (b_mn == 1); the accumulator dh = dy W_e^T (resp. dy W_e) is consumed by the epilogue.
+int launch_grouped_swiglu_bwd_2cta(const void* DY, const void* W, const void* GU, void* DGU, const void* offsets, int rows,
+                                   int E, int F, int K, long long lda, long long ldgu, int b_mn, int num_sms, cudaStream_t st,
+                                   int* status) {
+  CUtensorMap ma, mb;
+  int rc = make_map_2d_bf16(&ma, DY, rows, K, lda, BK, CTA_M);
+  if (rc) return 100 + rc;
+  rc = b_mn ? make_map_2d_bf16(&mb, W, uint64_t(E) * K, F, F, 64, BK) : make_map_2d_bf16(&mb, W, uint64_t(E) * F, K, K, BK, HALF_N);
+  if (rc) return 200 + rc;
+  const int upper = ((rows + TILE_M - 1) / TILE_M + E) * ((F + TILE_N - 1) / TILE_N);
+  int pairs = num_sms / 2;
+  if (upper < pairs) pairs = upper;
+  void* gu = const_cast<void*>(GU);
+  return b_mn ? launch<true, 2>(ma, mb, mb, DGU, gu, offsets, E, F, K, ldgu, ldgu, 0, pairs, st, status)
+              : launch<false, 2>(ma, mb, mb, DGU, gu, offsets, E, F, K, ldgu, ldgu, 0, pairs, st, status);
 }
 
 }  // namespace grp2

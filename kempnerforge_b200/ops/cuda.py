@@ -85,6 +85,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "kf_grouped_gemm_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
         "kf_grouped_gemm_acc_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, i, vp],
         "kf_grouped_swiglu_bf16": [vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp],
+        "kf_grouped_swiglu_bwd_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, i, i, vp],
         "kf_swiglu_bwd_ragged_bf16": [vp, vp, vp, ll, vp, i, vp],
         "kf_grouped_wgrad_bf16": [vp, vp, vp, vp, i, i, i, i, ll, ll, i, vp],
         "kf_ag_gemm_bf16": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, i, i, vp],
@@ -631,6 +632,26 @@ def grouped_swiglu(a: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, offsets:
 def grouped_swiglu_supported(a: torch.Tensor, wg: torch.Tensor, b_mn: bool) -> bool:
     return getattr(lib(), "kf_grouped_swiglu_bf16", None) is not None and grouped_gemm_supported(a, wg, b_mn) \
         and not os.environ.get("KF_DISABLE_GROUPED_SWIGLU")
+
+
+def grouped_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, offsets: torch.Tensor, b_mn: bool) -> torch.Tensor:
+    """d[gate | up] (rows, 2F), written over ``gu``: the input-gradient product of the experts' down projection
+    (``dy`` (rows, K) times ``w_down``: (E, F, K), or (E, K, F) with ``b_mn``) with the SwiGLU gradient in its epilogue;
+    the gradient of the hidden activation is never written to memory.  Rows past ``offsets[E]`` stay untouched."""
+    rows, k = dy.shape
+    e = w_down.shape[0]
+    f = w_down.shape[2] if b_mn else w_down.shape[1]
+    assert gu.shape == (rows, 2 * f) and gu.is_contiguous() and w_down.is_contiguous() and dy.stride(1) == 1
+    _check(lib().kf_grouped_swiglu_bwd_bf16(dy.data_ptr(), w_down.data_ptr(), gu.data_ptr(), gu.data_ptr(), offsets.data_ptr(),
+                                            rows, e, f, k, dy.stride(0), 2 * f, int(b_mn), sm_count(), _stream()),
+           "kf_grouped_swiglu_bwd_bf16")
+    return gu
+
+
+def grouped_swiglu_bwd_supported(dy: torch.Tensor, w_down: torch.Tensor, b_mn: bool) -> bool:
+    return (getattr(lib(), "kf_grouped_swiglu_bwd_bf16", None) is not None and grouped_gemm_supported(dy, w_down, b_mn)
+            and os.environ.get("KF_SWIGLU_BWD_EPILOGUE", "1") == "1" and not os.environ.get("KF_DISABLE_GROUPED_SWIGLU")
+            and dy.shape[0] >= 256 and sm_count() >= 2)
 
 
 def swiglu_bwd_ragged(dh: torch.Tensor, gu: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:

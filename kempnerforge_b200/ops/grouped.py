@@ -94,6 +94,53 @@ class _GroupedSwiGLUFn(torch.autograd.Function):
         return dx, dwg, dwu, None, None
 
 
+class _GroupedFFNFn(torch.autograd.Function):
+    """The whole expert feed-forward, down(silu(x @ Wg_e) * (x @ Wu_e)), over ragged expert rows as one node.
+
+    Forward: the gate / up grouped GEMM with the SwiGLU epilogue, then the down projection.  Backward: the down
+    projection's input-gradient product with the SwiGLU gradient in its epilogue (the gradient of the hidden
+    activation never reaches memory; d[gate | up] overwrites the saved pre-activations), two input-gradient grouped
+    GEMMs (the second accumulating into the first's output) and three ragged weight-gradient reductions."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu, wd, offsets, layout):
+        kc = _cuda_binding
+        kn = layout == "kn"
+        h, gu = kc.grouped_swiglu(x, wg, wu, offsets, b_mn=kn, want_gu=True)
+        y = kc.grouped_gemm(h, wd, offsets, b_mn=kn)
+        ctx.save_for_backward(x, wg, wu, wd, offsets, gu, h)
+        ctx.layout = layout
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        kc = _cuda_binding
+        x, wg, wu, wd, offsets, gu, h = ctx.saved_tensors
+        layout = ctx.layout
+        kn = layout == "kn"
+        f = h.shape[1]
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+
+        def wgrad(a, b):   # per-expert a_e^T b_e in the weight's own layout
+            a, b = (a, b) if kn else (b, a)
+            if kc.grouped_wgrad_supported(a, b):
+                return kc.grouped_wgrad(a, b, offsets)
+            return torch._grouped_mm(a.contiguous().t(), b.contiguous(), offs=offsets[1:])
+
+        dwd = wgrad(h, dy) if ctx.needs_input_grad[3] else None
+        # dh = dy @ Wd_e^T: 'kn' stores Wd_e as (F, D), read with the reduction index D contiguous
+        dgu = kc.grouped_swiglu_bwd(dy, wd, gu, offsets, b_mn=not kn)   # gu is dead after this; reuse its storage
+        dgate, dup = dgu[:, :f], dgu[:, f:]
+        dx = dwg = dwu = None
+        if ctx.needs_input_grad[0]:
+            dx = kc.grouped_gemm(dgate, wg, offsets, b_mn=not kn)
+            kc.grouped_gemm(dup, wu, offsets, b_mn=not kn, out=dx, accumulate=True)
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            dwg, dwu = wgrad(x, dgate), wgrad(x, dup)
+        return dx, dwg, dwu, dwd, None, None
+
+
 def _native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
     from kempnerforge_b200.ops import functional as _F
 
@@ -148,6 +195,9 @@ def grouped_ffn(x_sorted, counts, gate_w, up_w, down_w, layout: str, activation=
         if down_ok and (layout != "nk" or (down_w.shape[1] % 64 == 0)):
             off = offsets if offsets is not None else offsets_of(counts)
             xs = x_sorted if x_sorted.is_contiguous() else x_sorted.contiguous()
+            # the output gradient has the shape of the input (dim -> hidden -> dim)
+            if _cuda_binding.grouped_swiglu_bwd_supported(xs, down_w, layout != "kn"):
+                return _GroupedFFNFn.apply(xs, gate_w, up_w, down_w, off, layout)
             hidden = _GroupedSwiGLUFn.apply(xs, gate_w, up_w, off, layout)
             return _GroupedLinearFn.apply(hidden, down_w, off, layout)
     up = grouped_linear(x_sorted, up_w, counts, layout)

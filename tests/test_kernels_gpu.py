@@ -1107,6 +1107,27 @@ def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, ext
         _close(got.grad, ref_w.grad, rtol=4e-2, atol=4e-2)
 
 
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [700, 24, 300]])
+def test_grouped_swiglu_backward_epilogue_matches_two_kernel_path(native_lib, counts, b_mn):
+    """Experts' down-projection input gradient with the SwiGLU gradient in its epilogue against the grouped GEMM
+    followed by the ragged element-wise kernel (same roundings: bit-identical on the experts' rows)."""
+    torch.manual_seed(2)
+    e, d, f = len(counts), 192, 328 if not b_mn else 320
+    rows = sum(counts)
+    dy = _rand(rows + 40, d)
+    wd = _rand(e, d, f, scale=0.1) if b_mn else _rand(e, f, d, scale=0.1)
+    gu = _rand(rows + 40, 2 * f)
+    off = torch.zeros(e + 1, dtype=torch.int32, device="cuda")
+    off[1:] = torch.tensor(counts, device="cuda").cumsum(0)
+    dh = native_lib.grouped_gemm(dy, wd, off, b_mn=b_mn)
+    want = native_lib.swiglu_bwd_ragged(dh, gu, off)
+    got = native_lib.grouped_swiglu_bwd(dy, wd, gu.clone(), off, b_mn=b_mn)
+    assert native_lib.read_status() == 0
+    assert torch.equal(got[:rows], want[:rows])
+    assert torch.equal(got[rows:], gu[rows:])          # rows past the last expert are not touched
+
+
 @pytest.mark.parametrize("shape", [(256, 256, 128), (512, 1536, 512), (1000, 768, 320)])
 def test_gemm_swiglu_backward_epilogue_matches_two_kernel_path(native_lib, shape):
     """Input-gradient GEMM of the down projection with the SwiGLU gradient in its epilogue against the plain GEMM
