@@ -21,6 +21,7 @@ import torch
 from torch import nn
 
 from kempnerforge_b200.config.registry import registry
+from kempnerforge_b200.ops import functional as F
 
 
 def _counts(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
@@ -38,7 +39,7 @@ class SoftmaxTopKRouter(nn.Module):
         self.expert_counts = torch.zeros(num_experts)
 
     def forward(self, x: torch.Tensor):
-        logits = self.gate(x)
+        logits = F.linear(x, self.gate.weight)   # the native GEMM on a GPU (the gate has no bias)
         from kempnerforge_b200.ops import moe_ops
 
         if moe_ops.native_ok(logits, self.num_experts, self.top_k):
@@ -123,7 +124,7 @@ class SigmoidTopKRouter(nn.Module):
         return self.expert_bias, ph != "recompute"
 
     def forward(self, x: torch.Tensor):
-        logits = self.gate(x)
+        logits = F.linear(x, self.gate.weight)   # the native GEMM on a GPU (the gate has no bias)
         from kempnerforge_b200.ops import moe_ops
 
         bias, may_update = self._bias_for_this_pass()

@@ -1107,6 +1107,27 @@ def test_grouped_expert_ffn_with_swiglu_epilogue(native_lib, counts, layout, ext
         _close(got.grad, ref_w.grad, rtol=4e-2, atol=4e-2)
 
 
+@pytest.mark.parametrize("experts", [8, 64])
+def test_router_gate_projection_runs_on_the_native_gemm(native_lib, experts):
+    """The router's gate is a GEMM with 8 .. 64 output columns: forward, input gradient and the (experts x dim)
+    weight gradient go through the tcgen05 kernels and agree with fp32 matmuls."""
+    from kempnerforge_b200.ops import functional as F
+
+    torch.manual_seed(3)
+    x = _rand(1000, 512).requires_grad_(True)
+    w = _rand(experts, 512, scale=0.05).requires_grad_(True)
+    before = native_lib.LAUNCH_COUNT
+    y = F.linear(x, w)
+    g = _rand(1000, experts)
+    y.backward(g)
+    assert native_lib.LAUNCH_COUNT >= before + 3 and native_lib.read_status() == 0
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    (xf @ wf.t()).backward(g.float())
+    _close(y, xf @ wf.t())
+    _close(x.grad, xf.grad)
+    _close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("b_mn", [False, True])
 @pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77, 130, 1], [700, 24, 300]])
 def test_grouped_swiglu_backward_epilogue_matches_two_kernel_path(native_lib, counts, b_mn):
