@@ -280,3 +280,28 @@ def test_generate_greedy_matches_full_forward():
         nxt = m(seq)[:, -1].argmax(-1, keepdim=True)
         seq = torch.cat([seq, nxt], dim=1)
     assert torch.equal(out, seq)
+
+
+def test_moe_blocks_keep_the_op_by_op_attention_path_off_the_gpu():
+    """The fused attention sub-layer node is a GPU path: on CPU tensors its guard says no and the block's output is the
+    plain residual formulation; the router's gate projection equals its ``nn.Linear``."""
+    from kempnerforge_b200.models.router import build_router
+    from kempnerforge_b200.ops import fused_block
+
+    torch.manual_seed(0)
+    cfg = ModelConfig(dim=64, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=128, max_seq_len=32, ffn_hidden_dim=128,
+                      num_experts=4, moe_top_k=2)
+    model = Transformer(cfg)
+    blk = next(iter(model.layers.values()))
+    x = torch.randn(2, 16, 64)
+    assert not fused_block.attn_half_supported(blk, x, None, None, None)
+    cos, sin = model._rope_cos[:16], model._rope_sin[:16]
+    want = x + blk.attention(blk.attention_norm(x), cos, sin)
+    want = want + blk.mlp(blk.mlp_norm(want))
+    assert torch.allclose(blk(x, cos, sin), want, atol=1e-6)
+    router = build_router("softmax_topk", 64, 8, 2)
+    tokens = torch.randn(10, 64)
+    weights, indices = router(tokens)
+    probs = torch.softmax(router.gate(tokens).float(), dim=-1)
+    top_w, top_i = torch.topk(probs, 2, dim=-1)
+    assert torch.equal(indices, top_i) and torch.allclose(weights, top_w / top_w.sum(-1, keepdim=True), atol=1e-6)
