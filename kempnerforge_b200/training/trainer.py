@@ -315,6 +315,14 @@ class Trainer:
         self.pipeline.share_scalars(self._loss_acc)
         return self._finish_step()
 
+    def _native_status(self) -> int:
+        """Status word of the native kernel library on this rank's GPU (0 on CPU and when every wait completed)."""
+        if self.device.type != "cuda":
+            return 0
+        from kempnerforge_b200.resilience import check_native_kernel_status
+
+        return check_native_kernel_status()
+
     def _apply_phase_lr(self) -> None:
         if self.phase_idx >= 0 and self.phases:
             scale = self.phases[self.phase_idx].lr_scale
@@ -441,6 +449,14 @@ class Trainer:
                 stop_reason = "hook"
                 log.info("a training hook asked to stop at step %d", self.step)
                 break
+            if self.step % cfg.metrics.log_interval == 0 or self.step == 1:
+                # the step's host read already synchronised: the status word of the native kernels costs one small
+                # copy here.  Non-zero = a bounded device-side wait gave up (the kernel returned without its result).
+                word = self._native_status()
+                if word:
+                    stop_reason = "kernel_status"
+                    log.error("native kernel status word is %d at step %d (a device-side wait ran out); stopping", word, self.step)
+                    break
             if tc.nccl_health_check_interval > 0 and self.step % tc.nccl_health_check_interval == 0:
                 from kempnerforge_b200.resilience import check_nccl_health
 

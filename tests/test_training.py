@@ -295,3 +295,17 @@ def test_trainer_learns_repeating_pattern():
     batch = {"input_ids": pattern[:, :-1], "labels": pattern[:, 1:]}
     losses = [t.train_step([batch])["loss"] for _ in range(40)]
     assert losses[-1] < 0.5 * losses[0]
+
+
+def test_fit_stops_when_the_native_kernel_status_word_is_set(monkeypatch):
+    """A non-zero status word (a device-side wait that ran out) ends the run at the next logging step with its own
+    stop reason instead of training on with a missing result."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_tiny_job(max_steps=6), init_dist=False)
+    assert t._native_status() == 0                       # CPU: nothing to read
+    words = iter([0, 6])
+    monkeypatch.setattr(Trainer, "_native_status", lambda self: next(words))
+    t.config.metrics.log_interval = 2
+    out = t.fit()
+    assert out["stop_reason"] == "kernel_status" and out["step"] == 2   # checked at step 1 (clean) and step 2 (set)
