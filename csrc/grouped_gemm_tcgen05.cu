@@ -169,12 +169,7 @@ kf_grouped_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
               store_chunk<__nv_bfloat16>(gu_row + c * 32, g, valid_cols, false, nullptr);
               store_chunk<__nv_bfloat16>(gu_row + N + c * 32, u, valid_cols, false, nullptr);
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {  // the activation sees the bf16 pre-activations, like the two-kernel path
-              const float gf = __bfloat162float(__float2bfloat16(__uint_as_float(g[i])));
-              const float uf = __bfloat162float(__float2bfloat16(__uint_as_float(u[i])));
-              g[i] = __float_as_uint(gf / (1.f + __expf(-gf)) * uf);
-            }
+            swiglu_chunk(g, u);
             store_chunk<__nv_bfloat16>(c_row + c * 32, g, valid_cols, false, nullptr);
           }
         }

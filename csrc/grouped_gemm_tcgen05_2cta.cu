@@ -188,26 +188,7 @@ kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __
           tmem_ld_wait();
           const int valid_cols = min(32, N - (col0 + c * 32));
           if (r < tl.valid && valid_cols > 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (q * 8 >= valid_cols) break;
-              const uint4 gq = *reinterpret_cast<const uint4*>(gu_row + c * 32 + q * 8);
-              const uint4 uq = *reinterpret_cast<const uint4*>(gu_row + N + c * 32 + q * 8);
-              const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
-              uint32_t dg[4], du[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 g2 = unpack_bf16(gw[e]), u2 = unpack_bf16(uw[e]);
-                // the gradient of the hidden activation is rounded to bf16 first, like the two-kernel path
-                const float d0 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e])));
-                const float d1 = __bfloat162float(__float2bfloat16(__uint_as_float(v[q * 8 + 2 * e + 1])));
-                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
-                du[e] = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
-                dg[e] = pack_bf16(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
-              }
-              *reinterpret_cast<uint4*>(c_row + c * 32 + q * 8) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
-              *reinterpret_cast<uint4*>(c_row + N + c * 32 + q * 8) = make_uint4(du[0], du[1], du[2], du[3]);
-            }
+            swiglu_bwd_chunk(v, gu_row + c * 32, gu_row + N + c * 32, c_row + c * 32, c_row + N + c * 32, valid_cols);
           }
         }
       } else if constexpr (SWIGLU) {
@@ -224,12 +205,7 @@ kf_grouped_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a, const __
               store_chunk<__nv_bfloat16>(gu_row + c * 32, g, valid_cols, false, nullptr);
               store_chunk<__nv_bfloat16>(gu_row + N + c * 32, u, valid_cols, false, nullptr);
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {  // the activation sees the bf16 pre-activations, like the two-kernel path
-              const float gf = __bfloat162float(__float2bfloat16(__uint_as_float(g[i])));
-              const float uf = __bfloat162float(__float2bfloat16(__uint_as_float(u[i])));
-              g[i] = __float_as_uint(gf / (1.f + __expf(-gf)) * uf);
-            }
+            swiglu_chunk(g, u);
             store_chunk<__nv_bfloat16>(c_row + c * 32, g, valid_cols, false, nullptr);
           }
         }
