@@ -11,7 +11,8 @@ fp8_cast (abs-max + cast of the 8192 x 4096 activation, row-major + transposed),
 dim 2048 x 5632; ``grouped_single`` / ``grouped_swiglu_single``: the single-CTA tiling instead of CTA pairs), attn_fwd, attn_bwd (B=2, S=4096, 32 / 8 heads, head dim 128, causal; ``--dq-mode red|bulk``),
 rmsnorm_bwd (16384 x 4096), adamw (one block's flat unit); gemm_symm / gemm_symm_plain (Gram matrix of a 4096 x 14336
 weight from its upper-triangle tiles, and the plain GEMM it replaces; both report the full product's flops), muon_ns
-(five Newton-Schulz iterations of that weight); gemm_gather (QKV projection whose weight is gathered
+(five Newton-Schulz iterations of that weight); gemm_wgrad_expert (one expert's weight gradient as a dense GEMM with both
+operands MN-major: the dense counterpart of grouped_wgrad); gemm_gather (QKV projection whose weight is gathered
 inside the kernel from 8 parameter shards; on one GPU the shards are 8 local buffers, so the kernel and its copy
 warps run exactly as in a job but the "peer" loads stay on this GPU), symm_pull, symm_rs_shard (one block unit, 8
 emulated ranks).  Prints one JSON line.
@@ -127,6 +128,10 @@ def build(target: str, K, args):
         grads = [torch.randn(unit, device=dev, dtype=bf) for _ in range(world)]
         out = torch.empty(unit // world, device=dev, dtype=bf)
         return (lambda: K.symm_rs_shard(Peers(grads, 3), [0], [unit], [0], out, False)), 0, (world + 1) * (unit // world) * 2
+    if target == "gemm_wgrad_expert":   # one expert's weight gradient as a dense MN-major GEMM (2048 x 5632 over 4096 rows)
+        x = torch.randn(4096, 2048, device=dev, dtype=bf)
+        dy = torch.randn(4096, 5632, device=dev, dtype=bf)
+        return (lambda: K.gemm(x, dy, a_kmajor=False, b_kmajor=False, mode=2)), 2 * 4096 * 2048 * 5632, 0
     if target in ("gemm_symm", "gemm_symm_plain", "muon_ns"):
         x = torch.randn(4096, 14336, device=dev, dtype=bf) * 0.01     # an MLP weight: Gram matrix on the short side
         if target == "muon_ns":   # five Newton-Schulz iterations of one MLP weight
