@@ -18,7 +18,6 @@ per direction (measured peer copy on this pool).  Prints one JSON line per kerne
 from __future__ import annotations
 
 import json
-import math
 import os
 import sys
 

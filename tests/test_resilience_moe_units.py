@@ -4,7 +4,6 @@ Mirrors tests/unit/test_resilience.py, test_router.py and test_moe.py of the ref
 
 from __future__ import annotations
 
-import math
 import os
 import signal
 

@@ -9,7 +9,6 @@ from __future__ import annotations
 import json
 import logging
 import math
-from types import SimpleNamespace
 
 import pytest
 import torch

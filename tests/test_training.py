@@ -17,7 +17,6 @@ from kempnerforge_b200.training import (
     TrainingHook,
     build_loss_fn,
     build_optimizer,
-    build_scheduler,
     chunked_cross_entropy,
     cross_entropy,
     is_muon_eligible,
