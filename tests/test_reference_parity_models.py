@@ -187,6 +187,34 @@ def test_every_reference_preset_parses_to_the_same_values():
         assert cfg.train.param_dtype == ref_cfg.train.param_dtype and cfg.train.is_fp8 == ref_cfg.train.is_fp8, name
 
 
+def test_presets_shipped_here_carry_the_values_of_the_reference_presets_of_the_same_name():
+    """`configs/train/<name>.toml` of this repository must describe the same run as the reference's preset of that name:
+    every field the reference defines has the same value after loading (layout and comments of the files are ours)."""
+    import glob
+    import os
+
+    _ref_path()
+    from kempnerforge.config.loader import load_config as ref_load
+
+    from kempnerforge_b200.config import load_config
+
+    root = os.environ.get("KF_REFERENCE_ROOT") or str(ROOT.parent / "reference")
+    presets = sorted(glob.glob(os.path.join(root, "configs", "train", "*.toml")))
+    if not presets:
+        pytest.skip("reference presets not available")
+    for path in presets:
+        name = os.path.basename(path)
+        ours = ROOT / "configs" / "train" / name
+        assert ours.exists(), f"preset {name} is missing here"
+        want, got = _norm(ref_load(path, [])), _norm(load_config(str(ours), []))
+        for section, fields in want.items():
+            if fields is None:
+                assert got.get(section) is None, (name, section)
+                continue
+            for key, value in fields.items():
+                assert got[section][key] == value, (name, section, key, value, got[section][key])
+
+
 @pytest.mark.parametrize("name,kw", [("cosine", {}), ("linear", {}), ("constant", {}), ("rex", {"rex_alpha": 2.0}),
                                      ("wsd", {"stable_steps": 30, "wsd_decay_type": "sqrt"}),
                                      ("wsd", {"stable_steps": 10, "wsd_decay_type": "linear", "decay_steps": 40})])
