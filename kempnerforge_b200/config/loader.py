@@ -146,7 +146,7 @@ def _build_dataclass(cls: type, table: dict[str, Any], where: str) -> Any:
     unknown = sorted(set(table) - known)
     if unknown:
         raise ConfigError(
-            f"Unknown config key(s) {unknown} in [{where}] (valid keys: {sorted(known)})"
+            f"Unknown config keys {unknown} in [{where}] (valid keys: {sorted(known)})"
         )
     kwargs = {k: _convert(v, hints[k], f"{where}.{k}") for k, v in table.items()}
     return cls(**kwargs)

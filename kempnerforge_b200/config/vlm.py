@@ -42,9 +42,9 @@ def pooled_token_count(num_input_tokens: int, window: int, require_divisible: bo
     """Tokens left after pooling a square grid of ``num_input_tokens`` with a ``window``² kernel."""
     _require(window > 0, f"pool_window must be positive (got {window})")
     side = math.isqrt(num_input_tokens)
-    _require(side * side == num_input_tokens, f"pooling adapters need a square token grid (got {num_input_tokens})")
+    _require(side * side == num_input_tokens, f"pooling adapters need a square patch grid (got {num_input_tokens} tokens)")
     if require_divisible:
-        _require(side % window == 0, f"token grid side {side} is not divisible by pool_window {window}")
+        _require(side % window == 0, f"ragged grid: token grid side {side} is not divisible by pool_window {window}")
     out_side = -(-side // window)
     return out_side * out_side
 

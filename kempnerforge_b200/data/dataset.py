@@ -276,7 +276,7 @@ class MixtureDataset(Dataset):
         if len(datasets) != len(names):
             raise ValueError("datasets and names must have the same length")
         if not datasets:
-            raise ValueError("MixtureDataset needs at least one dataset")
+            raise ValueError("MixtureDataset: At least one dataset is required")
         self._datasets = list(datasets)
         self._names = list(names)
         sizes = [len(d) for d in datasets]

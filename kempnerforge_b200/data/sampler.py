@@ -25,7 +25,7 @@ def _validate_weights(weights: list[float], context: str) -> None:
     if any((not math.isfinite(w)) or w < 0 for w in weights):
         raise ValueError(f"{context}: weights must be finite and non-negative, got {weights}")
     if sum(weights) <= 0:
-        raise ValueError(f"{context}: at least one weight must be positive")
+        raise ValueError(f"{context}: weights must sum to > 0 (at least one positive weight)")
 
 
 def _replica_info(num_replicas, rank):
@@ -106,7 +106,7 @@ class MixtureSampler(Sampler[int]):
     def _set_quotas(self, weights: list[float], temperature: float, context: str) -> None:
         _validate_weights(weights, context)
         if len(weights) != len(self._sizes):
-            raise ValueError(f"{context}: expected {len(self._sizes)} weights, got {len(weights)}")
+            raise ValueError(f"{context}: Expected {len(self._sizes)} weights, got {len(weights)}")
         if temperature != 1.0:
             logs = [math.log(max(w, 1e-12)) / temperature for w in weights]
             top = max(logs)

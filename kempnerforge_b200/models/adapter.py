@@ -69,7 +69,7 @@ def _to_windows(x: torch.Tensor, window: int):
     b, n, f = x.shape
     side = math.isqrt(n)
     if side * side != n:
-        raise ValueError(f"pooling adapters need a square token grid (got {n} tokens)")
+        raise ValueError(f"pooling adapters need a square patch grid (got {n} tokens)")
     out_side = -(-side // window)
     pad = out_side * window - side
     grid = x.reshape(b, side, side, f)
@@ -132,7 +132,7 @@ class AttentionalPoolAdapter(VisionAdapter):
             raise ValueError(f"pool_window must be positive (got {window})")
         side = math.isqrt(x.shape[1])
         if side % window:
-            raise ValueError(f"token grid side {side} is not divisible by pool_window {window}")
+            raise ValueError(f"ragged grid: token grid side {side} is not divisible by pool_window {window}")
         win, _ = _to_windows(x, window)  # (B, W, P, F)
         b, w, p, f = win.shape
         hd = f // self.heads

@@ -1,6 +1,6 @@
 """Activation capture for analysis: forward hooks that copy named sub-module outputs to the host.
 
-``ActivationStore(model, ["layers.0.attention", "norm"])`` records, per forward pass, the output of each
+``ActivationStore(model, ["layers.0.attention", "norm"])`` keeps, once enabled, the latest output of each
 named module (the first element for tuple outputs) as a detached CPU tensor; ``extract_representations``
 runs a model over batches and stacks what was captured; ``save_activations`` writes an ``.npz``.
 Blocks with a capture hook run op by op (the fused block node is bypassed), so every named sub-module fires.
@@ -22,32 +22,47 @@ class _MissingModule(KeyError, ValueError):
 
 
 class ActivationStore:
-    """Hooks are live from construction; ``disable()`` / ``enable()`` (or leaving the ``with`` block) remove and
-    re-install them.  ``layers=`` is accepted as another spelling of ``layer_names``."""
+    """Forward hooks on named sub-modules that keep each module's LATEST output as a detached host tensor.
 
-    def __init__(self, model: nn.Module, layer_names: list[str] | None = None, detach_to_cpu: bool = True, *,
-                 layers: list[str] | None = None) -> None:
+    Hooks are installed by ``enable()`` (or on entering a ``with`` block) and removed by ``disable()``; a module name
+    that does not exist raises at ``enable()`` (a ``ValueError`` that is also a ``KeyError``).  ``get(name)`` returns the
+    tensor captured by the last forward pass, or ``None``; every pass overwrites the previous capture.  With
+    ``keep_history=True`` the store also keeps one tensor per pass (``history(name)``).  ``layer_names=`` is accepted
+    as another spelling of ``layers``."""
+
+    def __init__(self, model: nn.Module, layers: list[str] | None = None, detach_to_cpu: bool = True, *,
+                 layer_names: list[str] | None = None, keep_history: bool = False) -> None:
         self.model = model
-        self.layer_names = list(layer_names if layer_names is not None else (layers or []))
+        self._layers = list(layers if layers is not None else (layer_names or []))
         self.to_cpu = detach_to_cpu
-        self.activations: dict[str, list[torch.Tensor]] = defaultdict(list)
+        self.keep_history = keep_history
+        self._activations: dict[str, torch.Tensor] = {}
+        self._history: dict[str, list[torch.Tensor]] = defaultdict(list)
         self._handles = []
         self._on = False
-        self.enable()
 
     @property
     def enabled(self) -> bool:
         return self._on
+
+    @property
+    def layer_names(self) -> list[str]:
+        return list(self._layers)
+
+    @property
+    def activations(self) -> dict[str, torch.Tensor]:
+        """A copy of the captured activations (latest per module)."""
+        return dict(self._activations)
 
     def enable(self) -> None:
         """Install the forward hooks (no-op while they are installed)."""
         if self._on:
             return
         modules = dict(self.model.named_modules())
-        missing = [n for n in self.layer_names if n not in modules]
+        missing = [n for n in self._layers if n not in modules]
         if missing:
-            raise _MissingModule(f"modules not found: {missing}; e.g. {sorted(modules)[:8]}")
-        for name in self.layer_names:
+            raise _MissingModule(f"modules not found in model: {missing}; available e.g. {sorted(modules)[:8]}")
+        for name in self._layers:
             self._handles.append(modules[name].register_forward_hook(self._make_hook(name)))
             # make sure the parents of a hooked module run their ordinary (op-by-op) forward
             parts = name.split(".")
@@ -59,37 +74,46 @@ class ActivationStore:
 
     def _make_hook(self, name: str):
         def hook(module, inputs, output):
-            out = output[0] if isinstance(output, (tuple, list)) else output
+            out = output[0] if isinstance(output, (tuple, list)) and len(output) else output
             if isinstance(out, dict):
                 out = next(iter(out.values()))
             if torch.is_tensor(out):
                 out = out.detach()
-                self.activations[name].append(out.float().cpu() if self.to_cpu else out)
+                out = out.cpu() if self.to_cpu else out
+                self._activations[name] = out
+                if self.keep_history:
+                    self._history[name].append(out)
 
         return hook
 
     def clear(self) -> None:
-        self.activations.clear()
+        """Forget what was captured (the hooks stay installed)."""
+        self._activations.clear()
+        self._history.clear()
 
-    def get(self, name: str, concat: bool = True):
-        items = self.activations.get(name, [])
-        if concat and items:
-            return torch.cat(items, dim=0)
-        return items
+    def get(self, name: str) -> torch.Tensor | None:
+        """The activation captured by the last forward pass for ``name``, or None."""
+        return self._activations.get(name)
 
-    def remove(self) -> None:
+    def history(self, name: str) -> list[torch.Tensor]:
+        """One tensor per forward pass since the last ``clear()`` (``keep_history=True`` only)."""
+        return list(self._history.get(name, []))
+
+    def disable(self) -> None:
+        """Remove every hook."""
         for h in self._handles:
             h.remove()
         self._handles = []
         self._on = False
 
-    disable = remove
+    remove = disable
 
     def __enter__(self):
+        self.enable()
         return self
 
     def __exit__(self, *exc):
-        self.remove()
+        self.disable()
 
 
 @torch.no_grad()
@@ -141,8 +165,8 @@ def save_activations(activations: dict[str, torch.Tensor], path) -> None:
         path = path.with_suffix(".npz")
     path.parent.mkdir(parents=True, exist_ok=True)
     def as_array(v):
-        if isinstance(v, (list, tuple)):          # an ActivationStore's per-pass lists
+        if isinstance(v, (list, tuple)):          # per-pass lists (ActivationStore.history)
             v = torch.cat(list(v), dim=0)
-        return v.float().numpy()
+        return v.float().numpy()                  # numpy has no bfloat16
 
     np.savez(str(path), **{k: as_array(v) for k, v in activations.items() if not isinstance(v, (list, tuple)) or len(v)})

@@ -24,7 +24,7 @@ class ModalityContext:
         routes = [self.inputs_embeds, self.prefix_embeds, self.image_features]
         if sum(r is not None for r in routes) > 1:
             raise ValueError(
-                "ModalityContext: at most one of inputs_embeds, prefix_embeds, image_features may be set"
+                "ModalityContext: inputs_embeds, prefix_embeds and image_features are mutually exclusive (at most one may be set)"
             )
         if self.image_mask is not None and self.image_features is None:
             raise ValueError("ModalityContext: image_mask requires image_features to be set")

@@ -51,7 +51,7 @@ class MoTAttention(nn.Module):
     def forward(self, streams: dict[str, torch.Tensor], rope: dict, is_causal: bool = True,
                 key_padding_mask: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
         if set(streams) != set(self.modalities):
-            raise ValueError(f"MoTAttention.forward: streams {sorted(streams)} != modalities {sorted(self.modalities)}")
+            raise ValueError(f"MoTAttention.forward: streams keys {sorted(streams)} != modalities {sorted(self.modalities)}")
         hd, h, hkv = self.head_dim, self.n_heads, self.n_kv_heads
         qs, ks, vs, lengths = [], [], [], {}
         for m in self.modalities:
@@ -110,7 +110,7 @@ class MoTBlock(nn.Module):
 
     def forward(self, streams: dict[str, torch.Tensor], rope: dict, key_padding_mask: torch.Tensor | None = None):
         if set(streams) != set(self.modalities):
-            raise ValueError(f"MoTBlock.forward: streams {sorted(streams)} != modalities {sorted(self.modalities)}")
+            raise ValueError(f"MoTBlock.forward: streams keys {sorted(streams)} != modalities {sorted(self.modalities)}")
         attn = self.attn({m: self.attn_norm[m](streams[m]) for m in self.modalities}, rope, True, key_padding_mask)
         mid = {m: streams[m] + attn[m] for m in self.modalities}
         return {m: mid[m] + self.mlp[m](self.mlp_norm[m](mid[m])) for m in self.modalities}

@@ -29,7 +29,7 @@ def compute_layer_assignment(n_layers: int, pp_size: int) -> list[tuple[int, int
     if pp_size <= 0:
         raise ValueError("pp_size must be positive")
     if n_layers < pp_size:
-        raise ValueError(f"n_layers ({n_layers}) must be >= pp_size ({pp_size})")
+        raise ValueError(f"pp_size ({pp_size}) cannot exceed n_layers ({n_layers})")
     base, extra = divmod(n_layers, pp_size)
     out, start = [], 0
     for s in range(pp_size):

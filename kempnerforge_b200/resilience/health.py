@@ -49,8 +49,8 @@ class NaNDetector:
         st.total_nans += 1
         if len(st.nan_steps) < self.max_history:
             st.nan_steps.append(step)
-        where = "loss" if local_bad else "another rank"
-        msg = (f"NaN/Inf detected ({where}) at step {step} (consecutive={st.consecutive_nans}, "
+        where = "loss" if local_bad else "loss on another rank"
+        msg = (f"NaN/Inf {where} detected at step {step} (consecutive={st.consecutive_nans}, "
                f"total={st.total_nans}, last_good_step={st.last_good_step})")
         if self.action == "raise":
             raise RuntimeError(msg)
@@ -126,8 +126,9 @@ def check_nccl_health(timeout_sec: float = 10.0, group=None) -> bool:
     if not (dist.is_available() and dist.is_initialized()):
         return True
     try:
-        world = dist.get_world_size(group)
-        dev = "cuda" if torch.cuda.is_available() and "nccl" in str(dist.get_backend(group)) else "cpu"
+        world = dist.get_world_size(group) if group is not None else dist.get_world_size()
+        backend = dist.get_backend(group) if group is not None else dist.get_backend()
+        dev = "cuda" if torch.cuda.is_available() and "nccl" in str(backend) else "cpu"
         t = torch.ones(1, device=dev)
         work = dist.all_reduce(t, group=group, async_op=True)
         if not work.wait(timeout=timedelta(seconds=timeout_sec)):

@@ -26,16 +26,17 @@ def test_activation_store_and_extract_representations(tmp_path):
     model, cfg = _tiny_model()
     tokens = torch.randint(0, 128, (3, 16))
     names = ["layers.0.attention", "layers.1.mlp", "norm"]
-    with ActivationStore(model, names) as store:
+    with ActivationStore(model, names, keep_history=True) as store:
         model(tokens)
         model(tokens)
         got = store.get("layers.1.mlp")
-        assert got.shape == (6, 16, 64) and got.device.type == "cpu"       # two calls concatenated along the batch
-        assert store.get("norm", concat=False)[0].shape == (3, 16, 64)
-    model(tokens)  # hooks are gone: nothing new is recorded
-    assert store.get("norm").shape[0] == 6
+        assert got.shape == (3, 16, 64) and got.device.type == "cpu"       # the latest pass
+        assert len(store.history("norm")) == 2 and store.history("norm")[0].shape == (3, 16, 64)
+    kept = store.get("norm").clone()
+    model(torch.randint(0, 128, (3, 16)))  # hooks are gone: nothing new is recorded
+    assert torch.equal(store.get("norm"), kept)
     with pytest.raises(KeyError):
-        ActivationStore(model, ["layers.9.mlp"])
+        ActivationStore(model, ["layers.9.mlp"]).enable()
     reps = extract_representations(model, [{"input_ids": tokens}, tokens[:1]], names, pool="mean")
     assert reps["norm"].shape == (4, 64) and model.training
     last = extract_representations(model, [tokens], ["norm"], pool="last")["norm"]

@@ -40,10 +40,15 @@ def test_activation_store_captures_named_modules_detached():
             act = store.get(name)
             assert act.shape == (2, 7, 32) and not act.requires_grad and act.device.type == "cpu"
             assert act.abs().sum() > 0
-        m(ids)
-        assert store.get("norm").shape == (4, 7, 32) and len(store.get("norm", concat=False)) == 2
+        first = store.get("norm").clone()
+        m(torch.randint(0, 40, (2, 7)))
+        assert store.get("norm").shape == (2, 7, 32) and not torch.equal(store.get("norm"), first)   # the latest pass only
         store.clear()
-        assert store.get("norm") == []
+        assert store.get("norm") is None and store.activations == {}
+    with ActivationStore(m, ["norm"], keep_history=True) as hist:
+        m(ids)
+        m(ids)
+        assert len(hist.history("norm")) == 2 and torch.equal(hist.history("norm")[1], hist.get("norm"))
     assert not any(mod._forward_hooks for mod in m.modules())          # no hook outlives the context
     m(ids)                                                            # and the model still runs
 
@@ -51,7 +56,7 @@ def test_activation_store_captures_named_modules_detached():
 def test_activation_store_rejects_unknown_modules_and_does_not_touch_weights():
     m = _model()
     with pytest.raises(KeyError):
-        ActivationStore(m, ["layers.99"])
+        ActivationStore(m, ["layers.99"]).enable()          # unknown names surface when the hooks are installed
     before = copy.deepcopy(m.state_dict())
     with ActivationStore(m, ["layers.1"]) as store:
         m(torch.randint(0, 40, (1, 5)))
@@ -294,19 +299,19 @@ def test_optimizer_config_rules():
 def test_activation_store_enable_disable_and_dataset_extraction(tmp_path):
     m = _model()
     store = ActivationStore(m, layers=["norm"])
-    assert store.enabled and store.layer_names == ["norm"]
-    store.disable()
-    assert not store.enabled
+    assert not store.enabled and store.layer_names == ["norm"]      # hooks are installed by enable(), not at construction
     tokens = torch.randint(0, 40, (2, 5))
     m(tokens)
-    assert store.get("norm") == []            # nothing captured while disabled
+    assert store.get("norm") is None          # nothing captured while disabled
     store.enable()
     store.enable()                            # idempotent
+    assert store.enabled and sum(len(mod._forward_hooks) for mod in m.modules()) == 1
     m(tokens)
     assert store.get("norm").shape[0] == 2
     store.disable()
-    with pytest.raises(ValueError):
-        ActivationStore(m, layers=["nope"])
+    assert not store.enabled
+    with pytest.raises(ValueError, match="not found"):
+        ActivationStore(m, layers=["nope"]).enable()
 
     class Samples(torch.utils.data.Dataset):
         def __len__(self):
