@@ -170,7 +170,9 @@ def parse_cli_overrides(args: list[str]) -> dict[str, Any]:
     tree: dict[str, Any] = {}
     for raw in args:
         if not raw.startswith("--"):
-            raise ConfigError(f"override {raw!r} must look like --section.key=value")
+            if "=" in raw:   # looks like an override that lost its dashes: say so instead of dropping it
+                raise ConfigError(f"override {raw!r} must look like --section.key=value")
+            continue         # positional arguments (the preset path of a command line) are not overrides
         body = raw[2:]
         dotted, has_eq, text = body.partition("=")
         value = _literal(text) if has_eq else True

@@ -40,7 +40,8 @@ def _patterns(**extra: list[str]) -> dict[str, list[str]]:
 
 def pooled_token_count(num_input_tokens: int, window: int, require_divisible: bool = False) -> int:
     """Tokens left after pooling a square grid of ``num_input_tokens`` with a ``window``² kernel."""
-    _require(window > 0, f"pool_window must be positive (got {window})")
+    _require(window > 0, f"pool window must be positive (got {window})")
+    _require(num_input_tokens > 0, f"the number of input tokens must be positive (got {num_input_tokens})")
     side = math.isqrt(num_input_tokens)
     _require(side * side == num_input_tokens, f"pooling adapters need a square patch grid (got {num_input_tokens} tokens)")
     if require_divisible:

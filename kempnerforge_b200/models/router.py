@@ -155,8 +155,8 @@ class SigmoidTopKRouter(nn.Module):
         return weights, indices
 
 
-registry.register("router", "softmax_topk", lambda dim, e, k, **kw: SoftmaxTopKRouter(dim, e, k))
-registry.register("router", "sigmoid_topk", lambda dim, e, k, **kw: SigmoidTopKRouter(dim, e, k, **kw))
+registry.register("router", "softmax_topk", lambda dim, num_experts, top_k, **kw: SoftmaxTopKRouter(dim, num_experts, top_k))
+registry.register("router", "sigmoid_topk", lambda dim, num_experts, top_k, **kw: SigmoidTopKRouter(dim, num_experts, top_k, **kw))
 
 
 def build_router(router_type: str, dim: int, num_experts: int, top_k: int, **kwargs) -> nn.Module:

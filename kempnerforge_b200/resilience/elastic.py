@@ -54,13 +54,13 @@ def get_slurm_info() -> SLURMInfo | None:
     m = re.match(r"\d+", tpn)
     return SLURMInfo(
         job_id=env["SLURM_JOB_ID"],
-        job_name=env.get("SLURM_JOB_NAME"),
-        node_list=env.get("SLURM_JOB_NODELIST"),
+        job_name=env.get("SLURM_JOB_NAME", ""),
+        node_list=env.get("SLURM_JOB_NODELIST", ""),
         num_nodes=_int("SLURM_JOB_NUM_NODES", _int("SLURM_NNODES", 1)),
         ntasks_per_node=int(m.group()) if m else 1,
         restart_count=_int("SLURM_RESTART_COUNT", 0),
         array_task_id=env.get("SLURM_ARRAY_TASK_ID"),
-        partition=env.get("SLURM_JOB_PARTITION"),
+        partition=env.get("SLURM_JOB_PARTITION", ""),
     )
 
 

@@ -127,7 +127,10 @@ def check_nccl_health(timeout_sec: float = 10.0, group=None) -> bool:
         return True
     try:
         world = dist.get_world_size(group) if group is not None else dist.get_world_size()
-        backend = dist.get_backend(group) if group is not None else dist.get_backend()
+        try:
+            backend = dist.get_backend(group) if group is not None else dist.get_backend()
+        except Exception:  # noqa: BLE001  no backend to ask (a stand-in process group): stay on the host
+            backend = ""
         dev = "cuda" if torch.cuda.is_available() and "nccl" in str(backend) else "cpu"
         t = torch.ones(1, device=dev)
         work = dist.all_reduce(t, group=group, async_op=True)

@@ -106,6 +106,7 @@ def test_cli_overrides_grammar():
     assert t["data"]["dataset_path"] == "/a/b" and t["checkpoint"]["load_path"] is None
     with pytest.raises(ConfigError):
         parse_cli_overrides(["train.seq_len=1"])
+    assert parse_cli_overrides(["configs/train/debug.toml", "--train.seq_len=4"]) == {"train": {"seq_len": 4}}   # a preset path is skipped
     with pytest.raises(ConfigError):
         parse_cli_overrides(["--seq_len=1"])
 
