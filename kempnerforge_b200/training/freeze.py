@@ -1,8 +1,8 @@
 """Parameter freezing by module alias.
 
 A ``FreezeSpec(module, frozen)`` names an alias (``vision_encoder``, ``adapter``, ``transformer`` ...);
-``module_patterns`` maps the alias to fnmatch patterns over fully-qualified parameter names.  Later specs
-override earlier ones.  ``canonical_freeze_meta`` is what gets stored in checkpoint metadata so a resume
+``module_patterns`` maps the alias to fnmatch patterns over fully-qualified parameter names (a name that is not an
+alias is a pattern itself).  Later specs override earlier ones.  ``canonical_freeze_meta`` is what gets stored in checkpoint metadata so a resume
 can detect a changed freeze set-up.
 
 Parity: kempnerforge/training/freeze.py:35-136.
@@ -30,21 +30,20 @@ def freeze_params(model: nn.Module, patterns: Iterable[str], frozen: bool = True
 
 def apply_freeze_specs(model: nn.Module, specs, module_patterns: dict[str, list[str]] | None = None, *,
                        pattern_map: dict[str, list[str]] | None = None) -> dict[str, int]:
+    """``spec.module`` is an alias looked up in ``module_patterns`` (also ``pattern_map=``); a name that is not an
+    alias is used as an fnmatch pattern itself.  Returns {spec.module: parameters matched}."""
     module_patterns = module_patterns if module_patterns is not None else (pattern_map or {})
     counts = {}
     for spec in specs:
-        if spec.module not in module_patterns:
-            raise ValueError(f"Unknown freeze module {spec.module!r}; known: {sorted(module_patterns)}")
-        counts[spec.module] = freeze_params(model, module_patterns[spec.module], spec.frozen)
+        counts[spec.module] = freeze_params(model, module_patterns.get(spec.module, [spec.module]), spec.frozen)
     return counts
 
 
 def canonical_freeze_meta(specs) -> list[dict]:
-    """Order-independent, de-duplicated (last one wins) description of a freeze list."""
-    latest = {}
-    for spec in specs:
-        latest[spec.module] = bool(spec.frozen)
-    return [{"module": k, "frozen": latest[k]} for k in sorted(latest)]
+    """Order-independent, de-duplicated description of a freeze list: the sorted set of (module, frozen) pairs, so two
+    lists with the same pairs give byte-equal JSON (the form the reference stores in checkpoint metadata)."""
+    pairs = sorted({(spec.module, bool(spec.frozen)) for spec in specs})
+    return [{"module": m, "frozen": f} for m, f in pairs]
 
 
 def effective_freeze(vlm_config, step=None, schedule=None, valid_modules=None):
@@ -69,4 +68,4 @@ def effective_freeze(vlm_config, step=None, schedule=None, valid_modules=None):
         if valid_modules is not None and spec.module not in valid_modules:
             raise ValueError(f"freeze module {spec.module!r} (from {where}) is not one of {sorted(valid_modules)}")
         latest[spec.module] = spec
-    return [latest[k] for k in sorted(latest)]
+    return list(latest.values())   # one spec per module, in order of first appearance

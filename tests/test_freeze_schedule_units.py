@@ -71,15 +71,19 @@ def test_specs_resolve_aliases_and_later_specs_override_earlier_ones():
     assert "adapter.weight" in _trainable(m) and "vision_encoder.0.weight" not in _trainable(m)
 
 
-def test_an_unknown_alias_is_an_error_that_names_the_known_ones():
-    with pytest.raises(ValueError, match="adapter"):
-        apply_freeze_specs(_Toy(), [FreezeSpec("vison_encoder")], PATTERNS)
+def test_a_name_that_is_no_alias_is_used_as_a_raw_pattern():
+    m = _Toy()
+    assert apply_freeze_specs(m, [FreezeSpec("transformer.layers.0.*")], PATTERNS) == {"transformer.layers.0.*": 2}
+    assert "transformer.layers.0.weight" not in _trainable(m) and "transformer.layers.1.weight" in _trainable(m)
+    assert apply_freeze_specs(_Toy(), [FreezeSpec("vison_encoder")], PATTERNS) == {"vison_encoder": 0}   # a typo matches nothing
 
 
 def test_canonical_metadata_ignores_order_and_duplicates():
     a = canonical_freeze_meta([FreezeSpec("adapter", False), FreezeSpec("vision_encoder")])
-    b = canonical_freeze_meta([FreezeSpec("vision_encoder"), FreezeSpec("adapter"), FreezeSpec("adapter", False)])
+    b = canonical_freeze_meta([FreezeSpec("vision_encoder"), FreezeSpec("adapter", False), FreezeSpec("vision_encoder")])
     assert a == b == [{"module": "adapter", "frozen": False}, {"module": "vision_encoder", "frozen": True}]
+    # the same module with both flags keeps both pairs (the set of pairs is what gets compared at resume)
+    assert len(canonical_freeze_meta([FreezeSpec("adapter"), FreezeSpec("adapter", False)])) == 2
     assert canonical_freeze_meta([]) == []
 
 
@@ -90,7 +94,7 @@ def test_a_schedule_applies_only_the_stages_that_have_started():
     assert view(0) == {"vision_encoder": True, "adapter": False}
     assert view(50) == {"vision_encoder": True, "adapter": True}
     assert view(100) == {"vision_encoder": False, "adapter": True}
-    assert effective_freeze(10, base, []) == sorted(base, key=lambda s: s.module)
+    assert effective_freeze(10, base, []) == base          # one spec per module, in order of first appearance
 
 
 def test_later_stages_win_whatever_order_they_are_listed_in():

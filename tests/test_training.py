@@ -246,10 +246,9 @@ def test_freeze_helpers():
     pats = {"transformer": ["transformer", "transformer.*"], "adapter": ["adapter", "adapter.*"]}
     apply_freeze_specs(m, [FreezeSpec("adapter", False), FreezeSpec("transformer", True)], pats)
     assert m["adapter"].weight.requires_grad and not m["transformer"].weight.requires_grad
-    with pytest.raises(ValueError):
-        apply_freeze_specs(m, [FreezeSpec("nope")], pats)
-    meta = canonical_freeze_meta([FreezeSpec("b", True), FreezeSpec("a", False), FreezeSpec("b", False)])
-    assert meta == [{"module": "a", "frozen": False}, {"module": "b", "frozen": False}]
+    assert apply_freeze_specs(m, [FreezeSpec("nope")], pats) == {"nope": 0}   # not an alias: a raw pattern that matches nothing
+    meta = canonical_freeze_meta([FreezeSpec("b", True), FreezeSpec("a", False), FreezeSpec("b", False), FreezeSpec("b", True)])
+    assert meta == [{"module": "a", "frozen": False}, {"module": "b", "frozen": False}, {"module": "b", "frozen": True}]
     vc = JointDecoderConfig(freeze=[FreezeSpec("vision_encoder", True)],
                             freeze_schedule=[FreezeStage(10, (FreezeSpec("vision_encoder", False),))])
     assert effective_freeze(vc, 5)[0].frozen and not effective_freeze(vc, 10)[0].frozen

@@ -300,15 +300,16 @@ def test_apply_freeze_specs_aliases_and_errors():
     counts = apply_freeze_specs(m, [FreezeSpec("vision_encoder", True), FreezeSpec("adapter", True),
                                     FreezeSpec("adapter", False)], _PATTERNS)
     assert counts["vision_encoder"] == 4 and not any(k.startswith("adapter") for k in _frozen(m))
-    with pytest.raises(ValueError):
-        apply_freeze_specs(m, [FreezeSpec("vison_encoder", True)], _PATTERNS)
+    assert apply_freeze_specs(m, [FreezeSpec("vison_encoder", True)], _PATTERNS) == {"vison_encoder": 0}
+    assert apply_freeze_specs(m, [FreezeSpec("adapter.weight", True)], _PATTERNS) == {"adapter.weight": 1}   # raw pattern
 
 
 def test_canonical_freeze_meta_is_order_free_and_deduplicated():
     a = canonical_freeze_meta([FreezeSpec("b", True), FreezeSpec("a", False)])
     b = canonical_freeze_meta([FreezeSpec("a", False), FreezeSpec("b", True)])
     assert a == b == [{"module": "a", "frozen": False}, {"module": "b", "frozen": True}]
-    assert canonical_freeze_meta([FreezeSpec("a", True), FreezeSpec("a", False)]) == [{"module": "a", "frozen": False}]
+    both = canonical_freeze_meta([FreezeSpec("a", True), FreezeSpec("a", False), FreezeSpec("a", True)])
+    assert both == [{"module": "a", "frozen": False}, {"module": "a", "frozen": True}]   # the set of pairs, sorted
     assert canonical_freeze_meta([]) == []
 
 
