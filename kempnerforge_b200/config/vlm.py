@@ -23,6 +23,8 @@ BASE_MODULE_PATTERNS: dict[str, list[str]] = {
     "adapter": ["adapter", "adapter.*"],
 }
 
+DEFAULT_MODULE_PATTERNS = BASE_MODULE_PATTERNS   # the name this table has in the reference (kempnerforge/config/vlm.py)
+
 # adapter families that shrink the visual token grid
 POOLING_ADAPTER_TYPES: tuple[str, ...] = ("avgpool", "attentional_pool")
 DIVISIBLE_ONLY_POOL_TYPES: tuple[str, ...] = ("attentional_pool",)

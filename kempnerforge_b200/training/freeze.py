@@ -17,15 +17,16 @@ from torch import nn
 
 
 def freeze_params(model: nn.Module, patterns: Iterable[str], frozen: bool = True) -> int:
-    """Set ``requires_grad = not frozen`` on every parameter whose name matches a pattern; returns the count."""
+    """Set ``requires_grad = not frozen`` on every parameter whose fully-qualified name matches a pattern.  Only
+    parameters whose state differs are touched, and the return value is the number of ELEMENTS flipped (so a second
+    identical call returns 0)."""
     patterns = list(patterns)
-    hit = 0
+    flipped = 0
     for name, p in model.named_parameters():
-        owner = name.rsplit(".", 1)[0] if "." in name else name
-        if any(fnmatch.fnmatch(name, pat) or fnmatch.fnmatch(owner, pat) for pat in patterns):
+        if p.requires_grad == frozen and any(fnmatch.fnmatch(name, pat) for pat in patterns):
             p.requires_grad_(not frozen)
-            hit += 1
-    return hit
+            flipped += p.numel()
+    return flipped
 
 
 def apply_freeze_specs(model: nn.Module, specs, module_patterns: dict[str, list[str]] | None = None, *,
@@ -46,18 +47,20 @@ def canonical_freeze_meta(specs) -> list[dict]:
     return [{"module": m, "frozen": f} for m, f in pairs]
 
 
-def effective_freeze(vlm_config, step=None, schedule=None, valid_modules=None):
+def effective_freeze(step=None, base=None, schedule=None, valid_modules=None):
     """Static freeze list overlaid by every schedule stage whose start_step <= step (later stages win per module).
 
-    Two call forms: ``effective_freeze(vlm_config, step)`` and ``effective_freeze(step, base, schedule,
-    valid_modules=None)`` with explicit lists; the latter raises ValueError for a module key outside
-    ``valid_modules``.  Parity: kempnerforge/training/freeze.py:91-140.
+    Two call forms: ``effective_freeze(step, base, schedule, valid_modules=None)`` with explicit lists (also by
+    keyword), which raises ValueError for a module key outside ``valid_modules``, and ``effective_freeze(vlm_config,
+    step)`` which takes both lists from a VLM config (``None`` config: no freezing).
+    Parity: kempnerforge/training/freeze.py:91-140.
     """
-    if isinstance(vlm_config, int) and not isinstance(vlm_config, bool):
-        step, base, stages = vlm_config, list(step or []), list(schedule or [])
-    elif vlm_config is None:
+    if isinstance(step, int) and not isinstance(step, bool):
+        base, stages = list(base or []), list(schedule or [])
+    elif step is None:          # effective_freeze(None, step): a model without a VLM section freezes nothing
         return []
     else:
+        vlm_config, step = step, base
         base, stages = list(vlm_config.freeze), list(vlm_config.freeze_schedule)
     applied = [("base", spec) for spec in base]
     for stage in sorted(stages, key=lambda s: s.start_step):

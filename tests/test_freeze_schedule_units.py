@@ -33,7 +33,7 @@ def _trainable(model):
 
 def test_matching_parameters_are_frozen_and_counted():
     m = _Toy()
-    assert freeze_params(m, ["vision_encoder.*"]) == 4
+    assert freeze_params(m, ["vision_encoder.*"]) == 2 * (16 + 4)        # the number of ELEMENTS whose flag changed
     assert not any(n.startswith("vision_encoder") for n in _trainable(m)) and "adapter.weight" in _trainable(m)
 
 
@@ -41,10 +41,9 @@ def test_no_patterns_change_nothing_and_freezing_twice_is_the_same_as_once():
     m = _Toy()
     before = _trainable(m)
     assert freeze_params(m, []) == 0 and _trainable(m) == before
-    freeze_params(m, ["adapter.*"])
+    assert freeze_params(m, ["adapter.*"]) == 20
     once = _trainable(m)
-    freeze_params(m, ["adapter.*"])
-    assert _trainable(m) == once
+    assert freeze_params(m, ["adapter.*"]) == 0 and _trainable(m) == once      # nothing left to flip
 
 
 def test_thawing_is_freezing_with_the_flag_off():
@@ -55,25 +54,26 @@ def test_thawing_is_freezing_with_the_flag_off():
     assert _trainable(m) == {"adapter.weight", "adapter.bias"}
 
 
-def test_a_pattern_may_name_one_parameter_or_one_module_and_patterns_add_up():
+def test_patterns_match_fully_qualified_parameter_names_and_add_up():
     m = _Toy()
-    assert freeze_params(m, ["transformer.layers.1.weight"]) == 1
-    assert freeze_params(m, ["vision_encoder.0"]) == 2            # the owning module's name matches as well
+    assert freeze_params(m, ["transformer.layers.1.weight"]) == 16
+    assert freeze_params(m, ["vision_encoder.0"]) == 0            # a module name alone is not a parameter name
+    assert freeze_params(m, ["vision_encoder.0.*"]) == 20
     m2 = _Toy()
-    assert freeze_params(m2, ["adapter.*", "transformer.layers.0.*"]) == 4
+    assert freeze_params(m2, ["adapter.*", "transformer.layers.0.*"]) == 40
 
 
 def test_specs_resolve_aliases_and_later_specs_override_earlier_ones():
     m = _Toy()
     counts = apply_freeze_specs(m, [FreezeSpec("vision_encoder"), FreezeSpec("adapter"), FreezeSpec("adapter", frozen=False)],
                                 PATTERNS)
-    assert counts == {"vision_encoder": 4, "adapter": 2}
+    assert counts == {"vision_encoder": 40, "adapter": 20}       # per alias: elements flipped by its LAST spec
     assert "adapter.weight" in _trainable(m) and "vision_encoder.0.weight" not in _trainable(m)
 
 
 def test_a_name_that_is_no_alias_is_used_as_a_raw_pattern():
     m = _Toy()
-    assert apply_freeze_specs(m, [FreezeSpec("transformer.layers.0.*")], PATTERNS) == {"transformer.layers.0.*": 2}
+    assert apply_freeze_specs(m, [FreezeSpec("transformer.layers.0.*")], PATTERNS) == {"transformer.layers.0.*": 20}
     assert "transformer.layers.0.weight" not in _trainable(m) and "transformer.layers.1.weight" in _trainable(m)
     assert apply_freeze_specs(_Toy(), [FreezeSpec("vison_encoder")], PATTERNS) == {"vison_encoder": 0}   # a typo matches nothing
 

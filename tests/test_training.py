@@ -241,7 +241,7 @@ def test_freeze_helpers():
     from kempnerforge_b200.config import FreezeSpec, FreezeStage, JointDecoderConfig
 
     m = torch.nn.ModuleDict({"transformer": torch.nn.Linear(2, 2), "adapter": torch.nn.Linear(2, 2)})
-    assert freeze_params(m, ["adapter", "adapter.*"]) == 2
+    assert freeze_params(m, ["adapter", "adapter.*"]) == 6          # elements flipped: a 2 x 2 weight and a bias of 2
     assert not m["adapter"].weight.requires_grad and m["transformer"].weight.requires_grad
     pats = {"transformer": ["transformer", "transformer.*"], "adapter": ["adapter", "adapter.*"]}
     apply_freeze_specs(m, [FreezeSpec("adapter", False), FreezeSpec("transformer", True)], pats)
