@@ -32,13 +32,18 @@ MESH_DIM_ORDER = ("pp", "dp_replicate", "dp_shard", "ep", "tp")
 
 
 def get_world_info() -> tuple[int, int, int]:
-    """(rank, local_rank, world_size) from torchrun variables, else SLURM, else a single process."""
+    """(rank, local_rank, world_size) from torchrun variables, else SLURM, else a single process.  The three standard
+    variables are exported when they were missing, so that an ``env://`` rendezvous started under ``srun`` finds them."""
     env = os.environ
     if "RANK" in env:
-        return int(env["RANK"]), int(env.get("LOCAL_RANK", 0)), int(env.get("WORLD_SIZE", 1))
-    if "SLURM_PROCID" in env:
-        return int(env["SLURM_PROCID"]), int(env.get("SLURM_LOCALID", 0)), int(env.get("SLURM_NTASKS", 1))
-    return 0, 0, 1
+        info = int(env["RANK"]), int(env.get("LOCAL_RANK", 0)), int(env.get("WORLD_SIZE", 1))
+    elif "SLURM_PROCID" in env:
+        info = int(env["SLURM_PROCID"]), int(env.get("SLURM_LOCALID", 0)), int(env.get("SLURM_NTASKS", 1))
+    else:
+        info = 0, 0, 1
+    for key, value in zip(("RANK", "LOCAL_RANK", "WORLD_SIZE"), info):
+        env.setdefault(key, str(value))
+    return info
 
 
 def is_rank_zero() -> bool:
@@ -58,18 +63,22 @@ def _detect_ib_interface() -> str | None:
 
 
 def _set_nccl_env() -> None:
-    """Defaults only — anything the user exported wins."""
+    """Defaults only: anything the user exported wins.  NCCL and Gloo are bound to the same interface (the one the
+    user named for NCCL, else the first InfiniBand interface that is up); the InfiniBand / GPUDirect defaults are set
+    whether or not such an interface was found; TORCH_NCCL_ASYNC_ERROR_HANDLING defaults to 1 and an explicit 0 is
+    kept but warned about (process-group timeouts are then advisory)."""
     env = os.environ
-    iface = None
-    if "NCCL_SOCKET_IFNAME" not in env or "GLOO_SOCKET_IFNAME" not in env:
-        iface = _detect_ib_interface()
+    iface = env.get("NCCL_SOCKET_IFNAME") or _detect_ib_interface()
     if iface:
         env.setdefault("NCCL_SOCKET_IFNAME", iface)
         env.setdefault("GLOO_SOCKET_IFNAME", iface)
-        env.setdefault("NCCL_IB_DISABLE", "0")
-        env.setdefault("NCCL_NET_GDR_LEVEL", "2")
-    if env.get("TORCH_NCCL_ASYNC_ERROR_HANDLING") != "0":
-        env["TORCH_NCCL_ASYNC_ERROR_HANDLING"] = "1"
+    env.setdefault("NCCL_IB_DISABLE", "0")
+    env.setdefault("NCCL_NET_GDR_LEVEL", "2")
+    if env.get("TORCH_NCCL_ASYNC_ERROR_HANDLING") == "0":
+        log.warning("TORCH_NCCL_ASYNC_ERROR_HANDLING=0 detected: NCCL timeouts are advisory, a stuck collective can hang "
+                    "for ever")
+    else:
+        env.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
 
 
 def barrier_with_timeout(timeout_sec: float = 60.0, group=None, reason: str = "") -> None:

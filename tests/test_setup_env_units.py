@@ -15,21 +15,38 @@ from kempnerforge_b200.parallel import setup as kf_setup
 _RANK_VARS = ("RANK", "LOCAL_RANK", "WORLD_SIZE", "SLURM_PROCID", "SLURM_LOCALID", "SLURM_NTASKS")
 
 
+_ENV_VARS = _RANK_VARS + ("NCCL_SOCKET_IFNAME", "GLOO_SOCKET_IFNAME", "NCCL_IB_DISABLE", "NCCL_NET_GDR_LEVEL",
+                          "TORCH_NCCL_ASYNC_ERROR_HANDLING", "MASTER_ADDR", "MASTER_PORT", "SLURM_JOB_NODELIST", "SLURM_JOB_ID")
+
+
 @pytest.fixture
 def clean_env(monkeypatch):
-    for k in _RANK_VARS + ("NCCL_SOCKET_IFNAME", "GLOO_SOCKET_IFNAME", "NCCL_IB_DISABLE", "NCCL_NET_GDR_LEVEL",
-                           "TORCH_NCCL_ASYNC_ERROR_HANDLING", "MASTER_ADDR", "MASTER_PORT", "SLURM_JOB_NODELIST",
-                           "SLURM_JOB_ID"):
-        monkeypatch.delenv(k, raising=False)
-    return monkeypatch
+    import os
+
+    saved = {k: os.environ.get(k) for k in _ENV_VARS}
+    for k in _ENV_VARS:
+        os.environ.pop(k, None)
+    yield monkeypatch
+    monkeypatch.undo()
+    for k, v in saved.items():        # the functions under test export variables themselves: put the process back
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
 
 
 def test_world_info_precedence(clean_env):
+    import os
+
     assert kf_setup.get_world_info() == (0, 0, 1)
+    assert (os.environ["RANK"], os.environ["LOCAL_RANK"], os.environ["WORLD_SIZE"]) == ("0", "0", "1")   # exported for env://
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        del os.environ[k]
     clean_env.setenv("SLURM_PROCID", "5")
     clean_env.setenv("SLURM_LOCALID", "1")
     clean_env.setenv("SLURM_NTASKS", "8")
     assert kf_setup.get_world_info() == (5, 1, 8)
+    assert (os.environ["RANK"], os.environ["LOCAL_RANK"], os.environ["WORLD_SIZE"]) == ("5", "1", "8")
     clean_env.setenv("RANK", "3")
     clean_env.setenv("LOCAL_RANK", "3")
     clean_env.setenv("WORLD_SIZE", "4")
@@ -82,7 +99,7 @@ def test_nccl_defaults_never_override_the_user(clean_env):
     _fake_ip(clean_env, "ib0 UP 10.1.0.2/16\n")
     kf_setup._set_nccl_env()
     assert os.environ["NCCL_SOCKET_IFNAME"] == "eth7" and os.environ["TORCH_NCCL_ASYNC_ERROR_HANDLING"] == "0"
-    assert "NCCL_IB_DISABLE" not in os.environ
+    assert os.environ["NCCL_IB_DISABLE"] == "0"            # a default nobody set: filled in
 
 
 def test_nccl_defaults_without_infiniband(clean_env):
@@ -90,7 +107,20 @@ def test_nccl_defaults_without_infiniband(clean_env):
 
     _fake_ip(clean_env, "eth0 UP 10.0.0.2/24\n")
     kf_setup._set_nccl_env()
-    assert "NCCL_SOCKET_IFNAME" not in os.environ and os.environ["TORCH_NCCL_ASYNC_ERROR_HANDLING"] == "1"
+    assert "NCCL_SOCKET_IFNAME" not in os.environ and "GLOO_SOCKET_IFNAME" not in os.environ
+    assert os.environ["TORCH_NCCL_ASYNC_ERROR_HANDLING"] == "1" and os.environ["NCCL_IB_DISABLE"] == "0"
+
+
+def test_gloo_follows_the_interface_the_user_named_for_nccl_and_a_disabled_watchdog_is_warned_about(clean_env, caplog):
+    import os
+
+    clean_env.setenv("NCCL_SOCKET_IFNAME", "eth3")
+    clean_env.setenv("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
+    _fake_ip(clean_env, error=AssertionError("no detection when the user named an interface"))
+    with caplog.at_level("WARNING", logger=kf_setup.log.name):
+        kf_setup._set_nccl_env()
+    assert os.environ["GLOO_SOCKET_IFNAME"] == "eth3" and os.environ["TORCH_NCCL_ASYNC_ERROR_HANDLING"] == "0"
+    assert any("TORCH_NCCL_ASYNC_ERROR_HANDLING=0" in r.getMessage() for r in caplog.records)
 
 
 def test_master_resolution(clean_env):
