@@ -49,14 +49,27 @@ class CrossAttention(nn.Module):
 
 
 class CrossAttentionBlock(nn.Module):
-    def __init__(self, config, n_heads: int | None = None, n_kv_heads: int | None = None) -> None:
+    """Two ways to build one: from a model config (``CrossAttentionBlock(config, n_heads=, n_kv_heads=)``) or from loose
+    dimensions as in the reference (``CrossAttentionBlock(dim=, n_heads=, n_kv_heads=, ffn_hidden_dim=, norm_type=,
+    activation=)``)."""
+
+    def __init__(self, config=None, n_heads: int | None = None, n_kv_heads: int | None = None, ffn_hidden_dim: int | None = None,
+                 norm_type: str = "rmsnorm", activation: str = "silu", *, dim: int | None = None) -> None:
         super().__init__()
-        n_heads = n_heads or config.n_heads
+        if config is None or isinstance(config, int):          # loose dimensions
+            dim = dim if dim is not None else config
+            if dim is None or n_heads is None or ffn_hidden_dim is None:
+                raise TypeError("CrossAttentionBlock needs a model config, or dim, n_heads and ffn_hidden_dim")
+            eps, hidden = 1e-5, ffn_hidden_dim
+        else:
+            dim, norm_type, activation, eps = config.dim, config.norm_type, config.activation, config.norm_eps
+            n_heads = n_heads or config.n_heads
+            hidden = ffn_hidden_dim or config.computed_ffn_hidden_dim
         n_kv_heads = n_kv_heads or n_heads
-        self.attn_norm = build_norm(config.norm_type, config.dim, config.norm_eps)
-        self.attn = CrossAttention(config.dim, n_heads, n_kv_heads)
-        self.mlp_norm = build_norm(config.norm_type, config.dim, config.norm_eps)
-        self.mlp = build_mlp(config.dim, config.computed_ffn_hidden_dim, config.activation)
+        self.attn_norm = build_norm(norm_type, dim, eps)
+        self.attn = CrossAttention(dim, n_heads, n_kv_heads)
+        self.mlp_norm = build_norm(norm_type, dim, eps)
+        self.mlp = build_mlp(dim, hidden, activation)
         self.mlp.down_proj.weight._kf_zero_init = True
         nn.init.zeros_(self.mlp.down_proj.weight)
 

@@ -128,8 +128,24 @@ class MoMaFFN(nn.Module):
 
 
 class MoMaBlock(nn.Module):
-    def __init__(self, config, vlm_config, layer_idx: int) -> None:
+    def __init__(self, config, modalities, experts_per_modality=None, capacity_factor_per_modality=None,
+                 gumbel_noise: bool | None = None, layer_idx: int | None = None) -> None:
+        """Either ``MoMaBlock(config, vlm_config, layer_idx)`` (everything from the VLM section) or the reference's
+        explicit form ``MoMaBlock(config, modalities, experts_per_modality, capacity_factor_per_modality, gumbel_noise,
+        layer_idx)``."""
         super().__init__()
+        if hasattr(modalities, "moma_modalities"):
+            vlm_config = modalities
+            if layer_idx is None:
+                layer_idx = experts_per_modality        # third positional argument of the short form
+        else:
+            from types import SimpleNamespace
+
+            caps_in = dict(capacity_factor_per_modality or {})
+            vlm_config = SimpleNamespace(moma_modalities=tuple(modalities),
+                                         moma_experts_per_modality=dict(experts_per_modality or {}),
+                                         moma_gumbel_noise=bool(gumbel_noise),
+                                         effective_capacity_factor=lambda m: caps_in.get(m, 0.0))
         self.layer_idx = layer_idx
         self.ac_mode = "none"
         self.modalities = tuple(vlm_config.moma_modalities)

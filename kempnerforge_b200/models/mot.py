@@ -80,9 +80,10 @@ class MoTAttention(nn.Module):
 
 
 class MoTBlock(nn.Module):
-    def __init__(self, config, vlm_config_or_modalities, layer_idx: int) -> None:
+    def __init__(self, config, modalities, layer_idx: int) -> None:
+        """``modalities``: a tuple of stream names, or a VLM config that carries ``mot_modalities``."""
         super().__init__()
-        mods = getattr(vlm_config_or_modalities, "mot_modalities", vlm_config_or_modalities)
+        mods = getattr(modalities, "mot_modalities", modalities)
         if not mods:
             raise ValueError("MoTBlock requires at least one modality")
         self.layer_idx = layer_idx
