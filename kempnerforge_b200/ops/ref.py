@@ -24,10 +24,15 @@ IGNORE_INDEX = -100
 
 
 # --------------------------------------------------------------------------- norm
+def _wide(x: torch.Tensor) -> torch.Tensor:
+    """fp32 for the arithmetic of half-precision inputs; float64 stays float64 (gradient checks run in double)."""
+    return x if x.dtype == torch.float64 else x.float()
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
+    xf = _wide(x)
     inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
-    return (xf * inv * weight.float()).to(x.dtype)
+    return (xf * inv * weight.to(xf.dtype)).to(x.dtype)
 
 
 # --------------------------------------------------------------------------- rope
@@ -98,9 +103,9 @@ def attention(
     sk, hkv = k.shape[1], k.shape[2]
     group = h // hkv
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
-    qf = q.transpose(1, 2).float().reshape(b, hkv, group, sq, hd)
-    kf = k.transpose(1, 2).float()[:, :, None]
-    vf = v.transpose(1, 2).float()[:, :, None]
+    qf = _wide(q.transpose(1, 2)).reshape(b, hkv, group, sq, hd)
+    kf = _wide(k.transpose(1, 2))[:, :, None]
+    vf = _wide(v.transpose(1, 2))[:, :, None]
     scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale  # (B, Hkv, G, Sq, Sk)
     mask = attention_mask(sq, sk, causal, doc_ids, key_padding_mask, device=q.device)
     if mask is not None:
@@ -120,7 +125,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- loss
 def cross_entropy_parts(logits: torch.Tensor, labels: torch.Tensor):
     """Returns (sum of nll over valid tokens, sum of logsumexp², valid count), all fp32 scalars."""
-    lf = logits.float()
+    lf = _wide(logits)
     lse = torch.logsumexp(lf, dim=-1)
     valid = labels != IGNORE_INDEX
     safe = labels.clamp_min(0)
