@@ -42,17 +42,29 @@ from kempnerforge_b200.resilience.elastic import list_step_dirs
 log = logging.getLogger(__name__)
 
 
-class UntrustedCheckpointError(RuntimeError):
-    pass
+class UntrustedCheckpointError(PermissionError, RuntimeError):
+    """``train_state.pt`` is a pickle: a file that another user owns is not loaded."""
 
 
 def check_trusted_file(path: Path) -> None:
-    """Refuse to unpickle a file that another (non-root) user owns or that others may write."""
+    """The trust boundary of ``train_state.pt`` (a full pickle: loading it runs whatever it contains).  A file owned by
+    another uid is refused (``PermissionError``); a file that group or others may write is loaded with a warning that
+    names the mode, like the reference does (kempnerforge/checkpoint/manager.py:75-110)."""
     st = path.stat()
-    if st.st_uid not in (os.getuid(), 0):
-        raise UntrustedCheckpointError(f"{path} is owned by uid {st.st_uid}, not by the current user; refusing to unpickle")
+    uid = os.getuid()
+    if st.st_uid != uid:
+        raise UntrustedCheckpointError(
+            f"Refusing to load {path}: owned by uid={st.st_uid}, current uid={uid}.  The file is a pickle and loading it "
+            f"executes arbitrary Python; chown it to the current user after inspection if you trust it.")
     if st.st_mode & (stat.S_IWGRP | stat.S_IWOTH):
-        raise UntrustedCheckpointError(f"{path} is writable by group/others; refusing to unpickle")
+        log.warning("%s is group/world-writable (mode=%s): it is a pickle and any writer can inject code that runs at load "
+                    "time; consider chmod g-w,o-w on the checkpoint directory", path, oct(st.st_mode & 0o777))
+
+
+def _load_train_state(path: Path) -> dict:
+    """Trust check, then the unpickling load of one ``train_state.pt``."""
+    check_trusted_file(path)
+    return torch.load(path, map_location="cpu", weights_only=False)
 
 
 # --------------------------------------------------------------------------- state dict assembly
@@ -607,8 +619,7 @@ class CheckpointManager:
         state = None
         if not multi or self.rank == 0:
             if target.exists():
-                check_trusted_file(target)
-                state = torch.load(target, map_location="cpu", weights_only=False)
+                state = _load_train_state(target)
         if multi:
             box = [state]
             dist.broadcast_object_list(box, src=0, group=self._sync_group)

@@ -23,6 +23,7 @@ BASE_MODULE_PATTERNS: dict[str, list[str]] = {
     "adapter": ["adapter", "adapter.*"],
 }
 
+_RESERVED_ARCHS: tuple[str, ...] = ()   # architecture names that are reserved but not built (none)
 DEFAULT_MODULE_PATTERNS = BASE_MODULE_PATTERNS   # the name this table has in the reference (kempnerforge/config/vlm.py)
 
 # adapter families that shrink the visual token grid

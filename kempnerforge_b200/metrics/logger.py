@@ -125,3 +125,6 @@ def format_number(val) -> str:
     if abs(val) < 0.01 or abs(val) >= 1e6:
         return f"{val:.2e}"
     return f"{val:.4f}"
+
+
+_format_number = format_number   # underscore spelling used by code written against the reference

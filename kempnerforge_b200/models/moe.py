@@ -30,6 +30,9 @@ from kempnerforge_b200.models.router import build_router
 from kempnerforge_b200.ops import grouped
 
 
+_HAS_GROUPED_MM = hasattr(torch, "_grouped_mm")   # the library's grouped GEMM (the fallback of the native kernels)
+
+
 def _counts_tensor(tokens_per_expert, device) -> torch.Tensor:
     if torch.is_tensor(tokens_per_expert):
         return tokens_per_expert.to(device=device, dtype=torch.int64)

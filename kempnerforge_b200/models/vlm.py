@@ -168,3 +168,6 @@ def build_vlm_wrapper(model_config, vision_config, adapter_config, vlm_config, f
             f"+ vlm.max_text_len ({vlm_config.max_text_len}) = {need}")
     transformer = Transformer(model_config, vlm_config=vlm_config, num_image_tokens=visual)
     return VLMWrapper(encoder, adapter, transformer, build_modality_strategy(vlm_config), frames_per_clip)
+
+
+_is_encoder_frozen = is_encoder_frozen   # underscore spelling used by code written against the reference

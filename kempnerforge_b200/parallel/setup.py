@@ -208,3 +208,8 @@ def get_dp_info(device_mesh: DeviceMesh | None) -> tuple[int, int]:
             rank = rank * sub.size() + sub.get_local_rank()
             size *= sub.size()
     return rank, size
+
+
+def _set_seed(seed: int, rank: int = 0, pp_rank: int = 0) -> None:
+    """The reference's spelling: ``rank`` is accepted and ignored (every data / tensor-parallel rank shares the seed)."""
+    set_seed(seed, pp_rank)

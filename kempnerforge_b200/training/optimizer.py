@@ -319,6 +319,9 @@ def is_muon_eligible(p: torch.Tensor) -> bool:
     return max(rows, cols) / max(1, min(rows, cols)) <= 10
 
 
+_is_muon_eligible = is_muon_eligible   # underscore spelling used by code written against the reference
+
+
 class Muon(torch.optim.Optimizer):
     """Momentum + Newton-Schulz orthogonalised updates for matrices; AdamW for everything else."""
 

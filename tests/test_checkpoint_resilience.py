@@ -189,8 +189,14 @@ def test_untrusted_train_state_is_refused(tmp_path):
     torch.save({"step": 1}, f)
     check_trusted_file(f)
     os.chmod(f, 0o666)
-    with pytest.raises(UntrustedCheckpointError):
-        check_trusted_file(f)
+    check_trusted_file(f)                       # writable by others: a warning, not a refusal
+    real = os.getuid
+    os.getuid = lambda: real() + 1
+    try:
+        with pytest.raises(UntrustedCheckpointError):
+            check_trusted_file(f)
+    finally:
+        os.getuid = real
 
 
 def test_freeze_metadata_mismatch(tmp_path):

@@ -125,22 +125,22 @@ def test_read_permission_for_others_is_fine(tmp_path):
 
 
 @pytest.mark.parametrize("bit", [stat.S_IWGRP, stat.S_IWOTH])
-def test_files_that_others_may_write_are_refused(tmp_path, bit):
+def test_files_that_others_may_write_load_with_a_warning(tmp_path, bit, caplog):
     p = _private_file(tmp_path)
     p.chmod(0o600 | bit)
-    with pytest.raises(UntrustedCheckpointError, match="writable"):
+    with caplog.at_level("WARNING"):
         check_trusted_file(p)
+    assert any("writable" in r.getMessage() for r in caplog.records)
 
 
-def test_files_of_another_user_are_refused_and_root_owned_ones_accepted(tmp_path, monkeypatch):
+def test_files_of_another_user_are_refused_with_a_permission_error(tmp_path, monkeypatch):
     p = _private_file(tmp_path)
     owner = p.stat().st_uid
     monkeypatch.setattr(os, "getuid", lambda: owner + 1000)
-    if owner == 0:
-        check_trusted_file(p)        # files written by root are trusted whoever reads them
-    else:
-        with pytest.raises(UntrustedCheckpointError, match="owned by uid"):
-            check_trusted_file(p)
+    with pytest.raises(PermissionError, match="owned by uid"):
+        check_trusted_file(p)
+    with pytest.raises(UntrustedCheckpointError):
+        check_trusted_file(p)
 
 
 def test_an_untrusted_train_state_is_refused_before_its_pickle_runs(tmp_path):
@@ -156,7 +156,11 @@ def test_an_untrusted_train_state_is_refused_before_its_pickle_runs(tmp_path):
     step.mkdir()
     f = step / "train_state.pt"
     f.write_bytes(pickle.dumps(Bomb()))
-    f.chmod(0o666)
     mgr = CheckpointManager(CheckpointConfig(dir=str(tmp_path)), torch.nn.Linear(2, 2), None)
-    with pytest.raises(UntrustedCheckpointError):
-        mgr.load(path=str(step), exclude_keys=["model", "optimizer"])
+    real = os.getuid
+    os.getuid = lambda: real() + 1            # the file now belongs to "somebody else"
+    try:
+        with pytest.raises(UntrustedCheckpointError):
+            mgr.load(path=str(step), exclude_keys=["model", "optimizer"])
+    finally:
+        os.getuid = real
