@@ -73,10 +73,11 @@ class JobConfig:
             self.adapter = AdapterConfig()
         enc = self.vision_encoder
         if enc.type in _HF_ENCODERS and (enc.feature_dim > 0 or enc.num_tokens > 0):
+            given = ", ".join(f"{k}={getattr(enc, k)}" for k in ("feature_dim", "num_tokens") if getattr(enc, k) > 0)
             _log.warning(
-                "vision_encoder.type=%r probes its own dims; explicit feature_dim/num_tokens "
-                "override the probe and may disagree with the loaded model",
-                enc.type,
+                "vision_encoder.type=%r probes its own dims; the explicit %s overrides the probe and may disagree with "
+                "the loaded model",
+                enc.type, given,
             )
         need = self._vlm_required_positions()
         if need is not None:

@@ -15,10 +15,12 @@ import math
 
 import torch
 from torch import nn
+from torch.utils.checkpoint import checkpoint
 
 from kempnerforge_b200.models.attention import Attention
 from kempnerforge_b200.models.mlp import build_mlp
 from kempnerforge_b200.models.norm import build_norm
+from kempnerforge_b200.models.recompute import checkpoint_contexts
 
 
 def _gumbel_like(t: torch.Tensor) -> torch.Tensor:
@@ -157,7 +159,25 @@ class MoMaBlock(nn.Module):
         self.mlp = MoMaFFN(config, self.modalities, dict(vlm_config.moma_experts_per_modality), caps,
                            vlm_config.moma_gumbel_noise)
 
-    def forward(self, x, rope_cos, rope_sin, modality_ids, *, doc_ids=None, key_padding_mask=None):
-        x = x + self.attention(self.attention_norm(x), rope_cos, rope_sin, doc_ids=doc_ids,
-                               key_padding_mask=key_padding_mask)
+    def _attn_branch(self, x, rope_cos, rope_sin, doc_ids, key_padding_mask):
+        return self.attention(self.attention_norm(x), rope_cos, rope_sin, doc_ids=doc_ids, key_padding_mask=key_padding_mask)
+
+    def _body(self, x, rope_cos, rope_sin, modality_ids, doc_ids, key_padding_mask, selective):
+        if selective:
+            attn = checkpoint(self._attn_branch, x, rope_cos, rope_sin, doc_ids, key_padding_mask, use_reentrant=False,
+                              context_fn=checkpoint_contexts)
+        else:
+            attn = self._attn_branch(x, rope_cos, rope_sin, doc_ids, key_padding_mask)
+        x = x + attn
         return x + self.mlp(self.mlp_norm(x), modality_ids=modality_ids, key_padding_mask=key_padding_mask)
+
+    def forward(self, x, rope_cos, rope_sin, modality_ids, *, doc_ids=None, key_padding_mask=None):
+        """``ac_mode`` (set by ``apply_ac``): "full" recomputes the whole block in the backward pass (the random state is
+        restored, so Gumbel routing noise repeats), "selective" only its attention branch.  (In the reference whole-block
+        checkpointing does not reach this block type.)"""
+        recompute = self.training and torch.is_grad_enabled()
+        if recompute and self.ac_mode == "full":
+            return checkpoint(self._body, x, rope_cos, rope_sin, modality_ids, doc_ids, key_padding_mask, False,
+                              use_reentrant=False, context_fn=checkpoint_contexts)
+        return self._body(x, rope_cos, rope_sin, modality_ids, doc_ids, key_padding_mask,
+                          recompute and self.ac_mode == "selective")

@@ -16,10 +16,12 @@ import logging
 
 import torch
 from torch import nn
+from torch.utils.checkpoint import checkpoint
 
 from kempnerforge_b200.models.mlp import build_mlp
 from kempnerforge_b200.models.moe import MoEMLP, build_moe
 from kempnerforge_b200.models.norm import RMSNorm, build_norm
+from kempnerforge_b200.models.recompute import checkpoint_contexts
 from kempnerforge_b200.ops import functional as F
 
 log = logging.getLogger(__name__)
@@ -109,12 +111,28 @@ class MoTBlock(nn.Module):
                 sub.down_proj.weight._kf_zero_init = True
                 nn.init.zeros_(sub.down_proj.weight)
 
-    def forward(self, streams: dict[str, torch.Tensor], rope: dict, key_padding_mask: torch.Tensor | None = None):
-        if set(streams) != set(self.modalities):
-            raise ValueError(f"MoTBlock.forward: streams keys {sorted(streams)} != modalities {sorted(self.modalities)}")
-        attn = self.attn({m: self.attn_norm[m](streams[m]) for m in self.modalities}, rope, True, key_padding_mask)
+    def _attn_branch(self, streams, rope, key_padding_mask):
+        return self.attn({m: self.attn_norm[m](streams[m]) for m in self.modalities}, rope, True, key_padding_mask)
+
+    def _body(self, streams, rope, key_padding_mask, selective):
+        if selective:
+            attn = checkpoint(self._attn_branch, streams, rope, key_padding_mask, use_reentrant=False,
+                              context_fn=checkpoint_contexts)
+        else:
+            attn = self._attn_branch(streams, rope, key_padding_mask)
         mid = {m: streams[m] + attn[m] for m in self.modalities}
         return {m: mid[m] + self.mlp[m](self.mlp_norm[m](mid[m])) for m in self.modalities}
+
+    def forward(self, streams: dict[str, torch.Tensor], rope: dict, key_padding_mask: torch.Tensor | None = None):
+        """``ac_mode`` (set by ``apply_ac``): "full" recomputes the whole block in the backward pass, "selective" only
+        the joint attention over the streams."""
+        if set(streams) != set(self.modalities):
+            raise ValueError(f"MoTBlock.forward: streams keys {sorted(streams)} != modalities {sorted(self.modalities)}")
+        recompute = self.training and torch.is_grad_enabled()
+        if recompute and self.ac_mode == "full":
+            return checkpoint(self._body, streams, rope, key_padding_mask, False, use_reentrant=False,
+                              context_fn=checkpoint_contexts)
+        return self._body(streams, rope, key_padding_mask, recompute and self.ac_mode == "selective")
 
 
 _PER_MODALITY = ("attention_norm", "attention.q_proj", "attention.k_proj", "attention.v_proj", "attention.o_proj",

@@ -211,3 +211,30 @@ def test_moe_backbone_inside_a_vlm_trains_and_exposes_moe_accessors():
     assert hasattr(t, "get_moe_aux_loss") or hasattr(t, "moe_aux_loss")
     routers = [p for n, p in model.named_parameters() if "router" in n or "gate" in n]
     assert routers and any(p.grad is not None and p.grad.abs().sum() > 0 for p in routers)
+
+
+@pytest.mark.parametrize("arch,mode", [("mot", "full"), ("mot", "selective"), ("moma", "full"), ("moma", "selective")])
+def test_activation_checkpointing_reaches_mot_and_moma_blocks_and_leaves_gradients_unchanged(arch, mode):
+    from kempnerforge_b200.parallel.parallel import apply_ac
+
+    kw = dict(moma_gumbel_noise=True) if arch == "moma" else {}      # routing noise must repeat in the recomputation
+    px, ids, labels = _batch()
+    grads = {}
+    for m in ("none", mode):
+        model, _ = _build(arch, **kw)
+        for p in model.parameters():                 # open the zero-initialised output projections
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                torch.nn.init.normal_(p, std=0.05, generator=torch.Generator().manual_seed(2))
+        if m != "none":
+            apply_ac(model, m)
+            blocks = [b for b in model.transformer.modules() if type(b).__name__ in ("MoTBlock", "MoMaBlock")]
+            assert blocks and all(b.ac_mode == m for b in blocks)
+        model.train()
+        torch.manual_seed(11)
+        loss = model.compute_loss(px, ids, labels)
+        loss.backward()
+        grads[m] = (float(loss), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None})
+    assert grads["none"][0] == pytest.approx(grads[mode][0], rel=1e-6)
+    assert grads["none"][1].keys() == grads[mode][1].keys()
+    for n, g in grads["none"][1].items():
+        assert torch.allclose(g, grads[mode][1][n], atol=1e-6), n
