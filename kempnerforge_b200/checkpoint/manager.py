@@ -61,6 +61,13 @@ def check_trusted_file(path: Path) -> None:
                     "time; consider chmod g-w,o-w on the checkpoint directory", path, oct(st.st_mode & 0o777))
 
 
+def _intersect_freeze_meta_by_module(saved: list[dict], expected: list[dict]) -> tuple[list[dict], list[dict]]:
+    """Both freeze records restricted to the modules that appear in each of them, input order kept.  A checkpoint of
+    one vision-language architecture can be resumed into another: modules only one side knows are not compared."""
+    shared = {e["module"] for e in saved} & {e["module"] for e in expected}
+    return [e for e in saved if e["module"] in shared], [e for e in expected if e["module"] in shared]
+
+
 def _load_train_state(path: Path) -> dict:
     """Trust check, then the unpickling load of one ``train_state.pt``."""
     check_trusted_file(path)
@@ -632,13 +639,18 @@ class CheckpointManager:
         meta_path = step_dir / "metadata.json"
         if not meta_path.exists():
             return
-        saved = json.loads(meta_path.read_text()).get("vlm_freeze")
+        try:
+            saved = json.loads(meta_path.read_text()).get("vlm_freeze")
+        except (OSError, ValueError, AttributeError) as e:
+            log.warning("could not read %s (%s): freeze configuration not compared", meta_path, e)
+            return
         if saved is None:
             return
-        saved_map = {e["module"]: e["frozen"] for e in saved}
-        want_map = {e["module"]: e["frozen"] for e in expected}
-        diff = {k: (saved_map[k], want_map[k]) for k in saved_map.keys() & want_map.keys() if saved_map[k] != want_map[k]}
-        if diff:
+        saved_shared, want_shared = _intersect_freeze_meta_by_module(saved, expected)
+        pairs = lambda meta: {(e["module"], bool(e["frozen"])) for e in meta}  # noqa: E731  order carries no meaning
+        if pairs(saved_shared) != pairs(want_shared):
+            one_sided = sorted({e["module"] for e in saved} ^ {e["module"] for e in expected})
+            diff = {"saved": saved_shared, "expected": want_shared, "ignored_one_sided_modules": one_sided}
             msg = f"freeze configuration differs from the checkpoint: {diff}"
             if self.config.ignore_freeze_mismatch:
                 log.warning(msg)
@@ -646,10 +658,11 @@ class CheckpointManager:
                 raise ValueError(msg + " (set checkpoint.ignore_freeze_mismatch=true to continue)")
 
     def apply_dataloader_state(self, dataloader) -> None:
-        """Hand a data-loader state that was loaded before the loader existed over to the loader."""
-        if self._stashed_dataloader_state is not None and dataloader is not None and hasattr(dataloader, "load_state_dict"):
-            dataloader.load_state_dict(self._stashed_dataloader_state)
-            self._stashed_dataloader_state = None
+        """Hand a data-loader state that was loaded before the loader existed over to the loader.  The state is dropped
+        afterwards in every case (a loader without ``load_state_dict``, or none, cannot take it later either)."""
+        state, self._stashed_dataloader_state = self._stashed_dataloader_state, None
+        if state is not None and dataloader is not None and hasattr(dataloader, "load_state_dict"):
+            dataloader.load_state_dict(state)
 
     # ------------------------------------------------------------------ retention
     def _cleanup(self) -> None:

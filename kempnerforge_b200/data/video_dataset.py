@@ -62,48 +62,61 @@ class WebVidVideoDataset(VideoDataset):
                  image_mean=DEFAULT_IMAGE_MEAN, image_std=DEFAULT_IMAGE_STD, tokenizer: Any = None) -> None:
         if split not in _CLIP_DIR:
             raise ValueError(f"split must be one of {tuple(_CLIP_DIR)} (got {split!r})")
-        self.split = split
-        self.clip_dir = os.path.join(data_root, "raw", "videos", _CLIP_DIR[split])
-        self.ids, self.captions = read_manifest(
+        self._split = split
+        self._video_dir = os.path.join(data_root, "raw", "videos", _CLIP_DIR[split])
+        self._ids, self._caps = read_manifest(
             os.path.join(data_root, "raw", dataset_name, "data", _MANIFEST_DIR[split], "partitions"), max_samples)
         if tokenizer is None:
             from transformers import AutoTokenizer
 
             tokenizer = AutoTokenizer.from_pretrained(tokenizer_path)
-        self.tokenizer = tokenizer
-        self.pad_id = pad_token_id(tokenizer)
-        self.max_text_len, self.prompt = max_text_len, prompt
-        self.max_frames, self.min_frames, self.fps, self.frame_size = max_frames, min_frames, fps, frame_size
-        self.sampling_policy = sampling_policy
-        self.image_mean, self.image_std = tuple(image_mean), tuple(image_std)
+        self._tokenizer = tokenizer
+        self._pad_id = pad_token_id(tokenizer)
+        self._max_text_len, self._prompt = max_text_len, prompt
+        self._max_frames, self._min_frames, self._fps, self._frame_size = max_frames, min_frames, fps, frame_size
+        self._sampling_policy = sampling_policy
+        self._image_mean, self._image_std = tuple(image_mean), tuple(image_std)
         log.info("WebVidVideoDataset %s/%s[%s]: %d clips, <=%d frames at %s fps, %dpx", data_root, dataset_name, split,
-                 len(self.ids), max_frames, fps, frame_size)
+                 len(self._ids), max_frames, fps, frame_size)
+
+    # read-only public views of the fields (subclasses that skip __init__ set the underscored names directly)
+    split = property(lambda self: self._split)
+    clip_dir = property(lambda self: self._video_dir)
+    ids = property(lambda self: self._ids)
+    captions = property(lambda self: self._caps)
+    tokenizer = property(lambda self: self._tokenizer)
+    pad_id = property(lambda self: self._pad_id)
+    max_text_len = property(lambda self: self._max_text_len)
+    max_frames = property(lambda self: self._max_frames)
+
+    def _video_path(self, videoid: str) -> str:
+        return self.clip_path(videoid)
 
     def clip_path(self, videoid: str) -> str:
         s = str(videoid)
-        if self.split == "train":
-            return os.path.join(self.clip_dir, s[:2], s[:4], s[:6], s + ".mp4")
-        return os.path.join(self.clip_dir, s + ".mp4")
+        if self._split == "train":
+            return os.path.join(self._video_dir, s[:2], s[:4], s[:6], s + ".mp4")
+        return os.path.join(self._video_dir, s + ".mp4")
 
     def __len__(self) -> int:
-        return len(self.ids)
+        return len(self._ids)
 
     def __getitem__(self, idx: int) -> dict[str, torch.Tensor]:
         import kempnerforge_b200.data.video_dataset as this_module
 
-        path = self.clip_path(self.ids[idx])
+        path = self.clip_path(self._ids[idx])
         try:
-            frames = this_module.decode_video_frames(path, fps=self.fps, min_frames=self.min_frames,
-                                                     max_frames=self.max_frames, sampling_policy=self.sampling_policy)
+            frames = this_module.decode_video_frames(path, fps=self._fps, min_frames=self._min_frames,
+                                                     max_frames=self._max_frames, sampling_policy=self._sampling_policy)
         except Exception as e:  # noqa: BLE001  any decoding problem turns into a masked sample
             log.debug("could not decode %s: %s", path, e)
             frames = []
-        pixels = torch.zeros(self.max_frames, 3, self.frame_size, self.frame_size)
-        mask = torch.zeros(self.max_frames, dtype=torch.bool)
-        for i, frame in enumerate(frames[: self.max_frames]):
-            pixels[i] = image_to_tensor(frame, self.frame_size, self.image_mean, self.image_std)
+        pixels = torch.zeros(self._max_frames, 3, self._frame_size, self._frame_size)
+        mask = torch.zeros(self._max_frames, dtype=torch.bool)
+        for i, frame in enumerate(frames[: self._max_frames]):
+            pixels[i] = image_to_tensor(frame, self._frame_size, self._image_mean, self._image_std)
             mask[i] = True
-        ids, labels = encode_text(self.tokenizer, self.captions[idx], self.max_text_len, self.prompt or None)
+        ids, labels = encode_text(self._tokenizer, self._caps[idx], self._max_text_len, self._prompt or None)
         if not mask.any():
             labels = torch.full_like(labels, IGNORE_INDEX)
         return {"pixel_values": pixels, "frame_mask": mask, "input_ids": ids, "labels": labels}

@@ -135,4 +135,5 @@ class VLMCollator:
                 "labels": labels, "image_positions": torch.zeros(len(samples), dtype=torch.long)}
 
 
-_pil_to_tensor = image_to_tensor   # underscore spelling used by code written against the reference
+_pil_to_tensor = image_to_tensor   # underscore spellings used by code written against the reference
+_tokenize_and_mask = encode_text

@@ -30,20 +30,27 @@ def _rank() -> int:
 class RankFilter(logging.Filter):
     """Let records through on rank 0 only (or on every rank when ``all_ranks``)."""
 
-    def __init__(self, all_ranks: bool = False) -> None:
+    def __init__(self, all_ranks: bool = False, rank: int = 0) -> None:
         super().__init__()
         self.all_ranks = all_ranks
+        self.allowed_rank = rank
 
     def filter(self, record: logging.LogRecord) -> bool:
-        return self.all_ranks or _rank() == 0 or record.levelno >= logging.ERROR
+        return self.all_ranks or _rank() == self.allowed_rank or record.levelno >= logging.ERROR
+
+
+def _supports_color() -> bool:
+    """Colour only on an interactive stream and never when NO_COLOR is set."""
+    if os.environ.get("NO_COLOR"):
+        return False
+    stream = sys.stdout
+    return bool(getattr(stream, "isatty", None)) and stream.isatty()
 
 
 class RankFormatter(logging.Formatter):
     def __init__(self, use_color: bool | None = None) -> None:
         super().__init__()
-        if use_color is None:
-            use_color = sys.stderr.isatty() and "NO_COLOR" not in os.environ
-        self.use_color = use_color
+        self.use_color = _supports_color() if use_color is None else (bool(use_color) and _supports_color())
 
     def format(self, record: logging.LogRecord) -> str:
         level = record.levelname
@@ -55,6 +62,8 @@ class RankFormatter(logging.Formatter):
             msg += "\n" + self.formatException(record.exc_info)
         return f"{stamp} [rank {_rank()}] {level} {record.name}: {msg}"
 
+
+_RankFilter, _RankFormatter = RankFilter, RankFormatter   # underscore spellings used by code written against the reference
 
 _configured = False
 
@@ -72,6 +81,12 @@ def setup_logging(level: int | str = logging.INFO, all_ranks: bool = False) -> N
         _configured = True
 
 
+def _configure_root(rank_zero_only: bool = True) -> None:
+    """Configure the package logger once (later calls do nothing)."""
+    if not _configured:
+        setup_logging(all_ranks=not rank_zero_only)
+
+
 def get_logger(name: str = "kempnerforge_b200", rank_zero_only: bool = True) -> logging.Logger:
     """``rank_zero_only=False`` on the call that first configures logging lets every rank print."""
     if not _configured:
@@ -85,6 +100,9 @@ def format_metrics(step: int, metrics: dict) -> str:
     """``[step 12] loss=2.3456 | lr=3.00e-04 | grad_norm=0.812 | tok/s=12,345 | mfu=41.2% | mem=10.1/180GB | step_time=0.53s``"""
     parts = []
     for key, val in metrics.items():
+        if isinstance(val, str):                 # already rendered by the caller
+            parts.append(f"{key}={val}")
+            continue
         if key == "loss" or key.endswith("/loss") or key.startswith("loss/"):
             parts.append(f"{key}={val:.4f}")
         elif key == "lr":

@@ -88,18 +88,38 @@ class DeviceMemoryMonitor:
             torch.cuda.memory._record_memory_history(max_entries=max_entries)
             self._recording = True
 
-    def capture_snapshot(self, tag: str | int = "snapshot") -> str | None:
-        """Writes ``<snapshot_dir>/<tag>.pickle`` (``snapshot_step_<n>_device_<d>.pickle`` for an integer step)."""
-        if not (self._recording and self.snapshot_dir):
+    def capture_snapshot(self, tag: str | int = "snapshot", *, step: int | None = None) -> str | None:
+        """Writes ``<snapshot_dir>/<tag>.pickle`` (``snapshot_step_<n>_device_<d>.pickle`` for an integer step) and
+        returns its path.  Without a GPU, a snapshot directory or a working allocator history it returns None: a
+        diagnostic must never end a run.  When no recording is active, one is started and stopped around the capture."""
+        import logging
+
+        if step is not None:
+            tag = int(step)
+        if not torch.cuda.is_available() or not self.snapshot_dir:
             return None
-        os.makedirs(self.snapshot_dir, exist_ok=True)
-        if isinstance(tag, int):
-            dev = self.device if self.device is not None else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
-            tag = f"snapshot_step_{tag}_device_{dev}"
-        path = os.path.join(self.snapshot_dir, f"{tag}.pickle")
-        with open(path, "wb") as fh:
-            pickle.dump(torch.cuda.memory._snapshot(), fh)
-        return path
+        own_recording = not self._recording
+        try:
+            if own_recording:
+                self.start_recording()
+                torch.cuda.synchronize(self.device)
+            os.makedirs(self.snapshot_dir, exist_ok=True)
+            if isinstance(tag, int):
+                dev = self.device if self.device is not None else torch.cuda.current_device()
+                tag = f"snapshot_step_{tag}_device_{dev}"
+            path = os.path.join(self.snapshot_dir, f"{tag}.pickle")
+            with open(path, "wb") as fh:
+                pickle.dump(torch.cuda.memory._snapshot(), fh)
+            return path
+        except Exception as e:  # noqa: BLE001
+            logging.getLogger(__name__).warning("memory snapshot failed: %s", e)
+            return None
+        finally:
+            if own_recording:
+                try:
+                    self.stop_recording()
+                except Exception:  # noqa: BLE001
+                    self._recording = False
 
     def stop_recording(self) -> None:
         if self._recording:

@@ -318,9 +318,13 @@ def test_rank_filter_and_formatter(monkeypatch):
     assert kf_logger.RankFilter().filter(err)  # errors are shown from every rank
     plain = kf_logger.RankFormatter(use_color=False).format(rec)
     assert "[rank 3]" in plain and "hello world" in plain and "\x1b[" not in plain
+    monkeypatch.setattr(kf_logger, "_supports_color", lambda: True)      # an interactive terminal
     assert "\x1b[" in kf_logger.RankFormatter(use_color=True).format(rec)
+    monkeypatch.undo()
     monkeypatch.setenv("NO_COLOR", "1")
-    assert kf_logger.RankFormatter().use_color is False
+    assert kf_logger.RankFormatter().use_color is False and kf_logger.RankFormatter(use_color=True).use_color is False
+    monkeypatch.setenv("RANK", "3")
+    assert kf_logger.RankFilter(rank=3).filter(rec) and not kf_logger.RankFilter(rank=1).filter(rec)
 
 
 def test_get_logger_namespaces_and_format_metrics():
@@ -373,3 +377,98 @@ def test_memory_monitor_interval_report_without_a_gpu(caplog):
     assert {"allocated_gb", "peak_gb", "reserved_gb", "total_gb", "mem_utilization"} <= set(stats)
     assert "[step 3] GPU mem:" in caplog.text and mon._snapshot_taken
     assert DeviceMemoryMonitor(None, "somewhere").snapshot_dir == "somewhere"
+
+
+# --------------------------------------------------------------------------- record fields, back-end keys, lazy back-ends
+def test_step_record_and_backend_keys_are_the_reference_ones():
+    """Dashboards and scripts written against kempnerforge/metrics/tracker.py read these names."""
+    tr = _tracker(model_config=_dense(), seq_len=128)
+    be = _Backend()
+    tr.backends.append(be)
+    tr.start_step()
+    m = tr.end_step(1, 3.0, 0.5, 1e-3, 1000)
+    for field in ("loss", "grad_norm", "lr", "tokens_per_sec", "mfu", "step_time_sec", "allocated_gb", "peak_gb",
+                  "reserved_gb", "total_gb", "mem_utilization"):
+        assert hasattr(m, field), field
+    assert m.step_time == m.step_time_sec and m.peak_memory_gb == m.peak_gb and m.total_memory_gb == m.total_gb
+    assert type(m)() .loss == 0.0                                      # every field has a default
+    _, payload = be.logged[0]
+    assert {"train/loss", "train/grad_norm", "train/lr", "train/tokens_per_sec", "train/mfu", "train/step_time_sec",
+            "gpu/allocated_gb", "gpu/peak_gb", "gpu/reserved_gb", "gpu/mem_utilization", "smoothed/loss",
+            "smoothed/tokens_per_sec", "smoothed/mfu", "smoothed/step_time"} <= payload.keys()
+    assert payload["smoothed/loss"] == 3.0 and tr._smoothed["loss"] == 3.0
+
+
+def test_backends_start_lazily_and_a_failed_start_only_disables_them(monkeypatch, tmp_path):
+    import sys
+    import types
+
+    from kempnerforge_b200.metrics.tracker import TensorBoardBackend, WandBBackend
+
+    cfg = MetricsConfig(enable_wandb=True, wandb_project="p", wandb_run_name="r")
+    calls = []
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: calls.append(kw) or types.SimpleNamespace(id="abc123", url="http://x")
+    fake.log = lambda metrics, step: calls.append(("log", step, dict(metrics)))
+    fake.finish = lambda: calls.append("finish")
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    be = WandBBackend(cfg)
+    assert calls == [] and be.active                                   # nothing happens at construction
+    be.log({"train/loss": 1.0}, step=3)
+    assert calls[0]["project"] == "p" and calls[0]["resume"] == "allow" and "id" not in calls[0]
+    assert calls[1] == ("log", 3, {"train/loss": 1.0}) and cfg.wandb_run_id == "abc123" and be.run_id == "abc123"
+    be.close()
+    assert calls[-1] == "finish"
+    resumed = WandBBackend(cfg)                                        # the stored id resumes the same run
+    resumed._ensure_init()
+    assert calls[-1]["id"] == "abc123"
+
+    def boom(**kw):
+        raise RuntimeError("no API key")
+
+    fake.init = boom
+    bad = WandBBackend(MetricsConfig(enable_wandb=True))
+    bad.log({"x": 1.0}, step=1)                                        # warns, does not raise
+    assert not bad.active
+    bad.close()
+
+    tb = TensorBoardBackend(MetricsConfig(tensorboard_dir=str(tmp_path / "tb")))
+    assert tb._writer is None and not (tmp_path / "tb").exists()
+    monkeypatch.setitem(sys.modules, "torch.utils.tensorboard", None)  # the import fails
+    tb.log({"a": 1.0}, step=1)
+    assert tb._writer is False and not tb.active
+    tb.close()
+
+
+def test_init_backends_runs_once(monkeypatch):
+    from kempnerforge_b200.metrics import tracker as tracker_mod
+
+    made = []
+
+    class FakeTB(_Backend):
+        def __init__(self, cfg):
+            super().__init__()
+            made.append(self)
+
+        def _ensure_init(self):
+            pass
+
+    monkeypatch.setattr(tracker_mod, "TensorBoardBackend", FakeTB)
+    tr = MetricsTracker(MetricsConfig(enable_tensorboard=True), rank=0, peak_tflops=1.0)
+    tr.init_backends()
+    tr.init_backends()
+    assert len(made) == 1 and tr.backends == made
+
+
+def test_memory_snapshot_never_raises(monkeypatch, tmp_path):
+    from kempnerforge_b200.metrics.memory import DeviceMemoryMonitor
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    assert DeviceMemoryMonitor(snapshot_dir=str(tmp_path)).capture_snapshot(step=10) is None
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+
+    def boom(*a, **k):
+        raise RuntimeError("allocator history unavailable")
+
+    monkeypatch.setattr(torch.cuda.memory, "_record_memory_history", boom)
+    assert DeviceMemoryMonitor(device=0, snapshot_dir=str(tmp_path)).capture_snapshot(step=1) is None
