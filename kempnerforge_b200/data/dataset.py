@@ -51,7 +51,7 @@ class MemoryMappedDataset(Dataset):
         self._files = sorted(Path(data_dir).glob(file_pattern))
         if not self._files:
             raise FileNotFoundError(f"No files matching {file_pattern!r} in {data_dir}")
-        self._maps: list[np.ndarray] = []
+        self._mmaps: list[np.ndarray] = []
         bounds = [0]
         total = 0
         try:
@@ -62,7 +62,7 @@ class MemoryMappedDataset(Dataset):
                     arr = np.memmap(str(f), dtype=dt, mode="r", shape=(size // np.dtype(dt).itemsize,))
                 else:
                     arr = np.load(str(f), mmap_mode="r")
-                self._maps.append(arr)
+                self._mmaps.append(arr)
                 total += len(arr)
                 bounds.append(bounds[-1] + len(arr) // seq_len)
         except Exception:
@@ -81,7 +81,7 @@ class MemoryMappedDataset(Dataset):
             raise IndexError(f"Index {idx} out of range [0, {len(self)})")
         f = int(np.searchsorted(self._bounds, idx, side="right") - 1)
         lo = (idx - int(self._bounds[f])) * self.seq_len
-        window = np.asarray(self._maps[f][lo : lo + self.seq_len])
+        window = np.asarray(self._mmaps[f][lo : lo + self.seq_len])
         if self._pack:
             return compute_packed_output(window, self._eos)
         tok = torch.from_numpy(window.astype(np.int64))
@@ -94,14 +94,14 @@ class MemoryMappedDataset(Dataset):
         self._epoch = state.get("epoch", 0)
 
     def close(self) -> None:
-        for arr in getattr(self, "_maps", []):
+        for arr in getattr(self, "_mmaps", []):
             mm = getattr(arr, "_mmap", None)
             if mm is not None:
                 try:
                     mm.close()
                 except (BufferError, ValueError):
                     pass
-        self._maps = []
+        self._mmaps = []
 
     def __del__(self) -> None:
         try:
@@ -206,7 +206,7 @@ class StreamingHuggingFaceDataset(IterableDataset):
         self._tokenizer = tokenizer
         self._raw_stream = raw_stream
         self._docs_consumed = 0
-        self._skip_docs = 0
+        self._skip_rank_docs = 0
         self._epoch = 0
 
     def _ensure_tokenizer(self):
@@ -240,7 +240,7 @@ class StreamingHuggingFaceDataset(IterableDataset):
             if i % stride != mine:
                 continue
             seen += 1
-            if seen <= self._skip_docs:
+            if seen <= self._skip_rank_docs:
                 continue
             self._docs_consumed = seen
             ids = _encode_plain(tok, row[self.text_field] or "")
@@ -256,7 +256,7 @@ class StreamingHuggingFaceDataset(IterableDataset):
                 else:
                     t = torch.from_numpy(window)
                     yield {"input_ids": t[:-1], "labels": t[1:]}
-        self._skip_docs = 0
+        self._skip_rank_docs = 0
         self._docs_consumed = 0
         self._epoch += 1
 
@@ -264,8 +264,8 @@ class StreamingHuggingFaceDataset(IterableDataset):
         return {"epoch": self._epoch, "rank_docs_consumed": self._docs_consumed}
 
     def load_state_dict(self, state: dict) -> None:
-        self._skip_docs = state.get("rank_docs_consumed", state.get("docs_consumed", 0))
-        self._docs_consumed = self._skip_docs
+        self._skip_rank_docs = state.get("rank_docs_consumed", state.get("docs_consumed", 0))
+        self._docs_consumed = self._skip_rank_docs
         self._epoch = state.get("epoch", 0)
 
 

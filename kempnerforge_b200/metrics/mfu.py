@@ -44,7 +44,12 @@ def get_gpu_peak_tflops(device: int | None = None, measured_peaks_path: str | No
             pass
     if not torch.cuda.is_available():
         return 1.0
-    name = torch.cuda.get_device_name(device if device is not None else torch.cuda.current_device())
+    if device is None:
+        try:
+            device = torch.cuda.current_device()
+        except Exception:  # noqa: BLE001  no usable context yet
+            device = 0
+    name = torch.cuda.get_device_name(device)
     for key in sorted(GPU_PEAK_TFLOPS, key=len, reverse=True):
         if key.lower() in name.lower():
             return GPU_PEAK_TFLOPS[key]

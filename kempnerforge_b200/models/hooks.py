@@ -38,7 +38,7 @@ class ActivationStore:
         self.keep_history = keep_history
         self._activations: dict[str, torch.Tensor] = {}
         self._history: dict[str, list[torch.Tensor]] = defaultdict(list)
-        self._handles = []
+        self._hooks = []
         self._on = False
 
     @property
@@ -63,13 +63,13 @@ class ActivationStore:
         if missing:
             raise _MissingModule(f"modules not found in model: {missing}; available e.g. {sorted(modules)[:8]}")
         for name in self._layers:
-            self._handles.append(modules[name].register_forward_hook(self._make_hook(name)))
+            self._hooks.append(modules[name].register_forward_hook(self._make_hook(name)))
             # make sure the parents of a hooked module run their ordinary (op-by-op) forward
             parts = name.split(".")
             for i in range(1, len(parts)):
                 parent = modules.get(".".join(parts[:i]))
                 if parent is not None and hasattr(parent, "ac_mode"):
-                    self._handles.append(parent.register_forward_hook(lambda *a: None))
+                    self._hooks.append(parent.register_forward_hook(lambda *a: None))
         self._on = True
 
     def _make_hook(self, name: str):
@@ -101,9 +101,9 @@ class ActivationStore:
 
     def disable(self) -> None:
         """Remove every hook."""
-        for h in self._handles:
+        for h in self._hooks:
             h.remove()
-        self._handles = []
+        self._hooks = []
         self._on = False
 
     remove = disable

@@ -41,15 +41,27 @@ class RandomVisionEncoder(VisionEncoder):
 
 
 class HFVisionEncoder(VisionEncoder):
-    def __init__(self, path: str, drop_cls: bool, num_tokens: int | None = None, feature_dim: int | None = None) -> None:
+    def __init__(self, path: str, drop_cls: bool | None = None, num_tokens: int | None = None,
+                 feature_dim: int | None = None, *, has_cls_token: bool | None = None, strip_cls: bool | None = None) -> None:
+        """``drop_cls`` (``strip_cls`` in the reference's spelling) removes position 0 of the tower's output;
+        ``has_cls_token`` says whether the tower emits a class token at all (default: it does exactly when it is
+        dropped).  ``num_tokens`` is what ``forward`` returns per image: the patch grid, plus one for a class token
+        that is kept."""
         super().__init__()
+        if strip_cls is not None:
+            drop_cls = strip_cls
+        drop_cls = bool(drop_cls)
+        if has_cls_token is None:
+            has_cls_token = drop_cls
+        if drop_cls and not has_cls_token:
+            raise ValueError("strip_cls=True is meaningless when has_cls_token=False: the tower emits no class token")
         from transformers import AutoModel
 
         full = AutoModel.from_pretrained(path)
         self.model = getattr(full, "vision_model", full)
         cfg = self.model.config
-        self.drop_cls = drop_cls
-        self.num_tokens = num_tokens or (cfg.image_size // cfg.patch_size) ** 2
+        self.drop_cls, self.has_cls_token = drop_cls, has_cls_token
+        self.num_tokens = num_tokens or (cfg.image_size // cfg.patch_size) ** 2 + int(has_cls_token and not drop_cls)
         self.feature_dim = feature_dim or cfg.hidden_size
 
     def forward(self, pixel_values: torch.Tensor) -> torch.Tensor:
@@ -79,7 +91,10 @@ def _build_siglip2(path: str, num_tokens: int | None = None, feature_dim: int | 
 @registry.register("vision_encoder", "clip")
 def _build_clip(path: str, num_tokens: int | None = None, feature_dim: int | None = None):
     _require_path(path, "clip")
-    return HFVisionEncoder(path, drop_cls=True, num_tokens=num_tokens, feature_dim=feature_dim)
+    return HFVisionEncoder(path, drop_cls=True, num_tokens=num_tokens, feature_dim=feature_dim, has_cls_token=True)
+
+
+_HFVisionEncoder = HFVisionEncoder   # underscore spelling used by code written against the reference
 
 
 def build_vision_encoder(config) -> VisionEncoder:

@@ -49,7 +49,7 @@ def visual_token_mask(frame_mask: torch.Tensor | None, num_visual_tokens: int) -
         return None
     frames = frame_mask.shape[1]
     if num_visual_tokens % frames:
-        raise ValueError(f"num_visual_tokens ({num_visual_tokens}) is not a multiple of num_frames ({frames})")
+        raise ValueError(f"num_visual_tokens ({num_visual_tokens}) must be a multiple of num_frames ({frames})")
     return frame_mask.bool().repeat_interleave(num_visual_tokens // frames, dim=1)
 
 
@@ -165,9 +165,11 @@ def build_vlm_wrapper(model_config, vision_config, adapter_config, vlm_config, f
     if model_config.max_seq_len < need:
         raise ValueError(
             f"max_seq_len ({model_config.max_seq_len}) insufficient for VLM at build time: visual tokens {visual} "
+            f"(frames_per_clip {frames_per_clip} x adapter output of encoder.num_tokens {encoder.num_tokens}) "
             f"+ vlm.max_text_len ({vlm_config.max_text_len}) = {need}")
     transformer = Transformer(model_config, vlm_config=vlm_config, num_image_tokens=visual)
     return VLMWrapper(encoder, adapter, transformer, build_modality_strategy(vlm_config), frames_per_clip)
 
 
-_is_encoder_frozen = is_encoder_frozen   # underscore spelling used by code written against the reference
+_is_encoder_frozen = is_encoder_frozen   # underscore spellings used by code written against the reference
+_visual_token_mask = visual_token_mask

@@ -102,9 +102,9 @@ def resolve_resume_path(checkpoint_dir: str | Path) -> Path | None:
 def log_job_info() -> None:
     info = get_slurm_info()
     if info is None:
-        log.info("not running under SLURM")
+        log.info("Not running under SLURM")
         return
     log.info("SLURM job %s (%s) nodes=%d tasks/node=%d partition=%s restart_count=%d", info.job_id,
              info.job_name, info.num_nodes, info.tasks_per_node, info.partition, info.restart_count)
     if info.restart_count > 0:
-        log.info("this is requeue #%d — will resume from the newest checkpoint", info.restart_count)
+        log.info("Job was requeued (restart #%d): resuming from the newest checkpoint", info.restart_count)

@@ -169,3 +169,34 @@ def test_convert_checkpoint_round_trip(tmp_path):
     CheckpointManager(cfg.checkpoint, t.model, t.optimizer).load(path=back_dir, exclude_keys=["optimizer"])
     for n, p in t.model.named_parameters():
         assert torch.allclose(p, want[n]), n
+
+
+def test_profile_analysis_counts_each_kernel_once_and_writes_a_summary(tmp_path):
+    """Self times are summed (inclusive times would count a kernel under every caller), every bucket is present
+    (attention kernels included), and the reference's flat keys are filled (kempnerforge/profiling/profiler.py:71-127)."""
+    from types import SimpleNamespace
+
+    from kempnerforge_b200.profiling.profiler import analyze_profiler, print_profiler_summary, save_profiler_summary
+
+    def evt(key, self_us, flops=0, count=1):
+        return SimpleNamespace(key=key, self_device_time_total=self_us, device_time_total=10 * self_us, flops=flops, count=count)
+
+    events = [evt("ProfilerStep#3", 99999), evt("kf::kf_gemm_bf16_tcgen05_2cta", 5000, int(1e12), 8),
+              evt("kf_attn_fwd_tcgen05", 1000), evt("ncclDevKernel_AllReduce", 1500), evt("kf::kf_gemm_rs_tcgen05", 500),
+              evt("Memcpy DtoD", 250), evt("elementwise_kernel", 750), evt("aten::linear", 0)]
+    prof = SimpleNamespace(key_averages=lambda: events)
+    st = analyze_profiler(prof)
+    assert st["total_cuda_time_us"] == 9000 and st["totals_us"]["attention"] == 1000
+    assert st["matmul_time_us"] == 6000 and st["comm_time_us"] == 2000 and st["memory_time_us"] == 250 and st["other_time_us"] == 750
+    assert abs(st["matmul_pct"] + st["comm_pct"] + st["memory_pct"] + st["other_pct"] - 100.0) < 1e-9
+    assert st["total_flops"] == int(1e12) and abs(st["achieved_tflops"] - 1e12 / 9e-3 / 1e12) < 1e-9
+    assert st["top_kernels"][0][0] == "kf::kf_gemm_bf16_tcgen05_2cta" and st["peak_tflops"] > 0
+    path = save_profiler_summary(st, prof, str(tmp_path / "t"))
+    text = open(path).read()
+    assert "attention" in text and "kf_gemm_bf16_tcgen05_2cta" in text and "TFLOP/s" in text
+    assert analyze_profiler(SimpleNamespace(key_averages=lambda: []))["total_cuda_time_us"] == 0
+    # a real (CPU-only) profile goes through without device events
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as real:
+        torch.ones(64, 64) @ torch.ones(64, 64)
+    out = print_profiler_summary(real, str(tmp_path / "real"))
+    assert out["total_cuda_time_us"] == 0 and (tmp_path / "real" / "summary.md").exists()

@@ -127,9 +127,9 @@ def _write_shards(d: Path, n=3, tokens=64):
 def test_mmap_dataset_close_is_idempotent(tmp_path):
     _write_shards(tmp_path)
     ds = MemoryMappedDataset(str(tmp_path), seq_len=16)
-    assert len(ds) == 12 and len(ds._maps) == 3
+    assert len(ds) == 12 and len(ds._mmaps) == 3
     ds.close()
-    assert ds._maps == []
+    assert ds._mmaps == []
     ds.close()
 
 
@@ -149,7 +149,7 @@ def test_mmap_dataset_releases_earlier_maps_when_a_later_file_is_bad(tmp_path, m
     real_close = MemoryMappedDataset.close
 
     def close(self):
-        closed.append(len(self._maps))
+        closed.append(len(self._mmaps))
         real_close(self)
 
     monkeypatch.setattr(MemoryMappedDataset, "close", close)
