@@ -195,3 +195,36 @@ def test_pipeline_stage_spellings():
     assert list(c.layers.keys()) == ["0", "1", "2", "3", "4"] and c.is_first and not c.is_last
     with pytest.raises(TypeError):
         PipelineStageModule(cfg)
+
+
+def test_reference_module_paths_resolve_to_the_same_module_objects():
+    """One import finder serves the reference's layout (kempnerforge/config/<section>.py, kempnerforge/model/*,
+    kempnerforge/distributed/*): an alias is the target module itself, never a second execution of its file."""
+    import importlib
+    import sys
+
+    from kempnerforge_b200 import _reference_paths as rp
+
+    for alias, real in [("config.model", "config.sections"), ("config.optimizer", "config.sections"),
+                        ("config.vision", "config.vlm"), ("config.schema", "config"), ("model", "models"),
+                        ("model.moe", "models.moe"), ("distributed", "parallel"),
+                        ("distributed.tensor_parallel", "parallel.tensor_parallel"), ("distributed.utils", "parallel")]:
+        assert rp.resolve(f"kempnerforge_b200.{alias}") == f"kempnerforge_b200.{real}"
+        assert importlib.import_module(f"kempnerforge_b200.{alias}") is importlib.import_module(f"kempnerforge_b200.{real}")
+    assert rp.resolve("kempnerforge_b200.models.moe") is None and rp.resolve("torch.distributed") is None
+    assert sum(isinstance(f, rp.ReferencePathFinder) for f in sys.meta_path) == 1
+    rp.install()                                   # installing twice adds nothing
+    assert sum(isinstance(f, rp.ReferencePathFinder) for f in sys.meta_path) == 1
+    from kempnerforge_b200.config.schema import JobConfig, ModelConfig, MoMaConfig, SchedulerType  # noqa: F401
+    from kempnerforge_b200.distributed import (apply_ac, apply_fsdp2, apply_tensor_parallel, build_pipeline_schedule,  # noqa: F401
+                                               build_stage_module, clip_grad_norm_, default_mp_policy, get_dp_mesh,
+                                               get_pp_rank, get_tp_mesh, is_rank_zero)
+    from kempnerforge_b200.models.moe import MoEMLP
+
+    assert sys.modules["kempnerforge_b200.model.moe"].MoEMLP is MoEMLP
+    try:
+        importlib.import_module("kempnerforge_b200.model.no_such_module")
+    except ModuleNotFoundError:
+        pass
+    else:
+        raise AssertionError("an alias of a missing module must not import")
