@@ -27,7 +27,7 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
         sorted_logits, order = torch.sort(logits, descending=True, dim=-1)
         probs = torch.softmax(sorted_logits, dim=-1)
         cum = probs.cumsum(dim=-1)
-        drop = cum - probs > top_p  # keep the first token that crosses the threshold
+        drop = cum - probs >= top_p  # a token is kept while the mass before it is still below the threshold
         sorted_logits = sorted_logits.masked_fill(drop, float("-inf"))
         logits = torch.full_like(logits, float("-inf")).scatter(-1, order, sorted_logits)
     probs = torch.softmax(logits, dim=-1)
