@@ -159,3 +159,132 @@ def test_other_optimizers_match_the_reference(monkeypatch, opt_overrides):
     worst = max((final[k].float() - ref_final[k].float()).abs().max().item() for k in keys)
     assert worst < 2e-3, worst
 
+
+
+# --------------------------------------------------------------------------- two gloo ranks against the reference's FSDP2
+def _rank_batches(rank, world, steps):
+    """The global batch of 4 sequences split over the ranks, drawn from one stream on every rank."""
+    out = []
+    for ids, labels in _batches(steps):
+        rows = slice(rank * 4 // world, (rank + 1) * 4 // world)
+        out.append((ids[rows].contiguous(), labels[rows].contiguous()))
+    return out
+
+
+def _two_rank_worker(rank, world, port, impl, steps, init_file, out_dir, plan="resident"):
+    import os
+    import traceback
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), CUDA_VISIBLE_DEVICES="")
+    torch.set_num_threads(1)
+    try:
+        batches = _rank_batches(rank, world, steps)
+        init = torch.load(init_file)
+        traj = []
+        if impl == "reference":          # the reference library: fully_shard over a CPU mesh, its own clip / optimizer / schedule
+            if str(REF) not in sys.path:
+                sys.path.insert(0, str(REF))
+            from kempnerforge.config.loader import load_config
+            from kempnerforge.distributed.parallel import apply_fsdp2
+            from kempnerforge.distributed.utils import clip_grad_norm_
+            from kempnerforge.model.transformer import Transformer
+            from kempnerforge.training.loss import build_loss_fn
+            from kempnerforge.training.optimizer import build_optimizer
+            from kempnerforge.training.scheduler import build_scheduler
+            from torch.distributed.device_mesh import init_device_mesh
+            from torch.distributed.fsdp import MixedPrecisionPolicy
+
+            dist.init_process_group("gloo")
+            cfg = load_config(PRESET, [])
+            model = Transformer(cfg.model)
+            model.load_state_dict(init)
+            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp_shard",))
+            apply_fsdp2(model, mesh, mp_policy=MixedPrecisionPolicy(param_dtype=torch.float32, reduce_dtype=torch.float32))
+            opt = build_optimizer(model, cfg.optimizer)
+            sched = build_scheduler(opt, cfg.scheduler, max_steps=cfg.train.max_steps)
+            loss_fn = build_loss_fn(cfg.train)
+            for ids, labels in batches:
+                loss = loss_fn(model(ids), labels)
+                loss.backward()
+                norm = clip_grad_norm_(model, cfg.train.grad_clip_norm)
+                opt.step()
+                sched.step()
+                opt.zero_grad()
+                mean = loss.detach().clone()
+                dist.all_reduce(mean)
+                traj.append((float(mean) / world, float(norm)))
+            final = {k: (v.full_tensor() if hasattr(v, "full_tensor") else v).detach().clone()
+                     for k, v in model.state_dict().items()}
+        else:
+            from kempnerforge_b200.config import load_config
+            from kempnerforge_b200.training.trainer import Trainer
+
+            cfg = load_config(PRESET, [f"--distributed.dp_shard={world}", f"--distributed.param_sharding={plan}",
+                                       "--metrics.log_interval=1000"])
+            t = Trainer(cfg)
+
+            def is_sharded(p):
+                return getattr(getattr(p, "_kf_flat", None), "sharded", False)
+
+            assert any(is_sharded(p) for p in t.model.parameters()) == (plan == "sharded")
+            for name, p in t.model.named_parameters():     # same starting point as the reference
+                if is_sharded(p):
+                    t.engine.load_full_parameter(p, init[name])
+                else:
+                    p.data.copy_(init[name])
+            for ids, labels in batches:
+                out = t.train_step([{"input_ids": ids, "labels": labels}])
+                mean = torch.tensor(out["loss"], dtype=torch.float64)
+                dist.all_reduce(mean)
+                traj.append((float(mean) / world, out["grad_norm"]))
+            final = {n: (t.engine.full_parameter(p) if is_sharded(p) else p.detach()).clone()
+                     for n, p in t.model.named_parameters()}
+        if rank == 0:
+            torch.save((traj, final), os.path.join(out_dir, f"{impl}.pt"))
+    except Exception:
+        with open(os.path.join(out_dir, f"err_{impl}_{rank}.txt"), "w") as fh:
+            fh.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("plan", ["resident", "sharded"])
+def test_two_gloo_ranks_follow_the_reference_fsdp2_run(tmp_path, plan):
+    """The CPU plumbing configuration at world size 2: this package's data-parallel engine, with resident and with
+    sharded (ZeRO-3) parameters, against the reference's FSDP2 (``fully_shard`` over a CPU mesh); same initial weights,
+    same per-rank batches."""
+    import os
+    import socket
+
+    import torch.multiprocessing as mp
+
+    if str(REF) not in sys.path:
+        sys.path.insert(0, str(REF))
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.model.transformer import Transformer as RefTransformer
+
+    torch.manual_seed(0)
+    init_file = str(tmp_path / "init.pt")
+    torch.save(RefTransformer(ref_load(PRESET, []).model).state_dict(), init_file)
+    steps, world = 8, 2
+    results = {}
+    for impl in ("reference", "ours"):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        mp.spawn(_two_rank_worker, args=(world, port, impl, steps, init_file, str(tmp_path), plan), nprocs=world, join=True)
+        errs = [open(tmp_path / f).read() for f in sorted(os.listdir(tmp_path)) if f.startswith("err_")]
+        assert not errs, "\n".join(errs)
+        results[impl] = torch.load(tmp_path / f"{impl}.pt")
+    (ref_traj, ref_final), (traj, final) = results["reference"], results["ours"]
+    for step, (a, b) in enumerate(zip(traj, ref_traj)):
+        assert a[0] == pytest.approx(b[0], rel=2e-4, abs=2e-4), ("loss", step, a, b)
+        assert a[1] == pytest.approx(b[1], rel=2e-3, abs=2e-4), ("grad norm", step, a, b)
+    assert traj[-1][0] < traj[0][0]
+    assert set(final) <= set(ref_final) and len(final) == len(ref_final)      # untied model: parameters = state dict
+    worst = max((final[k].float() - ref_final[k].float()).abs().max().item() for k in final)
+    assert worst < 5e-4, worst
