@@ -181,7 +181,8 @@ def _two_rank_worker(rank, world, port, impl, steps, init_file, out_dir, plan="r
                       LOCAL_RANK=str(rank), CUDA_VISIBLE_DEVICES="")
     torch.set_num_threads(1)
     try:
-        batches = _rank_batches(rank, world, steps)
+        # tensor-parallel ranks share the whole batch; data-parallel ranks split it
+        batches = _batches(steps) if plan == "tensor_parallel" else _rank_batches(rank, world, steps)
         init = torch.load(init_file)
         traj = []
         if impl == "reference":          # the reference library: fully_shard over a CPU mesh, its own clip / optimizer / schedule
@@ -201,8 +202,13 @@ def _two_rank_worker(rank, world, port, impl, steps, init_file, out_dir, plan="r
             cfg = load_config(PRESET, [])
             model = Transformer(cfg.model)
             model.load_state_dict(init)
-            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp_shard",))
-            apply_fsdp2(model, mesh, mp_policy=MixedPrecisionPolicy(param_dtype=torch.float32, reduce_dtype=torch.float32))
+            if plan == "tensor_parallel":
+                from kempnerforge.distributed.tensor_parallel import apply_tensor_parallel
+
+                apply_tensor_parallel(model, init_device_mesh("cpu", (world,), mesh_dim_names=("tp",)))
+            else:
+                mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp_shard",))
+                apply_fsdp2(model, mesh, mp_policy=MixedPrecisionPolicy(param_dtype=torch.float32, reduce_dtype=torch.float32))
             opt = build_optimizer(model, cfg.optimizer)
             sched = build_scheduler(opt, cfg.scheduler, max_steps=cfg.train.max_steps)
             loss_fn = build_loss_fn(cfg.train)
@@ -222,28 +228,43 @@ def _two_rank_worker(rank, world, port, impl, steps, init_file, out_dir, plan="r
             from kempnerforge_b200.config import load_config
             from kempnerforge_b200.training.trainer import Trainer
 
-            cfg = load_config(PRESET, [f"--distributed.dp_shard={world}", f"--distributed.param_sharding={plan}",
-                                       "--metrics.log_interval=1000"])
+            layout = ([f"--distributed.tp={world}", "--distributed.dp_shard=1"] if plan == "tensor_parallel" else
+                      [f"--distributed.dp_shard={world}", f"--distributed.param_sharding={plan}"])
+            cfg = load_config(PRESET, layout + ["--metrics.log_interval=1000"])
             t = Trainer(cfg)
 
             def is_sharded(p):
                 return getattr(getattr(p, "_kf_flat", None), "sharded", False)
 
             assert any(is_sharded(p) for p in t.model.parameters()) == (plan == "sharded")
+            def tp_dim(p):
+                spec = getattr(p, "_kf_shard", None)
+                return spec[1] if spec is not None and spec[0] == "tp" else None
+
+            assert any(tp_dim(p) is not None for p in t.model.parameters()) == (plan == "tensor_parallel")
             for name, p in t.model.named_parameters():     # same starting point as the reference
                 if is_sharded(p):
                     t.engine.load_full_parameter(p, init[name])
+                elif tp_dim(p) is not None:
+                    p.data.copy_(init[name].chunk(world, dim=tp_dim(p))[rank])
                 else:
                     p.data.copy_(init[name])
             for ids, labels in batches:
                 out = t.train_step([{"input_ids": ids, "labels": labels}])
                 mean = torch.tensor(out["loss"], dtype=torch.float64)
-                dist.all_reduce(mean)
+                dist.all_reduce(mean)                      # (tensor-parallel ranks report the same loss: mean = itself)
                 traj.append((float(mean) / world, out["grad_norm"]))
-            final = {n: (t.engine.full_parameter(p) if is_sharded(p) else p.detach()).clone()
-                     for n, p in t.model.named_parameters()}
-        if rank == 0:
-            torch.save((traj, final), os.path.join(out_dir, f"{impl}.pt"))
+            final = {}
+            for n, p in t.model.named_parameters():
+                if is_sharded(p):
+                    final[n] = t.engine.full_parameter(p).clone()
+                elif tp_dim(p) is not None:
+                    parts = [torch.empty_like(p.data) for _ in range(world)]
+                    dist.all_gather(parts, p.data.contiguous())
+                    final[n] = torch.cat(parts, dim=tp_dim(p))
+                else:
+                    final[n] = p.detach().clone()
+        torch.save((traj, final), os.path.join(out_dir, f"{impl}_{rank}.pt"))
     except Exception:
         with open(os.path.join(out_dir, f"err_{impl}_{rank}.txt"), "w") as fh:
             fh.write(traceback.format_exc())
@@ -252,11 +273,11 @@ def _two_rank_worker(rank, world, port, impl, steps, init_file, out_dir, plan="r
             dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("plan", ["resident", "sharded"])
+@pytest.mark.parametrize("plan", ["resident", "sharded", "tensor_parallel"])
 def test_two_gloo_ranks_follow_the_reference_fsdp2_run(tmp_path, plan):
     """The CPU plumbing configuration at world size 2: this package's data-parallel engine, with resident and with
-    sharded (ZeRO-3) parameters, against the reference's FSDP2 (``fully_shard`` over a CPU mesh); same initial weights,
-    same per-rank batches."""
+    sharded (ZeRO-3) parameters, against the reference's FSDP2 (``fully_shard`` over a CPU mesh), and this package's
+    tensor parallelism against the reference's DTensor plan; same initial weights, same batches."""
     import os
     import socket
 
@@ -279,7 +300,7 @@ def test_two_gloo_ranks_follow_the_reference_fsdp2_run(tmp_path, plan):
         mp.spawn(_two_rank_worker, args=(world, port, impl, steps, init_file, str(tmp_path), plan), nprocs=world, join=True)
         errs = [open(tmp_path / f).read() for f in sorted(os.listdir(tmp_path)) if f.startswith("err_")]
         assert not errs, "\n".join(errs)
-        results[impl] = torch.load(tmp_path / f"{impl}.pt")
+        results[impl] = torch.load(tmp_path / f"{impl}_0.pt")
     (ref_traj, ref_final), (traj, final) = results["reference"], results["ours"]
     for step, (a, b) in enumerate(zip(traj, ref_traj)):
         assert a[0] == pytest.approx(b[0], rel=2e-4, abs=2e-4), ("loss", step, a, b)
@@ -288,3 +309,111 @@ def test_two_gloo_ranks_follow_the_reference_fsdp2_run(tmp_path, plan):
     assert set(final) <= set(ref_final) and len(final) == len(ref_final)      # untied model: parameters = state dict
     worst = max((final[k].float() - ref_final[k].float()).abs().max().item() for k in final)
     assert worst < 5e-4, worst
+
+
+def _pipeline_worker(rank, world, port, impl, steps, init_file, out_dir):
+    """Two pipeline stages, two micro-batches per step, clipping switched off (the reference clips each stage by its own
+    partial norm, this package by the norm over all stages)."""
+    import os
+    import traceback
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), CUDA_VISIBLE_DEVICES="")
+    torch.set_num_threads(1)
+    overrides = ["--train.grad_accum_steps=2", "--train.batch_size=2", "--train.grad_clip_norm=1e9"]
+    try:
+        init = torch.load(init_file)
+        traj = []
+        if impl == "reference":
+            if str(REF) not in sys.path:
+                sys.path.insert(0, str(REF))
+            from kempnerforge.config.loader import load_config
+            from kempnerforge.distributed.pipeline_parallel import (build_pipeline_schedule, build_pipeline_stage,
+                                                                    build_stage_module)
+            from kempnerforge.distributed.utils import clip_grad_norm_
+            from kempnerforge.training.loss import build_loss_fn
+            from kempnerforge.training.optimizer import build_optimizer
+            from kempnerforge.training.scheduler import build_scheduler
+            from torch.distributed.device_mesh import init_device_mesh
+
+            dist.init_process_group("gloo")
+            cfg = load_config(PRESET, overrides)
+            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("pp",))
+            device = torch.device("cpu")
+            model = build_stage_module(cfg.model, rank, world).to(device=device, dtype=torch.float32)
+            model.load_state_dict({k: init[k] for k in model.state_dict()})
+            stage = build_pipeline_stage(model, mesh, device, batch_size=2, seq_len=128, param_dtype=torch.float32)
+            schedule = build_pipeline_schedule(stage=stage, n_microbatches=2, loss_fn=build_loss_fn(cfg.train), schedule="1f1b")
+            opt = build_optimizer(model, cfg.optimizer)
+            sched = build_scheduler(opt, cfg.scheduler, max_steps=cfg.train.max_steps)
+            for ids, labels in _batches(steps):
+                losses: list = []
+                if rank == 0:
+                    schedule.step(ids, target=labels, losses=losses)
+                else:
+                    schedule.step(target=labels, losses=losses)
+                norm = clip_grad_norm_(model, cfg.train.grad_clip_norm)
+                opt.step()
+                sched.step()
+                opt.zero_grad()
+                traj.append((sum(float(x) for x in losses) / max(1, len(losses)), float(norm)))
+            final = {k: v.detach().clone() for k, v in model.state_dict().items()}
+        else:
+            from kempnerforge_b200.config import load_config
+            from kempnerforge_b200.training.trainer import Trainer
+
+            cfg = load_config(PRESET, overrides + [f"--distributed.pp={world}", "--distributed.dp_shard=1",
+                                                   "--metrics.log_interval=1000"])
+            t = Trainer(cfg)
+            assert not t.model.load_state_dict(init, strict=False).missing_keys
+            for ids, labels in _batches(steps):
+                out = t.train_step([{"input_ids": ids[:2], "labels": labels[:2]}, {"input_ids": ids[2:], "labels": labels[2:]}])
+                traj.append((out["loss"], out["grad_norm"]))
+            final = {k: v.detach().clone() for k, v in t.model.state_dict().items()}
+        torch.save((traj, final), os.path.join(out_dir, f"{impl}_{rank}.pt"))
+    except Exception:
+        with open(os.path.join(out_dir, f"err_{impl}_{rank}.txt"), "w") as fh:
+            fh.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_two_pipeline_stages_follow_the_reference_schedule(tmp_path):
+    """This package's 1F1B runner against the reference's ``torch.distributed.pipelining`` schedule on two gloo ranks."""
+    import os
+    import socket
+
+    import torch.multiprocessing as mp
+
+    if str(REF) not in sys.path:
+        sys.path.insert(0, str(REF))
+    from kempnerforge.config.loader import load_config as ref_load
+    from kempnerforge.model.transformer import Transformer as RefTransformer
+
+    torch.manual_seed(0)
+    init_file = str(tmp_path / "init.pt")
+    torch.save(RefTransformer(ref_load(PRESET, []).model).state_dict(), init_file)
+    steps, world = 6, 2
+    results = {}
+    for impl in ("reference", "ours"):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        mp.spawn(_pipeline_worker, args=(world, port, impl, steps, init_file, str(tmp_path)), nprocs=world, join=True)
+        errs = [open(tmp_path / f).read() for f in sorted(os.listdir(tmp_path)) if f.startswith("err_")]
+        assert not errs, "\n".join(errs)
+        results[impl] = [torch.load(tmp_path / f"{impl}_{r}.pt") for r in range(world)]
+    ref, ours = results["reference"], results["ours"]
+    for step in range(steps):
+        want_loss = ref[world - 1][0][step][0]                                   # the last stage holds the loss
+        want_norm = sum(ref[r][0][step][1] ** 2 for r in range(world)) ** 0.5    # its stages report partial norms
+        for r in range(world):                                                   # here every stage reports both
+            assert ours[r][0][step][0] == pytest.approx(want_loss, rel=2e-4, abs=2e-4), ("loss", step, r)
+            assert ours[r][0][step][1] == pytest.approx(want_norm, rel=2e-3, abs=2e-4), ("grad norm", step, r)
+    for r in range(world):
+        assert set(ours[r][1]) == set(ref[r][1]), r                              # same layer-to-stage assignment and names
+        worst = max((ours[r][1][k].float() - ref[r][1][k].float()).abs().max().item() for k in ref[r][1])
+        assert worst < 5e-4, (r, worst)
