@@ -468,6 +468,9 @@ class CheckpointManager:
         step_dir = self.step_dir(step)
         dcp_dir = self._dcp_dir(step_dir)
         dcp_dir.mkdir(parents=True, exist_ok=True)
+        # an optimizer that has not stepped yet (a save at step 0) gets its zero state first, so that every checkpoint
+        # carries the full set of keys a later load asks for
+        materialize_optimizer_state(self.model, self.optimizer)
         state = {"model": model_state_dict(self.model), "optimizer": optimizer_state_dict(self.model, self.optimizer)}
         self._saver.save(state, str(dcp_dir), self.process_group)  # waits for the previous flush first
         self._drain_pending_finalize()
@@ -598,11 +601,17 @@ class CheckpointManager:
     def _drop_unsaved_group_fields(opt_state: dict, dcp_dir: Path) -> None:
         """Hyper-parameter fields of the live param groups that the checkpoint does not contain (for instance
         ``initial_lr``, which only exists once a scheduler has been attached) keep their current values instead of
-        failing the load."""
+        failing the load.  The same goes for per-parameter state of a checkpoint written before the optimizer's first
+        step: the freshly created zero state stays."""
         try:
             saved = set(dcp.FileSystemReader(str(dcp_dir)).read_metadata().state_dict_metadata)
         except Exception:  # unreadable metadata is reported by dcp.load itself
             return
+        if not any(k.startswith("optimizer.state.") for k in saved):
+            if opt_state.get("state"):
+                log.warning("checkpoint %s has no optimizer state (saved before the first step): moments start at zero",
+                            dcp_dir)
+            opt_state["state"] = {}
         for i, group in enumerate(opt_state.get("param_groups", [])):
             for key in [k for k in group if k != "params"]:
                 if f"optimizer.param_groups.{i}.{key}" not in saved:
@@ -649,9 +658,11 @@ class CheckpointManager:
         saved_shared, want_shared = _intersect_freeze_meta_by_module(saved, expected)
         pairs = lambda meta: {(e["module"], bool(e["frozen"])) for e in meta}  # noqa: E731  order carries no meaning
         if pairs(saved_shared) != pairs(want_shared):
-            one_sided = sorted({e["module"] for e in saved} ^ {e["module"] for e in expected})
-            diff = {"saved": saved_shared, "expected": want_shared, "ignored_one_sided_modules": one_sided}
-            msg = f"freeze configuration differs from the checkpoint: {diff}"
+            only_saved = sorted({e["module"] for e in saved} - {e["module"] for e in expected})
+            only_now = sorted({e["module"] for e in expected} - {e["module"] for e in saved})
+            note = f" (cross-arch keys ignored, known to one side only: saved-only={only_saved}, current-only={only_now})" \
+                if only_saved or only_now else ""
+            msg = f"VLM freeze mismatch at {step_dir}: saved={saved_shared}, current={want_shared}{note}"
             if self.config.ignore_freeze_mismatch:
                 log.warning(msg)
             else:

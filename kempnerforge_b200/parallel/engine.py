@@ -49,6 +49,8 @@ class DataParallelEngine:
         self.grad_scale = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._reduced = False
+        self._manual_step = False    # this step's gradient reduction was started by an optimizer / clipping hook
+        self._scale_pending = False  # a clip factor was computed and not yet multiplied into whole gradients
         self._reduce_work: dict[int, object] = {}  # group index -> in-flight gradient reduction
         self._gather_work: dict[int, object] = {}  # group index -> in-flight parameter publication
         self._group_of_module: dict[int, int] = {}
@@ -311,8 +313,48 @@ class DataParallelEngine:
             self.grad_scale.fill_(1.0)
         return self.grad_norm
 
+    # ------------------------------------------------------------------ hand-written training loops
+    def bind_optimizer(self, optimizer) -> None:
+        """Make ``loss.backward(); clip_grad_norm_(model, c); optimizer.step(); optimizer.zero_grad()`` a complete
+        training step, as it is with FSDP2 in the reference: the step folds / reduces the gradients first when
+        :meth:`finish_backward` has not run since the last ``zero_grad``, applies a pending clip factor, publishes the
+        update afterwards, and ``optimizer.zero_grad`` also resets the flat gradient buffers.  A loop that drives the
+        engine itself (``finish_backward`` ... ``after_optimizer_step``, as the trainer does) is not affected: the
+        hooks find nothing left to do."""
+        if getattr(optimizer, "_kf_engine_bound", None) is self:
+            return
+        fused = bool(getattr(optimizer, "_flat_groups", None))
+        if fused:
+            optimizer.grad_scale = self.grad_scale
+
+        def before(_opt, _args, _kwargs):
+            if not self._reduced:
+                self.finish_backward()
+                self._manual_step = True
+            if self._manual_step and self._scale_pending and not fused:
+                self.apply_grad_scale()
+
+        def after(_opt, _args, _kwargs):
+            if self._manual_step:
+                self._manual_step = False
+                self.after_optimizer_step()
+                self._scale_pending = False    # a clip factor belongs to the step it was computed for
+                self.grad_scale.fill_(1.0)
+
+        optimizer.register_step_pre_hook(before)
+        optimizer.register_step_post_hook(after)
+        plain_zero_grad = optimizer.zero_grad
+
+        def zero_grad(set_to_none: bool = True):
+            plain_zero_grad(set_to_none=set_to_none)
+            self.zero_grad()
+
+        optimizer.zero_grad = zero_grad
+        optimizer._kf_engine_bound = self
+
     def apply_grad_scale(self) -> None:
         """Multiply the (shard) gradients by ``grad_scale``; only needed for optimizers that do not fuse it."""
+        self._scale_pending = False
         for g in self.groups:
             lo, hi = (0, g.numel) if self.full_grads else g.shard_range
             g.grad[lo:hi].mul_(self.grad_scale.to(g.grad.dtype))
@@ -463,7 +505,11 @@ def clip_grad_norm_(model: nn.Module, max_norm: float, foreach: bool | None = No
     """Clip the global gradient norm in place; returns the pre-clip norm.  Engine-aware."""
     engine = getattr(model, "_kf_engine", None)
     if engine is not None:
+        if not engine._reduced:            # a hand-written loop: nobody has reduced this step's gradients yet
+            engine.finish_backward()
+            engine._manual_step = True
         norm = engine.clip_grad_norm(max_norm)
+        engine._scale_pending = True
         return norm.reshape(())
     grads = [p.grad for p in model.parameters() if p.grad is not None]
     if not grads:

@@ -294,6 +294,7 @@ class ShardedDataParallelEngine(DataParallelEngine):
         return self.grad_norm
 
     def apply_grad_scale(self) -> None:
+        self._scale_pending = False
         for g in self.groups:
             if g.sharded:
                 g.grad_shard.mul_(self.grad_scale.to(g.grad_shard.dtype))

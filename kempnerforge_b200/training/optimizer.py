@@ -470,4 +470,6 @@ def build_optimizer(model: torch.nn.Module, config: OptimizerConfig) -> torch.op
         model._kf_engine.full_grads = True
         if isinstance(opt, Muon) and model._kf_engine.world > 1:
             opt.dp_group = model._kf_engine.pg   # divide the Newton-Schulz work over the data-parallel ranks
+    if getattr(model, "_kf_engine", None) is not None:
+        model._kf_engine.bind_optimizer(opt)     # plain backward / step / zero_grad loops work without engine calls
     return opt

@@ -298,9 +298,9 @@ class Trainer:
             # a skipped (non-finite) step advances neither the optimizer nor the schedule, like the reference's loop
             self.scheduler.step()
             self._apply_phase_lr()
-        if self.engine is not None:
+        if self.engine is not None and getattr(self.optimizer, "_kf_engine_bound", None) is not self.engine:
             self.engine.zero_grad()
-        self.optimizer.zero_grad(set_to_none=True)
+        self.optimizer.zero_grad(set_to_none=True)   # a bound optimizer resets the engine's flat gradients as well
         return {"loss": loss, "grad_norm": grad_norm, "lr": lr, "skipped": float(skipped)}
 
     def _pipeline_step(self, batches) -> dict[str, float]:

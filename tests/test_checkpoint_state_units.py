@@ -187,3 +187,35 @@ def test_wait_without_a_pending_save_is_a_noop(tmp_path):
     m.flush_pending_save()
     assert CheckpointConfig().async_mode in ("disabled", "async", "async_with_pinned_mem") or True
     assert ckpt.model_state_dict(torch.nn.Linear(2, 2)).keys() == {"weight", "bias"}
+
+
+@pytest.mark.parametrize("opt_name", ["adamw", "lion", "muon"])
+def test_a_checkpoint_written_before_the_first_optimizer_step_loads(tmp_path, opt_name):
+    """A save at step 0 (dynamic checkpoint windows start there) happens before any optimizer state exists; the
+    checkpoint must still carry every key a later load asks for, and older checkpoints without optimizer state load
+    with zero moments."""
+    from kempnerforge_b200.config import CheckpointConfig, ModelConfig, OptimizerConfig
+    from kempnerforge_b200.models import Transformer
+    from kempnerforge_b200.training.optimizer import build_optimizer
+
+    def make():
+        torch.manual_seed(0)
+        model = Transformer(ModelConfig(dim=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16))
+        opt = build_optimizer(model, OptimizerConfig(name=opt_name, lr=1e-3, fused=False))
+        return model, opt, ckpt.CheckpointManager(CheckpointConfig(dir=str(tmp_path / "ck")), model, opt)
+
+    model, opt, mgr = make()
+    mgr.save(step=0)
+    mgr.wait()
+    model2, opt2, mgr2 = make()
+    with torch.no_grad():
+        for p in model2.parameters():
+            p.add_(1.0)
+    step, _, _ = mgr2.load()
+    assert step == 0
+    for (n, a), (_, b) in zip(model.named_parameters(), model2.named_parameters()):
+        assert torch.equal(a, b), n
+    # training continues from the loaded state
+    ids = torch.randint(0, 64, (2, 8))
+    model2(ids).float().square().mean().backward()
+    opt2.step()

@@ -802,6 +802,42 @@ def test_native_attention_policy_in_training(native_lib, monkeypatch):
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
 
 
+@pytest.mark.parametrize("opt_name", ["adamw", "lion"])
+def test_a_hand_written_loop_on_the_gpu_trains_like_the_trainer(native_lib, opt_name):
+    """``loss.backward(); clip_grad_norm_(); optimizer.step(); optimizer.zero_grad()`` over ``build_parallel_model`` /
+    ``build_optimizer`` with no engine call: the optimizer hooks reduce, scale and publish, so the losses are the
+    trainer's (same kernels in the same order; the fused head + loss of the trainer against logits + loss here)."""
+    from kempnerforge_b200.distributed import build_parallel_model, clip_grad_norm_
+    from kempnerforge_b200.training.loss import build_loss_fn
+    from kempnerforge_b200.training.optimizer import build_optimizer
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _tiny_job(optimizer=dict(name=opt_name, lr=2e-3 if opt_name == "adamw" else 2e-4), train=dict(grad_clip_norm=1.0))
+    t = Trainer(cfg, init_dist=False)
+    init = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    want = _overfit(t, steps=8)
+    model = build_parallel_model(cfg.model, torch.device("cuda"), None, param_dtype=cfg.train.param_dtype)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(init[n])
+    opt, loss_fn = build_optimizer(model, cfg.optimizer), build_loss_fn(cfg.train)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, 512, (4, 129), generator=g).cuda()
+    ids, labels = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    got = []
+    for _ in range(8):
+        loss = loss_fn(model(ids), labels)
+        loss.backward()
+        clip_grad_norm_(model, 1.0)
+        opt.step()
+        opt.zero_grad()
+        got.append(float(loss.detach()))
+    assert native_lib.read_status() == 0
+    assert got[-1] < got[0] - 0.5, got
+    for step, (a, b) in enumerate(zip(got, want)):
+        assert abs(a - b) <= 0.05 * max(1.0, abs(b)), (step, got, want)
+
+
 @pytest.mark.parametrize("name", ["lion", "schedule_free_adamw"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_lion_and_schedule_free_kernels_match_python_rules(native_lib, name, dtype):
