@@ -28,7 +28,11 @@ class RandomVisionEncoder(VisionEncoder):
         self.num_tokens, self.feature_dim = num_tokens, feature_dim
         # a fixed random projection of coarse image statistics: deterministic per image, different across images
         gen = torch.Generator().manual_seed(1234 + seed)
-        self.register_buffer("basis", torch.randn(3 * 16, num_tokens * feature_dim, generator=gen) / 7.0, persistent=False)
+        # drawn on the CPU whatever device context the module is built under (the generator lives there), so the basis
+        # is the same on every device; ``.to(device)`` moves it with the module
+        basis = torch.randn(3 * 16, num_tokens * feature_dim, generator=gen, device="cpu") / 7.0
+        self.register_buffer("basis", basis.to(torch.empty(0).device if torch.empty(0).device.type != "meta" else "cpu"),
+                             persistent=False)
         # no parameters and nothing in the state dict (like the reference's stub): a non-persistent buffer carries
         # the module's device and dtype
         self.register_buffer("_anchor", torch.zeros(1), persistent=False)

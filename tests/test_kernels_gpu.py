@@ -1234,3 +1234,120 @@ def test_newton_schulz_on_symmetric_products_matches_fp32_iteration(native_lib):
         err = (got.float() - want).norm() / want.norm()
         assert err < 5e-2, err
     assert native_lib.read_status() == 0
+
+
+# --------------------------------------------------------------------------- vision-language models on one GPU
+def _vlm_job(arch, **vlm_extra):
+    from kempnerforge_b200.config import config_from_dict
+
+    return config_from_dict({
+        "model": dict(dim=256, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=512, ffn_hidden_dim=512, max_seq_len=128),
+        "train": dict(batch_size=4, seq_len=64, max_steps=20, mixed_precision="bf16", seed=0),
+        "optimizer": dict(lr=2e-3), "scheduler": dict(name="constant", warmup_steps=0),
+        "vision_encoder": dict(type="random", feature_dim=64, num_tokens=16),
+        "adapter": dict(type="mlp_2layer"),
+        "vlm": dict(arch=arch, max_text_len=32, **vlm_extra),
+        "metrics": dict(log_interval=1000),
+    })
+
+
+@pytest.mark.parametrize("arch", ["joint_decoder", "cross_attention", "mot", "moma"])
+def test_vlm_architectures_build_and_train_on_the_gpu(native_lib, arch):
+    """Every vision-language architecture is built on the device by the trainer (random encoder: no downloads),
+    trains in bf16 and leaves the frozen encoder alone."""
+    from kempnerforge_b200.training.trainer import Trainer
+
+    extra = {"cross_attention_every_n_layers": 2} if arch == "cross_attention" else {}
+    if arch == "moma":
+        extra = {"moma_experts_per_modality": {"image": 2, "text": 2}, "moma_gumbel_noise": False}
+    t = Trainer(_vlm_job(arch, freeze=[{"module": "vision_encoder", "frozen": True}], **extra), init_dist=False)
+    assert all(p.is_cuda for p in t.model.parameters()) and t.model.vision_encoder.basis.is_cuda
+    g = torch.Generator().manual_seed(0)
+    batch = {"pixel_values": torch.rand(4, 3, 32, 32, generator=g), "input_ids": torch.randint(1, 512, (4, 32), generator=g)}
+    batch["labels"] = batch["input_ids"].clone()
+    losses = [t.train_step([batch])["loss"] for _ in range(10)]
+    assert native_lib.read_status() == 0
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.5, (arch, losses)
+
+
+def test_vlm_all_padding_batch_is_harmless_on_the_gpu(native_lib):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_vlm_job("joint_decoder"), init_dist=False)
+    g = torch.Generator().manual_seed(1)
+    px, ids = torch.rand(4, 3, 32, 32, generator=g), torch.randint(1, 512, (4, 32), generator=g)
+    out = t.train_step([{"pixel_values": px, "input_ids": ids, "labels": torch.full((4, 32), -100)}])
+    assert out["loss"] == 0.0 or out["loss"] == out["loss"]
+    out = t.train_step([{"pixel_values": px, "input_ids": ids, "labels": ids.clone()}])
+    assert out["loss"] == out["loss"] and out["loss"] > 0 and native_lib.read_status() == 0
+
+
+# --------------------------------------------------------------------------- the rest of the user-facing paths on one GPU
+def test_generation_evaluation_and_activation_capture_on_the_gpu(native_lib):
+    """Decoding against per-layer KV caches, evaluation and activation capture run on the device through the same
+    model object the trainer updates (bf16, native kernels where the shapes allow)."""
+    from kempnerforge_b200.models.generate import generate
+    from kempnerforge_b200.models.hooks import ActivationStore
+    from kempnerforge_b200.training.eval import run_eval
+    from kempnerforge_b200.training.loss import cross_entropy_loss
+    from kempnerforge_b200.training.trainer import Trainer
+
+    t = Trainer(_tiny_job(), init_dist=False)
+    _overfit(t, steps=3)
+    model = t.model
+    prompt = torch.randint(0, 512, (2, 8), generator=torch.Generator().manual_seed(2)).cuda()
+    out = generate(model, prompt, max_new_tokens=6, temperature=0.0)
+    assert out.shape == (2, 14) and out.is_cuda and torch.equal(out[:, :8], prompt)
+    assert int(out.min()) >= 0 and int(out.max()) < 512
+    assert torch.equal(out, generate(model, prompt, max_new_tokens=6, temperature=0.0))       # greedy decoding repeats
+    sampled = generate(model, prompt, max_new_tokens=4, temperature=0.8, top_k=20, top_p=0.9)
+    assert sampled.shape == (2, 12)
+    model.eval()
+    with torch.no_grad():       # the first generated token is the argmax of a plain forward pass over the prompt
+        last = model(prompt)[:, -1].float()
+    chosen = last.gather(1, out[:, 8:9]).squeeze(1)     # (up to bf16 noise between the cached and the plain kernels)
+    assert bool((last.max(-1).values - chosen <= 0.25).all()), (last.max(-1).values, chosen)
+    g = torch.Generator().manual_seed(3)
+    batches = []
+    for _ in range(2):
+        tok = torch.randint(0, 512, (4, 65), generator=g)
+        batches.append({"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()})
+    res = run_eval(model, batches, cross_entropy_loss, torch.device("cuda"), 3)
+    assert res["eval/loss"] == res["eval/loss"] and res["eval/loss"] > 0
+    assert abs(res["eval/perplexity"] - math.exp(res["eval/loss"])) <= 1e-3 * res["eval/perplexity"]
+    store = ActivationStore(model, layers=["layers.0.attention", "layers.1.mlp", "norm"])
+    store.enable()
+    with torch.no_grad():
+        model(prompt)
+    store.disable()
+    for name in ("layers.0.attention", "layers.1.mlp", "norm"):
+        act = store.get(name)
+        assert act is not None and tuple(act.shape) == (2, 8, 256), name
+        assert bool(torch.isfinite(act.float()).all()), name
+    assert native_lib.read_status() == 0
+
+
+def test_checkpoint_round_trip_on_the_gpu_resumes_the_same_trajectory(native_lib, tmp_path):
+    from kempnerforge_b200.training.trainer import Trainer
+
+    def job():
+        return _tiny_job(checkpoint=dict(dir=str(tmp_path / "ck"), interval=1000))
+
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, 512, (4, 129), generator=g)
+    batch = {"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+    a = Trainer(job(), init_dist=False)
+    a.setup_checkpointing()
+    for _ in range(3):
+        a.train_step([batch])
+        a.step += 1
+    a.save_checkpoint()
+    a.ckpt.wait()
+    want = [a.train_step([batch])["loss"] for _ in range(2)]
+    b = Trainer(job(), init_dist=False)
+    b.setup_checkpointing()
+    assert b.step == 3
+    got = [b.train_step([batch])["loss"] for _ in range(2)]
+    assert native_lib.read_status() == 0
+    for x, y in zip(got, want):
+        assert abs(x - y) <= 2e-3 * max(1.0, abs(y)), (got, want)
