@@ -50,6 +50,7 @@ class DataParallelEngine:
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._reduced = False
         self._manual_step = False    # this step's gradient reduction was started by an optimizer / clipping hook
+        self._expose_queued = False  # an end-of-backward callback is already queued for the running backward pass
         self._scale_pending = False  # a clip factor was computed and not yet multiplied into whole gradients
         self._reduce_work: dict[int, object] = {}  # group index -> in-flight gradient reduction
         self._gather_work: dict[int, object] = {}  # group index -> in-flight parameter publication
@@ -141,7 +142,25 @@ class DataParallelEngine:
             if work is not None:
                 work.wait()
 
+    def queue_expose_flat_grads(self) -> None:
+        """Called from inside a backward pass: when the pass ends, parameters whose gradient a fused node wrote straight
+        into the flat buffer (autograd saw ``None`` for them) show that slot as ``.grad``, so code that looks at
+        gradients between ``backward()`` and ``step()`` finds them where it expects them."""
+        if not self._expose_queued:
+            self._expose_queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._expose_flat_grads)
+
+    def _expose_flat_grads(self) -> None:
+        self._expose_queued = False
+        for g in self.groups:
+            if getattr(g, "sharded", False):
+                continue          # slots of sharded units live in a staging buffer that the next block reuses
+            for p in g.params:
+                if p.grad is None and getattr(p, "_kf_grad_live", False):
+                    p.grad = p._kf_grad
+
     def _block_backward_done(self, idxs) -> None:
+        self.queue_expose_flat_grads()
         if not (self.world > 1 and self.requires_sync):
             return None
         for i in idxs:
@@ -449,6 +468,7 @@ class DataParallelEngine:
                 if getattr(p, "_kf_tp_synced", False):
                     p._kf_tp_synced = False
         self._reduced = False
+        self._expose_queued = False
 
     # ------------------------------------------------------------------ checkpoint helpers
     def full_optimizer_state(self, g: FlatParamGroup) -> tuple[torch.Tensor, torch.Tensor]:

@@ -828,6 +828,10 @@ def test_a_hand_written_loop_on_the_gpu_trains_like_the_trainer(native_lib, opt_
     for _ in range(8):
         loss = loss_fn(model(ids), labels)
         loss.backward()
+        # gradients that fused nodes wrote into the flat buffers are visible as ``.grad`` once backward has returned
+        missing = [n for n, p in model.named_parameters() if p.requires_grad and p.grad is None]
+        assert not missing, missing
+        assert all(bool(torch.isfinite(p.grad.float()).all()) for p in model.parameters())
         clip_grad_norm_(model, 1.0)
         opt.step()
         opt.zero_grad()

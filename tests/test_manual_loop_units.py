@@ -189,3 +189,27 @@ def test_a_plain_loop_on_two_ranks_trains_like_the_trainer(opt_name):
             assert torch.allclose(got_params[n], want_params[n], atol=1e-7), n
     for n in results[0][3]:                                   # and the ranks agree with each other
         assert torch.equal(results[0][3][n], results[1][3][n]), n
+
+
+def test_gradients_written_into_the_flat_buffers_show_up_as_grad_after_backward():
+    """On a GPU the fused nodes hand ``None`` to autograd and write weight gradients into the flat buffer; the engine's
+    end-of-backward callback must then present those slots as ``.grad``.  Here the deposit is imitated on the CPU."""
+    from kempnerforge_b200.distributed import build_parallel_model
+
+    cfg = _job("adamw")
+    model = build_parallel_model(cfg.model, torch.device("cpu"), None, param_dtype=torch.float32)
+    engine = model._kf_engine
+    b = _batches(1)[0]
+    model(b["input_ids"]).float().mean().backward()      # the block hooks queue the callback during this pass
+    assert not engine._expose_queued and all(p.grad is not None for p in model.parameters())
+    name, p = next((n, q) for n, q in model.named_parameters() if n.endswith("q_proj.weight"))
+    other = next(q for n, q in model.named_parameters() if n.endswith("k_proj.weight"))
+    kept = other.grad
+    p.grad = None                                         # what a fused node leaves behind: no autograd gradient,
+    p._kf_grad.fill_(2.0)                                 # the value in the flat slot,
+    p._kf_grad_live = True                                # and the slot marked as written
+    engine._expose_flat_grads()
+    assert p.grad is not None and p.grad.data_ptr() == p._kf_grad.data_ptr() and float(p.grad.mean()) == 2.0, name
+    assert other.grad is kept                             # gradients that autograd produced are left alone
+    model._kf_engine.zero_grad()
+    assert all(q.grad is None for q in model.parameters()) and not p._kf_grad_live
