@@ -80,6 +80,9 @@ class DataParallelEngine:
         if self.world > 1:
             self.broadcast_parameters()
             self._install_overlap_hooks()
+        # whatever the hooks above cover: a backward pass that starts from the model's output ends by presenting the
+        # flat gradient slots as ``.grad`` (see queue_expose_flat_grads)
+        self._aux_handles = [model.register_forward_hook(self._attach_expose)]
 
     # ------------------------------------------------------------------ set-up
     def broadcast_parameters(self, src: int = 0) -> None:
@@ -142,6 +145,11 @@ class DataParallelEngine:
             if work is not None:
                 work.wait()
 
+    def _attach_expose(self, module, args, output) -> None:
+        out = output[0] if isinstance(output, (tuple, list)) and output else output
+        if torch.is_tensor(out) and out.requires_grad and torch.is_grad_enabled():
+            out.register_hook(lambda grad: self.queue_expose_flat_grads())
+
     def queue_expose_flat_grads(self) -> None:
         """Called from inside a backward pass: when the pass ends, parameters whose gradient a fused node wrote straight
         into the flat buffer (autograd saw ``None`` for them) show that slot as ``.grad``, so code that looks at
@@ -156,8 +164,14 @@ class DataParallelEngine:
             if getattr(g, "sharded", False):
                 continue          # slots of sharded units live in a staging buffer that the next block reuses
             for p in g.params:
-                if p.grad is None and getattr(p, "_kf_grad_live", False):
-                    p.grad = p._kf_grad
+                if p.grad is not None or not p.requires_grad:
+                    continue
+                if not getattr(p, "_kf_grad_live", False):
+                    # nothing reached this parameter in the pass (an unused branch): the optimizer's flat update
+                    # treats it as a zero gradient, so that is what ``.grad`` shows
+                    p._kf_grad.zero_()
+                    p._kf_grad_live = True
+                p.grad = p._kf_grad
 
     def _block_backward_done(self, idxs) -> None:
         self.queue_expose_flat_grads()
@@ -437,9 +451,10 @@ class DataParallelEngine:
         """Detach from the model (before another engine is built over a changed set of trainable parameters):
         drains communication, removes hooks and wrappers, and gives every parameter storage of its own."""
         self.wait_all()
-        for h in self._handles:
+        for h in self._handles + getattr(self, "_aux_handles", []):
             h.remove()
         self._handles.clear()
+        self._aux_handles = []
         for name in self._wrapped:
             self.model.__dict__.pop(name, None)
         self._wrapped.clear()

@@ -213,3 +213,24 @@ def test_gradients_written_into_the_flat_buffers_show_up_as_grad_after_backward(
     assert other.grad is kept                             # gradients that autograd produced are left alone
     model._kf_engine.zero_grad()
     assert all(q.grad is None for q in model.parameters()) and not p._kf_grad_live
+
+
+def test_a_trainable_parameter_no_node_reached_shows_a_zero_gradient():
+    """The flat optimizer update treats a parameter without a gradient as a zero gradient (weight decay still applies);
+    ``.grad`` says the same instead of staying ``None``."""
+    from torch import nn
+
+    from kempnerforge_b200.config import ModelConfig
+    from kempnerforge_b200.models import Transformer
+    from kempnerforge_b200.parallel.parallel import apply_fsdp2
+
+    model = Transformer(ModelConfig(**MODEL))
+    model.unused = nn.Parameter(torch.ones(8))           # takes no part in the forward pass
+    apply_fsdp2(model, None)
+    b = _batches(1)[0]
+    model(b["input_ids"]).float().mean().backward()
+    assert model.unused.grad is not None and float(model.unused.grad.abs().max()) == 0.0
+    assert float(model.layers["0"].attention.q_proj.weight.grad.abs().max()) > 0.0
+    with torch.no_grad():                                # no graph, no hook, nothing queued
+        model(b["input_ids"])
+    assert not model._kf_engine._expose_queued
