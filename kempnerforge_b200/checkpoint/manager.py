@@ -429,6 +429,10 @@ class CheckpointManager:
             # collectives DCP issues from its background thread on the default group
             self._sync_group = dist.new_group(backend="gloo")
         self._saver = AsyncCheckpointer(str(config.async_mode), process_group)
+        if self._saver.is_async and self._dist and dist.get_world_size() > 1 and process_group is None:
+            # the background flush exchanges its plans through collectives of its own: on the default group they would
+            # run concurrently with the training step's (and this manager's) collectives issued by the main thread
+            self._saver.process_group = dist.new_group(backend="gloo")
         self._pending_finalize: tuple[Path, int] | None = None
         self._stashed_dataloader_state: dict | None = None
 
@@ -468,6 +472,8 @@ class CheckpointManager:
         step_dir = self.step_dir(step)
         dcp_dir = self._dcp_dir(step_dir)
         dcp_dir.mkdir(parents=True, exist_ok=True)
+        # the previous flush must be over before this save issues collectives of its own (gathering sharded moments)
+        self._saver.wait()
         # an optimizer that has not stepped yet (a save at step 0) gets its zero state first, so that every checkpoint
         # carries the full set of keys a later load asks for
         materialize_optimizer_state(self.model, self.optimizer)

@@ -481,3 +481,41 @@ def test_tensor_parallel_times_data_parallel_matches_single_process():
         assert _params_close(full, want), name
         # the second TP group holds the same weights as the first
         assert torch.equal(results[2][1][name][0], t0), name
+
+
+def _async_ckpt_worker(rank, world, model_cfg, ckpt_dir):
+    """Back-to-back asynchronous saves with training steps (main-thread collectives) in between, no barrier from the
+    caller: the flush thread's own collectives must not meet the main thread's on one process group."""
+    from pathlib import Path
+
+    from kempnerforge_b200.training.trainer import Trainer
+
+    cfg = _job(model_cfg, {"dp_shard": world})
+    cfg.checkpoint.dir = ckpt_dir
+    cfg.checkpoint.async_mode = "async_with_pinned_mem"
+    cfg.checkpoint.keep_last_n = 3
+    t = Trainer(cfg)
+    t.setup_checkpointing()
+    data = _batches(world * 10)
+    latest = Path(ckpt_dir) / "latest"
+    durable = []
+    for s in range(1, 5):
+        t.train_step([data[(2 * s) * world + rank]])
+        t.step = s
+        t.save_checkpoint()
+        t.train_step([data[(2 * s + 1) * world + rank]])       # gradient reduction while the flush may still be running
+        if rank == 0 and latest.exists():
+            durable.append((latest.resolve() / ".metadata").exists())
+    t.ckpt.wait()
+    target = latest.resolve().name if rank == 0 else ""
+    params = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    step, _, _ = t.ckpt.load(scheduler=t.scheduler)
+    return durable, target, step, params
+
+
+def test_back_to_back_async_saves_between_training_steps_on_two_ranks(tmp_path):
+    results = run_ranks(_async_ckpt_worker, 2, TINY, str(tmp_path / "ck"))
+    durable, target, step, _ = results[0]
+    assert all(durable) and target == "step_4" and step == 4 and results[1][2] == 4
+    for n, p in results[0][3].items():               # the ranks kept training in lock-step throughout
+        assert torch.equal(p, results[1][3][n]), n
