@@ -565,7 +565,11 @@ class CheckpointManager:
             dist.broadcast_object_list(box, src=0, group=self._sync_group)
             step_dir, exists = (Path(box[0]), True) if box[0] else (None, False)
         if not exists:
-            log.info("no checkpoint found under %s; starting from scratch", self.dir)
+            asked = path or self.config.load_path
+            if asked:
+                log.warning("checkpoint path %s does not exist; starting from scratch", asked)
+            else:
+                log.info("no checkpoint found under %s; starting from scratch", self.dir)
             return 0, 0, {}
         exclude = set(exclude_keys or [])
         wants_tensors = not {"model", "optimizer"} <= exclude

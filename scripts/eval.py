@@ -37,6 +37,11 @@ def main(argv=None) -> int:
     model = build_parallel_model(cfg.model, device, mesh, ac_mode="none", param_dtype=cfg.train.param_dtype, fp8=False)
     dummy = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.0)
     mgr = CheckpointManager(cfg.checkpoint, model, dummy)
+    if mgr._resolve_load_path(None) is None:     # evaluating freshly initialised weights is never what was asked for
+        where = cfg.checkpoint.load_path or cfg.checkpoint.dir
+        print(f"error: no checkpoint found at {where!r}; set --checkpoint.load_path or --checkpoint.dir", file=sys.stderr)
+        destroy_distributed()
+        return 1
     step, tokens, _ = mgr.load(exclude_keys=["optimizer"])
     dp_rank, dp_size = get_dp_info(mesh)
     loader = build_eval_dataloader(cfg, dp_rank, dp_size)

@@ -223,3 +223,19 @@ dataset_weights = {{ web = 1.0, code = 3.0 }}
             assert 3.0 < float(value) < 8.0
         assert re.search(r"data/(web|code)/tokens=", line)
     assert seen == {"web", "code"}
+
+
+def test_the_evaluation_script_refuses_to_run_without_a_checkpoint(tmp_path):
+    """A mistyped ``--checkpoint.load_path`` must not end in metrics of freshly initialised weights."""
+    import numpy as np
+
+    data_dir = tmp_path / "eval_tokens"
+    data_dir.mkdir()
+    np.save(data_dir / "shard_0.npy", np.random.default_rng(0).integers(0, 256, size=2048, dtype=np.uint16))
+    ev = subprocess.run([sys.executable, os.path.join(ROOT, "scripts", "eval.py"),
+                         os.path.join(ROOT, "configs", "train", "debug.toml"), *TINY,
+                         f"--checkpoint.load_path={tmp_path / 'no_such_run' / 'step_10'}",
+                         f"--eval.dataset_path={data_dir}", "--eval.steps=1"],
+                        capture_output=True, text=True, env=_env(), timeout=600, cwd=ROOT)
+    assert ev.returncode == 1, ev.stdout[-1000:] + ev.stderr[-1000:]
+    assert "no checkpoint found" in ev.stderr and "eval/loss" not in ev.stdout
