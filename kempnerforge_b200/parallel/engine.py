@@ -359,6 +359,8 @@ class DataParallelEngine:
         fused = bool(getattr(optimizer, "_flat_groups", None))
         if fused:
             optimizer.grad_scale = self.grad_scale
+        else:
+            self.full_grads = True    # it steps on whole parameters: every rank needs the whole averaged gradient
 
         def before(_opt, _args, _kwargs):
             if not self._reduced:

@@ -234,3 +234,52 @@ def test_a_trainable_parameter_no_node_reached_shows_a_zero_gradient():
     with torch.no_grad():                                # no graph, no hook, nothing queued
         model(b["input_ids"])
     assert not model._kf_engine._expose_queued
+
+
+def _hand_built_optimizer_entry(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), CUDA_VISIBLE_DEVICES="")
+    torch.set_num_threads(1)
+    try:
+        from kempnerforge_b200.distributed import build_parallel_model
+        from kempnerforge_b200.parallel.setup import init_distributed
+        from kempnerforge_b200.training.loss import build_loss_fn
+
+        cfg, init = _job("adamw", world), _init_weights()
+        mesh = init_distributed(cfg.distributed, seed=0)
+        model = build_parallel_model(cfg.model, torch.device("cpu"), mesh, param_dtype=torch.float32)
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                p.copy_(init[n])
+        opt = torch.optim.SGD(model.parameters(), lr=0.1)       # not from build_optimizer
+        model._kf_engine.bind_optimizer(opt)
+        loss_fn = build_loss_fn(cfg.train)
+        for b in _batches(2 * world)[rank::world]:              # every rank sees different data
+            loss_fn(model(b["input_ids"]), b["labels"]).backward()
+            opt.step()
+            opt.zero_grad()
+        torch.save({n: p.detach().clone() for n, p in model.named_parameters()}, os.path.join(out_dir, f"r{rank}.pt"))
+    except Exception:
+        with open(os.path.join(out_dir, f"err{rank}.txt"), "w") as fh:
+            fh.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_a_hand_built_optimizer_bound_to_the_engine_keeps_the_ranks_in_step():
+    """A whole-parameter optimizer needs the whole averaged gradient on every rank, not only the local shard of the
+    reduce-scatter: after two steps on different data the ranks must hold identical, changed weights."""
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_hand_built_optimizer_entry, args=(world, port, d), nprocs=world, join=True)
+        errs = [open(os.path.join(d, f)).read() for f in sorted(os.listdir(d)) if f.startswith("err")]
+        assert not errs, "\n".join(errs)
+        a, b = (torch.load(os.path.join(d, f"r{r}.pt")) for r in range(world))
+    init = _init_weights()
+    for n in a:
+        assert torch.equal(a[n], b[n]), n
+        assert not torch.equal(a[n], init[n]), n
